@@ -1,0 +1,122 @@
+"""The CPU oracle against the fixtures produced by the reference's own PyTorch code."""
+
+import os
+
+import numpy as np
+import pytest
+
+from oracle import mxfp8_oracle as orc
+
+
+def _load(golden_dir, name):
+    return np.load(os.path.join(golden_dir, name))
+
+
+def test_sf_layout_matches_reference(golden_dir):
+    g = _load(golden_dir, "sf_layout.npz")
+    vals = g["values"]  # [L, MN, KB]
+    l, mn, kb = vals.shape
+    assert tuple(g["shape"]) == (32, 4, orc.ceil_div(mn, 128), 4, orc.ceil_div(kb, 4), l)
+    rm, rk = orc.sf_rest(mn, int(g["k"]))
+    assert tuple(g["stride"]) == (16, 4, rk * 512, 1, 512, rm * rk * 512)
+    packed = orc.sf_pack(vals)
+    assert packed.shape == g["flat"].shape
+    np.testing.assert_array_equal(packed, g["flat"])
+    np.testing.assert_array_equal(orc.sf_unpack(g["flat"], mn, kb, l), vals)
+    assert orc.sf_nbytes(mn, int(g["k"]), l) == packed.size
+
+
+def test_offsets_match_reference(golden_dir):
+    g = _load(golden_dir, "offsets.npz")
+    valid_m, aligned, offs = orc.padded_end_offsets(g["groups"].tolist(), 256)
+    assert valid_m == int(g["valid_m"])
+    assert aligned == g["aligned"].tolist()
+    assert offs.dtype == np.int32
+    np.testing.assert_array_equal(offs, g["offsets"])
+
+
+def test_fc1_matches_reference(golden_dir):
+    g = _load(golden_dir, "fc1_swiglu.npz")
+    out = orc.fc1_reference(g["a"], g["sfa"], g["b"], g["sfb"], g["offsets"], g["alpha"], g["prob"])
+    # same float32 maths, only the summation order of the matmul may differ
+    np.testing.assert_allclose(out["c"], g["c_ref"], rtol=1e-5, atol=1e-4)
+    np.testing.assert_allclose(out["d"], g["d_ref"], rtol=1e-4, atol=1e-3)
+    np.testing.assert_allclose(out["amax"], g["amax_ref"], rtol=1e-5)
+
+
+def test_fc2_matches_reference(golden_dir):
+    g = _load(golden_dir, "fc2_quant.npz")
+    out = orc.fc2_reference(g["a"], g["sfa"], g["b"], g["sfb"], g["offsets"], g["alpha"], g["prob"])
+    np.testing.assert_allclose(out["d"], g["d_ref"], rtol=1e-5, atol=1e-4)
+    assert out["amax"][2] == -np.inf  # empty expert keeps the initial value
+
+
+def test_e8m0_rounds_up_and_saturates():
+    x = np.array([0.0, 1.0, 1.0000001, 1.5, 2.0, 3.9, 2.0**-126, 2.0**-127, 1e-45, 3e38, np.inf], dtype=np.float32)
+    b = orc.e8m0_encode(x)
+    assert b.tolist() == [0, 127, 128, 128, 128, 129, 1, 0, 0, 0xFE, 0xFE]
+    assert orc.e8m0_encode(np.array([np.nan], dtype=np.float32))[0] == 0xFF
+    dec = orc.e8m0_decode(np.array([0, 1, 127, 128, 254], dtype=np.uint8))
+    assert dec.tolist() == [2.0**-127, 2.0**-126, 1.0, 2.0, 2.0**127]
+    # decoded scale is never below the encoded magnitude
+    r = np.random.default_rng(0).uniform(0, 1e3, 10000).astype(np.float32)
+    assert (orc.e8m0_decode(orc.e8m0_encode(r)) >= r).all()
+
+
+def test_e4m3_saturates_and_rounds_to_nearest_even():
+    x = np.array([0.0, 448.0, 449.0, 1e9, -1e9, 17.0, 19.0, 2.0**-9, 2.0**-10], dtype=np.float32)
+    d = orc.e4m3_decode(orc.e4m3_encode(x))
+    assert d.tolist() == [0.0, 448.0, 448.0, 448.0, -448.0, 16.0, 20.0, 2.0**-9, 0.0]
+    assert orc.e4m3_ulp_distance(orc.e4m3_encode(np.float32([1.0])), orc.e4m3_encode(np.float32([1.125])))[0] == 1
+
+
+@pytest.mark.parametrize("norm", [1.0, 0.01])
+def test_row_quantisation_never_overflows_and_round_trips(norm):
+    r = np.random.default_rng(1)
+    x = (r.standard_normal((64, 160)) * np.exp(r.uniform(-8, 8, (64, 1)))).astype(np.float32)
+    x[3] = 0.0
+    d, sf = orc.quantize_rows(x, norm)
+    assert sf.shape == (64, 5)
+    assert (np.abs(orc.e4m3_decode(d)) <= 448).all()
+    back = orc.dequantize_rows(d, sf, norm)
+    blk = np.abs(x).reshape(64, 5, 32).max(axis=2).repeat(32, axis=1)
+    # error per element is at most half an E4M3 step of the block maximum (2^-3 relative)
+    assert (np.abs(back - x) <= blk * 2.0**-3 + 1e-30).all()
+    assert (d[3] == 0).all()
+
+
+def test_col_quantisation_is_row_quantisation_of_the_transpose():
+    r = np.random.default_rng(2)
+    x = r.standard_normal((128, 64)).astype(np.float32)
+    d, sf = orc.quantize_cols(x, 1.0)
+    d_t, sf_t = orc.quantize_rows(x.T.copy(), 1.0)
+    np.testing.assert_array_equal(d, d_t.T)
+    np.testing.assert_array_equal(sf, sf_t)
+    assert sf.shape == (64, 4)
+
+
+def test_route_rows_is_a_stable_grouping():
+    r = np.random.default_rng(3)
+    ids = r.integers(0, 7, 1000)
+    ids[ids == 4] = 5  # expert 4 empty
+    counts, offs, dst = orc.route_rows(ids, 7, 128)
+    assert counts.sum() == 1000 and counts[4] == 0
+    assert (offs % 128 == 0).all() and offs[4] == offs[3]
+    assert len(np.unique(dst)) == 1000
+    starts = offs - ((counts + 127) // 128) * 128
+    for e in range(7):
+        rows = dst[ids == e]
+        assert (np.diff(rows) == 1).all() if len(rows) > 1 else True
+        if len(rows):
+            assert rows[0] == starts[e] and rows[-1] < offs[e]
+
+
+def test_interleave_gate_up_layout():
+    g = np.arange(64 * 2, dtype=np.float32).reshape(64, 2)
+    u = -g
+    w = orc.interleave_gate_up(g, u)
+    assert w.shape == (128, 2)
+    np.testing.assert_array_equal(w[0:32], g[0:32])
+    np.testing.assert_array_equal(w[32:64], u[0:32])
+    np.testing.assert_array_equal(w[64:96], g[32:64])
+    np.testing.assert_array_equal(w[96:128], u[32:64])
