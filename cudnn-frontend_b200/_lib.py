@@ -1,0 +1,111 @@
+"""ctypes binding of libb200moe.so (declarations mirror include/b200moe.h).
+
+There is no fallback: if the library is missing the import of any operator fails loudly.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import POINTER, Structure, c_char_p, c_float, c_int32, c_int64, c_void_p
+
+from . import _build
+
+E_NULL, E_SHAPE, E_ALIGN, E_UNSUPPORTED, E_WORKSPACE, E_DEVICE = -1, -2, -3, -4, -5, -6
+DTYPE_BF16, DTYPE_E4M3 = 0, 1
+FLAG_DISCRETE_COL_SFD = 1
+
+
+class GemmArgs(Structure):
+    _fields_ = [
+        ("a", c_void_p),
+        ("sfa", c_void_p),
+        ("b", c_void_p),
+        ("sfb", c_void_p),
+        ("b_ptrs", c_void_p),
+        ("sfb_ptrs", c_void_p),
+        ("padded_offsets", c_void_p),
+        ("alpha", c_void_p),
+        ("prob", c_void_p),
+        ("norm_const", c_void_p),
+        ("c", c_void_p),
+        ("d", c_void_p),
+        ("d_col", c_void_p),
+        ("amax", c_void_p),
+        ("sfd_row", c_void_p),
+        ("sfd_col", c_void_p),
+        ("workspace", c_void_p),
+        ("workspace_bytes", c_int64),
+        ("m_rows", c_int64),
+        ("n", c_int64),
+        ("k", c_int64),
+        ("num_experts", c_int32),
+        ("d_dtype", c_int32),
+        ("flags", c_int32),
+        ("sm_margin", c_int32),
+    ]
+
+
+_SIGNATURES = {
+    "b200moe_fc1_swiglu": (ctypes.c_int, [POINTER(GemmArgs), c_void_p]),
+    "b200moe_fc2_quant": (ctypes.c_int, [POINTER(GemmArgs), c_void_p]),
+    "b200moe_workspace_bytes": (c_int64, [c_int32, c_int32]),
+    "b200moe_quantize_mxfp8": (ctypes.c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
+    "b200moe_route": (
+        ctypes.c_int,
+        [c_void_p, c_int64, c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+    ),
+    "b200moe_route_scratch_bytes": (c_int64, [c_int64, c_int32]),
+    "b200moe_zero_pad_rows": (ctypes.c_int, [c_void_p, c_void_p, c_void_p, c_int32, c_int64, c_void_p, c_void_p]),
+    "b200moe_scatter_rows": (
+        ctypes.c_int,
+        [c_void_p, c_void_p, c_int64, c_int32, c_int64, c_void_p, c_void_p, c_void_p, c_void_p],
+    ),
+    "b200moe_combine_rows": (ctypes.c_int, [c_void_p, c_void_p, c_int64, c_int32, c_int64, c_void_p, c_void_p]),
+    "b200moe_last_error": (c_char_p, []),
+    "b200moe_device_status": (ctypes.c_int, [ctypes.c_int]),
+    "b200moe_abi_version": (ctypes.c_int, []),
+}
+
+EXPORTED_SYMBOLS = tuple(_SIGNATURES)
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    """Load (building first when nvcc is present and the library is stale) and type the library."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = _build.LIB_PATH
+    if _build.is_stale():
+        try:
+            _build.build()
+        except RuntimeError:
+            if not os.path.exists(path):
+                raise
+    if not os.path.exists(path):
+        raise RuntimeError(f"{path} is missing: build it with `python -m cudnn_frontend_b200._build` (needs nvcc)")
+    lib = ctypes.CDLL(path)
+    for name, (restype, argtypes) in _SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = restype
+        fn.argtypes = argtypes
+    _lib = lib
+    return lib
+
+
+def last_error() -> str:
+    return load().b200moe_last_error().decode()
+
+
+def check(rc: int) -> None:
+    """Map a C-ABI status to the exception type the reference raises for that class of error."""
+    if rc == 0:
+        return
+    msg = last_error() or f"libb200moe error {rc}"
+    if rc == E_UNSUPPORTED:
+        raise NotImplementedError(msg)
+    if rc < 0 and rc != E_DEVICE:
+        raise ValueError(msg)
+    raise RuntimeError(msg)

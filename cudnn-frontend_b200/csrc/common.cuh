@@ -1,0 +1,320 @@
+// Shared device helpers: PTX wrappers for mbarrier, TMA, tcgen05 (sm_100a) and number formats.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace b200moe {
+
+// ---------------------------------------------------------------------------------------
+// Host-side error plumbing (thread-local text, int status codes across the C ABI)
+// ---------------------------------------------------------------------------------------
+void set_error(const char* fmt, ...);
+int fail(int code, const char* fmt, ...);
+
+#define B200_CUDA_CHECK(expr)                                                        \
+  do {                                                                               \
+    cudaError_t _e = (expr);                                                         \
+    if (_e != cudaSuccess) {                                                         \
+      return ::b200moe::fail((int)_e, "%s failed: %s", #expr, cudaGetErrorString(_e)); \
+    }                                                                                \
+  } while (0)
+
+// Device status word: first bounded wait that gave up records its code here.  The library is
+// built as one translation unit (b200moe.cu includes every kernel file), so this is the single
+// definition.
+__device__ int g_device_status = 0;
+
+// ---------------------------------------------------------------------------------------
+// Small utilities
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+__device__ __forceinline__ uint32_t lane_id() { return threadIdx.x & 31; }
+
+// ---------------------------------------------------------------------------------------
+// mbarrier
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void fence_mbar_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+__device__ __forceinline__ void fence_proxy_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done;
+}
+
+// Bounded wait.  Spins on the barrier phase; after kWaitLimitNs without progress it records
+// `code` in the device status word, raises the CTA's abort flag and returns false so the
+// caller can leave its loop and fall through to the kernel's teardown.  A raised abort flag
+// makes every other waiter of the CTA give up quickly as well.
+constexpr uint64_t kWaitLimitNs = 4000000000ull;  // 4 s: far above any legitimate wait
+
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int code) {
+#pragma unroll 1
+  for (int i = 0; i < 128; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+  }
+  const uint64_t t0 = global_timer_ns();
+#pragma unroll 1
+  while (true) {
+#pragma unroll 1
+    for (int i = 0; i < 256; ++i) {
+      if (mbar_try_wait(bar, parity)) return true;
+    }
+    if (*abort_flag) return false;
+    if (global_timer_ns() - t0 > kWaitLimitNs) {
+      atomicCAS(&g_device_status, 0, code);
+      *abort_flag = 1;
+      return false;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// TMA (bulk tensor loads into this CTA's shared memory; no cluster multicast anywhere)
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, uint32_t bar, int c0,
+                                            int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, "
+      "{%3, %4}], [%2];" ::"r"(dst),
+      "l"(tmap), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* tmap, uint32_t bar, int c0,
+                                            int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, "
+      "{%3, %4, %5}], [%2];" ::"r"(dst),
+      "l"(tmap), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+
+// Untiled bulk copy global -> shared (16-byte aligned addresses, size multiple of 16).
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes,
+                                          uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
+          "r"(dst),
+      "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+
+__device__ __forceinline__ void tensormap_fence_acquire(const void* tmap) {
+  asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;" ::"l"(tmap) : "memory");
+}
+
+__device__ __forceinline__ void prefetch_tensormap(const void* tmap) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
+}
+
+// ---------------------------------------------------------------------------------------
+// tcgen05 (5th-generation tensor cores, TMEM)
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Arrive on an mbarrier of this CTA once every tcgen05 operation issued so far by this
+// thread has completed.
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   bar)
+               : "memory");
+}
+
+// Shared-memory matrix descriptor (sm_100 format, version 1).
+//   bits [0,14)  start address >> 4      bits [16,30) leading byte offset >> 4
+//   bits [32,46) stride byte offset >> 4 bits [46,48) version = 1
+//   bits [61,64) swizzle mode: 0 none, 2 = 128-byte, 4 = 64-byte, 6 = 32-byte
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes,
+                                                   uint32_t sbo_bytes, uint32_t swizzle) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3FFF);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)swizzle << 61;
+  return d;
+}
+
+// Instruction descriptor of tcgen05.mma.kind::mxf8f6f4.block_scale, E4M3 x E4M3 (K-major
+// both), E8M0 scales, f32 accumulate.
+//   [4,6) B scale id  [7,10) A format (0 = E4M3)  [10,13) B format  [15] A major  [16] B major
+//   [17,23) N >> 3    [23] scale format (1 = E8M0) [24,29) M >> 4   [29,31) A scale id
+__host__ __device__ constexpr uint32_t make_idesc_mxf8(int m, int n) {
+  return ((uint32_t)(n >> 3) << 17) | (1u << 23) | ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ uint32_t idesc_with_sf_id(uint32_t idesc, uint32_t a_id, uint32_t b_id) {
+  return idesc | (a_id << 29) | (b_id << 4);
+}
+
+__device__ __forceinline__ void mma_mxf8_ss(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                            uint32_t idesc, uint32_t tmem_sfa, uint32_t tmem_sfb,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t"
+      "}" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
+      : "memory");
+}
+
+// Copy 32 rows x 16 bytes of shared memory into TMEM columns [taddr, taddr+4), replicated
+// into the four 32-lane quarters (the scale-factor operand format of block-scaled MMA).
+__device__ __forceinline__ void tmem_cp_sf(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc)
+               : "memory");
+}
+
+// 32 lanes x 32 consecutive 32-bit columns -> 32 registers per thread (thread = lane).
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, float* v) {
+  uint32_t* r = reinterpret_cast<uint32_t*>(v);
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+
+// Compiler-level fence on 32 registers: makes every later use of v[] depend on this point, so
+// arithmetic on the results of an asynchronous tcgen05.ld cannot be scheduled above the
+// tcgen05.wait::ld that precedes this call.
+__device__ __forceinline__ void reg_fence32(float* v) {
+  asm volatile(""
+               : "+f"(v[0]), "+f"(v[1]), "+f"(v[2]), "+f"(v[3]), "+f"(v[4]), "+f"(v[5]), "+f"(v[6]), "+f"(v[7]),
+                 "+f"(v[8]), "+f"(v[9]), "+f"(v[10]), "+f"(v[11]), "+f"(v[12]), "+f"(v[13]), "+f"(v[14]),
+                 "+f"(v[15]), "+f"(v[16]), "+f"(v[17]), "+f"(v[18]), "+f"(v[19]), "+f"(v[20]), "+f"(v[21]),
+                 "+f"(v[22]), "+f"(v[23]), "+f"(v[24]), "+f"(v[25]), "+f"(v[26]), "+f"(v[27]), "+f"(v[28]),
+                 "+f"(v[29]), "+f"(v[30]), "+f"(v[31])::"memory");
+}
+
+// ---------------------------------------------------------------------------------------
+// Number formats and fast math (the reference kernel's arithmetic,
+// python/cudnn/grouped_gemm/utils.py:157-309, grouped_gemm_swiglu_quant.py:1067-1188)
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ float rcp_approx(float x) {
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+__device__ __forceinline__ float fmin_nan(float a, float b) {
+  float r;
+  asm("min.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+  return r;
+}
+// max |x| over the 32 lanes of the warp
+__device__ __forceinline__ float warp_absmax(float x) {
+  float r;
+  asm volatile("redux.sync.max.abs.NaN.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(x));
+  return r;
+}
+
+// float32 (>= 0) -> E8M0 byte: round up to a power of two, saturate to finite.
+__device__ __forceinline__ uint32_t e8m0_from_float(float x) {
+  uint16_t out;
+  asm("cvt.rp.satfinite.ue8m0x2.f32 %0, 0f00000000, %1;" : "=h"(out) : "f"(x));
+  return (uint32_t)(out & 0xFF);
+}
+// E8M0 byte -> float32 (2^(b-127); byte 0 = 2^-127 as a float32 denormal)
+__device__ __forceinline__ float e8m0_to_float(uint32_t b) {
+  return __uint_as_float(b == 0 ? 0x00400000u : (b << 23));
+}
+// two float32 -> packed E4M3 pair (lo in bits 0-7, hi in bits 8-15), RNE, saturating
+__device__ __forceinline__ uint32_t e4m3x2_from_float(float lo, float hi) {
+  uint16_t out;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(out) : "f"(hi), "f"(lo));
+  return (uint32_t)out;
+}
+__device__ __forceinline__ uint32_t e4m3x4_from_float(float a, float b, float c, float d) {
+  return e4m3x2_from_float(a, b) | (e4m3x2_from_float(c, d) << 16);
+}
+__device__ __forceinline__ uint32_t bf16x2_from_float(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Scale applied to a block before the E4M3 conversion: norm / sf, clamped to FLT_MAX.
+__device__ __forceinline__ float quant_scale(float norm_const, float sf_value) {
+  return fmin_nan(norm_const * rcp_approx(sf_value), 3.40282346638528859812e38f);
+}
+
+// Byte offset of the scale of row `mn`, K block `kb` in the "128x4" layout
+// (32 x 4 x rest_mn x 4 x rest_k; test/python/fe_api/test_fe_api_utils.py:95-114).
+__host__ __device__ __forceinline__ int64_t sf_offset(int64_t mn, int64_t kb, int64_t rest_k) {
+  return (mn % 32) * 16 + ((mn / 32) % 4) * 4 + (kb % 4) + (kb / 4) * 512 +
+         (mn / 128) * rest_k * 512;
+}
+
+}  // namespace b200moe

@@ -1,0 +1,798 @@
+// Block-scaled MXFP8 grouped GEMM for MoE experts with fused epilogues (sm_100a).
+//
+//   FC1: C = alpha_e (A SFA)(B_e SFB_e)^T ; D = up * silu(gate) * prob   (gate/up = even/odd
+//        32-column blocks of C) ; per-expert amax, or row / column MXFP8 re-quantisation.
+//   FC2: D = alpha_e acc * prob ; bf16 + amax, or E4M3 + row / column E8M0 scale factors.
+//
+// One persistent CTA per SM walks a static tile schedule derived on the device from the
+// per-expert END offsets.  Warp roles:
+//   warp 0      producer: TMA loads of the A / B tiles (128-byte swizzle) and untiled bulk
+//               copies of the 512-byte scale-factor chunks into a 4-stage shared-memory ring
+//   warp 1      TMEM owner and MMA issuer: tcgen05.cp moves the scale factors to TMEM, then
+//               tcgen05.mma.kind::mxf8f6f4.block_scale (128 x 256 x 32) accumulates into TMEM
+//   warps 2..9  epilogue: tcgen05.ld, alpha / SwiGLU / prob / amax / re-quantisation, stores
+//
+// TMEM (512 columns): accumulator 0 at columns [0,256), accumulator 1 at [224,480), scale
+// factors at [480,512).  The two accumulators share 32 columns; the epilogue drains those
+// first (even tiles from the top, odd tiles from the bottom) and then lets the MMA warp start
+// the next tile while it finishes the rest.
+//
+// No cluster launch and no multicast: every CTA loads what it needs into its own shared
+// memory, so the same binary serves single- and multi-GPU processes.
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <mutex>
+
+#include "b200moe.h"
+#include "common.cuh"
+
+namespace b200moe {
+
+// ---------------------------------------------------------------------------------------
+// Tile configuration
+// ---------------------------------------------------------------------------------------
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 128;  // bytes == elements (E4M3); one 128-byte swizzle row
+constexpr int STAGES = 4;
+constexpr int A_STAGE_BYTES = BM * BK;  // 16 KiB
+constexpr int B_STAGE_BYTES = BN * BK;  // 32 KiB
+constexpr int SFA_STAGE_BYTES = 512;
+constexpr int SFB_STAGE_BYTES = 1024;
+constexpr int NUM_EPI_WARPS = 8;
+constexpr int NUM_THREADS = (2 + NUM_EPI_WARPS) * 32;
+constexpr int MAX_EXPERTS = 1024;
+constexpr int RASTER_GROUP_M = 8;  // M tiles of one expert that share a B tile back to back
+
+constexpr int TMEM_COLS = 512;
+constexpr int TMEM_ACC1_COL = 224;
+constexpr int TMEM_SF_COL = 480;  // per SF buffer i: SFA at +16 i (4 cols), SFB at +16 i + 4 (8 cols)
+
+// status codes recorded by bounded waits
+constexpr int ST_PRODUCER_EMPTY = 101;
+constexpr int ST_MMA_FULL = 102;
+constexpr int ST_MMA_OVERLAP = 103;
+constexpr int ST_EPI_ACC = 104;
+
+struct SmemLayout {
+  static constexpr int A_OFF = 0;
+  static constexpr int B_OFF = A_OFF + STAGES * A_STAGE_BYTES;
+  static constexpr int SFA_OFF = B_OFF + STAGES * B_STAGE_BYTES;
+  static constexpr int SFB_OFF = SFA_OFF + STAGES * SFA_STAGE_BYTES;
+  static constexpr int BAR_OFF = SFB_OFF + STAGES * SFB_STAGE_BYTES;  // 8-byte barriers
+  static constexpr int NUM_BARS = 2 * STAGES + 2 + 1;
+  static constexpr int MISC_OFF = BAR_OFF + NUM_BARS * 8;  // tmem ptr, abort flag, total tiles
+  static constexpr int PREFIX_OFF = MISC_OFF + 16;         // (E + 1) int32 tile prefix
+  static constexpr int TOTAL = PREFIX_OFF + (MAX_EXPERTS + 1) * 4;
+};
+constexpr int SMEM_BYTES = SmemLayout::TOTAL + 1024;  // slack for manual 1024-byte alignment
+static_assert(SMEM_BYTES <= 232448, "shared memory budget exceeded");
+
+enum : int { EPI_FC1 = 0, EPI_FC2 = 1 };
+
+struct GemmParams {
+  const uint8_t* sfa;
+  const uint8_t* sfb;         // dense: expert e at sfb + e * sfb_expert_bytes
+  const int64_t* sfb_ptrs;    // discrete
+  const CUtensorMap* b_maps;  // discrete: E tensor maps in the workspace
+  const int32_t* offsets;
+  const float* alpha;
+  const float* prob;
+  const float* norm_const;
+  __nv_bfloat16* c;
+  void* d;
+  uint8_t* d_col;
+  float* amax;
+  uint8_t* sfd_row;
+  uint8_t* sfd_col;
+  int64_t sfb_expert_bytes;
+  int m_rows, n, k, num_experts;
+  int n_out;           // n / 2 (FC1) or n (FC2)
+  int n_tiles;         // ceil(n / 256)
+  int k_tiles;         // ceil(k / 128)
+  int rest_k;          // ceil(ceil(k / 32) / 4): K groups of SFA / SFB
+  int n_blocks;        // ceil(n / 128): 128-row blocks of SFB
+  int sfd_row_rest_k;  // ceil(ceil(n_out / 32) / 4)
+  int sfd_col_rest_k;  // ceil(ceil(m_rows / 32) / 4)
+  int d_is_fp8;
+  int discrete_col_sfd;
+};
+
+// ---------------------------------------------------------------------------------------
+// Tile schedule.  Expert e owns tiles [prefix[e], prefix[e+1]); inside an expert tiles run
+// in groups of RASTER_GROUP_M row tiles, row tile fastest, so that CTAs working on adjacent
+// schedule slots read the same B tile (L2 reuse) and every B tile of a small expert is
+// fetched from HBM once.
+// ---------------------------------------------------------------------------------------
+struct Tile {
+  int expert, row0, n_tile;
+};
+
+__device__ __forceinline__ Tile decode_tile(const int* prefix, const int32_t* offsets, int num_experts,
+                                            int n_tiles, int t) {
+  int lo = 0, hi = num_experts;  // find e with prefix[e] <= t < prefix[e + 1]
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (prefix[mid] <= t) lo = mid; else hi = mid;
+  }
+  const int e = lo;
+  const int j = t - prefix[e];
+  const int m_tiles = (prefix[e + 1] - prefix[e]) / n_tiles;
+  const int per_group = RASTER_GROUP_M * n_tiles;
+  const int g = j / per_group;
+  const int first_m = g * RASTER_GROUP_M;
+  const int gsize = min(RASTER_GROUP_M, m_tiles - first_m);
+  const int jj = j - g * per_group;
+  Tile tile;
+  tile.expert = e;
+  tile.n_tile = jj / gsize;
+  const int start = e == 0 ? 0 : offsets[e - 1];
+  tile.row0 = start + (first_m + jj % gsize) * BM;
+  return tile;
+}
+
+// ---------------------------------------------------------------------------------------
+// Epilogue helpers.  A thread owns one row of the tile; `v` holds 32 consecutive output
+// columns of that row in float32.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void store_bf16x32(__nv_bfloat16* dst, const float* v) {
+  uint4* p = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint4 o;
+    o.x = bf16x2_from_float(v[8 * i + 0], v[8 * i + 1]);
+    o.y = bf16x2_from_float(v[8 * i + 2], v[8 * i + 3]);
+    o.z = bf16x2_from_float(v[8 * i + 4], v[8 * i + 5]);
+    o.w = bf16x2_from_float(v[8 * i + 6], v[8 * i + 7]);
+    p[i] = o;
+  }
+}
+
+__device__ __forceinline__ void store_e4m3x32(uint8_t* dst, const float* v, float scale) {
+  uint4* p = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    uint4 o;
+    o.x = e4m3x4_from_float(v[16 * i + 0] * scale, v[16 * i + 1] * scale, v[16 * i + 2] * scale, v[16 * i + 3] * scale);
+    o.y = e4m3x4_from_float(v[16 * i + 4] * scale, v[16 * i + 5] * scale, v[16 * i + 6] * scale, v[16 * i + 7] * scale);
+    o.z = e4m3x4_from_float(v[16 * i + 8] * scale, v[16 * i + 9] * scale, v[16 * i + 10] * scale, v[16 * i + 11] * scale);
+    o.w = e4m3x4_from_float(v[16 * i + 12] * scale, v[16 * i + 13] * scale, v[16 * i + 14] * scale, v[16 * i + 15] * scale);
+    p[i] = o;
+  }
+}
+
+// Row-wise MXFP8 of one 32-element block: returns the E8M0 byte, stores 32 E4M3 bytes.
+__device__ __forceinline__ uint32_t quant_row_block(uint8_t* dst, const float* v, float norm_const) {
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(v[i]));
+  const float pv = amax * (1.0f / 448.0f) * norm_const;
+  const uint32_t sf = e8m0_from_float(pv);
+  store_e4m3x32(dst, v, quant_scale(norm_const, e8m0_to_float(sf)));
+  return sf;
+}
+
+// Column-wise MXFP8: the 32 rows of a scale block are the 32 lanes of the warp.  Lane i
+// returns the E8M0 byte of column i; every lane stores its row's 32 E4M3 bytes.
+__device__ __forceinline__ uint32_t quant_col_block(uint8_t* dst, bool do_store, const float* v, float norm_const) {
+  uint32_t my_sf = 0;
+  uint32_t packed[8];
+#pragma unroll
+  for (int i = 0; i < 32; i += 4) {
+    float s[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float cmax = warp_absmax(v[i + j]);
+      const float pv = cmax * (1.0f / 448.0f) * norm_const;
+      const uint32_t sf = e8m0_from_float(pv);
+      const float sfv = e8m0_to_float(sf);
+      float sc = sfv == 0.0f ? 0.0f : norm_const * rcp_approx(sfv);
+      sc = fminf(sc, 3.40282346638528859812e38f);
+      s[j] = v[i + j] * sc;
+      if ((int)lane_id() == i + j) my_sf = sf;
+    }
+    packed[i >> 2] = e4m3x4_from_float(s[0], s[1], s[2], s[3]);
+  }
+  if (do_store) {
+    uint4* p = reinterpret_cast<uint4*>(dst);
+    p[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+    p[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+  }
+  return my_sf;
+}
+
+// ---------------------------------------------------------------------------------------
+// The kernel
+// ---------------------------------------------------------------------------------------
+template <int kEpi, bool kDiscrete>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+    grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                        const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_base = smem_base + SmemLayout::BAR_OFF;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto acc_full_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + b); };
+  const uint32_t overlap_bar = bar_base + 8u * (2 * STAGES + 2);
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(smem + SmemLayout::MISC_OFF);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SmemLayout::MISC_OFF + 4);
+  int* total_tiles_smem = reinterpret_cast<int*>(smem + SmemLayout::MISC_OFF + 8);
+  int* prefix = reinterpret_cast<int*>(smem + SmemLayout::PREFIX_OFF);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  // ---- set-up -----------------------------------------------------------------------
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    mbar_init(acc_full_bar(0), 1);
+    mbar_init(acc_full_bar(1), 1);
+    mbar_init(overlap_bar, NUM_EPI_WARPS);
+    *abort_flag = 0;
+    fence_mbar_init();
+    prefetch_tensormap(&tmap_a);
+    if (!kDiscrete) prefetch_tensormap(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_ptr_smem), TMEM_COLS);
+    tmem_relinquish();
+  }
+  if (warp == 2) {
+    // tile prefix over experts: lane l scans a contiguous chunk, then a warp scan of the sums
+    const int chunk = (p.num_experts + 31) / 32;
+    const int e0 = lane * chunk;
+    int sum = 0;
+    for (int e = e0; e < min(e0 + chunk, p.num_experts); ++e) {
+      const int start = e == 0 ? 0 : p.offsets[e - 1];
+      const int rows = max(p.offsets[e] - start, 0);
+      sum += ((rows + BM - 1) / BM) * p.n_tiles;
+    }
+    int incl = sum;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, incl, d);
+      if (lane >= d) incl += t;
+    }
+    int run = incl - sum;
+    for (int e = e0; e < min(e0 + chunk, p.num_experts); ++e) {
+      prefix[e] = run;
+      const int start = e == 0 ? 0 : p.offsets[e - 1];
+      const int rows = max(p.offsets[e] - start, 0);
+      run += ((rows + BM - 1) / BM) * p.n_tiles;
+    }
+    if (lane == 31) {
+      prefix[p.num_experts] = incl;
+      *total_tiles_smem = incl;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+  const int total_tiles = *total_tiles_smem;
+
+  if (warp == 0) {
+    // ================= producer =======================================================
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const Tile tile = decode_tile(prefix, p.offsets, p.num_experts, p.n_tiles, t);
+        const int n0 = tile.n_tile * BN;
+        const uint8_t* sfa_src = p.sfa + (int64_t)(tile.row0 / BM) * p.rest_k * 512;
+        const uint8_t* sfb_e;
+        const CUtensorMap* bmap = &tmap_b;
+        if (kDiscrete) {
+          sfb_e = reinterpret_cast<const uint8_t*>(p.sfb_ptrs[tile.expert]);
+          bmap = p.b_maps + tile.expert;
+          tensormap_fence_acquire(bmap);
+        } else {
+          sfb_e = p.sfb + (int64_t)tile.expert * p.sfb_expert_bytes;
+        }
+        const int nblk0 = n0 / 128;
+        const int sfb_chunks = min(2, p.n_blocks - nblk0);
+        const uint32_t tx = A_STAGE_BYTES + B_STAGE_BYTES + SFA_STAGE_BYTES + 512u * sfb_chunks;
+        for (int kt = 0; kt < p.k_tiles; ++kt) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, ST_PRODUCER_EMPTY)) { ok = false; break; }
+          const uint32_t fb = full_bar(stage);
+          mbar_arrive_expect_tx(fb, tx);
+          tma_load_2d(smem_base + SmemLayout::A_OFF + stage * A_STAGE_BYTES, &tmap_a, fb, kt * BK, tile.row0);
+          if (kDiscrete)
+            tma_load_2d(smem_base + SmemLayout::B_OFF + stage * B_STAGE_BYTES, bmap, fb, kt * BK, n0);
+          else
+            tma_load_3d(smem_base + SmemLayout::B_OFF + stage * B_STAGE_BYTES, bmap, fb, kt * BK, n0, tile.expert);
+          bulk_load(smem_base + SmemLayout::SFA_OFF + stage * SFA_STAGE_BYTES, sfa_src + (int64_t)kt * 512, 512, fb);
+          for (int j = 0; j < sfb_chunks; ++j)
+            bulk_load(smem_base + SmemLayout::SFB_OFF + stage * SFB_STAGE_BYTES + j * 512,
+                      sfb_e + ((int64_t)(nblk0 + j) * p.rest_k + kt) * 512, 512, fb);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ================= MMA issuer =======================================================
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_mxf8(BM, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t sf_buf = 0;
+      int it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
+        const uint32_t acc = tmem_base + ((it & 1) ? TMEM_ACC1_COL : 0);
+        if (it > 0) {
+          // previous tile's epilogue has drained the 32 columns both accumulators share
+          if (!mbar_wait(overlap_bar, (it - 1) & 1, abort_flag, ST_MMA_OVERLAP)) { ok = false; break; }
+          tc_fence_after();
+        }
+        for (int kt = 0; kt < p.k_tiles; ++kt) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag, ST_MMA_FULL)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sfa_t = tmem_base + TMEM_SF_COL + 16 * sf_buf;
+          const uint32_t sfb_t = sfa_t + 4;
+          const uint32_t sfa_s = smem_base + SmemLayout::SFA_OFF + stage * SFA_STAGE_BYTES;
+          const uint32_t sfb_s = smem_base + SmemLayout::SFB_OFF + stage * SFB_STAGE_BYTES;
+          tmem_cp_sf(sfa_t, make_smem_desc(sfa_s, 0, 128, 0));
+          tmem_cp_sf(sfb_t, make_smem_desc(sfb_s, 0, 128, 0));
+          tmem_cp_sf(sfb_t + 4, make_smem_desc(sfb_s + 512, 0, 128, 0));
+          const uint64_t adesc = make_smem_desc(smem_base + SmemLayout::A_OFF + stage * A_STAGE_BYTES, 16, 1024, 2);
+          const uint64_t bdesc = make_smem_desc(smem_base + SmemLayout::B_OFF + stage * B_STAGE_BYTES, 16, 1024, 2);
+          const int k_left = p.k - kt * BK;
+          const int kblocks = min(4, (k_left + 31) / 32);
+          for (int kb = 0; kb < kblocks; ++kb) {
+            // advance 32 bytes along K inside the 128-byte swizzle row: +2 in 16-byte units
+            mma_mxf8_ss(acc, adesc + 2 * kb, bdesc + 2 * kb, idesc_with_sf_id(idesc, kb, kb), sfa_t, sfb_t,
+                        (kt | kb) != 0);
+          }
+          tc_commit(empty_bar(stage));  // frees the smem stage once these MMAs have read it
+          sf_buf ^= 1;
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok) tc_commit(acc_full_bar(it & 1));
+      }
+    }
+    __syncwarp();
+  } else {
+    // ================= epilogue =========================================================
+    const int ew = warp - 2;            // 0..7
+    const int quarter = warp & 3;       // TMEM lanes [32 quarter, 32 quarter + 32) belong to this warp
+    const int half = ew >> 2;           // column half of the tile: [128 half, 128 half + 128)
+    const int r_in_tile = quarter * 32 + lane;
+    const float norm_const = p.norm_const ? *p.norm_const : 1.0f;
+    int it = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
+      const Tile tile = decode_tile(prefix, p.offsets, p.num_experts, p.n_tiles, t);
+      const int n0 = tile.n_tile * BN;
+      const int row = tile.row0 + r_in_tile;
+      const bool row_ok = row < p.m_rows;
+      const float alpha = p.alpha[tile.expert];
+      const float prob = (p.prob && row_ok) ? p.prob[row] : 1.0f;
+      const uint32_t acc = tmem_base + ((it & 1) ? TMEM_ACC1_COL : 0) + ((uint32_t)(quarter * 32) << 16);
+      const bool reverse = (it & 1) == 0;  // even tiles drain from the top (shared columns first)
+      float thread_amax = 0.f;
+      uint32_t sf_row_word = 0;  // four E8M0 bytes of this row (K group = 128 output columns)
+
+      if (!mbar_wait(acc_full_bar(it & 1), (it >> 1) & 1, abort_flag, ST_EPI_ACC)) { ok = false; break; }
+      tc_fence_after();
+
+      if (kEpi == EPI_FC1) {
+        // 2 (gate, up) pairs per half: accumulator columns [128 half + 64 pp, +64)
+#pragma unroll 1
+        for (int i = 0; i < 2; ++i) {
+          const int pp = reverse ? 1 - i : i;
+          const int col = half * 128 + pp * 64;  // accumulator column of the gate block
+          float g[32], u[32];
+          tmem_ld_32x32(acc + col, g);
+          tmem_ld_32x32(acc + col + 32, u);
+          tmem_ld_wait();
+          reg_fence32(g);
+          reg_fence32(u);
+          if (i == 0) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(overlap_bar);
+          }
+          const int cn = n0 + col;          // column of C
+          const int dn = (n0 >> 1) + half * 64 + pp * 32;  // column of D
+          if (cn >= p.n) continue;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) { g[j] *= alpha; u[j] *= alpha; }
+          if (p.c && row_ok) {
+            store_bf16x32(p.c + (int64_t)row * p.n + cn, g);
+            store_bf16x32(p.c + (int64_t)row * p.n + cn + 32, u);
+          }
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float e = ex2_approx(g[j] * -1.4426950408889634f);
+            const float s = rcp_approx(1.0f + e);
+            g[j] = ((s * g[j]) * u[j]) * prob;
+          }
+          if (!p.d_is_fp8) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) thread_amax = fmaxf(thread_amax, fabsf(g[j]));
+            if (row_ok) store_bf16x32(reinterpret_cast<__nv_bfloat16*>(p.d) + (int64_t)row * p.n_out + dn, g);
+          } else {
+            if (row_ok) {
+              const uint32_t sf = quant_row_block(reinterpret_cast<uint8_t*>(p.d) + (int64_t)row * p.n_out + dn, g, norm_const);
+              sf_row_word |= sf << (8 * (half * 2 + pp));
+            }
+            if (p.d_col) {
+              // column scales: one byte per (column, 32-row block); rows beyond m_rows count as zero
+              if (!row_ok) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) g[j] = 0.f;
+              }
+              const uint32_t sfc = quant_col_block(p.d_col + (int64_t)row * p.n_out + dn, row_ok, g, norm_const);
+              int64_t blk_base = 0;
+              int rb = (tile.row0 >> 5) + quarter;
+              int rest = p.sfd_col_rest_k;
+              if (p.discrete_col_sfd) {
+                // per-expert block: rows counted from the expert's first row
+                const int start = tile.expert == 0 ? 0 : p.offsets[tile.expert - 1];
+                blk_base = (int64_t)(start / 128) * ((p.n_out + 127) / 128) * 512;
+                rb = ((tile.row0 - start) >> 5) + quarter;
+                rest = ((p.offsets[tile.expert] - start) / 32 + 3) / 4;
+              }
+              p.sfd_col[blk_base + sf_offset(dn + lane, rb, rest)] = (uint8_t)sfc;
+            }
+          }
+        }
+        if (p.d_is_fp8 && row_ok && p.sfd_row) {
+          // output columns [128 n_tile + 64 half, +64) = scale blocks 2 half, 2 half + 1 of K group n_tile
+          uint8_t* dst = p.sfd_row + sf_offset(row, (int64_t)tile.n_tile * 4 + half * 2, p.sfd_row_rest_k);
+          const int blocks_left = (p.n_out - ((n0 >> 1) + half * 64) + 31) / 32;
+          if (blocks_left >= 2)
+            *reinterpret_cast<uint16_t*>(dst) = (uint16_t)(sf_row_word >> (16 * half));
+          else if (blocks_left == 1)
+            *dst = (uint8_t)(sf_row_word >> (16 * half));
+        }
+      } else {
+        // FC2: 4 blocks of 32 columns per half
+#pragma unroll 1
+        for (int i = 0; i < 4; ++i) {
+          const int bb = reverse ? 3 - i : i;
+          const int col = half * 128 + bb * 32;
+          float v[32];
+          tmem_ld_32x32(acc + col, v);
+          tmem_ld_wait();
+          reg_fence32(v);
+          if (i == 0) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(overlap_bar);
+          }
+          const int dn = n0 + col;
+          if (dn >= p.n) continue;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = (v[j] * alpha) * prob;
+          if (!p.d_is_fp8) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) thread_amax = fmaxf(thread_amax, fabsf(v[j]));
+            if (row_ok) store_bf16x32(reinterpret_cast<__nv_bfloat16*>(p.d) + (int64_t)row * p.n_out + dn, v);
+          } else {
+            if (row_ok) {
+              const uint32_t sf = quant_row_block(reinterpret_cast<uint8_t*>(p.d) + (int64_t)row * p.n_out + dn, v, norm_const);
+              sf_row_word |= sf << (8 * bb);
+            }
+            if (p.d_col) {
+              if (!row_ok) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = 0.f;
+              }
+              const uint32_t sfc = quant_col_block(p.d_col + (int64_t)row * p.n_out + dn, row_ok, v, norm_const);
+              int64_t blk_base = 0;
+              int rb = (tile.row0 >> 5) + quarter;
+              int rest = p.sfd_col_rest_k;
+              if (p.discrete_col_sfd) {
+                const int start = tile.expert == 0 ? 0 : p.offsets[tile.expert - 1];
+                blk_base = (int64_t)(start / 128) * ((p.n_out + 127) / 128) * 512;
+                rb = ((tile.row0 - start) >> 5) + quarter;
+                rest = ((p.offsets[tile.expert] - start) / 32 + 3) / 4;
+              }
+              p.sfd_col[blk_base + sf_offset(dn + lane, rb, rest)] = (uint8_t)sfc;
+            }
+          }
+        }
+        if (p.d_is_fp8 && row_ok && p.sfd_row) {
+          // output columns [256 n_tile + 128 half, +128) = K group 2 n_tile + half, 4 blocks
+          uint8_t* dst = p.sfd_row + sf_offset(row, (int64_t)(tile.n_tile * 2 + half) * 4, p.sfd_row_rest_k);
+          const int blocks_left = (p.n_out - (n0 + half * 128) + 31) / 32;
+          if (blocks_left >= 4) {
+            *reinterpret_cast<uint32_t*>(dst) = sf_row_word;
+          } else {
+            for (int b = 0; b < blocks_left; ++b) dst[b] = (uint8_t)(sf_row_word >> (8 * b));
+          }
+        }
+      }
+
+      if (p.amax && !p.d_is_fp8) {
+        float wmax = thread_amax;
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) wmax = fmaxf(wmax, __shfl_xor_sync(0xffffffffu, wmax, d));
+        // non-negative floats order like their bit patterns; -inf (the caller's initial
+        // value) has a negative pattern, so a signed integer max is exact
+        if (lane == 0) atomicMax(reinterpret_cast<int*>(p.amax) + tile.expert, __float_as_int(wmax));
+      }
+    }
+  }
+
+  // ---- teardown ----------------------------------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Discrete weights: build one tensor map per expert in the caller's workspace.  The host
+// encodes a prototype map of an [n, k] matrix; this kernel copies it per expert and patches
+// the global address with the pointer read from the device-resident pointer array, so the
+// host never needs the pointer values (the launch stays capturable in a CUDA graph).
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(32)
+    build_expert_tensormaps_kernel(const __grid_constant__ CUtensorMap proto, const int64_t* b_ptrs,
+                                   const void* fallback, CUtensorMap* out, int num_experts) {
+  __shared__ __align__(128) CUtensorMap s_map;
+  const int e = blockIdx.x;
+  if (e >= num_experts) return;
+  const int lane = threadIdx.x;
+  reinterpret_cast<uint32_t*>(&s_map)[lane] = reinterpret_cast<const uint32_t*>(&proto)[lane];
+  __syncwarp();
+  if (lane == 0) {
+    uint64_t addr = (uint64_t)b_ptrs[e];
+    if (addr == 0 || (addr & 15)) {
+      // a misaligned or null weight pointer would fault the TMA unit: record it and point the
+      // map at memory that is known to be valid instead
+      atomicCAS(&g_device_status, 0, 201);
+      addr = (uint64_t)fallback;
+    }
+    asm volatile("tensormap.replace.tile.global_address.shared::cta.b1024.b64 [%0], %1;" ::"r"(
+                     smem_u32(&s_map)),
+                 "l"(addr)
+                 : "memory");
+  }
+  __syncwarp();
+  asm volatile(
+      "tensormap.cp_fenceproxy.global.shared::cta.tensormap::generic.release.gpu.sync.aligned [%0], "
+      "[%1], 128;" ::"l"(out + e),
+      "r"(smem_u32(&s_map))
+      : "memory");
+}
+
+// ---------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------
+static thread_local char tl_error[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(tl_error, sizeof(tl_error), fmt, ap);
+  va_end(ap);
+}
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(tl_error, sizeof(tl_error), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  });
+  return fn;
+}
+
+// uint8 tensor map, innermost dim = K bytes, 128-byte swizzle, box = (128, box_rows[, 1]).
+static int encode_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const uint64_t* strides,
+                      uint32_t box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return fail(B200MOE_E_DEVICE, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t gdim[3] = {dims[0], dims[1], rank > 2 ? dims[2] : 1};
+  cuuint64_t gstr[2] = {strides[0], rank > 2 ? strides[1] : 0};
+  cuuint32_t box[3] = {(cuuint32_t)BK, box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, (cuuint32_t)rank, const_cast<void*>(base), gdim, gstr, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(B200MOE_E_SHAPE, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return B200MOE_OK;
+}
+
+struct DeviceInfo {
+  int sm_count = 0;
+  int cc_major = 0;
+  bool attr_set[2][2] = {{false, false}, {false, false}};
+};
+
+static int get_device_info(DeviceInfo** out) {
+  static DeviceInfo infos[64];
+  static std::mutex mu;
+  int dev = 0;
+  B200_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(B200MOE_E_DEVICE, "device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  DeviceInfo& di = infos[dev];
+  if (di.sm_count == 0) {
+    B200_CUDA_CHECK(cudaDeviceGetAttribute(&di.cc_major, cudaDevAttrComputeCapabilityMajor, dev));
+    B200_CUDA_CHECK(cudaDeviceGetAttribute(&di.sm_count, cudaDevAttrMultiProcessorCount, dev));
+  }
+  *out = &di;
+  return B200MOE_OK;
+}
+
+template <int kEpi, bool kDiscrete>
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, DeviceInfo* di,
+                  cudaStream_t stream) {
+  auto kern = grouped_gemm_kernel<kEpi, kDiscrete>;
+  if (!di->attr_set[kEpi][kDiscrete ? 1 : 0]) {
+    B200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    di->attr_set[kEpi][kDiscrete ? 1 : 0] = true;
+  }
+  kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200MOE_OK;
+}
+
+static int run_gemm(int epi, const b200moe_gemm_args* a, void* stream_v) {
+  cudaStream_t stream = (cudaStream_t)stream_v;
+  if (!a) return fail(B200MOE_E_NULL, "args is NULL");
+  const bool discrete = a->b_ptrs != nullptr || a->sfb_ptrs != nullptr;
+  const char* op = epi == EPI_FC1 ? "fc1_swiglu" : "fc2_quant";
+  if (a->m_rows == 0 || a->num_experts == 0) return B200MOE_OK;
+  if (!a->a || !a->sfa || !a->padded_offsets || !a->alpha || !a->d)
+    return fail(B200MOE_E_NULL, "%s: a, sfa, padded_offsets, alpha and d are required", op);
+  if (discrete) {
+    if (!a->b_ptrs || !a->sfb_ptrs || a->b || a->sfb)
+      return fail(B200MOE_E_NULL, "%s: pass either (b, sfb) or (b_ptrs, sfb_ptrs)", op);
+  } else if (!a->b || !a->sfb) {
+    return fail(B200MOE_E_NULL, "%s: b and sfb are required in dense mode", op);
+  }
+  if (epi == EPI_FC2 && !a->prob) return fail(B200MOE_E_NULL, "%s: prob is required", op);
+  if (a->m_rows < 0 || a->m_rows > (1ll << 30) || a->n <= 0 || a->k <= 0 || a->num_experts < 0)
+    return fail(B200MOE_E_SHAPE, "%s: bad sizes m=%lld n=%lld k=%lld E=%d", op, (long long)a->m_rows, (long long)a->n,
+                (long long)a->k, a->num_experts);
+  if (a->num_experts > MAX_EXPERTS)
+    return fail(B200MOE_E_SHAPE, "%s: at most %d experts are supported, got %d", op, MAX_EXPERTS, a->num_experts);
+  if (a->k % 16 != 0) return fail(B200MOE_E_SHAPE, "%s: k (%lld) must be a multiple of 16", op, (long long)a->k);
+  if (epi == EPI_FC1 && a->n % 64 != 0)
+    return fail(B200MOE_E_SHAPE, "%s: n (%lld) must be a multiple of 64 (32-column gate/up blocks)", op, (long long)a->n);
+  if (epi == EPI_FC2 && a->n % 32 != 0)
+    return fail(B200MOE_E_SHAPE, "%s: n (%lld) must be a multiple of 32", op, (long long)a->n);
+  if (a->n * a->k > (1ll << 40)) return fail(B200MOE_E_SHAPE, "%s: n*k too large", op);
+  const bool d_fp8 = a->d_dtype == B200MOE_DTYPE_E4M3;
+  if (a->d_dtype != B200MOE_DTYPE_BF16 && !d_fp8) return fail(B200MOE_E_UNSUPPORTED, "%s: d_dtype %d", op, a->d_dtype);
+  if (d_fp8) {
+    if (!a->sfd_row || !a->norm_const)
+      return fail(B200MOE_E_NULL, "%s: E4M3 output needs sfd_row and norm_const", op);
+    if ((a->d_col == nullptr) != (a->sfd_col == nullptr))
+      return fail(B200MOE_E_NULL, "%s: d_col and sfd_col go together", op);
+  }
+  const uintptr_t align_or = (uintptr_t)a->a | (uintptr_t)a->sfa | (uintptr_t)a->b | (uintptr_t)a->sfb | (uintptr_t)a->c |
+                             (uintptr_t)a->d | (uintptr_t)a->d_col | (uintptr_t)a->sfd_row | (uintptr_t)a->sfd_col;
+  if (align_or & 15) return fail(B200MOE_E_ALIGN, "%s: tensor base addresses must be 16-byte aligned", op);
+
+  DeviceInfo* di = nullptr;
+  int rc = get_device_info(&di);
+  if (rc) return rc;
+  if (di->cc_major != 10) return fail(B200MOE_E_DEVICE, "%s: needs an sm_100 device, found compute capability %d.x", op, di->cc_major);
+
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.sfa = (const uint8_t*)a->sfa;
+  p.sfb = (const uint8_t*)a->sfb;
+  p.sfb_ptrs = a->sfb_ptrs;
+  p.offsets = a->padded_offsets;
+  p.alpha = a->alpha;
+  p.prob = a->prob;
+  p.norm_const = a->norm_const;
+  p.c = epi == EPI_FC1 ? (__nv_bfloat16*)a->c : nullptr;
+  p.d = a->d;
+  p.d_col = d_fp8 ? (uint8_t*)a->d_col : nullptr;
+  p.amax = a->amax;
+  p.sfd_row = (uint8_t*)a->sfd_row;
+  p.sfd_col = (uint8_t*)a->sfd_col;
+  p.m_rows = (int)a->m_rows;
+  p.n = (int)a->n;
+  p.k = (int)a->k;
+  p.num_experts = a->num_experts;
+  p.n_out = epi == EPI_FC1 ? p.n / 2 : p.n;
+  p.n_tiles = (p.n + BN - 1) / BN;
+  p.k_tiles = (p.k + BK - 1) / BK;
+  p.rest_k = ((p.k + 31) / 32 + 3) / 4;
+  p.n_blocks = (p.n + 127) / 128;
+  p.sfb_expert_bytes = (int64_t)p.n_blocks * p.rest_k * 512;
+  p.sfd_row_rest_k = ((p.n_out + 31) / 32 + 3) / 4;
+  p.sfd_col_rest_k = ((p.m_rows + 31) / 32 + 3) / 4;
+  p.d_is_fp8 = d_fp8;
+  p.discrete_col_sfd = (a->flags & B200MOE_FLAG_DISCRETE_COL_SFD) ? 1 : 0;
+
+  CUtensorMap ta, tb;
+  {
+    const uint64_t dims[2] = {(uint64_t)p.k, (uint64_t)p.m_rows};
+    const uint64_t strides[1] = {(uint64_t)p.k};
+    rc = encode_map(&ta, a->a, 2, dims, strides, BM);
+    if (rc) return rc;
+  }
+  if (!discrete) {
+    const uint64_t dims[3] = {(uint64_t)p.k, (uint64_t)p.n, (uint64_t)p.num_experts};
+    const uint64_t strides[2] = {(uint64_t)p.k, (uint64_t)p.n * (uint64_t)p.k};
+    rc = encode_map(&tb, a->b, 3, dims, strides, BN);
+    if (rc) return rc;
+  } else {
+    const int64_t need = b200moe_workspace_bytes(p.num_experts, 1);
+    if (!a->workspace || a->workspace_bytes < need || ((uintptr_t)a->workspace & 127))
+      return fail(B200MOE_E_WORKSPACE, "%s: discrete mode needs a 128-byte aligned workspace of %lld bytes", op, (long long)need);
+    const uint64_t dims[2] = {(uint64_t)p.k, (uint64_t)p.n};
+    const uint64_t strides[1] = {(uint64_t)p.k};
+    rc = encode_map(&tb, a->a, 2, dims, strides, BN);  // prototype; the address is patched per expert
+    if (rc) return rc;
+    p.b_maps = (const CUtensorMap*)a->workspace;
+    build_expert_tensormaps_kernel<<<p.num_experts, 32, 0, stream>>>(tb, a->b_ptrs, a->a, (CUtensorMap*)a->workspace,
+                                                                      p.num_experts);
+    B200_CUDA_CHECK(cudaGetLastError());
+  }
+
+  const int64_t max_tiles = ((a->m_rows + BM - 1) / BM) * p.n_tiles;
+  int grid = di->sm_count - (a->sm_margin > 0 ? a->sm_margin : 0);
+  if (grid < 1) grid = 1;
+  if ((int64_t)grid > max_tiles) grid = (int)max_tiles;
+
+  if (epi == EPI_FC1)
+    return discrete ? launch<EPI_FC1, true>(ta, tb, p, grid, di, stream) : launch<EPI_FC1, false>(ta, tb, p, grid, di, stream);
+  return discrete ? launch<EPI_FC2, true>(ta, tb, p, grid, di, stream) : launch<EPI_FC2, false>(ta, tb, p, grid, di, stream);
+}
+
+}  // namespace b200moe
+
+extern "C" {
+
+int b200moe_fc1_swiglu(const b200moe_gemm_args* args, void* stream) { return b200moe::run_gemm(b200moe::EPI_FC1, args, stream); }
+
+int b200moe_fc2_quant(const b200moe_gemm_args* args, void* stream) { return b200moe::run_gemm(b200moe::EPI_FC2, args, stream); }
+
+int64_t b200moe_workspace_bytes(int32_t num_experts, int32_t discrete) {
+  if (!discrete || num_experts <= 0) return 0;
+  return (int64_t)num_experts * 128;
+}
+
+const char* b200moe_last_error(void) { return b200moe::tl_error; }
+
+int b200moe_device_status(int clear) {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, b200moe::g_device_status, sizeof(int)) != cudaSuccess) return -1;
+  if (clear) {
+    int z = 0;
+    cudaMemcpyToSymbol(b200moe::g_device_status, &z, sizeof(int));
+  }
+  return v;
+}
+
+int b200moe_abi_version(void) { return 1; }
+
+}  // extern "C"

@@ -1,0 +1,220 @@
+// Routing helpers of the MoE layer: stable grouping of routed rows by expert, the padded
+// per-expert END offsets the grouped GEMMs consume, row scatter (dispatch side) and the
+// top-k combine.  All integer results are exact and deterministic (no float atomics, no
+// order-dependent placement): rows of one expert keep their original order.
+#include "b200moe.h"
+#include "common.cuh"
+
+namespace b200moe {
+
+constexpr int ROUTE_CHUNK = 1024;  // routed rows ranked by one warp
+
+// per-chunk histogram: hist[chunk][e] = rows of expert e inside the chunk
+__global__ void __launch_bounds__(256)
+    route_hist_kernel(const int32_t* __restrict__ ids, int64_t num_rows, int num_experts, int32_t* __restrict__ hist) {
+  extern __shared__ int s_hist[];
+  for (int e = threadIdx.x; e < num_experts; e += blockDim.x) s_hist[e] = 0;
+  __syncthreads();
+  const int64_t base = (int64_t)blockIdx.x * ROUTE_CHUNK;
+  for (int i = threadIdx.x; i < ROUTE_CHUNK; i += blockDim.x) {
+    const int64_t r = base + i;
+    if (r < num_rows) {
+      const int e = ids[r];
+      if (e >= 0 && e < num_experts) atomicAdd(&s_hist[e], 1);
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < num_experts; e += blockDim.x) hist[(int64_t)blockIdx.x * num_experts + e] = s_hist[e];
+}
+
+// one block: exclusive scan over chunks per expert (in place), counts, padded END offsets,
+// group starts (scratch tail)
+__global__ void __launch_bounds__(1024)
+    route_scan_kernel(int32_t* __restrict__ hist, int num_chunks, int num_experts, int m_aligned,
+                      int32_t* __restrict__ counts, int32_t* __restrict__ padded_offsets, int32_t* __restrict__ starts) {
+  __shared__ int s_pad[1024];
+  const int e = threadIdx.x;
+  int run = 0;
+  if (e < num_experts) {
+    for (int c = 0; c < num_chunks; ++c) {
+      const int v = hist[(int64_t)c * num_experts + e];
+      hist[(int64_t)c * num_experts + e] = run;
+      run += v;
+    }
+    counts[e] = run;
+  }
+  const int padded = e < num_experts ? ((run + m_aligned - 1) / m_aligned) * m_aligned : 0;
+  s_pad[e] = padded;
+  __syncthreads();
+  // inclusive Hillis-Steele scan over up to 1024 experts
+  for (int d = 1; d < 1024; d <<= 1) {
+    const int t = e >= d ? s_pad[e - d] : 0;
+    __syncthreads();
+    s_pad[e] += t;
+    __syncthreads();
+  }
+  if (e < num_experts) {
+    padded_offsets[e] = s_pad[e];
+    starts[e] = s_pad[e] - padded;
+  }
+}
+
+// one warp per chunk: rows are visited in order, 32 at a time; lanes holding the same
+// expert are ranked by lane index, so the placement is the stable sort order
+__global__ void __launch_bounds__(32)
+    route_place_kernel(const int32_t* __restrict__ ids, int64_t num_rows, int num_experts,
+                       const int32_t* __restrict__ hist, const int32_t* __restrict__ starts,
+                       int32_t* __restrict__ dst_row) {
+  extern __shared__ int s_cnt[];
+  const int lane = threadIdx.x;
+  for (int e = lane; e < num_experts; e += 32)
+    s_cnt[e] = starts[e] + hist[(int64_t)blockIdx.x * num_experts + e];
+  __syncwarp();
+  const int64_t base = (int64_t)blockIdx.x * ROUTE_CHUNK;
+  for (int i = 0; i < ROUTE_CHUNK; i += 32) {
+    const int64_t r = base + i + lane;
+    const bool valid = r < num_rows;
+    int e = valid ? ids[r] : -1;
+    if (e < 0 || e >= num_experts) e = -1;
+    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    const int rank = __popc(peers & ((1u << lane) - 1));
+    int slot = 0;
+    if (e >= 0) slot = s_cnt[e] + rank;
+    __syncwarp();
+    if (e >= 0 && rank == 0) s_cnt[e] += __popc(peers);
+    __syncwarp();
+    if (valid) dst_row[r] = e >= 0 ? slot : -1;
+  }
+}
+
+// out[dst_row[r], :] = in[r / rows_per_src, :], 16 bytes per thread per step
+__global__ void __launch_bounds__(128)
+    scatter_rows_kernel(const uint4* __restrict__ in, const int32_t* __restrict__ dst_row, int rows_per_src,
+                        int vec_per_row, uint4* __restrict__ out, const float* __restrict__ in_prob,
+                        float* __restrict__ out_prob) {
+  const int64_t r = blockIdx.x;
+  const int d = dst_row[r];
+  if (d < 0) return;
+  const uint4* src = in + (r / rows_per_src) * vec_per_row;
+  uint4* dst = out + (int64_t)d * vec_per_row;
+  for (int i = threadIdx.x; i < vec_per_row; i += blockDim.x) dst[i] = __ldg(src + i);
+  if (threadIdx.x == 0 && in_prob && out_prob) out_prob[d] = in_prob[r];
+}
+
+// rows [start_e + count_e, end_e) of every expert group are set to zero
+__global__ void __launch_bounds__(128)
+    zero_pad_rows_kernel(uint4* __restrict__ buf, const int32_t* __restrict__ counts,
+                         const int32_t* __restrict__ padded_offsets, int vec_per_row, float* __restrict__ prob) {
+  const int e = blockIdx.x;
+  const int end = padded_offsets[e];
+  const int start = e == 0 ? 0 : padded_offsets[e - 1];
+  for (int row = start + counts[e] + blockIdx.y; row < end; row += gridDim.y) {
+    uint4* dst = buf + (int64_t)row * vec_per_row;
+    for (int i = threadIdx.x; i < vec_per_row; i += blockDim.x) dst[i] = make_uint4(0, 0, 0, 0);
+    if (prob && threadIdx.x == 0) prob[row] = 0.f;
+  }
+}
+
+// out[t, :] = sum_j in[dst_row[t * topk + j], :], float32 accumulation in slot order
+__global__ void __launch_bounds__(128)
+    combine_rows_kernel(const uint4* __restrict__ in, const int32_t* __restrict__ dst_row, int topk, int vec_per_row,
+                        uint4* __restrict__ out) {
+  const int64_t t = blockIdx.x;
+  for (int i = threadIdx.x; i < vec_per_row; i += blockDim.x) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int j = 0; j < topk; ++j) {
+      const int d = dst_row[t * topk + j];
+      if (d < 0) continue;
+      const uint4 v = __ldg(in + (int64_t)d * vec_per_row + i);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 f = __bfloat1622float2(h[q]);
+        acc[2 * q] += f.x;
+        acc[2 * q + 1] += f.y;
+      }
+    }
+    uint4 o;
+    o.x = bf16x2_from_float(acc[0], acc[1]);
+    o.y = bf16x2_from_float(acc[2], acc[3]);
+    o.z = bf16x2_from_float(acc[4], acc[5]);
+    o.w = bf16x2_from_float(acc[6], acc[7]);
+    out[t * vec_per_row + i] = o;
+  }
+}
+
+}  // namespace b200moe
+
+extern "C" {
+
+int64_t b200moe_route_scratch_bytes(int64_t num_rows, int32_t num_experts) {
+  const int64_t chunks = (num_rows + b200moe::ROUTE_CHUNK - 1) / b200moe::ROUTE_CHUNK;
+  return (chunks * num_experts + num_experts) * (int64_t)sizeof(int32_t);
+}
+
+int b200moe_route(const int32_t* expert_ids, int64_t num_rows, int32_t num_experts, int32_t m_aligned, int32_t* counts,
+                  int32_t* padded_offsets, int32_t* dst_row, int32_t* scratch, void* stream_v) {
+  using namespace b200moe;
+  cudaStream_t stream = (cudaStream_t)stream_v;
+  if (num_experts <= 0 || num_experts > 1024) return fail(B200MOE_E_SHAPE, "route: num_experts must be in [1, 1024], got %d", num_experts);
+  if (m_aligned <= 0 || m_aligned % 128 != 0) return fail(B200MOE_E_SHAPE, "route: m_aligned must be a positive multiple of 128");
+  if (num_rows < 0 || num_rows > (1ll << 30)) return fail(B200MOE_E_SHAPE, "route: bad num_rows");
+  if (!counts || !padded_offsets || !scratch || (num_rows > 0 && (!expert_ids || !dst_row)))
+    return fail(B200MOE_E_NULL, "route: null pointer");
+  const int chunks = (int)((num_rows + ROUTE_CHUNK - 1) / ROUTE_CHUNK);
+  int32_t* hist = scratch;
+  int32_t* starts = scratch + (int64_t)chunks * num_experts;
+  if (chunks > 0) {
+    route_hist_kernel<<<chunks, 256, num_experts * sizeof(int), stream>>>(expert_ids, num_rows, num_experts, hist);
+    B200_CUDA_CHECK(cudaGetLastError());
+  }
+  route_scan_kernel<<<1, 1024, 0, stream>>>(hist, chunks, num_experts, m_aligned, counts, padded_offsets, starts);
+  B200_CUDA_CHECK(cudaGetLastError());
+  if (chunks > 0) {
+    route_place_kernel<<<chunks, 32, num_experts * sizeof(int), stream>>>(expert_ids, num_rows, num_experts, hist, starts, dst_row);
+    B200_CUDA_CHECK(cudaGetLastError());
+  }
+  return B200MOE_OK;
+}
+
+int b200moe_scatter_rows(const void* in, const int32_t* dst_row, int64_t num_rows, int32_t rows_per_src, int64_t cols,
+                         void* out, const float* in_prob, float* out_prob, void* stream) {
+  using namespace b200moe;
+  if (num_rows == 0) return B200MOE_OK;
+  if (!in || !dst_row || !out) return fail(B200MOE_E_NULL, "scatter_rows: null pointer");
+  if (cols <= 0 || cols % 8 != 0 || rows_per_src <= 0 || num_rows < 0 || num_rows > 0x7fffffffll)
+    return fail(B200MOE_E_SHAPE, "scatter_rows: cols must be a positive multiple of 8");
+  if (((uintptr_t)in | (uintptr_t)out) & 15) return fail(B200MOE_E_ALIGN, "scatter_rows: 16-byte alignment required");
+  scatter_rows_kernel<<<(unsigned)num_rows, 128, 0, (cudaStream_t)stream>>>((const uint4*)in, dst_row, rows_per_src,
+                                                                           (int)(cols / 8), (uint4*)out, in_prob, out_prob);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200MOE_OK;
+}
+
+int b200moe_zero_pad_rows(void* buf, const int32_t* counts, const int32_t* padded_offsets, int32_t num_experts,
+                          int64_t cols, float* prob, void* stream) {
+  using namespace b200moe;
+  if (num_experts == 0) return B200MOE_OK;
+  if (!buf || !counts || !padded_offsets) return fail(B200MOE_E_NULL, "zero_pad_rows: null pointer");
+  if (cols <= 0 || cols % 8 != 0) return fail(B200MOE_E_SHAPE, "zero_pad_rows: cols must be a positive multiple of 8");
+  dim3 grid((unsigned)num_experts, 8);
+  zero_pad_rows_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>((uint4*)buf, counts, padded_offsets, (int)(cols / 8), prob);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200MOE_OK;
+}
+
+int b200moe_combine_rows(const void* in, const int32_t* dst_row, int64_t num_tokens, int32_t topk, int64_t cols, void* out,
+                         void* stream) {
+  using namespace b200moe;
+  if (num_tokens == 0) return B200MOE_OK;
+  if (!in || !dst_row || !out) return fail(B200MOE_E_NULL, "combine_rows: null pointer");
+  if (cols <= 0 || cols % 8 != 0 || topk <= 0 || num_tokens < 0 || num_tokens > 0x7fffffffll)
+    return fail(B200MOE_E_SHAPE, "combine_rows: cols must be a positive multiple of 8");
+  if (((uintptr_t)in | (uintptr_t)out) & 15) return fail(B200MOE_E_ALIGN, "combine_rows: 16-byte alignment required");
+  combine_rows_kernel<<<(unsigned)num_tokens, 128, 0, (cudaStream_t)stream>>>((const uint4*)in, dst_row, topk, (int)(cols / 8),
+                                                                             (uint4*)out);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200MOE_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,168 @@
+/*
+ * b200moe.h - C ABI of the B200-native MoE grouped-GEMM hot path.
+ *
+ * One shared library (libb200moe.so) built for sm_100a only.  Every entry point takes
+ * plain device pointers, sizes and a CUDA stream (passed as void*), launches its kernels
+ * asynchronously on that stream, never synchronises, never allocates device memory and
+ * never throws.  Return value: 0 = launched, < 0 = argument error (B200MOE_E_*),
+ * > 0 = CUDA runtime / driver error code.  b200moe_last_error() returns a thread-local
+ * human-readable description of the last non-zero return.
+ *
+ * The entry points stand in for the reference's JIT-compiled CuTe-DSL kernels; each
+ * comment names the reference interface it replaces (path inside NVIDIA/cudnn-frontend).
+ */
+#ifndef B200MOE_H_
+#define B200MOE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200MOE_OK 0
+#define B200MOE_E_NULL (-1)        /* a required pointer is NULL                        */
+#define B200MOE_E_SHAPE (-2)       /* a size is out of range / violates a divisibility  */
+#define B200MOE_E_ALIGN (-3)       /* a pointer or pitch is not 16-byte aligned          */
+#define B200MOE_E_UNSUPPORTED (-4) /* valid in the reference, not built here             */
+#define B200MOE_E_WORKSPACE (-5)   /* workspace missing or too small                     */
+#define B200MOE_E_DEVICE (-6)      /* not an sm_100 device / driver entry point missing  */
+
+/* d_dtype values */
+#define B200MOE_DTYPE_BF16 0
+#define B200MOE_DTYPE_E4M3 1
+
+/* flags */
+#define B200MOE_FLAG_DISCRETE_COL_SFD 1 /* per-expert column scale-factor blocks */
+
+/*
+ * Arguments of one grouped GEMM launch.  All pointers are device pointers.
+ *
+ * Layouts (the reference's, python/cudnn/grouped_gemm/grouped_gemm_swiglu/api.py:193-247):
+ *   a      [m_rows, k]  E4M3, K contiguous
+ *   sfa    E8M0, "128x4" swizzled layout of (m_rows, k/32)
+ *   b      [E, n, k]    E4M3, K contiguous (dense mode)           | exactly one of
+ *   sfb    E blocks, each the 128x4 layout of (n, k/32)           | (b, sfb) and
+ *   b_ptrs / sfb_ptrs   int64 device arrays [E] of per-expert     | (b_ptrs, sfb_ptrs)
+ *                       addresses of [n, k] / its 128x4 layout    | is non-NULL
+ *   padded_offsets [E]  int32 END offsets, multiples of 128
+ *   alpha  [E] f32, prob [m_rows] f32 (optional for FC1), norm_const [1] f32
+ *   c      [m_rows, n]      bf16 (FC1 only; NULL = do not write it)
+ *   d      [m_rows, n_out]  bf16 or E4M3 (n_out = n/2 for FC1, n for FC2)
+ *   d_col  [m_rows, n_out]  E4M3 quantised with the column scales (optional)
+ *   amax   [E] f32, updated with atomic max (caller initialises, e.g. to -inf)
+ *   sfd_row  128x4 layout of (m_rows, n_out/32); sfd_col  128x4 layout of (n_out, m_rows/32)
+ *   workspace  only for discrete mode, b200moe_workspace_bytes(E, 1) bytes, 128-B aligned
+ */
+typedef struct b200moe_gemm_args {
+  const void* a;
+  const void* sfa;
+  const void* b;
+  const void* sfb;
+  const int64_t* b_ptrs;
+  const int64_t* sfb_ptrs;
+  const int32_t* padded_offsets;
+  const float* alpha;
+  const float* prob;
+  const float* norm_const;
+  void* c;
+  void* d;
+  void* d_col;
+  float* amax;
+  void* sfd_row;
+  void* sfd_col;
+  void* workspace;
+  int64_t workspace_bytes;
+  int64_t m_rows;
+  int64_t n;
+  int64_t k;
+  int32_t num_experts;
+  int32_t d_dtype;
+  int32_t flags;
+  int32_t sm_margin; /* SMs left free for a concurrent kernel (CUDNNFE_CLUSTER_OVERLAP_MARGIN) */
+} b200moe_gemm_args;
+
+/*
+ * FC1: C = alpha_e * (A*SFA)(B_e*SFB_e)^T ; D[:, 32j:32j+32] = up_j * silu(gate_j) * prob,
+ * gate/up = even/odd 32-column blocks of C; per-expert amax (bf16 D) or row/column MXFP8
+ * re-quantisation (E4M3 D).
+ * Replaces the launch done by GroupedGemmSwigluSm100.execute
+ * (python/cudnn/grouped_gemm/grouped_gemm_swiglu/api.py:706-771), i.e. the kernel
+ * BlockScaledContiguousGroupedGemmKernel
+ * (python/cudnn/grouped_gemm/grouped_gemm_swiglu/grouped_gemm_swiglu_quant.py:1241-2636),
+ * and, with b_ptrs/sfb_ptrs, DiscreteGroupedGemmSwigluSm100.execute
+ * (python/cudnn/discrete_grouped_gemm/discrete_grouped_gemm_swiglu/api.py:710-795).
+ */
+int b200moe_fc1_swiglu(const b200moe_gemm_args* args, void* stream);
+
+/*
+ * FC2: D = quant(alpha_e * acc * prob); bf16 D + per-expert amax, or E4M3 D + row/column
+ * E8M0 scale factors.
+ * Replaces GroupedGemmQuantSm100.execute
+ * (python/cudnn/grouped_gemm/grouped_gemm_quant/api.py:974-1089), kernel
+ * BlockScaledMoEGroupedGemmQuantKernel
+ * (python/cudnn/grouped_gemm/grouped_gemm_quant/grouped_gemm_quant.py:1073-1985).
+ */
+int b200moe_fc2_quant(const b200moe_gemm_args* args, void* stream);
+
+/*
+ * Bytes of caller-owned workspace a launch needs (0 in dense mode; E tensor-map slots of
+ * 128 bytes in discrete mode).  Mirrors the workspace the reference allocates in compile()
+ * (python/cudnn/grouped_gemm/grouped_gemm_quant/grouped_gemm_quant.py:425-445).
+ */
+int64_t b200moe_workspace_bytes(int32_t num_experts, int32_t discrete);
+
+/*
+ * Activation quantiser: x [rows, cols] bf16 (row pitch ld_elems) -> q [rows, cols] E4M3
+ * + E8M0 scales per 32 elements along cols, written in the 128x4 layout of (rows, cols/32).
+ * sf must hold ceil(rows/128) * ceil(cols/128) * 512 bytes.  No reference counterpart
+ * (the reference's tests delegate input quantisation to TransformerEngine,
+ * test/python/sdpa/mxfp8.py:137-187); the arithmetic is the row-quantisation formula of
+ * grouped_gemm_swiglu_quant.py:1067-1139 with norm_const = 1.
+ */
+int b200moe_quantize_mxfp8(const void* x, int64_t rows, int64_t cols, int64_t ld_elems,
+                           void* q, void* sf, void* stream);
+
+/*
+ * Routing helpers (no reference counterpart; the reference's tests build offsets on the
+ * host, test/python/fe_api/test_grouped_gemm_swiglu_utils.py:270-312).
+ *
+ * b200moe_route: expert_ids [num_rows] int32 (expert of every routed row, token-major) ->
+ *   counts [E] int32, padded_offsets [E] int32 END offsets with each group rounded up to
+ *   m_aligned, dst_row [num_rows] int32 = row of the expert-grouped padded buffer (stable:
+ *   rows of one expert keep their order).  scratch: (E + 1) int32, caller-owned.
+ * b200moe_scatter_rows: out[dst_row[r], :] = in[r / rows_per_src, :]  (bf16, cols % 8 == 0);
+ *   also out_prob[dst_row[r]] = in_prob[r] when both are non-NULL.
+ * b200moe_combine_rows: out[t, :] = sum_j in[dst_row[t*topk + j], :] (bf16 in, f32 accumulate,
+ *   bf16 out).
+ */
+int b200moe_route(const int32_t* expert_ids, int64_t num_rows, int32_t num_experts,
+                  int32_t m_aligned, int32_t* counts, int32_t* padded_offsets, int32_t* dst_row,
+                  int32_t* scratch, void* stream);
+int64_t b200moe_route_scratch_bytes(int64_t num_rows, int32_t num_experts);
+int b200moe_zero_pad_rows(void* buf, const int32_t* counts, const int32_t* padded_offsets,
+                          int32_t num_experts, int64_t cols, float* prob, void* stream);
+int b200moe_scatter_rows(const void* in, const int32_t* dst_row, int64_t num_rows,
+                         int32_t rows_per_src, int64_t cols, void* out, const float* in_prob,
+                         float* out_prob, void* stream);
+int b200moe_combine_rows(const void* in, const int32_t* dst_row, int64_t num_tokens, int32_t topk,
+                         int64_t cols, void* out, void* stream);
+
+/* Last error text of the calling thread ("" if none).  Never NULL. */
+const char* b200moe_last_error(void);
+
+/*
+ * Device-side status word of the current device: 0, or the code of the first bounded wait
+ * that gave up inside a kernel (the kernel then returns early instead of hanging).  Reading
+ * it synchronises the device; clear = 1 resets it.
+ */
+int b200moe_device_status(int clear);
+
+/* ABI version of this header. */
+int b200moe_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200MOE_H_ */
