@@ -61,6 +61,7 @@ _SIGNATURES = {
         ctypes.c_int,
         [c_void_p, c_void_p, c_int64, c_int32, c_int64, c_void_p, c_void_p, c_void_p, c_void_p],
     ),
+    "b200moe_gather_rows": (ctypes.c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p]),
     "b200moe_combine_rows": (ctypes.c_int, [c_void_p, c_void_p, c_int64, c_int32, c_int64, c_void_p, c_void_p]),
     "b200moe_last_error": (c_char_p, []),
     "b200moe_device_status": (ctypes.c_int, [ctypes.c_int]),

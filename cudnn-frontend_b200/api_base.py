@@ -176,5 +176,4 @@ def check_tile_and_cluster(op: OperatorBase, mma_tiler_mn, cluster_shape_mn, m_a
     )
     cluster_tiler_m = (cm // (2 if use_2cta else 1)) * mma_tiler_mn[0]
     op._value_error_if(cluster_tiler_m not in (128, 256), f"Invalid cluster tiler shape: expected cluster_tiler_m in {{128, 256}}, got {cluster_tiler_m}")
-    op._value_error_if(m_aligned % mma_tiler_mn[0] != 0, f"Invalid m_aligned: expected m_aligned to be divisible by mma_tiler_mn[0], got {m_aligned} % {mma_tiler_mn[0]} != 0")
     op._value_error_if(m_aligned <= 0 or m_aligned % 128 != 0, f"m_aligned must be a positive multiple of 128, got {m_aligned}")

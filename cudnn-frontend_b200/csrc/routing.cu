@@ -101,6 +101,21 @@ __global__ void __launch_bounds__(128)
   if (threadIdx.x == 0 && in_prob && out_prob) out_prob[d] = in_prob[r];
 }
 
+// out[r, :] = in[src_row[r], :]
+__global__ void __launch_bounds__(128)
+    gather_rows_kernel(const uint4* __restrict__ in, const int32_t* __restrict__ src_row, int vec_per_row,
+                       uint4* __restrict__ out) {
+  const int64_t r = blockIdx.x;
+  const int s = src_row[r];
+  uint4* dst = out + r * vec_per_row;
+  if (s < 0) {
+    for (int i = threadIdx.x; i < vec_per_row; i += blockDim.x) dst[i] = make_uint4(0, 0, 0, 0);
+    return;
+  }
+  const uint4* src = in + (int64_t)s * vec_per_row;
+  for (int i = threadIdx.x; i < vec_per_row; i += blockDim.x) dst[i] = __ldg(src + i);
+}
+
 // rows [start_e + count_e, end_e) of every expert group are set to zero
 __global__ void __launch_bounds__(128)
     zero_pad_rows_kernel(uint4* __restrict__ buf, const int32_t* __restrict__ counts,
@@ -157,7 +172,7 @@ int b200moe_route(const int32_t* expert_ids, int64_t num_rows, int32_t num_exper
   using namespace b200moe;
   cudaStream_t stream = (cudaStream_t)stream_v;
   if (num_experts <= 0 || num_experts > 1024) return fail(B200MOE_E_SHAPE, "route: num_experts must be in [1, 1024], got %d", num_experts);
-  if (m_aligned <= 0 || m_aligned % 128 != 0) return fail(B200MOE_E_SHAPE, "route: m_aligned must be a positive multiple of 128");
+  if (m_aligned <= 0) return fail(B200MOE_E_SHAPE, "route: m_aligned must be positive");
   if (num_rows < 0 || num_rows > (1ll << 30)) return fail(B200MOE_E_SHAPE, "route: bad num_rows");
   if (!counts || !padded_offsets || !scratch || (num_rows > 0 && (!expert_ids || !dst_row)))
     return fail(B200MOE_E_NULL, "route: null pointer");
@@ -187,6 +202,18 @@ int b200moe_scatter_rows(const void* in, const int32_t* dst_row, int64_t num_row
   if (((uintptr_t)in | (uintptr_t)out) & 15) return fail(B200MOE_E_ALIGN, "scatter_rows: 16-byte alignment required");
   scatter_rows_kernel<<<(unsigned)num_rows, 128, 0, (cudaStream_t)stream>>>((const uint4*)in, dst_row, rows_per_src,
                                                                            (int)(cols / 8), (uint4*)out, in_prob, out_prob);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200MOE_OK;
+}
+
+int b200moe_gather_rows(const void* in, const int32_t* src_row, int64_t num_rows, int64_t cols, void* out, void* stream) {
+  using namespace b200moe;
+  if (num_rows == 0) return B200MOE_OK;
+  if (!in || !src_row || !out) return fail(B200MOE_E_NULL, "gather_rows: null pointer");
+  if (cols <= 0 || cols % 8 != 0 || num_rows < 0 || num_rows > 0x7fffffffll)
+    return fail(B200MOE_E_SHAPE, "gather_rows: cols must be a positive multiple of 8");
+  if (((uintptr_t)in | (uintptr_t)out) & 15) return fail(B200MOE_E_ALIGN, "gather_rows: 16-byte alignment required");
+  gather_rows_kernel<<<(unsigned)num_rows, 128, 0, (cudaStream_t)stream>>>((const uint4*)in, src_row, (int)(cols / 8), (uint4*)out);
   B200_CUDA_CHECK(cudaGetLastError());
   return B200MOE_OK;
 }

@@ -1,0 +1,206 @@
+"""Expert-parallel MoE layer: experts sharded over the ranks of a process group, tokens
+dispatched and combined with all-to-all (NCCL over NVLink on GPUs).
+
+    route -> sort rows by (destination rank, expert) -> exchange counts -> all-to-all dispatch
+    -> group by local expert (padded to 128) -> MXFP8 quantise -> FC1 (+SwiGLU, MXFP8 out)
+    -> FC2 (x gating probability) -> all-to-all combine -> un-permute and sum each token's k rows
+
+The reference has no multi-GPU code at all; this is the layer its kernels are meant to sit in.
+Expert ``e`` lives on rank ``e // (E / G)``.
+
+Two parts:
+* :func:`plan_dispatch` - pure integer index maths plus the tiny count exchange.  It only uses
+  device-agnostic torch ops and ``torch.distributed``, so the same code runs on CUDA/NCCL and on
+  CPU/Gloo ranks (the latter is how the multi-rank logic is tested without GPUs).
+* :class:`ExpertParallelMoE` - holds this rank's expert weights and runs the CUDA path (row
+  movement kernels, quantiser, grouped GEMMs).  CUDA only; there is no CPU implementation.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+
+@dataclass
+class DispatchPlan:
+    num_tokens: int
+    topk: int
+    send_pos: torch.Tensor  # [R] int32: routed row r -> position in the send buffer
+    in_splits: List[int]  # rows sent to each rank
+    out_splits: List[int]  # rows received from each rank
+    recv_dst: torch.Tensor  # [R_recv] int32: received row i -> row of the padded expert-grouped buffer
+    counts_local: torch.Tensor  # [E_local] int32 rows per local expert
+    padded_offsets: torch.Tensor  # [E_local] int32 END offsets (groups padded to m_aligned)
+    m_rows: int  # padded_offsets[-1]
+
+    @property
+    def rows_sent(self) -> int:
+        return sum(self.in_splits)
+
+    @property
+    def rows_received(self) -> int:
+        return sum(self.out_splits)
+
+
+def _all_to_all_counts(counts_by_rank: torch.Tensor, group) -> torch.Tensor:
+    """[G, E_local] rows I send to (rank, expert) -> [G, E_local] rows I receive from (rank, expert)."""
+    if group is None or dist.get_world_size(group) == 1:
+        return counts_by_rank.clone()
+    recv = torch.empty_like(counts_by_rank)
+    dist.all_to_all_single(recv, counts_by_rank.contiguous(), group=group)
+    return recv
+
+
+def plan_dispatch(topk_ids: torch.Tensor, num_experts: int, group=None, m_aligned: int = 128) -> DispatchPlan:
+    """Index maths of one dispatch.  ``topk_ids [T, k]`` holds global expert ids.
+
+    Send order = stable sort of the routed rows by expert id (experts are contiguous per rank, so
+    this is also sorted by destination rank).  A receiver sees rows ordered by (source rank, local
+    expert, original order) and regroups them by local expert with a second stable sort.  One host
+    synchronisation reads the split sizes (needed by ``all_to_all_single``) and the padded row count.
+    """
+    world = 1 if group is None else dist.get_world_size(group)
+    if num_experts % world != 0:
+        raise ValueError(f"num_experts ({num_experts}) must be divisible by the group size ({world})")
+    e_local = num_experts // world
+    t, k = topk_ids.shape
+    dev = topk_ids.device
+    flat = topk_ids.reshape(-1).to(torch.int64)
+    r = flat.numel()
+    order = torch.argsort(flat, stable=True)
+    send_pos = torch.empty(r, dtype=torch.int64, device=dev)
+    send_pos[order] = torch.arange(r, device=dev)
+    counts = torch.bincount(flat, minlength=num_experts).to(torch.int32).view(world, e_local)
+    recv_counts = _all_to_all_counts(counts, group)  # [src rank, local expert]
+    counts_local = recv_counts.sum(0)
+    padded = ((counts_local + m_aligned - 1) // m_aligned) * m_aligned
+    offsets = torch.cumsum(padded, 0)
+    host = torch.cat([counts.sum(1), recv_counts.sum(1), offsets[-1:]]).cpu().tolist()  # the one sync
+    in_splits, out_splits, m_rows = host[:world], host[world : 2 * world], int(host[-1])
+    r_recv = sum(out_splits)
+    # expert of every received row: rows arrive as (src, expert, j)
+    expert_of_slot = torch.arange(e_local, device=dev).repeat(world)
+    ids_recv = torch.repeat_interleave(expert_of_slot, recv_counts.reshape(-1).to(torch.int64), output_size=r_recv)
+    order2 = torch.argsort(ids_recv, stable=True)
+    first = torch.cumsum(counts_local.to(torch.int64), 0) - counts_local
+    starts = (offsets - padded).to(torch.int64)
+    sorted_ids = ids_recv[order2]
+    rank_in_expert = torch.arange(r_recv, device=dev) - first[sorted_ids]
+    recv_dst = torch.empty(r_recv, dtype=torch.int64, device=dev)
+    recv_dst[order2] = starts[sorted_ids] + rank_in_expert
+    return DispatchPlan(t, k, send_pos.to(torch.int32), in_splits, out_splits, recv_dst.to(torch.int32),
+                        counts_local.to(torch.int32), offsets.to(torch.int32), m_rows)  # fmt: skip
+
+
+def exchange_rows(send: torch.Tensor, out_rows: int, in_splits, out_splits, group) -> torch.Tensor:
+    """All-to-all of whole rows (first dimension split)."""
+    if group is None or dist.get_world_size(group) == 1:
+        return send
+    recv = torch.empty((out_rows,) + tuple(send.shape[1:]), dtype=send.dtype, device=send.device)
+    dist.all_to_all_single(recv, send, output_split_sizes=list(out_splits), input_split_sizes=list(in_splits), group=group)
+    return recv
+
+
+class ExpertParallelMoE:
+    """One MoE layer with this rank's ``E / G`` experts resident in HBM as MXFP8.
+
+    ``w1 (2I, H, E_local)`` is the FC1 weight in the 32-row interleaved gate/up order, ``w2 (H, I,
+    E_local)`` the FC2 weight, both float8_e4m3fn K-major with E8M0 scales in the 128x4 layout
+    (as produced by ``synthetic.make_weights`` or by quantising real weights with
+    ``quantize_mxfp8``)."""
+
+    def __init__(self, w1, sfw1, w2, sfw2, num_experts: int, group=None, m_aligned: int = 128):
+        if not w1.is_cuda:
+            raise RuntimeError("ExpertParallelMoE runs on CUDA devices only")
+        from . import grouped_gemm_quant, grouped_gemm_swiglu  # noqa: F401  (fails loudly without the CUDA library)
+
+        self.w1, self.sfw1, self.w2, self.sfw2 = w1, sfw1, w2, sfw2
+        self.num_experts = num_experts
+        self.group = group
+        self.world = 1 if group is None else dist.get_world_size(group)
+        self.e_local = num_experts // self.world
+        self.m_aligned = m_aligned
+        self.hidden = w1.shape[1]
+        self.inter = w2.shape[1]
+        assert w1.shape[0] == 2 * self.inter and w2.shape[0] == self.hidden and w1.shape[2] == self.e_local
+        dev = w1.device
+        self.alpha = torch.ones(self.e_local, dtype=torch.float32, device=dev)
+        self.norm = torch.ones(1, dtype=torch.float32, device=dev)
+        self._ops = {}
+        self.last_plan: Optional[DispatchPlan] = None
+
+    def _fc_ops(self, m_rows: int, bufs):
+        """Operator objects are cached per padded row count (shapes are part of their samples)."""
+        from .grouped_gemm_quant import GroupedGemmQuantSm100
+        from .grouped_gemm_swiglu import GroupedGemmSwigluSm100
+
+        key = m_rows
+        if key not in self._ops:
+            a, sfa, h8, sfh, y, prob, offs = bufs
+            fc1 = GroupedGemmSwigluSm100(a, self.w1, None, h8, sfa, self.sfw1, offs, self.alpha, h8, sample_sfd_row=sfh,
+                                         sample_sfd_col=_dummy_sf_col(self.inter, m_rows, a.device), sample_norm_const=self.norm,
+                                         sf_vec_size=32, m_aligned=self.m_aligned)  # fmt: skip
+            fc2 = GroupedGemmQuantSm100(h8, sfh, offs, self.alpha, y, sample_b=self.w2, sample_sfb=self.sfw2, sample_prob=prob,
+                                        sf_vec_size=32, m_aligned=self.m_aligned)  # fmt: skip
+            assert fc1.check_support() and fc2.check_support()
+            fc1.compile()
+            fc2.compile()
+            self._ops[key] = (fc1, fc2)
+        return self._ops[key]
+
+    def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_prob: torch.Tensor) -> torch.Tensor:
+        """``x [T, H]`` bf16, ``topk_ids [T, k]`` int32 global expert ids, ``topk_prob [T, k]`` f32
+        -> ``[T, H]`` bf16 = sum over the token's k experts of prob * FC2(SwiGLU(FC1(x)))."""
+        from . import moe, ops
+
+        if not x.is_cuda:
+            raise RuntimeError("ExpertParallelMoE.forward needs CUDA tensors")
+        t, k = topk_ids.shape
+        h = self.hidden
+        dev = x.device
+        plan = plan_dispatch(topk_ids, self.num_experts, self.group, self.m_aligned)
+        self.last_plan = plan
+        # dispatch: rows in send order, gating probabilities travel with them
+        send = torch.empty((t * k, h), dtype=torch.bfloat16, device=dev)
+        send_p = torch.empty((t * k,), dtype=torch.float32, device=dev)
+        moe.scatter_rows(x, plan.send_pos, send, rows_per_src=k, in_prob=topk_prob.reshape(-1).contiguous(), out_prob=send_p)
+        recv = exchange_rows(send, plan.rows_received, plan.in_splits, plan.out_splits, self.group)
+        recv_p = exchange_rows(send_p, plan.rows_received, plan.in_splits, plan.out_splits, self.group)
+        m = plan.m_rows
+        if m == 0:
+            y_recv = torch.zeros((plan.rows_received, h), dtype=torch.bfloat16, device=dev)
+        else:
+            # group by local expert (padding rows zero), quantise, FC1, FC2
+            xg = torch.empty((m, h), dtype=torch.bfloat16, device=dev)
+            pg = torch.empty((m,), dtype=torch.float32, device=dev)
+            moe.scatter_rows(recv, plan.recv_dst, xg, rows_per_src=1, in_prob=recv_p, out_prob=pg)
+            moe.zero_pad_rows(xg, plan.counts_local, plan.padded_offsets, pg)
+            a = torch.empty((m, h, 1), dtype=torch.float8_e4m3fn, device=dev)
+            sfa = ops.empty_sf(m, h, 1, device=dev)
+            ops.quantize_mxfp8_out(xg, a.view(m, h), sfa)
+            h8 = torch.empty((m, self.inter, 1), dtype=torch.float8_e4m3fn, device=dev)
+            sfh = ops.empty_sf(m, self.inter, 1, device=dev)
+            y = torch.empty((m, h, 1), dtype=torch.bfloat16, device=dev)
+            prob3 = pg.view(m, 1, 1)
+            fc1, fc2 = self._fc_ops(m, (a, sfa, h8, sfh, y, prob3, plan.padded_offsets))
+            fc1.execute(a, self.w1, None, h8, sfa, self.sfw1, plan.padded_offsets, self.alpha, sfd_row_tensor=sfh, norm_const_tensor=self.norm)
+            fc2.execute(h8, sfh, plan.padded_offsets, self.alpha, y, b_tensor=self.w2, sfb_tensor=self.sfw2, prob_tensor=prob3)
+            # combine: back to arrival order, return to the senders
+            y_recv = moe.gather_rows(y.view(m, h), plan.recv_dst)
+        back = exchange_rows(y_recv, plan.rows_sent, plan.out_splits, plan.in_splits, self.group)
+        return moe.combine_rows(back, plan.send_pos, t, k)
+
+    __call__ = forward
+
+
+def _dummy_sf_col(n_out: int, m_rows: int, device):
+    """Column scale factors are not produced inside the layer, but the operator's validation
+    wants a sample of the right shape; a meta tensor costs no memory."""
+    from . import ops
+
+    shape, stride = ops.sf_shape_stride(n_out, m_rows, 1)
+    return torch.empty_strided(shape, stride, dtype=torch.float8_e8m0fnu, device="meta")

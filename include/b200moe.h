@@ -130,10 +130,11 @@ int b200moe_quantize_mxfp8(const void* x, int64_t rows, int64_t cols, int64_t ld
  *
  * b200moe_route: expert_ids [num_rows] int32 (expert of every routed row, token-major) ->
  *   counts [E] int32, padded_offsets [E] int32 END offsets with each group rounded up to
- *   m_aligned, dst_row [num_rows] int32 = row of the expert-grouped padded buffer (stable:
+ *   m_aligned (1 = compact; the GEMMs need a multiple of 128), dst_row [num_rows] int32 = row of the expert-grouped padded buffer (stable:
  *   rows of one expert keep their order).  scratch: (E + 1) int32, caller-owned.
  * b200moe_scatter_rows: out[dst_row[r], :] = in[r / rows_per_src, :]  (bf16, cols % 8 == 0);
  *   also out_prob[dst_row[r]] = in_prob[r] when both are non-NULL.
+ * b200moe_gather_rows: out[r, :] = in[src_row[r], :] (bf16; a negative index gives a zero row).
  * b200moe_combine_rows: out[t, :] = sum_j in[dst_row[t*topk + j], :] (bf16 in, f32 accumulate,
  *   bf16 out).
  */
@@ -146,6 +147,8 @@ int b200moe_zero_pad_rows(void* buf, const int32_t* counts, const int32_t* padde
 int b200moe_scatter_rows(const void* in, const int32_t* dst_row, int64_t num_rows,
                          int32_t rows_per_src, int64_t cols, void* out, const float* in_prob,
                          float* out_prob, void* stream);
+int b200moe_gather_rows(const void* in, const int32_t* src_row, int64_t num_rows, int64_t cols,
+                        void* out, void* stream);
 int b200moe_combine_rows(const void* in, const int32_t* dst_row, int64_t num_tokens, int32_t topk,
                          int64_t cols, void* out, void* stream);
 

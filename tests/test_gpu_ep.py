@@ -1,0 +1,96 @@
+"""Expert-parallel MoE layer on GPUs: one rank against the layer oracle, and (when the box has
+two GPUs) two NCCL ranks against the single-rank result."""
+
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import mxfp8_oracle as orc
+from tests import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+T, HID, INTER, E, K = 384, 256, 128, 8, 2
+
+
+def _inputs(seed, device):
+    from cudnn_frontend_b200 import synthetic
+
+    g = torch.Generator(device=device).manual_seed(seed)
+    x = torch.randn(T, HID, generator=g, device=device).to(torch.bfloat16)
+    ids = torch.multinomial(torch.ones(T, E, device=device), K, generator=g).to(torch.int32)
+    prob = torch.softmax(torch.randn(T, K, generator=g, device=device), -1)
+    w1, sfw1 = synthetic.make_weights(E, 2 * INTER, HID, seed + 1, device, std=0.05)
+    w2, sfw2 = synthetic.make_weights(E, HID, INTER, seed + 2, device, std=0.05)
+    return x, ids, prob, w1, sfw1, w2, sfw2
+
+
+def test_single_rank_layer_matches_oracle():
+    from cudnn_frontend_b200.ep_layer import ExpertParallelMoE
+
+    x, ids, prob, w1, sfw1, w2, sfw2 = _inputs(3, "cuda")
+    layer = ExpertParallelMoE(w1, sfw1, w2, sfw2, E)
+    y = layer(x, ids, prob)
+    torch.cuda.synchronize()
+    ref = orc.moe_layer_reference(
+        x.float().cpu().numpy(), ids.cpu().numpy(), prob.cpu().numpy(),
+        w1.permute(2, 0, 1).contiguous().view(torch.uint8).cpu().numpy(), H.sf_to_numpy(sfw1, 2 * INTER, HID // 32, E),
+        w2.permute(2, 0, 1).contiguous().view(torch.uint8).cpu().numpy(), H.sf_to_numpy(sfw2, HID, INTER // 32, E), 128,
+    )  # fmt: skip
+    assert H.rel_fro(y.float().cpu().numpy(), ref) <= 2e-2
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _ep_worker(rank, world, port, ret):
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from cudnn_frontend_b200.ep_layer import ExpertParallelMoE
+
+        # every rank builds the same global weights, keeps its shard; tokens differ per rank
+        _, _, _, w1, sfw1, w2, sfw2 = _inputs(3, dev)
+        x, ids, prob, *_ = _inputs(10 + rank, dev)
+        e_local = E // world
+        sl = slice(rank * e_local, (rank + 1) * e_local)
+        sf1 = torch.as_strided(sfw1.view(torch.uint8), (sfw1.numel(),), (1,)).view(E, -1)[sl].contiguous()
+        sf2 = torch.as_strided(sfw2.view(torch.uint8), (sfw2.numel(),), (1,)).view(E, -1)[sl].contiguous()
+        from cudnn_frontend_b200 import ops
+
+        def as_sf(flat, mn, kk):
+            shape, stride = ops.sf_shape_stride(mn, kk, e_local)
+            return torch.as_strided(flat.view(-1).view(torch.float8_e8m0fnu), shape, stride)
+
+        w1l = w1.permute(2, 0, 1)[sl].contiguous().permute(1, 2, 0)
+        w2l = w2.permute(2, 0, 1)[sl].contiguous().permute(1, 2, 0)
+        layer = ExpertParallelMoE(w1l, as_sf(sf1, 2 * INTER, HID), w2l, as_sf(sf2, HID, INTER), E, dist.group.WORLD)
+        y = layer(x, ids, prob)
+        # same tokens through a single-rank layer that owns all experts
+        full = ExpertParallelMoE(w1, sfw1, w2, sfw2, E)
+        y1 = full(x, ids, prob)
+        torch.cuda.synchronize()
+        # row order inside an expert group differs between the two runs, the per-row maths does not
+        ret[rank] = bool(torch.equal(y, y1))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_ranks_equal_single_rank():
+    import torch.multiprocessing as mp
+
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_ep_worker, args=(2, _free_port(), ret), nprocs=2, join=True)
+    assert all(ret.get(r) for r in range(2)), dict(ret)

@@ -1,0 +1,162 @@
+"""CPU-only checks: the C-ABI library loads and exports every declared symbol, and the
+operator classes validate their arguments with the reference's exception types."""
+
+import ctypes
+import logging
+import os
+import re
+
+import pytest
+import torch
+
+import cudnn_frontend_b200 as cf
+from cudnn_frontend_b200 import _build, _lib, api_base, ops
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "b200moe.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(b200moe_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_builds_loads_and_exports_every_declared_symbol():
+    path = _build.build()
+    assert os.path.exists(path)
+    lib = ctypes.CDLL(path)
+    declared = _declared_symbols()
+    assert len(declared) >= 10
+    for name in declared:
+        assert hasattr(lib, name), f"{name} declared in include/b200moe.h but not exported"
+    assert set(declared) == set(_lib.EXPORTED_SYMBOLS)
+    assert _lib.load().b200moe_abi_version() == 1
+    assert _lib.load().b200moe_workspace_bytes(256, 1) == 256 * 128
+    assert _lib.load().b200moe_workspace_bytes(256, 0) == 0
+
+
+def test_c_abi_rejects_bad_arguments_without_touching_a_device():
+    lib = _lib.load()
+    args = _lib.GemmArgs()
+    args.m_rows, args.n, args.k, args.num_experts = 128, 256, 128, 2
+    assert lib.b200moe_fc1_swiglu(ctypes.byref(args), None) == _lib.E_NULL
+    assert "required" in _lib.last_error()
+    assert lib.b200moe_quantize_mxfp8(16, 4, 24, 24, 16, 16, None) == _lib.E_SHAPE  # cols % 16 != 0
+    assert lib.b200moe_route(None, 0, 2000, 128, 16, 16, 16, 16, None) == _lib.E_SHAPE
+    with pytest.raises(ValueError):
+        _lib.check(_lib.E_SHAPE)
+    with pytest.raises(NotImplementedError):
+        _lib.check(_lib.E_UNSUPPORTED)
+    with pytest.raises(RuntimeError):
+        _lib.check(700)
+
+
+def test_sf_shape_and_stride_follow_the_128x4_layout():
+    shape, stride = ops.sf_shape_stride(300, 288, 2)
+    assert shape == (32, 4, 3, 4, 3, 2)
+    assert stride == (16, 4, 3 * 512, 1, 512, 3 * 3 * 512)
+
+
+def test_tuple_dict_unpacks_and_indexes():
+    t = api_base.TupleDict(a=1, b=None, c=3)
+    x, y, z = t
+    assert (x, y, z) == (1, None, 3)
+    assert t[0] == 1 and t["c"] == 3 and t[2] == 3
+    with pytest.raises(IndexError):
+        t[3]
+
+
+def _fc1_samples(m=256, n=256, k=128, e=2, d_dtype=torch.bfloat16):
+    a = torch.empty((m, k, 1), dtype=torch.float8_e4m3fn)
+    b = torch.empty((e, n, k), dtype=torch.float8_e4m3fn).permute(1, 2, 0)
+    c = torch.empty((m, n, 1), dtype=torch.bfloat16)
+    d = torch.empty((m, n // 2, 1), dtype=d_dtype)
+    sfa = ops.empty_sf(m, k, 1, device="cpu")
+    sfb = ops.empty_sf(n, k, e, device="cpu")
+    offs = torch.zeros(e, dtype=torch.int32)
+    alpha = torch.ones(e)
+    return dict(sample_a=a, sample_b=b, sample_c=c, sample_d=d, sample_sfa=sfa, sample_sfb=sfb,
+                sample_padded_offsets=offs, sample_alpha=alpha, sample_d_col=None)  # fmt: skip
+
+
+def test_fc1_check_support_error_classes():
+    ok = _fc1_samples()
+    # sf_vec_size 16 with fp8 inputs is rejected like in the reference
+    vec16 = dict(ok, sample_sfa=ops.empty_sf(256, 256, 1, device="cpu"), sample_sfb=ops.empty_sf(256, 256, 2, device="cpu"))
+    with pytest.raises(ValueError, match="sf_vec_size"):
+        cf.GroupedGemmSwigluSm100(**vec16, sf_vec_size=16).check_support()
+    bad = dict(ok, sample_d=torch.empty((256, 100, 1), dtype=torch.bfloat16))
+    with pytest.raises(ValueError, match="D must have shape"):
+        cf.GroupedGemmSwigluSm100(**bad, sf_vec_size=32).check_support()
+    bad = dict(ok, sample_sfd_row=ops.empty_sf(256, 128, 1, device="cpu"))
+    with pytest.raises(ValueError, match="all None or all not None"):
+        cf.GroupedGemmSwigluSm100(**bad, sf_vec_size=32).check_support()
+    with pytest.raises(ValueError, match="m_aligned"):
+        cf.GroupedGemmSwigluSm100(**ok, sf_vec_size=32, m_aligned=192).check_support()
+    with pytest.raises(ValueError, match="cluster"):
+        cf.GroupedGemmSwigluSm100(**ok, sf_vec_size=32, cluster_shape_mn=(3, 1)).check_support()
+    bad = dict(ok, sample_a=torch.empty((256, 128, 1), dtype=torch.float8_e5m2), sample_b=ok["sample_b"].view(torch.float8_e5m2))
+    with pytest.raises(NotImplementedError):
+        cf.GroupedGemmSwigluSm100(**bad, sf_vec_size=32).check_support()
+    bad = dict(ok, sample_a=torch.empty((128, 256, 1), dtype=torch.float8_e4m3fn).permute(1, 0, 2))
+    with pytest.raises(ValueError, match="k-major"):
+        cf.GroupedGemmSwigluSm100(**bad, sf_vec_size=32).check_support()
+    # a valid configuration gets as far as the device check
+    if not torch.cuda.is_available():
+        with pytest.raises(RuntimeError, match="CUDA"):
+            cf.GroupedGemmSwigluSm100(**ok, sf_vec_size=32).check_support()
+    op = cf.GroupedGemmSwigluSm100(**ok, sf_vec_size=32)
+    with pytest.raises(RuntimeError, match="compile"):
+        op.execute(None, None, None, None, None, None, None, None)
+
+
+def test_fc2_requires_prob_and_one_weight_mode():
+    m, n, k, e = 256, 256, 128, 2
+    a = torch.empty((m, k, 1), dtype=torch.float8_e4m3fn)
+    b = torch.empty((e, n, k), dtype=torch.float8_e4m3fn).permute(1, 2, 0)
+    sfa, sfb = ops.empty_sf(m, k, 1, device="cpu"), ops.empty_sf(n, k, e, device="cpu")
+    d = torch.empty((m, n, 1), dtype=torch.bfloat16)
+    offs, alpha = torch.zeros(e, dtype=torch.int32), torch.ones(e)
+    with pytest.raises(ValueError, match="prob_tensor is required"):
+        cf.GroupedGemmQuantSm100(a, sfa, offs, alpha, d, sample_b=b, sample_sfb=sfb, sf_vec_size=32).check_support()
+    with pytest.raises(ValueError, match="not both"):
+        cf.grouped_gemm_quant_wrapper_sm100(a, sfa, offs, alpha, b_tensor=b, sfb_tensor=sfb, b_ptrs=torch.zeros(2, dtype=torch.int64))
+    with pytest.raises(ValueError, match="Must provide"):
+        cf.grouped_gemm_quant_wrapper_sm100(a, sfa, offs, alpha)
+    prob = torch.ones((m, 1, 1))
+    with pytest.raises(NotImplementedError, match="bias"):
+        cf.GroupedGemmQuantSm100(a, sfa, offs, alpha, d, sample_b=b, sample_sfb=sfb, sample_prob=prob, sf_vec_size=32,
+                                 sample_bias=torch.empty((e, n), dtype=torch.bfloat16).t()).check_support()  # fmt: skip
+    with pytest.raises(ValueError, match="MMA tiler N"):
+        cf.GroupedGemmQuantSm100(a, sfa, offs, alpha, d, sample_b=b, sample_sfb=sfb, sample_prob=prob, sf_vec_size=32,
+                                 mma_tiler_mn=(256, 128)).check_support()  # fmt: skip
+
+
+def test_pointer_tensors_are_validated():
+    from cudnn_frontend_b200.grouped_gemm_quant import _require_pointer_tensor
+
+    with pytest.raises(ValueError):
+        _require_pointer_tensor(torch.zeros(4, dtype=torch.int32), "b_ptrs")
+    with pytest.raises(ValueError):
+        _require_pointer_tensor(torch.zeros(4, dtype=torch.int64), "b_ptrs")  # not on a CUDA device
+    with pytest.raises(ValueError):
+        _require_pointer_tensor([1, 2], "b_ptrs")
+
+
+def test_experimental_warning_is_emitted_once_per_class(caplog):
+    api_base._reset_experimental_api_warning_registry()
+    ok = _fc1_samples()
+    with caplog.at_level(logging.WARNING):
+        cf.GroupedGemmSwigluSm100(**ok, sf_vec_size=32)
+        cf.GroupedGemmSwigluSm100(**ok, sf_vec_size=32)
+    msgs = [r for r in caplog.records if "experimental API" in r.getMessage()]
+    assert len(msgs) == 1
+
+
+def test_interleave_gate_up_matches_oracle():
+    from oracle import mxfp8_oracle as orc
+
+    g = torch.arange(3 * 64 * 4, dtype=torch.float32).reshape(3, 64, 4)
+    u = -g
+    w = cf.interleave_gate_up(g, u)
+    assert torch.equal(w, torch.from_numpy(orc.interleave_gate_up(g.numpy(), u.numpy())))
