@@ -28,6 +28,9 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 METRIC = "MXFP8 grouped-GEMM+SwiGLU TFLOP/s"
+# reduced Mixtral-shape case for profiler captures: same K, a quarter of N, a quarter of the rows;
+# operands (A 33 MB + B 235 MB) still exceed the 126 MB L2
+SMALL_CASE = dict(experts=8, k=4096, n=7168, tokens=4096, topk=2, routing="uniform")
 UNIT = "TFLOP/s"
 FP8_NOMINAL_TFLOPS = 4500.0
 
@@ -207,8 +210,8 @@ def bench_single(args):
     dev = torch.device("cuda", 0)
     stream = torch.cuda.current_stream()
     peaks = load_peaks()
-    cfg = synthetic.CONFIGS["c2"]
-    prob_ = synthetic.make_problem("c2", dev, seed=0, m_aligned=128)
+    cfg = synthetic.CONFIGS["c2"] if args.workload == "c2" else SMALL_CASE
+    prob_ = synthetic.make_problem(cfg, dev, seed=0, m_aligned=128)
     e, n, k = cfg["experts"], cfg["n"], cfg["k"]
     m = prob_["m_rows"]
     flops = prob_["flops"]
@@ -233,6 +236,10 @@ def bench_single(args):
         ms = time_steps(step, args.steps, args.warmup, stream)
     value = flops / (ms * 1e-3) / 1e12
     assert ops.device_status(clear=True) == 0, "a bounded wait inside the kernel gave up"
+    if args.kernel_only:
+        print(json.dumps({"metric": METRIC, "value": value, "unit": UNIT, "ms_per_step": ms, "steps": args.steps, "warmup": args.warmup,
+                          "config": {"workload": f"kernel only, {args.workload}: {cfg}"}, "clocks": clk.summary()}))  # fmt: skip
+        return
 
     # the same call with the bf16 pre-activation C also written (what the reference's wrapper always does)
     step_c, outs_c = make_op(write_c=True)
@@ -409,6 +416,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="own", choices=["own", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the DeepSeek-shape side measurements")
+    ap.add_argument("--workload", default="c2", choices=["c2", "small"], help="c2 = Mixtral-shape FC1 (the benchmark); small = reduced case for profiler captures")
+    ap.add_argument("--kernel-only", action="store_true", help="time the FC1 kernel only (no end-to-end, CPU baseline or side measurements)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "own" else args.warmup
     if args.impl == "reference":

@@ -78,8 +78,9 @@ def load() -> ctypes.CDLL:
     global _lib
     if _lib is not None:
         return _lib
-    path = _build.LIB_PATH
-    if _build.is_stale():
+    override = os.environ.get("B200MOE_LIBRARY")  # load a prebuilt library from another path
+    path = override or _build.LIB_PATH
+    if not override and _build.is_stale():
         try:
             _build.build()
         except RuntimeError:
