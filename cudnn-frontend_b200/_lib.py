@@ -14,6 +14,7 @@ from . import _build
 E_NULL, E_SHAPE, E_ALIGN, E_UNSUPPORTED, E_WORKSPACE, E_DEVICE = -1, -2, -3, -4, -5, -6
 DTYPE_BF16, DTYPE_E4M3 = 0, 1
 FLAG_DISCRETE_COL_SFD = 1
+NOALLOC_MAX_EXPERTS = 256
 
 
 class GemmArgs(Structure):
@@ -49,6 +50,7 @@ class GemmArgs(Structure):
 _SIGNATURES = {
     "b200moe_fc1_swiglu": (ctypes.c_int, [POINTER(GemmArgs), c_void_p]),
     "b200moe_fc2_quant": (ctypes.c_int, [POINTER(GemmArgs), c_void_p]),
+    "b200moe_fc1_swiglu_discrete_noalloc": (ctypes.c_int, [POINTER(GemmArgs), c_void_p]),
     "b200moe_workspace_bytes": (c_int64, [c_int32, c_int32]),
     "b200moe_quantize_mxfp8": (ctypes.c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
     "b200moe_route": (

@@ -768,9 +768,66 @@ static int run_gemm(int epi, const b200moe_gemm_args* a, void* stream_v) {
   return discrete ? launch<EPI_FC2, true>(ta, tb, p, grid, di, stream) : launch<EPI_FC2, false>(ta, tb, p, grid, di, stream);
 }
 
+// ---------------------------------------------------------------------------------------
+// Discrete-weight FC1 for callers that cannot allocate device memory.
+//
+// The per-expert tensor maps normally live in a workspace the caller allocates.  Some callers have
+// no way to do that: code running after an inference server has handed every free byte of the GPU
+// to its own arena, plugins that are given tensors but no allocator handle, and latency-critical
+// loops that must never reach cudaMalloc because it synchronises the whole device.  For them the
+// maps live in the fixed array below, which is part of the library image: every GPU that loads
+// the library holds these bytes from load until the process exits.
+//
+// The array's name is only a host-side handle; the device address is looked up once per device
+// (with that device current) and cached.  All calls on a device share the array, and it keeps
+// whatever the previous call wrote: each call rewrites the slots of its own experts before its
+// GEMM reads them, so nothing has to be cleared, but two calls that overlap on the same GPU
+// (different streams) race on it.
+// ---------------------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_noalloc_scratch[B200MOE_NOALLOC_SCRATCH_BYTES];
+
+static int noalloc_scratch_address(void** out) {
+  static void* address[64] = {nullptr};
+  static std::mutex mu;
+  int dev = 0;
+  B200_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(B200MOE_E_DEVICE, "device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (address[dev] == nullptr) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess || p == nullptr)
+      return fail(e != cudaSuccess ? (int)e : B200MOE_E_DEVICE, "cudaGetSymbolAddress(scratch) failed on device %d: %s", dev,
+                  cudaGetErrorString(e));
+    address[dev] = p;
+  }
+  *out = address[dev];
+  return B200MOE_OK;
+}
+
 }  // namespace b200moe
 
 extern "C" {
+
+int b200moe_fc1_swiglu_discrete_noalloc(const b200moe_gemm_args* args, void* stream) {
+  using namespace b200moe;
+  if (!args) return fail(B200MOE_E_NULL, "args is NULL");
+  if (!args->b_ptrs || !args->sfb_ptrs || args->b || args->sfb)
+    return fail(B200MOE_E_NULL, "fc1_swiglu_discrete_noalloc: takes discrete weights only (b_ptrs and sfb_ptrs, no b / sfb)");
+  if (args->num_experts > B200MOE_NOALLOC_MAX_EXPERTS)
+    return fail(B200MOE_E_SHAPE, "fc1_swiglu_discrete_noalloc: %d experts exceed the built-in scratch (at most %d); use b200moe_fc1_swiglu with a caller workspace",
+                args->num_experts, B200MOE_NOALLOC_MAX_EXPERTS);
+  if (b200moe_workspace_bytes(args->num_experts, 1) > (int64_t)B200MOE_NOALLOC_SCRATCH_BYTES)
+    return fail(B200MOE_E_SHAPE, "fc1_swiglu_discrete_noalloc: built-in scratch too small for %d experts", args->num_experts);
+  if (args->m_rows == 0 || args->num_experts <= 0) return run_gemm(EPI_FC1, args, stream);
+  void* scratch = nullptr;
+  int rc = noalloc_scratch_address(&scratch);
+  if (rc) return rc;
+  b200moe_gemm_args local = *args;
+  local.workspace = scratch;
+  local.workspace_bytes = B200MOE_NOALLOC_SCRATCH_BYTES;
+  return run_gemm(EPI_FC1, &local, stream);
+}
 
 int b200moe_fc1_swiglu(const b200moe_gemm_args* args, void* stream) { return b200moe::run_gemm(b200moe::EPI_FC1, args, stream); }
 

@@ -97,6 +97,25 @@ typedef struct b200moe_gemm_args {
 int b200moe_fc1_swiglu(const b200moe_gemm_args* args, void* stream);
 
 /*
+ * Discrete-weight FC1 that allocates nothing and needs no workspace.  It has no counterpart in
+ * the reference.  It is b200moe_fc1_swiglu in discrete mode (b_ptrs / sfb_ptrs; args->workspace is
+ * ignored) with the per-expert descriptor table kept in a fixed device array inside the library
+ * (B200MOE_NOALLOC_SCRATCH_BYTES per GPU, held from library load to process exit) instead of in
+ * caller memory.  Meant for callers that cannot obtain device memory at call time: code that runs
+ * after the host application has given all free GPU memory to its own arena, plugins that receive
+ * tensors but no allocator, and loops that must never trigger cudaMalloc (it synchronises the
+ * device).  Limits and rules:
+ *   - at most B200MOE_NOALLOC_MAX_EXPERTS experts; more returns B200MOE_E_SHAPE;
+ *   - the first call on each device looks up the array's device address (cudaGetSymbolAddress,
+ *     with that device current); make that first call outside any stream capture;
+ *   - every call on a device uses the same array: calls that overlap on the GPU (different
+ *     streams) race with each other; calls ordered on one stream are safe.
+ */
+#define B200MOE_NOALLOC_MAX_EXPERTS 256
+#define B200MOE_NOALLOC_SCRATCH_BYTES (B200MOE_NOALLOC_MAX_EXPERTS * 256)
+int b200moe_fc1_swiglu_discrete_noalloc(const b200moe_gemm_args* args, void* stream);
+
+/*
  * FC2: D = quant(alpha_e * acc * prob); bf16 D + per-expert amax, or E4M3 D + row/column
  * E8M0 scale factors.
  * Replaces GroupedGemmQuantSm100.execute
