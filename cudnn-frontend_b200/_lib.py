@@ -14,6 +14,8 @@ from . import _build
 E_NULL, E_SHAPE, E_ALIGN, E_UNSUPPORTED, E_WORKSPACE, E_DEVICE = -1, -2, -3, -4, -5, -6
 DTYPE_BF16, DTYPE_E4M3 = 0, 1
 FLAG_DISCRETE_COL_SFD = 1
+FLAG_TILE_SINGLE = 2
+FLAG_TILE_PAIR = 4
 NOALLOC_MAX_EXPERTS = 256
 
 

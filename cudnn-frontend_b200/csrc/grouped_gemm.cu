@@ -4,21 +4,29 @@
 //        32-column blocks of C) ; per-expert amax, or row / column MXFP8 re-quantisation.
 //   FC2: D = alpha_e acc * prob ; bf16 + amax, or E4M3 + row / column E8M0 scale factors.
 //
-// One persistent CTA per SM walks a static tile schedule derived on the device from the
-// per-expert END offsets.  Warp roles:
-//   warp 0      producer: TMA loads of the A / B tiles (128-byte swizzle) and untiled bulk
-//               copies of the 512-byte scale-factor chunks into a 4-stage shared-memory ring
+// Persistent kernel, one CTA per SM, walking a static tile schedule derived on the device from
+// the per-expert END offsets.  Warp roles:
+//   warp 0      producer: TMA loads of the A / B tiles (128-byte swizzle) and of the 512-byte
+//               scale-factor chunks into a shared-memory ring
 //   warp 1      TMEM owner and MMA issuer: tcgen05.cp moves the scale factors to TMEM, then
-//               tcgen05.mma.kind::mxf8f6f4.block_scale (128 x 256 x 32) accumulates into TMEM
+//               tcgen05.mma.kind::mxf8f6f4.block_scale accumulates into TMEM
 //   warps 2..9  epilogue: tcgen05.ld, alpha / SwiGLU / prob / amax / re-quantisation, stores
+//
+// Two tile modes, one template:
+//   single  one CTA computes 128 x 256 (cta_group::1), 4 stages of 48 KB, scale chunks by untiled
+//           bulk copies.  Suits small expert groups (no padding beyond 128 rows).
+//   pair    two CTAs of a (2,1,1) cluster compute 256 x 256 (cta_group::2): each loads its own
+//           128 rows of A and its own 128-row half of B, so a B tile crosses L2 -> SM once per
+//           256 rows; 6 stages of 33.5 KB.  Only the leader issues MMAs; every load of either CTA
+//           credits the leader's "full" barrier; tcgen05.commit releases the stage in both CTAs.
 //
 // TMEM (512 columns): accumulator 0 at columns [0,256), accumulator 1 at [224,480), scale
 // factors at [480,512).  The two accumulators share 32 columns; the epilogue drains those
 // first (even tiles from the top, odd tiles from the bottom) and then lets the MMA warp start
 // the next tile while it finishes the rest.
 //
-// No cluster launch and no multicast: every CTA loads what it needs into its own shared
-// memory, so the same binary serves single- and multi-GPU processes.
+// Every CTA loads what it needs into its own shared memory with plain (one-destination) TMA
+// loads, so the same binary serves single- and multi-GPU processes.
 #include <stdarg.h>
 #include <stdio.h>
 #include <string.h>
@@ -33,18 +41,16 @@ namespace b200moe {
 // ---------------------------------------------------------------------------------------
 // Tile configuration
 // ---------------------------------------------------------------------------------------
-constexpr int BM = 128;
+constexpr int BM = 128;  // rows per CTA
 constexpr int BN = 256;
 constexpr int BK = 128;  // bytes == elements (E4M3); one 128-byte swizzle row
-constexpr int STAGES = 4;
 constexpr int A_STAGE_BYTES = BM * BK;  // 16 KiB
-constexpr int B_STAGE_BYTES = BN * BK;  // 32 KiB
 constexpr int SFA_STAGE_BYTES = 512;
 constexpr int SFB_STAGE_BYTES = 1024;
 constexpr int NUM_EPI_WARPS = 8;
 constexpr int NUM_THREADS = (2 + NUM_EPI_WARPS) * 32;
 constexpr int MAX_EXPERTS = 1024;
-constexpr int RASTER_GROUP_M = 8;  // M tiles of one expert that share a B tile back to back
+constexpr int RASTER_GROUP_M = 8;  // row tiles of one expert that share a B tile back to back
 
 constexpr int TMEM_COLS = 512;
 constexpr int TMEM_ACC1_COL = 224;
@@ -56,7 +62,13 @@ constexpr int ST_MMA_FULL = 102;
 constexpr int ST_MMA_OVERLAP = 103;
 constexpr int ST_EPI_ACC = 104;
 
-struct SmemLayout {
+template <bool kPair>
+struct Cfg {
+  static constexpr int STAGES = kPair ? 6 : 4;
+  static constexpr int B_ROWS = kPair ? 128 : 256;  // rows of B this CTA loads per stage
+  static constexpr int B_STAGE_BYTES = B_ROWS * BK;
+  static constexpr int TILE_M = kPair ? 256 : 128;  // rows of one scheduled tile
+  static constexpr int CTAS = kPair ? 2 : 1;
   static constexpr int A_OFF = 0;
   static constexpr int B_OFF = A_OFF + STAGES * A_STAGE_BYTES;
   static constexpr int SFA_OFF = B_OFF + STAGES * B_STAGE_BYTES;
@@ -66,9 +78,11 @@ struct SmemLayout {
   static constexpr int MISC_OFF = BAR_OFF + NUM_BARS * 8;  // tmem ptr, abort flag, total tiles
   static constexpr int PREFIX_OFF = MISC_OFF + 16;         // (E + 1) int32 tile prefix
   static constexpr int TOTAL = PREFIX_OFF + (MAX_EXPERTS + 1) * 4;
+  static constexpr int SMEM_BYTES = TOTAL + 1024;  // slack for manual 1024-byte alignment
+  // bytes credited to a "full" barrier per stage (both CTAs of a pair together)
+  static constexpr uint32_t TX_BYTES = CTAS * (A_STAGE_BYTES + B_STAGE_BYTES + SFA_STAGE_BYTES + SFB_STAGE_BYTES);
 };
-constexpr int SMEM_BYTES = SmemLayout::TOTAL + 1024;  // slack for manual 1024-byte alignment
-static_assert(SMEM_BYTES <= 232448, "shared memory budget exceeded");
+static_assert(Cfg<false>::SMEM_BYTES <= 232448 && Cfg<true>::SMEM_BYTES <= 232448, "shared memory budget exceeded");
 
 enum : int { EPI_FC1 = 0, EPI_FC2 = 1 };
 
@@ -76,7 +90,7 @@ struct GemmParams {
   const uint8_t* sfa;
   const uint8_t* sfb;         // dense: expert e at sfb + e * sfb_expert_bytes
   const int64_t* sfb_ptrs;    // discrete
-  const CUtensorMap* b_maps;  // discrete: E tensor maps in the workspace
+  const CUtensorMap* b_maps;  // discrete: E tensor maps of B, then E tensor maps of SFB, in the workspace
   const int32_t* offsets;
   const float* alpha;
   const float* prob;
@@ -104,14 +118,14 @@ struct GemmParams {
 // Tile schedule.  Expert e owns tiles [prefix[e], prefix[e+1]); inside an expert tiles run
 // in groups of RASTER_GROUP_M row tiles, row tile fastest, so that CTAs working on adjacent
 // schedule slots read the same B tile (L2 reuse) and every B tile of a small expert is
-// fetched from HBM once.
+// fetched from HBM once.  A row tile is 128 rows (single) or 256 rows (pair).
 // ---------------------------------------------------------------------------------------
 struct Tile {
-  int expert, row0, n_tile;
+  int expert, row0, n_tile, row_end;
 };
 
 __device__ __forceinline__ Tile decode_tile(const int* prefix, const int32_t* offsets, int num_experts,
-                                            int n_tiles, int t) {
+                                            int n_tiles, int tile_m, int t) {
   int lo = 0, hi = num_experts;  // find e with prefix[e] <= t < prefix[e + 1]
   while (hi - lo > 1) {
     const int mid = (lo + hi) >> 1;
@@ -129,7 +143,8 @@ __device__ __forceinline__ Tile decode_tile(const int* prefix, const int32_t* of
   tile.expert = e;
   tile.n_tile = jj / gsize;
   const int start = e == 0 ? 0 : offsets[e - 1];
-  tile.row0 = start + (first_m + jj % gsize) * BM;
+  tile.row0 = start + (first_m + jj % gsize) * tile_m;
+  tile.row_end = offsets[e];
   return tile;
 }
 
@@ -206,25 +221,33 @@ __device__ __forceinline__ uint32_t quant_col_block(uint8_t* dst, bool do_store,
 // ---------------------------------------------------------------------------------------
 // The kernel
 // ---------------------------------------------------------------------------------------
-template <int kEpi, bool kDiscrete>
+template <int kEpi, bool kDiscrete, bool kPair>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-    grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                        const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+    grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                        const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
+                        const GemmParams p) {
+  using C = Cfg<kPair>;
+  constexpr int STAGES = C::STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const uint32_t smem_base = smem_u32(smem);
-  const uint32_t bar_base = smem_base + SmemLayout::BAR_OFF;
+  const uint32_t bar_base = smem_base + C::BAR_OFF;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
   auto acc_full_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + b); };
   const uint32_t overlap_bar = bar_base + 8u * (2 * STAGES + 2);
-  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(smem + SmemLayout::MISC_OFF);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SmemLayout::MISC_OFF + 4);
-  int* total_tiles_smem = reinterpret_cast<int*>(smem + SmemLayout::MISC_OFF + 8);
-  int* prefix = reinterpret_cast<int*>(smem + SmemLayout::PREFIX_OFF);
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(smem + C::MISC_OFF);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::MISC_OFF + 4);
+  int* total_tiles_smem = reinterpret_cast<int*>(smem + C::MISC_OFF + 8);
+  int* prefix = reinterpret_cast<int*>(smem + C::PREFIX_OFF);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  // pair mode: rank 0 of the 2-CTA cluster is the leader (issues the MMAs, owns the "full" and
+  // "overlap" barriers); a scheduled tile is 256 rows and this CTA covers rows [128 rank, +128)
+  const uint32_t cta_rank = kPair ? cluster_ctarank() : 0u;
+  const int sched_id = kPair ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int sched_stride = kPair ? (int)(gridDim.x >> 1) : (int)gridDim.x;
 
   // ---- set-up -----------------------------------------------------------------------
   if (threadIdx.x == 0) {
@@ -234,15 +257,24 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     }
     mbar_init(acc_full_bar(0), 1);
     mbar_init(acc_full_bar(1), 1);
-    mbar_init(overlap_bar, NUM_EPI_WARPS);
+    mbar_init(overlap_bar, C::CTAS * NUM_EPI_WARPS);
     *abort_flag = 0;
     fence_mbar_init();
     prefetch_tensormap(&tmap_a);
     if (!kDiscrete) prefetch_tensormap(&tmap_b);
+    if (kPair) {
+      prefetch_tensormap(&tmap_sfa);
+      if (!kDiscrete) prefetch_tensormap(&tmap_sfb);
+    }
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_ptr_smem), TMEM_COLS);
-    tmem_relinquish();
+    if (kPair) {
+      tmem_alloc_pair(smem_u32(tmem_ptr_smem), TMEM_COLS);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(smem_u32(tmem_ptr_smem), TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   if (warp == 2) {
     // tile prefix over experts: lane l scans a contiguous chunk, then a warp scan of the sums
@@ -252,7 +284,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     for (int e = e0; e < min(e0 + chunk, p.num_experts); ++e) {
       const int start = e == 0 ? 0 : p.offsets[e - 1];
       const int rows = max(p.offsets[e] - start, 0);
-      sum += ((rows + BM - 1) / BM) * p.n_tiles;
+      sum += ((rows + C::TILE_M - 1) / C::TILE_M) * p.n_tiles;
     }
     int incl = sum;
 #pragma unroll
@@ -265,7 +297,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       prefix[e] = run;
       const int start = e == 0 ? 0 : p.offsets[e - 1];
       const int rows = max(p.offsets[e] - start, 0);
-      run += ((rows + BM - 1) / BM) * p.n_tiles;
+      run += ((rows + C::TILE_M - 1) / C::TILE_M) * p.n_tiles;
     }
     if (lane == 31) {
       prefix[p.num_experts] = incl;
@@ -274,6 +306,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
   }
   tc_fence_before();
   __syncthreads();
+  if (kPair) {
+    // barriers of both CTAs are initialised before either touches the other's
+    cluster_arrive();
+    cluster_wait();
+  }
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr_smem;
   const int total_tiles = *total_tiles_smem;
@@ -284,50 +321,75 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        const Tile tile = decode_tile(prefix, p.offsets, p.num_experts, p.n_tiles, t);
+      for (int t = sched_id; t < total_tiles && ok; t += sched_stride) {
+        const Tile tile = decode_tile(prefix, p.offsets, p.num_experts, p.n_tiles, C::TILE_M, t);
         const int n0 = tile.n_tile * BN;
-        const uint8_t* sfa_src = p.sfa + (int64_t)(tile.row0 / BM) * p.rest_k * 512;
-        const uint8_t* sfb_e;
+        const int my_row0 = tile.row0 + (int)cta_rank * BM;
+        const int nblk0 = n0 / 128;
         const CUtensorMap* bmap = &tmap_b;
+        const CUtensorMap* sfbmap = &tmap_sfb;
         if (kDiscrete) {
-          sfb_e = reinterpret_cast<const uint8_t*>(p.sfb_ptrs[tile.expert]);
           bmap = p.b_maps + tile.expert;
           tensormap_fence_acquire(bmap);
-        } else {
-          sfb_e = p.sfb + (int64_t)tile.expert * p.sfb_expert_bytes;
+          if (kPair) {
+            sfbmap = p.b_maps + p.num_experts + tile.expert;
+            tensormap_fence_acquire(sfbmap);
+          }
         }
-        const int nblk0 = n0 / 128;
-        const int sfb_chunks = min(2, p.n_blocks - nblk0);
-        const uint32_t tx = A_STAGE_BYTES + B_STAGE_BYTES + SFA_STAGE_BYTES + 512u * sfb_chunks;
-        for (int kt = 0; kt < p.k_tiles; ++kt) {
-          if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, ST_PRODUCER_EMPTY)) { ok = false; break; }
-          const uint32_t fb = full_bar(stage);
-          mbar_arrive_expect_tx(fb, tx);
-          tma_load_2d(smem_base + SmemLayout::A_OFF + stage * A_STAGE_BYTES, &tmap_a, fb, kt * BK, tile.row0);
-          if (kDiscrete)
-            tma_load_2d(smem_base + SmemLayout::B_OFF + stage * B_STAGE_BYTES, bmap, fb, kt * BK, n0);
-          else
-            tma_load_3d(smem_base + SmemLayout::B_OFF + stage * B_STAGE_BYTES, bmap, fb, kt * BK, n0, tile.expert);
-          bulk_load(smem_base + SmemLayout::SFA_OFF + stage * SFA_STAGE_BYTES, sfa_src + (int64_t)kt * 512, 512, fb);
-          for (int j = 0; j < sfb_chunks; ++j)
-            bulk_load(smem_base + SmemLayout::SFB_OFF + stage * SFB_STAGE_BYTES + j * 512,
-                      sfb_e + ((int64_t)(nblk0 + j) * p.rest_k + kt) * 512, 512, fb);
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        if constexpr (kPair) {
+          // every load of either CTA credits the leader's barrier of this stage
+          for (int kt = 0; kt < p.k_tiles; ++kt) {
+            if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, ST_PRODUCER_EMPTY)) { ok = false; break; }
+            if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(stage), C::TX_BYTES);
+            const uint32_t fb = map_to_cta(full_bar(stage), 0);
+            tma_load_2d_pair(smem_base + C::A_OFF + stage * A_STAGE_BYTES, &tmap_a, fb, kt * BK, my_row0);
+            if (kDiscrete)
+              tma_load_2d_pair(smem_base + C::B_OFF + stage * C::B_STAGE_BYTES, bmap, fb, kt * BK, n0 + (int)cta_rank * 128);
+            else
+              tma_load_3d_pair(smem_base + C::B_OFF + stage * C::B_STAGE_BYTES, bmap, fb, kt * BK, n0 + (int)cta_rank * 128,
+                               tile.expert);
+            tma_load_3d_pair(smem_base + C::SFA_OFF + stage * SFA_STAGE_BYTES, &tmap_sfa, fb, 0, kt, my_row0 / BM);
+            if (kDiscrete)
+              tma_load_3d_pair(smem_base + C::SFB_OFF + stage * SFB_STAGE_BYTES, sfbmap, fb, 0, kt, nblk0);
+            else
+              tma_load_4d_pair(smem_base + C::SFB_OFF + stage * SFB_STAGE_BYTES, sfbmap, fb, 0, kt, nblk0, tile.expert);
+            if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          }
+        } else {
+          const uint8_t* sfa_src = p.sfa + (int64_t)(tile.row0 / BM) * p.rest_k * 512;
+          const uint8_t* sfb_e = kDiscrete ? reinterpret_cast<const uint8_t*>(p.sfb_ptrs[tile.expert])
+                                           : p.sfb + (int64_t)tile.expert * p.sfb_expert_bytes;
+          const int sfb_chunks = min(2, p.n_blocks - nblk0);
+          const uint32_t tx = A_STAGE_BYTES + C::B_STAGE_BYTES + SFA_STAGE_BYTES + 512u * sfb_chunks;
+          for (int kt = 0; kt < p.k_tiles; ++kt) {
+            if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, ST_PRODUCER_EMPTY)) { ok = false; break; }
+            const uint32_t fb = full_bar(stage);
+            mbar_arrive_expect_tx(fb, tx);
+            tma_load_2d(smem_base + C::A_OFF + stage * A_STAGE_BYTES, &tmap_a, fb, kt * BK, tile.row0);
+            if (kDiscrete)
+              tma_load_2d(smem_base + C::B_OFF + stage * C::B_STAGE_BYTES, bmap, fb, kt * BK, n0);
+            else
+              tma_load_3d(smem_base + C::B_OFF + stage * C::B_STAGE_BYTES, bmap, fb, kt * BK, n0, tile.expert);
+            bulk_load(smem_base + C::SFA_OFF + stage * SFA_STAGE_BYTES, sfa_src + (int64_t)kt * 512, 512, fb);
+            for (int j = 0; j < sfb_chunks; ++j)
+              bulk_load(smem_base + C::SFB_OFF + stage * SFB_STAGE_BYTES + j * 512,
+                        sfb_e + ((int64_t)(nblk0 + j) * p.rest_k + kt) * 512, 512, fb);
+            if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          }
         }
       }
     }
     __syncwarp();
   } else if (warp == 1) {
-    // ================= MMA issuer =======================================================
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_mxf8(BM, BN);
+    // ================= MMA issuer (the leader CTA only, in pair mode) =====================
+    if (lane == 0 && cta_rank == 0) {
+      constexpr uint32_t idesc = make_idesc_mxf8(C::TILE_M, BN);
       int stage = 0;
       uint32_t phase = 0;
       uint32_t sf_buf = 0;
       int it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
+      for (int t = sched_id; t < total_tiles && ok; t += sched_stride, ++it) {
         const uint32_t acc = tmem_base + ((it & 1) ? TMEM_ACC1_COL : 0);
         if (it > 0) {
           // previous tile's epilogue has drained the 32 columns both accumulators share
@@ -339,25 +401,39 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           tc_fence_after();
           const uint32_t sfa_t = tmem_base + TMEM_SF_COL + 16 * sf_buf;
           const uint32_t sfb_t = sfa_t + 4;
-          const uint32_t sfa_s = smem_base + SmemLayout::SFA_OFF + stage * SFA_STAGE_BYTES;
-          const uint32_t sfb_s = smem_base + SmemLayout::SFB_OFF + stage * SFB_STAGE_BYTES;
-          tmem_cp_sf(sfa_t, make_smem_desc(sfa_s, 0, 128, 0));
-          tmem_cp_sf(sfb_t, make_smem_desc(sfb_s, 0, 128, 0));
-          tmem_cp_sf(sfb_t + 4, make_smem_desc(sfb_s + 512, 0, 128, 0));
-          const uint64_t adesc = make_smem_desc(smem_base + SmemLayout::A_OFF + stage * A_STAGE_BYTES, 16, 1024, 2);
-          const uint64_t bdesc = make_smem_desc(smem_base + SmemLayout::B_OFF + stage * B_STAGE_BYTES, 16, 1024, 2);
+          const uint32_t sfa_s = smem_base + C::SFA_OFF + stage * SFA_STAGE_BYTES;
+          const uint32_t sfb_s = smem_base + C::SFB_OFF + stage * SFB_STAGE_BYTES;
+          const uint64_t adesc = make_smem_desc(smem_base + C::A_OFF + stage * A_STAGE_BYTES, 16, 1024, 2);
+          const uint64_t bdesc = make_smem_desc(smem_base + C::B_OFF + stage * C::B_STAGE_BYTES, 16, 1024, 2);
           const int k_left = p.k - kt * BK;
           const int kblocks = min(4, (k_left + 31) / 32);
-          for (int kb = 0; kb < kblocks; ++kb) {
-            // advance 32 bytes along K inside the 128-byte swizzle row: +2 in 16-byte units
-            mma_mxf8_ss(acc, adesc + 2 * kb, bdesc + 2 * kb, idesc_with_sf_id(idesc, kb, kb), sfa_t, sfb_t,
-                        (kt | kb) != 0);
+          if constexpr (kPair) {
+            // one instruction acts on both CTAs: each copies from its own smem to its own TMEM
+            tmem_cp_sf_pair(sfa_t, make_smem_desc(sfa_s, 0, 128, 0));
+            tmem_cp_sf_pair(sfb_t, make_smem_desc(sfb_s, 0, 128, 0));
+            tmem_cp_sf_pair(sfb_t + 4, make_smem_desc(sfb_s + 512, 0, 128, 0));
+            for (int kb = 0; kb < kblocks; ++kb)
+              mma_mxf8_ss_pair(acc, adesc + 2 * kb, bdesc + 2 * kb, idesc_with_sf_id(idesc, kb, kb), sfa_t, sfb_t,
+                               (kt | kb) != 0);
+            tc_commit_pair(empty_bar(stage), 3);  // frees this stage in both CTAs
+          } else {
+            tmem_cp_sf(sfa_t, make_smem_desc(sfa_s, 0, 128, 0));
+            tmem_cp_sf(sfb_t, make_smem_desc(sfb_s, 0, 128, 0));
+            tmem_cp_sf(sfb_t + 4, make_smem_desc(sfb_s + 512, 0, 128, 0));
+            for (int kb = 0; kb < kblocks; ++kb) {
+              // advance 32 bytes along K inside the 128-byte swizzle row: +2 in 16-byte units
+              mma_mxf8_ss(acc, adesc + 2 * kb, bdesc + 2 * kb, idesc_with_sf_id(idesc, kb, kb), sfa_t, sfb_t,
+                          (kt | kb) != 0);
+            }
+            tc_commit(empty_bar(stage));  // frees the smem stage once these MMAs have read it
           }
-          tc_commit(empty_bar(stage));  // frees the smem stage once these MMAs have read it
           sf_buf ^= 1;
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
-        if (ok) tc_commit(acc_full_bar(it & 1));
+        if (ok) {
+          if constexpr (kPair) tc_commit_pair(acc_full_bar(it & 1), 3);
+          else tc_commit(acc_full_bar(it & 1));
+        }
       }
     }
     __syncwarp();
@@ -368,13 +444,19 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     const int half = ew >> 2;           // column half of the tile: [128 half, 128 half + 128)
     const int r_in_tile = quarter * 32 + lane;
     const float norm_const = p.norm_const ? *p.norm_const : 1.0f;
+    const uint32_t overlap_target = kPair ? map_to_cta(overlap_bar, 0) : overlap_bar;
+    auto arrive_overlap = [&]() {
+      if (kPair) mbar_arrive_cluster(overlap_target); else mbar_arrive(overlap_bar);
+    };
     int it = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
-      const Tile tile = decode_tile(prefix, p.offsets, p.num_experts, p.n_tiles, t);
+    for (int t = sched_id; t < total_tiles && ok; t += sched_stride, ++it) {
+      Tile tile = decode_tile(prefix, p.offsets, p.num_experts, p.n_tiles, C::TILE_M, t);
+      tile.row0 += (int)cta_rank * BM;  // this CTA's 128 rows
       const int n0 = tile.n_tile * BN;
       const int row = tile.row0 + r_in_tile;
-      const bool row_ok = row < p.m_rows;
+      // in pair mode the second half of a 256-row tile may lie beyond the expert's last row
+      const bool row_ok = row < min(p.m_rows, tile.row_end);
       const float alpha = p.alpha[tile.expert];
       const float prob = (p.prob && row_ok) ? p.prob[row] : 1.0f;
       const uint32_t acc = tmem_base + ((it & 1) ? TMEM_ACC1_COL : 0) + ((uint32_t)(quarter * 32) << 16);
@@ -400,7 +482,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           if (i == 0) {
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(overlap_bar);
+            if (lane == 0) arrive_overlap();
           }
           const int cn = n0 + col;          // column of C
           const int dn = (n0 >> 1) + half * 64 + pp * 32;  // column of D
@@ -418,8 +500,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             g[j] = ((s * g[j]) * u[j]) * prob;
           }
           if (!p.d_is_fp8) {
+            if (row_ok) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) thread_amax = fmaxf(thread_amax, fabsf(g[j]));
+              for (int j = 0; j < 32; ++j) thread_amax = fmaxf(thread_amax, fabsf(g[j]));
+            }
             if (row_ok) store_bf16x32(reinterpret_cast<__nv_bfloat16*>(p.d) + (int64_t)row * p.n_out + dn, g);
           } else {
             if (row_ok) {
@@ -443,7 +527,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 rb = ((tile.row0 - start) >> 5) + quarter;
                 rest = ((p.offsets[tile.expert] - start) / 32 + 3) / 4;
               }
-              p.sfd_col[blk_base + sf_offset(dn + lane, rb, rest)] = (uint8_t)sfc;
+              if (tile.row0 + quarter * 32 < min(p.m_rows, tile.row_end)) p.sfd_col[blk_base + sf_offset(dn + lane, rb, rest)] = (uint8_t)sfc;
             }
           }
         }
@@ -469,15 +553,17 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           if (i == 0) {
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(overlap_bar);
+            if (lane == 0) arrive_overlap();
           }
           const int dn = n0 + col;
           if (dn >= p.n) continue;
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = (v[j] * alpha) * prob;
           if (!p.d_is_fp8) {
+            if (row_ok) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) thread_amax = fmaxf(thread_amax, fabsf(v[j]));
+              for (int j = 0; j < 32; ++j) thread_amax = fmaxf(thread_amax, fabsf(v[j]));
+            }
             if (row_ok) store_bf16x32(reinterpret_cast<__nv_bfloat16*>(p.d) + (int64_t)row * p.n_out + dn, v);
           } else {
             if (row_ok) {
@@ -499,7 +585,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 rb = ((tile.row0 - start) >> 5) + quarter;
                 rest = ((p.offsets[tile.expert] - start) / 32 + 3) / 4;
               }
-              p.sfd_col[blk_base + sf_offset(dn + lane, rb, rest)] = (uint8_t)sfc;
+              if (tile.row0 + quarter * 32 < min(p.m_rows, tile.row_end)) p.sfd_col[blk_base + sf_offset(dn + lane, rb, rest)] = (uint8_t)sfc;
             }
           }
         }
@@ -529,9 +615,16 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
   // ---- teardown ----------------------------------------------------------------------
   tc_fence_before();
   __syncthreads();
+  if (kPair) {
+    // the peer may still arrive on this CTA's barriers and the leader's MMAs write the peer's TMEM:
+    // neither CTA frees anything before both are done
+    cluster_arrive();
+    cluster_wait();
+  }
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, TMEM_COLS);
+    if (kPair) tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    else tmem_dealloc(tmem_base, TMEM_COLS);
   }
 }
 
@@ -542,19 +635,24 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 // host never needs the pointer values (the launch stays capturable in a CUDA graph).
 // ---------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(32)
-    build_expert_tensormaps_kernel(const __grid_constant__ CUtensorMap proto, const int64_t* b_ptrs,
-                                   const void* fallback, CUtensorMap* out, int num_experts) {
+    build_expert_tensormaps_kernel(const __grid_constant__ CUtensorMap proto_b, const __grid_constant__ CUtensorMap proto_sfb,
+                                   const int64_t* b_ptrs, const int64_t* sfb_ptrs, const void* fallback, CUtensorMap* out,
+                                   int num_experts) {
+  // slots [0, E): weight maps; slots [E, 2E): scale-factor maps
   __shared__ __align__(128) CUtensorMap s_map;
-  const int e = blockIdx.x;
-  if (e >= num_experts) return;
+  const int slot = blockIdx.x;
+  if (slot >= 2 * num_experts) return;
+  const bool is_sf = slot >= num_experts;
+  const int e = is_sf ? slot - num_experts : slot;
   const int lane = threadIdx.x;
-  reinterpret_cast<uint32_t*>(&s_map)[lane] = reinterpret_cast<const uint32_t*>(&proto)[lane];
+  const uint32_t* proto = reinterpret_cast<const uint32_t*>(is_sf ? &proto_sfb : &proto_b);
+  reinterpret_cast<uint32_t*>(&s_map)[lane] = proto[lane];
   __syncwarp();
   if (lane == 0) {
-    uint64_t addr = (uint64_t)b_ptrs[e];
+    uint64_t addr = (uint64_t)(is_sf ? sfb_ptrs[e] : b_ptrs[e]);
     if (addr == 0 || (addr & 15)) {
-      // a misaligned or null weight pointer would fault the TMA unit: record it and point the
-      // map at memory that is known to be valid instead
+      // a misaligned or null pointer would fault the TMA unit: record it and point the map at
+      // memory that is known to be valid instead
       atomicCAS(&g_device_status, 0, 201);
       addr = (uint64_t)fallback;
     }
@@ -566,7 +664,7 @@ __global__ void __launch_bounds__(32)
   __syncwarp();
   asm volatile(
       "tensormap.cp_fenceproxy.global.shared::cta.tensormap::generic.release.gpu.sync.aligned [%0], "
-      "[%1], 128;" ::"l"(out + e),
+      "[%1], 128;" ::"l"(out + slot),
       "r"(smem_u32(&s_map))
       : "memory");
 }
@@ -608,18 +706,23 @@ static EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-// uint8 tensor map, innermost dim = K bytes, 128-byte swizzle, box = (128, box_rows[, 1]).
-static int encode_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const uint64_t* strides,
-                      uint32_t box_rows) {
+// Tiled tensor map over `rank` dimensions (innermost first).  strides[i] is the byte stride of
+// dimension i + 1.
+static int encode_map(CUtensorMap* map, CUtensorMapDataType dtype, const void* base, int rank, const uint64_t* dims,
+                      const uint64_t* strides, const uint32_t* box, CUtensorMapSwizzle swizzle) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return fail(B200MOE_E_DEVICE, "cuTensorMapEncodeTiled is not available from this driver");
-  cuuint64_t gdim[3] = {dims[0], dims[1], rank > 2 ? dims[2] : 1};
-  cuuint64_t gstr[2] = {strides[0], rank > 2 ? strides[1] : 0};
-  cuuint32_t box[3] = {(cuuint32_t)BK, box_rows, 1};
-  cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, (cuuint32_t)rank, const_cast<void*>(base), gdim, gstr, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  cuuint64_t gdim[5] = {1, 1, 1, 1, 1};
+  cuuint64_t gstr[4] = {0, 0, 0, 0};
+  cuuint32_t bx[5] = {1, 1, 1, 1, 1};
+  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  for (int i = 0; i < rank; ++i) {
+    gdim[i] = dims[i];
+    bx[i] = box[i];
+    if (i + 1 < rank) gstr[i] = strides[i];
+  }
+  CUresult r = fn(map, dtype, (cuuint32_t)rank, const_cast<void*>(base), gdim, gstr, bx, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(B200MOE_E_SHAPE, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
   return B200MOE_OK;
 }
@@ -627,7 +730,7 @@ static int encode_map(CUtensorMap* map, const void* base, int rank, const uint64
 struct DeviceInfo {
   int sm_count = 0;
   int cc_major = 0;
-  bool attr_set[2][2] = {{false, false}, {false, false}};
+  bool attr_set[2][2][2] = {};
 };
 
 static int get_device_info(DeviceInfo** out) {
@@ -646,17 +749,40 @@ static int get_device_info(DeviceInfo** out) {
   return B200MOE_OK;
 }
 
-template <int kEpi, bool kDiscrete>
-static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, DeviceInfo* di,
-                  cudaStream_t stream) {
-  auto kern = grouped_gemm_kernel<kEpi, kDiscrete>;
-  if (!di->attr_set[kEpi][kDiscrete ? 1 : 0]) {
-    B200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    di->attr_set[kEpi][kDiscrete ? 1 : 0] = true;
+template <int kEpi, bool kDiscrete, bool kPair>
+static int launch(const CUtensorMap* maps, const GemmParams& p, int grid, DeviceInfo* di, cudaStream_t stream) {
+  auto kern = grouped_gemm_kernel<kEpi, kDiscrete, kPair>;
+  constexpr int smem = Cfg<kPair>::SMEM_BYTES;
+  if (!di->attr_set[kEpi][kDiscrete ? 1 : 0][kPair ? 1 : 0]) {
+    B200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    di->attr_set[kEpi][kDiscrete ? 1 : 0][kPair ? 1 : 0] = true;
   }
-  kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
-  B200_CUDA_CHECK(cudaGetLastError());
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  if (kPair) {
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  B200_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kern, maps[0], maps[1], maps[2], maps[3], p));
   return B200MOE_OK;
+}
+
+template <int kEpi>
+static int dispatch(bool discrete, bool pair, const CUtensorMap* maps, const GemmParams& p, int grid, DeviceInfo* di,
+                    cudaStream_t stream) {
+  if (discrete) {
+    return pair ? launch<kEpi, true, true>(maps, p, grid, di, stream) : launch<kEpi, true, false>(maps, p, grid, di, stream);
+  }
+  return pair ? launch<kEpi, false, true>(maps, p, grid, di, stream) : launch<kEpi, false, false>(maps, p, grid, di, stream);
 }
 
 static int run_gemm(int epi, const b200moe_gemm_args* a, void* stream_v) {
@@ -732,40 +858,78 @@ static int run_gemm(int epi, const b200moe_gemm_args* a, void* stream_v) {
   p.d_is_fp8 = d_fp8;
   p.discrete_col_sfd = (a->flags & B200MOE_FLAG_DISCRETE_COL_SFD) ? 1 : 0;
 
-  CUtensorMap ta, tb;
+  // Tile mode.  A pair (two CTAs, 256 x 256) moves half the weight bytes per SM but rounds every
+  // expert group up to 256 rows; the host sees only the average group size, so pairs are used when
+  // groups are large on average or the caller forces them.
+  bool pair;
+  if (a->flags & B200MOE_FLAG_TILE_SINGLE) pair = false;
+  else if (a->flags & B200MOE_FLAG_TILE_PAIR) pair = true;
+  else pair = a->m_rows / a->num_experts >= 1024;
+
+  CUtensorMap maps[4];  // A, B (or its prototype), SFA, SFB (or its prototype); the last two only in pair mode
+  memset(maps, 0, sizeof(maps));
+  const uint32_t b_rows = pair ? 128 : BN;
   {
     const uint64_t dims[2] = {(uint64_t)p.k, (uint64_t)p.m_rows};
     const uint64_t strides[1] = {(uint64_t)p.k};
-    rc = encode_map(&ta, a->a, 2, dims, strides, BM);
+    const uint32_t box[2] = {BK, BM};
+    rc = encode_map(&maps[0], CU_TENSOR_MAP_DATA_TYPE_UINT8, a->a, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+  }
+  const uint64_t sf_chunk_stride = 512, sf_row_stride = (uint64_t)p.rest_k * 512;
+  if (pair) {
+    // scale factors as 512-byte chunks of 128 uint32: (chunk word, K group, 128-row block[, expert])
+    const uint64_t dims[3] = {128, (uint64_t)p.rest_k, (uint64_t)((p.m_rows + 127) / 128)};
+    const uint64_t strides[2] = {sf_chunk_stride, sf_row_stride};
+    const uint32_t box[3] = {128, 1, 1};
+    rc = encode_map(&maps[2], CU_TENSOR_MAP_DATA_TYPE_UINT32, a->sfa, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (rc) return rc;
   }
   if (!discrete) {
     const uint64_t dims[3] = {(uint64_t)p.k, (uint64_t)p.n, (uint64_t)p.num_experts};
     const uint64_t strides[2] = {(uint64_t)p.k, (uint64_t)p.n * (uint64_t)p.k};
-    rc = encode_map(&tb, a->b, 3, dims, strides, BN);
+    const uint32_t box[3] = {BK, b_rows, 1};
+    rc = encode_map(&maps[1], CU_TENSOR_MAP_DATA_TYPE_UINT8, a->b, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
+    if (pair) {
+      const uint64_t sdims[4] = {128, (uint64_t)p.rest_k, (uint64_t)p.n_blocks, (uint64_t)p.num_experts};
+      const uint64_t sstrides[3] = {sf_chunk_stride, sf_row_stride, (uint64_t)p.sfb_expert_bytes};
+      const uint32_t sbox[4] = {128, 1, 2, 1};
+      rc = encode_map(&maps[3], CU_TENSOR_MAP_DATA_TYPE_UINT32, a->sfb, 4, sdims, sstrides, sbox, CU_TENSOR_MAP_SWIZZLE_NONE);
+      if (rc) return rc;
+    }
   } else {
     const int64_t need = b200moe_workspace_bytes(p.num_experts, 1);
     if (!a->workspace || a->workspace_bytes < need || ((uintptr_t)a->workspace & 127))
       return fail(B200MOE_E_WORKSPACE, "%s: discrete mode needs a 128-byte aligned workspace of %lld bytes", op, (long long)need);
+    // prototypes; the global addresses are patched per expert on the device
     const uint64_t dims[2] = {(uint64_t)p.k, (uint64_t)p.n};
     const uint64_t strides[1] = {(uint64_t)p.k};
-    rc = encode_map(&tb, a->a, 2, dims, strides, BN);  // prototype; the address is patched per expert
+    const uint32_t box[2] = {BK, b_rows};
+    rc = encode_map(&maps[1], CU_TENSOR_MAP_DATA_TYPE_UINT8, a->a, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    const uint64_t sdims[3] = {128, (uint64_t)p.rest_k, (uint64_t)p.n_blocks};
+    const uint64_t sstrides[2] = {sf_chunk_stride, sf_row_stride};
+    const uint32_t sbox[3] = {128, 1, 2};
+    rc = encode_map(&maps[3], CU_TENSOR_MAP_DATA_TYPE_UINT32, a->sfa, 3, sdims, sstrides, sbox, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (rc) return rc;
     p.b_maps = (const CUtensorMap*)a->workspace;
-    build_expert_tensormaps_kernel<<<p.num_experts, 32, 0, stream>>>(tb, a->b_ptrs, a->a, (CUtensorMap*)a->workspace,
-                                                                      p.num_experts);
+    build_expert_tensormaps_kernel<<<2 * p.num_experts, 32, 0, stream>>>(maps[1], maps[3], a->b_ptrs, a->sfb_ptrs, a->a,
+                                                                          (CUtensorMap*)a->workspace, p.num_experts);
     B200_CUDA_CHECK(cudaGetLastError());
   }
 
-  const int64_t max_tiles = ((a->m_rows + BM - 1) / BM) * p.n_tiles;
-  int grid = di->sm_count - (a->sm_margin > 0 ? a->sm_margin : 0);
-  if (grid < 1) grid = 1;
-  if ((int64_t)grid > max_tiles) grid = (int)max_tiles;
+  const int tile_m = pair ? 256 : 128;
+  // upper bound of scheduled tiles: every expert may add one partial row tile
+  const int64_t max_tiles = ((a->m_rows + tile_m - 1) / tile_m + (pair ? a->num_experts : 0)) * p.n_tiles;
+  int units = di->sm_count - (a->sm_margin > 0 ? a->sm_margin : 0);
+  if (pair) units /= 2;
+  if (units < 1) units = 1;
+  if ((int64_t)units > max_tiles) units = (int)max_tiles;
+  const int grid = pair ? 2 * units : units;
 
-  if (epi == EPI_FC1)
-    return discrete ? launch<EPI_FC1, true>(ta, tb, p, grid, di, stream) : launch<EPI_FC1, false>(ta, tb, p, grid, di, stream);
-  return discrete ? launch<EPI_FC2, true>(ta, tb, p, grid, di, stream) : launch<EPI_FC2, false>(ta, tb, p, grid, di, stream);
+  return epi == EPI_FC1 ? dispatch<EPI_FC1>(discrete, pair, maps, p, grid, di, stream)
+                        : dispatch<EPI_FC2>(discrete, pair, maps, p, grid, di, stream);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -835,7 +999,7 @@ int b200moe_fc2_quant(const b200moe_gemm_args* args, void* stream) { return b200
 
 int64_t b200moe_workspace_bytes(int32_t num_experts, int32_t discrete) {
   if (!discrete || num_experts <= 0) return 0;
-  return (int64_t)num_experts * 128;
+  return (int64_t)num_experts * 256;  // one weight map and one scale-factor map per expert
 }
 
 const char* b200moe_last_error(void) { return b200moe::tl_error; }

@@ -279,6 +279,7 @@ class GroupedGemmQuantSm100(OperatorBase):
             num_experts=self.expert_cnt,
             discrete_col_sfd=self.discrete_col_sfd,
             sm_margin=self.num_cluster_overlap_margin,
+            tile_mode="single" if self.mma_tiler_mn[0] <= 128 else None,
             stream=current_stream,
         )
 

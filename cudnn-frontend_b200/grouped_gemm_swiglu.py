@@ -229,6 +229,7 @@ class GroupedGemmSwigluSm100(OperatorBase):
             num_experts=l,
             discrete_col_sfd=self.discrete_col_sfd,
             sm_margin=self.num_cluster_overlap_margin,
+            tile_mode="single" if self.mma_tiler_mn[0] <= 128 else None,
             stream=current_stream,
         )
 

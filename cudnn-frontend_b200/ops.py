@@ -12,6 +12,7 @@ for that registration style is python/cudnn/experimental/ops/moe_grouped_matmul.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -112,9 +113,14 @@ def launch_grouped_gemm(
     workspace: Optional[torch.Tensor] = None,
     discrete_col_sfd: bool = False,
     sm_margin: int = 0,
+    tile_mode: Optional[str] = None,
     stream=None,
 ) -> None:
-    """Fill the C struct and call b200moe_fc1_swiglu / b200moe_fc2_quant."""
+    """Fill the C struct and call b200moe_fc1_swiglu / b200moe_fc2_quant.
+
+    ``tile_mode``: ``"single"`` (128 x 256 tiles, one CTA), ``"pair"`` (256 x 256 tiles on CTA pairs)
+    or ``None`` / ``"auto"`` (the library picks from the average group size).  The environment
+    variable ``B200MOE_TILE_MODE`` overrides ``None``."""
     _require_cuda(a, sfa, padded_offsets, alpha, d, b, sfb, b_ptrs, sfb_ptrs, prob, norm_const, c, d_col, amax, sfd_row, sfd_col)
     args = _lib.GemmArgs()
     args.a, args.sfa = _ptr(a), _ptr(sfa)
@@ -129,6 +135,10 @@ def launch_grouped_gemm(
     args.m_rows, args.n, args.k, args.num_experts = m_rows, n, k, num_experts
     args.d_dtype = _lib.DTYPE_E4M3 if d.dtype in _FP8_BYTES else _lib.DTYPE_BF16
     args.flags = _lib.FLAG_DISCRETE_COL_SFD if discrete_col_sfd else 0
+    mode = tile_mode or os.environ.get("B200MOE_TILE_MODE", "auto")
+    if mode not in ("auto", "single", "pair"):
+        raise ValueError(f"tile_mode must be 'auto', 'single' or 'pair', got {mode!r}")
+    args.flags |= {"auto": 0, "single": _lib.FLAG_TILE_SINGLE, "pair": _lib.FLAG_TILE_PAIR}[mode]
     args.sm_margin = sm_margin
     lib = _lib.load()
     fn = lib.b200moe_fc1_swiglu if kind == "fc1" else lib.b200moe_fc2_quant

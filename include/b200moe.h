@@ -35,6 +35,8 @@ extern "C" {
 
 /* flags */
 #define B200MOE_FLAG_DISCRETE_COL_SFD 1 /* per-expert column scale-factor blocks */
+#define B200MOE_FLAG_TILE_SINGLE 2      /* force 128 x 256 single-CTA tiles                    */
+#define B200MOE_FLAG_TILE_PAIR 4        /* force 256 x 256 CTA-pair tiles (cta_group::2)       */
 
 /*
  * Arguments of one grouped GEMM launch.  All pointers are device pointers.
@@ -126,8 +128,8 @@ int b200moe_fc1_swiglu_discrete_noalloc(const b200moe_gemm_args* args, void* str
 int b200moe_fc2_quant(const b200moe_gemm_args* args, void* stream);
 
 /*
- * Bytes of caller-owned workspace a launch needs (0 in dense mode; E tensor-map slots of
- * 128 bytes in discrete mode).  Mirrors the workspace the reference allocates in compile()
+ * Bytes of caller-owned workspace a launch needs (0 in dense mode; two 128-byte tensor-map
+ * slots per expert in discrete mode).  Mirrors the workspace the reference allocates in compile()
  * (python/cudnn/grouped_gemm/grouped_gemm_quant/grouped_gemm_quant.py:425-445).
  */
 int64_t b200moe_workspace_bytes(int32_t num_experts, int32_t discrete);

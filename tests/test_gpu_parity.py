@@ -21,6 +21,13 @@ pytestmark = pytest.mark.gpu
 BF16_GATE = 2e-2
 
 
+@pytest.fixture(params=["single", "pair"])
+def tile_mode(request, monkeypatch):
+    """Run a test once per tile mode of the GEMM kernel (128 x 256 single-CTA tiles, 256 x 256 CTA pairs)."""
+    monkeypatch.setenv("B200MOE_TILE_MODE", request.param)
+    return request.param
+
+
 def _api():
     import cudnn_frontend_b200 as cf
 
@@ -246,7 +253,7 @@ CASES_BF16 = [
 
 @pytest.mark.parametrize("kind,groups,n,k", CASES_BF16)
 @pytest.mark.parametrize("discrete", [False, True])
-def test_bf16_output_and_amax(kind, groups, n, k, discrete):
+def test_bf16_output_and_amax(kind, groups, n, k, discrete, tile_mode):
     out, ref, info = _run(kind, 11, groups, n, k, discrete=discrete)
     _check(kind, out, ref, info, d_fp8=False)
 
@@ -262,7 +269,7 @@ CASES_FP8 = [
 
 
 @pytest.mark.parametrize("kind,groups,n,k,norm", CASES_FP8)
-def test_mxfp8_requantised_output(kind, groups, n, k, norm):
+def test_mxfp8_requantised_output(kind, groups, n, k, norm, tile_mode):
     out, ref, info = _run(kind, 23, groups, n, k, d_fp8=True, norm=norm)
     _check(kind, out, ref, info, d_fp8=True)
 
@@ -275,7 +282,7 @@ def test_wrappers_allocate_and_match(kind):
     _check(kind, out, ref, info, d_fp8=False)
 
 
-def test_discrete_equals_dense_bitwise():
+def test_discrete_equals_dense_bitwise(tile_mode):
     """Same tiles, same order of operations: the two weight layouts must agree exactly (the
     reference only asks for atol 0.1 / rtol 1e-2, test_discrete_grouped_gemm_swiglu.py:448-688)."""
     o1, _, _ = _run("fc1", 31, [256, 0, 384], 512, 384, discrete=False)
@@ -284,7 +291,7 @@ def test_discrete_equals_dense_bitwise():
         assert torch.equal(o1[key], o2[key]), key
 
 
-def test_zero_alpha_gives_exact_zeros():
+def test_zero_alpha_gives_exact_zeros(tile_mode):
     """Known-answer case of the reference (test_grouped_gemm_quant.py:372-401)."""
     out, _, info = _run("fc2", 3, [64, 256, 320], 384, 160, alpha=np.zeros(3, dtype=np.float32), m_aligned=256)
     d = out["d_tensor"][: info["valid"]].float()
@@ -292,7 +299,7 @@ def test_zero_alpha_gives_exact_zeros():
     assert torch.count_nonzero(out["amax_tensor"]) == 0
 
 
-def test_rows_beyond_last_offset_are_untouched():
+def test_rows_beyond_last_offset_are_untouched(tile_mode):
     """Tensors may be longer than padded_offsets[-1] (CUDA-graph padding); those rows are never written."""
     for kind, fp8 in (("fc1", False), ("fc2", True)):
         out, _, info = _run(kind, 9, [128, 256], 256, 128, d_fp8=fp8, extra_rows=256)
@@ -308,7 +315,7 @@ def test_c_store_is_optional_and_prob_is_optional_for_fc1():
     _check("fc1", out, ref, info, d_fp8=False)
 
 
-def test_discrete_col_sfd_layout():
+def test_discrete_col_sfd_layout(tile_mode):
     """Per-expert column scale blocks (grouped_gemm_swiglu_quant.py:1199-1238): expert e's block is
     the 128x4 layout of (n_out, rows_e / 32), placed at byte offset (start_e / 128) * ceil(n_out / 128) * 512."""
     groups = [256, 128, 384]
@@ -369,7 +376,7 @@ def test_scatter_and_combine_round_trip():
 # ---------------------------------------------------------------------------------------------
 # FC1 -> FC2 chain against the single-process layer oracle
 # ---------------------------------------------------------------------------------------------
-def test_fc1_fc2_chain_matches_layer_oracle():
+def test_fc1_fc2_chain_matches_layer_oracle(tile_mode):
     cf = _api()
     from cudnn_frontend_b200 import moe, ops, synthetic
 
