@@ -46,6 +46,7 @@ class GemmArgs(Structure):
         ("d_dtype", c_int32),
         ("flags", c_int32),
         ("sm_margin", c_int32),
+        ("d_row_map", c_void_p),
     ]
 
 
@@ -64,6 +65,14 @@ _SIGNATURES = {
     "b200moe_scatter_rows": (
         ctypes.c_int,
         [c_void_p, c_void_p, c_int64, c_int32, c_int64, c_void_p, c_void_p, c_void_p, c_void_p],
+    ),
+    "b200moe_dispatch_quantize": (
+        ctypes.c_int,
+        [c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_int64, c_void_p, c_void_p, c_void_p, c_void_p],
+    ),
+    "b200moe_place_quantized_rows": (
+        ctypes.c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p],
     ),
     "b200moe_gather_rows": (ctypes.c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p]),
     "b200moe_combine_rows": (ctypes.c_int, [c_void_p, c_void_p, c_int64, c_int32, c_int64, c_void_p, c_void_p]),

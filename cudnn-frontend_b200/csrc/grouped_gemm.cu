@@ -95,6 +95,7 @@ struct GemmParams {
   const float* alpha;
   const float* prob;
   const float* norm_const;
+  const int32_t* d_row_map;  // optional scatter of bf16 D rows
   __nv_bfloat16* c;
   void* d;
   uint8_t* d_col;
@@ -459,6 +460,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       const bool row_ok = row < min(p.m_rows, tile.row_end);
       const float alpha = p.alpha[tile.expert];
       const float prob = (p.prob && row_ok) ? p.prob[row] : 1.0f;
+      const int out_row = (p.d_row_map && row_ok) ? p.d_row_map[row] : row;
       const uint32_t acc = tmem_base + ((it & 1) ? TMEM_ACC1_COL : 0) + ((uint32_t)(quarter * 32) << 16);
       const bool reverse = (it & 1) == 0;  // even tiles drain from the top (shared columns first)
       float thread_amax = 0.f;
@@ -504,7 +506,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 #pragma unroll
               for (int j = 0; j < 32; ++j) thread_amax = fmaxf(thread_amax, fabsf(g[j]));
             }
-            if (row_ok) store_bf16x32(reinterpret_cast<__nv_bfloat16*>(p.d) + (int64_t)row * p.n_out + dn, g);
+            if (row_ok && out_row >= 0) store_bf16x32(reinterpret_cast<__nv_bfloat16*>(p.d) + (int64_t)out_row * p.n_out + dn, g);
           } else {
             if (row_ok) {
               const uint32_t sf = quant_row_block(reinterpret_cast<uint8_t*>(p.d) + (int64_t)row * p.n_out + dn, g, norm_const);
@@ -564,7 +566,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 #pragma unroll
               for (int j = 0; j < 32; ++j) thread_amax = fmaxf(thread_amax, fabsf(v[j]));
             }
-            if (row_ok) store_bf16x32(reinterpret_cast<__nv_bfloat16*>(p.d) + (int64_t)row * p.n_out + dn, v);
+            if (row_ok && out_row >= 0) store_bf16x32(reinterpret_cast<__nv_bfloat16*>(p.d) + (int64_t)out_row * p.n_out + dn, v);
           } else {
             if (row_ok) {
               const uint32_t sf = quant_row_block(reinterpret_cast<uint8_t*>(p.d) + (int64_t)row * p.n_out + dn, v, norm_const);
@@ -812,6 +814,7 @@ static int run_gemm(int epi, const b200moe_gemm_args* a, void* stream_v) {
     return fail(B200MOE_E_SHAPE, "%s: n (%lld) must be a multiple of 32", op, (long long)a->n);
   if (a->n * a->k > (1ll << 40)) return fail(B200MOE_E_SHAPE, "%s: n*k too large", op);
   const bool d_fp8 = a->d_dtype == B200MOE_DTYPE_E4M3;
+  if (a->d_row_map && (d_fp8 || a->c)) return fail(B200MOE_E_UNSUPPORTED, "%s: d_row_map needs a bf16 D and no C", op);
   if (a->d_dtype != B200MOE_DTYPE_BF16 && !d_fp8) return fail(B200MOE_E_UNSUPPORTED, "%s: d_dtype %d", op, a->d_dtype);
   if (d_fp8) {
     if (!a->sfd_row || !a->norm_const)
@@ -837,6 +840,7 @@ static int run_gemm(int epi, const b200moe_gemm_args* a, void* stream_v) {
   p.alpha = a->alpha;
   p.prob = a->prob;
   p.norm_const = a->norm_const;
+  p.d_row_map = a->d_row_map;
   p.c = epi == EPI_FC1 ? (__nv_bfloat16*)a->c : nullptr;
   p.d = a->d;
   p.d_col = d_fp8 ? (uint8_t*)a->d_col : nullptr;

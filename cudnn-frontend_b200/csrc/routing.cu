@@ -116,6 +116,71 @@ __global__ void __launch_bounds__(128)
   for (int i = threadIdx.x; i < vec_per_row; i += blockDim.x) dst[i] = __ldg(src + i);
 }
 
+// Dispatch side, fused: one block per token reads the bf16 row once, quantises it to MXFP8 and
+// writes the E4M3 row, its E8M0 scales (row-major, cols / 32 bytes per row) and the gate
+// probability to each of the token's `topk` positions of the send buffers.
+__global__ void __launch_bounds__(128)
+    dispatch_quantize_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ send_pos,
+                             const float* __restrict__ topk_prob, int topk, int cols, uint8_t* __restrict__ q,
+                             uint8_t* __restrict__ sf, float* __restrict__ prob_out) {
+  const int64_t t = blockIdx.x;
+  const int lane = threadIdx.x & 31;
+  const int sf_cols = cols / 32;
+  __shared__ int s_dst[16];
+  if (threadIdx.x < topk) {
+    const int d = send_pos[t * topk + threadIdx.x];
+    s_dst[threadIdx.x] = d;
+    if (d >= 0 && prob_out) prob_out[d] = topk_prob ? topk_prob[t * topk + threadIdx.x] : 1.0f;
+  }
+  __syncthreads();
+  for (int v = threadIdx.x; v < cols / 8; v += blockDim.x) {
+    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(x + t * cols) + v);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    float f[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 p2 = __bfloat1622float2(h[j]);
+      f[2 * j] = p2.x;
+      f[2 * j + 1] = p2.y;
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(f[j]));
+    // the four lanes of one 32-element block are consecutive lanes of one warp (cols % 32 == 0)
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    const uint32_t sfb = e8m0_from_float(amax * (1.0f / 448.0f));
+    const float scale = quant_scale(1.0f, e8m0_to_float(sfb));
+    uint2 o;
+    o.x = e4m3x4_from_float(f[0] * scale, f[1] * scale, f[2] * scale, f[3] * scale);
+    o.y = e4m3x4_from_float(f[4] * scale, f[5] * scale, f[6] * scale, f[7] * scale);
+    for (int j = 0; j < topk; ++j) {
+      const int d = s_dst[j];
+      if (d < 0) continue;
+      reinterpret_cast<uint2*>(q + (int64_t)d * cols)[v] = o;
+      if ((lane & 3) == 0) sf[(int64_t)d * sf_cols + (v >> 2)] = (uint8_t)sfb;
+    }
+  }
+}
+
+// Receive side: row i of the arrival-order buffers goes to row dst_row[i] of the expert-grouped
+// operand; its scales are written into the 128x4 swizzled layout the GEMM reads.
+__global__ void __launch_bounds__(128)
+    place_quantized_rows_kernel(const uint8_t* __restrict__ q_in, const uint8_t* __restrict__ sf_in,
+                                const float* __restrict__ prob_in, const int32_t* __restrict__ dst_row, int cols,
+                                int rest_k, uint8_t* __restrict__ q_out, uint8_t* __restrict__ sf_out,
+                                float* __restrict__ prob_out) {
+  const int64_t i = blockIdx.x;
+  const int d = dst_row[i];
+  if (d < 0) return;
+  const uint4* src = reinterpret_cast<const uint4*>(q_in + i * cols);
+  uint4* dst = reinterpret_cast<uint4*>(q_out + (int64_t)d * cols);
+  for (int v = threadIdx.x; v < cols / 16; v += blockDim.x) dst[v] = __ldg(src + v);
+  const int sf_cols = cols / 32;
+  for (int kb = threadIdx.x; kb < sf_cols; kb += blockDim.x) sf_out[sf_offset(d, kb, rest_k)] = sf_in[i * sf_cols + kb];
+  if (threadIdx.x == 0 && prob_in && prob_out) prob_out[d] = prob_in[i];
+}
+
 // rows [start_e + count_e, end_e) of every expert group are set to zero
 __global__ void __launch_bounds__(128)
     zero_pad_rows_kernel(uint4* __restrict__ buf, const int32_t* __restrict__ counts,
@@ -214,6 +279,35 @@ int b200moe_gather_rows(const void* in, const int32_t* src_row, int64_t num_rows
     return fail(B200MOE_E_SHAPE, "gather_rows: cols must be a positive multiple of 8");
   if (((uintptr_t)in | (uintptr_t)out) & 15) return fail(B200MOE_E_ALIGN, "gather_rows: 16-byte alignment required");
   gather_rows_kernel<<<(unsigned)num_rows, 128, 0, (cudaStream_t)stream>>>((const uint4*)in, src_row, (int)(cols / 8), (uint4*)out);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200MOE_OK;
+}
+
+int b200moe_dispatch_quantize(const void* x, const int32_t* send_pos, const float* topk_prob, int64_t num_tokens,
+                              int32_t topk, int64_t cols, void* q, void* sf, float* prob_out, void* stream) {
+  using namespace b200moe;
+  if (num_tokens == 0) return B200MOE_OK;
+  if (!x || !send_pos || !q || !sf) return fail(B200MOE_E_NULL, "dispatch_quantize: null pointer");
+  if (cols <= 0 || cols % 32 != 0 || topk <= 0 || topk > 16 || num_tokens < 0 || num_tokens > 0x7fffffffll)
+    return fail(B200MOE_E_SHAPE, "dispatch_quantize: cols must be a positive multiple of 32 and topk in [1, 16]");
+  if (((uintptr_t)x | (uintptr_t)q) & 15) return fail(B200MOE_E_ALIGN, "dispatch_quantize: 16-byte alignment required");
+  dispatch_quantize_kernel<<<(unsigned)num_tokens, 128, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)x, send_pos, topk_prob, topk, (int)cols, (uint8_t*)q, (uint8_t*)sf, prob_out);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200MOE_OK;
+}
+
+int b200moe_place_quantized_rows(const void* q_in, const void* sf_in, const float* prob_in, const int32_t* dst_row,
+                                 int64_t num_rows, int64_t cols, void* q_out, void* sf_out, float* prob_out, void* stream) {
+  using namespace b200moe;
+  if (num_rows == 0) return B200MOE_OK;
+  if (!q_in || !sf_in || !dst_row || !q_out || !sf_out) return fail(B200MOE_E_NULL, "place_quantized_rows: null pointer");
+  if (cols <= 0 || cols % 32 != 0 || num_rows < 0 || num_rows > 0x7fffffffll)
+    return fail(B200MOE_E_SHAPE, "place_quantized_rows: cols must be a positive multiple of 32");
+  if (((uintptr_t)q_in | (uintptr_t)q_out) & 15) return fail(B200MOE_E_ALIGN, "place_quantized_rows: 16-byte alignment required");
+  const int rest_k = (int)((cols / 32 + 3) / 4);
+  place_quantized_rows_kernel<<<(unsigned)num_rows, 128, 0, (cudaStream_t)stream>>>(
+      (const uint8_t*)q_in, (const uint8_t*)sf_in, prob_in, dst_row, (int)cols, rest_k, (uint8_t*)q_out, (uint8_t*)sf_out, prob_out);
   B200_CUDA_CHECK(cudaGetLastError());
   return B200MOE_OK;
 }

@@ -1,9 +1,13 @@
 """Expert-parallel MoE layer: experts sharded over the ranks of a process group, tokens
 dispatched and combined with all-to-all (NCCL over NVLink on GPUs).
 
-    route -> sort rows by (destination rank, expert) -> exchange counts -> all-to-all dispatch
-    -> group by local expert (padded to 128) -> MXFP8 quantise -> FC1 (+SwiGLU, MXFP8 out)
-    -> FC2 (x gating probability) -> all-to-all combine -> un-permute and sum each token's k rows
+    route -> sort rows by (destination rank, expert) -> exchange counts
+    -> fused [read token row once, MXFP8 quantise, write to its k send positions]
+    -> all-to-all dispatch of E4M3 rows + E8M0 scales + gate probabilities (half the bytes of bf16;
+       row-wise quantisation commutes with the row permutation, so results equal quantising after)
+    -> regroup by local expert (padded to 128) straight into the GEMM operand / swizzled scale layout
+    -> FC1 (+SwiGLU, MXFP8 out) -> FC2 (x gating probability; its epilogue stores every row at its
+       all-to-all arrival index) -> all-to-all combine -> un-permute and sum each token's k rows
 
 The reference has no multi-GPU code at all; this is the layer its kernels are meant to sit in.
 Expert ``e`` lives on rank ``e // (E / G)``.
@@ -33,6 +37,7 @@ class DispatchPlan:
     in_splits: List[int]  # rows sent to each rank
     out_splits: List[int]  # rows received from each rank
     recv_dst: torch.Tensor  # [R_recv] int32: received row i -> row of the padded expert-grouped buffer
+    row_map: torch.Tensor  # [m_rows] int32: row of the grouped buffer -> arrival index (-1 for padding rows)
     counts_local: torch.Tensor  # [E_local] int32 rows per local expert
     padded_offsets: torch.Tensor  # [E_local] int32 END offsets (groups padded to m_aligned)
     m_rows: int  # padded_offsets[-1]
@@ -92,7 +97,9 @@ def plan_dispatch(topk_ids: torch.Tensor, num_experts: int, group=None, m_aligne
     rank_in_expert = torch.arange(r_recv, device=dev) - first[sorted_ids]
     recv_dst = torch.empty(r_recv, dtype=torch.int64, device=dev)
     recv_dst[order2] = starts[sorted_ids] + rank_in_expert
-    return DispatchPlan(t, k, send_pos.to(torch.int32), in_splits, out_splits, recv_dst.to(torch.int32),
+    row_map = torch.full((m_rows,), -1, dtype=torch.int32, device=dev)
+    row_map[recv_dst] = torch.arange(r_recv, device=dev, dtype=torch.int32)
+    return DispatchPlan(t, k, send_pos.to(torch.int32), in_splits, out_splits, recv_dst.to(torch.int32), row_map,
                         counts_local.to(torch.int32), offsets.to(torch.int32), m_rows)  # fmt: skip
 
 
@@ -141,6 +148,7 @@ class ExpertParallelMoE:
         key = m_rows
         if key not in self._ops:
             a, sfa, h8, sfh, y, prob, offs = bufs
+            y = torch.empty((m_rows, self.hidden, 1), dtype=torch.bfloat16, device="meta")  # shape sample only
             fc1 = GroupedGemmSwigluSm100(a, self.w1, None, h8, sfa, self.sfw1, offs, self.alpha, h8, sample_sfd_row=sfh,
                                          sample_sfd_col=_dummy_sf_col(self.inter, m_rows, a.device), sample_norm_const=self.norm,
                                          sf_vec_size=32, m_aligned=self.m_aligned)  # fmt: skip
@@ -164,33 +172,24 @@ class ExpertParallelMoE:
         dev = x.device
         plan = plan_dispatch(topk_ids, self.num_experts, self.group, self.m_aligned)
         self.last_plan = plan
-        # dispatch: rows in send order, gating probabilities travel with them
-        send = torch.empty((t * k, h), dtype=torch.bfloat16, device=dev)
-        send_p = torch.empty((t * k,), dtype=torch.float32, device=dev)
-        moe.scatter_rows(x, plan.send_pos, send, rows_per_src=k, in_prob=topk_prob.reshape(-1).contiguous(), out_prob=send_p)
-        recv = exchange_rows(send, plan.rows_received, plan.in_splits, plan.out_splits, self.group)
+        # dispatch: each token row is read once, quantised, and written to its k send positions
+        # (E4M3 + row-major scales + gate probability travel together: half the bytes of bf16)
+        send_q, send_sf, send_p = moe.dispatch_quantize(x, plan.send_pos, k, topk_prob.reshape(-1).contiguous())
+        recv_q = exchange_rows(send_q, plan.rows_received, plan.in_splits, plan.out_splits, self.group)
+        recv_sf = exchange_rows(send_sf, plan.rows_received, plan.in_splits, plan.out_splits, self.group)
         recv_p = exchange_rows(send_p, plan.rows_received, plan.in_splits, plan.out_splits, self.group)
         m = plan.m_rows
-        if m == 0:
-            y_recv = torch.zeros((plan.rows_received, h), dtype=torch.bfloat16, device=dev)
-        else:
-            # group by local expert (padding rows zero), quantise, FC1, FC2
-            xg = torch.empty((m, h), dtype=torch.bfloat16, device=dev)
-            pg = torch.empty((m,), dtype=torch.float32, device=dev)
-            moe.scatter_rows(recv, plan.recv_dst, xg, rows_per_src=1, in_prob=recv_p, out_prob=pg)
-            moe.zero_pad_rows(xg, plan.counts_local, plan.padded_offsets, pg)
-            a = torch.empty((m, h, 1), dtype=torch.float8_e4m3fn, device=dev)
-            sfa = ops.empty_sf(m, h, 1, device=dev)
-            ops.quantize_mxfp8_out(xg, a.view(m, h), sfa)
+        y_recv = torch.empty((plan.rows_received, h), dtype=torch.bfloat16, device=dev)
+        if m > 0:
+            # regroup by local expert straight into the GEMM operand layout (scales swizzled here)
+            a, sfa, prob3 = moe.place_quantized_rows(recv_q, recv_sf, recv_p, plan.recv_dst, m, plan.counts_local, plan.padded_offsets)
             h8 = torch.empty((m, self.inter, 1), dtype=torch.float8_e4m3fn, device=dev)
             sfh = ops.empty_sf(m, self.inter, 1, device=dev)
-            y = torch.empty((m, h, 1), dtype=torch.bfloat16, device=dev)
-            prob3 = pg.view(m, 1, 1)
-            fc1, fc2 = self._fc_ops(m, (a, sfa, h8, sfh, y, prob3, plan.padded_offsets))
+            fc1, fc2 = self._fc_ops(m, (a, sfa, h8, sfh, y_recv.view(-1, h, 1), prob3, plan.padded_offsets))
             fc1.execute(a, self.w1, None, h8, sfa, self.sfw1, plan.padded_offsets, self.alpha, sfd_row_tensor=sfh, norm_const_tensor=self.norm)
-            fc2.execute(h8, sfh, plan.padded_offsets, self.alpha, y, b_tensor=self.w2, sfb_tensor=self.sfw2, prob_tensor=prob3)
-            # combine: back to arrival order, return to the senders
-            y_recv = moe.gather_rows(y.view(m, h), plan.recv_dst)
+            # FC2 stores every result row at its arrival index: y_recv is already in all-to-all order
+            fc2.execute(h8, sfh, plan.padded_offsets, self.alpha, y_recv.view(-1, h, 1), b_tensor=self.w2, sfb_tensor=self.sfw2,
+                        prob_tensor=prob3, d_row_map=plan.row_map)  # fmt: skip
         back = exchange_rows(y_recv, plan.rows_sent, plan.out_splits, plan.in_splits, self.group)
         return moe.combine_rows(back, plan.send_pos, t, k)
 

@@ -238,7 +238,11 @@ class GroupedGemmQuantSm100(OperatorBase):
         norm_const_tensor: Optional[torch.Tensor] = None,
         prob_tensor: Optional[torch.Tensor] = None,
         current_stream=None,
+        d_row_map: Optional[torch.Tensor] = None,
     ) -> None:
+        """Launch on ``current_stream``; allocates nothing.  ``d_row_map`` (int32 ``[M]``, not in the
+        reference) stores row ``r`` of a bf16 result at row ``d_row_map[r]`` of ``d_tensor`` (negative:
+        not stored), so a caller can receive the rows in another order, e.g. all-to-all order."""
         self._ensure_compiled()
         tensor_m, k = a_tensor.shape[0], a_tensor.shape[1]
         if tensor_m == 0:
@@ -280,6 +284,7 @@ class GroupedGemmQuantSm100(OperatorBase):
             discrete_col_sfd=self.discrete_col_sfd,
             sm_margin=self.num_cluster_overlap_margin,
             tile_mode="single" if self.mma_tiler_mn[0] <= 128 else None,
+            d_row_map=d_row_map,
             stream=current_stream,
         )
 

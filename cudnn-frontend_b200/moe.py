@@ -56,6 +56,53 @@ def scatter_rows(
     _lib.check(rc)
 
 
+def dispatch_quantize(x: torch.Tensor, send_pos: torch.Tensor, topk: int, topk_prob: Optional[torch.Tensor] = None, stream=None):
+    """Fused dispatch-side pass: every token row of ``x [T, H]`` (bf16) is read once, quantised to
+    MXFP8 and written to its ``topk`` positions ``send_pos[t * topk + j]`` of the send buffers.
+    Returns ``(q [R, H] uint8 E4M3, sf [R, H/32] uint8 E8M0 row-major, prob [R] f32)``."""
+    if x.dtype != torch.bfloat16 or not x.is_contiguous():
+        raise ValueError("x must be a contiguous bf16 tensor")
+    t, h = x.shape
+    r = t * topk
+    dev = x.device
+    q = torch.empty((r, h), dtype=torch.uint8, device=dev)
+    sf = torch.empty((r, h // 32), dtype=torch.uint8, device=dev)
+    prob = torch.empty((r,), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.load().b200moe_dispatch_quantize(
+            x.data_ptr(), send_pos.data_ptr(), None if topk_prob is None else topk_prob.data_ptr(), t, topk, h,
+            q.data_ptr(), sf.data_ptr(), prob.data_ptr(), _stream_ptr(stream),
+        )  # fmt: skip
+    _lib.check(rc)
+    return q, sf, prob
+
+
+def place_quantized_rows(q_in, sf_in, prob_in, dst_row, m_rows: int, counts=None, padded_offsets=None, stream=None):
+    """Receive-side pass: arrival-order MXFP8 rows -> expert-grouped GEMM operand.  Returns
+    ``(a (M, H, 1) float8_e4m3fn, sfa 6-D E8M0 in the 128x4 layout, prob (M, 1, 1) f32)``; with
+    ``counts`` / ``padded_offsets`` the padding rows of every group are zeroed."""
+    from .ops import empty_sf
+
+    h = q_in.shape[1]
+    dev = q_in.device
+    a = torch.empty((m_rows, h), dtype=torch.uint8, device=dev)
+    sfa = empty_sf(m_rows, h, 1, device=dev)
+    prob = torch.empty((m_rows,), dtype=torch.float32, device=dev)
+    lib = _lib.load()
+    with torch.cuda.device(dev):
+        rc = lib.b200moe_place_quantized_rows(
+            q_in.data_ptr(), sf_in.data_ptr(), prob_in.data_ptr(), dst_row.data_ptr(), dst_row.numel(), h,
+            a.data_ptr(), sfa.data_ptr(), prob.data_ptr(), _stream_ptr(stream),
+        )  # fmt: skip
+        _lib.check(rc)
+        if counts is not None:
+            # an E4M3 row of H bytes is zeroed as H/2 bf16 elements
+            rc = lib.b200moe_zero_pad_rows(a.data_ptr(), counts.data_ptr(), padded_offsets.data_ptr(), counts.numel(), h // 2,
+                                           prob.data_ptr(), _stream_ptr(stream))  # fmt: skip
+            _lib.check(rc)
+    return a.view(torch.float8_e4m3fn).view(m_rows, h, 1), sfa, prob.view(m_rows, 1, 1)
+
+
 def gather_rows(x: torch.Tensor, src_row: torch.Tensor, out: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
     """``out[r] = x[src_row[r]]`` for bf16 rows (a negative index gives a zero row)."""
     if x.dtype != torch.bfloat16 or not x.is_contiguous():

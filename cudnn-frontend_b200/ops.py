@@ -114,6 +114,7 @@ def launch_grouped_gemm(
     discrete_col_sfd: bool = False,
     sm_margin: int = 0,
     tile_mode: Optional[str] = None,
+    d_row_map: Optional[torch.Tensor] = None,
     stream=None,
 ) -> None:
     """Fill the C struct and call b200moe_fc1_swiglu / b200moe_fc2_quant.
@@ -140,6 +141,7 @@ def launch_grouped_gemm(
         raise ValueError(f"tile_mode must be 'auto', 'single' or 'pair', got {mode!r}")
     args.flags |= {"auto": 0, "single": _lib.FLAG_TILE_SINGLE, "pair": _lib.FLAG_TILE_PAIR}[mode]
     args.sm_margin = sm_margin
+    args.d_row_map = _ptr(d_row_map)
     lib = _lib.load()
     fn = lib.b200moe_fc1_swiglu if kind == "fc1" else lib.b200moe_fc2_quant
     with torch.cuda.device(a.device):

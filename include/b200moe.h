@@ -83,6 +83,9 @@ typedef struct b200moe_gemm_args {
   int32_t d_dtype;
   int32_t flags;
   int32_t sm_margin; /* SMs left free for a concurrent kernel (CUDNNFE_CLUSTER_OVERLAP_MARGIN) */
+  /* optional, bf16 D only: row r of the result is stored at row d_row_map[r] of d (negative =
+     the row is not stored).  Lets the layer write FC2 results straight in all-to-all order. */
+  const int32_t* d_row_map;
 } b200moe_gemm_args;
 
 /*
@@ -155,6 +158,13 @@ int b200moe_quantize_mxfp8(const void* x, int64_t rows, int64_t cols, int64_t ld
  *   rows of one expert keep their order).  scratch: (E + 1) int32, caller-owned.
  * b200moe_scatter_rows: out[dst_row[r], :] = in[r / rows_per_src, :]  (bf16, cols % 8 == 0);
  *   also out_prob[dst_row[r]] = in_prob[r] when both are non-NULL.
+ * b200moe_dispatch_quantize: fused dispatch-side pass.  For token t the bf16 row x[t, :] is read
+ *   once, quantised to MXFP8 (same arithmetic as b200moe_quantize_mxfp8) and written to rows
+ *   send_pos[t*topk + j] (j < topk; negative = skip) of q [R, cols] (E4M3), sf [R, cols/32] (E8M0,
+ *   row-major: this buffer is for transport, not for the GEMM) and prob_out [R].
+ * b200moe_place_quantized_rows: receive-side pass.  Arrival-order row i of (q_in, sf_in, prob_in)
+ *   goes to row dst_row[i] of the GEMM operand: q_out [M, cols], sf_out in the 128x4 layout of
+ *   (M, cols/32), prob_out [M].
  * b200moe_gather_rows: out[r, :] = in[src_row[r], :] (bf16; a negative index gives a zero row).
  * b200moe_combine_rows: out[t, :] = sum_j in[dst_row[t*topk + j], :] (bf16 in, f32 accumulate,
  *   bf16 out).
@@ -168,6 +178,12 @@ int b200moe_zero_pad_rows(void* buf, const int32_t* counts, const int32_t* padde
 int b200moe_scatter_rows(const void* in, const int32_t* dst_row, int64_t num_rows,
                          int32_t rows_per_src, int64_t cols, void* out, const float* in_prob,
                          float* out_prob, void* stream);
+int b200moe_dispatch_quantize(const void* x, const int32_t* send_pos, const float* topk_prob,
+                              int64_t num_tokens, int32_t topk, int64_t cols, void* q, void* sf,
+                              float* prob_out, void* stream);
+int b200moe_place_quantized_rows(const void* q_in, const void* sf_in, const float* prob_in,
+                                 const int32_t* dst_row, int64_t num_rows, int64_t cols, void* q_out,
+                                 void* sf_out, float* prob_out, void* stream);
 int b200moe_gather_rows(const void* in, const int32_t* src_row, int64_t num_rows, int64_t cols,
                         void* out, void* stream);
 int b200moe_combine_rows(const void* in, const int32_t* dst_row, int64_t num_tokens, int32_t topk,
