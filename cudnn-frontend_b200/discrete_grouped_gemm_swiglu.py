@@ -195,7 +195,7 @@ class DiscreteGroupedGemmSwigluSm100(OperatorBase):
         _require_pointer_tensor(b_ptrs, "b_ptrs", self.expert_cnt)
         _require_pointer_tensor(sfb_ptrs, "sfb_ptrs", self.expert_cnt)
         fp8_out = d_tensor.dtype == torch.float8_e4m3fn
-        ops.launch_grouped_gemm(
+        ops.grouped_gemm_op(
             "fc1",
             a=a_tensor,
             sfa=sfa_tensor,
@@ -212,10 +212,7 @@ class DiscreteGroupedGemmSwigluSm100(OperatorBase):
             sfd_row=sfd_row_tensor if fp8_out else None,
             sfd_col=sfd_col_tensor if fp8_out and d_col_tensor is not None else None,
             workspace=self._workspace,
-            m_rows=tensor_m,
             n=self._n,
-            k=k,
-            num_experts=self.expert_cnt,
             discrete_col_sfd=self.discrete_col_sfd,
             sm_margin=self.num_cluster_overlap_margin,
             tile_mode="single" if self.mma_tiler_mn[0] <= 128 else None,

@@ -207,7 +207,7 @@ class GroupedGemmSwigluSm100(OperatorBase):
             return
         n, l = b_tensor.shape[0], b_tensor.shape[2]
         fp8_out = d_tensor.dtype == torch.float8_e4m3fn
-        ops.launch_grouped_gemm(
+        ops.grouped_gemm_op(
             "fc1",
             a=a_tensor,
             sfa=sfa_tensor,
@@ -223,10 +223,7 @@ class GroupedGemmSwigluSm100(OperatorBase):
             amax=None if fp8_out else amax_tensor,
             sfd_row=sfd_row_tensor if fp8_out else None,
             sfd_col=sfd_col_tensor if fp8_out and d_col_tensor is not None else None,
-            m_rows=tensor_m,
             n=n,
-            k=k,
-            num_experts=l,
             discrete_col_sfd=self.discrete_col_sfd,
             sm_margin=self.num_cluster_overlap_margin,
             tile_mode="single" if self.mma_tiler_mn[0] <= 128 else None,

@@ -156,3 +156,90 @@ def workspace_bytes(num_experts: int, discrete: bool) -> int:
 def device_status(clear: bool = False) -> int:
     """Device-side status word (0 unless a bounded wait inside a kernel gave up)."""
     return int(_lib.load().b200moe_device_status(1 if clear else 0))
+
+
+# ---------------------------------------------------------------------------------------------
+# torch custom ops: the C-ABI launches as first-class PyTorch operators (schema, fake kernels for
+# tracing, mutation annotations).  Outputs are caller-provided and mutated in place, as with the
+# reference's compiled kernels; optional tensors are passed as None.
+# ---------------------------------------------------------------------------------------------
+_T = Optional[torch.Tensor]
+
+
+@torch.library.custom_op("b200moe::quantize_mxfp8", mutates_args=("q", "sf"), device_types="cuda")
+def _quantize_mxfp8_op(x: torch.Tensor, q: torch.Tensor, sf: torch.Tensor) -> None:
+    quantize_mxfp8_out(x, q, sf)
+
+
+@_quantize_mxfp8_op.register_fake
+def _(x, q, sf) -> None:
+    return None
+
+
+@torch.library.custom_op(
+    "b200moe::fc1_swiglu", mutates_args=("c", "d", "d_col", "amax", "sfd_row", "sfd_col", "workspace"), device_types="cuda"
+)
+def _fc1_swiglu_op(
+    a: torch.Tensor, sfa: torch.Tensor, b: _T, sfb: _T, b_ptrs: _T, sfb_ptrs: _T, padded_offsets: torch.Tensor,
+    alpha: torch.Tensor, prob: _T, norm_const: _T, c: _T, d: torch.Tensor, d_col: _T, amax: _T, sfd_row: _T,
+    sfd_col: _T, workspace: _T, n: int, discrete_col_sfd: bool, sm_margin: int, tile_mode: str,
+) -> None:  # fmt: skip
+    launch_grouped_gemm(
+        "fc1", a=a, sfa=sfa, b=b, sfb=sfb, b_ptrs=b_ptrs, sfb_ptrs=sfb_ptrs, padded_offsets=padded_offsets, alpha=alpha,
+        prob=prob, norm_const=norm_const, c=c, d=d, d_col=d_col, amax=amax, sfd_row=sfd_row, sfd_col=sfd_col,
+        workspace=workspace, m_rows=a.shape[0], n=n, k=a.shape[1], num_experts=padded_offsets.shape[0],
+        discrete_col_sfd=discrete_col_sfd, sm_margin=sm_margin, tile_mode=tile_mode or None,
+    )  # fmt: skip
+
+
+@_fc1_swiglu_op.register_fake
+def _(a, sfa, b, sfb, b_ptrs, sfb_ptrs, padded_offsets, alpha, prob, norm_const, c, d, d_col, amax, sfd_row, sfd_col,
+      workspace, n, discrete_col_sfd, sm_margin, tile_mode) -> None:  # fmt: skip
+    return None
+
+
+@torch.library.custom_op(
+    "b200moe::fc2_quant", mutates_args=("d", "d_col", "amax", "sfd_row", "sfd_col", "workspace"), device_types="cuda"
+)
+def _fc2_quant_op(
+    a: torch.Tensor, sfa: torch.Tensor, b: _T, sfb: _T, b_ptrs: _T, sfb_ptrs: _T, padded_offsets: torch.Tensor,
+    alpha: torch.Tensor, prob: torch.Tensor, norm_const: _T, d: torch.Tensor, d_col: _T, amax: _T, sfd_row: _T,
+    sfd_col: _T, workspace: _T, d_row_map: _T, n: int, discrete_col_sfd: bool, sm_margin: int, tile_mode: str,
+) -> None:  # fmt: skip
+    launch_grouped_gemm(
+        "fc2", a=a, sfa=sfa, b=b, sfb=sfb, b_ptrs=b_ptrs, sfb_ptrs=sfb_ptrs, padded_offsets=padded_offsets, alpha=alpha,
+        prob=prob, norm_const=norm_const, d=d, d_col=d_col, amax=amax, sfd_row=sfd_row, sfd_col=sfd_col,
+        workspace=workspace, m_rows=a.shape[0], n=n, k=a.shape[1], num_experts=padded_offsets.shape[0],
+        discrete_col_sfd=discrete_col_sfd, sm_margin=sm_margin, tile_mode=tile_mode or None, d_row_map=d_row_map,
+    )  # fmt: skip
+
+
+@_fc2_quant_op.register_fake
+def _(a, sfa, b, sfb, b_ptrs, sfb_ptrs, padded_offsets, alpha, prob, norm_const, d, d_col, amax, sfd_row, sfd_col, workspace,
+      d_row_map, n, discrete_col_sfd, sm_margin, tile_mode) -> None:  # fmt: skip
+    return None
+
+
+def grouped_gemm_op(kind: str, *, stream=None, **kw) -> None:
+    """Launch FC1 / FC2 through the registered custom op (``torch.ops.b200moe.fc1_swiglu`` /
+    ``fc2_quant``).  An explicit ``stream`` is honoured by making it current for the call: custom
+    ops take tensors and plain scalars only."""
+    ctx = torch.cuda.stream(stream) if isinstance(stream, torch.cuda.Stream) else None
+    if stream is not None and ctx is None:
+        ctx = torch.cuda.stream(torch.cuda.ExternalStream(int(stream)))
+    common = (kw["a"], kw["sfa"], kw.get("b"), kw.get("sfb"), kw.get("b_ptrs"), kw.get("sfb_ptrs"), kw["padded_offsets"],
+              kw["alpha"], kw.get("prob"), kw.get("norm_const"))  # fmt: skip
+    tail = (kw["n"], bool(kw.get("discrete_col_sfd", False)), int(kw.get("sm_margin", 0)), kw.get("tile_mode") or "")
+    outs = (kw["d"], kw.get("d_col"), kw.get("amax"), kw.get("sfd_row"), kw.get("sfd_col"), kw.get("workspace"))
+
+    def call():
+        if kind == "fc1":
+            torch.ops.b200moe.fc1_swiglu(*common, kw.get("c"), *outs, *tail)
+        else:
+            torch.ops.b200moe.fc2_quant(*common, *outs, kw.get("d_row_map"), *tail)
+
+    if ctx is None:
+        call()
+    else:
+        with ctx:
+            call()

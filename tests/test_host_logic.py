@@ -160,3 +160,14 @@ def test_interleave_gate_up_matches_oracle():
     u = -g
     w = cf.interleave_gate_up(g, u)
     assert torch.equal(w, torch.from_numpy(orc.interleave_gate_up(g.numpy(), u.numpy())))
+
+
+def test_custom_ops_are_registered_with_mutation_schemas():
+    from cudnn_frontend_b200 import ops  # noqa: F401  (registration happens at import)
+
+    for name, mutated in (("fc1_swiglu", ("c", "d", "amax", "sfd_row")), ("fc2_quant", ("d", "amax", "sfd_row")), ("quantize_mxfp8", ("q", "sf"))):
+        schema = getattr(torch.ops.b200moe, name).default._schema
+        args = {a.name: a for a in schema.arguments}
+        for m in mutated:
+            assert args[m].alias_info is not None and args[m].alias_info.is_write, f"{name}.{m} must be declared mutable"
+        assert not args["a" if name != "quantize_mxfp8" else "x"].alias_info
