@@ -1,0 +1,190 @@
+"""Run the reference's own CuTe-DSL grouped-GEMM kernels next to this repository's on one GPU.
+
+Needs the overlay made by baseline/make_ref_overlay.py (baseline/_ref/cudnn) and the CuTe DSL
+(nvidia-cutlass-dsl) of the image.  For each case the same device tensors go through
+
+    reference:  cudnn.grouped_gemm_swiglu_wrapper_sm100 / grouped_gemm_quant_wrapper_sm100
+    here:       cudnn_frontend_b200.<same names>
+
+with the reference's constraints (groups padded to 256, mma_tiler (256, 256)), then outputs are
+compared (C bf16, E8M0 scale bytes, E4M3 ULP distance) and both are timed with CUDA events
+(3 warm-ups, 10 trials, 256 MiB L2 flush between trials, median and best).  Results go to
+gpurun_out/reference_kernels_<cases>.json; the tiny case's inputs and reference-kernel outputs are saved
+to gpurun_out/reference_kernel_golden.npz so they can be committed as golden vectors.
+
+    python baseline/run_reference_kernels.py --cases tiny      # one case per process: the reference's
+    python baseline/run_reference_kernels.py --cases c2        # wrapper cache does not key on the expert count
+"""
+
+import argparse
+import json
+import os
+import sys
+import time
+import traceback
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+
+
+def timed(fn, trials=10, warmup=3):
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for _ in range(warmup):
+        fn()
+    times = []
+    for _ in range(trials):
+        flush.zero_()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        times.append(s.elapsed_time(e))
+    ordered = sorted(times)
+    return ordered[len(ordered) // 2], ordered[0], times
+
+
+def timed_back_to_back(fn, steps=20, warmup=3):
+    """Sustained protocol: `steps` launches in a row between two events (what bench.py does)."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(steps):
+        fn()
+    e.record()
+    torch.cuda.synchronize()
+    return s.elapsed_time(e) / steps
+
+
+def ulp(a, b):
+    def order(v):
+        v = v.to(torch.int32)
+        mag = v & 0x7F
+        return torch.where((v & 0x80) != 0, -mag, mag)
+
+    return (order(a) - order(b)).abs()
+
+
+def run_case(name, cfg, out):
+    import cuda.bindings.driver as cuda
+    import cudnn as ref  # the overlay
+
+    import cudnn_frontend_b200 as ours
+    from cudnn_frontend_b200 import synthetic
+
+    p = synthetic.make_problem(cfg, "cuda", seed=3, m_aligned=256)
+    n, k = cfg["n"], cfg["k"]
+    norm = torch.tensor([1.0], dtype=torch.float32, device="cuda")
+    stream = cuda.CUstream(torch.cuda.current_stream().cuda_stream)
+    common = dict(norm_const_tensor=norm, prob_tensor=p["prob"], d_dtype=torch.float8_e4m3fn, sf_vec_size=32, m_aligned=256)
+    res = {"case": name, "cfg": cfg, "m_rows": p["m_rows"], "flops": p["flops"]}
+
+    t0 = time.time()
+    r_ref = ref.grouped_gemm_swiglu_wrapper_sm100(p["a"], p["b"], p["sfa"], p["sfb"], p["padded_offsets"], p["alpha"],
+                                                  mma_tiler_mn=(256, 256), current_stream=stream, **common)  # fmt: skip
+    torch.cuda.synchronize()
+    res["ref_first_call_s"] = time.time() - t0
+    r_own = ours.grouped_gemm_swiglu_wrapper_sm100(p["a"], p["b"], p["sfa"], p["sfb"], p["padded_offsets"], p["alpha"], **common)
+    torch.cuda.synchronize()
+
+    if PROFILE_ONLY:  # two launches of each kernel for a profiler capture, nothing else
+        ref.grouped_gemm_swiglu_wrapper_sm100(p["a"], p["b"], p["sfa"], p["sfb"], p["padded_offsets"], p["alpha"],
+                                              mma_tiler_mn=(256, 256), current_stream=stream, **common)  # fmt: skip
+        ours.grouped_gemm_swiglu_wrapper_sm100(p["a"], p["b"], p["sfa"], p["sfb"], p["padded_offsets"], p["alpha"], **common)
+        torch.cuda.synchronize()
+        return
+    m = p["m_rows"]
+    c_ref, c_own = r_ref["c_tensor"][:m].float(), r_own["c_tensor"][:m].float()
+    res["c_rel_fro"] = float((c_ref - c_own).norm() / c_ref.norm())
+    res["c_equal_frac"] = float((r_ref["c_tensor"][:m] == r_own["c_tensor"][:m]).float().mean())
+
+    def flat(t):
+        t = t.view(torch.uint8)
+        return torch.as_strided(t, (t.numel(),), (1,))
+
+    sf_r, sf_o = flat(r_ref["sfd_row_tensor"]), flat(r_own["sfd_row_tensor"])
+    res["sfd_row_bytes_equal_frac"] = float((sf_r == sf_o).float().mean())
+    d_r, d_o = r_ref["d_tensor"][:m].view(torch.uint8), r_own["d_tensor"][:m].view(torch.uint8)
+    u = ulp(d_r, d_o)
+    res["d_e4m3_within_1ulp_frac"] = float((u <= 1).float().mean())
+    res["d_e4m3_equal_frac"] = float((u == 0).float().mean())
+    sc_r, sc_o = flat(r_ref["sfd_col_tensor"]), flat(r_own["sfd_col_tensor"])
+    res["sfd_col_bytes_equal_frac"] = float((sc_r == sc_o).float().mean())
+    uc = ulp(r_ref["d_col_tensor"][:m].view(torch.uint8), r_own["d_col_tensor"][:m].view(torch.uint8))
+    res["d_col_within_1ulp_frac"] = float((uc <= 1).float().mean())
+
+    ms_ref = timed(lambda: ref.grouped_gemm_swiglu_wrapper_sm100(p["a"], p["b"], p["sfa"], p["sfb"], p["padded_offsets"], p["alpha"],
+                                                                mma_tiler_mn=(256, 256), current_stream=stream, **common))  # fmt: skip
+    ms_own = timed(lambda: ours.grouped_gemm_swiglu_wrapper_sm100(p["a"], p["b"], p["sfa"], p["sfb"], p["padded_offsets"], p["alpha"], **common))
+    res["ref_ms_median_best"] = ms_ref[:2]
+    res["own_ms_median_best"] = ms_own[:2]
+    res["ref_ms_trials"] = ms_ref[2]
+    res["own_ms_trials"] = ms_own[2]
+    res["ref_ms_back_to_back"] = timed_back_to_back(lambda: ref.grouped_gemm_swiglu_wrapper_sm100(
+        p["a"], p["b"], p["sfa"], p["sfb"], p["padded_offsets"], p["alpha"], mma_tiler_mn=(256, 256), current_stream=stream, **common))
+    res["own_ms_back_to_back"] = timed_back_to_back(lambda: ours.grouped_gemm_swiglu_wrapper_sm100(
+        p["a"], p["b"], p["sfa"], p["sfb"], p["padded_offsets"], p["alpha"], **common))
+    res["own_over_ref_back_to_back"] = res["ref_ms_back_to_back"] / res["own_ms_back_to_back"]
+    res["ref_tflops"] = p["flops"] / (ms_ref[0] * 1e-3) / 1e12
+    res["own_tflops"] = p["flops"] / (ms_own[0] * 1e-3) / 1e12
+    res["own_over_ref"] = ms_ref[0] / ms_own[0]
+    out.append(res)
+    print(json.dumps(res), flush=True)
+
+    if name == "tiny":
+        np.savez_compressed(
+            os.path.join(ROOT, "gpurun_out", "reference_kernel_golden.npz"),
+            a=p["a"][:, :, 0].view(torch.uint8).cpu().numpy(),
+            b=p["b"].permute(2, 0, 1).contiguous().view(torch.uint8).cpu().numpy(),
+            sfa=flat(p["sfa"]).cpu().numpy(),
+            sfb=flat(p["sfb"]).cpu().numpy(),
+            offsets=p["padded_offsets"].cpu().numpy(),
+            prob=p["prob"].view(-1).cpu().numpy(),
+            c=r_ref["c_tensor"][:, :, 0].view(torch.int16).cpu().numpy(),
+            d=d_r[:, :, 0].cpu().numpy(),
+            d_col=r_ref["d_col_tensor"][:m, :, 0].view(torch.uint8).cpu().numpy(),
+            sfd_row=sf_r.cpu().numpy(),
+            sfd_col=sc_r.cpu().numpy(),
+        )
+
+
+PROFILE_ONLY = False
+
+CASES = {
+    # reduced Mixtral shape for profiler captures (operands still exceed L2)
+    "mid": dict(experts=8, k=4096, n=7168, tokens=4096, topk=2, routing="uniform"),
+    # small enough to commit its inputs and the reference kernel's outputs as a fixture
+    "tiny": dict(experts=2, k=128, n=128, tokens=128, topk=2, routing="uniform"),
+    "small": dict(experts=4, k=512, n=512, tokens=512, topk=2, routing="uniform"),
+    "c2": dict(experts=8, k=4096, n=28672, tokens=16384, topk=2, routing="uniform"),
+    "c3": dict(experts=256, k=7168, n=4096, tokens=8192, topk=8, routing="zipf"),
+}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--cases", default="tiny")
+    ap.add_argument("--profile", action="store_true", help="launch each kernel twice and exit (for ncu)")
+    args = ap.parse_args()
+    global PROFILE_ONLY
+    PROFILE_ONLY = args.profile
+    os.makedirs(os.path.join(ROOT, "gpurun_out"), exist_ok=True)
+    out = []
+    for name in args.cases.split(","):
+        try:
+            run_case(name, CASES[name], out)
+        except Exception as exc:  # keep going: a JIT failure of one case is a result too
+            out.append({"case": name, "error": f"{type(exc).__name__}: {exc}"})
+            traceback.print_exc()
+        with open(os.path.join(ROOT, "gpurun_out", f"reference_kernels_{args.cases.replace(',', '_')}.json"), "w") as f:
+            json.dump(out, f, indent=1)
+
+
+if __name__ == "__main__":
+    main()

@@ -216,6 +216,26 @@ def bench_single(args):
     m = prob_["m_rows"]
     flops = prob_["flops"]
 
+    def make_full_op():
+        """The output set of the reference's wrapper for fp8 inputs: C (bf16), D and D_col (E4M3), row
+        and column scale factors."""
+        d8 = torch.empty((m, n // 2, 1), dtype=torch.float8_e4m3fn, device=dev)
+        dc8 = torch.empty((m, n // 2, 1), dtype=torch.float8_e4m3fn, device=dev)
+        c = torch.empty((m, n, 1), dtype=torch.bfloat16, device=dev)
+        sr, sc = ops.empty_sf(m, n // 2, 1, device=dev), ops.empty_sf(n // 2, m, 1, device=dev)
+        norm = torch.ones(1, device=dev)
+        op = cf.GroupedGemmSwigluSm100(prob_["a"], prob_["b"], c, d8, prob_["sfa"], prob_["sfb"], prob_["padded_offsets"], prob_["alpha"],
+                                       dc8, sample_sfd_row=sr, sample_sfd_col=sc, sample_norm_const=norm, sample_prob=prob_["prob"],
+                                       sf_vec_size=32, m_aligned=128)  # fmt: skip
+        assert op.check_support()
+        op.compile()
+
+        def step():
+            op.execute(prob_["a"], prob_["b"], c, d8, prob_["sfa"], prob_["sfb"], prob_["padded_offsets"], prob_["alpha"],
+                       d_col_tensor=dc8, sfd_row_tensor=sr, sfd_col_tensor=sc, norm_const_tensor=norm, prob_tensor=prob_["prob"])  # fmt: skip
+
+        return step, (c, d8, dc8, sr, sc)
+
     def make_op(write_c):
         d = torch.empty((m, n // 2, 1), dtype=torch.bfloat16, device=dev)
         c = torch.empty((m, n, 1), dtype=torch.bfloat16, device=dev) if write_c else None
@@ -231,7 +251,7 @@ def bench_single(args):
 
         return step, (c, d, amax)
 
-    step, outs = make_op(write_c=False)
+    step, outs = make_full_op() if args.outputs == "full" else make_op(write_c=False)
     with ClockSampler(0) as clk:
         ms = time_steps(step, args.steps, args.warmup, stream)
     value = flops / (ms * 1e-3) / 1e12
@@ -241,10 +261,14 @@ def bench_single(args):
                           "config": {"workload": f"kernel only, {args.workload}: {cfg}"}, "clocks": clk.summary()}))  # fmt: skip
         return
 
-    # the same call with the bf16 pre-activation C also written (what the reference's wrapper always does)
+    # the same call with the bf16 pre-activation C also written, and with the full output set of the
+    # reference's wrapper (C, E4M3 D and D_col, row and column scale factors)
     step_c, outs_c = make_op(write_c=True)
     ms_c = time_steps(step_c, max(args.steps // 2, 3), 3, stream)
     del outs_c, step_c
+    step_f, outs_f = make_full_op()
+    ms_full = time_steps(step_f, max(args.steps // 2, 3), 3, stream)
+    del outs_f, step_f
 
     # ---- end to end through the public API from pinned host memory -------------------------
     routing = prob_["routing"]
@@ -295,7 +319,7 @@ def bench_single(args):
     quant = {"gbs": q_bytes / (ms_q * 1e-3) / 1e9, "frac_of_measured_hbm": q_bytes / (ms_q * 1e-3) / 1e9 / peaks["hbm_gbs"], "shape": [32768, 4096]}
     del xq, q_out, sf_out
 
-    extras = {"fc1_with_c_store_tflops": flops / (ms_c * 1e-3) / 1e12, "quantiser": quant, "e2e_amax_matches_resident_run": e2e_amax_ok}
+    extras = {"fc1_with_c_store_tflops": flops / (ms_c * 1e-3) / 1e12, "fc1_full_output_set_tflops": flops / (ms_full * 1e-3) / 1e12, "quantiser": quant, "e2e_amax_matches_resident_run": e2e_amax_ok}
     if not args.no_extras:
         del prob_, outs, op2, xg, aq, d2
         torch.cuda.empty_cache()
@@ -417,6 +441,7 @@ def main():
     ap.add_argument("--impl", default="own", choices=["own", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the DeepSeek-shape side measurements")
     ap.add_argument("--workload", default="c2", choices=["c2", "small"], help="c2 = Mixtral-shape FC1 (the benchmark); small = reduced case for profiler captures")
+    ap.add_argument("--outputs", default="d", choices=["d", "full"], help="with --kernel-only: d = bf16 D + amax (the benchmark); full = C + E4M3 D + D_col + scale factors")
     ap.add_argument("--kernel-only", action="store_true", help="time the FC1 kernel only (no end-to-end, CPU baseline or side measurements)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "own" else args.warmup

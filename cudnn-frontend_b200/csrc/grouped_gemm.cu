@@ -322,6 +322,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      const uint32_t a_dst0 = smem_base + C::A_OFF, b_dst0 = smem_base + C::B_OFF;
+      const uint32_t sfa_dst0 = smem_base + C::SFA_OFF, sfb_dst0 = smem_base + C::SFB_OFF;
+      const uint32_t leader_full0 = kPair ? map_to_cta(full_bar(0), 0) : full_bar(0);
       for (int t = sched_id; t < total_tiles && ok; t += sched_stride) {
         const Tile tile = decode_tile(prefix, p.offsets, p.num_experts, p.n_tiles, C::TILE_M, t);
         const int n0 = tile.n_tile * BN;
@@ -337,44 +340,50 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             tensormap_fence_acquire(sfbmap);
           }
         }
+        // Everything that changes per k-tile is a running value: the K coordinate, the scale-chunk
+        // pointers and the stage's shared-memory / barrier addresses.  The issuing thread's
+        // instruction count per k-tile bounds how fast stages can be refilled.
+        int kc = 0;
         if constexpr (kPair) {
           // every load of either CTA credits the leader's barrier of this stage
-          for (int kt = 0; kt < p.k_tiles; ++kt) {
+          const int b_row = n0 + (int)cta_rank * 128;
+          const int m_blk = my_row0 / BM;
+          for (int kt = 0; kt < p.k_tiles; ++kt, kc += BK) {
             if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, ST_PRODUCER_EMPTY)) { ok = false; break; }
             if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(stage), C::TX_BYTES);
-            const uint32_t fb = map_to_cta(full_bar(stage), 0);
-            tma_load_2d_pair(smem_base + C::A_OFF + stage * A_STAGE_BYTES, &tmap_a, fb, kt * BK, my_row0);
+            const uint32_t fb = leader_full0 + 8u * stage;
+            tma_load_2d_pair(a_dst0 + stage * A_STAGE_BYTES, &tmap_a, fb, kc, my_row0);
             if (kDiscrete)
-              tma_load_2d_pair(smem_base + C::B_OFF + stage * C::B_STAGE_BYTES, bmap, fb, kt * BK, n0 + (int)cta_rank * 128);
+              tma_load_2d_pair(b_dst0 + stage * C::B_STAGE_BYTES, bmap, fb, kc, b_row);
             else
-              tma_load_3d_pair(smem_base + C::B_OFF + stage * C::B_STAGE_BYTES, bmap, fb, kt * BK, n0 + (int)cta_rank * 128,
-                               tile.expert);
-            tma_load_3d_pair(smem_base + C::SFA_OFF + stage * SFA_STAGE_BYTES, &tmap_sfa, fb, 0, kt, my_row0 / BM);
+              tma_load_3d_pair(b_dst0 + stage * C::B_STAGE_BYTES, bmap, fb, kc, b_row, tile.expert);
+            tma_load_3d_pair(sfa_dst0 + stage * SFA_STAGE_BYTES, &tmap_sfa, fb, 0, kt, m_blk);
             if (kDiscrete)
-              tma_load_3d_pair(smem_base + C::SFB_OFF + stage * SFB_STAGE_BYTES, sfbmap, fb, 0, kt, nblk0);
+              tma_load_3d_pair(sfb_dst0 + stage * SFB_STAGE_BYTES, sfbmap, fb, 0, kt, nblk0);
             else
-              tma_load_4d_pair(smem_base + C::SFB_OFF + stage * SFB_STAGE_BYTES, sfbmap, fb, 0, kt, nblk0, tile.expert);
+              tma_load_4d_pair(sfb_dst0 + stage * SFB_STAGE_BYTES, sfbmap, fb, 0, kt, nblk0, tile.expert);
             if (++stage == STAGES) { stage = 0; phase ^= 1; }
           }
         } else {
           const uint8_t* sfa_src = p.sfa + (int64_t)(tile.row0 / BM) * p.rest_k * 512;
           const uint8_t* sfb_e = kDiscrete ? reinterpret_cast<const uint8_t*>(p.sfb_ptrs[tile.expert])
                                            : p.sfb + (int64_t)tile.expert * p.sfb_expert_bytes;
-          const int sfb_chunks = min(2, p.n_blocks - nblk0);
-          const uint32_t tx = A_STAGE_BYTES + C::B_STAGE_BYTES + SFA_STAGE_BYTES + 512u * sfb_chunks;
-          for (int kt = 0; kt < p.k_tiles; ++kt) {
+          const uint8_t* sfb_src0 = sfb_e + (int64_t)nblk0 * p.rest_k * 512;
+          const uint8_t* sfb_src1 = sfb_src0 + (int64_t)p.rest_k * 512;
+          const bool two_chunks = p.n_blocks - nblk0 >= 2;
+          const uint32_t tx = A_STAGE_BYTES + C::B_STAGE_BYTES + SFA_STAGE_BYTES + (two_chunks ? 1024u : 512u);
+          for (int kt = 0; kt < p.k_tiles; ++kt, kc += BK, sfa_src += 512, sfb_src0 += 512, sfb_src1 += 512) {
             if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, ST_PRODUCER_EMPTY)) { ok = false; break; }
             const uint32_t fb = full_bar(stage);
             mbar_arrive_expect_tx(fb, tx);
-            tma_load_2d(smem_base + C::A_OFF + stage * A_STAGE_BYTES, &tmap_a, fb, kt * BK, tile.row0);
+            tma_load_2d(a_dst0 + stage * A_STAGE_BYTES, &tmap_a, fb, kc, tile.row0);
             if (kDiscrete)
-              tma_load_2d(smem_base + C::B_OFF + stage * C::B_STAGE_BYTES, bmap, fb, kt * BK, n0);
+              tma_load_2d(b_dst0 + stage * C::B_STAGE_BYTES, bmap, fb, kc, n0);
             else
-              tma_load_3d(smem_base + C::B_OFF + stage * C::B_STAGE_BYTES, bmap, fb, kt * BK, n0, tile.expert);
-            bulk_load(smem_base + C::SFA_OFF + stage * SFA_STAGE_BYTES, sfa_src + (int64_t)kt * 512, 512, fb);
-            for (int j = 0; j < sfb_chunks; ++j)
-              bulk_load(smem_base + C::SFB_OFF + stage * SFB_STAGE_BYTES + j * 512,
-                        sfb_e + ((int64_t)(nblk0 + j) * p.rest_k + kt) * 512, 512, fb);
+              tma_load_3d(b_dst0 + stage * C::B_STAGE_BYTES, bmap, fb, kc, n0, tile.expert);
+            bulk_load(sfa_dst0 + stage * SFA_STAGE_BYTES, sfa_src, 512, fb);
+            bulk_load(sfb_dst0 + stage * SFB_STAGE_BYTES, sfb_src0, 512, fb);
+            if (two_chunks) bulk_load(sfb_dst0 + stage * SFB_STAGE_BYTES + 512, sfb_src1, 512, fb);
             if (++stage == STAGES) { stage = 0; phase ^= 1; }
           }
         }
@@ -384,7 +393,18 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
   } else if (warp == 1) {
     // ================= MMA issuer (the leader CTA only, in pair mode) =====================
     if (lane == 0 && cta_rank == 0) {
+      // The issuing thread is a serial instruction stream: four MMAs, three scale copies and a
+      // commit per k-tile must cost as few instructions as possible, so every descriptor is
+      // (constant high word, running low word) and the instruction descriptors are immediates.
       constexpr uint32_t idesc = make_idesc_mxf8(C::TILE_M, BN);
+      constexpr uint32_t AB_HI = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO 1024, version 1, 128-byte swizzle
+      constexpr uint32_t SF_HI = (128u >> 4) | (1u << 14);                // SBO 128, version 1, no swizzle
+      constexpr uint32_t AB_LBO = 1u << 16;                               // leading byte offset 16 (unused by swizzled K-major)
+      const uint32_t a_lo0 = ((smem_base + C::A_OFF) >> 4) | AB_LBO;
+      const uint32_t b_lo0 = ((smem_base + C::B_OFF) >> 4) | AB_LBO;
+      const uint32_t sfa_lo0 = (smem_base + C::SFA_OFF) >> 4;
+      const uint32_t sfb_lo0 = (smem_base + C::SFB_OFF) >> 4;
+      auto desc = [](uint32_t lo, uint32_t hi) { return ((uint64_t)hi << 32) | lo; };
       int stage = 0;
       uint32_t phase = 0;
       uint32_t sf_buf = 0;
@@ -398,33 +418,50 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           tc_fence_after();
         }
         for (int kt = 0; kt < p.k_tiles; ++kt) {
-          if (!mbar_wait(full_bar(stage), phase, abort_flag, ST_MMA_FULL)) { ok = false; break; }
+          if (!mbar_try_wait(full_bar(stage), phase)) {
+            if (!mbar_wait(full_bar(stage), phase, abort_flag, ST_MMA_FULL)) { ok = false; break; }
+          }
           tc_fence_after();
           const uint32_t sfa_t = tmem_base + TMEM_SF_COL + 16 * sf_buf;
           const uint32_t sfb_t = sfa_t + 4;
-          const uint32_t sfa_s = smem_base + C::SFA_OFF + stage * SFA_STAGE_BYTES;
-          const uint32_t sfb_s = smem_base + C::SFB_OFF + stage * SFB_STAGE_BYTES;
-          const uint64_t adesc = make_smem_desc(smem_base + C::A_OFF + stage * A_STAGE_BYTES, 16, 1024, 2);
-          const uint64_t bdesc = make_smem_desc(smem_base + C::B_OFF + stage * C::B_STAGE_BYTES, 16, 1024, 2);
-          const int k_left = p.k - kt * BK;
-          const int kblocks = min(4, (k_left + 31) / 32);
+          const uint32_t a_lo = a_lo0 + stage * (A_STAGE_BYTES >> 4);
+          const uint32_t b_lo = b_lo0 + stage * (C::B_STAGE_BYTES >> 4);
+          const uint32_t sfa_lo = sfa_lo0 + stage * (SFA_STAGE_BYTES >> 4);
+          const uint32_t sfb_lo = sfb_lo0 + stage * (SFB_STAGE_BYTES >> 4);
+          const uint32_t not_first = kt != 0;
+          const bool full_k = p.k - kt * BK >= BK;
           if constexpr (kPair) {
             // one instruction acts on both CTAs: each copies from its own smem to its own TMEM
-            tmem_cp_sf_pair(sfa_t, make_smem_desc(sfa_s, 0, 128, 0));
-            tmem_cp_sf_pair(sfb_t, make_smem_desc(sfb_s, 0, 128, 0));
-            tmem_cp_sf_pair(sfb_t + 4, make_smem_desc(sfb_s + 512, 0, 128, 0));
-            for (int kb = 0; kb < kblocks; ++kb)
-              mma_mxf8_ss_pair(acc, adesc + 2 * kb, bdesc + 2 * kb, idesc_with_sf_id(idesc, kb, kb), sfa_t, sfb_t,
-                               (kt | kb) != 0);
+            tmem_cp_sf_pair(sfa_t, desc(sfa_lo, SF_HI));
+            tmem_cp_sf_pair(sfb_t, desc(sfb_lo, SF_HI));
+            tmem_cp_sf_pair(sfb_t + 4, desc(sfb_lo + 32, SF_HI));
+            if (full_k) {
+              // 32 bytes along K inside the 128-byte swizzle row = +2 in 16-byte units
+              mma_mxf8_ss_pair(acc, desc(a_lo, AB_HI), desc(b_lo, AB_HI), idesc_with_sf_id(idesc, 0, 0), sfa_t, sfb_t, not_first);
+              mma_mxf8_ss_pair(acc, desc(a_lo + 2, AB_HI), desc(b_lo + 2, AB_HI), idesc_with_sf_id(idesc, 1, 1), sfa_t, sfb_t, 1);
+              mma_mxf8_ss_pair(acc, desc(a_lo + 4, AB_HI), desc(b_lo + 4, AB_HI), idesc_with_sf_id(idesc, 2, 2), sfa_t, sfb_t, 1);
+              mma_mxf8_ss_pair(acc, desc(a_lo + 6, AB_HI), desc(b_lo + 6, AB_HI), idesc_with_sf_id(idesc, 3, 3), sfa_t, sfb_t, 1);
+            } else {
+              const int kblocks = (p.k - kt * BK + 31) / 32;
+              for (int kb = 0; kb < kblocks; ++kb)
+                mma_mxf8_ss_pair(acc, desc(a_lo + 2 * kb, AB_HI), desc(b_lo + 2 * kb, AB_HI), idesc_with_sf_id(idesc, kb, kb), sfa_t,
+                                 sfb_t, (kt | kb) != 0);
+            }
             tc_commit_pair(empty_bar(stage), 3);  // frees this stage in both CTAs
           } else {
-            tmem_cp_sf(sfa_t, make_smem_desc(sfa_s, 0, 128, 0));
-            tmem_cp_sf(sfb_t, make_smem_desc(sfb_s, 0, 128, 0));
-            tmem_cp_sf(sfb_t + 4, make_smem_desc(sfb_s + 512, 0, 128, 0));
-            for (int kb = 0; kb < kblocks; ++kb) {
-              // advance 32 bytes along K inside the 128-byte swizzle row: +2 in 16-byte units
-              mma_mxf8_ss(acc, adesc + 2 * kb, bdesc + 2 * kb, idesc_with_sf_id(idesc, kb, kb), sfa_t, sfb_t,
-                          (kt | kb) != 0);
+            tmem_cp_sf(sfa_t, desc(sfa_lo, SF_HI));
+            tmem_cp_sf(sfb_t, desc(sfb_lo, SF_HI));
+            tmem_cp_sf(sfb_t + 4, desc(sfb_lo + 32, SF_HI));
+            if (full_k) {
+              mma_mxf8_ss(acc, desc(a_lo, AB_HI), desc(b_lo, AB_HI), idesc_with_sf_id(idesc, 0, 0), sfa_t, sfb_t, not_first);
+              mma_mxf8_ss(acc, desc(a_lo + 2, AB_HI), desc(b_lo + 2, AB_HI), idesc_with_sf_id(idesc, 1, 1), sfa_t, sfb_t, 1);
+              mma_mxf8_ss(acc, desc(a_lo + 4, AB_HI), desc(b_lo + 4, AB_HI), idesc_with_sf_id(idesc, 2, 2), sfa_t, sfb_t, 1);
+              mma_mxf8_ss(acc, desc(a_lo + 6, AB_HI), desc(b_lo + 6, AB_HI), idesc_with_sf_id(idesc, 3, 3), sfa_t, sfb_t, 1);
+            } else {
+              const int kblocks = (p.k - kt * BK + 31) / 32;
+              for (int kb = 0; kb < kblocks; ++kb)
+                mma_mxf8_ss(acc, desc(a_lo + 2 * kb, AB_HI), desc(b_lo + 2 * kb, AB_HI), idesc_with_sf_id(idesc, kb, kb), sfa_t, sfb_t,
+                            (kt | kb) != 0);
             }
             tc_commit(empty_bar(stage));  // frees the smem stage once these MMAs have read it
           }

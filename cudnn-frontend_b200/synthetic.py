@@ -90,7 +90,8 @@ def make_activations(routing: Routing, k: int, seed: int, device):
     moe.zero_pad_rows(xg, routing.counts, routing.padded_offsets, prob)
     a, sfa = ops.quantize_mxfp8(xg)
     del xg
-    return x, a.view(m, k, 1), sfa, prob.view(m, 1, 1)
+    # the reference validates the stride of the unit dimension too: (K, 1, M*K)
+    return x, torch.as_strided(a, (m, k, 1), (k, 1, m * k)), sfa, prob.view(m, 1, 1)
 
 
 def make_problem(name_or_cfg, device="cuda", seed: int = 0, m_aligned: int = 128, with_weights: bool = True) -> dict:

@@ -400,3 +400,45 @@ def test_fc1_fc2_chain_matches_layer_oracle(tile_mode):
         w1b, H.sf_to_numpy(sfw1, 2 * inter, h // 32, e), w2b, H.sf_to_numpy(sfw2, h, inter // 32, e), 128,
     )  # fmt: skip
     assert H.rel_fro(y.float().cpu().numpy(), ref) <= BF16_GATE
+
+
+# ---------------------------------------------------------------------------------------------
+# fixture produced by the reference's own CuTe-DSL kernel on a B200 (baseline/run_reference_kernels.py)
+# ---------------------------------------------------------------------------------------------
+def test_fc1_is_bit_identical_to_the_reference_kernel_fixture(golden_dir, tile_mode):
+    """Inputs and outputs of cudnn-frontend's grouped_gemm_swiglu_wrapper_sm100 (fp8 in, E4M3 D,
+    norm_const 1, groups padded to 256) recorded on a B200: C, D, D_col and both scale-factor
+    tensors must match byte for byte (E8M0 round-up, E4M3 RNE-saturate, approx-SiLU order)."""
+    path = os.path.join(golden_dir, "reference_kernel_fc1.npz")
+    if not os.path.exists(path):
+        pytest.skip("reference-kernel fixture not recorded")
+    cf = _api()
+    from cudnn_frontend_b200 import ops
+
+    g = np.load(path)
+    m, k = g["a"].shape
+    e, n, _ = g["b"].shape
+    dev = "cuda"
+
+    def sf(flat, mn, kk, l):
+        shape, stride = ops.sf_shape_stride(mn, kk, l)
+        return torch.as_strided(torch.from_numpy(flat).to(dev).view(torch.float8_e8m0fnu), shape, stride)
+
+    a = H.dev_fp8(g["a"]).view(m, k, 1)
+    b = H.dev_fp8(g["b"]).permute(1, 2, 0)
+    out = cf.grouped_gemm_swiglu_wrapper_sm100(
+        a, b, sf(g["sfa"], m, k, 1), sf(g["sfb"], n, k, e), torch.from_numpy(g["offsets"]).to(dev), torch.ones(e, device=dev),
+        norm_const_tensor=torch.ones(1, device=dev), prob_tensor=torch.from_numpy(g["prob"]).to(dev).view(m, 1, 1),
+        d_dtype=torch.float8_e4m3fn, sf_vec_size=32, m_aligned=256,
+    )  # fmt: skip
+    torch.cuda.synchronize()
+
+    def flat(t):
+        t = t.view(torch.uint8)
+        return torch.as_strided(t, (t.numel(),), (1,)).cpu().numpy()
+
+    np.testing.assert_array_equal(out["c_tensor"][:, :, 0].view(torch.int16).cpu().numpy(), g["c"])
+    np.testing.assert_array_equal(out["d_tensor"][:, :, 0].view(torch.uint8).cpu().numpy(), g["d"])
+    np.testing.assert_array_equal(flat(out["sfd_row_tensor"]), g["sfd_row"])
+    np.testing.assert_array_equal(out["d_col_tensor"][:, :, 0].view(torch.uint8).cpu().numpy(), g["d_col"])
+    np.testing.assert_array_equal(flat(out["sfd_col_tensor"]), g["sfd_col"])
