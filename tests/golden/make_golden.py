@@ -17,7 +17,9 @@ inputs, and stores inputs + outputs as small .npz files:
                        (test/python/fe_api/test_grouped_gemm_quant_utils.py:270-345)
 
 The re-quantisation branch of those functions (generate_sfd=True) needs a GPU and the CuTe
-DSL, so it is not part of these fixtures.
+DSL, so it is not part of these fixtures.  reference_kernel_fc1.npz is different: it holds inputs
+and outputs of the reference's own CuTe-DSL FC1 kernel recorded on a B200 by
+baseline/run_reference_kernels.py --cases tiny (after baseline/make_ref_overlay.py).
 """
 
 import os

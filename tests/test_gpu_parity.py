@@ -439,6 +439,9 @@ def test_fc1_is_bit_identical_to_the_reference_kernel_fixture(golden_dir, tile_m
 
     np.testing.assert_array_equal(out["c_tensor"][:, :, 0].view(torch.int16).cpu().numpy(), g["c"])
     np.testing.assert_array_equal(out["d_tensor"][:, :, 0].view(torch.uint8).cpu().numpy(), g["d"])
-    np.testing.assert_array_equal(flat(out["sfd_row_tensor"]), g["sfd_row"])
+    # scale buffers hold unwritten padding bytes (n_out = 64 fills 2 of the 4 slots of a K group):
+    # compare the addressed scales only
+    n_out = n // 2
+    np.testing.assert_array_equal(orc.sf_unpack(flat(out["sfd_row_tensor"]), m, n_out // 32), orc.sf_unpack(g["sfd_row"], m, n_out // 32))
     np.testing.assert_array_equal(out["d_col_tensor"][:, :, 0].view(torch.uint8).cpu().numpy(), g["d_col"])
-    np.testing.assert_array_equal(flat(out["sfd_col_tensor"]), g["sfd_col"])
+    np.testing.assert_array_equal(orc.sf_unpack(flat(out["sfd_col_tensor"]), n_out, m // 32), orc.sf_unpack(g["sfd_col"], n_out, m // 32))
