@@ -43,6 +43,21 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 
 __device__ __forceinline__ uint32_t lane_id() { return threadIdx.x & 31; }
 
+// True in exactly one lane of a converged warp.  Unlike a `lane == 0` test, the compiler knows
+// the warp stays convergent around the elected region, so descriptors and addresses of TMA and
+// tcgen05 instructions can live in uniform registers.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred P;\n\t"
+      "elect.sync _|P, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t"
+      "}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
 // ---------------------------------------------------------------------------------------
 // mbarrier
 // ---------------------------------------------------------------------------------------

@@ -6,8 +6,8 @@
 //
 // Persistent kernel, one CTA per SM, walking a static tile schedule derived on the device from
 // the per-expert END offsets.  Warp roles:
-//   warp 0      producer: TMA loads of the A / B tiles (128-byte swizzle) and of the 512-byte
-//               scale-factor chunks into a shared-memory ring
+//   warp 0, 10  producers: TMA loads of the A tile (warp 0) and the B tile (warp 10), 128-byte
+//               swizzled, plus their 512-byte scale-factor chunks, into a shared-memory ring
 //   warp 1      TMEM owner and MMA issuer: tcgen05.cp moves the scale factors to TMEM, then
 //               tcgen05.mma.kind::mxf8f6f4.block_scale accumulates into TMEM
 //   warps 2..9  epilogue: tcgen05.ld, alpha / SwiGLU / prob / amax / re-quantisation, stores
@@ -48,7 +48,8 @@ constexpr int A_STAGE_BYTES = BM * BK;  // 16 KiB
 constexpr int SFA_STAGE_BYTES = 512;
 constexpr int SFB_STAGE_BYTES = 1024;
 constexpr int NUM_EPI_WARPS = 8;
-constexpr int NUM_THREADS = (2 + NUM_EPI_WARPS) * 32;
+constexpr int PRODUCER_B_WARP = 2 + NUM_EPI_WARPS;  // the last warp
+constexpr int NUM_THREADS = (3 + NUM_EPI_WARPS) * 32;
 constexpr int MAX_EXPERTS = 1024;
 constexpr int RASTER_GROUP_M = 8;  // row tiles of one expert that share a B tile back to back
 
@@ -316,9 +317,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
   const uint32_t tmem_base = *tmem_ptr_smem;
   const int total_tiles = *total_tiles_smem;
 
-  if (warp == 0) {
-    // ================= producer =======================================================
-    if (lane == 0) {
+  if (warp == 0 || warp == PRODUCER_B_WARP) {
+    // ================= producers ======================================================
+    // Two single-thread producers share the ring: warp 0 loads the A tile and its scale chunk
+    // (and announces the stage's byte count), the last warp loads the B tile and its scale
+    // chunks.  One thread issuing every copy of a k-tile was the slowest stream of the kernel.
+    const bool side_b = warp != 0;
+    {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -332,7 +337,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         const int nblk0 = n0 / 128;
         const CUtensorMap* bmap = &tmap_b;
         const CUtensorMap* sfbmap = &tmap_sfb;
-        if (kDiscrete) {
+        if (kDiscrete && side_b) {
           bmap = p.b_maps + tile.expert;
           tensormap_fence_acquire(bmap);
           if (kPair) {
@@ -341,50 +346,66 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           }
         }
         // Everything that changes per k-tile is a running value: the K coordinate, the scale-chunk
-        // pointers and the stage's shared-memory / barrier addresses.  The issuing thread's
-        // instruction count per k-tile bounds how fast stages can be refilled.
+        // pointers and the stage's shared-memory / barrier addresses.
         int kc = 0;
         if constexpr (kPair) {
           // every load of either CTA credits the leader's barrier of this stage
           const int b_row = n0 + (int)cta_rank * 128;
           const int m_blk = my_row0 / BM;
           for (int kt = 0; kt < p.k_tiles; ++kt, kc += BK) {
-            if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, ST_PRODUCER_EMPTY)) { ok = false; break; }
-            if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(stage), C::TX_BYTES);
+            if (!__all_sync(0xffffffffu, mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, ST_PRODUCER_EMPTY))) { ok = false; break; }
             const uint32_t fb = leader_full0 + 8u * stage;
-            tma_load_2d_pair(a_dst0 + stage * A_STAGE_BYTES, &tmap_a, fb, kc, my_row0);
-            if (kDiscrete)
-              tma_load_2d_pair(b_dst0 + stage * C::B_STAGE_BYTES, bmap, fb, kc, b_row);
-            else
-              tma_load_3d_pair(b_dst0 + stage * C::B_STAGE_BYTES, bmap, fb, kc, b_row, tile.expert);
-            tma_load_3d_pair(sfa_dst0 + stage * SFA_STAGE_BYTES, &tmap_sfa, fb, 0, kt, m_blk);
-            if (kDiscrete)
-              tma_load_3d_pair(sfb_dst0 + stage * SFB_STAGE_BYTES, sfbmap, fb, 0, kt, nblk0);
-            else
-              tma_load_4d_pair(sfb_dst0 + stage * SFB_STAGE_BYTES, sfbmap, fb, 0, kt, nblk0, tile.expert);
+            if (elect_one()) {
+              if (!side_b) {
+                if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(stage), C::TX_BYTES);
+                tma_load_2d_pair(a_dst0 + stage * A_STAGE_BYTES, &tmap_a, fb, kc, my_row0);
+                tma_load_3d_pair(sfa_dst0 + stage * SFA_STAGE_BYTES, &tmap_sfa, fb, 0, kt, m_blk);
+              } else if (kDiscrete) {
+                tma_load_2d_pair(b_dst0 + stage * C::B_STAGE_BYTES, bmap, fb, kc, b_row);
+                tma_load_3d_pair(sfb_dst0 + stage * SFB_STAGE_BYTES, sfbmap, fb, 0, kt, nblk0);
+              } else {
+                tma_load_3d_pair(b_dst0 + stage * C::B_STAGE_BYTES, bmap, fb, kc, b_row, tile.expert);
+                tma_load_4d_pair(sfb_dst0 + stage * SFB_STAGE_BYTES, sfbmap, fb, 0, kt, nblk0, tile.expert);
+              }
+            }
+            __syncwarp();
             if (++stage == STAGES) { stage = 0; phase ^= 1; }
           }
         } else {
-          const uint8_t* sfa_src = p.sfa + (int64_t)(tile.row0 / BM) * p.rest_k * 512;
-          const uint8_t* sfb_e = kDiscrete ? reinterpret_cast<const uint8_t*>(p.sfb_ptrs[tile.expert])
-                                           : p.sfb + (int64_t)tile.expert * p.sfb_expert_bytes;
-          const uint8_t* sfb_src0 = sfb_e + (int64_t)nblk0 * p.rest_k * 512;
-          const uint8_t* sfb_src1 = sfb_src0 + (int64_t)p.rest_k * 512;
           const bool two_chunks = p.n_blocks - nblk0 >= 2;
-          const uint32_t tx = A_STAGE_BYTES + C::B_STAGE_BYTES + SFA_STAGE_BYTES + (two_chunks ? 1024u : 512u);
-          for (int kt = 0; kt < p.k_tiles; ++kt, kc += BK, sfa_src += 512, sfb_src0 += 512, sfb_src1 += 512) {
-            if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, ST_PRODUCER_EMPTY)) { ok = false; break; }
-            const uint32_t fb = full_bar(stage);
-            mbar_arrive_expect_tx(fb, tx);
-            tma_load_2d(a_dst0 + stage * A_STAGE_BYTES, &tmap_a, fb, kc, tile.row0);
-            if (kDiscrete)
-              tma_load_2d(b_dst0 + stage * C::B_STAGE_BYTES, bmap, fb, kc, n0);
-            else
-              tma_load_3d(b_dst0 + stage * C::B_STAGE_BYTES, bmap, fb, kc, n0, tile.expert);
-            bulk_load(sfa_dst0 + stage * SFA_STAGE_BYTES, sfa_src, 512, fb);
-            bulk_load(sfb_dst0 + stage * SFB_STAGE_BYTES, sfb_src0, 512, fb);
-            if (two_chunks) bulk_load(sfb_dst0 + stage * SFB_STAGE_BYTES + 512, sfb_src1, 512, fb);
-            if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          if (!side_b) {
+            const uint8_t* sfa_src = p.sfa + (int64_t)(tile.row0 / BM) * p.rest_k * 512;
+            const uint32_t tx = A_STAGE_BYTES + C::B_STAGE_BYTES + SFA_STAGE_BYTES + (two_chunks ? 1024u : 512u);
+            for (int kt = 0; kt < p.k_tiles; ++kt, kc += BK, sfa_src += 512) {
+              if (!__all_sync(0xffffffffu, mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, ST_PRODUCER_EMPTY))) { ok = false; break; }
+              const uint32_t fb = full_bar(stage);
+              if (elect_one()) {
+                mbar_arrive_expect_tx(fb, tx);
+                tma_load_2d(a_dst0 + stage * A_STAGE_BYTES, &tmap_a, fb, kc, tile.row0);
+                bulk_load(sfa_dst0 + stage * SFA_STAGE_BYTES, sfa_src, 512, fb);
+              }
+              __syncwarp();
+              if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            }
+          } else {
+            const uint8_t* sfb_e = kDiscrete ? reinterpret_cast<const uint8_t*>(p.sfb_ptrs[tile.expert])
+                                             : p.sfb + (int64_t)tile.expert * p.sfb_expert_bytes;
+            const uint8_t* sfb_src0 = sfb_e + (int64_t)nblk0 * p.rest_k * 512;
+            const uint8_t* sfb_src1 = sfb_src0 + (int64_t)p.rest_k * 512;
+            for (int kt = 0; kt < p.k_tiles; ++kt, kc += BK, sfb_src0 += 512, sfb_src1 += 512) {
+              if (!__all_sync(0xffffffffu, mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, ST_PRODUCER_EMPTY))) { ok = false; break; }
+              const uint32_t fb = full_bar(stage);
+              if (elect_one()) {
+                if (kDiscrete)
+                  tma_load_2d(b_dst0 + stage * C::B_STAGE_BYTES, bmap, fb, kc, n0);
+                else
+                  tma_load_3d(b_dst0 + stage * C::B_STAGE_BYTES, bmap, fb, kc, n0, tile.expert);
+                bulk_load(sfb_dst0 + stage * SFB_STAGE_BYTES, sfb_src0, 512, fb);
+                if (two_chunks) bulk_load(sfb_dst0 + stage * SFB_STAGE_BYTES + 512, sfb_src1, 512, fb);
+              }
+              __syncwarp();
+              if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            }
           }
         }
       }
@@ -392,7 +413,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     __syncwarp();
   } else if (warp == 1) {
     // ================= MMA issuer (the leader CTA only, in pair mode) =====================
-    if (lane == 0 && cta_rank == 0) {
+    if (cta_rank == 0) {
+      // The whole warp walks the loop (so it stays convergent); one elected lane issues.
       // The issuing thread is a serial instruction stream: four MMAs, three scale copies and a
       // commit per k-tile must cost as few instructions as possible, so every descriptor is
       // (constant high word, running low word) and the instruction descriptors are immediates.
@@ -414,14 +436,16 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         const uint32_t acc = tmem_base + ((it & 1) ? TMEM_ACC1_COL : 0);
         if (it > 0) {
           // previous tile's epilogue has drained the 32 columns both accumulators share
-          if (!mbar_wait(overlap_bar, (it - 1) & 1, abort_flag, ST_MMA_OVERLAP)) { ok = false; break; }
+          if (!__all_sync(0xffffffffu, mbar_wait(overlap_bar, (it - 1) & 1, abort_flag, ST_MMA_OVERLAP))) { ok = false; break; }
           tc_fence_after();
         }
         for (int kt = 0; kt < p.k_tiles; ++kt) {
-          if (!mbar_try_wait(full_bar(stage), phase)) {
-            if (!mbar_wait(full_bar(stage), phase, abort_flag, ST_MMA_FULL)) { ok = false; break; }
-          }
-          tc_fence_after();
+          // the stage's bytes were written by TMA (async proxy) and are made visible by the barrier's
+          // transaction count; no tcgen05 fence is needed between this wait and the MMAs
+          // (the verdict is voted so that a wait that gives up takes the whole warp out of the loop)
+          bool landed = mbar_try_wait(full_bar(stage), phase);
+          if (!landed) landed = mbar_wait(full_bar(stage), phase, abort_flag, ST_MMA_FULL);
+          if (!__all_sync(0xffffffffu, landed)) { ok = false; break; }
           const uint32_t sfa_t = tmem_base + TMEM_SF_COL + 16 * sf_buf;
           const uint32_t sfb_t = sfa_t + 4;
           const uint32_t a_lo = a_lo0 + stage * (A_STAGE_BYTES >> 4);
@@ -430,6 +454,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           const uint32_t sfb_lo = sfb_lo0 + stage * (SFB_STAGE_BYTES >> 4);
           const uint32_t not_first = kt != 0;
           const bool full_k = p.k - kt * BK >= BK;
+          if (elect_one()) {
           if constexpr (kPair) {
             // one instruction acts on both CTAs: each copies from its own smem to its own TMEM
             tmem_cp_sf_pair(sfa_t, desc(sfa_lo, SF_HI));
@@ -465,13 +490,18 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             }
             tc_commit(empty_bar(stage));  // frees the smem stage once these MMAs have read it
           }
+          }
+          __syncwarp();
           sf_buf ^= 1;
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
-        if (ok) {
+        // the commit must come from the lane that issued the MMAs: elect.sync picks the same lane of
+        // an unchanged, fully active warp every time
+        if (ok && elect_one()) {
           if constexpr (kPair) tc_commit_pair(acc_full_bar(it & 1), 3);
           else tc_commit(acc_full_bar(it & 1));
         }
+        __syncwarp();
       }
     }
     __syncwarp();
