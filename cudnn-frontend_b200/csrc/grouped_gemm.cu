@@ -114,6 +114,7 @@ struct GemmParams {
   int sfd_col_rest_k;  // ceil(ceil(m_rows / 32) / 4)
   int d_is_fp8;
   int discrete_col_sfd;
+  int wide_stores;     // every output row segment of 32 bytes is 32-byte aligned
 };
 
 // ---------------------------------------------------------------------------------------
@@ -154,69 +155,124 @@ __device__ __forceinline__ Tile decode_tile(const int* prefix, const int32_t* of
 // Epilogue helpers.  A thread owns one row of the tile; `v` holds 32 consecutive output
 // columns of that row in float32.
 // ---------------------------------------------------------------------------------------
-__device__ __forceinline__ void store_bf16x32(__nv_bfloat16* dst, const float* v) {
-  uint4* p = reinterpret_cast<uint4*>(dst);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    uint4 o;
-    o.x = bf16x2_from_float(v[8 * i + 0], v[8 * i + 1]);
-    o.y = bf16x2_from_float(v[8 * i + 2], v[8 * i + 3]);
-    o.z = bf16x2_from_float(v[8 * i + 4], v[8 * i + 5]);
-    o.w = bf16x2_from_float(v[8 * i + 6], v[8 * i + 7]);
-    p[i] = o;
+// 32 bytes to one row: a single 256-bit store when the caller's buffers allow it (`wide`), else two
+// 128-bit stores.  A 128-bit store per lane fills only half of a 32-byte sector of the row it
+// touches; the 256-bit form halves the store instructions and writes whole sectors.
+__device__ __forceinline__ void store_32B(void* dst, uint4 lo, uint4 hi, bool wide) {
+  if (wide) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst), "r"(lo.x), "r"(lo.y), "r"(lo.z),
+                 "r"(lo.w), "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w)
+                 : "memory");
+  } else {
+    reinterpret_cast<uint4*>(dst)[0] = lo;
+    reinterpret_cast<uint4*>(dst)[1] = hi;
   }
 }
 
-__device__ __forceinline__ void store_e4m3x32(uint8_t* dst, const float* v, float scale) {
-  uint4* p = reinterpret_cast<uint4*>(dst);
+__device__ __forceinline__ void store_bf16x32(__nv_bfloat16* dst, const float* v, bool wide) {
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
-    uint4 o;
-    o.x = e4m3x4_from_float(v[16 * i + 0] * scale, v[16 * i + 1] * scale, v[16 * i + 2] * scale, v[16 * i + 3] * scale);
-    o.y = e4m3x4_from_float(v[16 * i + 4] * scale, v[16 * i + 5] * scale, v[16 * i + 6] * scale, v[16 * i + 7] * scale);
-    o.z = e4m3x4_from_float(v[16 * i + 8] * scale, v[16 * i + 9] * scale, v[16 * i + 10] * scale, v[16 * i + 11] * scale);
-    o.w = e4m3x4_from_float(v[16 * i + 12] * scale, v[16 * i + 13] * scale, v[16 * i + 14] * scale, v[16 * i + 15] * scale);
-    p[i] = o;
+    uint4 lo, hi;
+    lo.x = bf16x2_from_float(v[16 * i + 0], v[16 * i + 1]);
+    lo.y = bf16x2_from_float(v[16 * i + 2], v[16 * i + 3]);
+    lo.z = bf16x2_from_float(v[16 * i + 4], v[16 * i + 5]);
+    lo.w = bf16x2_from_float(v[16 * i + 6], v[16 * i + 7]);
+    hi.x = bf16x2_from_float(v[16 * i + 8], v[16 * i + 9]);
+    hi.y = bf16x2_from_float(v[16 * i + 10], v[16 * i + 11]);
+    hi.z = bf16x2_from_float(v[16 * i + 12], v[16 * i + 13]);
+    hi.w = bf16x2_from_float(v[16 * i + 14], v[16 * i + 15]);
+    store_32B(dst + 16 * i, lo, hi, wide);
   }
+}
+
+__device__ __forceinline__ void store_e4m3x32(uint8_t* dst, const float* v, float scale, bool wide) {
+  uint4 o[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    o[i].x = e4m3x4_from_float(v[16 * i + 0] * scale, v[16 * i + 1] * scale, v[16 * i + 2] * scale, v[16 * i + 3] * scale);
+    o[i].y = e4m3x4_from_float(v[16 * i + 4] * scale, v[16 * i + 5] * scale, v[16 * i + 6] * scale, v[16 * i + 7] * scale);
+    o[i].z = e4m3x4_from_float(v[16 * i + 8] * scale, v[16 * i + 9] * scale, v[16 * i + 10] * scale, v[16 * i + 11] * scale);
+    o[i].w = e4m3x4_from_float(v[16 * i + 12] * scale, v[16 * i + 13] * scale, v[16 * i + 14] * scale, v[16 * i + 15] * scale);
+  }
+  store_32B(dst, o[0], o[1], wide);
 }
 
 // Row-wise MXFP8 of one 32-element block: returns the E8M0 byte, stores 32 E4M3 bytes.
-__device__ __forceinline__ uint32_t quant_row_block(uint8_t* dst, const float* v, float norm_const) {
+__device__ __forceinline__ uint32_t quant_row_block(uint8_t* dst, const float* v, float norm_const, bool wide) {
   float amax = 0.f;
 #pragma unroll
   for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(v[i]));
   const float pv = amax * (1.0f / 448.0f) * norm_const;
   const uint32_t sf = e8m0_from_float(pv);
-  store_e4m3x32(dst, v, quant_scale(norm_const, e8m0_to_float(sf)));
+  store_e4m3x32(dst, v, quant_scale(norm_const, e8m0_to_float(sf)), wide);
   return sf;
 }
 
 // Column-wise MXFP8: the 32 rows of a scale block are the 32 lanes of the warp.  Lane i
 // returns the E8M0 byte of column i; every lane stores its row's 32 E4M3 bytes.
-__device__ __forceinline__ uint32_t quant_col_block(uint8_t* dst, bool do_store, const float* v, float norm_const) {
-  uint32_t my_sf = 0;
+//
+// The 32 column maxima come from a halving exchange: in the step of distance d a lane keeps the
+// half of its columns whose bit d matches its own lane bit and trades the other half with lane
+// (lane ^ d), so 16 + 8 + 4 + 2 + 1 shuffles leave lane i with the maximum of column i (a
+// butterfly per column would take 160).  Each lane then derives the scale of its own column
+// once, and 32 broadcasts hand the scales round.
+__device__ __forceinline__ uint32_t quant_col_block(uint8_t* dst, bool do_store, const float* v, float norm_const, bool wide) {
+  const uint32_t lane = lane_id();
+  float m16[16], m8[8], m4[4], m2[2];
+  {
+    const bool up = lane & 16;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const float keep = up ? v[j + 16] : v[j];
+      const float send = up ? v[j] : v[j + 16];
+      m16[j] = fmaxf(fabsf(keep), fabsf(__shfl_xor_sync(0xffffffffu, send, 16)));
+    }
+  }
+  {
+    const bool up = lane & 8;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float keep = up ? m16[j + 8] : m16[j];
+      const float send = up ? m16[j] : m16[j + 8];
+      m8[j] = fmaxf(keep, __shfl_xor_sync(0xffffffffu, send, 8));
+    }
+  }
+  {
+    const bool up = lane & 4;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float keep = up ? m8[j + 4] : m8[j];
+      const float send = up ? m8[j] : m8[j + 4];
+      m4[j] = fmaxf(keep, __shfl_xor_sync(0xffffffffu, send, 4));
+    }
+  }
+  {
+    const bool up = lane & 2;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const float keep = up ? m4[j + 2] : m4[j];
+      const float send = up ? m4[j] : m4[j + 2];
+      m2[j] = fmaxf(keep, __shfl_xor_sync(0xffffffffu, send, 2));
+    }
+  }
+  const bool up1 = lane & 1;
+  const float cmax = fmaxf(up1 ? m2[1] : m2[0], __shfl_xor_sync(0xffffffffu, up1 ? m2[0] : m2[1], 1));
+  // scale of column `lane`
+  const float pv = cmax * (1.0f / 448.0f) * norm_const;
+  const uint32_t my_sf = e8m0_from_float(pv);
+  const float sfv = e8m0_to_float(my_sf);
+  float my_sc = sfv == 0.0f ? 0.0f : norm_const * rcp_approx(sfv);
+  my_sc = fminf(my_sc, 3.40282346638528859812e38f);
   uint32_t packed[8];
 #pragma unroll
   for (int i = 0; i < 32; i += 4) {
     float s[4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float cmax = warp_absmax(v[i + j]);
-      const float pv = cmax * (1.0f / 448.0f) * norm_const;
-      const uint32_t sf = e8m0_from_float(pv);
-      const float sfv = e8m0_to_float(sf);
-      float sc = sfv == 0.0f ? 0.0f : norm_const * rcp_approx(sfv);
-      sc = fminf(sc, 3.40282346638528859812e38f);
-      s[j] = v[i + j] * sc;
-      if ((int)lane_id() == i + j) my_sf = sf;
-    }
+    for (int j = 0; j < 4; ++j) s[j] = v[i + j] * __shfl_sync(0xffffffffu, my_sc, i + j);
     packed[i >> 2] = e4m3x4_from_float(s[0], s[1], s[2], s[3]);
   }
-  if (do_store) {
-    uint4* p = reinterpret_cast<uint4*>(dst);
-    p[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-    p[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-  }
+  if (do_store)
+    store_32B(dst, make_uint4(packed[0], packed[1], packed[2], packed[3]), make_uint4(packed[4], packed[5], packed[6], packed[7]), wide);
   return my_sf;
 }
 
@@ -512,6 +568,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     const int half = ew >> 2;           // column half of the tile: [128 half, 128 half + 128)
     const int r_in_tile = quarter * 32 + lane;
     const float norm_const = p.norm_const ? *p.norm_const : 1.0f;
+    const bool wide = p.wide_stores != 0;
     const uint32_t overlap_target = kPair ? map_to_cta(overlap_bar, 0) : overlap_bar;
     auto arrive_overlap = [&]() {
       if (kPair) mbar_arrive_cluster(overlap_target); else mbar_arrive(overlap_bar);
@@ -559,8 +616,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 #pragma unroll
           for (int j = 0; j < 32; ++j) { g[j] *= alpha; u[j] *= alpha; }
           if (p.c && row_ok) {
-            store_bf16x32(p.c + (int64_t)row * p.n + cn, g);
-            store_bf16x32(p.c + (int64_t)row * p.n + cn + 32, u);
+            store_bf16x32(p.c + (int64_t)row * p.n + cn, g, wide);
+            store_bf16x32(p.c + (int64_t)row * p.n + cn + 32, u, wide);
           }
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
@@ -573,10 +630,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 #pragma unroll
               for (int j = 0; j < 32; ++j) thread_amax = fmaxf(thread_amax, fabsf(g[j]));
             }
-            if (row_ok && out_row >= 0) store_bf16x32(reinterpret_cast<__nv_bfloat16*>(p.d) + (int64_t)out_row * p.n_out + dn, g);
+            if (row_ok && out_row >= 0) store_bf16x32(reinterpret_cast<__nv_bfloat16*>(p.d) + (int64_t)out_row * p.n_out + dn, g, wide);
           } else {
             if (row_ok) {
-              const uint32_t sf = quant_row_block(reinterpret_cast<uint8_t*>(p.d) + (int64_t)row * p.n_out + dn, g, norm_const);
+              const uint32_t sf = quant_row_block(reinterpret_cast<uint8_t*>(p.d) + (int64_t)row * p.n_out + dn, g, norm_const, wide);
               sf_row_word |= sf << (8 * (half * 2 + pp));
             }
             if (p.d_col) {
@@ -585,7 +642,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 #pragma unroll
                 for (int j = 0; j < 32; ++j) g[j] = 0.f;
               }
-              const uint32_t sfc = quant_col_block(p.d_col + (int64_t)row * p.n_out + dn, row_ok, g, norm_const);
+              const uint32_t sfc = quant_col_block(p.d_col + (int64_t)row * p.n_out + dn, row_ok, g, norm_const, wide);
               int64_t blk_base = 0;
               int rb = (tile.row0 >> 5) + quarter;
               int rest = p.sfd_col_rest_k;
@@ -633,10 +690,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 #pragma unroll
               for (int j = 0; j < 32; ++j) thread_amax = fmaxf(thread_amax, fabsf(v[j]));
             }
-            if (row_ok && out_row >= 0) store_bf16x32(reinterpret_cast<__nv_bfloat16*>(p.d) + (int64_t)out_row * p.n_out + dn, v);
+            if (row_ok && out_row >= 0) store_bf16x32(reinterpret_cast<__nv_bfloat16*>(p.d) + (int64_t)out_row * p.n_out + dn, v, wide);
           } else {
             if (row_ok) {
-              const uint32_t sf = quant_row_block(reinterpret_cast<uint8_t*>(p.d) + (int64_t)row * p.n_out + dn, v, norm_const);
+              const uint32_t sf = quant_row_block(reinterpret_cast<uint8_t*>(p.d) + (int64_t)row * p.n_out + dn, v, norm_const, wide);
               sf_row_word |= sf << (8 * bb);
             }
             if (p.d_col) {
@@ -644,7 +701,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 #pragma unroll
                 for (int j = 0; j < 32; ++j) v[j] = 0.f;
               }
-              const uint32_t sfc = quant_col_block(p.d_col + (int64_t)row * p.n_out + dn, row_ok, v, norm_const);
+              const uint32_t sfc = quant_col_block(p.d_col + (int64_t)row * p.n_out + dn, row_ok, v, norm_const, wide);
               int64_t blk_base = 0;
               int rb = (tile.row0 >> 5) + quarter;
               int rest = p.sfd_col_rest_k;
@@ -928,6 +985,12 @@ static int run_gemm(int epi, const b200moe_gemm_args* a, void* stream_v) {
   p.sfd_col_rest_k = ((p.m_rows + 31) / 32 + 3) / 4;
   p.d_is_fp8 = d_fp8;
   p.discrete_col_sfd = (a->flags & B200MOE_FLAG_DISCRETE_COL_SFD) ? 1 : 0;
+  {
+    // 256-bit stores need 32-byte aligned bases and row pitches that keep a 32-column block aligned
+    const int64_t d_pitch = (int64_t)p.n_out * (d_fp8 ? 1 : 2);
+    const uintptr_t bases = (uintptr_t)a->c | (uintptr_t)a->d | (uintptr_t)a->d_col;
+    p.wide_stores = (bases % 32 == 0) && (d_pitch % 32 == 0) && (((int64_t)p.n * 2) % 32 == 0);
+  }
 
   // Tile mode.  A pair (two CTAs, 256 x 256) moves half the weight bytes per SM but rounds every
   // expert group up to 256 rows; the host sees only the average group size, so pairs are used when
