@@ -8,7 +8,8 @@ Needs the overlay made by baseline/make_ref_overlay.py (baseline/_ref/cudnn) and
 
 with the reference's constraints (groups padded to 256, mma_tiler (256, 256)), then outputs are
 compared (C bf16, E8M0 scale bytes, E4M3 ULP distance) and both are timed with CUDA events
-(3 warm-ups, 10 trials, 256 MiB L2 flush between trials, median and best).  Results go to
+(3 warm-ups, 10 trials, 256 MiB L2 flush between trials, median and best; back to back; and
+interleaved A B A B in one queue, which is the comparison that is independent of the GPU's power state).  Results go to
 gpurun_out/reference_kernels_<cases>.json; the tiny case's inputs and reference-kernel outputs are saved
 to gpurun_out/reference_kernel_golden.npz so they can be committed as golden vectors.
 
@@ -60,6 +61,26 @@ def timed_back_to_back(fn, steps=20, warmup=3):
     e.record()
     torch.cuda.synchronize()
     return s.elapsed_time(e) / steps
+
+
+def timed_interleaved(fn_a, fn_b, rounds=30, warmup=3):
+    """A B A B ... in one queue, every call bracketed by events: both kernels see the same clocks,
+    temperature and power state.  Returns the median ms of each."""
+    for _ in range(warmup):
+        fn_a()
+        fn_b()
+    torch.cuda.synchronize()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2 * rounds + 1)]
+    ev[0].record()
+    for i in range(rounds):
+        fn_a()
+        ev[2 * i + 1].record()
+        fn_b()
+        ev[2 * i + 2].record()
+    torch.cuda.synchronize()
+    ta = sorted(ev[2 * i].elapsed_time(ev[2 * i + 1]) for i in range(rounds))
+    tb = sorted(ev[2 * i + 1].elapsed_time(ev[2 * i + 2]) for i in range(rounds))
+    return ta[rounds // 2], tb[rounds // 2]
 
 
 def ulp(a, b):
@@ -135,6 +156,9 @@ def run_case(name, cfg, out):
         for name_, fn in order:
             b2b[name_].append(timed_back_to_back(fn))
     ms_ref, ms_own = iso["ref"], iso["own"]
+    il_ref, il_own = timed_interleaved(run_ref, run_own)
+    res["ref_ms_interleaved"], res["own_ms_interleaved"] = il_ref, il_own
+    res["own_over_ref_interleaved"] = il_ref / il_own
     res["order"] = [n for n, _ in order]
     res["ref_ms_median_best"] = ms_ref[:2]
     res["own_ms_median_best"] = ms_own[:2]

@@ -177,3 +177,14 @@ def check_tile_and_cluster(op: OperatorBase, mma_tiler_mn, cluster_shape_mn, m_a
     cluster_tiler_m = (cm // (2 if use_2cta else 1)) * mma_tiler_mn[0]
     op._value_error_if(cluster_tiler_m not in (128, 256), f"Invalid cluster tiler shape: expected cluster_tiler_m in {{128, 256}}, got {cluster_tiler_m}")
     op._value_error_if(m_aligned <= 0 or m_aligned % 128 != 0, f"m_aligned must be a positive multiple of 128, got {m_aligned}")
+
+
+def pick_tile_mode(mma_tiler_mn, m_aligned: int):
+    """Tile mode of the launch from the caller's tiler and group alignment: a 128-row tiler maps to
+    single-CTA tiles; groups padded to a multiple of 256 rows waste nothing in 256-row CTA-pair
+    tiles, whatever their size; otherwise the library decides from the average group size."""
+    if mma_tiler_mn[0] <= 128:
+        return "single"
+    if m_aligned % 256 == 0:
+        return "pair"
+    return None

@@ -22,7 +22,7 @@ from typing import Optional, Tuple
 import torch
 
 from . import ops
-from .api_base import OperatorBase, TensorSpec, TupleDict, ceil_div, check_tile_and_cluster
+from .api_base import OperatorBase, TensorSpec, TupleDict, ceil_div, check_tile_and_cluster, pick_tile_mode
 from .grouped_gemm_swiglu import _SF_STRIDE_MSG, _alloc_sfd
 
 _logger = logging.getLogger(__name__)
@@ -280,7 +280,7 @@ class GroupedGemmQuantSm100(OperatorBase):
             n=self._n,
             discrete_col_sfd=self.discrete_col_sfd,
             sm_margin=self.num_cluster_overlap_margin,
-            tile_mode="single" if self.mma_tiler_mn[0] <= 128 else None,
+            tile_mode=pick_tile_mode(self.mma_tiler_mn, self.m_aligned),
             d_row_map=d_row_map,
             stream=current_stream,
         )

@@ -25,7 +25,7 @@ from typing import Optional, Tuple
 import torch
 
 from . import ops
-from .api_base import OperatorBase, TensorSpec, TupleDict, ceil_div, check_tile_and_cluster
+from .api_base import OperatorBase, TensorSpec, TupleDict, ceil_div, check_tile_and_cluster, pick_tile_mode
 
 _logger = logging.getLogger(__name__)
 
@@ -226,7 +226,7 @@ class GroupedGemmSwigluSm100(OperatorBase):
             n=n,
             discrete_col_sfd=self.discrete_col_sfd,
             sm_margin=self.num_cluster_overlap_margin,
-            tile_mode="single" if self.mma_tiler_mn[0] <= 128 else None,
+            tile_mode=pick_tile_mode(self.mma_tiler_mn, self.m_aligned),
             stream=current_stream,
         )
 
