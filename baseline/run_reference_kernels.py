@@ -15,6 +15,7 @@ to gpurun_out/reference_kernel_golden.npz so they can be committed as golden vec
 
     python baseline/run_reference_kernels.py --cases tiny      # one case per process: the reference's
     python baseline/run_reference_kernels.py --cases c2        # wrapper cache does not key on the expert count
+    python baseline/run_reference_kernels.py --cases c4        # FC2 (grouped_gemm_quant): fc2_tiny, fc2_mixtral, c4
 """
 
 import argparse
@@ -192,6 +193,82 @@ def run_case(name, cfg, out):
         )
 
 
+def run_case_fc2(name, cfg, out):
+    """FC2: grouped GEMM + gating + MXFP8 re-quantisation (grouped_gemm_quant), full output set."""
+    import cuda.bindings.driver as cuda
+    from cudnn.grouped_gemm.grouped_gemm_quant.api import grouped_gemm_quant_wrapper_sm100 as ref_quant  # the overlay
+
+    import cudnn_frontend_b200 as ours
+    from cudnn_frontend_b200 import synthetic
+
+    p = synthetic.make_problem(cfg, "cuda", seed=5, m_aligned=256)
+    norm = torch.tensor([1.0], dtype=torch.float32, device="cuda")
+    stream = cuda.CUstream(torch.cuda.current_stream().cuda_stream)
+    kw = dict(b_tensor=p["b"], sfb_tensor=p["sfb"], norm_const_tensor=norm, prob_tensor=p["prob"], d_dtype=torch.float8_e4m3fn,
+              sf_vec_size=32, m_aligned=256)  # fmt: skip
+    res = {"case": name, "op": "fc2", "cfg": cfg, "m_rows": p["m_rows"], "flops": p["flops"]}
+
+    def run_ref():
+        return ref_quant(p["a"], p["sfa"], p["padded_offsets"], p["alpha"], mma_tiler_mn=(256, 256), current_stream=stream, **kw)
+
+    def run_own():
+        return ours.grouped_gemm_quant_wrapper_sm100(p["a"], p["sfa"], p["padded_offsets"], p["alpha"], **kw)
+
+    t0 = time.time()
+    r_ref = run_ref()
+    torch.cuda.synchronize()
+    res["ref_first_call_s"] = time.time() - t0
+    r_own = run_own()
+    torch.cuda.synchronize()
+    if PROFILE_ONLY:
+        run_ref()
+        run_own()
+        torch.cuda.synchronize()
+        return
+    m = p["m_rows"]
+
+    def flat(t):
+        t = t.view(torch.uint8)
+        return torch.as_strided(t, (t.numel(),), (1,))
+
+    u = ulp(r_ref["d_tensor"][:m].view(torch.uint8), r_own["d_tensor"][:m].view(torch.uint8))
+    res["d_e4m3_equal_frac"] = float((u == 0).float().mean())
+    res["d_e4m3_within_1ulp_frac"] = float((u <= 1).float().mean())
+    uc = ulp(r_ref["d_col_tensor"][:m].view(torch.uint8), r_own["d_col_tensor"][:m].view(torch.uint8))
+    res["d_col_equal_frac"] = float((uc == 0).float().mean())
+    res["sfd_row_bytes_equal_frac"] = float((flat(r_ref["sfd_row_tensor"]) == flat(r_own["sfd_row_tensor"])).float().mean())
+    res["sfd_col_bytes_equal_frac"] = float((flat(r_ref["sfd_col_tensor"]) == flat(r_own["sfd_col_tensor"])).float().mean())
+
+    iso_ref, iso_own = timed(run_ref), timed(run_own)
+    res["ref_ms_median_best"], res["own_ms_median_best"] = iso_ref[:2], iso_own[:2]
+    res["ref_ms_back_to_back"] = sorted(timed_back_to_back(run_ref) for _ in range(3))[1]
+    res["own_ms_back_to_back"] = sorted(timed_back_to_back(run_own) for _ in range(3))[1]
+    il_ref, il_own = timed_interleaved(run_ref, run_own)
+    res["ref_ms_interleaved"], res["own_ms_interleaved"] = il_ref, il_own
+    res["own_over_ref_interleaved"] = il_ref / il_own
+    res["own_over_ref_back_to_back"] = res["ref_ms_back_to_back"] / res["own_ms_back_to_back"]
+    res["own_over_ref"] = iso_ref[0] / iso_own[0]
+    res["ref_tflops_interleaved"] = p["flops"] / (il_ref * 1e-3) / 1e12
+    res["own_tflops_interleaved"] = p["flops"] / (il_own * 1e-3) / 1e12
+    out.append(res)
+    print(json.dumps(res), flush=True)
+
+    if name == "fc2_tiny":
+        np.savez_compressed(
+            os.path.join(ROOT, "gpurun_out", "reference_kernel_fc2_golden.npz"),
+            a=p["a"][:, :, 0].view(torch.uint8).cpu().numpy(),
+            b=p["b"].permute(2, 0, 1).contiguous().view(torch.uint8).cpu().numpy(),
+            sfa=flat(p["sfa"]).cpu().numpy(),
+            sfb=flat(p["sfb"]).cpu().numpy(),
+            offsets=p["padded_offsets"].cpu().numpy(),
+            prob=p["prob"].view(-1).cpu().numpy(),
+            d=r_ref["d_tensor"][:m, :, 0].view(torch.uint8).cpu().numpy(),
+            d_col=r_ref["d_col_tensor"][:m, :, 0].view(torch.uint8).cpu().numpy(),
+            sfd_row=flat(r_ref["sfd_row_tensor"]).cpu().numpy(),
+            sfd_col=flat(r_ref["sfd_col_tensor"]).cpu().numpy(),
+        )
+
+
 PROFILE_ONLY = False
 OWN_FIRST = False
 
@@ -203,7 +280,12 @@ CASES = {
     "small": dict(experts=4, k=512, n=512, tokens=512, topk=2, routing="uniform"),
     "c2": dict(experts=8, k=4096, n=28672, tokens=16384, topk=2, routing="uniform"),
     "c3": dict(experts=256, k=7168, n=4096, tokens=8192, topk=8, routing="zipf"),
+    # FC2 (grouped_gemm_quant) cases: K = intermediate size, N = hidden size
+    "fc2_tiny": dict(experts=2, k=128, n=256, tokens=128, topk=2, routing="uniform"),
+    "fc2_mixtral": dict(experts=8, k=14336, n=4096, tokens=16384, topk=2, routing="uniform"),
+    "c4": dict(experts=256, k=2048, n=7168, tokens=8192, topk=8, routing="zipf"),
 }
+FC2_CASES = ("fc2_tiny", "fc2_mixtral", "c4")
 
 
 def main():
@@ -219,7 +301,7 @@ def main():
     out = []
     for name in args.cases.split(","):
         try:
-            run_case(name, CASES[name], out)
+            (run_case_fc2 if name in FC2_CASES else run_case)(name, CASES[name], out)
         except Exception as exc:  # keep going: a JIT failure of one case is a result too
             out.append({"case": name, "error": f"{type(exc).__name__}: {exc}"})
             traceback.print_exc()
