@@ -324,6 +324,11 @@ def bench_single(args):
         del prob_, outs, op2, xg, aq, d2
         torch.cuda.empty_cache()
         extras.update(bench_other_configs(dev, stream))
+        torch.cuda.empty_cache()
+        from cudnn_frontend_b200 import ep_bench
+
+        # the workload of the multi-GPU runs (--gpus 2/4/8) with all experts on this GPU
+        extras["ep_layer_1gpu"] = ep_bench.single_gpu_layer(dev)
 
     cpu = cpu_baseline_fc1()
     peak = 2.0 * peaks["bf16_sustained"]

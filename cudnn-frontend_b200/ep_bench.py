@@ -17,6 +17,45 @@ import torch.distributed as dist
 EXPERTS, HIDDEN, INTER, TOPK = 256, 7168, 2048, 8
 
 
+def _synthetic_tokens(tokens: int, dev, seed: int):
+    g = torch.Generator(device=dev).manual_seed(seed)
+    x = torch.randn(tokens, HIDDEN, generator=g, device=dev).to(torch.bfloat16)
+    rank_w = torch.arange(1, EXPERTS + 1, device=dev, dtype=torch.float32).pow(-1.2)
+    perm = torch.randperm(EXPERTS, generator=torch.Generator(device=dev).manual_seed(7), device=dev)  # same on every rank
+    w = torch.empty(EXPERTS, device=dev)
+    w[perm] = rank_w
+    ids = torch.multinomial(w.expand(tokens, EXPERTS), TOPK, replacement=False, generator=g).to(torch.int32)
+    prob = torch.softmax(torch.randn(tokens, TOPK, generator=g, device=dev), dim=-1)
+    return x, ids, prob
+
+
+def layer_flops(tokens_total: int) -> float:
+    return 2.0 * tokens_total * TOPK * (2 * INTER * HIDDEN + HIDDEN * INTER)
+
+
+def single_gpu_layer(dev, steps: int = 5, warmup: int = 3, tokens: int = 65536) -> dict:
+    """The same layer with all 256 experts on one GPU (no exchange): the like-for-like N = 1 point of
+    the multi-GPU series."""
+    from . import synthetic
+    from .ep_layer import ExpertParallelMoE
+
+    w1, sfw1 = synthetic.make_weights(EXPERTS, 2 * INTER, HIDDEN, 100, dev)
+    w2, sfw2 = synthetic.make_weights(EXPERTS, HIDDEN, INTER, 200, dev)
+    layer = ExpertParallelMoE(w1, sfw1, w2, sfw2, EXPERTS, None)
+    x, ids, prob = _synthetic_tokens(tokens, dev, 1000)
+    for _ in range(warmup):
+        layer(x, ids, prob)
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        layer(x, ids, prob)
+    stop.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(stop) / steps
+    return {"tflops": layer_flops(tokens) / (ms * 1e-3) / 1e12, "ms": ms, "tokens": tokens, "launches_per_step": 5}
+
+
 def run(args, tokens_per_gpu: int = 65536):
     from . import synthetic
     from .ep_layer import ExpertParallelMoE
@@ -35,43 +74,70 @@ def run(args, tokens_per_gpu: int = 65536):
     w2, sfw2 = synthetic.make_weights(e_local, HIDDEN, INTER, 200 + rank, dev)
     layer = ExpertParallelMoE(w1, sfw1, w2, sfw2, EXPERTS, group)
 
-    g = torch.Generator(device=dev).manual_seed(1000 + rank)
-    x = torch.randn(tokens_per_gpu, HIDDEN, generator=g, device=dev).to(torch.bfloat16)
-    rank_w = torch.arange(1, EXPERTS + 1, device=dev, dtype=torch.float32).pow(-1.2)
-    perm = torch.randperm(EXPERTS, generator=torch.Generator(device=dev).manual_seed(7), device=dev)  # same on every rank
-    w = torch.empty(EXPERTS, device=dev)
-    w[perm] = rank_w
-    ids = torch.multinomial(w.expand(tokens_per_gpu, EXPERTS), TOPK, replacement=False, generator=g).to(torch.int32)
-    prob = torch.softmax(torch.randn(tokens_per_gpu, TOPK, generator=g, device=dev), dim=-1)
+    x, ids, prob = _synthetic_tokens(tokens_per_gpu, dev, 1000 + rank)
 
     def barrier():
         if world > 1:
             dist.barrier()
 
+    micro = int(os.environ.get("B200MOE_EP_MICRO_BATCHES", "4" if world > 1 else "1"))
+
+    def step():
+        return layer.forward_pipelined(x, ids, prob, micro) if micro > 1 else layer(x, ids, prob)
+
     stream = torch.cuda.current_stream()
     for _ in range(max(args.warmup, 3)):
-        y = layer(x, ids, prob)
+        y = step()
     barrier()
     torch.cuda.synchronize()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record(stream)
     for _ in range(args.steps):
-        y = layer(x, ids, prob)
+        y = step()
     stop.record(stream)
     torch.cuda.synchronize()
     barrier()
     ms = torch.tensor([start.elapsed_time(stop) / args.steps], device=dev)
-    rows_recv = torch.tensor([float(layer.last_plan.rows_received)], device=dev)
+    rows_recv = torch.tensor([float(layer.last_rows_received)], device=dev)
     rows_max = rows_recv.clone()
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         dist.all_reduce(rows_max, op=dist.ReduceOp.MAX)
         dist.all_reduce(rows_recv, op=dist.ReduceOp.SUM)
     ms = ms.item()
-    total_rows = tokens_per_gpu * TOPK * world
-    flops = 2.0 * total_rows * (2 * INTER * HIDDEN + HIDDEN * INTER)
+    flops = layer_flops(tokens_per_gpu * world)
     value = flops / (ms * 1e-3) / 1e12
     finite = bool(torch.isfinite(y.float()).all().item())
+
+    # end to end: tokens, expert ids and gate probabilities start in pinned host memory every step,
+    # and a checksum of the layer's output is read back to the host
+    x_h, ids_h, prob_h = x.cpu().pin_memory(), ids.cpu().pin_memory(), prob.cpu().pin_memory()
+    x_d, ids_d, prob_d = torch.empty_like(x), torch.empty_like(ids), torch.empty_like(prob)
+    check_h = torch.empty(1, dtype=torch.float32).pin_memory()
+
+    def e2e_step():
+        x_d.copy_(x_h, non_blocking=True)
+        ids_d.copy_(ids_h, non_blocking=True)
+        prob_d.copy_(prob_h, non_blocking=True)
+        out = layer.forward_pipelined(x_d, ids_d, prob_d, micro) if micro > 1 else layer(x_d, ids_d, prob_d)
+        check_h.copy_(out.float().abs().max().view(1), non_blocking=True)
+
+    e2e_steps = max(args.steps // 4, 3)
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    torch.cuda.synchronize()
+    start.record(stream)
+    for _ in range(e2e_steps):
+        e2e_step()
+    stop.record(stream)
+    torch.cuda.synchronize()
+    barrier()
+    ms_e2e = torch.tensor([start.elapsed_time(stop) / e2e_steps], device=dev)
+    if world > 1:
+        dist.all_reduce(ms_e2e, op=dist.ReduceOp.MAX)
+    ms_e2e = ms_e2e.item()
+    h2d = x_h.numel() * 2 + ids_h.numel() * 4 + prob_h.numel() * 4
     if rank == 0:
         line = {
             "metric": "MXFP8 grouped-GEMM+SwiGLU TFLOP/s",
@@ -89,13 +155,16 @@ def run(args, tokens_per_gpu: int = 65536):
             "config": {
                 "workload": f"expert-parallel MoE layer: E=256 sharded {e_local}/GPU, hidden 7168, intermediate 2048, {tokens_per_gpu} tokens/GPU top-8 Zipf(1.2); dispatch all-to-all + quantise + FC1 + FC2 + combine all-to-all",
                 "parallelism": f"ep{world}",
+                "micro_batches": micro,
+                "overlap": "dispatch / combine all-to-all of neighbouring micro-batches run beside the GEMMs" if micro > 1 and world > 1 else "none",
                 "l2": "inputs larger than L2 (0.94 GB tokens, 11 GB local weights), no flush",
                 "rows_received_max_over_mean": rows_max.item() / (rows_recv.item() / world),
                 "pct_of_fp8_nominal_4500_per_gpu": 100.0 * value / world / 4500.0,
                 "output_finite": finite,
             },
-            "gpu_launches": args.steps * 9,
-            "e2e": None,
+            "gpu_launches": args.steps * 5 * micro,
+            "e2e": {"value": flops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
+                    "ms_per_step": ms_e2e, "note": "per rank: bytes are one rank's; the value is the aggregate over ranks"},
             "roofline": None,
             "cpu_baseline": None,
         }

@@ -112,6 +112,19 @@ def exchange_rows(send: torch.Tensor, out_rows: int, in_splits, out_splits, grou
     return recv
 
 
+def exchange_rows_async(send: torch.Tensor, out_rows: int, in_splits, out_splits, group):
+    """As :func:`exchange_rows`, but returns ``(recv, work)`` without making the caller's stream wait:
+    the exchange runs on the process group's own stream (it starts once the kernels already queued on
+    the caller's stream have produced ``send``) and ``work.wait()`` later orders the caller's stream
+    behind it.  ``work`` is None for a single rank."""
+    if group is None or dist.get_world_size(group) == 1:
+        return send, None
+    recv = torch.empty((out_rows,) + tuple(send.shape[1:]), dtype=send.dtype, device=send.device)
+    work = dist.all_to_all_single(recv, send, output_split_sizes=list(out_splits), input_split_sizes=list(in_splits), group=group,
+                                  async_op=True)  # fmt: skip
+    return recv, work
+
+
 class ExpertParallelMoE:
     """One MoE layer with this rank's ``E / G`` experts resident in HBM as MXFP8.
 
@@ -120,7 +133,7 @@ class ExpertParallelMoE:
     (as produced by ``synthetic.make_weights`` or by quantising real weights with
     ``quantize_mxfp8``)."""
 
-    def __init__(self, w1, sfw1, w2, sfw2, num_experts: int, group=None, m_aligned: int = 128):
+    def __init__(self, w1, sfw1, w2, sfw2, num_experts: int, group=None, m_aligned: int = 128, overlap_sm_margin: int = 16):
         if not w1.is_cuda:
             raise RuntimeError("ExpertParallelMoE runs on CUDA devices only")
         from . import grouped_gemm_quant, grouped_gemm_swiglu  # noqa: F401  (fails loudly without the CUDA library)
@@ -139,13 +152,16 @@ class ExpertParallelMoE:
         self.norm = torch.ones(1, dtype=torch.float32, device=dev)
         self._ops = {}
         self.last_plan: Optional[DispatchPlan] = None
+        self.last_rows_received = 0
+        # SMs the GEMMs leave to the all-to-all kernels that run beside them in the pipelined path
+        self.overlap_sm_margin = overlap_sm_margin if self.world > 1 else 0
 
-    def _fc_ops(self, m_rows: int, bufs):
+    def _fc_ops(self, m_rows: int, bufs, sm_margin: int = 0):
         """Operator objects are cached per padded row count (shapes are part of their samples)."""
         from .grouped_gemm_quant import GroupedGemmQuantSm100
         from .grouped_gemm_swiglu import GroupedGemmSwigluSm100
 
-        key = m_rows
+        key = (m_rows, sm_margin)
         if key not in self._ops:
             a, sfa, h8, sfh, y, prob, offs = bufs
             y = torch.empty((m_rows, self.hidden, 1), dtype=torch.bfloat16, device="meta")  # shape sample only
@@ -157,8 +173,67 @@ class ExpertParallelMoE:
             assert fc1.check_support() and fc2.check_support()
             fc1.compile()
             fc2.compile()
+            fc1.num_cluster_overlap_margin = fc2.num_cluster_overlap_margin = sm_margin
             self._ops[key] = (fc1, fc2)
         return self._ops[key]
+
+    def _experts(self, plan: DispatchPlan, recv_q, recv_sf, recv_p, sm_margin: int = 0) -> torch.Tensor:
+        """Received rows -> regroup by local expert -> FC1 -> FC2 -> result rows in arrival order."""
+        from . import moe, ops
+
+        h, dev, m = self.hidden, recv_q.device, plan.m_rows
+        y_recv = torch.empty((plan.rows_received, h), dtype=torch.bfloat16, device=dev)
+        if m > 0:
+            a, sfa, prob3 = moe.place_quantized_rows(recv_q, recv_sf, recv_p, plan.recv_dst, m, plan.counts_local, plan.padded_offsets)
+            h8 = torch.empty((m, self.inter, 1), dtype=torch.float8_e4m3fn, device=dev)
+            sfh = ops.empty_sf(m, self.inter, 1, device=dev)
+            fc1, fc2 = self._fc_ops(m, (a, sfa, h8, sfh, y_recv.view(-1, h, 1), prob3, plan.padded_offsets), sm_margin)
+            fc1.execute(a, self.w1, None, h8, sfa, self.sfw1, plan.padded_offsets, self.alpha, sfd_row_tensor=sfh, norm_const_tensor=self.norm)
+            fc2.execute(h8, sfh, plan.padded_offsets, self.alpha, y_recv.view(-1, h, 1), b_tensor=self.w2, sfb_tensor=self.sfw2,
+                        prob_tensor=prob3, d_row_map=plan.row_map)  # fmt: skip
+        return y_recv
+
+    def forward_pipelined(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_prob: torch.Tensor, micro_batches: int = 4) -> torch.Tensor:
+        """Same result as :meth:`forward`, computed as ``micro_batches`` slices of the tokens in a
+        software pipeline: while the GEMMs of slice i run on the caller's stream, the dispatch
+        all-to-all of slice i + 1 and the combine all-to-all of slice i - 1 run on the process group's
+        stream.  All index plans (and their host synchronisations) come first, so no host wait sits
+        between the stages.  Exchanges are issued in the same order on every rank:
+        d0, d1, c0, d2, c1, ... ; the GEMMs leave ``overlap_sm_margin`` SMs to the exchange kernels.
+        Every token's result depends on its own row only, so slicing changes nothing numerically."""
+        from . import moe
+
+        if not x.is_cuda:
+            raise RuntimeError("ExpertParallelMoE.forward needs CUDA tensors")
+        t, k = topk_ids.shape
+        n = max(1, min(micro_batches, t))
+        bounds = [(i * t // n, (i + 1) * t // n) for i in range(n)]
+        plans = [plan_dispatch(topk_ids[lo:hi], self.num_experts, self.group, self.m_aligned) for lo, hi in bounds]
+        self.last_plan = plans[-1]
+        self.last_rows_received = sum(p.rows_received for p in plans)
+        flat_prob = topk_prob.reshape(t * k).contiguous()
+        sends = [moe.dispatch_quantize(x[lo:hi], p.send_pos, k, flat_prob[lo * k : hi * k]) for (lo, hi), p in zip(bounds, plans)]
+
+        def start_dispatch(i):
+            p = plans[i]
+            return [exchange_rows_async(buf, p.rows_received, p.in_splits, p.out_splits, self.group) for buf in sends[i]]
+
+        out = torch.empty((t, self.hidden), dtype=torch.bfloat16, device=x.device)
+        inflight = start_dispatch(0)
+        backs = []
+        for i in range(n):
+            nxt = start_dispatch(i + 1) if i + 1 < n else None
+            for _, work in inflight:
+                if work is not None:
+                    work.wait()
+            y_recv = self._experts(plans[i], *(buf for buf, _ in inflight), sm_margin=self.overlap_sm_margin)
+            backs.append(exchange_rows_async(y_recv, plans[i].rows_sent, plans[i].out_splits, plans[i].in_splits, self.group))
+            inflight = nxt
+        for (lo, hi), p, (back, work) in zip(bounds, plans, backs):
+            if work is not None:
+                work.wait()
+            moe.combine_rows(back, p.send_pos, hi - lo, k, out=out[lo:hi])
+        return out
 
     def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_prob: torch.Tensor) -> torch.Tensor:
         """``x [T, H]`` bf16, ``topk_ids [T, k]`` int32 global expert ids, ``topk_prob [T, k]`` f32
@@ -172,6 +247,7 @@ class ExpertParallelMoE:
         dev = x.device
         plan = plan_dispatch(topk_ids, self.num_experts, self.group, self.m_aligned)
         self.last_plan = plan
+        self.last_rows_received = plan.rows_received
         # dispatch: each token row is read once, quantised, and written to its k send positions
         # (E4M3 + row-major scales + gate probability travel together: half the bytes of bf16)
         send_q, send_sf, send_p = moe.dispatch_quantize(x, plan.send_pos, k, topk_prob.reshape(-1).contiguous())

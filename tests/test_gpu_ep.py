@@ -43,6 +43,20 @@ def test_single_rank_layer_matches_oracle():
     assert H.rel_fro(y.float().cpu().numpy(), ref) <= 2e-2
 
 
+@pytest.mark.parametrize("micro_batches", [1, 3, 4])
+def test_pipelined_layer_equals_the_plain_layer(micro_batches):
+    """Slicing the tokens into micro-batches changes nothing: every token's result depends on its own row."""
+    from cudnn_frontend_b200.ep_layer import ExpertParallelMoE
+
+    x, ids, prob, w1, sfw1, w2, sfw2 = _inputs(4, "cuda")
+    layer = ExpertParallelMoE(w1, sfw1, w2, sfw2, E)
+    y = layer(x, ids, prob)
+    yp = layer.forward_pipelined(x, ids, prob, micro_batches=micro_batches)
+    torch.cuda.synchronize()
+    assert torch.equal(y, yp)
+    assert layer.last_rows_received == T * K
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
@@ -79,9 +93,10 @@ def _ep_worker(rank, world, port, ret):
         # same tokens through a single-rank layer that owns all experts
         full = ExpertParallelMoE(w1, sfw1, w2, sfw2, E)
         y1 = full(x, ids, prob)
+        yp = layer.forward_pipelined(x, ids, prob, micro_batches=3)
         torch.cuda.synchronize()
         # row order inside an expert group differs between the two runs, the per-row maths does not
-        ret[rank] = bool(torch.equal(y, y1))
+        ret[rank] = bool(torch.equal(y, y1)) and bool(torch.equal(yp, y1))
     finally:
         dist.destroy_process_group()
 
