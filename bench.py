@@ -332,6 +332,8 @@ def bench_single(args):
 
     cpu = cpu_baseline_fc1()
     peak = 2.0 * peaks["bf16_sustained"]
+    routed = t * topk
+    prob_bytes = routed * k * (1 + 1 / 32) + e * n * k * (1 + 1 / 32) + routed * (n // 2) * 2
     line = {
         "metric": METRIC,
         "value": value,
@@ -356,7 +358,11 @@ def bench_single(args):
             "peak": peak,
             "unit": UNIT,
             "frac": value / peak,
-            "traffic": None,
+            # HBM bytes of one launch (dram__bytes_read.sum + dram__bytes_write.sum) from the one-pass ncu
+            # launch list of this same workload (profiles/bench_c2_launch_list.md); algorithmic bytes beside it
+            "traffic": 1.60e9 + 0.93e9 if args.workload == "c2" else None,
+            "traffic_unit": "bytes per launch (ncu, this workload)",
+            "algorithmic_bytes": prob_bytes,
             "peak_source": f"2 x bf16_tflops_sustained of {peaks['source']} MEASURED_PEAKS.json (dense fp8 proxy)",
             "kernel": "grouped_gemm_kernel<FC1, dense>",
         },

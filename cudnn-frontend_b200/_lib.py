@@ -47,6 +47,8 @@ class GemmArgs(Structure):
         ("flags", c_int32),
         ("sm_margin", c_int32),
         ("d_row_map", c_void_p),
+        ("d_peer_ptrs", c_void_p),
+        ("d_peer_slots", c_int64),
     ]
 
 
@@ -74,6 +76,15 @@ _SIGNATURES = {
         ctypes.c_int,
         [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p],
     ),
+    "b200moe_dispatch_quantize_peer": (
+        ctypes.c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_int64, c_int32, c_int32, c_int32, c_int64,
+         c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+    ),  # fmt: skip
+    "b200moe_peer_alloc": (ctypes.c_int, [c_int64, POINTER(c_void_p), c_void_p]),
+    "b200moe_peer_open": (ctypes.c_int, [c_void_p, POINTER(c_void_p)]),
+    "b200moe_peer_close": (ctypes.c_int, [c_void_p]),
+    "b200moe_peer_free": (ctypes.c_int, [c_void_p]),
     "b200moe_gather_rows": (ctypes.c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p]),
     "b200moe_combine_rows": (ctypes.c_int, [c_void_p, c_void_p, c_int64, c_int32, c_int64, c_void_p, c_void_p]),
     "b200moe_last_error": (c_char_p, []),

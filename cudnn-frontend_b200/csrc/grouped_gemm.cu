@@ -100,6 +100,8 @@ struct GemmParams {
   const float* prob;
   const float* norm_const;
   const int32_t* d_row_map;  // optional scatter of bf16 D rows
+  const int64_t* d_peer_ptrs;  // optional: the scatter targets are peer buffers, see b200moe.h
+  int64_t d_peer_slots;
   __nv_bfloat16* c;
   void* d;
   uint8_t* d_col;
@@ -590,7 +592,14 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       const bool row_ok = row < min(p.m_rows, tile.row_end);
       const float alpha = p.alpha[tile.expert];
       const float prob = (p.prob && row_ok) ? p.prob[row] : 1.0f;
-      const int out_row = (p.d_row_map && row_ok) ? p.d_row_map[row] : row;
+      int out_row = (p.d_row_map && row_ok) ? p.d_row_map[row] : row;
+      // destination of this thread's bf16 D row: d, or the buffer of the rank the row returns to
+      __nv_bfloat16* d_rows = reinterpret_cast<__nv_bfloat16*>(p.d);
+      if (p.d_peer_ptrs && out_row >= 0) {
+        const int64_t rank = out_row / p.d_peer_slots;
+        d_rows = reinterpret_cast<__nv_bfloat16*>(p.d_peer_ptrs[rank]);
+        out_row -= (int)(rank * p.d_peer_slots);
+      }
       const uint32_t acc = tmem_base + ((it & 1) ? TMEM_ACC1_COL : 0) + ((uint32_t)(quarter * 32) << 16);
       const bool reverse = (it & 1) == 0;  // even tiles drain from the top (shared columns first)
       float thread_amax = 0.f;
@@ -636,7 +645,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 #pragma unroll
               for (int j = 0; j < 32; ++j) thread_amax = fmaxf(thread_amax, fabsf(g[j]));
             }
-            if (row_ok && out_row >= 0) store_bf16x32(reinterpret_cast<__nv_bfloat16*>(p.d) + (int64_t)out_row * p.n_out + dn, g, wide);
+            if (row_ok && out_row >= 0) store_bf16x32(d_rows + (int64_t)out_row * p.n_out + dn, g, wide);
           } else {
             if (row_ok) {
               const uint32_t sf = quant_row_block(reinterpret_cast<uint8_t*>(p.d) + (int64_t)row * p.n_out + dn, g, norm_const, wide);
@@ -696,7 +705,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 #pragma unroll
               for (int j = 0; j < 32; ++j) thread_amax = fmaxf(thread_amax, fabsf(v[j]));
             }
-            if (row_ok && out_row >= 0) store_bf16x32(reinterpret_cast<__nv_bfloat16*>(p.d) + (int64_t)out_row * p.n_out + dn, v, wide);
+            if (row_ok && out_row >= 0) store_bf16x32(d_rows + (int64_t)out_row * p.n_out + dn, v, wide);
           } else {
             if (row_ok) {
               const uint32_t sf = quant_row_block(reinterpret_cast<uint8_t*>(p.d) + (int64_t)row * p.n_out + dn, v, norm_const, wide);
@@ -945,6 +954,8 @@ static int run_gemm(int epi, const b200moe_gemm_args* a, void* stream_v) {
   if (a->n * a->k > (1ll << 40)) return fail(B200MOE_E_SHAPE, "%s: n*k too large", op);
   const bool d_fp8 = a->d_dtype == B200MOE_DTYPE_E4M3;
   if (a->d_row_map && (d_fp8 || a->c)) return fail(B200MOE_E_UNSUPPORTED, "%s: d_row_map needs a bf16 D and no C", op);
+  if (a->d_peer_ptrs && (!a->d_row_map || a->d_peer_slots <= 0))
+    return fail(B200MOE_E_SHAPE, "%s: d_peer_ptrs needs d_row_map and a positive d_peer_slots", op);
   if (a->d_dtype != B200MOE_DTYPE_BF16 && !d_fp8) return fail(B200MOE_E_UNSUPPORTED, "%s: d_dtype %d", op, a->d_dtype);
   if (d_fp8) {
     if (!a->sfd_row || !a->norm_const)
@@ -971,6 +982,8 @@ static int run_gemm(int epi, const b200moe_gemm_args* a, void* stream_v) {
   p.prob = a->prob;
   p.norm_const = a->norm_const;
   p.d_row_map = a->d_row_map;
+  p.d_peer_ptrs = a->d_row_map ? a->d_peer_ptrs : nullptr;
+  p.d_peer_slots = a->d_peer_slots;
   p.c = epi == EPI_FC1 ? (__nv_bfloat16*)a->c : nullptr;
   p.d = a->d;
   p.d_col = d_fp8 ? (uint8_t*)a->d_col : nullptr;
@@ -1158,6 +1171,6 @@ int b200moe_device_status(int clear) {
   return v;
 }
 
-int b200moe_abi_version(void) { return 1; }
+int b200moe_abi_version(void) { return 2; }
 
 }  // extern "C"

@@ -163,6 +163,79 @@ __global__ void __launch_bounds__(128)
   }
 }
 
+// Dispatch over peer memory: as dispatch_quantize_kernel, but every slot's row goes straight into
+// the expert-grouped GEMM operand of the rank that owns the expert (E4M3 bytes, swizzled scales,
+// gate probability, return address), with plain stores to peer-mapped addresses.
+__global__ void __launch_bounds__(128)
+    dispatch_quantize_peer_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ expert_ids,
+                                  const int32_t* __restrict__ local_row, const int32_t* __restrict__ delta,
+                                  const float* __restrict__ topk_prob, int topk, int cols, int rest_k, int experts_per_rank,
+                                  int num_ranks, int my_rank, int64_t slot_capacity, int64_t row_capacity,
+                                  const int64_t* __restrict__ peer_q, const int64_t* __restrict__ peer_sf,
+                                  const int64_t* __restrict__ peer_prob, const int64_t* __restrict__ peer_map) {
+  const int64_t t = blockIdx.x;
+  const int lane = threadIdx.x & 31;
+  __shared__ int64_t s_row[16];
+  __shared__ uint8_t* s_q[16];
+  __shared__ uint8_t* s_sf[16];
+  if (threadIdx.x < topk) {
+    const int64_t slot = t * topk + threadIdx.x;
+    const int e = expert_ids[slot];
+    int64_t row = -1;
+    int rank = 0;
+    if (e >= 0 && e < experts_per_rank * num_ranks) {
+      rank = e / experts_per_rank;
+      row = (int64_t)delta[e] + local_row[slot];
+      if (row < 0 || row >= row_capacity) {
+        atomicCAS(&g_device_status, 0, 301);  // never store outside a peer's buffer
+        row = -1;
+      }
+    }
+    s_row[threadIdx.x] = row;
+    s_q[threadIdx.x] = reinterpret_cast<uint8_t*>(peer_q[rank]);
+    s_sf[threadIdx.x] = reinterpret_cast<uint8_t*>(peer_sf[rank]);
+    if (row >= 0) {
+      reinterpret_cast<float*>(peer_prob[rank])[row] = topk_prob ? topk_prob[slot] : 1.0f;
+      reinterpret_cast<int32_t*>(peer_map[rank])[row] = (int32_t)(my_rank * slot_capacity + slot);
+    }
+  }
+  __syncthreads();
+  for (int v = threadIdx.x; v < cols / 8; v += blockDim.x) {
+    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(x + t * cols) + v);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    float f[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 p2 = __bfloat1622float2(h[j]);
+      f[2 * j] = p2.x;
+      f[2 * j + 1] = p2.y;
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(f[j]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    const uint32_t sfb = e8m0_from_float(amax * (1.0f / 448.0f));
+    const float scale = quant_scale(1.0f, e8m0_to_float(sfb));
+    uint2 o;
+    o.x = e4m3x4_from_float(f[0] * scale, f[1] * scale, f[2] * scale, f[3] * scale);
+    o.y = e4m3x4_from_float(f[4] * scale, f[5] * scale, f[6] * scale, f[7] * scale);
+    // the scales of four consecutive K blocks are four consecutive bytes of the swizzled layout:
+    // lanes 0 and 16 collect them (K blocks sit 4 lanes apart) and store one 32-bit word
+    uint32_t word = sfb;
+    word |= __shfl_down_sync(0xffffffffu, sfb, 4) << 8;
+    word |= __shfl_down_sync(0xffffffffu, sfb, 8) << 16;
+    word |= __shfl_down_sync(0xffffffffu, sfb, 12) << 24;
+    const int kb = v >> 2;  // K block of this lane; a multiple of 4 in lanes 0 and 16
+    for (int j = 0; j < topk; ++j) {
+      const int64_t row = s_row[j];
+      if (row < 0) continue;
+      reinterpret_cast<uint2*>(s_q[j] + row * cols)[v] = o;
+      if ((lane & 15) == 0) *reinterpret_cast<uint32_t*>(s_sf[j] + sf_offset(row, kb, rest_k)) = word;
+    }
+  }
+}
+
 // Receive side: row i of the arrival-order buffers goes to row dst_row[i] of the expert-grouped
 // operand; its scales are written into the 128x4 swizzled layout the GEMM reads.
 __global__ void __launch_bounds__(128)
@@ -294,6 +367,67 @@ int b200moe_dispatch_quantize(const void* x, const int32_t* send_pos, const floa
   dispatch_quantize_kernel<<<(unsigned)num_tokens, 128, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)x, send_pos, topk_prob, topk, (int)cols, (uint8_t*)q, (uint8_t*)sf, prob_out);
   B200_CUDA_CHECK(cudaGetLastError());
+  return B200MOE_OK;
+}
+
+int b200moe_dispatch_quantize_peer(const void* x, const int32_t* expert_ids, const int32_t* local_row, const int32_t* delta,
+                                   const float* topk_prob, int64_t num_tokens, int32_t topk, int64_t cols,
+                                   int32_t experts_per_rank, int32_t num_ranks, int32_t my_rank, int64_t slot_capacity,
+                                   int64_t row_capacity, const int64_t* peer_q, const int64_t* peer_sf,
+                                   const int64_t* peer_prob, const int64_t* peer_map, void* stream) {
+  using namespace b200moe;
+  if (num_tokens == 0) return B200MOE_OK;
+  if (!x || !expert_ids || !local_row || !delta || !peer_q || !peer_sf || !peer_prob || !peer_map)
+    return fail(B200MOE_E_NULL, "dispatch_quantize_peer: null pointer");
+  // whole warps only (the scale word is assembled by full-mask shuffles): 32 lanes x 8 columns
+  if (cols <= 0 || cols % 256 != 0 || topk <= 0 || topk > 16 || num_tokens < 0 || num_tokens > 0x7fffffffll)
+    return fail(B200MOE_E_SHAPE, "dispatch_quantize_peer: cols must be a positive multiple of 256 and topk in [1, 16]");
+  if (experts_per_rank <= 0 || num_ranks <= 0 || my_rank < 0 || my_rank >= num_ranks || slot_capacity < num_tokens * topk ||
+      (int64_t)num_ranks * slot_capacity > 0x7fffffffll || row_capacity <= 0)
+    return fail(B200MOE_E_SHAPE, "dispatch_quantize_peer: bad rank layout or capacities");
+  if ((uintptr_t)x & 15) return fail(B200MOE_E_ALIGN, "dispatch_quantize_peer: 16-byte alignment required");
+  const int rest_k = (int)((cols / 32 + 3) / 4);
+  dispatch_quantize_peer_kernel<<<(unsigned)num_tokens, 128, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)x, expert_ids, local_row, delta, topk_prob, topk, (int)cols, rest_k, experts_per_rank, num_ranks,
+      my_rank, slot_capacity, row_capacity, peer_q, peer_sf, peer_prob, peer_map);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200MOE_OK;
+}
+
+int b200moe_peer_alloc(int64_t bytes, void** ptr, void* handle64) {
+  using namespace b200moe;
+  if (!ptr || !handle64 || bytes <= 0) return fail(B200MOE_E_NULL, "peer_alloc: null pointer or empty size");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+  B200_CUDA_CHECK(cudaMalloc(ptr, (size_t)bytes));
+  cudaIpcMemHandle_t h;
+  const cudaError_t e = cudaIpcGetMemHandle(&h, *ptr);
+  if (e != cudaSuccess) {
+    cudaFree(*ptr);
+    *ptr = nullptr;
+    B200_CUDA_CHECK(e);
+  }
+  memcpy(handle64, &h, 64);
+  return B200MOE_OK;
+}
+
+int b200moe_peer_open(const void* handle64, void** ptr) {
+  using namespace b200moe;
+  if (!ptr || !handle64) return fail(B200MOE_E_NULL, "peer_open: null pointer");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, 64);
+  B200_CUDA_CHECK(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+  return B200MOE_OK;
+}
+
+int b200moe_peer_close(void* ptr) {
+  using namespace b200moe;
+  if (ptr) B200_CUDA_CHECK(cudaIpcCloseMemHandle(ptr));
+  return B200MOE_OK;
+}
+
+int b200moe_peer_free(void* ptr) {
+  using namespace b200moe;
+  if (ptr) B200_CUDA_CHECK(cudaFree(ptr));
   return B200MOE_OK;
 }
 

@@ -44,16 +44,17 @@ def single_gpu_layer(dev, steps: int = 5, warmup: int = 3, tokens: int = 65536) 
     layer = ExpertParallelMoE(w1, sfw1, w2, sfw2, EXPERTS, None)
     x, ids, prob = _synthetic_tokens(tokens, dev, 1000)
     for _ in range(warmup):
-        layer(x, ids, prob)
+        layer.forward_fused(x, ids, prob)
     torch.cuda.synchronize()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
     for _ in range(steps):
-        layer(x, ids, prob)
+        layer.forward_fused(x, ids, prob)
     stop.record()
     torch.cuda.synchronize()
     ms = start.elapsed_time(stop) / steps
-    return {"tflops": layer_flops(tokens) / (ms * 1e-3) / 1e12, "ms": ms, "tokens": tokens, "launches_per_step": 5}
+    layer.release_peer_buffers()
+    return {"tflops": layer_flops(tokens) / (ms * 1e-3) / 1e12, "ms": ms, "tokens": tokens, "launches_per_step": 7}
 
 
 def run(args, tokens_per_gpu: int = 65536):
@@ -80,10 +81,18 @@ def run(args, tokens_per_gpu: int = 65536):
         if world > 1:
             dist.barrier()
 
-    micro = int(os.environ.get("B200MOE_EP_MICRO_BATCHES", "4" if world > 1 else "1"))
+    # data path: "peer" = rows cross NVLink by stores from the dispatch kernel and the FC2 epilogue;
+    # "nccl" = all-to-all of rows (optionally pipelined over micro-batches)
+    path = os.environ.get("B200MOE_EP_PATH", "peer")
+    micro = int(os.environ.get("B200MOE_EP_MICRO_BATCHES", "1"))
+
+    def run_layer(xx, ii, pp):
+        if path == "peer":
+            return layer.forward_fused(xx, ii, pp)
+        return layer.forward_pipelined(xx, ii, pp, micro) if micro > 1 else layer(xx, ii, pp)
 
     def step():
-        return layer.forward_pipelined(x, ids, prob, micro) if micro > 1 else layer(x, ids, prob)
+        return run_layer(x, ids, prob)
 
     stream = torch.cuda.current_stream()
     for _ in range(max(args.warmup, 3)):
@@ -119,7 +128,7 @@ def run(args, tokens_per_gpu: int = 65536):
         x_d.copy_(x_h, non_blocking=True)
         ids_d.copy_(ids_h, non_blocking=True)
         prob_d.copy_(prob_h, non_blocking=True)
-        out = layer.forward_pipelined(x_d, ids_d, prob_d, micro) if micro > 1 else layer(x_d, ids_d, prob_d)
+        out = run_layer(x_d, ids_d, prob_d)
         check_h.copy_(out.float().abs().max().view(1), non_blocking=True)
 
     e2e_steps = max(args.steps // 4, 3)
@@ -155,19 +164,19 @@ def run(args, tokens_per_gpu: int = 65536):
             "config": {
                 "workload": f"expert-parallel MoE layer: E=256 sharded {e_local}/GPU, hidden 7168, intermediate 2048, {tokens_per_gpu} tokens/GPU top-8 Zipf(1.2); dispatch all-to-all + quantise + FC1 + FC2 + combine all-to-all",
                 "parallelism": f"ep{world}",
-                "micro_batches": micro,
-                "overlap": "dispatch / combine all-to-all of neighbouring micro-batches run beside the GEMMs" if micro > 1 and world > 1 else "none",
+                "data_path": "peer stores over NVLink from the quantise+dispatch kernel and from the FC2 epilogue; no all-to-all of rows" if path == "peer" else f"NCCL all-to-all, {micro} micro-batch(es)",
                 "l2": "inputs larger than L2 (0.94 GB tokens, 11 GB local weights), no flush",
                 "rows_received_max_over_mean": rows_max.item() / (rows_recv.item() / world),
                 "pct_of_fp8_nominal_4500_per_gpu": 100.0 * value / world / 4500.0,
                 "output_finite": finite,
             },
-            "gpu_launches": args.steps * 5 * micro,
+            "gpu_launches": args.steps * (7 if path == "peer" else 5 * micro),
             "e2e": {"value": flops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
                     "ms_per_step": ms_e2e, "note": "per rank: bytes are one rank's; the value is the aggregate over ranks"},
             "roofline": None,
             "cpu_baseline": None,
         }
         print(json.dumps(line))
+    layer.release_peer_buffers()
     if world > 1:
         dist.destroy_process_group()

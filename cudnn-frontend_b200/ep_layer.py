@@ -103,6 +103,34 @@ def plan_dispatch(topk_ids: torch.Tensor, num_experts: int, group=None, m_aligne
                         counts_local.to(torch.int32), offsets.to(torch.int32), m_rows)  # fmt: skip
 
 
+@dataclass
+class FusedPlan:
+    """Index plan of the peer-memory path, identical inputs give identical plans on every rank."""
+
+    delta: torch.Tensor  # [E] int32: destination row = delta[e] + compact local row of the routed slot
+    padded_offsets: torch.Tensor  # [E_local] int32 END offsets of this rank's expert groups
+    m_rows_all: torch.Tensor  # [G] int64 padded rows every rank will hold
+    rows_all: torch.Tensor  # [G] int64 true rows every rank receives
+
+
+def plan_fused(counts_all: torch.Tensor, rank: int, m_aligned: int = 128) -> FusedPlan:
+    """``counts_all [G, E]``: rows source rank s routes to global expert e (the all-gathered
+    per-rank histograms).  Expert e lives on rank ``e // (E / G)``; its group there holds the rows of
+    source rank 0 first, then rank 1, ..., each in the sender's own (stable) order, and starts at the
+    padded end of the previous local expert.  Pure integer torch ops: runs on any device."""
+    g, e = counts_all.shape
+    e_local = e // g
+    c = counts_all.to(torch.int64)
+    total = c.sum(0)  # rows of every expert over all sources
+    padded = ((total + m_aligned - 1) // m_aligned) * m_aligned
+    ends = torch.cumsum(padded.view(g, e_local), dim=1)  # END offsets on the owning rank
+    group_start = (ends - padded.view(g, e_local)).reshape(e)
+    before = torch.cumsum(c, dim=0) - c  # rows of earlier source ranks inside each group
+    compact_start = torch.cumsum(c[rank], 0) - c[rank]  # this rank's route(m_aligned=1) starts
+    delta = group_start + before[rank] - compact_start
+    return FusedPlan(delta.to(torch.int32), ends[rank].to(torch.int32), ends[:, -1].contiguous(), total.view(g, e_local).sum(1))
+
+
 def exchange_rows(send: torch.Tensor, out_rows: int, in_splits, out_splits, group) -> torch.Tensor:
     """All-to-all of whole rows (first dimension split)."""
     if group is None or dist.get_world_size(group) == 1:
@@ -192,6 +220,115 @@ class ExpertParallelMoE:
             fc2.execute(h8, sfh, plan.padded_offsets, self.alpha, y_recv.view(-1, h, 1), b_tensor=self.w2, sfb_tensor=self.sfw2,
                         prob_tensor=prob3, d_row_map=plan.row_map)  # fmt: skip
         return y_recv
+
+    # ------------------------------------------------------------------------------------------
+    # peer-memory path: no all-to-all of rows at all
+    # ------------------------------------------------------------------------------------------
+    def _peer_setup(self, tokens: int, topk: int, capacity_factor: float):
+        """Peer-addressable buffers, allocated once per (tokens, topk): the expert-grouped GEMM operand
+        of this rank (E4M3 rows, swizzled scales, gate probabilities, return addresses) that every
+        rank's dispatch kernel stores into, and the [T * k, H] result buffer that every rank's FC2
+        epilogue stores into."""
+        from .peer_memory import PeerBuffer
+
+        key = (tokens, topk, capacity_factor)
+        if getattr(self, "_peer_key", None) == key:
+            return self._peer
+        if getattr(self, "_peer", None) is not None:
+            self.release_peer_buffers()
+        slots = tokens * topk
+        # rows this rank may receive: its fair share times the factor, plus the padding of every group
+        cap = int(slots * capacity_factor) + self.e_local * self.m_aligned
+        cap = ((cap + 127) // 128) * 128
+        h = self.hidden
+        rest_k = (h // 32 + 3) // 4
+        bufs = {
+            "q": PeerBuffer(cap * h, self.group),
+            "sf": PeerBuffer((cap // 128) * rest_k * 512, self.group),
+            "prob": PeerBuffer(cap * 4, self.group),
+            "map": PeerBuffer(cap * 4, self.group),
+            "back": PeerBuffer(slots * h * 2, self.group),
+        }
+        self._peer = dict(bufs=bufs, cap=cap, slots=slots, identity=torch.arange(slots, dtype=torch.int32, device=self.w1.device))
+        self._peer_key = key
+        return self._peer
+
+    def release_peer_buffers(self) -> None:
+        """Unmap and free the peer buffers (every rank, after the last step; ends with a barrier)."""
+        peer = getattr(self, "_peer", None)
+        if peer is None:
+            return
+        torch.cuda.synchronize()
+        if self.world > 1:
+            dist.barrier(group=self.group)
+        for b in peer["bufs"].values():
+            b.close()
+        self._peer, self._peer_key = None, None
+
+    def _rank_barrier(self):
+        """Orders the ranks on the device: kernels queued after it start only when every rank has
+        finished the kernels it queued before it (a one-element all-reduce on the compute stream;
+        the host does not wait)."""
+        if self.world > 1:
+            dist.all_reduce(self._token, group=self.group)
+
+    def forward_fused(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_prob: torch.Tensor, capacity_factor: float = 2.0) -> torch.Tensor:
+        """Same result as :meth:`forward`, without any all-to-all of rows: the dispatch kernel stores
+        quantised rows straight into the owning rank's GEMM operand over NVLink, and the FC2 epilogue
+        stores result rows straight into the source rank's result buffer.
+
+            histogram of my slots -> all-gather of the histograms (G x E ints) -> plan (same on every rank)
+            -> [quantise + dispatch + regroup] one kernel, peer stores -> barrier
+            -> FC1 -> FC2 (epilogue: peer stores to the slot the row came from) -> barrier -> top-k sum
+
+        One host synchronisation reads this rank's padded row count.  ``capacity_factor`` bounds the
+        rows a rank may receive (times its fair share); more raises instead of overrunning a buffer."""
+        from . import moe, ops
+
+        if not x.is_cuda:
+            raise RuntimeError("ExpertParallelMoE.forward_fused needs CUDA tensors")
+        t, k = topk_ids.shape
+        h, dev, g = self.hidden, x.device, self.world
+        rank = 0 if self.group is None else dist.get_rank(self.group)
+        if not hasattr(self, "_token"):
+            self._token = torch.zeros(1, dtype=torch.float32, device=dev)
+        peer = self._peer_setup(t, k, capacity_factor)
+        bufs, cap, slots = peer["bufs"], peer["cap"], peer["slots"]
+
+        ids = topk_ids.contiguous()
+        counts, _, local_row = moe.route(ids.view(-1), self.num_experts, 1)
+        bufs["map"].view(torch.int32, (cap,)).fill_(-1)  # padding rows return nowhere
+        if g > 1:
+            counts_all = torch.empty((g, self.num_experts), dtype=torch.int32, device=dev)
+            dist.all_gather_into_tensor(counts_all, counts, group=self.group)
+        else:
+            counts_all = counts.view(1, -1)
+        plan = plan_fused(counts_all, rank, self.m_aligned)
+        m_all = plan.m_rows_all.cpu().tolist()  # the one host synchronisation
+        m = int(m_all[rank])
+        self.last_rows_received = int(plan.rows_all[rank].item()) if g > 1 else t * k
+        if max(m_all) > cap:
+            raise RuntimeError(f"a rank would receive {max(m_all)} padded rows, capacity is {cap}: raise capacity_factor")
+        # the all-gather above already ordered this step's stores behind every rank's map reset
+        moe.dispatch_quantize_peer(x, ids, local_row, plan.delta, topk_prob.reshape(t * k).contiguous(), self.e_local, g, rank,
+                                   slots, cap, bufs["q"].ptrs_dev, bufs["sf"].ptrs_dev, bufs["prob"].ptrs_dev, bufs["map"].ptrs_dev)  # fmt: skip
+        self._rank_barrier()
+        if m > 0:
+            a = torch.as_strided(bufs["q"].view(torch.float8_e4m3fn, (m, h)), (m, h, 1), (h, 1, m * h))
+            shape, stride = ops.sf_shape_stride(m, h, 1)
+            sfa = torch.as_strided(bufs["sf"].local.view(torch.float8_e8m0fnu), shape, stride)
+            prob3 = bufs["prob"].view(torch.float32, (m,)).view(m, 1, 1)
+            row_map = bufs["map"].view(torch.int32, (m,))
+            back_local = bufs["back"].view(torch.bfloat16, (slots, h))
+            h8 = torch.empty((m, self.inter, 1), dtype=torch.float8_e4m3fn, device=dev)
+            sfh = ops.empty_sf(m, self.inter, 1, device=dev)
+            fc1, fc2 = self._fc_ops(m, (a, sfa, h8, sfh, None, prob3, plan.padded_offsets))
+            fc1.execute(a, self.w1, None, h8, sfa, self.sfw1, plan.padded_offsets, self.alpha, sfd_row_tensor=sfh, norm_const_tensor=self.norm)
+            fc2.execute(h8, sfh, plan.padded_offsets, self.alpha, back_local.view(slots, h, 1),
+                        b_tensor=self.w2, sfb_tensor=self.sfw2, prob_tensor=prob3, d_row_map=row_map,
+                        d_peer_ptrs=bufs["back"].ptrs_dev, d_peer_slots=slots)  # fmt: skip
+        self._rank_barrier()
+        return moe.combine_rows(bufs["back"].view(torch.bfloat16, (slots, h)), peer["identity"], t, k)
 
     def forward_pipelined(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_prob: torch.Tensor, micro_batches: int = 4) -> torch.Tensor:
         """Same result as :meth:`forward`, computed as ``micro_batches`` slices of the tokens in a

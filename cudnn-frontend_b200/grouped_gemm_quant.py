@@ -239,10 +239,15 @@ class GroupedGemmQuantSm100(OperatorBase):
         prob_tensor: Optional[torch.Tensor] = None,
         current_stream=None,
         d_row_map: Optional[torch.Tensor] = None,
+        d_peer_ptrs: Optional[torch.Tensor] = None,
+        d_peer_slots: int = 0,
     ) -> None:
         """Launch on ``current_stream``; allocates nothing.  ``d_row_map`` (int32 ``[M]``, not in the
         reference) stores row ``r`` of a bf16 result at row ``d_row_map[r]`` of ``d_tensor`` (negative:
-        not stored), so a caller can receive the rows in another order, e.g. all-to-all order."""
+        not stored), so a caller can receive the rows in another order, e.g. all-to-all order.  With
+        ``d_peer_ptrs`` (int64 device tensor of G buffer addresses, each ``[d_peer_slots, N]`` bf16) a map
+        value ``v`` addresses row ``v % d_peer_slots`` of rank ``v // d_peer_slots``'s buffer: the epilogue
+        stores over NVLink into the ranks the rows came from."""
         self._ensure_compiled()
         tensor_m, k = a_tensor.shape[0], a_tensor.shape[1]
         if tensor_m == 0:
@@ -282,6 +287,8 @@ class GroupedGemmQuantSm100(OperatorBase):
             sm_margin=self.num_cluster_overlap_margin,
             tile_mode=pick_tile_mode(self.mma_tiler_mn, self.m_aligned),
             d_row_map=d_row_map,
+            d_peer_ptrs=d_peer_ptrs,
+            d_peer_slots=d_peer_slots,
             stream=current_stream,
         )
 

@@ -125,6 +125,29 @@ def zero_pad_rows(buf: torch.Tensor, counts: torch.Tensor, padded_offsets: torch
     _lib.check(rc)
 
 
+def dispatch_quantize_peer(x: torch.Tensor, topk_ids: torch.Tensor, local_row: torch.Tensor, delta: torch.Tensor,
+                           topk_prob: Optional[torch.Tensor], experts_per_rank: int, num_ranks: int, my_rank: int,
+                           slot_capacity: int, row_capacity: int, peer_q: torch.Tensor, peer_sf: torch.Tensor,
+                           peer_prob: torch.Tensor, peer_map: torch.Tensor, stream=None) -> None:  # fmt: skip
+    """Fused quantise + dispatch over peer memory: token rows of ``x [T, H]`` are quantised to MXFP8 and
+    stored straight into the expert-grouped GEMM operand of the rank that owns each slot's expert
+    (see ``b200moe_dispatch_quantize_peer`` in include/b200moe.h).  ``peer_*`` are int64 device tensors
+    of ``num_ranks`` base addresses."""
+    if x.dtype != torch.bfloat16 or not x.is_contiguous():
+        raise ValueError("x must be a contiguous bf16 tensor")
+    t, h = x.shape
+    k = topk_ids.shape[1]
+    for name, ten in (("topk_ids", topk_ids), ("local_row", local_row), ("delta", delta)):
+        if ten.dtype != torch.int32 or not ten.is_contiguous():
+            raise ValueError(f"{name} must be a contiguous int32 tensor")
+    with torch.cuda.device(x.device):
+        rc = _lib.load().b200moe_dispatch_quantize_peer(
+            x.data_ptr(), topk_ids.data_ptr(), local_row.data_ptr(), delta.data_ptr(),
+            None if topk_prob is None else topk_prob.data_ptr(), t, k, h, experts_per_rank, num_ranks, my_rank, slot_capacity,
+            row_capacity, peer_q.data_ptr(), peer_sf.data_ptr(), peer_prob.data_ptr(), peer_map.data_ptr(), _stream_ptr(stream))  # fmt: skip
+    _lib.check(rc)
+
+
 def combine_rows(y: torch.Tensor, dst_row: torch.Tensor, num_tokens: int, topk: int, out: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
     """``out[t] = sum_j y[dst_row[t * topk + j]]`` (bf16 in, float32 accumulate, bf16 out)."""
     if y.dtype != torch.bfloat16 or not y.is_contiguous():

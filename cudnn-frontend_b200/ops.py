@@ -115,6 +115,8 @@ def launch_grouped_gemm(
     sm_margin: int = 0,
     tile_mode: Optional[str] = None,
     d_row_map: Optional[torch.Tensor] = None,
+    d_peer_ptrs: Optional[torch.Tensor] = None,
+    d_peer_slots: int = 0,
     stream=None,
 ) -> None:
     """Fill the C struct and call b200moe_fc1_swiglu / b200moe_fc2_quant.
@@ -142,6 +144,8 @@ def launch_grouped_gemm(
     args.flags |= {"auto": 0, "single": _lib.FLAG_TILE_SINGLE, "pair": _lib.FLAG_TILE_PAIR}[mode]
     args.sm_margin = sm_margin
     args.d_row_map = _ptr(d_row_map)
+    args.d_peer_ptrs = _ptr(d_peer_ptrs)
+    args.d_peer_slots = int(d_peer_slots)
     lib = _lib.load()
     fn = lib.b200moe_fc1_swiglu if kind == "fc1" else lib.b200moe_fc2_quant
     with torch.cuda.device(a.device):
@@ -204,19 +208,21 @@ def _(a, sfa, b, sfb, b_ptrs, sfb_ptrs, padded_offsets, alpha, prob, norm_const,
 def _fc2_quant_op(
     a: torch.Tensor, sfa: torch.Tensor, b: _T, sfb: _T, b_ptrs: _T, sfb_ptrs: _T, padded_offsets: torch.Tensor,
     alpha: torch.Tensor, prob: torch.Tensor, norm_const: _T, d: torch.Tensor, d_col: _T, amax: _T, sfd_row: _T,
-    sfd_col: _T, workspace: _T, d_row_map: _T, n: int, discrete_col_sfd: bool, sm_margin: int, tile_mode: str,
+    sfd_col: _T, workspace: _T, d_row_map: _T, d_peer_ptrs: _T, d_peer_slots: int, n: int, discrete_col_sfd: bool,
+    sm_margin: int, tile_mode: str,
 ) -> None:  # fmt: skip
     launch_grouped_gemm(
         "fc2", a=a, sfa=sfa, b=b, sfb=sfb, b_ptrs=b_ptrs, sfb_ptrs=sfb_ptrs, padded_offsets=padded_offsets, alpha=alpha,
         prob=prob, norm_const=norm_const, d=d, d_col=d_col, amax=amax, sfd_row=sfd_row, sfd_col=sfd_col,
         workspace=workspace, m_rows=a.shape[0], n=n, k=a.shape[1], num_experts=padded_offsets.shape[0],
         discrete_col_sfd=discrete_col_sfd, sm_margin=sm_margin, tile_mode=tile_mode or None, d_row_map=d_row_map,
+        d_peer_ptrs=d_peer_ptrs, d_peer_slots=d_peer_slots,
     )  # fmt: skip
 
 
 @_fc2_quant_op.register_fake
 def _(a, sfa, b, sfb, b_ptrs, sfb_ptrs, padded_offsets, alpha, prob, norm_const, d, d_col, amax, sfd_row, sfd_col, workspace,
-      d_row_map, n, discrete_col_sfd, sm_margin, tile_mode) -> None:  # fmt: skip
+      d_row_map, d_peer_ptrs, d_peer_slots, n, discrete_col_sfd, sm_margin, tile_mode) -> None:  # fmt: skip
     return None
 
 
@@ -236,7 +242,7 @@ def grouped_gemm_op(kind: str, *, stream=None, **kw) -> None:
         if kind == "fc1":
             torch.ops.b200moe.fc1_swiglu(*common, kw.get("c"), *outs, *tail)
         else:
-            torch.ops.b200moe.fc2_quant(*common, *outs, kw.get("d_row_map"), *tail)
+            torch.ops.b200moe.fc2_quant(*common, *outs, kw.get("d_row_map"), kw.get("d_peer_ptrs"), int(kw.get("d_peer_slots", 0)), *tail)
 
     if ctx is None:
         call()

@@ -86,6 +86,13 @@ typedef struct b200moe_gemm_args {
   /* optional, bf16 D only: row r of the result is stored at row d_row_map[r] of d (negative =
      the row is not stored).  Lets the layer write FC2 results straight in all-to-all order. */
   const int32_t* d_row_map;
+  /* optional, with d_row_map: the destination rows live in peer-accessible buffers of G ranks.
+     d_peer_ptrs = device array of G base addresses (this rank's own buffer included), every buffer
+     [d_peer_slots, N_out] bf16; a map value v >= 0 then means row (v % d_peer_slots) of the buffer
+     of rank (v / d_peer_slots).  The epilogue stores over NVLink, which replaces the combine
+     all-to-all of an expert-parallel layer.  NULL = d_row_map indexes d. */
+  const int64_t* d_peer_ptrs;
+  int64_t d_peer_slots;
 } b200moe_gemm_args;
 
 /*
@@ -188,6 +195,38 @@ int b200moe_gather_rows(const void* in, const int32_t* src_row, int64_t num_rows
                         void* out, void* stream);
 int b200moe_combine_rows(const void* in, const int32_t* dst_row, int64_t num_tokens, int32_t topk,
                          int64_t cols, void* out, void* stream);
+
+/*
+ * Expert-parallel dispatch over peer memory (no reference counterpart: the reference has no
+ * multi-GPU code).  Replaces quantise + all-to-all + regroup by one kernel that stores over NVLink.
+ *
+ * b200moe_dispatch_quantize_peer: for token t the bf16 row x[t, :] is read once and quantised to
+ *   MXFP8; for every slot j < topk with expert e = expert_ids[t*topk + j] the row goes to rank
+ *   e / experts_per_rank, at row  r = delta[e] + local_row[t*topk + j]  of that rank's expert-grouped
+ *   GEMM operand: E4M3 bytes to peer_q[rank] + r*cols, E8M0 scales into the swizzled 128x4 layout at
+ *   peer_sf[rank], the gate probability to peer_prob[rank][r] and the return address
+ *   my_rank*slot_capacity + t*topk + j to peer_map[rank][r] (the d_row_map of that rank's FC2).
+ *   local_row = b200moe_route(..., m_aligned = 1) of this rank's rows; delta[e] = first row this rank
+ *   owns inside expert e's group on the destination, minus this rank's compact start of e.
+ *   peer_* are device arrays of G addresses.  Rows r outside [0, row_capacity) are not written and
+ *   raise device status 301.  The caller orders the ranks (all ranks finish this kernel, then a
+ *   barrier, then the GEMMs) -- the kernel itself never waits for a peer.
+ *
+ * b200moe_peer_alloc / _open / _close / _free: device buffers that other processes of this node can
+ *   map (CUDA IPC).  alloc returns the pointer and a 64-byte handle to hand to the peers; open maps a
+ *   peer's handle (peer access is enabled on first use) and close unmaps it.
+ */
+int b200moe_dispatch_quantize_peer(const void* x, const int32_t* expert_ids, const int32_t* local_row,
+                                   const int32_t* delta, const float* topk_prob, int64_t num_tokens,
+                                   int32_t topk, int64_t cols, int32_t experts_per_rank,
+                                   int32_t num_ranks, int32_t my_rank, int64_t slot_capacity,
+                                   int64_t row_capacity, const int64_t* peer_q,
+                                   const int64_t* peer_sf, const int64_t* peer_prob,
+                                   const int64_t* peer_map, void* stream);
+int b200moe_peer_alloc(int64_t bytes, void** ptr, void* handle64);
+int b200moe_peer_open(const void* handle64, void** ptr);
+int b200moe_peer_close(void* ptr);
+int b200moe_peer_free(void* ptr);
 
 /* Last error text of the calling thread ("" if none).  Never NULL. */
 const char* b200moe_last_error(void);

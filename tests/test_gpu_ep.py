@@ -57,6 +57,23 @@ def test_pipelined_layer_equals_the_plain_layer(micro_batches):
     assert layer.last_rows_received == T * K
 
 
+def test_peer_memory_layer_equals_the_plain_layer():
+    """One rank: the fused quantise + dispatch kernel and the FC2 epilogue address this rank's own
+    buffers through the same pointer tables the multi-rank path uses."""
+    from cudnn_frontend_b200 import ops
+    from cudnn_frontend_b200.ep_layer import ExpertParallelMoE
+
+    x, ids, prob, w1, sfw1, w2, sfw2 = _inputs(5, "cuda")
+    layer = ExpertParallelMoE(w1, sfw1, w2, sfw2, E)
+    y = layer(x, ids, prob)
+    yf = layer.forward_fused(x, ids, prob)
+    yf2 = layer.forward_fused(x, ids, prob)  # buffers are reused from step to step
+    torch.cuda.synchronize()
+    assert ops.device_status(clear=True) == 0
+    assert torch.equal(y, yf) and torch.equal(y, yf2)
+    layer.release_peer_buffers()
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
@@ -94,9 +111,15 @@ def _ep_worker(rank, world, port, ret):
         full = ExpertParallelMoE(w1, sfw1, w2, sfw2, E)
         y1 = full(x, ids, prob)
         yp = layer.forward_pipelined(x, ids, prob, micro_batches=3)
+        yf = layer.forward_fused(x, ids, prob)  # rows cross NVLink by peer stores, no all-to-all
+        yf2 = layer.forward_fused(x, ids, prob)
         torch.cuda.synchronize()
-        # row order inside an expert group differs between the two runs, the per-row maths does not
-        ret[rank] = bool(torch.equal(y, y1)) and bool(torch.equal(yp, y1))
+        from cudnn_frontend_b200 import ops as _ops
+
+        status = _ops.device_status(clear=True)
+        layer.release_peer_buffers()
+        # row order inside an expert group differs between the runs, the per-row maths does not
+        ret[rank] = bool(torch.equal(y, y1)) and bool(torch.equal(yp, y1)) and bool(torch.equal(yf, y1)) and bool(torch.equal(yf2, y1)) and status == 0
     finally:
         dist.destroy_process_group()
 

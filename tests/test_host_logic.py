@@ -30,7 +30,7 @@ def test_library_builds_loads_and_exports_every_declared_symbol():
     for name in declared:
         assert hasattr(lib, name), f"{name} declared in include/b200moe.h but not exported"
     assert set(declared) == set(_lib.EXPORTED_SYMBOLS)
-    assert _lib.load().b200moe_abi_version() == 1
+    assert _lib.load().b200moe_abi_version() == 2
     assert _lib.load().b200moe_workspace_bytes(256, 1) == 256 * 256
     assert _lib.load().b200moe_workspace_bytes(256, 0) == 0
 
@@ -171,3 +171,52 @@ def test_custom_ops_are_registered_with_mutation_schemas():
         for m in mutated:
             assert args[m].alias_info is not None and args[m].alias_info.is_write, f"{name}.{m} must be declared mutable"
         assert not args["a" if name != "quantize_mxfp8" else "x"].alias_info
+
+
+def test_fused_plan_places_every_routed_row_once_inside_its_expert_group():
+    """plan_fused against a brute-force construction: on the owning rank, expert groups are padded to
+    m_aligned, and inside a group the rows of source rank 0 come first, then rank 1, ..., each in the
+    sender's own order."""
+    import numpy as np
+    import torch
+
+    from cudnn_frontend_b200.ep_layer import plan_fused
+
+    g, e, m_aligned = 4, 12, 8
+    e_local = e // g
+    rng = np.random.default_rng(5)
+    ids = [rng.integers(0, e, size=rng.integers(20, 60)) for _ in range(g)]
+    ids[2][:] = ids[2] % 5  # some experts get nothing from rank 2
+    counts = np.stack([np.bincount(i, minlength=e) for i in ids])
+    counts[:, 7] = 0  # an expert nobody routes to
+    ids = [i[i != 7] for i in ids]
+    plans = [plan_fused(torch.from_numpy(counts).to(torch.int32), r, m_aligned) for r in range(g)]
+
+    total = counts.sum(0)
+    padded = -(-total // m_aligned) * m_aligned
+    seen = [dict() for _ in range(g)]
+    for s in range(g):
+        order = np.argsort(ids[s], kind="stable")  # compact local rows = stable grouping by expert
+        local_row = np.empty_like(order)
+        local_row[order] = np.arange(len(order))
+        for slot, ex in enumerate(ids[s]):
+            d = ex // e_local
+            row = int(plans[s].delta[ex]) + int(local_row[slot])
+            assert row not in seen[d]
+            seen[d][row] = (s, slot, ex)
+    for d in range(g):
+        ends = np.cumsum(padded[d * e_local : (d + 1) * e_local])
+        assert plans[d].padded_offsets.tolist() == ends.tolist()
+        assert int(plans[0].m_rows_all[d]) == int(ends[-1])
+        assert int(plans[0].rows_all[d]) == int(total[d * e_local : (d + 1) * e_local].sum()) == len(seen[d])
+        start = 0
+        for el in range(e_local):
+            ex = d * e_local + el
+            rows = sorted(r for r, v in seen[d].items() if v[2] == ex)
+            assert rows == list(range(start, start + int(total[ex])))  # compact from the group start
+            srcs = [seen[d][r][0] for r in rows]
+            assert srcs == sorted(srcs)  # by source rank
+            for s in range(g):  # and in the sender's order within a source
+                slots = [seen[d][r][1] for r in rows if seen[d][r][0] == s]
+                assert slots == sorted(slots)
+            start = int(ends[el])
