@@ -43,6 +43,17 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 
 __device__ __forceinline__ uint32_t lane_id() { return threadIdx.x & 31; }
 
+// Asynchronous row copy shared memory -> global memory (also a peer GPU's), tracked by bulk groups.
+// Both addresses 16-byte aligned, size a multiple of 16 bytes.
+__device__ __forceinline__ void bulk_store(void* gdst, uint32_t smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// the issuing thread's copies have finished reading shared memory (it may be rewritten)
+__device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// the issuing thread's copies are complete
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 // True in exactly one lane of a converged warp.  Unlike a `lane == 0` test, the compiler knows
 // the warp stays convergent around the elected region, so descriptors and addresses of TMA and
 // tcgen05 instructions can live in uniform registers.

@@ -66,9 +66,15 @@ constexpr int ST_MMA_FULL = 102;
 constexpr int ST_MMA_OVERLAP = 103;
 constexpr int ST_EPI_ACC = 104;
 
-template <bool kPair>
+// kBulk: bf16 D rows leave through a shared-memory staging area and one bulk copy per row (used
+// when the rows go to peer GPUs: 256-byte bursts instead of 32-byte stores); the staging area
+// takes the place of two (pair) or one (single) pipeline stages.
+constexpr int STAGING_ROW_BYTES = 256 + 16;  // 128 bf16 columns of one row, padded against bank conflicts
+constexpr int STAGING_WARP_BYTES = 32 * STAGING_ROW_BYTES;
+
+template <bool kPair, bool kBulk = false>
 struct Cfg {
-  static constexpr int STAGES = kPair ? 6 : 4;
+  static constexpr int STAGES = kBulk ? (kPair ? 4 : 3) : (kPair ? 6 : 4);
   static constexpr int B_ROWS = kPair ? 128 : 256;  // rows of B this CTA loads per stage
   static constexpr int B_STAGE_BYTES = B_ROWS * BK;
   static constexpr int TILE_M = kPair ? 256 : 128;  // rows of one scheduled tile
@@ -81,12 +87,14 @@ struct Cfg {
   static constexpr int NUM_BARS = 2 * STAGES + 2 + 1;
   static constexpr int MISC_OFF = BAR_OFF + NUM_BARS * 8;  // tmem ptr, abort flag, total tiles
   static constexpr int PREFIX_OFF = MISC_OFF + 16;         // (E + 1) int32 tile prefix
-  static constexpr int TOTAL = PREFIX_OFF + (MAX_EXPERTS + 1) * 4;
+  static constexpr int STAGING_OFF = (PREFIX_OFF + (MAX_EXPERTS + 1) * 4 + 15) & ~15;
+  static constexpr int TOTAL = STAGING_OFF + (kBulk ? NUM_EPI_WARPS * STAGING_WARP_BYTES : 0);
   static constexpr int SMEM_BYTES = TOTAL + 1024;  // slack for manual 1024-byte alignment
   // bytes credited to a "full" barrier per stage (both CTAs of a pair together)
   static constexpr uint32_t TX_BYTES = CTAS * (A_STAGE_BYTES + B_STAGE_BYTES + SFA_STAGE_BYTES + SFB_STAGE_BYTES);
 };
 static_assert(Cfg<false>::SMEM_BYTES <= 232448 && Cfg<true>::SMEM_BYTES <= 232448, "shared memory budget exceeded");
+static_assert(Cfg<false, true>::SMEM_BYTES <= 232448 && Cfg<true, true>::SMEM_BYTES <= 232448, "shared memory budget exceeded");
 
 enum : int { EPI_FC1 = 0, EPI_FC2 = 1 };
 
@@ -287,12 +295,12 @@ __device__ __forceinline__ uint32_t quant_col_block(uint8_t* dst, bool do_store,
 // ---------------------------------------------------------------------------------------
 // The kernel
 // ---------------------------------------------------------------------------------------
-template <int kEpi, bool kDiscrete, bool kPair>
+template <int kEpi, bool kDiscrete, bool kPair, bool kBulk = false>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
     grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                         const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
                         const GemmParams p) {
-  using C = Cfg<kPair>;
+  using C = Cfg<kPair, kBulk>;
   constexpr int STAGES = C::STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -577,6 +585,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     const int r_in_tile = quarter * 32 + lane;
     const float norm_const = p.norm_const ? *p.norm_const : 1.0f;
     const bool wide = p.wide_stores != 0;
+    uint8_t* const stage_row = smem + C::STAGING_OFF + ew * STAGING_WARP_BYTES + lane * STAGING_ROW_BYTES;  // kBulk only
     const uint32_t overlap_target = kPair ? map_to_cta(overlap_bar, 0) : overlap_bar;
     auto arrive_overlap = [&]() {
       if (kPair) mbar_arrive_cluster(overlap_target); else mbar_arrive(overlap_bar);
@@ -683,6 +692,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         }
       } else {
         // FC2: 4 blocks of 32 columns per half
+        if constexpr (kBulk) bulk_wait_read0();  // the previous tile's row copies have left the staging area
 #pragma unroll 1
         for (int i = 0; i < 4; ++i) {
           const int bb = reverse ? 3 - i : i;
@@ -705,7 +715,21 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 #pragma unroll
               for (int j = 0; j < 32; ++j) thread_amax = fmaxf(thread_amax, fabsf(v[j]));
             }
-            if (row_ok && out_row >= 0) store_bf16x32(d_rows + (int64_t)out_row * p.n_out + dn, v, wide);
+            if constexpr (kBulk) {
+              // this row's 32 columns -> its slot of the staging area (64 bytes)
+              uint4* st = reinterpret_cast<uint4*>(stage_row + bb * 64);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                uint4 o;
+                o.x = bf16x2_from_float(v[8 * q + 0], v[8 * q + 1]);
+                o.y = bf16x2_from_float(v[8 * q + 2], v[8 * q + 3]);
+                o.z = bf16x2_from_float(v[8 * q + 4], v[8 * q + 5]);
+                o.w = bf16x2_from_float(v[8 * q + 6], v[8 * q + 7]);
+                st[q] = o;
+              }
+            } else {
+              if (row_ok && out_row >= 0) store_bf16x32(d_rows + (int64_t)out_row * p.n_out + dn, v, wide);
+            }
           } else {
             if (row_ok) {
               const uint32_t sf = quant_row_block(reinterpret_cast<uint8_t*>(p.d) + (int64_t)row * p.n_out + dn, v, norm_const, wide);
@@ -728,6 +752,17 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
               }
               if (tile.row0 + quarter * 32 < min(p.m_rows, tile.row_end)) p.sfd_col[blk_base + sf_offset(dn + lane, rb, rest)] = (uint8_t)sfc;
             }
+          }
+        }
+        if constexpr (kBulk) {
+          if (!p.d_is_fp8) {
+            // one asynchronous copy per row: up to 128 columns = 256 contiguous bytes at the destination
+            fence_proxy_async_smem();
+            const int c0 = n0 + half * 128;
+            const int ncols = min(128, p.n - c0);
+            if (row_ok && out_row >= 0 && ncols > 0)
+              bulk_store(d_rows + (int64_t)out_row * p.n_out + c0, smem_u32(stage_row), (uint32_t)ncols * 2);
+            bulk_commit();
           }
         }
         if (p.d_is_fp8 && row_ok && p.sfd_row) {
@@ -754,6 +789,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
   }
 
   // ---- teardown ----------------------------------------------------------------------
+  if constexpr (kBulk) bulk_wait_all();  // row copies still reading this CTA's shared memory
   tc_fence_before();
   __syncthreads();
   if (kPair) {
@@ -872,6 +908,7 @@ struct DeviceInfo {
   int sm_count = 0;
   int cc_major = 0;
   bool attr_set[2][2][2] = {};
+  bool attr_set_bulk[2] = {};
 };
 
 static int get_device_info(DeviceInfo** out) {
@@ -890,13 +927,14 @@ static int get_device_info(DeviceInfo** out) {
   return B200MOE_OK;
 }
 
-template <int kEpi, bool kDiscrete, bool kPair>
+template <int kEpi, bool kDiscrete, bool kPair, bool kBulk = false>
 static int launch(const CUtensorMap* maps, const GemmParams& p, int grid, DeviceInfo* di, cudaStream_t stream) {
-  auto kern = grouped_gemm_kernel<kEpi, kDiscrete, kPair>;
-  constexpr int smem = Cfg<kPair>::SMEM_BYTES;
-  if (!di->attr_set[kEpi][kDiscrete ? 1 : 0][kPair ? 1 : 0]) {
+  auto kern = grouped_gemm_kernel<kEpi, kDiscrete, kPair, kBulk>;
+  constexpr int smem = Cfg<kPair, kBulk>::SMEM_BYTES;
+  bool& attr_set = kBulk ? di->attr_set_bulk[kPair ? 1 : 0] : di->attr_set[kEpi][kDiscrete ? 1 : 0][kPair ? 1 : 0];
+  if (!attr_set) {
     B200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    di->attr_set[kEpi][kDiscrete ? 1 : 0][kPair ? 1 : 0] = true;
+    attr_set = true;
   }
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
@@ -1085,6 +1123,10 @@ static int run_gemm(int epi, const b200moe_gemm_args* a, void* stream_v) {
   if ((int64_t)units > max_tiles) units = (int)max_tiles;
   const int grid = pair ? 2 * units : units;
 
+  // FC2 rows that go to peer buffers leave through shared memory and one bulk copy per row
+  if (epi == EPI_FC2 && !discrete && !d_fp8 && p.d_peer_ptrs && ((uintptr_t)a->d % 16 == 0))
+    return pair ? launch<EPI_FC2, false, true, true>(maps, p, grid, di, stream)
+                : launch<EPI_FC2, false, false, true>(maps, p, grid, di, stream);
   return epi == EPI_FC1 ? dispatch<EPI_FC1>(discrete, pair, maps, p, grid, di, stream)
                         : dispatch<EPI_FC2>(discrete, pair, maps, p, grid, di, stream);
 }
