@@ -164,8 +164,10 @@ __global__ void __launch_bounds__(128)
 }
 
 // Dispatch over peer memory: as dispatch_quantize_kernel, but every slot's row goes straight into
-// the expert-grouped GEMM operand of the rank that owns the expert (E4M3 bytes, swizzled scales,
-// gate probability, return address), with plain stores to peer-mapped addresses.
+// the expert-grouped GEMM operand of the rank that owns the expert.  The quantised row is built once
+// in shared memory and leaves as one asynchronous bulk copy per slot (a whole row per NVLink burst
+// instead of 8-byte stores); scales (4-byte words of the swizzled layout), gate probability and
+// return address are plain stores to the peer-mapped addresses.
 __global__ void __launch_bounds__(128)
     dispatch_quantize_peer_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ expert_ids,
                                   const int32_t* __restrict__ local_row, const int32_t* __restrict__ delta,
@@ -173,6 +175,7 @@ __global__ void __launch_bounds__(128)
                                   int num_ranks, int my_rank, int64_t slot_capacity, int64_t row_capacity,
                                   const int64_t* __restrict__ peer_q, const int64_t* __restrict__ peer_sf,
                                   const int64_t* __restrict__ peer_prob, const int64_t* __restrict__ peer_map) {
+  extern __shared__ __align__(16) uint8_t s_qrow[];  // cols bytes: the E4M3 row
   const int64_t t = blockIdx.x;
   const int lane = threadIdx.x & 31;
   __shared__ int64_t s_row[16];
@@ -220,19 +223,28 @@ __global__ void __launch_bounds__(128)
     uint2 o;
     o.x = e4m3x4_from_float(f[0] * scale, f[1] * scale, f[2] * scale, f[3] * scale);
     o.y = e4m3x4_from_float(f[4] * scale, f[5] * scale, f[6] * scale, f[7] * scale);
+    reinterpret_cast<uint2*>(s_qrow)[v] = o;
     // the scales of four consecutive K blocks are four consecutive bytes of the swizzled layout:
     // lanes 0 and 16 collect them (K blocks sit 4 lanes apart) and store one 32-bit word
     uint32_t word = sfb;
     word |= __shfl_down_sync(0xffffffffu, sfb, 4) << 8;
     word |= __shfl_down_sync(0xffffffffu, sfb, 8) << 16;
     word |= __shfl_down_sync(0xffffffffu, sfb, 12) << 24;
-    const int kb = v >> 2;  // K block of this lane; a multiple of 4 in lanes 0 and 16
-    for (int j = 0; j < topk; ++j) {
-      const int64_t row = s_row[j];
-      if (row < 0) continue;
-      reinterpret_cast<uint2*>(s_q[j] + row * cols)[v] = o;
-      if ((lane & 15) == 0) *reinterpret_cast<uint32_t*>(s_sf[j] + sf_offset(row, kb, rest_k)) = word;
+    if ((lane & 15) == 0) {
+      const int kb = v >> 2;  // a multiple of 4 in these lanes
+      for (int j = 0; j < topk; ++j) {
+        const int64_t row = s_row[j];
+        if (row >= 0) *reinterpret_cast<uint32_t*>(s_sf[j] + sf_offset(row, kb, rest_k)) = word;
+      }
     }
+  }
+  fence_proxy_async_smem();  // this thread's part of the row, for the bulk copies below
+  __syncthreads();
+  if (threadIdx.x < topk) {
+    const int64_t row = s_row[threadIdx.x];
+    if (row >= 0) bulk_store(s_q[threadIdx.x] + row * cols, smem_u32(s_qrow), (uint32_t)cols);
+    bulk_commit();
+    bulk_wait_read0();  // the shared-memory row must outlive the copy's reads
   }
 }
 
@@ -387,7 +399,8 @@ int b200moe_dispatch_quantize_peer(const void* x, const int32_t* expert_ids, con
     return fail(B200MOE_E_SHAPE, "dispatch_quantize_peer: bad rank layout or capacities");
   if ((uintptr_t)x & 15) return fail(B200MOE_E_ALIGN, "dispatch_quantize_peer: 16-byte alignment required");
   const int rest_k = (int)((cols / 32 + 3) / 4);
-  dispatch_quantize_peer_kernel<<<(unsigned)num_tokens, 128, 0, (cudaStream_t)stream>>>(
+  if (cols > 48 * 1024) return fail(B200MOE_E_SHAPE, "dispatch_quantize_peer: a row must fit 48 KiB of shared memory");
+  dispatch_quantize_peer_kernel<<<(unsigned)num_tokens, 128, (size_t)cols, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)x, expert_ids, local_row, delta, topk_prob, topk, (int)cols, rest_k, experts_per_rank, num_ranks,
       my_rank, slot_capacity, row_capacity, peer_q, peer_sf, peer_prob, peer_map);
   B200_CUDA_CHECK(cudaGetLastError());

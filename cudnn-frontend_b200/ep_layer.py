@@ -281,8 +281,9 @@ class ExpertParallelMoE:
             -> [quantise + dispatch + regroup] one kernel, peer stores -> barrier
             -> FC1 -> FC2 (epilogue: peer stores to the slot the row came from) -> barrier -> top-k sum
 
-        One host synchronisation reads this rank's padded row count.  ``capacity_factor`` bounds the
-        rows a rank may receive (times its fair share); more raises instead of overrunning a buffer."""
+        One host synchronisation reads every rank's padded row count.  ``capacity_factor`` sizes the
+        buffers (rows a rank may receive, times its fair share); when a step needs more, all ranks
+        reallocate larger ones together."""
         from . import moe, ops
 
         if not x.is_cuda:
@@ -304,12 +305,20 @@ class ExpertParallelMoE:
         else:
             counts_all = counts.view(1, -1)
         plan = plan_fused(counts_all, rank, self.m_aligned)
-        m_all = plan.m_rows_all.cpu().tolist()  # the one host synchronisation
+        host = torch.cat([plan.m_rows_all, plan.rows_all]).cpu().tolist()  # the one host synchronisation
+        m_all = host[:g]
         m = int(m_all[rank])
-        self.last_rows_received = int(plan.rows_all[rank].item()) if g > 1 else t * k
+        self.last_rows_received = int(host[g + rank])
         if max(m_all) > cap:
-            raise RuntimeError(f"a rank would receive {max(m_all)} padded rows, capacity is {cap}: raise capacity_factor")
-        # the all-gather above already ordered this step's stores behind every rank's map reset
+            # every rank sees the same row counts, so every rank takes this branch together: new, larger
+            # buffers, their maps reset, and a barrier so that no rank stores before every reset is done
+            if max(m_all) > 64 * slots:
+                raise RuntimeError(f"a rank would receive {max(m_all)} padded rows from {slots} slots per rank")
+            peer = self._peer_setup(t, k, 1.25 * max(m_all) / slots)
+            bufs, cap = peer["bufs"], peer["cap"]
+            bufs["map"].view(torch.int32, (cap,)).fill_(-1)
+            self._rank_barrier()
+        # (otherwise the all-gather above already ordered this step's stores behind every rank's map reset)
         moe.dispatch_quantize_peer(x, ids, local_row, plan.delta, topk_prob.reshape(t * k).contiguous(), self.e_local, g, rank,
                                    slots, cap, bufs["q"].ptrs_dev, bufs["sf"].ptrs_dev, bufs["prob"].ptrs_dev, bufs["map"].ptrs_dev)  # fmt: skip
         self._rank_barrier()
