@@ -79,8 +79,10 @@ _SIGNATURES = {
     "b200moe_dispatch_quantize_peer": (
         ctypes.c_int,
         [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_int64, c_int32, c_int32, c_int32, c_int64,
-         c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+         c_int64, c_void_p, c_void_p, c_void_p],
     ),  # fmt: skip
+    "b200moe_dispatch_record_pitch": (ctypes.c_int, [c_int64]),
+    "b200moe_unpack_dispatch_records": (ctypes.c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p]),
     "b200moe_peer_alloc": (ctypes.c_int, [c_int64, POINTER(c_void_p), c_void_p]),
     "b200moe_peer_open": (ctypes.c_int, [c_void_p, POINTER(c_void_p)]),
     "b200moe_peer_close": (ctypes.c_int, [c_void_p]),

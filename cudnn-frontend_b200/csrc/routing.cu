@@ -2,6 +2,8 @@
 // per-expert END offsets the grouped GEMMs consume, row scatter (dispatch side) and the
 // top-k combine.  All integer results are exact and deterministic (no float atomics, no
 // order-dependent placement): rows of one expert keep their original order.
+#include <algorithm>
+
 #include "b200moe.h"
 #include "common.cuh"
 
@@ -165,22 +167,24 @@ __global__ void __launch_bounds__(128)
 
 // Dispatch over peer memory: as dispatch_quantize_kernel, but every slot's row goes straight into
 // the expert-grouped GEMM operand of the rank that owns the expert.  The quantised row is built once
-// in shared memory and leaves as one asynchronous bulk copy per slot (a whole row per NVLink burst
-// instead of 8-byte stores); scales (4-byte words of the swizzled layout), gate probability and
-// return address are plain stores to the peer-mapped addresses.
+// in shared memory and leaves as one asynchronous bulk copy per slot; the row's scales travel with
+// the slot's gate probability and return address as one small record per slot (a second bulk copy),
+// because thousands of 4-byte stores per row are what NVLink is worst at.  Record layout
+// (rec_pitch bytes, a multiple of 16): [cols / 32 scale bytes | padding | f32 prob | i32 return address].
 __global__ void __launch_bounds__(128)
     dispatch_quantize_peer_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ expert_ids,
                                   const int32_t* __restrict__ local_row, const int32_t* __restrict__ delta,
-                                  const float* __restrict__ topk_prob, int topk, int cols, int rest_k, int experts_per_rank,
+                                  const float* __restrict__ topk_prob, int topk, int cols, int rec_pitch, int experts_per_rank,
                                   int num_ranks, int my_rank, int64_t slot_capacity, int64_t row_capacity,
-                                  const int64_t* __restrict__ peer_q, const int64_t* __restrict__ peer_sf,
-                                  const int64_t* __restrict__ peer_prob, const int64_t* __restrict__ peer_map) {
-  extern __shared__ __align__(16) uint8_t s_qrow[];  // cols bytes: the E4M3 row
+                                  const int64_t* __restrict__ peer_q, const int64_t* __restrict__ peer_rec) {
+  extern __shared__ __align__(16) uint8_t s_dyn[];  // [cols] E4M3 row, then topk records of rec_pitch bytes
+  uint8_t* const s_qrow = s_dyn;
+  uint8_t* const s_rec = s_dyn + cols;
   const int64_t t = blockIdx.x;
   const int lane = threadIdx.x & 31;
+  const int sf_cols = cols / 32;
   __shared__ int64_t s_row[16];
-  __shared__ uint8_t* s_q[16];
-  __shared__ uint8_t* s_sf[16];
+  __shared__ int s_rank[16];
   if (threadIdx.x < topk) {
     const int64_t slot = t * topk + threadIdx.x;
     const int e = expert_ids[slot];
@@ -195,14 +199,11 @@ __global__ void __launch_bounds__(128)
       }
     }
     s_row[threadIdx.x] = row;
-    s_q[threadIdx.x] = reinterpret_cast<uint8_t*>(peer_q[rank]);
-    s_sf[threadIdx.x] = reinterpret_cast<uint8_t*>(peer_sf[rank]);
-    if (row >= 0) {
-      reinterpret_cast<float*>(peer_prob[rank])[row] = topk_prob ? topk_prob[slot] : 1.0f;
-      reinterpret_cast<int32_t*>(peer_map[rank])[row] = (int32_t)(my_rank * slot_capacity + slot);
-    }
+    s_rank[threadIdx.x] = rank;
+    uint8_t* rec = s_rec + threadIdx.x * rec_pitch;
+    *reinterpret_cast<float*>(rec + rec_pitch - 8) = topk_prob ? topk_prob[slot] : 1.0f;
+    *reinterpret_cast<int32_t*>(rec + rec_pitch - 4) = (int32_t)(my_rank * slot_capacity + slot);
   }
-  __syncthreads();
   for (int v = threadIdx.x; v < cols / 8; v += blockDim.x) {
     const uint4 raw = __ldg(reinterpret_cast<const uint4*>(x + t * cols) + v);
     const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
@@ -224,27 +225,47 @@ __global__ void __launch_bounds__(128)
     o.x = e4m3x4_from_float(f[0] * scale, f[1] * scale, f[2] * scale, f[3] * scale);
     o.y = e4m3x4_from_float(f[4] * scale, f[5] * scale, f[6] * scale, f[7] * scale);
     reinterpret_cast<uint2*>(s_qrow)[v] = o;
-    // the scales of four consecutive K blocks are four consecutive bytes of the swizzled layout:
-    // lanes 0 and 16 collect them (K blocks sit 4 lanes apart) and store one 32-bit word
-    uint32_t word = sfb;
-    word |= __shfl_down_sync(0xffffffffu, sfb, 4) << 8;
-    word |= __shfl_down_sync(0xffffffffu, sfb, 8) << 16;
-    word |= __shfl_down_sync(0xffffffffu, sfb, 12) << 24;
-    if ((lane & 15) == 0) {
-      const int kb = v >> 2;  // a multiple of 4 in these lanes
-      for (int j = 0; j < topk; ++j) {
-        const int64_t row = s_row[j];
-        if (row >= 0) *reinterpret_cast<uint32_t*>(s_sf[j] + sf_offset(row, kb, rest_k)) = word;
-      }
+    if ((lane & 3) == 0) {
+      for (int j = 0; j < topk; ++j) s_rec[j * rec_pitch + (v >> 2)] = (uint8_t)sfb;
     }
   }
-  fence_proxy_async_smem();  // this thread's part of the row, for the bulk copies below
+  fence_proxy_async_smem();  // this thread's writes, for the bulk copies below
   __syncthreads();
   if (threadIdx.x < topk) {
     const int64_t row = s_row[threadIdx.x];
-    if (row >= 0) bulk_store(s_q[threadIdx.x] + row * cols, smem_u32(s_qrow), (uint32_t)cols);
+    if (row >= 0) {
+      const int rank = s_rank[threadIdx.x];
+      bulk_store(reinterpret_cast<uint8_t*>(peer_q[rank]) + row * cols, smem_u32(s_qrow), (uint32_t)cols);
+      bulk_store(reinterpret_cast<uint8_t*>(peer_rec[rank]) + row * rec_pitch, smem_u32(s_rec + threadIdx.x * rec_pitch),
+                 (uint32_t)rec_pitch);
+    }
     bulk_commit();
-    bulk_wait_read0();  // the shared-memory row must outlive the copy's reads
+    bulk_wait_read0();  // shared memory must outlive the copies' reads
+  }
+  (void)sf_cols;
+}
+
+// Receive side of the peer dispatch, after the ranks' barrier: records -> scales in the swizzled
+// 128x4 layout, gate probabilities and return addresses of the first m_rows rows.  A record that no
+// sender wrote still holds the reset pattern (all bits set): return address -1, the row is padding.
+__global__ void __launch_bounds__(256)
+    unpack_dispatch_records_kernel(const uint8_t* __restrict__ rec, int64_t m_rows, int sf_cols, int rec_pitch, int rest_k,
+                                   uint8_t* __restrict__ sfa, float* __restrict__ prob, int32_t* __restrict__ row_map) {
+  const int words = (sf_cols + 3) / 4;  // 4 scale bytes = 4 consecutive bytes of the swizzled layout
+  const int64_t total = m_rows * (words + 1);
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = i / (words + 1);
+    const int w = (int)(i - row * (words + 1));
+    const uint8_t* r = rec + row * rec_pitch;
+    if (w == words) {
+      const int32_t ret = *reinterpret_cast<const int32_t*>(r + rec_pitch - 4);
+      row_map[row] = ret;
+      prob[row] = ret < 0 ? 0.f : *reinterpret_cast<const float*>(r + rec_pitch - 8);
+    } else if (4 * w + 4 <= sf_cols) {
+      *reinterpret_cast<uint32_t*>(sfa + sf_offset(row, 4 * w, rest_k)) = *reinterpret_cast<const uint32_t*>(r + 4 * w);
+    } else {
+      for (int kb = 4 * w; kb < sf_cols; ++kb) sfa[sf_offset(row, kb, rest_k)] = r[kb];
+    }
   }
 }
 
@@ -382,27 +403,45 @@ int b200moe_dispatch_quantize(const void* x, const int32_t* send_pos, const floa
   return B200MOE_OK;
 }
 
+int b200moe_dispatch_record_pitch(int64_t cols) { return (int)(((cols / 32 + 8) + 15) / 16 * 16); }
+
 int b200moe_dispatch_quantize_peer(const void* x, const int32_t* expert_ids, const int32_t* local_row, const int32_t* delta,
                                    const float* topk_prob, int64_t num_tokens, int32_t topk, int64_t cols,
                                    int32_t experts_per_rank, int32_t num_ranks, int32_t my_rank, int64_t slot_capacity,
-                                   int64_t row_capacity, const int64_t* peer_q, const int64_t* peer_sf,
-                                   const int64_t* peer_prob, const int64_t* peer_map, void* stream) {
+                                   int64_t row_capacity, const int64_t* peer_q, const int64_t* peer_rec, void* stream) {
   using namespace b200moe;
   if (num_tokens == 0) return B200MOE_OK;
-  if (!x || !expert_ids || !local_row || !delta || !peer_q || !peer_sf || !peer_prob || !peer_map)
+  if (!x || !expert_ids || !local_row || !delta || !peer_q || !peer_rec)
     return fail(B200MOE_E_NULL, "dispatch_quantize_peer: null pointer");
-  // whole warps only (the scale word is assembled by full-mask shuffles): 32 lanes x 8 columns
-  if (cols <= 0 || cols % 256 != 0 || topk <= 0 || topk > 16 || num_tokens < 0 || num_tokens > 0x7fffffffll)
-    return fail(B200MOE_E_SHAPE, "dispatch_quantize_peer: cols must be a positive multiple of 256 and topk in [1, 16]");
+  if (cols <= 0 || cols % 32 != 0 || topk <= 0 || topk > 16 || num_tokens < 0 || num_tokens > 0x7fffffffll)
+    return fail(B200MOE_E_SHAPE, "dispatch_quantize_peer: cols must be a positive multiple of 32 and topk in [1, 16]");
   if (experts_per_rank <= 0 || num_ranks <= 0 || my_rank < 0 || my_rank >= num_ranks || slot_capacity < num_tokens * topk ||
       (int64_t)num_ranks * slot_capacity > 0x7fffffffll || row_capacity <= 0)
     return fail(B200MOE_E_SHAPE, "dispatch_quantize_peer: bad rank layout or capacities");
   if ((uintptr_t)x & 15) return fail(B200MOE_E_ALIGN, "dispatch_quantize_peer: 16-byte alignment required");
-  const int rest_k = (int)((cols / 32 + 3) / 4);
-  if (cols > 48 * 1024) return fail(B200MOE_E_SHAPE, "dispatch_quantize_peer: a row must fit 48 KiB of shared memory");
-  dispatch_quantize_peer_kernel<<<(unsigned)num_tokens, 128, (size_t)cols, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)x, expert_ids, local_row, delta, topk_prob, topk, (int)cols, rest_k, experts_per_rank, num_ranks,
-      my_rank, slot_capacity, row_capacity, peer_q, peer_sf, peer_prob, peer_map);
+  const int rec_pitch = b200moe_dispatch_record_pitch(cols);
+  const size_t smem = (size_t)cols + (size_t)topk * rec_pitch;
+  if (smem > 48 * 1024) return fail(B200MOE_E_SHAPE, "dispatch_quantize_peer: a row and its records must fit 48 KiB of shared memory");
+  dispatch_quantize_peer_kernel<<<(unsigned)num_tokens, 128, smem, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)x, expert_ids, local_row, delta, topk_prob, topk, (int)cols, rec_pitch, experts_per_rank, num_ranks,
+      my_rank, slot_capacity, row_capacity, peer_q, peer_rec);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200MOE_OK;
+}
+
+int b200moe_unpack_dispatch_records(const void* rec, int64_t m_rows, int64_t cols, void* sfa, float* prob, int32_t* row_map,
+                                    void* stream) {
+  using namespace b200moe;
+  if (m_rows == 0) return B200MOE_OK;
+  if (!rec || !sfa || !prob || !row_map) return fail(B200MOE_E_NULL, "unpack_dispatch_records: null pointer");
+  if (cols <= 0 || cols % 32 != 0 || m_rows < 0 || m_rows > 0x7fffffffll)
+    return fail(B200MOE_E_SHAPE, "unpack_dispatch_records: cols must be a positive multiple of 32");
+  const int sf_cols = (int)(cols / 32);
+  const int rest_k = (sf_cols + 3) / 4;
+  const int64_t total = m_rows * ((sf_cols + 3) / 4 + 1);
+  const unsigned blocks = (unsigned)std::min<int64_t>((total + 255) / 256, 148 * 32);
+  unpack_dispatch_records_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(
+      (const uint8_t*)rec, m_rows, sf_cols, b200moe_dispatch_record_pitch(cols), rest_k, (uint8_t*)sfa, prob, row_map);
   B200_CUDA_CHECK(cudaGetLastError());
   return B200MOE_OK;
 }

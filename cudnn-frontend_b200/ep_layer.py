@@ -242,14 +242,21 @@ class ExpertParallelMoE:
         cap = ((cap + 127) // 128) * 128
         h = self.hidden
         rest_k = (h // 32 + 3) // 4
+        from . import moe
+
+        pitch = moe.dispatch_record_pitch(h)
         bufs = {
-            "q": PeerBuffer(cap * h, self.group),
-            "sf": PeerBuffer((cap // 128) * rest_k * 512, self.group),
-            "prob": PeerBuffer(cap * 4, self.group),
-            "map": PeerBuffer(cap * 4, self.group),
-            "back": PeerBuffer(slots * h * 2, self.group),
+            "q": PeerBuffer(cap * h, self.group),  # E4M3 rows of this rank's expert groups
+            "rec": PeerBuffer(cap * pitch, self.group),  # per row: scales, gate probability, return address
+            "back": PeerBuffer(slots * h * 2, self.group),  # result rows, slot order
         }
-        self._peer = dict(bufs=bufs, cap=cap, slots=slots, identity=torch.arange(slots, dtype=torch.int32, device=self.w1.device))
+        dev = self.w1.device
+        local = {
+            "sf": torch.empty((cap // 128) * rest_k * 512, dtype=torch.uint8, device=dev),
+            "prob": torch.empty(cap, dtype=torch.float32, device=dev),
+            "map": torch.empty(cap, dtype=torch.int32, device=dev),
+        }
+        self._peer = dict(bufs=bufs, local=local, cap=cap, slots=slots, pitch=pitch, identity=torch.arange(slots, dtype=torch.int32, device=self.w1.device))
         self._peer_key = key
         return self._peer
 
@@ -298,7 +305,7 @@ class ExpertParallelMoE:
 
         ids = topk_ids.contiguous()
         counts, _, local_row = moe.route(ids.view(-1), self.num_experts, 1)
-        bufs["map"].view(torch.int32, (cap,)).fill_(-1)  # padding rows return nowhere
+        bufs["rec"].local.fill_(0xFF)  # a record nobody writes reads as "padding row, returns nowhere"
         if g > 1:
             counts_all = torch.empty((g, self.num_experts), dtype=torch.int32, device=dev)
             dist.all_gather_into_tensor(counts_all, counts, group=self.group)
@@ -316,18 +323,20 @@ class ExpertParallelMoE:
                 raise RuntimeError(f"a rank would receive {max(m_all)} padded rows from {slots} slots per rank")
             peer = self._peer_setup(t, k, 1.25 * max(m_all) / slots)
             bufs, cap = peer["bufs"], peer["cap"]
-            bufs["map"].view(torch.int32, (cap,)).fill_(-1)
+            bufs["rec"].local.fill_(0xFF)
             self._rank_barrier()
         # (otherwise the all-gather above already ordered this step's stores behind every rank's map reset)
         moe.dispatch_quantize_peer(x, ids, local_row, plan.delta, topk_prob.reshape(t * k).contiguous(), self.e_local, g, rank,
-                                   slots, cap, bufs["q"].ptrs_dev, bufs["sf"].ptrs_dev, bufs["prob"].ptrs_dev, bufs["map"].ptrs_dev)  # fmt: skip
+                                   slots, cap, bufs["q"].ptrs_dev, bufs["rec"].ptrs_dev)  # fmt: skip
         self._rank_barrier()
         if m > 0:
+            loc = peer["local"]
+            moe.unpack_dispatch_records(bufs["rec"].local, m, h, loc["sf"], loc["prob"], loc["map"])
             a = torch.as_strided(bufs["q"].view(torch.float8_e4m3fn, (m, h)), (m, h, 1), (h, 1, m * h))
             shape, stride = ops.sf_shape_stride(m, h, 1)
-            sfa = torch.as_strided(bufs["sf"].local.view(torch.float8_e8m0fnu), shape, stride)
-            prob3 = bufs["prob"].view(torch.float32, (m,)).view(m, 1, 1)
-            row_map = bufs["map"].view(torch.int32, (m,))
+            sfa = torch.as_strided(loc["sf"].view(torch.float8_e8m0fnu), shape, stride)
+            prob3 = loc["prob"][:m].view(m, 1, 1)
+            row_map = loc["map"][:m]
             back_local = bufs["back"].view(torch.bfloat16, (slots, h))
             h8 = torch.empty((m, self.inter, 1), dtype=torch.float8_e4m3fn, device=dev)
             sfh = ops.empty_sf(m, self.inter, 1, device=dev)

@@ -125,12 +125,17 @@ def zero_pad_rows(buf: torch.Tensor, counts: torch.Tensor, padded_offsets: torch
     _lib.check(rc)
 
 
+def dispatch_record_pitch(cols: int) -> int:
+    """Bytes of one dispatch record (scales + gate probability + return address) for rows of ``cols``."""
+    return int(_lib.load().b200moe_dispatch_record_pitch(cols))
+
+
 def dispatch_quantize_peer(x: torch.Tensor, topk_ids: torch.Tensor, local_row: torch.Tensor, delta: torch.Tensor,
                            topk_prob: Optional[torch.Tensor], experts_per_rank: int, num_ranks: int, my_rank: int,
-                           slot_capacity: int, row_capacity: int, peer_q: torch.Tensor, peer_sf: torch.Tensor,
-                           peer_prob: torch.Tensor, peer_map: torch.Tensor, stream=None) -> None:  # fmt: skip
+                           slot_capacity: int, row_capacity: int, peer_q: torch.Tensor, peer_rec: torch.Tensor, stream=None) -> None:  # fmt: skip
     """Fused quantise + dispatch over peer memory: token rows of ``x [T, H]`` are quantised to MXFP8 and
-    stored straight into the expert-grouped GEMM operand of the rank that owns each slot's expert
+    stored straight into the expert-grouped GEMM operand of the rank that owns each slot's expert,
+    each with a record of its scales, gate probability and return address
     (see ``b200moe_dispatch_quantize_peer`` in include/b200moe.h).  ``peer_*`` are int64 device tensors
     of ``num_ranks`` base addresses."""
     if x.dtype != torch.bfloat16 or not x.is_contiguous():
@@ -144,7 +149,17 @@ def dispatch_quantize_peer(x: torch.Tensor, topk_ids: torch.Tensor, local_row: t
         rc = _lib.load().b200moe_dispatch_quantize_peer(
             x.data_ptr(), topk_ids.data_ptr(), local_row.data_ptr(), delta.data_ptr(),
             None if topk_prob is None else topk_prob.data_ptr(), t, k, h, experts_per_rank, num_ranks, my_rank, slot_capacity,
-            row_capacity, peer_q.data_ptr(), peer_sf.data_ptr(), peer_prob.data_ptr(), peer_map.data_ptr(), _stream_ptr(stream))  # fmt: skip
+            row_capacity, peer_q.data_ptr(), peer_rec.data_ptr(), _stream_ptr(stream))  # fmt: skip
+    _lib.check(rc)
+
+
+def unpack_dispatch_records(rec: torch.Tensor, m_rows: int, cols: int, sfa: torch.Tensor, prob: torch.Tensor, row_map: torch.Tensor,
+                            stream=None) -> None:  # fmt: skip
+    """Records of the first ``m_rows`` received rows -> swizzled scale tensor, gate probabilities and
+    FC2 return addresses (``b200moe_unpack_dispatch_records``)."""
+    with torch.cuda.device(rec.device):
+        rc = _lib.load().b200moe_unpack_dispatch_records(rec.data_ptr(), m_rows, cols, sfa.data_ptr(), prob.data_ptr(),
+                                                         row_map.data_ptr(), _stream_ptr(stream))  # fmt: skip
     _lib.check(rc)
 
 

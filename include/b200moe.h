@@ -203,14 +203,18 @@ int b200moe_combine_rows(const void* in, const int32_t* dst_row, int64_t num_tok
  * b200moe_dispatch_quantize_peer: for token t the bf16 row x[t, :] is read once and quantised to
  *   MXFP8; for every slot j < topk with expert e = expert_ids[t*topk + j] the row goes to rank
  *   e / experts_per_rank, at row  r = delta[e] + local_row[t*topk + j]  of that rank's expert-grouped
- *   GEMM operand: E4M3 bytes to peer_q[rank] + r*cols, E8M0 scales into the swizzled 128x4 layout at
- *   peer_sf[rank], the gate probability to peer_prob[rank][r] and the return address
- *   my_rank*slot_capacity + t*topk + j to peer_map[rank][r] (the d_row_map of that rank's FC2).
+ *   GEMM operand: E4M3 bytes to peer_q[rank] + r*cols as one bulk copy, and one record of
+ *   b200moe_dispatch_record_pitch(cols) bytes to peer_rec[rank] + r*pitch as a second one:
+ *   [cols/32 E8M0 bytes | padding | f32 gate probability | i32 return address
+ *   my_rank*slot_capacity + t*topk + j].  The destination resets its records to all-ones before the
+ *   step (return address -1 = padding row) and, after all ranks finished the kernel,
+ *   b200moe_unpack_dispatch_records turns the first m_rows records into the swizzled 128x4 scale
+ *   tensor, the prob vector and the d_row_map of its FC2.
  *   local_row = b200moe_route(..., m_aligned = 1) of this rank's rows; delta[e] = first row this rank
  *   owns inside expert e's group on the destination, minus this rank's compact start of e.
  *   peer_* are device arrays of G addresses.  Rows r outside [0, row_capacity) are not written and
  *   raise device status 301.  The caller orders the ranks (all ranks finish this kernel, then a
- *   barrier, then the GEMMs) -- the kernel itself never waits for a peer.
+ *   barrier, then unpack and the GEMMs) -- the kernel itself never waits for a peer.
  *
  * b200moe_peer_alloc / _open / _close / _free: device buffers that other processes of this node can
  *   map (CUDA IPC).  alloc returns the pointer and a 64-byte handle to hand to the peers; open maps a
@@ -221,8 +225,10 @@ int b200moe_dispatch_quantize_peer(const void* x, const int32_t* expert_ids, con
                                    int32_t topk, int64_t cols, int32_t experts_per_rank,
                                    int32_t num_ranks, int32_t my_rank, int64_t slot_capacity,
                                    int64_t row_capacity, const int64_t* peer_q,
-                                   const int64_t* peer_sf, const int64_t* peer_prob,
-                                   const int64_t* peer_map, void* stream);
+                                   const int64_t* peer_rec, void* stream);
+int b200moe_dispatch_record_pitch(int64_t cols);
+int b200moe_unpack_dispatch_records(const void* rec, int64_t m_rows, int64_t cols, void* sfa,
+                                    float* prob, int32_t* row_map, void* stream);
 int b200moe_peer_alloc(int64_t bytes, void** ptr, void* handle64);
 int b200moe_peer_open(const void* handle64, void** ptr);
 int b200moe_peer_close(void* ptr);
