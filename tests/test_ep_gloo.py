@@ -114,3 +114,79 @@ def test_plan_rejects_indivisible_expert_count():
 
         with mock.patch("torch.distributed.get_world_size", return_value=2):
             plan_dispatch(torch.zeros((4, 1), dtype=torch.int32), 7, FakeGroup(), 128)
+
+
+def _peer_worker(rank, world, port, ret):
+    """The peer-memory path's index logic on CPU ranks: peer stores are emulated by exchanging
+    (destination rank, row, payload) lists; everything else is the code the CUDA path runs."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from cudnn_frontend_b200.ep_layer import plan_fused
+        from oracle import mxfp8_oracle as orc
+
+        experts, t, k, h, m_aligned = 8, 40 + 9 * rank, 2, 8, 16
+        e_local = experts // world
+        g = torch.Generator().manual_seed(11 + rank)
+        ids = torch.stack([torch.randperm(experts, generator=g)[:k] for _ in range(t)]).to(torch.int32)
+        ids[ids == 5] = 6  # an expert nobody uses
+        x = torch.randn(t, h, generator=g)
+        p = torch.rand(t, k, generator=g)
+        slots = 64 * k  # slot capacity, the same on every rank
+        counts = torch.bincount(ids.reshape(-1).long(), minlength=experts).to(torch.int32)
+        gathered = [torch.empty_like(counts) for _ in range(world)]
+        dist.all_gather(gathered, counts)
+        plan = plan_fused(torch.stack(gathered), rank, m_aligned)
+        # compact local rows = stable grouping of my slots by expert (what b200moe_route(m_aligned=1) returns)
+        _, _, local_row = orc.route_rows(ids.reshape(-1).numpy(), experts, 1)
+        # "peer stores": (destination rank, destination row, payload row, prob, return address)
+        msgs = []
+        for slot in range(t * k):
+            e = int(ids.reshape(-1)[slot])
+            msgs.append((e // e_local, int(plan.delta[e]) + int(local_row[slot]), x[slot // k].clone(), float(p.reshape(-1)[slot]),
+                         rank * slots + slot, e))
+        everyone = [None] * world
+        dist.all_gather_object(everyone, msgs)
+        m = int(plan.m_rows_all[rank])
+        assert m == int(plan.padded_offsets[-1]) and m % m_aligned == 0
+        xg, pg = torch.zeros(m, h), torch.zeros(m)
+        row_map = torch.full((m,), -1, dtype=torch.int64)
+        expert_of_row = torch.full((m,), -1, dtype=torch.int64)
+        for src in everyone:
+            for d, row, payload, prob, ret_addr, e in src:
+                if d != rank:
+                    continue
+                assert 0 <= row < m and row_map[row] == -1  # inside my buffer, written once
+                xg[row], pg[row], row_map[row], expert_of_row[row] = payload, prob, ret_addr, e
+        assert int((row_map >= 0).sum()) == int(plan.rows_all[rank])
+        start = 0
+        for el in range(e_local):  # every group holds its expert's rows first, then padding
+            end = int(plan.padded_offsets[el])
+            inside = expert_of_row[start:end]
+            cnt = int((inside >= 0).sum())
+            assert (inside[:cnt] == rank * e_local + el).all() and (inside[cnt:] == -1).all()
+            start = end
+        # stand-in expert, then "peer stores" of the result rows to (source rank, slot)
+        yg = xg * (expert_of_row.clamp(min=0).float()[:, None] + 1) * pg[:, None]
+        returns = [(int(a) // slots, int(a) % slots, yg[r].clone()) for r, a in enumerate(row_map.tolist()) if a >= 0]
+        everyone = [None] * world
+        dist.all_gather_object(everyone, returns)
+        back = torch.zeros(slots, h)
+        for src in everyone:
+            for d, slot, row in src:
+                if d == rank:
+                    back[slot] = row
+        out = back[: t * k].view(t, k, h).sum(1)
+        ref = (x[:, None, :] * (ids.float()[:, :, None] + 1) * p[:, :, None]).sum(1)
+        ret[rank] = bool(torch.allclose(out, ref, rtol=1e-5, atol=1e-5))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_peer_memory_plan_round_trip_world_size_2():
+    world = 2
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_peer_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
+    assert all(ret.get(r) for r in range(world)), dict(ret)
