@@ -1,8 +1,10 @@
 """Multi-GPU leg of the benchmark: the expert-parallel MoE layer, one process per GPU.
 
 Per rank: 65536 tokens (bf16 ~ N(0,1), hidden 7168), top-8 Zipf(1.2) routing over 256 experts
-sharded 256/G per rank, MXFP8 weights ~ N(0, 0.02).  One step = the whole layer (dispatch
-all-to-all, quantise, FC1 + SwiGLU, FC2 with gating, combine all-to-all).  Weak scaling: tokens
+sharded 256/G per rank, MXFP8 weights ~ N(0, 0.02).  One step = the whole layer (quantise and
+dispatch to the owning ranks, FC1 + SwiGLU, FC2 with gating, return of the result rows, top-k sum);
+rows cross NVLink by peer stores from the kernels (default) or by NCCL all-to-all
+(B200MOE_EP_PATH=nccl).  Weak scaling: tokens
 per GPU are fixed.  FLOPs = 2 * routed rows * (N1 K1 + N2 K2) summed over ranks, true rows only.
 """
 
@@ -118,18 +120,38 @@ def run(args, tokens_per_gpu: int = 65536):
     value = flops / (ms * 1e-3) / 1e12
     finite = bool(torch.isfinite(y.float()).all().item())
 
-    # end to end: tokens, expert ids and gate probabilities start in pinned host memory every step,
-    # and a checksum of the layer's output is read back to the host
+    # end to end: tokens, expert ids and gate probabilities start in pinned host memory every step and a
+    # checksum of the layer's output is read back to the host; the copy of step i + 1 runs on a copy
+    # stream while step i computes (two sets of device input buffers, events in both directions)
     x_h, ids_h, prob_h = x.cpu().pin_memory(), ids.cpu().pin_memory(), prob.cpu().pin_memory()
-    x_d, ids_d, prob_d = torch.empty_like(x), torch.empty_like(ids), torch.empty_like(prob)
+    in_bufs = [(torch.empty_like(x), torch.empty_like(ids), torch.empty_like(prob)) for _ in range(2)]
     check_h = torch.empty(1, dtype=torch.float32).pin_memory()
+    copy_stream = torch.cuda.Stream()
+    copied = [torch.cuda.Event() for _ in range(2)]
+    consumed = [torch.cuda.Event() for _ in range(2)]
+    step_no = [0]
+
+    def start_copy(i):
+        x_d, ids_d, prob_d = in_bufs[i % 2]
+        with torch.cuda.stream(copy_stream):
+            if i >= 2:
+                copy_stream.wait_event(consumed[i % 2])
+            x_d.copy_(x_h, non_blocking=True)
+            ids_d.copy_(ids_h, non_blocking=True)
+            prob_d.copy_(prob_h, non_blocking=True)
+            copied[i % 2].record(copy_stream)
 
     def e2e_step():
-        x_d.copy_(x_h, non_blocking=True)
-        ids_d.copy_(ids_h, non_blocking=True)
-        prob_d.copy_(prob_h, non_blocking=True)
+        i = step_no[0]
+        if i == 0:
+            start_copy(0)
+        start_copy(i + 1)
+        x_d, ids_d, prob_d = in_bufs[i % 2]
+        stream.wait_event(copied[i % 2])
         out = run_layer(x_d, ids_d, prob_d)
+        consumed[i % 2].record(stream)
         check_h.copy_(out.float().abs().max().view(1), non_blocking=True)
+        step_no[0] = i + 1
 
     e2e_steps = max(args.steps // 4, 3)
     for _ in range(2):
@@ -162,7 +184,7 @@ def run(args, tokens_per_gpu: int = 65536):
             "dtype": "fp8_e4m3 x ue8m0 block scales, f32 accumulate",
             "data": "synthetic",
             "config": {
-                "workload": f"expert-parallel MoE layer: E=256 sharded {e_local}/GPU, hidden 7168, intermediate 2048, {tokens_per_gpu} tokens/GPU top-8 Zipf(1.2); dispatch all-to-all + quantise + FC1 + FC2 + combine all-to-all",
+                "workload": f"expert-parallel MoE layer: E=256 sharded {e_local}/GPU, hidden 7168, intermediate 2048, {tokens_per_gpu} tokens/GPU top-8 Zipf(1.2); one step = quantise + dispatch to the owning ranks, FC1 + SwiGLU, FC2 with gating, return + top-k sum",
                 "parallelism": f"ep{world}",
                 "data_path": "peer stores over NVLink from the quantise+dispatch kernel and from the FC2 epilogue; no all-to-all of rows" if path == "peer" else f"NCCL all-to-all, {micro} micro-batch(es)",
                 "l2": "inputs larger than L2 (0.94 GB tokens, 11 GB local weights), no flush",
@@ -172,7 +194,8 @@ def run(args, tokens_per_gpu: int = 65536):
             },
             "gpu_launches": args.steps * (7 if path == "peer" else 5 * micro),
             "e2e": {"value": flops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
-                    "ms_per_step": ms_e2e, "note": "per rank: bytes are one rank's; the value is the aggregate over ranks"},
+                    "ms_per_step": ms_e2e,
+                    "note": "bytes are one rank's, the value is the aggregate over ranks; the copy of step i + 1 overlaps step i"},
             "roofline": None,
             "cpu_baseline": None,
         }
