@@ -269,6 +269,72 @@ def run_case_fc2(name, cfg, out):
         )
 
 
+def run_case_glu(name, cfg, out):
+    """Unified FC1 (grouped_gemm_glu): GeGLU + fused bf16 bias, dense weights, full output set."""
+    import cuda.bindings.driver as cuda
+    from cudnn.grouped_gemm.grouped_gemm_glu.api import grouped_gemm_glu_wrapper_sm100 as ref_glu  # the overlay
+
+    import cudnn_frontend_b200 as ours
+    from cudnn_frontend_b200 import synthetic
+
+    p = synthetic.make_problem(cfg, "cuda", seed=9, m_aligned=256)
+    n, e = cfg["n"], cfg["experts"]
+    norm = torch.tensor([1.0], dtype=torch.float32, device="cuda")
+    stream = cuda.CUstream(torch.cuda.current_stream().cuda_stream)
+    g = torch.Generator(device="cuda").manual_seed(4)
+    bias = torch.empty((e, n), dtype=torch.float32, device="cuda").uniform_(-2.0, 2.0, generator=g).to(torch.bfloat16).t()
+    res = {"case": name, "op": "glu", "cfg": cfg, "m_rows": p["m_rows"], "flops": p["flops"]}
+    m = p["m_rows"]
+
+    def flat(t):
+        t = t.view(torch.uint8)
+        return torch.as_strided(t, (t.numel(),), (1,))
+
+    saved = {}
+    for act in ("geglu", "swiglu"):
+        kw = dict(b_tensor=p["b"], sfb_tensor=p["sfb"], bias_tensor=bias, norm_const_tensor=norm, prob_tensor=p["prob"],
+                  d_dtype=torch.float8_e4m3fn, sf_vec_size=32, m_aligned=256, act_func=act)  # fmt: skip
+        r_ref = ref_glu(p["a"], p["sfa"], p["padded_offsets"], p["alpha"], mma_tiler_mn=(256, 256), current_stream=stream, **kw)
+        torch.cuda.synchronize()
+        r_own = ours.grouped_gemm_glu_wrapper_sm100(p["a"], p["sfa"], p["padded_offsets"], p["alpha"], **kw)
+        torch.cuda.synchronize()
+        res[f"{act}_c_equal_frac"] = float((r_ref["c_tensor"][:m] == r_own["c_tensor"][:m]).float().mean())
+        u = ulp(r_ref["d_tensor"][:m].view(torch.uint8), r_own["d_tensor"][:m].view(torch.uint8))
+        res[f"{act}_d_equal_frac"] = float((u == 0).float().mean())
+        uc = ulp(r_ref["d_col_tensor"][:m].view(torch.uint8), r_own["d_col_tensor"][:m].view(torch.uint8))
+        res[f"{act}_d_col_equal_frac"] = float((uc == 0).float().mean())
+        res[f"{act}_sfd_row_bytes_equal_frac"] = float((flat(r_ref["sfd_row_tensor"]) == flat(r_own["sfd_row_tensor"])).float().mean())
+        res[f"{act}_sfd_col_bytes_equal_frac"] = float((flat(r_ref["sfd_col_tensor"]) == flat(r_own["sfd_col_tensor"])).float().mean())
+        if act == "geglu":
+            saved = dict(
+                c=r_ref["c_tensor"][:, :, 0].view(torch.int16).cpu().numpy(),
+                d=r_ref["d_tensor"][:m, :, 0].view(torch.uint8).cpu().numpy(),
+                d_col=r_ref["d_col_tensor"][:m, :, 0].view(torch.uint8).cpu().numpy(),
+                sfd_row=flat(r_ref["sfd_row_tensor"]).cpu().numpy(),
+                sfd_col=flat(r_ref["sfd_col_tensor"]).cpu().numpy(),
+            )
+            if not PROFILE_ONLY and name != "glu_tiny":
+                il_ref, il_own = timed_interleaved(
+                    lambda: ref_glu(p["a"], p["sfa"], p["padded_offsets"], p["alpha"], mma_tiler_mn=(256, 256), current_stream=stream, **kw),
+                    lambda: ours.grouped_gemm_glu_wrapper_sm100(p["a"], p["sfa"], p["padded_offsets"], p["alpha"], **kw))
+                res["ref_ms_interleaved"], res["own_ms_interleaved"] = il_ref, il_own
+                res["own_over_ref_interleaved"] = il_ref / il_own
+    out.append(res)
+    print(json.dumps(res), flush=True)
+    if name == "glu_tiny":
+        np.savez_compressed(
+            os.path.join(ROOT, "gpurun_out", "reference_kernel_glu_golden.npz"),
+            a=p["a"][:, :, 0].view(torch.uint8).cpu().numpy(),
+            b=p["b"].permute(2, 0, 1).contiguous().view(torch.uint8).cpu().numpy(),
+            sfa=flat(p["sfa"]).cpu().numpy(),
+            sfb=flat(p["sfb"]).cpu().numpy(),
+            offsets=p["padded_offsets"].cpu().numpy(),
+            prob=p["prob"].view(-1).cpu().numpy(),
+            bias=bias.t().contiguous().view(torch.int16).cpu().numpy(),  # [E, N] bf16 bits
+            **saved,
+        )
+
+
 PROFILE_ONLY = False
 OWN_FIRST = False
 
@@ -286,6 +352,10 @@ CASES = {
     "c4": dict(experts=256, k=2048, n=7168, tokens=8192, topk=8, routing="zipf"),
 }
 FC2_CASES = ("fc2_tiny", "fc2_mixtral", "c4")
+# unified GLU API (GeGLU + fused bias): glu_tiny records a fixture, glu_mid compares speed
+CASES["glu_tiny"] = dict(experts=2, k=128, n=128, tokens=128, topk=2, routing="uniform")
+CASES["glu_mid"] = dict(experts=8, k=4096, n=7168, tokens=4096, topk=2, routing="uniform")
+GLU_CASES = ("glu_tiny", "glu_mid")
 
 
 def main():
@@ -301,7 +371,7 @@ def main():
     out = []
     for name in args.cases.split(","):
         try:
-            (run_case_fc2 if name in FC2_CASES else run_case)(name, CASES[name], out)
+            (run_case_glu if name in GLU_CASES else run_case_fc2 if name in FC2_CASES else run_case)(name, CASES[name], out)
         except Exception as exc:  # keep going: a JIT failure of one case is a result too
             out.append({"case": name, "error": f"{type(exc).__name__}: {exc}"})
             traceback.print_exc()

@@ -6,6 +6,7 @@ Public names mirror what the reference exports from its package root through laz
     GroupedGemmSwigluSm100, grouped_gemm_swiglu_wrapper_sm100
     GroupedGemmQuantSm100, grouped_gemm_quant_wrapper_sm100
     DiscreteGroupedGemmSwigluSm100, discrete_grouped_gemm_swiglu_wrapper_sm100
+    GroupedGemmGluSm100, grouped_gemm_glu_wrapper_sm100      (unified FC1: swiglu / geglu, bias)
 
 plus what the reference does not have: ``quantize_mxfp8`` (activation quantiser), the routing
 helpers of ``moe`` and the expert-parallel layer ``ExpertParallelMoE``.
@@ -20,6 +21,8 @@ _LAZY = {
     "grouped_gemm_quant_wrapper_sm100": "grouped_gemm_quant",
     "DiscreteGroupedGemmSwigluSm100": "discrete_grouped_gemm_swiglu",
     "discrete_grouped_gemm_swiglu_wrapper_sm100": "discrete_grouped_gemm_swiglu",
+    "GroupedGemmGluSm100": "grouped_gemm_glu",
+    "grouped_gemm_glu_wrapper_sm100": "grouped_gemm_glu",
     "TupleDict": "api_base",
     "quantize_mxfp8": "ops",
     "quantize_mxfp8_out": "ops",

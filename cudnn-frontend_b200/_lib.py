@@ -12,7 +12,8 @@ from ctypes import POINTER, Structure, c_char_p, c_float, c_int32, c_int64, c_vo
 from . import _build
 
 E_NULL, E_SHAPE, E_ALIGN, E_UNSUPPORTED, E_WORKSPACE, E_DEVICE = -1, -2, -3, -4, -5, -6
-DTYPE_BF16, DTYPE_E4M3 = 0, 1
+DTYPE_BF16, DTYPE_E4M3, DTYPE_F16, DTYPE_F32 = 0, 1, 2, 3
+ACT_SWIGLU, ACT_GEGLU = 0, 1
 FLAG_DISCRETE_COL_SFD = 1
 FLAG_TILE_SINGLE = 2
 FLAG_TILE_PAIR = 4
@@ -49,6 +50,9 @@ class GemmArgs(Structure):
         ("d_row_map", c_void_p),
         ("d_peer_ptrs", c_void_p),
         ("d_peer_slots", c_int64),
+        ("bias", c_void_p),
+        ("bias_dtype", c_int32),
+        ("act_func", c_int32),
     ]
 
 

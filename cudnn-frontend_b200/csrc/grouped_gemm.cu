@@ -128,6 +128,9 @@ struct GemmParams {
   int d_is_fp8;
   int discrete_col_sfd;
   int wide_stores;     // every output row segment of 32 bytes is 32-byte aligned
+  const void* bias;    // optional [E][N] (element (n, e) at e * N + n), added after alpha
+  int bias_dtype;      // B200MOE_DTYPE_BF16 / _F16 / _F32
+  int act_geglu;       // FC1: 0 = SwiGLU, 1 = GeGLU
   int raster_group_m;  // row tiles per raster group
 };
 
@@ -290,6 +293,35 @@ __device__ __forceinline__ uint32_t quant_col_block(uint8_t* dst, bool do_store,
   if (do_store)
     store_32B(dst, make_uint4(packed[0], packed[1], packed[2], packed[3]), make_uint4(packed[4], packed[5], packed[6], packed[7]), wide);
   return my_sf;
+}
+
+// Eight consecutive bias values (same for every row of the tile) as float32.
+__device__ __forceinline__ void load_bias8(const void* bias, int dtype, int64_t idx, float* out) {
+  if (dtype == B200MOE_DTYPE_F32) {
+    const float4 a = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(bias) + idx));
+    const float4 b = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(bias) + idx) + 1);
+    out[0] = a.x; out[1] = a.y; out[2] = a.z; out[3] = a.w;
+    out[4] = b.x; out[5] = b.y; out[6] = b.z; out[7] = b.w;
+  } else {
+    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(bias) + idx));
+    if (dtype == B200MOE_DTYPE_BF16) {
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(h[j]);
+        out[2 * j] = f.x;
+        out[2 * j + 1] = f.y;
+      }
+    } else {
+      const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __half22float2(h[j]);
+        out[2 * j] = f.x;
+        out[2 * j + 1] = f.y;
+      }
+    }
+  }
 }
 
 // ---------------------------------------------------------------------------------------
@@ -637,17 +669,46 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           const int cn = n0 + col;          // column of C
           const int dn = (n0 >> 1) + half * 64 + pp * 32;  // column of D
           if (cn >= p.n) continue;
+          if (p.bias) {
+            // C = alpha * acc + bias (one FMA, as the reference's kernel), gate and up alike
+            const int64_t b0 = (int64_t)tile.expert * p.n + cn;
 #pragma unroll
-          for (int j = 0; j < 32; ++j) { g[j] *= alpha; u[j] *= alpha; }
+            for (int j = 0; j < 32; j += 8) {
+              float bg[8], bu[8];
+              load_bias8(p.bias, p.bias_dtype, b0 + j, bg);
+              load_bias8(p.bias, p.bias_dtype, b0 + 32 + j, bu);
+#pragma unroll
+              for (int q = 0; q < 8; ++q) {
+                g[j + q] = fmaf(g[j + q], alpha, bg[q]);
+                u[j + q] = fmaf(u[j + q], alpha, bu[q]);
+              }
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) { g[j] *= alpha; u[j] *= alpha; }
+          }
           if (p.c && row_ok) {
             store_bf16x32(p.c + (int64_t)row * p.n + cn, g, wide);
             store_bf16x32(p.c + (int64_t)row * p.n + cn + 32, u, wide);
           }
+          if (p.act_geglu) {
+            // GeGLU of the reference: gate <= 7, -7 <= up <= 7 (after the C store),
+            // D = (up + 1) * gate * sigmoid(1.702 gate) * prob
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const float e = ex2_approx(g[j] * -1.4426950408889634f);
-            const float s = rcp_approx(1.0f + e);
-            g[j] = ((s * g[j]) * u[j]) * prob;
+            for (int j = 0; j < 32; ++j) {
+              const float gate = fminf(g[j], 7.0f);
+              const float up = fmaxf(fminf(u[j], 7.0f), -7.0f);
+              const float e = ex2_approx((gate * 1.702f) * -1.4426950408889634f);
+              const float s = rcp_approx(1.0f + e);
+              g[j] = ((s * gate) * (1.0f + up)) * prob;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float e = ex2_approx(g[j] * -1.4426950408889634f);
+              const float s = rcp_approx(1.0f + e);
+              g[j] = ((s * g[j]) * u[j]) * prob;
+            }
           }
           if (!p.d_is_fp8) {
             if (row_ok) {
@@ -708,8 +769,20 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           }
           const int dn = n0 + col;
           if (dn >= p.n) continue;
+          if (p.bias) {
+            // D = alpha * acc + bias * prob: the reference's fused form (prob scales the bias only)
+            const int64_t b0 = (int64_t)tile.expert * p.n + dn;
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = (v[j] * alpha) * prob;
+            for (int j = 0; j < 32; j += 8) {
+              float bv[8];
+              load_bias8(p.bias, p.bias_dtype, b0 + j, bv);
+#pragma unroll
+              for (int q = 0; q < 8; ++q) v[j + q] = fmaf(v[j + q], alpha, prob * bv[q]);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = (v[j] * alpha) * prob;
+          }
           if (!p.d_is_fp8) {
             if (row_ok) {
 #pragma unroll
@@ -995,6 +1068,14 @@ static int run_gemm(int epi, const b200moe_gemm_args* a, void* stream_v) {
   if (a->d_peer_ptrs && (!a->d_row_map || a->d_peer_slots <= 0))
     return fail(B200MOE_E_SHAPE, "%s: d_peer_ptrs needs d_row_map and a positive d_peer_slots", op);
   if (a->d_dtype != B200MOE_DTYPE_BF16 && !d_fp8) return fail(B200MOE_E_UNSUPPORTED, "%s: d_dtype %d", op, a->d_dtype);
+  if (a->act_func != B200MOE_ACT_SWIGLU && a->act_func != B200MOE_ACT_GEGLU)
+    return fail(B200MOE_E_UNSUPPORTED, "%s: act_func %d", op, a->act_func);
+  if (a->bias) {
+    if (a->bias_dtype != B200MOE_DTYPE_BF16 && a->bias_dtype != B200MOE_DTYPE_F16 && a->bias_dtype != B200MOE_DTYPE_F32)
+      return fail(B200MOE_E_UNSUPPORTED, "%s: bias_dtype %d", op, a->bias_dtype);
+    if ((uintptr_t)a->bias % 16 != 0 || a->n % 8 != 0)
+      return fail(B200MOE_E_ALIGN, "%s: bias must be 16-byte aligned and n a multiple of 8", op);
+  }
   if (d_fp8) {
     if (!a->sfd_row || !a->norm_const)
       return fail(B200MOE_E_NULL, "%s: E4M3 output needs sfd_row and norm_const", op);
@@ -1019,6 +1100,9 @@ static int run_gemm(int epi, const b200moe_gemm_args* a, void* stream_v) {
   p.alpha = a->alpha;
   p.prob = a->prob;
   p.norm_const = a->norm_const;
+  p.bias = a->bias;
+  p.bias_dtype = a->bias_dtype;
+  p.act_geglu = (epi == EPI_FC1 && a->act_func == B200MOE_ACT_GEGLU) ? 1 : 0;
   p.d_row_map = a->d_row_map;
   p.d_peer_ptrs = a->d_row_map ? a->d_peer_ptrs : nullptr;
   p.d_peer_slots = a->d_peer_slots;
@@ -1213,6 +1297,6 @@ int b200moe_device_status(int clear) {
   return v;
 }
 
-int b200moe_abi_version(void) { return 2; }
+int b200moe_abi_version(void) { return 3; }
 
 }  // extern "C"

@@ -7,7 +7,8 @@ weight is its own ``(n, k)`` K-major allocation with its own 128x4 scale-factor 
 device addresses arrive as two 1-D int64 CUDA tensors that are only ever read on the device.
 ``execute`` allocates nothing (descriptor workspace is created in ``compile``).
 
-Not built (``NotImplementedError``): ``act_func="geglu"``, fused bias, N-major weights.
+``act_func="geglu"`` and a fused bias ``(n, l)`` (stride ``(1, n)``) are supported as in the reference's
+GLU kernel.  Not built (``NotImplementedError``): N-major weights.
 """
 
 from __future__ import annotations
@@ -143,8 +144,9 @@ class DiscreteGroupedGemmSwigluSm100(OperatorBase):
         if self.expert_cnt > 1024:
             raise ValueError(f"expert_cnt must be <= 1024, got {self.expert_cnt}")
 
-        self._not_implemented_error_if(self.act_func != "swiglu", "only act_func='swiglu' is built")
-        self._not_implemented_error_if(self.bias is not None, "fused bias is not built")
+        if self.bias is not None:
+            self._check_stride(self.bias, (1, n), "bias must have stride (1, n)")
+            self._check_dtype(self.bias, [torch.bfloat16, torch.float16], "bias")
         self._not_implemented_error_if(self.b_major != "k", "N-major B is not built; pass K-major weights")
         self._not_implemented_error_if(self.ab_dtype != torch.float8_e4m3fn, f"only MXFP8 E4M3 inputs are built, got {self.ab_dtype}")
         self._not_implemented_error_if(self.sf_dtype != torch.float8_e8m0fnu, f"only E8M0 scale factors are built, got {self.sf_dtype}")
@@ -190,8 +192,8 @@ class DiscreteGroupedGemmSwigluSm100(OperatorBase):
         tensor_m, k = a_tensor.shape[0], a_tensor.shape[1]
         if tensor_m == 0:
             return
-        if bias_tensor is not None:
-            raise NotImplementedError("fused bias is not built")
+        if (bias_tensor is not None) != (self.bias is not None):
+            raise ValueError("bias fusion is fixed at construction: pass bias_tensor exactly when sample_bias was given")
         _require_pointer_tensor(b_ptrs, "b_ptrs", self.expert_cnt)
         _require_pointer_tensor(sfb_ptrs, "sfb_ptrs", self.expert_cnt)
         fp8_out = d_tensor.dtype == torch.float8_e4m3fn
@@ -216,6 +218,8 @@ class DiscreteGroupedGemmSwigluSm100(OperatorBase):
             discrete_col_sfd=self.discrete_col_sfd,
             sm_margin=self.num_cluster_overlap_margin,
             tile_mode=pick_tile_mode(self.mma_tiler_mn, self.m_aligned),
+            bias=bias_tensor,
+            act_func=self.act_func,
             stream=current_stream,
         )
 

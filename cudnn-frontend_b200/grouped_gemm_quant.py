@@ -8,7 +8,7 @@ descriptors are built on the device from the pointer arrays into a workspace the
 allocates in ``compile()``, so ``execute()`` allocates nothing and never reads the pointers on
 the host.
 
-Not built (``NotImplementedError``): fused bias, N-major B (``b_major="n"``), inputs other than
+Not built (``NotImplementedError``): N-major B (``b_major="n"``), inputs other than
 E4M3 + E8M0/32, D other than bf16 / E4M3.  ``use_dynamic_sched`` is accepted and ignored: the
 tile schedule is static.
 """
@@ -194,7 +194,10 @@ class GroupedGemmQuantSm100(OperatorBase):
         if self.expert_cnt > 1024:
             raise ValueError(f"expert_cnt must be <= 1024, got {self.expert_cnt}")
 
-        self._not_implemented_error_if(self.bias is not None, "fused bias is not built")
+        if self.bias is not None:
+            # (n, l) with stride (1, n), as the reference demands
+            self._check_stride(self.bias, (1, n), "bias must have stride (1, n)")
+            self._check_dtype(self.bias, [torch.bfloat16, torch.float16, torch.float32], "bias")
         self._not_implemented_error_if(self.b_major != "k", "N-major B is not built; pass K-major weights")
         self._not_implemented_error_if(self.ab_dtype != torch.float8_e4m3fn, f"only MXFP8 E4M3 inputs are built, got {self.ab_dtype}")
         self._not_implemented_error_if(self.sf_dtype != torch.float8_e8m0fnu, f"only E8M0 scale factors are built, got {self.sf_dtype}")
@@ -252,8 +255,8 @@ class GroupedGemmQuantSm100(OperatorBase):
         tensor_m, k = a_tensor.shape[0], a_tensor.shape[1]
         if tensor_m == 0:
             return
-        if bias_tensor is not None:
-            raise NotImplementedError("fused bias is not built")
+        if (bias_tensor is not None) != (self.bias is not None):
+            raise ValueError("bias fusion is fixed at construction: pass bias_tensor exactly when sample_bias was given")
         if self.discrete:
             if b_ptrs is None or sfb_ptrs is None:
                 raise ValueError("discrete mode needs b_ptrs and sfb_ptrs")
@@ -289,6 +292,7 @@ class GroupedGemmQuantSm100(OperatorBase):
             d_row_map=d_row_map,
             d_peer_ptrs=d_peer_ptrs,
             d_peer_slots=d_peer_slots,
+            bias=bias_tensor,
             stream=current_stream,
         )
 

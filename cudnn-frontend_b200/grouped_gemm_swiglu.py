@@ -60,8 +60,15 @@ class GroupedGemmSwigluSm100(OperatorBase):
         vector_f32: bool = False,
         m_aligned: int = 256,
         discrete_col_sfd: bool = False,
+        sample_bias: Optional[torch.Tensor] = None,
+        act_func: str = "swiglu",
     ):
+        """The two trailing arguments are not in the reference's class of this name (its unified
+        successor ``GroupedGemmGluSm100`` has them): a fused bias ``(n, l)`` with stride ``(1, n)``
+        and ``act_func`` ``"swiglu"`` or ``"geglu"``."""
         super().__init__()
+        self.bias = TensorSpec.of(sample_bias, "sample_bias")
+        self.act_func = act_func
         self.a = TensorSpec.of(sample_a, "sample_a")
         self.b = TensorSpec.of(sample_b, "sample_b")
         self.c = TensorSpec.of(sample_c, "sample_c")
@@ -170,6 +177,11 @@ class GroupedGemmSwigluSm100(OperatorBase):
         self._not_implemented_error_if(not self.generate_sfd and self.d_dtype == torch.float8_e4m3fn, "E4M3 D needs sfd_row, sfd_col and norm_const")
         self._value_error_if(n % 64 != 0, f"n must be a multiple of 64 (32-column gate / up blocks), got {n}")
         self._value_error_if(self.generate_sfd and self.d_col is None, "sample_d_col is required when scale factors are generated")
+        self._value_error_if(self.act_func not in ("swiglu", "geglu"), f"act_func must be 'swiglu' or 'geglu', got {self.act_func}")
+        if self.bias is not None:
+            self._check_shape(self.bias, (n, l), "bias")
+            self._check_stride(self.bias, (1, n), "bias must have stride (1, n)")
+            self._check_dtype(self.bias, [torch.bfloat16, torch.float16, torch.float32], "bias")
 
         self._require_sm100()
         self._is_supported = True
@@ -198,6 +210,7 @@ class GroupedGemmSwigluSm100(OperatorBase):
         norm_const_tensor: Optional[torch.Tensor] = None,
         prob_tensor: Optional[torch.Tensor] = None,
         current_stream=None,
+        bias_tensor: Optional[torch.Tensor] = None,
     ) -> None:
         """Launch on ``current_stream`` (``None`` = torch's current stream).  Allocates nothing and
         does not synchronise; ``amax_tensor`` is only ever raised (atomic max)."""
@@ -205,6 +218,8 @@ class GroupedGemmSwigluSm100(OperatorBase):
         tensor_m, k = a_tensor.shape[0], a_tensor.shape[1]
         if tensor_m == 0:
             return
+        if (bias_tensor is not None) != (self.bias is not None):
+            raise ValueError("bias fusion is fixed at construction: pass bias_tensor exactly when sample_bias was given")
         n, l = b_tensor.shape[0], b_tensor.shape[2]
         fp8_out = d_tensor.dtype == torch.float8_e4m3fn
         ops.grouped_gemm_op(
@@ -227,6 +242,8 @@ class GroupedGemmSwigluSm100(OperatorBase):
             discrete_col_sfd=self.discrete_col_sfd,
             sm_margin=self.num_cluster_overlap_margin,
             tile_mode=pick_tile_mode(self.mma_tiler_mn, self.m_aligned),
+            bias=bias_tensor,
+            act_func=self.act_func,
             stream=current_stream,
         )
 

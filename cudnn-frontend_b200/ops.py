@@ -117,6 +117,8 @@ def launch_grouped_gemm(
     d_row_map: Optional[torch.Tensor] = None,
     d_peer_ptrs: Optional[torch.Tensor] = None,
     d_peer_slots: int = 0,
+    bias: Optional[torch.Tensor] = None,
+    act_func: str = "swiglu",
     stream=None,
 ) -> None:
     """Fill the C struct and call b200moe_fc1_swiglu / b200moe_fc2_quant.
@@ -146,11 +148,22 @@ def launch_grouped_gemm(
     args.d_row_map = _ptr(d_row_map)
     args.d_peer_ptrs = _ptr(d_peer_ptrs)
     args.d_peer_slots = int(d_peer_slots)
+    args.bias = _ptr(bias)
+    if bias is not None:
+        if bias.dtype not in _BIAS_DTYPES:
+            raise NotImplementedError(f"bias dtype {bias.dtype} is not built (bf16, f16, f32 are)")
+        args.bias_dtype = _BIAS_DTYPES[bias.dtype]
+    if act_func not in ("swiglu", "geglu"):
+        raise ValueError(f"act_func must be 'swiglu' or 'geglu', got {act_func!r}")
+    args.act_func = _lib.ACT_GEGLU if act_func == "geglu" else _lib.ACT_SWIGLU
     lib = _lib.load()
     fn = lib.b200moe_fc1_swiglu if kind == "fc1" else lib.b200moe_fc2_quant
     with torch.cuda.device(a.device):
         rc = fn(ctypes.byref(args), _stream_ptr(stream))
     _lib.check(rc)
+
+
+_BIAS_DTYPES = {torch.bfloat16: _lib.DTYPE_BF16, torch.float16: _lib.DTYPE_F16, torch.float32: _lib.DTYPE_F32}
 
 
 def workspace_bytes(num_experts: int, discrete: bool) -> int:
@@ -186,19 +199,19 @@ def _(x, q, sf) -> None:
 def _fc1_swiglu_op(
     a: torch.Tensor, sfa: torch.Tensor, b: _T, sfb: _T, b_ptrs: _T, sfb_ptrs: _T, padded_offsets: torch.Tensor,
     alpha: torch.Tensor, prob: _T, norm_const: _T, c: _T, d: torch.Tensor, d_col: _T, amax: _T, sfd_row: _T,
-    sfd_col: _T, workspace: _T, n: int, discrete_col_sfd: bool, sm_margin: int, tile_mode: str,
+    sfd_col: _T, workspace: _T, bias: _T, n: int, discrete_col_sfd: bool, sm_margin: int, tile_mode: str, act_func: str,
 ) -> None:  # fmt: skip
     launch_grouped_gemm(
         "fc1", a=a, sfa=sfa, b=b, sfb=sfb, b_ptrs=b_ptrs, sfb_ptrs=sfb_ptrs, padded_offsets=padded_offsets, alpha=alpha,
         prob=prob, norm_const=norm_const, c=c, d=d, d_col=d_col, amax=amax, sfd_row=sfd_row, sfd_col=sfd_col,
         workspace=workspace, m_rows=a.shape[0], n=n, k=a.shape[1], num_experts=padded_offsets.shape[0],
-        discrete_col_sfd=discrete_col_sfd, sm_margin=sm_margin, tile_mode=tile_mode or None,
+        discrete_col_sfd=discrete_col_sfd, sm_margin=sm_margin, tile_mode=tile_mode or None, bias=bias, act_func=act_func or "swiglu",
     )  # fmt: skip
 
 
 @_fc1_swiglu_op.register_fake
 def _(a, sfa, b, sfb, b_ptrs, sfb_ptrs, padded_offsets, alpha, prob, norm_const, c, d, d_col, amax, sfd_row, sfd_col,
-      workspace, n, discrete_col_sfd, sm_margin, tile_mode) -> None:  # fmt: skip
+      workspace, bias, n, discrete_col_sfd, sm_margin, tile_mode, act_func) -> None:  # fmt: skip
     return None
 
 
@@ -208,7 +221,7 @@ def _(a, sfa, b, sfb, b_ptrs, sfb_ptrs, padded_offsets, alpha, prob, norm_const,
 def _fc2_quant_op(
     a: torch.Tensor, sfa: torch.Tensor, b: _T, sfb: _T, b_ptrs: _T, sfb_ptrs: _T, padded_offsets: torch.Tensor,
     alpha: torch.Tensor, prob: torch.Tensor, norm_const: _T, d: torch.Tensor, d_col: _T, amax: _T, sfd_row: _T,
-    sfd_col: _T, workspace: _T, d_row_map: _T, d_peer_ptrs: _T, d_peer_slots: int, n: int, discrete_col_sfd: bool,
+    sfd_col: _T, workspace: _T, d_row_map: _T, d_peer_ptrs: _T, d_peer_slots: int, bias: _T, n: int, discrete_col_sfd: bool,
     sm_margin: int, tile_mode: str,
 ) -> None:  # fmt: skip
     launch_grouped_gemm(
@@ -216,13 +229,13 @@ def _fc2_quant_op(
         prob=prob, norm_const=norm_const, d=d, d_col=d_col, amax=amax, sfd_row=sfd_row, sfd_col=sfd_col,
         workspace=workspace, m_rows=a.shape[0], n=n, k=a.shape[1], num_experts=padded_offsets.shape[0],
         discrete_col_sfd=discrete_col_sfd, sm_margin=sm_margin, tile_mode=tile_mode or None, d_row_map=d_row_map,
-        d_peer_ptrs=d_peer_ptrs, d_peer_slots=d_peer_slots,
+        d_peer_ptrs=d_peer_ptrs, d_peer_slots=d_peer_slots, bias=bias,
     )  # fmt: skip
 
 
 @_fc2_quant_op.register_fake
 def _(a, sfa, b, sfb, b_ptrs, sfb_ptrs, padded_offsets, alpha, prob, norm_const, d, d_col, amax, sfd_row, sfd_col, workspace,
-      d_row_map, d_peer_ptrs, d_peer_slots, n, discrete_col_sfd, sm_margin, tile_mode) -> None:  # fmt: skip
+      d_row_map, d_peer_ptrs, d_peer_slots, bias, n, discrete_col_sfd, sm_margin, tile_mode) -> None:  # fmt: skip
     return None
 
 
@@ -240,9 +253,10 @@ def grouped_gemm_op(kind: str, *, stream=None, **kw) -> None:
 
     def call():
         if kind == "fc1":
-            torch.ops.b200moe.fc1_swiglu(*common, kw.get("c"), *outs, *tail)
+            torch.ops.b200moe.fc1_swiglu(*common, kw.get("c"), *outs, kw.get("bias"), *tail, kw.get("act_func") or "swiglu")
         else:
-            torch.ops.b200moe.fc2_quant(*common, *outs, kw.get("d_row_map"), kw.get("d_peer_ptrs"), int(kw.get("d_peer_slots", 0)), *tail)
+            torch.ops.b200moe.fc2_quant(*common, *outs, kw.get("d_row_map"), kw.get("d_peer_ptrs"), int(kw.get("d_peer_slots", 0)),
+                                        kw.get("bias"), *tail)  # fmt: skip
 
     if ctx is None:
         call()

@@ -32,6 +32,11 @@ extern "C" {
 /* d_dtype values */
 #define B200MOE_DTYPE_BF16 0
 #define B200MOE_DTYPE_E4M3 1
+#define B200MOE_DTYPE_F16 2
+#define B200MOE_DTYPE_F32 3
+
+#define B200MOE_ACT_SWIGLU 0
+#define B200MOE_ACT_GEGLU 1
 
 /* flags */
 #define B200MOE_FLAG_DISCRETE_COL_SFD 1 /* per-expert column scale-factor blocks */
@@ -93,6 +98,16 @@ typedef struct b200moe_gemm_args {
      all-to-all of an expert-parallel layer.  NULL = d_row_map indexes d. */
   const int64_t* d_peer_ptrs;
   int64_t d_peer_slots;
+  /* optional fused bias, [N, E] with strides (1, N) as in the reference (element (n, e) at
+     e * N + n), bf16 / f16 / f32.  FC1: C = alpha * acc + bias before the activation
+     (grouped_gemm_glu/moe_blockscaled_grouped_gemm_glu_bias.py:2628-2660).  FC2:
+     D = alpha * acc + bias * prob (grouped_gemm_quant/grouped_gemm_quant.py:1841-1865). */
+  const void* bias;
+  int32_t bias_dtype; /* B200MOE_DTYPE_BF16 / _F16 / _F32 */
+  /* FC1 activation: B200MOE_ACT_SWIGLU, or B200MOE_ACT_GEGLU = the reference's GeGLU
+     (gate <= 7, -7 <= up <= 7, D = (up + 1) * gate * sigmoid(1.702 gate) * prob;
+     moe_blockscaled_grouped_gemm_glu_bias.py:1414-1487,2702-2716) */
+  int32_t act_func;
 } b200moe_gemm_args;
 
 /*

@@ -484,3 +484,124 @@ def test_fc2_is_bit_identical_to_the_reference_kernel_fixture(golden_dir, tile_m
     np.testing.assert_array_equal(orc.sf_unpack(flat(out["sfd_row_tensor"]), m, n // 32), orc.sf_unpack(g["sfd_row"], m, n // 32))
     np.testing.assert_array_equal(out["d_col_tensor"][:, :, 0].view(torch.uint8).cpu().numpy(), g["d_col"])
     np.testing.assert_array_equal(orc.sf_unpack(flat(out["sfd_col_tensor"]), n, m // 32), orc.sf_unpack(g["sfd_col"], n, m // 32))
+
+
+# ---------------------------------------------------------------------------------------------
+# unified GLU API: GeGLU, fused bias (dense and discrete weights), FC2 bias
+# ---------------------------------------------------------------------------------------------
+def _glu_inputs(seed, groups, n, k, bias_dtype, m_aligned=128):
+    dev = "cuda"
+    e = len(groups)
+    valid, aligned, offs = orc.padded_end_offsets(groups, m_aligned)
+    a, b, sfa, sfb = H.gen_operands(seed, valid, n, k, e)
+    H.zero_padding_rows(a, groups, aligned)
+    rng = np.random.default_rng(seed)
+    alpha = rng.integers(1, 3, e).astype(np.float32)
+    prob = rng.uniform(0.1, 1.0, valid).astype(np.float32)
+    bias_t = None
+    if bias_dtype is not None:
+        # the reference's layout: (n, l) with stride (1, n)
+        bias_t = torch.empty((e, n), dtype=torch.float32).uniform_(-2.0, 2.0, generator=torch.Generator().manual_seed(seed)).to(bias_dtype).t()
+    host = dict(a=a, b=b, sfa=sfa, sfb=sfb, offs=offs, alpha=alpha, prob=prob, bias=None if bias_t is None else bias_t.float().numpy())
+    t = dict(
+        a=H.dev_fp8(a).view(valid, k, 1), sfa=H.dev_sf(sfa, valid, k), b_store=H.dev_fp8(b), offs=torch.from_numpy(offs).to(dev),
+        alpha=torch.from_numpy(alpha).to(dev), prob=torch.from_numpy(prob).to(dev).view(valid, 1, 1),
+        bias=None if bias_t is None else bias_t.to(dev), sfb=H.dev_sf(sfb, n, k, e),
+    )  # fmt: skip
+    return host, t, dict(valid=valid, m_rows=valid, offs=offs, e=e)
+
+
+@pytest.mark.parametrize("act_func", ["swiglu", "geglu"])
+@pytest.mark.parametrize("bias_dtype", [None, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("discrete", [False, True])
+def test_unified_glu_wrapper(act_func, bias_dtype, discrete, tile_mode):
+    if discrete and bias_dtype == torch.float32:
+        pytest.skip("the reference's discrete mode takes 16-bit bias only")
+    cf = _api()
+    groups, n, k = [100, 0, 256, 129], 512, 256
+    host, t, info = _glu_inputs(17, groups, n, k, bias_dtype)
+    e = info["e"]
+    keep = []
+    if discrete:
+        bl = [t["b_store"][i].clone() for i in range(e)]
+        sl = [H.dev_sf(host["sfb"][i], n, k) for i in range(e)]
+        keep += bl + sl
+        mode = dict(b_ptrs=torch.tensor([x.data_ptr() for x in bl], dtype=torch.int64, device="cuda"),
+                    sfb_ptrs=torch.tensor([x.data_ptr() for x in sl], dtype=torch.int64, device="cuda"), n=n, b_dtype=torch.float8_e4m3fn)  # fmt: skip
+    else:
+        mode = dict(b_tensor=t["b_store"].permute(1, 2, 0), sfb_tensor=t["sfb"])
+    for d_fp8 in (False, True):
+        norm = torch.ones(1, device="cuda") if d_fp8 else None
+        res = cf.grouped_gemm_glu_wrapper_sm100(
+            t["a"], t["sfa"], t["offs"], t["alpha"], bias_tensor=t["bias"], norm_const_tensor=norm, prob_tensor=t["prob"],
+            d_dtype=torch.float8_e4m3fn if d_fp8 else torch.bfloat16, sf_vec_size=32, m_aligned=128, act_func=act_func, **mode,
+        )  # fmt: skip
+        torch.cuda.synchronize()
+        ref = orc.fc1_reference(host["a"], host["sfa"], host["b"], host["sfb"], host["offs"], host["alpha"], host["prob"],
+                                norm_const=1.0 if d_fp8 else None, bias=host["bias"], act_func=act_func)  # fmt: skip
+        info.update(n_out=n // 2, norm=1.0)
+        _check("fc1", dict(res), ref, info, d_fp8)
+
+
+def test_unified_glu_class_equals_the_fc1_class_for_swiglu(tile_mode):
+    """Without bias and with act_func='swiglu' the unified class is the FC1 operator: same bytes."""
+    cf = _api()
+    groups, n, k = [128, 256], 256, 128
+    host, t, info = _glu_inputs(5, groups, n, k, None)
+    m = info["valid"]
+    b = t["b_store"].permute(1, 2, 0)
+    outs = []
+    for cls in ("glu", "fc1"):
+        c = torch.zeros((m, n, 1), dtype=torch.bfloat16, device="cuda")
+        d = torch.zeros((m, n // 2, 1), dtype=torch.bfloat16, device="cuda")
+        amax = torch.full((info["e"], 1), float("-inf"), device="cuda")
+        if cls == "glu":
+            op = cf.GroupedGemmGluSm100(t["a"], c, d, t["sfa"], t["offs"], t["alpha"], None, sample_b=b, sample_sfb=t["sfb"],
+                                        sample_amax=amax, sample_prob=t["prob"], sf_vec_size=32, m_aligned=128)  # fmt: skip
+            assert op.check_support()
+            op.compile()
+            op.execute(t["a"], c, d, t["sfa"], t["offs"], t["alpha"], b_tensor=b, sfb_tensor=t["sfb"], amax_tensor=amax, prob_tensor=t["prob"])
+        else:
+            op = cf.GroupedGemmSwigluSm100(t["a"], b, c, d, t["sfa"], t["sfb"], t["offs"], t["alpha"], None, sample_amax=amax,
+                                           sample_prob=t["prob"], sf_vec_size=32, m_aligned=128)  # fmt: skip
+            assert op.check_support()
+            op.compile()
+            op.execute(t["a"], b, c, d, t["sfa"], t["sfb"], t["offs"], t["alpha"], amax_tensor=amax, prob_tensor=t["prob"])
+        torch.cuda.synchronize()
+        outs.append((c, d, amax))
+    for x, y in zip(*outs):
+        assert torch.equal(x, y)
+
+
+@pytest.mark.parametrize("bias_dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("d_fp8", [False, True])
+def test_fc2_fused_bias(bias_dtype, d_fp8, tile_mode):
+    """D = alpha * acc + bias * prob, the reference's fused form (prob scales the bias, not the GEMM)."""
+    cf = _api()
+    from cudnn_frontend_b200 import ops
+
+    groups, n, k = [200, 128, 0, 77], 384, 256
+    host, t, info = _glu_inputs(23, groups, n, k, bias_dtype)
+    m, e = info["valid"], info["e"]
+    b = t["b_store"].permute(1, 2, 0)
+    d_dtype = torch.float8_e4m3fn if d_fp8 else torch.bfloat16
+    d = torch.zeros((m, n, 1), dtype=torch.float32, device="cuda").to(d_dtype)
+    d_col = torch.zeros((m, n, 1), dtype=torch.float32, device="cuda").to(d_dtype) if d_fp8 else None
+    amax = None if d_fp8 else torch.full((e, 1), float("-inf"), device="cuda")
+    sr = ops.empty_sf(m, n, 1, zero=True) if d_fp8 else None
+    sc = ops.empty_sf(n, m, 1, zero=True) if d_fp8 else None
+    norm = torch.ones(1, device="cuda") if d_fp8 else None
+    op = cf.GroupedGemmQuantSm100(t["a"], t["sfa"], t["offs"], t["alpha"], d, sample_d_col=d_col, sample_b=b, sample_sfb=t["sfb"],
+                                  sample_bias=t["bias"], sample_sfd_row=sr, sample_sfd_col=sc, sample_amax=amax, sample_norm_const=norm,
+                                  sample_prob=t["prob"], sf_vec_size=32, m_aligned=128)  # fmt: skip
+    assert op.check_support()
+    op.compile()
+    with pytest.raises(ValueError, match="bias"):
+        op.execute(t["a"], t["sfa"], t["offs"], t["alpha"], d, b_tensor=b, sfb_tensor=t["sfb"], prob_tensor=t["prob"])
+    op.execute(t["a"], t["sfa"], t["offs"], t["alpha"], d, b_tensor=b, sfb_tensor=t["sfb"], bias_tensor=t["bias"], d_col_tensor=d_col,
+               sfd_row_tensor=sr, sfd_col_tensor=sc, amax_tensor=amax, norm_const_tensor=norm, prob_tensor=t["prob"])  # fmt: skip
+    torch.cuda.synchronize()
+    ref = orc.fc2_reference(host["a"], host["sfa"], host["b"], host["sfb"], host["offs"], host["alpha"], host["prob"],
+                            norm_const=1.0 if d_fp8 else None, bias=host["bias"])  # fmt: skip
+    info.update(n_out=n, norm=1.0)
+    _check("fc2", dict(c_tensor=None, d_tensor=d, d_col_tensor=d_col, amax_tensor=amax, sfd_row_tensor=sr, sfd_col_tensor=sc), ref, info, d_fp8)

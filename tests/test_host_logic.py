@@ -30,7 +30,7 @@ def test_library_builds_loads_and_exports_every_declared_symbol():
     for name in declared:
         assert hasattr(lib, name), f"{name} declared in include/b200moe.h but not exported"
     assert set(declared) == set(_lib.EXPORTED_SYMBOLS)
-    assert _lib.load().b200moe_abi_version() == 2
+    assert _lib.load().b200moe_abi_version() == 3
     assert _lib.load().b200moe_workspace_bytes(256, 1) == 256 * 256
     assert _lib.load().b200moe_workspace_bytes(256, 0) == 0
 
@@ -124,9 +124,12 @@ def test_fc2_requires_prob_and_one_weight_mode():
     with pytest.raises(ValueError, match="Must provide"):
         cf.grouped_gemm_quant_wrapper_sm100(a, sfa, offs, alpha)
     prob = torch.ones((m, 1, 1))
-    with pytest.raises(NotImplementedError, match="bias"):
+    with pytest.raises(ValueError, match="stride"):  # the reference's layout is (n, l) with stride (1, n)
         cf.GroupedGemmQuantSm100(a, sfa, offs, alpha, d, sample_b=b, sample_sfb=sfb, sample_prob=prob, sf_vec_size=32,
-                                 sample_bias=torch.empty((e, n), dtype=torch.bfloat16).t()).check_support()  # fmt: skip
+                                 sample_bias=torch.empty((n, e), dtype=torch.bfloat16)).check_support()  # fmt: skip
+    with pytest.raises(ValueError, match="bias"):
+        cf.GroupedGemmQuantSm100(a, sfa, offs, alpha, d, sample_b=b, sample_sfb=sfb, sample_prob=prob, sf_vec_size=32,
+                                 sample_bias=torch.empty((e, n), dtype=torch.int32).t()).check_support()  # fmt: skip
     with pytest.raises(ValueError, match="MMA tiler N"):
         cf.GroupedGemmQuantSm100(a, sfa, offs, alpha, d, sample_b=b, sample_sfb=sfb, sample_prob=prob, sf_vec_size=32,
                                  mma_tiler_mn=(256, 128)).check_support()  # fmt: skip
@@ -220,3 +223,49 @@ def test_fused_plan_places_every_routed_row_once_inside_its_expert_group():
                 slots = [seen[d][r][1] for r in rows if seen[d][r][0] == s]
                 assert slots == sorted(slots)
             start = int(ends[el])
+
+
+def test_unified_glu_api_argument_rules():
+    """GroupedGemmGluSm100 / grouped_gemm_glu_wrapper_sm100: one of the two weight modes, known act_func."""
+    m, n, k, e = 256, 256, 128, 2
+    a = torch.empty((m, k, 1), dtype=torch.float8_e4m3fn)
+    b = torch.empty((e, n, k), dtype=torch.float8_e4m3fn).permute(1, 2, 0)
+    sfa, sfb = ops.empty_sf(m, k, 1, device="cpu"), ops.empty_sf(n, k, e, device="cpu")
+    d = torch.empty((m, n // 2, 1), dtype=torch.bfloat16)
+    offs, alpha = torch.zeros(e, dtype=torch.int32), torch.ones(e)
+    with pytest.raises(ValueError, match="not both"):
+        cf.GroupedGemmGluSm100(a, None, d, sfa, offs, alpha, None, sample_b=b, sample_sfb=sfb, num_experts=e, b_shape=(n, k),
+                               b_dtype=torch.float8_e4m3fn)  # fmt: skip
+    with pytest.raises(ValueError, match="Must provide"):
+        cf.GroupedGemmGluSm100(a, None, d, sfa, offs, alpha, None)
+    with pytest.raises(ValueError, match="act_func"):
+        cf.GroupedGemmGluSm100(a, None, d, sfa, offs, alpha, None, sample_b=b, sample_sfb=sfb, sf_vec_size=32,
+                               act_func="relu").check_support()  # fmt: skip
+    with pytest.raises(NotImplementedError, match="N-major"):
+        cf.GroupedGemmGluSm100(a, None, d, sfa, offs, alpha, None, sample_b=b, sample_sfb=sfb, sf_vec_size=32,
+                               b_major="n").check_support()  # fmt: skip
+    with pytest.raises(ValueError, match="not both"):
+        cf.grouped_gemm_glu_wrapper_sm100(a, sfa, offs, alpha, b_tensor=b, sfb_tensor=sfb, b_ptrs=torch.zeros(2, dtype=torch.int64))
+
+
+def test_oracle_geglu_and_bias_follow_the_reference_formulas():
+    import numpy as np
+
+    from oracle import mxfp8_oracle as orc
+
+    r = np.random.default_rng(3)
+    c = (r.standard_normal((8, 128)) * 6).astype(np.float32)
+    prob = r.random(8).astype(np.float32)
+    d = orc.geglu_interleaved(c, prob)
+    gate, up = c[:, :32], c[:, 32:64]
+    g = np.minimum(gate, 7.0)
+    u = np.clip(up, -7.0, 7.0)
+    want = (u + 1.0) * g / (1.0 + np.exp(-1.702 * g.astype(np.float64))) * prob[:, None]
+    np.testing.assert_allclose(d[:, :32], want, rtol=1e-6, atol=1e-6)
+    offs = np.array([3, 8], dtype=np.int32)
+    bias = r.standard_normal((128, 2)).astype(np.float32)
+    cb = orc.add_bias(c, bias, offs)
+    np.testing.assert_allclose(cb[:3], c[:3] + bias[:, 0], rtol=0, atol=0)
+    np.testing.assert_allclose(cb[3:], c[3:] + bias[:, 1], rtol=0, atol=0)
+    cb2 = orc.add_bias(c, bias, offs, row_scale=prob)
+    np.testing.assert_allclose(cb2[3:], c[3:] + bias[:, 1][None, :] * prob[3:, None], rtol=1e-6)
