@@ -605,3 +605,45 @@ def test_fc2_fused_bias(bias_dtype, d_fp8, tile_mode):
                             norm_const=1.0 if d_fp8 else None, bias=host["bias"])  # fmt: skip
     info.update(n_out=n, norm=1.0)
     _check("fc2", dict(c_tensor=None, d_tensor=d, d_col_tensor=d_col, amax_tensor=amax, sfd_row_tensor=sr, sfd_col_tensor=sc), ref, info, d_fp8)
+
+
+def test_geglu_with_bias_is_bit_identical_to_the_reference_kernel_fixture(golden_dir, tile_mode):
+    """Inputs and outputs of cudnn-frontend's grouped_gemm_glu_wrapper_sm100 (dense weights, act_func
+    'geglu', fused bf16 bias, E4M3 D, norm_const 1) recorded on a B200
+    (baseline/run_reference_kernels.py --cases glu_tiny): every output byte must match."""
+    path = os.path.join(golden_dir, "reference_kernel_glu.npz")
+    if not os.path.exists(path):
+        pytest.skip("reference-kernel fixture not recorded")
+    cf = _api()
+    from cudnn_frontend_b200 import ops
+
+    g = np.load(path)
+    m, k = g["a"].shape
+    e, n, _ = g["b"].shape
+    dev = "cuda"
+
+    def sf(flat, mn, kk, l):
+        shape, stride = ops.sf_shape_stride(mn, kk, l)
+        return torch.as_strided(torch.from_numpy(flat).to(dev).view(torch.float8_e8m0fnu), shape, stride)
+
+    a = torch.as_strided(H.dev_fp8(g["a"]), (m, k, 1), (k, 1, m * k))
+    b = H.dev_fp8(g["b"]).permute(1, 2, 0)
+    bias = torch.from_numpy(g["bias"]).to(dev).view(torch.bfloat16).t()  # (n, e), stride (1, n)
+    out = cf.grouped_gemm_glu_wrapper_sm100(
+        a, sf(g["sfa"], m, k, 1), torch.from_numpy(g["offsets"]).to(dev), torch.ones(e, device=dev),
+        b_tensor=b, sfb_tensor=sf(g["sfb"], n, k, e), bias_tensor=bias, norm_const_tensor=torch.ones(1, device=dev),
+        prob_tensor=torch.from_numpy(g["prob"]).to(dev).view(m, 1, 1), d_dtype=torch.float8_e4m3fn, sf_vec_size=32, m_aligned=256,
+        act_func="geglu",
+    )  # fmt: skip
+    torch.cuda.synchronize()
+
+    def flat(t):
+        t = t.view(torch.uint8)
+        return torch.as_strided(t, (t.numel(),), (1,)).cpu().numpy()
+
+    n_out = n // 2
+    np.testing.assert_array_equal(out["c_tensor"][:, :, 0].view(torch.int16).cpu().numpy(), g["c"])
+    np.testing.assert_array_equal(out["d_tensor"][:, :, 0].view(torch.uint8).cpu().numpy(), g["d"])
+    np.testing.assert_array_equal(orc.sf_unpack(flat(out["sfd_row_tensor"]), m, n_out // 32), orc.sf_unpack(g["sfd_row"], m, n_out // 32))
+    np.testing.assert_array_equal(out["d_col_tensor"][:, :, 0].view(torch.uint8).cpu().numpy(), g["d_col"])
+    np.testing.assert_array_equal(orc.sf_unpack(flat(out["sfd_col_tensor"]), n_out, m // 32), orc.sf_unpack(g["sfd_col"], n_out, m // 32))

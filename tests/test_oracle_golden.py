@@ -167,3 +167,20 @@ def test_fc2_oracle_against_the_reference_kernel_fixture(golden_dir):
     out = orc.fc2_reference(g["a"], sfa, g["b"], sfb, g["offsets"], np.ones(e, np.float32), g["prob"], norm_const=1.0)
     _check_quantised(out["d_q"], out["sfd_row"], g["d"], g["sfd_row"], m, n)
     _check_quantised(out["d_col_q"], out["sfd_col"], g["d_col"], g["sfd_col"], m, n, by_cols=True)
+
+
+def test_geglu_bias_oracle_against_the_reference_kernel_fixture(golden_dir):
+    """GeGLU and the fused bias exist in the reference only as kernel code; this fixture (recorded from
+    grouped_gemm_glu_wrapper_sm100 on a B200) is what pins the oracle's restatement of them."""
+    g = _load(golden_dir, "reference_kernel_glu.npz")
+    m, n = g["c"].shape
+    e = g["b"].shape[0]
+    k = g["a"].shape[1]
+    sfa, sfb = orc.sf_unpack(g["sfa"], m, k // 32)[0], orc.sf_unpack(g["sfb"], n, k // 32, e)
+    bias = _bf16_bits_to_f32(g["bias"].view(np.uint16)).T  # [N, E]
+    out = orc.fc1_reference(g["a"], sfa, g["b"], sfb, g["offsets"], np.ones(e, np.float32), g["prob"], norm_const=1.0, bias=bias,
+                            act_func="geglu")  # fmt: skip
+    c_ref = _bf16_bits_to_f32(g["c"].view(np.uint16))
+    assert np.mean(orc.bf16_round(out["c"][:m]) == c_ref) >= 0.99
+    _check_quantised(out["d_q"], out["sfd_row"], g["d"], g["sfd_row"], m, n // 2)
+    _check_quantised(out["d_col_q"], out["sfd_col"], g["d_col"], g["sfd_col"], m, n // 2, by_cols=True)
