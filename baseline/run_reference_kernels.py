@@ -350,8 +350,10 @@ CASES = {
     "fc2_tiny": dict(experts=2, k=128, n=256, tokens=128, topk=2, routing="uniform"),
     "fc2_mixtral": dict(experts=8, k=14336, n=4096, tokens=16384, topk=2, routing="uniform"),
     "c4": dict(experts=256, k=2048, n=7168, tokens=8192, topk=8, routing="zipf"),
+    # reduced Mixtral-shape FC2 for profiler captures
+    "fc2_mid": dict(experts=8, k=3584, n=4096, tokens=4096, topk=2, routing="uniform"),
 }
-FC2_CASES = ("fc2_tiny", "fc2_mixtral", "c4")
+FC2_CASES = ("fc2_tiny", "fc2_mixtral", "c4", "fc2_mid")
 # unified GLU API (GeGLU + fused bias): glu_tiny records a fixture, glu_mid compares speed
 CASES["glu_tiny"] = dict(experts=2, k=128, n=128, tokens=128, topk=2, routing="uniform")
 CASES["glu_mid"] = dict(experts=8, k=4096, n=7168, tokens=4096, topk=2, routing="uniform")
