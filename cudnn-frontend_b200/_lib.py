@@ -14,6 +14,7 @@ from . import _build
 E_NULL, E_SHAPE, E_ALIGN, E_UNSUPPORTED, E_WORKSPACE, E_DEVICE = -1, -2, -3, -4, -5, -6
 DTYPE_BF16, DTYPE_E4M3, DTYPE_F16, DTYPE_F32 = 0, 1, 2, 3
 ACT_SWIGLU, ACT_GEGLU = 0, 1
+ABI_VERSION = 3  # b200moe_abi_version() of the header these declarations mirror
 FLAG_DISCRETE_COL_SFD = 1
 FLAG_TILE_SINGLE = 2
 FLAG_TILE_PAIR = 4
@@ -119,6 +120,9 @@ def load() -> ctypes.CDLL:
     if not os.path.exists(path):
         raise RuntimeError(f"{path} is missing: build it with `python -m cudnn_frontend_b200._build` (needs nvcc)")
     lib = ctypes.CDLL(path)
+    lib.b200moe_abi_version.restype = ctypes.c_int
+    if lib.b200moe_abi_version() != ABI_VERSION:
+        raise RuntimeError(f"{path} has ABI version {lib.b200moe_abi_version()}, this package needs {ABI_VERSION}: rebuild the library")
     for name, (restype, argtypes) in _SIGNATURES.items():
         fn = getattr(lib, name)
         fn.restype = restype

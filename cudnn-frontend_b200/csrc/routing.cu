@@ -204,29 +204,43 @@ __global__ void __launch_bounds__(128)
     *reinterpret_cast<float*>(rec + rec_pitch - 8) = topk_prob ? topk_prob[slot] : 1.0f;
     *reinterpret_cast<int32_t*>(rec + rec_pitch - 4) = (int32_t)(my_rank * slot_capacity + slot);
   }
-  for (int v = threadIdx.x; v < cols / 8; v += blockDim.x) {
-    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(x + t * cols) + v);
-    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
-    float f[8];
+  // the row is read in batches of four 16-byte loads per thread, all issued before the first use
+  const int vecs = cols / 8;
+  const uint4* xrow = reinterpret_cast<const uint4*>(x + t * cols);
+  for (int v0 = threadIdx.x; v0 < vecs; v0 += 4 * blockDim.x) {
+    uint4 raw4[4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float2 p2 = __bfloat1622float2(h[j]);
-      f[2 * j] = p2.x;
-      f[2 * j + 1] = p2.y;
+    for (int u = 0; u < 4; ++u) {
+      const int v = v0 + u * blockDim.x;
+      raw4[u] = v < vecs ? __ldg(xrow + v) : make_uint4(0, 0, 0, 0);
     }
-    float amax = 0.f;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(f[j]));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-    const uint32_t sfb = e8m0_from_float(amax * (1.0f / 448.0f));
-    const float scale = quant_scale(1.0f, e8m0_to_float(sfb));
-    uint2 o;
-    o.x = e4m3x4_from_float(f[0] * scale, f[1] * scale, f[2] * scale, f[3] * scale);
-    o.y = e4m3x4_from_float(f[4] * scale, f[5] * scale, f[6] * scale, f[7] * scale);
-    reinterpret_cast<uint2*>(s_qrow)[v] = o;
-    if ((lane & 3) == 0) {
-      for (int j = 0; j < topk; ++j) s_rec[j * rec_pitch + (v >> 2)] = (uint8_t)sfb;
+    for (int u = 0; u < 4; ++u) {
+      const int v = v0 + u * blockDim.x;
+      // whole warps run in or out together: vecs is a multiple of 32 (host check), v - lane too
+      if (v - lane >= vecs) break;
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw4[u]);
+      float f[8];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 p2 = __bfloat1622float2(h[j]);
+        f[2 * j] = p2.x;
+        f[2 * j + 1] = p2.y;
+      }
+      float amax = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(f[j]));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+      const uint32_t sfb = e8m0_from_float(amax * (1.0f / 448.0f));
+      const float scale = quant_scale(1.0f, e8m0_to_float(sfb));
+      uint2 o;
+      o.x = e4m3x4_from_float(f[0] * scale, f[1] * scale, f[2] * scale, f[3] * scale);
+      o.y = e4m3x4_from_float(f[4] * scale, f[5] * scale, f[6] * scale, f[7] * scale);
+      reinterpret_cast<uint2*>(s_qrow)[v] = o;
+      if ((lane & 3) == 0) {
+        for (int j = 0; j < topk; ++j) s_rec[j * rec_pitch + (v >> 2)] = (uint8_t)sfb;
+      }
     }
   }
   fence_proxy_async_smem();  // this thread's writes, for the bulk copies below
@@ -413,8 +427,9 @@ int b200moe_dispatch_quantize_peer(const void* x, const int32_t* expert_ids, con
   if (num_tokens == 0) return B200MOE_OK;
   if (!x || !expert_ids || !local_row || !delta || !peer_q || !peer_rec)
     return fail(B200MOE_E_NULL, "dispatch_quantize_peer: null pointer");
-  if (cols <= 0 || cols % 32 != 0 || topk <= 0 || topk > 16 || num_tokens < 0 || num_tokens > 0x7fffffffll)
-    return fail(B200MOE_E_SHAPE, "dispatch_quantize_peer: cols must be a positive multiple of 32 and topk in [1, 16]");
+  // whole warps only (full-mask shuffles inside the row loop): 32 lanes x 8 columns
+  if (cols <= 0 || cols % 256 != 0 || topk <= 0 || topk > 16 || num_tokens < 0 || num_tokens > 0x7fffffffll)
+    return fail(B200MOE_E_SHAPE, "dispatch_quantize_peer: cols must be a positive multiple of 256 and topk in [1, 16]");
   if (experts_per_rank <= 0 || num_ranks <= 0 || my_rank < 0 || my_rank >= num_ranks || slot_capacity < num_tokens * topk ||
       (int64_t)num_ranks * slot_capacity > 0x7fffffffll || row_capacity <= 0)
     return fail(B200MOE_E_SHAPE, "dispatch_quantize_peer: bad rank layout or capacities");

@@ -74,6 +74,29 @@ def test_peer_memory_layer_equals_the_plain_layer():
     layer.release_peer_buffers()
 
 
+def test_peer_buffers_grow_when_a_step_needs_more_rows():
+    """A capacity factor far too small for the step: the layer reallocates larger peer buffers (all
+    ranks together in the multi-rank case) and still returns the plain layer's result."""
+    from cudnn_frontend_b200 import ops, synthetic
+    from cudnn_frontend_b200.ep_layer import ExpertParallelMoE
+
+    t = 2048
+    g = torch.Generator(device="cuda").manual_seed(21)
+    x = torch.randn(t, HID, generator=g, device="cuda").to(torch.bfloat16)
+    ids = torch.multinomial(torch.ones(t, E, device="cuda"), K, generator=g).to(torch.int32)
+    prob = torch.softmax(torch.randn(t, K, generator=g, device="cuda"), -1)
+    w1, sfw1 = synthetic.make_weights(E, 2 * INTER, HID, 31, "cuda", std=0.05)
+    w2, sfw2 = synthetic.make_weights(E, HID, INTER, 32, "cuda", std=0.05)
+    layer = ExpertParallelMoE(w1, sfw1, w2, sfw2, E)
+    y = layer(x, ids, prob)
+    yf = layer.forward_fused(x, ids, prob, capacity_factor=0.1)
+    torch.cuda.synchronize()
+    assert layer._peer["cap"] >= layer.last_plan.m_rows if layer.last_plan is not None else True
+    assert ops.device_status(clear=True) == 0
+    assert torch.equal(y, yf)
+    layer.release_peer_buffers()
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))

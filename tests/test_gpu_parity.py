@@ -647,3 +647,16 @@ def test_geglu_with_bias_is_bit_identical_to_the_reference_kernel_fixture(golden
     np.testing.assert_array_equal(orc.sf_unpack(flat(out["sfd_row_tensor"]), m, n_out // 32), orc.sf_unpack(g["sfd_row"], m, n_out // 32))
     np.testing.assert_array_equal(out["d_col_tensor"][:, :, 0].view(torch.uint8).cpu().numpy(), g["d_col"])
     np.testing.assert_array_equal(orc.sf_unpack(flat(out["sfd_col_tensor"]), n_out, m // 32), orc.sf_unpack(g["sfd_col"], n_out, m // 32))
+
+
+@pytest.mark.parametrize("kind", ["fc1", "fc2"])
+def test_custom_op_path_equals_the_direct_launch(kind, monkeypatch):
+    """Eager calls reach the C ABI directly; torch.compile graphs go through torch.ops.b200moe.*.
+    Both must launch the same thing."""
+    from cudnn_frontend_b200 import ops
+
+    out_direct, _, _ = _run(kind, 41, [128, 200], 256, 128, d_fp8=True)
+    monkeypatch.setattr(ops, "_FORCE_CUSTOM_OP", True)
+    out_op, _, _ = _run(kind, 41, [128, 200], 256, 128, d_fp8=True)
+    for key in ("d_tensor", "d_col_tensor", "sfd_row_tensor", "sfd_col_tensor"):
+        assert torch.equal(out_direct[key].view(torch.uint8), out_op[key].view(torch.uint8)), key
