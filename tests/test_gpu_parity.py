@@ -660,3 +660,82 @@ def test_custom_op_path_equals_the_direct_launch(kind, monkeypatch):
     out_op, _, _ = _run(kind, 41, [128, 200], 256, 128, d_fp8=True)
     for key in ("d_tensor", "d_col_tensor", "sfd_row_tensor", "sfd_col_tensor"):
         assert torch.equal(out_direct[key].view(torch.uint8), out_op[key].view(torch.uint8)), key
+
+
+@pytest.mark.parametrize("discrete", [False, True])
+def test_launches_are_capturable_in_a_cuda_graph(discrete):
+    """execute() never allocates or synchronises (discrete mode patches its tensor maps on the
+    device from the pointer arrays), so FC1 -> FC2 can be captured once and replayed with new data
+    in the same buffers."""
+    cf = _api()
+    from cudnn_frontend_b200 import ops
+
+    groups, n1, k1, n2 = [128, 256, 0, 128], 512, 256, 256
+    host, t, info = _glu_inputs(61, groups, n1, k1, None)
+    m, e = info["valid"], info["e"]
+    h2, w2, _, sfw2 = H.gen_operands(62, 1, n2, n1 // 2, e)
+    tw2_store = H.dev_fp8(w2)
+    keep = []
+    if discrete:
+        bl = [t["b_store"][i].clone() for i in range(e)]
+        sl = [H.dev_sf(host["sfb"][i], n1, k1) for i in range(e)]
+        keep += bl + sl
+        b_ptrs = torch.tensor([x.data_ptr() for x in bl], dtype=torch.int64, device="cuda")
+        sfb_ptrs = torch.tensor([x.data_ptr() for x in sl], dtype=torch.int64, device="cuda")
+    d1 = torch.zeros((m, n1 // 2, 1), dtype=torch.float32, device="cuda").to(torch.float8_e4m3fn)
+    sf1 = ops.empty_sf(m, n1 // 2, 1, zero=True)
+    sfc = ops.empty_sf(n1 // 2, m, 1, zero=True)
+    norm = torch.ones(1, device="cuda")
+    d2 = torch.zeros((m, n2, 1), dtype=torch.bfloat16, device="cuda")
+    amax = torch.full((e, 1), float("-inf"), device="cuda")
+    if discrete:
+        fc1 = cf.DiscreteGroupedGemmSwigluSm100(t["a"], e, (n1, k1), torch.float8_e4m3fn, None, d1, t["sfa"], t["offs"], t["alpha"], d1,
+                                                sample_sfd_row=sf1, sample_sfd_col=sfc, sample_norm_const=norm, sample_prob=t["prob"],
+                                                sf_vec_size=32, m_aligned=128)  # fmt: skip
+    else:
+        fc1 = cf.GroupedGemmSwigluSm100(t["a"], t["b_store"].permute(1, 2, 0), None, d1, t["sfa"], t["sfb"], t["offs"], t["alpha"], d1,
+                                        sample_sfd_row=sf1, sample_sfd_col=sfc, sample_norm_const=norm, sample_prob=t["prob"],
+                                        sf_vec_size=32, m_aligned=128)  # fmt: skip
+    fc2 = cf.GroupedGemmQuantSm100(d1, sf1, t["offs"], t["alpha"], d2, sample_b=tw2_store.permute(1, 2, 0), sample_sfb=H.dev_sf(sfw2, n2, n1 // 2, e),
+                                   sample_amax=amax, sample_prob=t["prob"], sf_vec_size=32, m_aligned=128)  # fmt: skip
+    for op in (fc1, fc2):
+        assert op.check_support()
+        op.compile()
+    tsfw2 = H.dev_sf(sfw2, n2, n1 // 2, e)
+
+    def run():
+        if discrete:
+            fc1.execute(t["a"], b_ptrs, None, d1, t["sfa"], sfb_ptrs, t["offs"], t["alpha"], sfd_row_tensor=sf1, norm_const_tensor=norm,
+                        prob_tensor=t["prob"])  # fmt: skip
+        else:
+            fc1.execute(t["a"], t["b_store"].permute(1, 2, 0), None, d1, t["sfa"], t["sfb"], t["offs"], t["alpha"], sfd_row_tensor=sf1,
+                        norm_const_tensor=norm, prob_tensor=t["prob"])  # fmt: skip
+        fc2.execute(d1, sf1, t["offs"], t["alpha"], d2, b_tensor=tw2_store.permute(1, 2, 0), sfb_tensor=tsfw2, amax_tensor=amax,
+                    prob_tensor=t["prob"])  # fmt: skip
+
+    run()
+    torch.cuda.synchronize()
+    want = d2.clone()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        run()  # warm-up on the capture stream
+        side.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            run()
+    d2.zero_()
+    d1.view(torch.uint8).zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    assert ops.device_status(clear=True) == 0
+    assert torch.equal(d2, want)
+    # new activations in the same buffer: the replay follows the data, not the capture-time values
+    t["a"].view(torch.uint8).copy_(torch.flip(t["a"].view(torch.uint8), dims=[0]))
+    run()
+    torch.cuda.synchronize()
+    want2 = d2.clone()
+    d2.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(d2, want2) and not torch.equal(want2, want)
