@@ -102,6 +102,13 @@ def run_case(name, cfg, out):
 
     p = synthetic.make_problem(cfg, "cuda", seed=3, m_aligned=256)
     n, k = cfg["n"], cfg["k"]
+    if cfg.get("ab") == "e5m2":
+        # same shapes and scale factors, operands drawn directly in E5M2 (reinterpreting E4M3 bytes would hit its Inf / NaN codes)
+        g5 = torch.Generator(device="cuda").manual_seed(11)
+        m_all = p["a"].shape[0]
+        a5 = torch.randn(m_all, k, generator=g5, device="cuda").to(torch.float8_e5m2)
+        p["a"] = torch.as_strided(a5, (m_all, k, 1), (k, 1, m_all * k))
+        p["b"] = (torch.randn(cfg["experts"], n, k, generator=g5, device="cuda") * 0.5).to(torch.float8_e5m2).permute(1, 2, 0)
     norm = torch.tensor([1.0], dtype=torch.float32, device="cuda")
     stream = cuda.CUstream(torch.cuda.current_stream().cuda_stream)
     common = dict(norm_const_tensor=norm, prob_tensor=p["prob"], d_dtype=torch.float8_e4m3fn, sf_vec_size=32, m_aligned=256)
@@ -176,9 +183,9 @@ def run_case(name, cfg, out):
     out.append(res)
     print(json.dumps(res), flush=True)
 
-    if name == "tiny":
+    if name in ("tiny", "tiny_e5m2"):
         np.savez_compressed(
-            os.path.join(ROOT, "gpurun_out", "reference_kernel_golden.npz"),
+            os.path.join(ROOT, "gpurun_out", "reference_kernel_golden.npz" if name == "tiny" else "reference_kernel_e5m2_golden.npz"),
             a=p["a"][:, :, 0].view(torch.uint8).cpu().numpy(),
             b=p["b"].permute(2, 0, 1).contiguous().view(torch.uint8).cpu().numpy(),
             sfa=flat(p["sfa"]).cpu().numpy(),
@@ -343,6 +350,7 @@ CASES = {
     "mid": dict(experts=8, k=4096, n=7168, tokens=4096, topk=2, routing="uniform"),
     # small enough to commit its inputs and the reference kernel's outputs as a fixture
     "tiny": dict(experts=2, k=128, n=128, tokens=128, topk=2, routing="uniform"),
+    "tiny_e5m2": dict(experts=2, k=128, n=128, tokens=128, topk=2, routing="uniform", ab="e5m2"),
     "small": dict(experts=4, k=512, n=512, tokens=512, topk=2, routing="uniform"),
     "c2": dict(experts=8, k=4096, n=28672, tokens=16384, topk=2, routing="uniform"),
     "c3": dict(experts=256, k=7168, n=4096, tokens=8192, topk=8, routing="zipf"),

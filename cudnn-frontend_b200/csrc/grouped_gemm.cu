@@ -131,6 +131,7 @@ struct GemmParams {
   const void* bias;    // optional [E][N] (element (n, e) at e * N + n), added after alpha
   int bias_dtype;      // B200MOE_DTYPE_BF16 / _F16 / _F32
   int act_geglu;       // FC1: 0 = SwiGLU, 1 = GeGLU
+  uint32_t ab_format;  // A / B format bits of the instruction descriptor (0 = E4M3, E5M2 = 1 in both fields)
   int raster_group_m;  // row tiles per raster group
 };
 
@@ -522,7 +523,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       // The issuing thread is a serial instruction stream: four MMAs, three scale copies and a
       // commit per k-tile must cost as few instructions as possible, so every descriptor is
       // (constant high word, running low word) and the instruction descriptors are immediates.
-      constexpr uint32_t idesc = make_idesc_mxf8(C::TILE_M, BN);
+      const uint32_t idesc = make_idesc_mxf8(C::TILE_M, BN) | p.ab_format;
       constexpr uint32_t AB_HI = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO 1024, version 1, 128-byte swizzle
       constexpr uint32_t SF_HI = (128u >> 4) | (1u << 14);                // SBO 128, version 1, no swizzle
       constexpr uint32_t AB_LBO = 1u << 16;                               // leading byte offset 16 (unused by swizzled K-major)
@@ -1068,6 +1069,8 @@ static int run_gemm(int epi, const b200moe_gemm_args* a, void* stream_v) {
   if (a->d_peer_ptrs && (!a->d_row_map || a->d_peer_slots <= 0))
     return fail(B200MOE_E_SHAPE, "%s: d_peer_ptrs needs d_row_map and a positive d_peer_slots", op);
   if (a->d_dtype != B200MOE_DTYPE_BF16 && !d_fp8) return fail(B200MOE_E_UNSUPPORTED, "%s: d_dtype %d", op, a->d_dtype);
+  if (a->ab_dtype != 0 && a->ab_dtype != B200MOE_DTYPE_E4M3 && a->ab_dtype != B200MOE_DTYPE_E5M2)
+    return fail(B200MOE_E_UNSUPPORTED, "%s: ab_dtype %d (E4M3 and E5M2 are built)", op, a->ab_dtype);
   if (a->act_func != B200MOE_ACT_SWIGLU && a->act_func != B200MOE_ACT_GEGLU)
     return fail(B200MOE_E_UNSUPPORTED, "%s: act_func %d", op, a->act_func);
   if (a->bias) {
@@ -1100,6 +1103,7 @@ static int run_gemm(int epi, const b200moe_gemm_args* a, void* stream_v) {
   p.alpha = a->alpha;
   p.prob = a->prob;
   p.norm_const = a->norm_const;
+  p.ab_format = a->ab_dtype == B200MOE_DTYPE_E5M2 ? ((1u << 7) | (1u << 10)) : 0u;
   p.bias = a->bias;
   p.bias_dtype = a->bias_dtype;
   p.act_geglu = (epi == EPI_FC1 && a->act_func == B200MOE_ACT_GEGLU) ? 1 : 0;
@@ -1297,6 +1301,6 @@ int b200moe_device_status(int clear) {
   return v;
 }
 
-int b200moe_abi_version(void) { return 3; }
+int b200moe_abi_version(void) { return 4; }
 
 }  // extern "C"

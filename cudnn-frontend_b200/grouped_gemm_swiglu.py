@@ -169,7 +169,7 @@ class GroupedGemmSwigluSm100(OperatorBase):
         )
 
         # what this build implements of the reference's surface
-        self._not_implemented_error_if(self.ab_dtype != torch.float8_e4m3fn, f"only MXFP8 E4M3 inputs are built, got {self.ab_dtype}")
+        self._not_implemented_error_if(self.ab_dtype not in (torch.float8_e4m3fn, torch.float8_e5m2), f"only MXFP8 (E4M3 or E5M2) inputs are built, got {self.ab_dtype}")
         self._not_implemented_error_if(self.sf_dtype != torch.float8_e8m0fnu, f"only E8M0 scale factors are built, got {self.sf_dtype}")
         self._not_implemented_error_if(self.c is not None and self.c_dtype != torch.bfloat16, f"only bf16 C is built, got {self.c_dtype}")
         self._not_implemented_error_if(self.d_dtype not in (torch.bfloat16, torch.float8_e4m3fn), f"only bf16 and E4M3 D are built, got {self.d_dtype}")

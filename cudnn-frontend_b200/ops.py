@@ -156,6 +156,13 @@ def launch_grouped_gemm(
     if act_func not in ("swiglu", "geglu"):
         raise ValueError(f"act_func must be 'swiglu' or 'geglu', got {act_func!r}")
     args.act_func = _lib.ACT_GEGLU if act_func == "geglu" else _lib.ACT_SWIGLU
+    if a.dtype == torch.float8_e5m2:
+        other = b.dtype if b is not None else torch.float8_e5m2  # discrete weights: the caller vouches for the pointers
+        if other != torch.float8_e5m2:
+            raise ValueError("A and B must have the same element type")
+        args.ab_dtype = _lib.DTYPE_E5M2
+    else:
+        args.ab_dtype = _lib.DTYPE_E4M3
     lib = _lib.load()
     fn = lib.b200moe_fc1_swiglu if kind == "fc1" else lib.b200moe_fc2_quant
     with torch.cuda.device(a.device):

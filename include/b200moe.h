@@ -34,6 +34,7 @@ extern "C" {
 #define B200MOE_DTYPE_E4M3 1
 #define B200MOE_DTYPE_F16 2
 #define B200MOE_DTYPE_F32 3
+#define B200MOE_DTYPE_E5M2 4
 
 #define B200MOE_ACT_SWIGLU 0
 #define B200MOE_ACT_GEGLU 1
@@ -108,6 +109,9 @@ typedef struct b200moe_gemm_args {
      (gate <= 7, -7 <= up <= 7, D = (up + 1) * gate * sigmoid(1.702 gate) * prob;
      moe_blockscaled_grouped_gemm_glu_bias.py:1414-1487,2702-2716) */
   int32_t act_func;
+  /* element type of A and B (both the same, as the reference demands): B200MOE_DTYPE_E4M3
+     (also when left 0) or B200MOE_DTYPE_E5M2 */
+  int32_t ab_dtype;
 } b200moe_gemm_args;
 
 /*

@@ -8,11 +8,11 @@ import torch
 from oracle import mxfp8_oracle as orc
 
 
-def gen_operands(seed, m_rows, n, k, e, sf_lo=124, sf_hi=131, scale=2.0):
-    """Random E4M3 bytes (uniform(-scale, scale) cast) and E8M0 bytes in [sf_lo, sf_hi)."""
+def gen_operands(seed, m_rows, n, k, e, sf_lo=124, sf_hi=131, scale=2.0, dtype=torch.float8_e4m3fn):
+    """Random E4M3 (or E5M2) bytes (uniform(-scale, scale) cast) and E8M0 bytes in [sf_lo, sf_hi)."""
     g = torch.Generator().manual_seed(seed)
-    a = torch.empty(m_rows, k).uniform_(-scale, scale, generator=g).to(torch.float8_e4m3fn).view(torch.uint8).numpy()
-    b = torch.empty(e, n, k).uniform_(-scale, scale, generator=g).to(torch.float8_e4m3fn).view(torch.uint8).numpy()
+    a = torch.empty(m_rows, k).uniform_(-scale, scale, generator=g).to(dtype).view(torch.uint8).numpy()
+    b = torch.empty(e, n, k).uniform_(-scale, scale, generator=g).to(dtype).view(torch.uint8).numpy()
     kb = (k + 31) // 32
     sfa = torch.randint(sf_lo, sf_hi, (m_rows, kb), generator=g, dtype=torch.int32).to(torch.uint8).numpy()
     sfb = torch.randint(sf_lo, sf_hi, (e, n, kb), generator=g, dtype=torch.int32).to(torch.uint8).numpy()
@@ -27,8 +27,8 @@ def zero_padding_rows(a, groups, aligned):
     return a
 
 
-def dev_fp8(x, device="cuda"):
-    return torch.from_numpy(np.ascontiguousarray(x)).to(device).view(torch.float8_e4m3fn)
+def dev_fp8(x, device="cuda", dtype=torch.float8_e4m3fn):
+    return torch.from_numpy(np.ascontiguousarray(x)).to(device).view(dtype)
 
 
 def dev_sf(sf_bytes, mn, k, l=1, device="cuda"):

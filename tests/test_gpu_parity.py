@@ -739,3 +739,44 @@ def test_launches_are_capturable_in_a_cuda_graph(discrete):
     graph.replay()
     torch.cuda.synchronize()
     assert torch.equal(d2, want2) and not torch.equal(want2, want)
+
+
+@pytest.mark.parametrize("kind", ["fc1", "fc2"])
+@pytest.mark.parametrize("d_fp8", [False, True])
+def test_e5m2_inputs(kind, d_fp8, tile_mode):
+    """A and B in E5M2 (the reference accepts E4M3 or E5M2 operands with E8M0 scales): same kernel,
+    other operand format in the instruction descriptor."""
+    cf = _api()
+    from cudnn_frontend_b200 import ops
+
+    e5 = torch.float8_e5m2
+    groups, n, k = [128, 60, 0, 256], 256, 256
+    e = len(groups)
+    valid, aligned, offs = orc.padded_end_offsets(groups, 128)
+    a, b, sfa, sfb = H.gen_operands(71, valid, n, k, e, dtype=e5)
+    H.zero_padding_rows(a, groups, aligned)
+    rng = np.random.default_rng(71)
+    alpha = rng.integers(1, 3, e).astype(np.float32)
+    prob = rng.uniform(0.1, 1.0, valid).astype(np.float32)
+    ta = H.dev_fp8(a, dtype=e5).view(valid, k, 1)
+    tb = H.dev_fp8(b, dtype=e5).permute(1, 2, 0)
+    common = dict(norm_const_tensor=torch.ones(1, device="cuda") if d_fp8 else None,
+                  prob_tensor=torch.from_numpy(prob).cuda().view(valid, 1, 1),
+                  d_dtype=torch.float8_e4m3fn if d_fp8 else torch.bfloat16, sf_vec_size=32, m_aligned=128)  # fmt: skip
+    toffs, talpha = torch.from_numpy(offs).cuda(), torch.from_numpy(alpha).cuda()
+    if kind == "fc1":
+        res = cf.grouped_gemm_swiglu_wrapper_sm100(ta, tb, H.dev_sf(sfa, valid, k), H.dev_sf(sfb, n, k, e), toffs, talpha, **common)
+        ref = orc.fc1_reference(a, sfa, b, sfb, offs, alpha, prob, norm_const=1.0 if d_fp8 else None, ab_dtype="e5m2")
+    else:
+        res = cf.grouped_gemm_quant_wrapper_sm100(ta, H.dev_sf(sfa, valid, k), toffs, talpha, b_tensor=tb, sfb_tensor=H.dev_sf(sfb, n, k, e),
+                                                  **common)  # fmt: skip
+        ref = orc.fc2_reference(a, sfa, b, sfb, offs, alpha, prob, norm_const=1.0 if d_fp8 else None, ab_dtype="e5m2")
+    torch.cuda.synchronize()
+    assert ops.device_status(clear=True) == 0
+    out = dict(res)
+    out.setdefault("c_tensor", None)
+    _check(kind, out, ref, dict(valid=valid, m_rows=valid, n_out=n // 2 if kind == "fc1" else n, offs=offs, norm=1.0, e=e), d_fp8)
+    # and the result differs from reading the same bytes as E4M3 (the format bits are honoured)
+    if not d_fp8:
+        ref4 = (orc.fc1_reference if kind == "fc1" else orc.fc2_reference)(a, sfa, b, sfb, offs, alpha, prob)
+        assert H.rel_fro(out["d_tensor"][:, :, 0].float().cpu().numpy()[:valid], ref4["d"][:valid]) > 0.1

@@ -30,7 +30,7 @@ def test_library_builds_loads_and_exports_every_declared_symbol():
     for name in declared:
         assert hasattr(lib, name), f"{name} declared in include/b200moe.h but not exported"
     assert set(declared) == set(_lib.EXPORTED_SYMBOLS)
-    assert _lib.load().b200moe_abi_version() == _lib.ABI_VERSION == 3
+    assert _lib.load().b200moe_abi_version() == _lib.ABI_VERSION == 4
     assert _lib.load().b200moe_workspace_bytes(256, 1) == 256 * 256
     assert _lib.load().b200moe_workspace_bytes(256, 0) == 0
 
@@ -95,8 +95,12 @@ def test_fc1_check_support_error_classes():
         cf.GroupedGemmSwigluSm100(**ok, sf_vec_size=32, m_aligned=192).check_support()
     with pytest.raises(ValueError, match="cluster"):
         cf.GroupedGemmSwigluSm100(**ok, sf_vec_size=32, cluster_shape_mn=(3, 1)).check_support()
-    bad = dict(ok, sample_a=torch.empty((256, 128, 1), dtype=torch.float8_e5m2), sample_b=ok["sample_b"].view(torch.float8_e5m2))
+    # FP4 inputs are in the reference's matrix but not built here; E4M3 and E5M2 are
+    bad = dict(ok, sample_a=torch.empty((256, 128, 1), dtype=torch.uint8), sample_b=ok["sample_b"].view(torch.uint8))
     with pytest.raises(NotImplementedError):
+        cf.GroupedGemmSwigluSm100(**bad, sf_vec_size=32).check_support()
+    bad = dict(ok, sample_a=torch.empty((256, 128, 1), dtype=torch.float8_e5m2))  # A and B must agree
+    with pytest.raises(ValueError):
         cf.GroupedGemmSwigluSm100(**bad, sf_vec_size=32).check_support()
     bad = dict(ok, sample_a=torch.empty((128, 256, 1), dtype=torch.float8_e4m3fn).permute(1, 0, 2))
     with pytest.raises(ValueError, match="k-major"):
