@@ -405,11 +405,13 @@ def test_fc1_fc2_chain_matches_layer_oracle(tile_mode):
 # ---------------------------------------------------------------------------------------------
 # fixture produced by the reference's own CuTe-DSL kernel on a B200 (baseline/run_reference_kernels.py)
 # ---------------------------------------------------------------------------------------------
-def test_fc1_is_bit_identical_to_the_reference_kernel_fixture(golden_dir, tile_mode):
+@pytest.mark.parametrize("fixture,ab_dtype", [("reference_kernel_fc1.npz", torch.float8_e4m3fn), ("reference_kernel_fc1_e5m2.npz", torch.float8_e5m2)])
+def test_fc1_is_bit_identical_to_the_reference_kernel_fixture(golden_dir, tile_mode, fixture, ab_dtype):
     """Inputs and outputs of cudnn-frontend's grouped_gemm_swiglu_wrapper_sm100 (fp8 in, E4M3 D,
-    norm_const 1, groups padded to 256) recorded on a B200: C, D, D_col and both scale-factor
-    tensors must match byte for byte (E8M0 round-up, E4M3 RNE-saturate, approx-SiLU order)."""
-    path = os.path.join(golden_dir, "reference_kernel_fc1.npz")
+    norm_const 1, groups padded to 256) recorded on a B200, once with E4M3 and once with E5M2
+    operands: C, D, D_col and both scale-factor tensors must match byte for byte (E8M0 round-up,
+    E4M3 RNE-saturate, approx-SiLU order)."""
+    path = os.path.join(golden_dir, fixture)
     if not os.path.exists(path):
         pytest.skip("reference-kernel fixture not recorded")
     cf = _api()
@@ -424,8 +426,8 @@ def test_fc1_is_bit_identical_to_the_reference_kernel_fixture(golden_dir, tile_m
         shape, stride = ops.sf_shape_stride(mn, kk, l)
         return torch.as_strided(torch.from_numpy(flat).to(dev).view(torch.float8_e8m0fnu), shape, stride)
 
-    a = H.dev_fp8(g["a"]).view(m, k, 1)
-    b = H.dev_fp8(g["b"]).permute(1, 2, 0)
+    a = torch.as_strided(H.dev_fp8(g["a"], dtype=ab_dtype), (m, k, 1), (k, 1, m * k))
+    b = H.dev_fp8(g["b"], dtype=ab_dtype).permute(1, 2, 0)
     out = cf.grouped_gemm_swiglu_wrapper_sm100(
         a, b, sf(g["sfa"], m, k, 1), sf(g["sfb"], n, k, e), torch.from_numpy(g["offsets"]).to(dev), torch.ones(e, device=dev),
         norm_const_tensor=torch.ones(1, device=dev), prob_tensor=torch.from_numpy(g["prob"]).to(dev).view(m, 1, 1),
