@@ -8,7 +8,10 @@ lacks two names the reference's ``python/cudnn/__init__.py`` imports, so the ove
 reference checkout.  baseline/_ref/ is not tracked by git; it exists so that the reference's own
 kernels can be run next to this repository's on a GPU box.
 
-    python baseline/make_ref_overlay.py            # needs /root/reference (or REFERENCE_ROOT)
+    REFERENCE_ROOT=<reference checkout> python baseline/make_ref_overlay.py
+
+Without REFERENCE_ROOT the checkout is looked for in a directory ``reference`` next to this
+repository.
 """
 
 import importlib.util
@@ -16,8 +19,8 @@ import os
 import shutil
 import sys
 
-REF = os.environ.get("REFERENCE_ROOT", "/root/reference")
 HERE = os.path.dirname(os.path.abspath(__file__))
+REF = os.environ.get("REFERENCE_ROOT", os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference"))
 DST = os.path.join(HERE, "_ref", "cudnn")
 
 

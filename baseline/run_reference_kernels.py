@@ -10,8 +10,9 @@ with the reference's constraints (groups padded to 256, mma_tiler (256, 256)), t
 compared (C bf16, E8M0 scale bytes, E4M3 ULP distance) and both are timed with CUDA events
 (3 warm-ups, 10 trials, 256 MiB L2 flush between trials, median and best; back to back; and
 interleaved A B A B in one queue, which is the comparison that is independent of the GPU's power state).  Results go to
-gpurun_out/reference_kernels_<cases>.json; the tiny case's inputs and reference-kernel outputs are saved
-to gpurun_out/reference_kernel_golden.npz so they can be committed as golden vectors.
+<out dir>/reference_kernels_<cases>.json; the tiny cases' inputs and reference-kernel outputs are saved
+to <out dir>/reference_kernel_*golden.npz so they can be committed as golden vectors (tests/golden/).  The
+output directory is B200MOE_OUT_DIR, else the directory named by OUT_DIR_DEFAULT below.
 
     python baseline/run_reference_kernels.py --cases tiny      # one case per process: the reference's
     python baseline/run_reference_kernels.py --cases c2        # wrapper cache does not key on the expert count
@@ -31,6 +32,9 @@ sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
 
 import numpy as np  # noqa: E402
 import torch  # noqa: E402
+
+OUT_DIR_DEFAULT = "gpurun_out"
+OUT_DIR = os.path.join(ROOT, os.environ.get("B200MOE_OUT_DIR", OUT_DIR_DEFAULT))
 
 
 def timed(fn, trials=10, warmup=3):
@@ -185,7 +189,7 @@ def run_case(name, cfg, out):
 
     if name in ("tiny", "tiny_e5m2"):
         np.savez_compressed(
-            os.path.join(ROOT, "gpurun_out", "reference_kernel_golden.npz" if name == "tiny" else "reference_kernel_e5m2_golden.npz"),
+            os.path.join(OUT_DIR, "reference_kernel_golden.npz" if name == "tiny" else "reference_kernel_e5m2_golden.npz"),
             a=p["a"][:, :, 0].view(torch.uint8).cpu().numpy(),
             b=p["b"].permute(2, 0, 1).contiguous().view(torch.uint8).cpu().numpy(),
             sfa=flat(p["sfa"]).cpu().numpy(),
@@ -262,7 +266,7 @@ def run_case_fc2(name, cfg, out):
 
     if name == "fc2_tiny":
         np.savez_compressed(
-            os.path.join(ROOT, "gpurun_out", "reference_kernel_fc2_golden.npz"),
+            os.path.join(OUT_DIR, "reference_kernel_fc2_golden.npz"),
             a=p["a"][:, :, 0].view(torch.uint8).cpu().numpy(),
             b=p["b"].permute(2, 0, 1).contiguous().view(torch.uint8).cpu().numpy(),
             sfa=flat(p["sfa"]).cpu().numpy(),
@@ -330,7 +334,7 @@ def run_case_glu(name, cfg, out):
     print(json.dumps(res), flush=True)
     if name == "glu_tiny":
         np.savez_compressed(
-            os.path.join(ROOT, "gpurun_out", "reference_kernel_glu_golden.npz"),
+            os.path.join(OUT_DIR, "reference_kernel_glu_golden.npz"),
             a=p["a"][:, :, 0].view(torch.uint8).cpu().numpy(),
             b=p["b"].permute(2, 0, 1).contiguous().view(torch.uint8).cpu().numpy(),
             sfa=flat(p["sfa"]).cpu().numpy(),
@@ -377,7 +381,7 @@ def main():
     global PROFILE_ONLY, OWN_FIRST
     PROFILE_ONLY = args.profile
     OWN_FIRST = args.own_first
-    os.makedirs(os.path.join(ROOT, "gpurun_out"), exist_ok=True)
+    os.makedirs(OUT_DIR, exist_ok=True)
     out = []
     for name in args.cases.split(","):
         try:
@@ -385,7 +389,7 @@ def main():
         except Exception as exc:  # keep going: a JIT failure of one case is a result too
             out.append({"case": name, "error": f"{type(exc).__name__}: {exc}"})
             traceback.print_exc()
-        with open(os.path.join(ROOT, "gpurun_out", f"reference_kernels_{args.cases.replace(',', '_')}.json"), "w") as f:
+        with open(os.path.join(OUT_DIR, f"reference_kernels_{args.cases.replace(',', '_')}.json"), "w") as f:
             json.dump(out, f, indent=1)
 
 

@@ -547,7 +547,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         for (int kt = 0; kt < p.k_tiles; ++kt) {
           // the stage's bytes were written by TMA (async proxy) and are made visible by the barrier's
           // transaction count; no tcgen05 fence is needed between this wait and the MMAs
-          // (the verdict is voted so that a wait that gives up takes the whole warp out of the loop)
+          // (the outcome is voted so that a wait that gives up takes the whole warp out of the loop)
           bool landed = mbar_try_wait(full_bar(stage), phase);
           if (!landed) landed = mbar_wait(full_bar(stage), phase, abort_flag, ST_MMA_FULL);
           if (!__all_sync(0xffffffffu, landed)) { ok = false; break; }

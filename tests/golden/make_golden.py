@@ -1,7 +1,7 @@
 """Generate the golden fixtures of tests/golden/ from the reference's own PyTorch code.
 
-Run in a container that has the reference checkout (default /root/reference, override with
-the REFERENCE_ROOT environment variable) and no GPU:
+Run where the reference checkout is available (the REFERENCE_ROOT environment variable, else a
+directory ``reference`` next to this repository); no GPU is needed:
 
     python tests/golden/make_golden.py
 
@@ -17,9 +17,10 @@ inputs, and stores inputs + outputs as small .npz files:
                        (test/python/fe_api/test_grouped_gemm_quant_utils.py:270-345)
 
 The re-quantisation branch of those functions (generate_sfd=True) needs a GPU and the CuTe
-DSL, so it is not part of these fixtures.  reference_kernel_fc1.npz is different: it holds inputs
-and outputs of the reference's own CuTe-DSL FC1 kernel recorded on a B200 by
-baseline/run_reference_kernels.py --cases tiny (after baseline/make_ref_overlay.py).
+DSL, so it is not part of these fixtures.  The reference_kernel_*.npz files are different: they
+hold inputs and outputs of the reference's own CuTe-DSL kernels recorded on a B200 by
+baseline/run_reference_kernels.py (cases tiny, tiny_e5m2, fc2_tiny, glu_tiny; after
+baseline/make_ref_overlay.py).
 """
 
 import os
@@ -28,8 +29,8 @@ import sys
 import numpy as np
 import torch
 
-REF = os.environ.get("REFERENCE_ROOT", "/root/reference")
 HERE = os.path.dirname(os.path.abspath(__file__))
+REF = os.environ.get("REFERENCE_ROOT", os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(HERE))), "reference"))
 
 # The reference's helpers call .cuda() and query the device capability at import time.
 torch.cuda.get_device_capability = lambda *a, **k: (10, 0)
