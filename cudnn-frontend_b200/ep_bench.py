@@ -104,6 +104,19 @@ def run(args, tokens_per_gpu: int = 65536):
 
     x, ids, prob = _synthetic_tokens(tokens_per_gpu, dev, 1000 + rank)
 
+    # Expert placement.  "contiguous": expert e on rank e // (E / G).  "balanced": an untimed
+    # observation of the routing (this step's histogram, summed over ranks) re-shards the experts so
+    # that every rank gets about the same number of rows, as load-aware expert placement does in
+    # production; the weights move between the ranks once, before the warm-up.
+    placement = os.environ.get("B200MOE_EP_PLACEMENT", "contiguous")
+    counts_global = torch.bincount(ids.reshape(-1).long(), minlength=EXPERTS).float()
+    if world > 1:
+        dist.all_reduce(counts_global)
+    per_rank = counts_global.view(world, e_local).sum(1)
+    contiguous_ratio = float(per_rank.max() / per_rank.mean())
+    if placement == "balanced" and world > 1:
+        layer.rebalance(counts_global)
+
     def barrier():
         if world > 1:
             dist.barrier()
@@ -213,7 +226,9 @@ def run(args, tokens_per_gpu: int = 65536):
                 "parallelism": f"ep{world}",
                 "data_path": "peer stores over NVLink from the quantise+dispatch kernel and from the FC2 epilogue; no all-to-all of rows" if path == "peer" else f"NCCL all-to-all, {micro} micro-batch(es)",
                 "l2": "inputs larger than L2 (0.94 GB tokens, 11 GB local weights), no flush",
+                "expert_placement": placement if world > 1 else "single rank",
                 "rows_received_max_over_mean": rows_max.item() / (rows_recv.item() / world),
+                "rows_received_max_over_mean_contiguous_placement": contiguous_ratio,
                 "pct_of_fp8_nominal_4500_per_gpu": 100.0 * value / world / 4500.0,
                 "output_finite": finite,
             },

@@ -131,6 +131,28 @@ def plan_fused(counts_all: torch.Tensor, rank: int, m_aligned: int = 128) -> Fus
     return FusedPlan(delta.to(torch.int32), ends[rank].to(torch.int32), ends[:, -1].contiguous(), total.view(g, e_local).sum(1))
 
 
+def balanced_placement(rows_per_expert, num_ranks: int):
+    """Placement of E experts on G ranks, E / G per rank, that evens out the rows per rank: experts in
+    order of decreasing load, each onto the least-loaded rank that still has a free slot (ties: lower
+    rank).  ``rows_per_expert``: E numbers (e.g. routed rows per expert summed over ranks and over some
+    steps).  Returns ``slot_of_expert`` (list of E ints): expert e lives in physical slot p, i.e. on rank
+    ``p // (E / G)`` as its local expert ``p % (E / G)``.  Deterministic: every rank computes the same."""
+    loads = [float(v) for v in rows_per_expert]
+    e = len(loads)
+    if e % num_ranks != 0:
+        raise ValueError(f"{e} experts cannot be split evenly over {num_ranks} ranks")
+    per = e // num_ranks
+    rank_load = [0.0] * num_ranks
+    rank_used = [0] * num_ranks
+    slot = [0] * e
+    for ex in sorted(range(e), key=lambda i: (-loads[i], i)):
+        r = min((r for r in range(num_ranks) if rank_used[r] < per), key=lambda r: (rank_load[r], r))
+        slot[ex] = r * per + rank_used[r]
+        rank_used[r] += 1
+        rank_load[r] += loads[ex]
+    return slot
+
+
 def exchange_rows(send: torch.Tensor, out_rows: int, in_splits, out_splits, group) -> torch.Tensor:
     """All-to-all of whole rows (first dimension split)."""
     if group is None or dist.get_world_size(group) == 1:
@@ -179,6 +201,9 @@ class ExpertParallelMoE:
         self.alpha = torch.ones(self.e_local, dtype=torch.float32, device=dev)
         self.norm = torch.ones(1, dtype=torch.float32, device=dev)
         self._ops = {}
+        # logical expert id -> physical slot (rank = slot // e_local); None = identity (contiguous sharding)
+        self.slot_of_expert: Optional[torch.Tensor] = None
+        self._slot_host: Optional[List[int]] = None
         self.last_plan: Optional[DispatchPlan] = None
         self.last_rows_received = 0
         # SMs the GEMMs leave to the all-to-all kernels that run beside them in the pipelined path
@@ -220,6 +245,76 @@ class ExpertParallelMoE:
             fc2.execute(h8, sfh, plan.padded_offsets, self.alpha, y_recv.view(-1, h, 1), b_tensor=self.w2, sfb_tensor=self.sfw2,
                         prob_tensor=prob3, d_row_map=plan.row_map)  # fmt: skip
         return y_recv
+
+    # ------------------------------------------------------------------------------------------
+    # expert placement
+    # ------------------------------------------------------------------------------------------
+    def _physical_ids(self, topk_ids: torch.Tensor) -> torch.Tensor:
+        """Logical expert ids of the router -> physical slots of the current placement."""
+        if self.slot_of_expert is None:
+            return topk_ids
+        return self.slot_of_expert[topk_ids.long()]
+
+    def rebalance(self, rows_per_expert: torch.Tensor) -> List[int]:
+        """Re-shard the experts so that every rank gets about the same number of rows, and move the
+        weights accordingly (collective: every rank calls it with the same ``rows_per_expert [E]``, e.g.
+        the routing histogram summed over ranks and over a few steps).  Afterwards ``forward*`` maps the
+        router's expert ids to the new slots; results do not change, only which rank computes them.
+        Returns the new ``slot_of_expert`` list."""
+        loads = rows_per_expert.detach().to("cpu", torch.float64).tolist()
+        new = balanced_placement(loads, self.world)
+        old = self._slot_host if self._slot_host is not None else list(range(self.num_experts))
+        if new != old:
+            self._move_weights(old, new)
+        self._slot_host = new
+        self.slot_of_expert = torch.tensor(new, dtype=torch.int32, device=self.w1.device)
+        return new
+
+    def _move_weights(self, old: List[int], new: List[int]) -> None:
+        """Weights of logical expert e move from slot old[e] to slot new[e].  One all-to-all per weight
+        tensor over whole experts; both sides order the experts they exchange by destination slot."""
+        el, g = self.e_local, self.world
+        rank = 0 if self.group is None else dist.get_rank(self.group)
+        # experts I hold now, by destination rank then destination slot; experts I will hold, by source
+        # rank then destination slot: the same order on the sending and the receiving side
+        mine = [e for e in range(self.num_experts) if old[e] // el == rank]
+        send = sorted(mine, key=lambda e: (new[e] // el, new[e]))
+        recv = sorted((e for e in range(self.num_experts) if new[e] // el == rank), key=lambda e: (old[e] // el, new[e]))
+        in_splits = [sum(1 for e in send if new[e] // el == d) for d in range(g)]
+        out_splits = [sum(1 for e in recv if old[e] // el == s_) for s_ in range(g)]
+        send_idx = torch.tensor([old[e] % el for e in send], dtype=torch.int64, device=self.w1.device)
+        recv_idx = torch.tensor([new[e] % el for e in recv], dtype=torch.int64, device=self.w1.device)
+
+        def move(per_expert: torch.Tensor) -> torch.Tensor:
+            """``per_expert [E_local, bytes]`` uint8 -> the same shape in the new placement."""
+            staged = per_expert.index_select(0, send_idx)
+            if g > 1:
+                got = torch.empty_like(staged)
+                dist.all_to_all_single(got, staged, output_split_sizes=out_splits, input_split_sizes=in_splits, group=self.group)
+            else:
+                got = staged
+            out = torch.empty_like(per_expert)
+            out.index_copy_(0, recv_idx, got)
+            return out
+
+        def flat_sf(sf: torch.Tensor) -> torch.Tensor:
+            t = sf.view(torch.uint8)
+            return torch.as_strided(t, (t.numel(),), (1,)).view(el, -1)
+
+        from . import ops
+
+        n1, k1 = self.w1.shape[0], self.w1.shape[1]
+        n2, k2 = self.w2.shape[0], self.w2.shape[1]
+        w1 = move(self.w1.permute(2, 0, 1).contiguous().view(torch.uint8).view(el, -1)).view(torch.float8_e4m3fn).view(el, n1, k1)
+        w2 = move(self.w2.permute(2, 0, 1).contiguous().view(torch.uint8).view(el, -1)).view(torch.float8_e4m3fn).view(el, n2, k2)
+        sf1 = move(flat_sf(self.sfw1).contiguous())
+        sf2 = move(flat_sf(self.sfw2).contiguous())
+        self.w1, self.w2 = w1.permute(1, 2, 0), w2.permute(1, 2, 0)
+        shape, stride = ops.sf_shape_stride(n1, k1, el)
+        self.sfw1 = torch.as_strided(sf1.view(-1).view(torch.float8_e8m0fnu), shape, stride)
+        shape, stride = ops.sf_shape_stride(n2, k2, el)
+        self.sfw2 = torch.as_strided(sf2.view(-1).view(torch.float8_e8m0fnu), shape, stride)
+        self._ops = {}  # operator objects hold samples of the old weight tensors
 
     # ------------------------------------------------------------------------------------------
     # peer-memory path: no all-to-all of rows at all
@@ -303,7 +398,7 @@ class ExpertParallelMoE:
         peer = self._peer_setup(t, k, capacity_factor)
         bufs, cap, slots = peer["bufs"], peer["cap"], peer["slots"]
 
-        ids = topk_ids.contiguous()
+        ids = self._physical_ids(topk_ids).contiguous()
         counts, _, local_row = moe.route(ids.view(-1), self.num_experts, 1)
         bufs["rec"].local.fill_(0xFF)  # a record nobody writes reads as "padding row, returns nowhere"
         if g > 1:
@@ -360,6 +455,7 @@ class ExpertParallelMoE:
 
         if not x.is_cuda:
             raise RuntimeError("ExpertParallelMoE.forward needs CUDA tensors")
+        topk_ids = self._physical_ids(topk_ids)
         t, k = topk_ids.shape
         n = max(1, min(micro_batches, t))
         bounds = [(i * t // n, (i + 1) * t // n) for i in range(n)]
@@ -397,6 +493,7 @@ class ExpertParallelMoE:
 
         if not x.is_cuda:
             raise RuntimeError("ExpertParallelMoE.forward needs CUDA tensors")
+        topk_ids = self._physical_ids(topk_ids)
         t, k = topk_ids.shape
         h = self.hidden
         dev = x.device

@@ -190,3 +190,61 @@ def test_peer_memory_plan_round_trip_world_size_2():
     ret = mgr.dict()
     mp.spawn(_peer_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
     assert all(ret.get(r) for r in range(world)), dict(ret)
+
+
+def _move_worker(rank, world, port, ret):
+    """Weight movement of ExpertParallelMoE.rebalance on CPU ranks: every expert's weight bytes carry
+    its logical id, so after the move each slot can be checked against the new placement."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from cudnn_frontend_b200 import ops
+        from cudnn_frontend_b200.ep_layer import ExpertParallelMoE, balanced_placement
+
+        experts, el = 8, 8 // world
+        n1, k1, n2, k2 = 256, 128, 128, 128
+        layer = object.__new__(ExpertParallelMoE)  # the constructor wants CUDA tensors; only the movement is under test
+        layer.group, layer.world, layer.e_local, layer.num_experts = dist.group.WORLD, world, el, experts
+        layer._ops = {}
+
+        def weights(n, k, tag):
+            w = torch.empty((el, n, k), dtype=torch.uint8)
+            sf_shape, sf_stride = ops.sf_shape_stride(n, k, el)
+            per = (n // 128) * ((k // 32 + 3) // 4) * 512
+            sf = torch.empty(el * per, dtype=torch.uint8)
+            for i in range(el):
+                w[i] = rank * el + i + tag
+                sf[i * per : (i + 1) * per] = 100 + rank * el + i + tag
+            return w.view(torch.float8_e4m3fn).permute(1, 2, 0), torch.as_strided(sf.view(torch.float8_e8m0fnu), sf_shape, sf_stride), per
+
+        layer.w1, layer.sfw1, per1 = weights(n1, k1, 0)
+        layer.w2, layer.sfw2, per2 = weights(n2, k2, 50)
+        old = list(range(experts))
+        new = balanced_placement([5, 1, 9, 2, 7, 3, 8, 4], world)
+        layer._move_weights(old, new)
+        ok = True
+        for e in range(experts):
+            if new[e] // el != rank:
+                continue
+            slot = new[e] % el
+            ok &= bool((layer.w1.permute(2, 0, 1)[slot].view(torch.uint8) == e).all())
+            ok &= bool((layer.w2.permute(2, 0, 1)[slot].view(torch.uint8) == e + 50).all())
+            f1 = torch.as_strided(layer.sfw1.view(torch.uint8), (layer.sfw1.numel(),), (1,)).view(el, per1)
+            f2 = torch.as_strided(layer.sfw2.view(torch.uint8), (layer.sfw2.numel(),), (1,)).view(el, per2)
+            ok &= bool((f1[slot] == 100 + e).all()) and bool((f2[slot] == 150 + e).all())
+        # and back again
+        layer._move_weights(new, old)
+        for i in range(el):
+            ok &= bool((layer.w1.permute(2, 0, 1)[i].view(torch.uint8) == rank * el + i).all())
+        ret[rank] = ok
+    finally:
+        dist.destroy_process_group()
+
+
+def test_rebalance_moves_every_expert_to_its_new_slot_world_size_2():
+    world = 2
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_move_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
+    assert all(ret.get(r) for r in range(world)), dict(ret)

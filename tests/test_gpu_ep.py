@@ -97,6 +97,24 @@ def test_peer_buffers_grow_when_a_step_needs_more_rows():
     layer.release_peer_buffers()
 
 
+def test_rebalanced_layer_computes_the_same_function():
+    """Moving experts to other slots (here within one rank) changes where rows are computed, not what."""
+    from cudnn_frontend_b200.ep_layer import ExpertParallelMoE
+
+    x, ids, prob, w1, sfw1, w2, sfw2 = _inputs(6, "cuda")
+    layer = ExpertParallelMoE(w1, sfw1, w2, sfw2, E)
+    y = layer(x, ids, prob)
+    counts = torch.bincount(ids.reshape(-1).long(), minlength=E)
+    counts[3] += 1000  # make the order of the placement differ from the identity
+    slot = layer.rebalance(counts)
+    assert sorted(slot) == list(range(E)) and slot != list(range(E))
+    y2 = layer(x, ids, prob)
+    y3 = layer.forward_fused(x, ids, prob)
+    torch.cuda.synchronize()
+    assert torch.equal(y, y2) and torch.equal(y, y3)
+    layer.release_peer_buffers()
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
@@ -136,13 +154,20 @@ def _ep_worker(rank, world, port, ret):
         yp = layer.forward_pipelined(x, ids, prob, micro_batches=3)
         yf = layer.forward_fused(x, ids, prob)  # rows cross NVLink by peer stores, no all-to-all
         yf2 = layer.forward_fused(x, ids, prob)
+        # re-shard by load (weights cross ranks) and run again: same function
+        counts = torch.bincount(ids.reshape(-1).long(), minlength=E).float()
+        dist.all_reduce(counts)
+        counts[1] += 500
+        layer.rebalance(counts)
+        yr = layer.forward_fused(x, ids, prob)
+        yr2 = layer(x, ids, prob)
         torch.cuda.synchronize()
         from cudnn_frontend_b200 import ops as _ops
 
         status = _ops.device_status(clear=True)
         layer.release_peer_buffers()
         # row order inside an expert group differs between the runs, the per-row maths does not
-        ret[rank] = bool(torch.equal(y, y1)) and bool(torch.equal(yp, y1)) and bool(torch.equal(yf, y1)) and bool(torch.equal(yf2, y1)) and status == 0
+        ret[rank] = bool(torch.equal(y, y1)) and bool(torch.equal(yp, y1)) and bool(torch.equal(yf, y1)) and bool(torch.equal(yf2, y1)) and bool(torch.equal(yr, y1)) and bool(torch.equal(yr2, y1)) and status == 0
     finally:
         dist.destroy_process_group()
 

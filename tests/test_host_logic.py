@@ -273,3 +273,24 @@ def test_oracle_geglu_and_bias_follow_the_reference_formulas():
     np.testing.assert_allclose(cb[3:], c[3:] + bias[:, 1], rtol=0, atol=0)
     cb2 = orc.add_bias(c, bias, offs, row_scale=prob)
     np.testing.assert_allclose(cb2[3:], c[3:] + bias[:, 1][None, :] * prob[3:, None], rtol=1e-6)
+
+
+def test_balanced_placement_fills_every_rank_and_evens_out_rows():
+    import numpy as np
+
+    from cudnn_frontend_b200.ep_layer import balanced_placement
+
+    rng = np.random.default_rng(2)
+    loads = (1000.0 / np.arange(1, 65) ** 1.2)[rng.permutation(64)]
+    slot = balanced_placement(loads, 8)
+    assert sorted(slot) == list(range(64))  # a permutation: 8 experts on each of the 8 ranks
+    per_rank = np.zeros(8)
+    for e, p in enumerate(slot):
+        per_rank[p // 8] += loads[e]
+    contiguous = loads.reshape(8, 8).sum(1)
+    assert per_rank.max() / per_rank.mean() < contiguous.max() / contiguous.mean()
+    # the heaviest expert alone is the floor of the busiest rank
+    assert per_rank.max() <= max(loads.max(), per_rank.mean()) * 1.35
+    assert balanced_placement(loads, 8) == slot  # deterministic
+    with pytest.raises(ValueError):
+        balanced_placement(loads[:63], 8)
