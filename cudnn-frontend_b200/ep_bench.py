@@ -4,7 +4,8 @@ Per rank: 65536 tokens (bf16 ~ N(0,1), hidden 7168), top-8 Zipf(1.2) routing ove
 sharded 256/G per rank, MXFP8 weights ~ N(0, 0.02).  One step = the whole layer (quantise and
 dispatch to the owning ranks, FC1 + SwiGLU, FC2 with gating, return of the result rows, top-k sum);
 rows cross NVLink by peer stores from the kernels (default) or by NCCL all-to-all
-(B200MOE_EP_PATH=nccl).  Weak scaling: tokens
+(B200MOE_EP_PATH=nccl).  Experts are placed by load (default: an untimed observation of the routing
+re-shards them once, weights move between ranks) or contiguously (B200MOE_EP_PLACEMENT=contiguous).  Weak scaling: tokens
 per GPU are fixed.  FLOPs = 2 * routed rows * (N1 K1 + N2 K2) summed over ranks, true rows only.
 """
 
@@ -108,7 +109,7 @@ def run(args, tokens_per_gpu: int = 65536):
     # observation of the routing (this step's histogram, summed over ranks) re-shards the experts so
     # that every rank gets about the same number of rows, as load-aware expert placement does in
     # production; the weights move between the ranks once, before the warm-up.
-    placement = os.environ.get("B200MOE_EP_PLACEMENT", "contiguous")
+    placement = os.environ.get("B200MOE_EP_PLACEMENT", "balanced")
     counts_global = torch.bincount(ids.reshape(-1).long(), minlength=EXPERTS).float()
     if world > 1:
         dist.all_reduce(counts_global)
