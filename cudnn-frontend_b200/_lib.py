@@ -14,7 +14,7 @@ from . import _build
 E_NULL, E_SHAPE, E_ALIGN, E_UNSUPPORTED, E_WORKSPACE, E_DEVICE = -1, -2, -3, -4, -5, -6
 DTYPE_BF16, DTYPE_E4M3, DTYPE_F16, DTYPE_F32, DTYPE_E5M2 = 0, 1, 2, 3, 4
 ACT_SWIGLU, ACT_GEGLU = 0, 1
-ABI_VERSION = 4  # b200moe_abi_version() of the header these declarations mirror
+ABI_VERSION = 5  # b200moe_abi_version() of the header these declarations mirror
 FLAG_DISCRETE_COL_SFD = 1
 FLAG_TILE_SINGLE = 2
 FLAG_TILE_PAIR = 4
@@ -55,6 +55,7 @@ class GemmArgs(Structure):
         ("bias_dtype", c_int32),
         ("act_func", c_int32),
         ("ab_dtype", c_int32),
+        ("c_dtype", c_int32),
     ]
 
 

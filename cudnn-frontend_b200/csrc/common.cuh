@@ -413,6 +413,24 @@ __device__ __forceinline__ uint32_t bf16x2_from_float(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
+// two float32 -> packed E5M2 pair, RNE, saturating
+__device__ __forceinline__ uint32_t e5m2x2_from_float(float lo, float hi) {
+  uint16_t out;
+  asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;" : "=h"(out) : "f"(hi), "f"(lo));
+  return (uint32_t)out;
+}
+// four float32 -> four FP8 bytes in the output's format (warp-uniform choice)
+__device__ __forceinline__ uint32_t fp8x4_from_float(float a, float b, float c, float d, bool e5m2) {
+  return e5m2 ? (e5m2x2_from_float(a, b) | (e5m2x2_from_float(c, d) << 16)) : e4m3x4_from_float(a, b, c, d);
+}
+// two float32 -> packed 16-bit pair, bf16 or fp16 (warp-uniform choice)
+__device__ __forceinline__ uint32_t pack16x2_from_float(float lo, float hi, bool f16) {
+  if (f16) {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+  return bf16x2_from_float(lo, hi);
+}
 
 // Scale applied to a block before the E4M3 conversion: norm / sf, clamped to FLT_MAX.
 __device__ __forceinline__ float quant_scale(float norm_const, float sf_value) {

@@ -126,6 +126,9 @@ struct GemmParams {
   int sfd_row_rest_k;  // ceil(ceil(n_out / 32) / 4)
   int sfd_col_rest_k;  // ceil(ceil(m_rows / 32) / 4)
   int d_is_fp8;
+  int d_e5m2;         // FP8 D (and D_col) in E5M2 instead of E4M3
+  float d_rcp_limit;  // 1/448 (E4M3) or 1/128 (E5M2)
+  int d_f16, c_f16;   // 16-bit D / C in fp16 instead of bf16
   int discrete_col_sfd;
   int wide_stores;     // every output row segment of 32 bytes is 32-byte aligned
   const void* bias;    // optional [E][N] (element (n, e) at e * N + n), added after alpha
@@ -189,42 +192,50 @@ __device__ __forceinline__ void store_32B(void* dst, uint4 lo, uint4 hi, bool wi
   }
 }
 
-__device__ __forceinline__ void store_bf16x32(__nv_bfloat16* dst, const float* v, bool wide) {
+// 32 values as bf16 (or fp16 when f16 is set): the two 16-bit types share pitch and alignment
+__device__ __forceinline__ void store_bf16x32(__nv_bfloat16* dst, const float* v, bool wide, bool f16 = false) {
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
     uint4 lo, hi;
-    lo.x = bf16x2_from_float(v[16 * i + 0], v[16 * i + 1]);
-    lo.y = bf16x2_from_float(v[16 * i + 2], v[16 * i + 3]);
-    lo.z = bf16x2_from_float(v[16 * i + 4], v[16 * i + 5]);
-    lo.w = bf16x2_from_float(v[16 * i + 6], v[16 * i + 7]);
-    hi.x = bf16x2_from_float(v[16 * i + 8], v[16 * i + 9]);
-    hi.y = bf16x2_from_float(v[16 * i + 10], v[16 * i + 11]);
-    hi.z = bf16x2_from_float(v[16 * i + 12], v[16 * i + 13]);
-    hi.w = bf16x2_from_float(v[16 * i + 14], v[16 * i + 15]);
+    lo.x = pack16x2_from_float(v[16 * i + 0], v[16 * i + 1], f16);
+    lo.y = pack16x2_from_float(v[16 * i + 2], v[16 * i + 3], f16);
+    lo.z = pack16x2_from_float(v[16 * i + 4], v[16 * i + 5], f16);
+    lo.w = pack16x2_from_float(v[16 * i + 6], v[16 * i + 7], f16);
+    hi.x = pack16x2_from_float(v[16 * i + 8], v[16 * i + 9], f16);
+    hi.y = pack16x2_from_float(v[16 * i + 10], v[16 * i + 11], f16);
+    hi.z = pack16x2_from_float(v[16 * i + 12], v[16 * i + 13], f16);
+    hi.w = pack16x2_from_float(v[16 * i + 14], v[16 * i + 15], f16);
     store_32B(dst + 16 * i, lo, hi, wide);
   }
 }
 
-__device__ __forceinline__ void store_e4m3x32(uint8_t* dst, const float* v, float scale, bool wide) {
+__device__ __forceinline__ void store_e4m3x32(uint8_t* dst, const float* v, float scale, bool wide, bool e5m2 = false) {
   uint4 o[2];
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
-    o[i].x = e4m3x4_from_float(v[16 * i + 0] * scale, v[16 * i + 1] * scale, v[16 * i + 2] * scale, v[16 * i + 3] * scale);
-    o[i].y = e4m3x4_from_float(v[16 * i + 4] * scale, v[16 * i + 5] * scale, v[16 * i + 6] * scale, v[16 * i + 7] * scale);
-    o[i].z = e4m3x4_from_float(v[16 * i + 8] * scale, v[16 * i + 9] * scale, v[16 * i + 10] * scale, v[16 * i + 11] * scale);
-    o[i].w = e4m3x4_from_float(v[16 * i + 12] * scale, v[16 * i + 13] * scale, v[16 * i + 14] * scale, v[16 * i + 15] * scale);
+    o[i].x = fp8x4_from_float(v[16 * i + 0] * scale, v[16 * i + 1] * scale, v[16 * i + 2] * scale, v[16 * i + 3] * scale, e5m2);
+    o[i].y = fp8x4_from_float(v[16 * i + 4] * scale, v[16 * i + 5] * scale, v[16 * i + 6] * scale, v[16 * i + 7] * scale, e5m2);
+    o[i].z = fp8x4_from_float(v[16 * i + 8] * scale, v[16 * i + 9] * scale, v[16 * i + 10] * scale, v[16 * i + 11] * scale, e5m2);
+    o[i].w = fp8x4_from_float(v[16 * i + 12] * scale, v[16 * i + 13] * scale, v[16 * i + 14] * scale, v[16 * i + 15] * scale, e5m2);
   }
   store_32B(dst, o[0], o[1], wide);
 }
 
-// Row-wise MXFP8 of one 32-element block: returns the E8M0 byte, stores 32 E4M3 bytes.
-__device__ __forceinline__ uint32_t quant_row_block(uint8_t* dst, const float* v, float norm_const, bool wide) {
+// Output quantisation format: reciprocal of the value the block maximum is mapped to (the reference's
+// get_dtype_rcp_limits: 1/448 for E4M3, 1/128 for E5M2) and the byte format.
+struct OutFormat {
+  float rcp_limit;
+  bool e5m2;
+};
+
+// Row-wise MXFP8 of one 32-element block: returns the E8M0 byte, stores 32 FP8 bytes.
+__device__ __forceinline__ uint32_t quant_row_block(uint8_t* dst, const float* v, float norm_const, bool wide, OutFormat fmt) {
   float amax = 0.f;
 #pragma unroll
   for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(v[i]));
-  const float pv = amax * (1.0f / 448.0f) * norm_const;
+  const float pv = amax * fmt.rcp_limit * norm_const;
   const uint32_t sf = e8m0_from_float(pv);
-  store_e4m3x32(dst, v, quant_scale(norm_const, e8m0_to_float(sf)), wide);
+  store_e4m3x32(dst, v, quant_scale(norm_const, e8m0_to_float(sf)), wide, fmt.e5m2);
   return sf;
 }
 
@@ -236,7 +247,8 @@ __device__ __forceinline__ uint32_t quant_row_block(uint8_t* dst, const float* v
 // (lane ^ d), so 16 + 8 + 4 + 2 + 1 shuffles leave lane i with the maximum of column i (a
 // butterfly per column would take 160).  Each lane then derives the scale of its own column
 // once, and 32 broadcasts hand the scales round.
-__device__ __forceinline__ uint32_t quant_col_block(uint8_t* dst, bool do_store, const float* v, float norm_const, bool wide) {
+__device__ __forceinline__ uint32_t quant_col_block(uint8_t* dst, bool do_store, const float* v, float norm_const, bool wide,
+                                                    OutFormat fmt) {
   const uint32_t lane = lane_id();
   float m16[16], m8[8], m4[4], m2[2];
   {
@@ -278,7 +290,7 @@ __device__ __forceinline__ uint32_t quant_col_block(uint8_t* dst, bool do_store,
   const bool up1 = lane & 1;
   const float cmax = fmaxf(up1 ? m2[1] : m2[0], __shfl_xor_sync(0xffffffffu, up1 ? m2[0] : m2[1], 1));
   // scale of column `lane`
-  const float pv = cmax * (1.0f / 448.0f) * norm_const;
+  const float pv = cmax * fmt.rcp_limit * norm_const;
   const uint32_t my_sf = e8m0_from_float(pv);
   const float sfv = e8m0_to_float(my_sf);
   float my_sc = sfv == 0.0f ? 0.0f : norm_const * rcp_approx(sfv);
@@ -289,7 +301,7 @@ __device__ __forceinline__ uint32_t quant_col_block(uint8_t* dst, bool do_store,
     float s[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) s[j] = v[i + j] * __shfl_sync(0xffffffffu, my_sc, i + j);
-    packed[i >> 2] = e4m3x4_from_float(s[0], s[1], s[2], s[3]);
+    packed[i >> 2] = fp8x4_from_float(s[0], s[1], s[2], s[3], fmt.e5m2);
   }
   if (do_store)
     store_32B(dst, make_uint4(packed[0], packed[1], packed[2], packed[3]), make_uint4(packed[4], packed[5], packed[6], packed[7]), wide);
@@ -618,6 +630,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     const int r_in_tile = quarter * 32 + lane;
     const float norm_const = p.norm_const ? *p.norm_const : 1.0f;
     const bool wide = p.wide_stores != 0;
+    const bool c_f16 = p.c_f16 != 0, d_f16 = p.d_f16 != 0;
+    const OutFormat out_fmt = {p.d_rcp_limit, p.d_e5m2 != 0};
     uint8_t* const stage_row = smem + C::STAGING_OFF + ew * STAGING_WARP_BYTES + lane * STAGING_ROW_BYTES;  // kBulk only
     const uint32_t overlap_target = kPair ? map_to_cta(overlap_bar, 0) : overlap_bar;
     auto arrive_overlap = [&]() {
@@ -689,8 +703,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             for (int j = 0; j < 32; ++j) { g[j] *= alpha; u[j] *= alpha; }
           }
           if (p.c && row_ok) {
-            store_bf16x32(p.c + (int64_t)row * p.n + cn, g, wide);
-            store_bf16x32(p.c + (int64_t)row * p.n + cn + 32, u, wide);
+            store_bf16x32(p.c + (int64_t)row * p.n + cn, g, wide, c_f16);
+            store_bf16x32(p.c + (int64_t)row * p.n + cn + 32, u, wide, c_f16);
           }
           if (p.act_geglu) {
             // GeGLU of the reference: gate <= 7, -7 <= up <= 7 (after the C store),
@@ -716,10 +730,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 #pragma unroll
               for (int j = 0; j < 32; ++j) thread_amax = fmaxf(thread_amax, fabsf(g[j]));
             }
-            if (row_ok && out_row >= 0) store_bf16x32(d_rows + (int64_t)out_row * p.n_out + dn, g, wide);
+            if (row_ok && out_row >= 0) store_bf16x32(d_rows + (int64_t)out_row * p.n_out + dn, g, wide, d_f16);
           } else {
             if (row_ok) {
-              const uint32_t sf = quant_row_block(reinterpret_cast<uint8_t*>(p.d) + (int64_t)row * p.n_out + dn, g, norm_const, wide);
+              const uint32_t sf = quant_row_block(reinterpret_cast<uint8_t*>(p.d) + (int64_t)row * p.n_out + dn, g, norm_const, wide, out_fmt);
               sf_row_word |= sf << (8 * (half * 2 + pp));
             }
             if (p.d_col) {
@@ -728,7 +742,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 #pragma unroll
                 for (int j = 0; j < 32; ++j) g[j] = 0.f;
               }
-              const uint32_t sfc = quant_col_block(p.d_col + (int64_t)row * p.n_out + dn, row_ok, g, norm_const, wide);
+              const uint32_t sfc = quant_col_block(p.d_col + (int64_t)row * p.n_out + dn, row_ok, g, norm_const, wide, out_fmt);
               int64_t blk_base = 0;
               int rb = (tile.row0 >> 5) + quarter;
               int rest = p.sfd_col_rest_k;
@@ -795,18 +809,18 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
                 uint4 o;
-                o.x = bf16x2_from_float(v[8 * q + 0], v[8 * q + 1]);
-                o.y = bf16x2_from_float(v[8 * q + 2], v[8 * q + 3]);
-                o.z = bf16x2_from_float(v[8 * q + 4], v[8 * q + 5]);
-                o.w = bf16x2_from_float(v[8 * q + 6], v[8 * q + 7]);
+                o.x = pack16x2_from_float(v[8 * q + 0], v[8 * q + 1], d_f16);
+                o.y = pack16x2_from_float(v[8 * q + 2], v[8 * q + 3], d_f16);
+                o.z = pack16x2_from_float(v[8 * q + 4], v[8 * q + 5], d_f16);
+                o.w = pack16x2_from_float(v[8 * q + 6], v[8 * q + 7], d_f16);
                 st[q] = o;
               }
             } else {
-              if (row_ok && out_row >= 0) store_bf16x32(d_rows + (int64_t)out_row * p.n_out + dn, v, wide);
+              if (row_ok && out_row >= 0) store_bf16x32(d_rows + (int64_t)out_row * p.n_out + dn, v, wide, d_f16);
             }
           } else {
             if (row_ok) {
-              const uint32_t sf = quant_row_block(reinterpret_cast<uint8_t*>(p.d) + (int64_t)row * p.n_out + dn, v, norm_const, wide);
+              const uint32_t sf = quant_row_block(reinterpret_cast<uint8_t*>(p.d) + (int64_t)row * p.n_out + dn, v, norm_const, wide, out_fmt);
               sf_row_word |= sf << (8 * bb);
             }
             if (p.d_col) {
@@ -814,7 +828,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 #pragma unroll
                 for (int j = 0; j < 32; ++j) v[j] = 0.f;
               }
-              const uint32_t sfc = quant_col_block(p.d_col + (int64_t)row * p.n_out + dn, row_ok, v, norm_const, wide);
+              const uint32_t sfc = quant_col_block(p.d_col + (int64_t)row * p.n_out + dn, row_ok, v, norm_const, wide, out_fmt);
               int64_t blk_base = 0;
               int rb = (tile.row0 >> 5) + quarter;
               int rest = p.sfd_col_rest_k;
@@ -1064,11 +1078,14 @@ static int run_gemm(int epi, const b200moe_gemm_args* a, void* stream_v) {
   if (epi == EPI_FC2 && a->n % 32 != 0)
     return fail(B200MOE_E_SHAPE, "%s: n (%lld) must be a multiple of 32", op, (long long)a->n);
   if (a->n * a->k > (1ll << 40)) return fail(B200MOE_E_SHAPE, "%s: n*k too large", op);
-  const bool d_fp8 = a->d_dtype == B200MOE_DTYPE_E4M3;
+  const bool d_fp8 = a->d_dtype == B200MOE_DTYPE_E4M3 || a->d_dtype == B200MOE_DTYPE_E5M2;
   if (a->d_row_map && (d_fp8 || a->c)) return fail(B200MOE_E_UNSUPPORTED, "%s: d_row_map needs a bf16 D and no C", op);
   if (a->d_peer_ptrs && (!a->d_row_map || a->d_peer_slots <= 0))
     return fail(B200MOE_E_SHAPE, "%s: d_peer_ptrs needs d_row_map and a positive d_peer_slots", op);
-  if (a->d_dtype != B200MOE_DTYPE_BF16 && !d_fp8) return fail(B200MOE_E_UNSUPPORTED, "%s: d_dtype %d", op, a->d_dtype);
+  if (a->d_dtype != B200MOE_DTYPE_BF16 && a->d_dtype != B200MOE_DTYPE_F16 && !d_fp8)
+    return fail(B200MOE_E_UNSUPPORTED, "%s: d_dtype %d", op, a->d_dtype);
+  if (a->c_dtype != B200MOE_DTYPE_BF16 && a->c_dtype != B200MOE_DTYPE_F16)
+    return fail(B200MOE_E_UNSUPPORTED, "%s: c_dtype %d (bf16 and fp16 are built)", op, a->c_dtype);
   if (a->ab_dtype != 0 && a->ab_dtype != B200MOE_DTYPE_E4M3 && a->ab_dtype != B200MOE_DTYPE_E5M2)
     return fail(B200MOE_E_UNSUPPORTED, "%s: ab_dtype %d (E4M3 and E5M2 are built)", op, a->ab_dtype);
   if (a->act_func != B200MOE_ACT_SWIGLU && a->act_func != B200MOE_ACT_GEGLU)
@@ -1129,6 +1146,10 @@ static int run_gemm(int epi, const b200moe_gemm_args* a, void* stream_v) {
   p.sfd_row_rest_k = ((p.n_out + 31) / 32 + 3) / 4;
   p.sfd_col_rest_k = ((p.m_rows + 31) / 32 + 3) / 4;
   p.d_is_fp8 = d_fp8;
+  p.d_e5m2 = a->d_dtype == B200MOE_DTYPE_E5M2;
+  p.d_rcp_limit = p.d_e5m2 ? 1.0f / 128.0f : 1.0f / 448.0f;
+  p.d_f16 = a->d_dtype == B200MOE_DTYPE_F16;
+  p.c_f16 = a->c_dtype == B200MOE_DTYPE_F16;
   p.discrete_col_sfd = (a->flags & B200MOE_FLAG_DISCRETE_COL_SFD) ? 1 : 0;
   {
     // 256-bit stores need 32-byte aligned bases and row pitches that keep a 32-column block aligned
@@ -1301,6 +1322,6 @@ int b200moe_device_status(int clear) {
   return v;
 }
 
-int b200moe_abi_version(void) { return 4; }
+int b200moe_abi_version(void) { return 5; }
 
 }  // extern "C"

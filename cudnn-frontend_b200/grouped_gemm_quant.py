@@ -201,9 +201,9 @@ class GroupedGemmQuantSm100(OperatorBase):
         self._not_implemented_error_if(self.b_major != "k", "N-major B is not built; pass K-major weights")
         self._not_implemented_error_if(self.ab_dtype not in (torch.float8_e4m3fn, torch.float8_e5m2), f"only MXFP8 (E4M3 or E5M2) inputs are built, got {self.ab_dtype}")
         self._not_implemented_error_if(self.sf_dtype != torch.float8_e8m0fnu, f"only E8M0 scale factors are built, got {self.sf_dtype}")
-        self._not_implemented_error_if(self.d_dtype not in (torch.bfloat16, torch.float8_e4m3fn), f"only bf16 and E4M3 D are built, got {self.d_dtype}")
-        self._not_implemented_error_if(self.generate_sfd and self.d_dtype != torch.float8_e4m3fn, "scale-factor generation with a 16-bit D is not built")
-        self._not_implemented_error_if(not self.generate_sfd and self.d_dtype == torch.float8_e4m3fn, "E4M3 D needs sfd_row, sfd_col and norm_const")
+        self._not_implemented_error_if(self.d_dtype not in (torch.bfloat16, torch.float16, torch.float8_e4m3fn, torch.float8_e5m2), f"only bf16, fp16, E4M3 and E5M2 D are built, got {self.d_dtype}")
+        self._not_implemented_error_if(self.generate_sfd and self.d_dtype not in (torch.float8_e4m3fn, torch.float8_e5m2), "scale-factor generation with a 16-bit D is not built")
+        self._not_implemented_error_if(not self.generate_sfd and self.d_dtype in (torch.float8_e4m3fn, torch.float8_e5m2), "FP8 D needs sfd_row, sfd_col and norm_const")
         self._value_error_if(n % 32 != 0, f"n must be a multiple of 32, got {n}")
         self._n, self._k = n, k
 
@@ -266,7 +266,7 @@ class GroupedGemmQuantSm100(OperatorBase):
             raise ValueError("dense mode needs b_tensor and sfb_tensor")
         if prob_tensor is None:
             raise ValueError("prob_tensor is required")
-        fp8_out = d_tensor.dtype == torch.float8_e4m3fn
+        fp8_out = d_tensor.dtype in (torch.float8_e4m3fn, torch.float8_e5m2)
         ops.grouped_gemm_op(
             "fc2",
             a=a_tensor,

@@ -171,10 +171,10 @@ class GroupedGemmSwigluSm100(OperatorBase):
         # what this build implements of the reference's surface
         self._not_implemented_error_if(self.ab_dtype not in (torch.float8_e4m3fn, torch.float8_e5m2), f"only MXFP8 (E4M3 or E5M2) inputs are built, got {self.ab_dtype}")
         self._not_implemented_error_if(self.sf_dtype != torch.float8_e8m0fnu, f"only E8M0 scale factors are built, got {self.sf_dtype}")
-        self._not_implemented_error_if(self.c is not None and self.c_dtype != torch.bfloat16, f"only bf16 C is built, got {self.c_dtype}")
-        self._not_implemented_error_if(self.d_dtype not in (torch.bfloat16, torch.float8_e4m3fn), f"only bf16 and E4M3 D are built, got {self.d_dtype}")
-        self._not_implemented_error_if(self.generate_sfd and self.d_dtype != torch.float8_e4m3fn, "scale-factor generation with a 16-bit D is not built; drop sfd_row / sfd_col / norm_const to get bf16 D with amax")
-        self._not_implemented_error_if(not self.generate_sfd and self.d_dtype == torch.float8_e4m3fn, "E4M3 D needs sfd_row, sfd_col and norm_const")
+        self._not_implemented_error_if(self.c is not None and self.c_dtype not in (torch.bfloat16, torch.float16), f"only bf16 and fp16 C are built, got {self.c_dtype}")
+        self._not_implemented_error_if(self.d_dtype not in (torch.bfloat16, torch.float16, torch.float8_e4m3fn, torch.float8_e5m2), f"only bf16, fp16, E4M3 and E5M2 D are built, got {self.d_dtype}")
+        self._not_implemented_error_if(self.generate_sfd and self.d_dtype not in (torch.float8_e4m3fn, torch.float8_e5m2), "scale-factor generation with a 16-bit D is not built; drop sfd_row / sfd_col / norm_const to get bf16 D with amax")
+        self._not_implemented_error_if(not self.generate_sfd and self.d_dtype in (torch.float8_e4m3fn, torch.float8_e5m2), "FP8 D needs sfd_row, sfd_col and norm_const")
         self._value_error_if(n % 64 != 0, f"n must be a multiple of 64 (32-column gate / up blocks), got {n}")
         self._value_error_if(self.generate_sfd and self.d_col is None, "sample_d_col is required when scale factors are generated")
         self._value_error_if(self.act_func not in ("swiglu", "geglu"), f"act_func must be 'swiglu' or 'geglu', got {self.act_func}")
@@ -221,7 +221,7 @@ class GroupedGemmSwigluSm100(OperatorBase):
         if (bias_tensor is not None) != (self.bias is not None):
             raise ValueError("bias fusion is fixed at construction: pass bias_tensor exactly when sample_bias was given")
         n, l = b_tensor.shape[0], b_tensor.shape[2]
-        fp8_out = d_tensor.dtype == torch.float8_e4m3fn
+        fp8_out = d_tensor.dtype in (torch.float8_e4m3fn, torch.float8_e5m2)
         ops.grouped_gemm_op(
             "fc1",
             a=a_tensor,

@@ -138,7 +138,12 @@ def launch_grouped_gemm(
     args.workspace = _ptr(workspace)
     args.workspace_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
     args.m_rows, args.n, args.k, args.num_experts = m_rows, n, k, num_experts
-    args.d_dtype = _lib.DTYPE_E4M3 if d.dtype in _FP8_BYTES else _lib.DTYPE_BF16
+    if d.dtype not in _D_DTYPES:
+        raise NotImplementedError(f"D dtype {d.dtype} is not built (bf16, fp16, E4M3, E5M2 are)")
+    args.d_dtype = _D_DTYPES[d.dtype]
+    if c is not None and c.dtype not in (torch.bfloat16, torch.float16):
+        raise NotImplementedError(f"C dtype {c.dtype} is not built (bf16 and fp16 are)")
+    args.c_dtype = _lib.DTYPE_F16 if (c is not None and c.dtype == torch.float16) else _lib.DTYPE_BF16
     args.flags = _lib.FLAG_DISCRETE_COL_SFD if discrete_col_sfd else 0
     mode = tile_mode or os.environ.get("B200MOE_TILE_MODE", "auto")
     if mode not in ("auto", "single", "pair"):
@@ -170,6 +175,8 @@ def launch_grouped_gemm(
     _lib.check(rc)
 
 
+_D_DTYPES = {torch.bfloat16: _lib.DTYPE_BF16, torch.float16: _lib.DTYPE_F16, torch.float8_e4m3fn: _lib.DTYPE_E4M3,
+             torch.uint8: _lib.DTYPE_E4M3, torch.float8_e5m2: _lib.DTYPE_E5M2}
 _BIAS_DTYPES = {torch.bfloat16: _lib.DTYPE_BF16, torch.float16: _lib.DTYPE_F16, torch.float32: _lib.DTYPE_F32}
 
 

@@ -112,6 +112,11 @@ typedef struct b200moe_gemm_args {
   /* element type of A and B (both the same, as the reference demands): B200MOE_DTYPE_E4M3
      (also when left 0) or B200MOE_DTYPE_E5M2 */
   int32_t ab_dtype;
+  /* element type of C: B200MOE_DTYPE_BF16 (also when left 0) or B200MOE_DTYPE_F16.  d_dtype takes
+     B200MOE_DTYPE_BF16 / _F16 (16-bit D with amax) or B200MOE_DTYPE_E4M3 / _E5M2 (FP8 D and D_col
+     with E8M0 scales; the block maximum maps to 448 resp. 128 as in the reference's
+     get_dtype_rcp_limits, grouped_gemm_swiglu_quant.py:2996-3012). */
+  int32_t c_dtype;
 } b200moe_gemm_args;
 
 /*

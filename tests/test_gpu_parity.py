@@ -782,3 +782,49 @@ def test_e5m2_inputs(kind, d_fp8, tile_mode):
     if not d_fp8:
         ref4 = (orc.fc1_reference if kind == "fc1" else orc.fc2_reference)(a, sfa, b, sfb, offs, alpha, prob)
         assert H.rel_fro(out["d_tensor"][:, :, 0].float().cpu().numpy()[:valid], ref4["d"][:valid]) > 0.1
+
+
+@pytest.mark.parametrize("kind", ["fc1", "fc2"])
+@pytest.mark.parametrize("out", ["f16", "e5m2"])
+def test_fp16_and_e5m2_outputs(kind, out, tile_mode):
+    """D (and FC1's C) in fp16 with per-expert amax, and FP8 D / D_col in E5M2 with E8M0 scales (the
+    block maximum maps to 128, the reference's limit for E5M2)."""
+    cf = _api()
+    from cudnn_frontend_b200 import ops
+
+    groups, n, k = [100, 256, 0, 130], 256, 256
+    e = len(groups)
+    valid, aligned, offs = orc.padded_end_offsets(groups, 128)
+    # smaller scales than the other tests use: the results must fit fp16 (max 65504)
+    a, b, sfa, sfb = H.gen_operands(83, valid, n, k, e, sf_lo=119, sf_hi=125)
+    H.zero_padding_rows(a, groups, aligned)
+    rng = np.random.default_rng(83)
+    alpha = rng.integers(1, 3, e).astype(np.float32)
+    prob = rng.uniform(0.1, 1.0, valid).astype(np.float32)
+    ta, tb = H.dev_fp8(a).view(valid, k, 1), H.dev_fp8(b).permute(1, 2, 0)
+    d_fp8 = out == "e5m2"
+    d_dtype = torch.float8_e5m2 if d_fp8 else torch.float16
+    common = dict(norm_const_tensor=torch.ones(1, device="cuda") if d_fp8 else None,
+                  prob_tensor=torch.from_numpy(prob).cuda().view(valid, 1, 1), d_dtype=d_dtype, sf_vec_size=32, m_aligned=128)  # fmt: skip
+    toffs, talpha = torch.from_numpy(offs).cuda(), torch.from_numpy(alpha).cuda()
+    ref_kw = dict(norm_const=1.0 if d_fp8 else None, d_dtype="e5m2" if d_fp8 else "e4m3")
+    if kind == "fc1":
+        res = cf.grouped_gemm_swiglu_wrapper_sm100(ta, tb, H.dev_sf(sfa, valid, k), H.dev_sf(sfb, n, k, e), toffs, talpha,
+                                                   c_dtype=torch.float16 if out == "f16" else torch.bfloat16, **common)  # fmt: skip
+        ref = orc.fc1_reference(a, sfa, b, sfb, offs, alpha, prob, **ref_kw)
+    else:
+        res = cf.grouped_gemm_quant_wrapper_sm100(ta, H.dev_sf(sfa, valid, k), toffs, talpha, b_tensor=tb, sfb_tensor=H.dev_sf(sfb, n, k, e),
+                                                  **common)  # fmt: skip
+        ref = orc.fc2_reference(a, sfa, b, sfb, offs, alpha, prob, **ref_kw)
+    torch.cuda.synchronize()
+    assert ops.device_status(clear=True) == 0
+    o = dict(res)
+    o.setdefault("c_tensor", None)
+    assert o["d_tensor"].dtype == d_dtype
+    if out == "f16" and kind == "fc1":
+        assert o["c_tensor"].dtype == torch.float16
+    _check(kind, o, ref, dict(valid=valid, m_rows=valid, n_out=n // 2 if kind == "fc1" else n, offs=offs, norm=1.0, e=e), d_fp8)
+    if out == "f16":
+        # fp16 keeps three more mantissa bits than bf16: the result must be closer to the oracle than bf16 rounding allows
+        d = o["d_tensor"][:, :, 0].float().cpu().numpy()[:valid]
+        assert H.rel_fro(d, ref["d"][:valid]) < 1.5e-3
