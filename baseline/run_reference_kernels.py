@@ -115,7 +115,8 @@ def run_case(name, cfg, out):
         p["b"] = (torch.randn(cfg["experts"], n, k, generator=g5, device="cuda") * 0.5).to(torch.float8_e5m2).permute(1, 2, 0)
     norm = torch.tensor([1.0], dtype=torch.float32, device="cuda")
     stream = cuda.CUstream(torch.cuda.current_stream().cuda_stream)
-    common = dict(norm_const_tensor=norm, prob_tensor=p["prob"], d_dtype=torch.float8_e4m3fn, sf_vec_size=32, m_aligned=256)
+    d_dtype = torch.float8_e5m2 if cfg.get("d") == "e5m2" else torch.float8_e4m3fn
+    common = dict(norm_const_tensor=norm, prob_tensor=p["prob"], d_dtype=d_dtype, sf_vec_size=32, m_aligned=256)
     res = {"case": name, "cfg": cfg, "m_rows": p["m_rows"], "flops": p["flops"]}
 
     t0 = time.time()
@@ -187,9 +188,10 @@ def run_case(name, cfg, out):
     out.append(res)
     print(json.dumps(res), flush=True)
 
-    if name in ("tiny", "tiny_e5m2"):
+    if name in ("tiny", "tiny_e5m2", "tiny_d_e5m2"):
         np.savez_compressed(
-            os.path.join(OUT_DIR, "reference_kernel_golden.npz" if name == "tiny" else "reference_kernel_e5m2_golden.npz"),
+            os.path.join(OUT_DIR, {"tiny": "reference_kernel_golden.npz", "tiny_e5m2": "reference_kernel_e5m2_golden.npz",
+                                   "tiny_d_e5m2": "reference_kernel_d_e5m2_golden.npz"}[name]),
             a=p["a"][:, :, 0].view(torch.uint8).cpu().numpy(),
             b=p["b"].permute(2, 0, 1).contiguous().view(torch.uint8).cpu().numpy(),
             sfa=flat(p["sfa"]).cpu().numpy(),
@@ -355,6 +357,7 @@ CASES = {
     # small enough to commit its inputs and the reference kernel's outputs as a fixture
     "tiny": dict(experts=2, k=128, n=128, tokens=128, topk=2, routing="uniform"),
     "tiny_e5m2": dict(experts=2, k=128, n=128, tokens=128, topk=2, routing="uniform", ab="e5m2"),
+    "tiny_d_e5m2": dict(experts=2, k=128, n=128, tokens=128, topk=2, routing="uniform", d="e5m2"),
     "small": dict(experts=4, k=512, n=512, tokens=512, topk=2, routing="uniform"),
     "c2": dict(experts=8, k=4096, n=28672, tokens=16384, topk=2, routing="uniform"),
     "c3": dict(experts=256, k=7168, n=4096, tokens=8192, topk=8, routing="zipf"),

@@ -405,8 +405,15 @@ def test_fc1_fc2_chain_matches_layer_oracle(tile_mode):
 # ---------------------------------------------------------------------------------------------
 # fixture produced by the reference's own CuTe-DSL kernel on a B200 (baseline/run_reference_kernels.py)
 # ---------------------------------------------------------------------------------------------
-@pytest.mark.parametrize("fixture,ab_dtype", [("reference_kernel_fc1.npz", torch.float8_e4m3fn), ("reference_kernel_fc1_e5m2.npz", torch.float8_e5m2)])
-def test_fc1_is_bit_identical_to_the_reference_kernel_fixture(golden_dir, tile_mode, fixture, ab_dtype):
+@pytest.mark.parametrize(
+    "fixture,ab_dtype,d_dtype",
+    [
+        ("reference_kernel_fc1.npz", torch.float8_e4m3fn, torch.float8_e4m3fn),
+        ("reference_kernel_fc1_e5m2.npz", torch.float8_e5m2, torch.float8_e4m3fn),  # E5M2 operands
+        ("reference_kernel_fc1_d_e5m2.npz", torch.float8_e4m3fn, torch.float8_e5m2),  # E5M2 D and D_col
+    ],
+)
+def test_fc1_is_bit_identical_to_the_reference_kernel_fixture(golden_dir, tile_mode, fixture, ab_dtype, d_dtype):
     """Inputs and outputs of cudnn-frontend's grouped_gemm_swiglu_wrapper_sm100 (fp8 in, E4M3 D,
     norm_const 1, groups padded to 256) recorded on a B200, once with E4M3 and once with E5M2
     operands: C, D, D_col and both scale-factor tensors must match byte for byte (E8M0 round-up,
@@ -431,7 +438,7 @@ def test_fc1_is_bit_identical_to_the_reference_kernel_fixture(golden_dir, tile_m
     out = cf.grouped_gemm_swiglu_wrapper_sm100(
         a, b, sf(g["sfa"], m, k, 1), sf(g["sfb"], n, k, e), torch.from_numpy(g["offsets"]).to(dev), torch.ones(e, device=dev),
         norm_const_tensor=torch.ones(1, device=dev), prob_tensor=torch.from_numpy(g["prob"]).to(dev).view(m, 1, 1),
-        d_dtype=torch.float8_e4m3fn, sf_vec_size=32, m_aligned=256,
+        d_dtype=d_dtype, sf_vec_size=32, m_aligned=256,
     )  # fmt: skip
     torch.cuda.synchronize()
 

@@ -143,14 +143,17 @@ def _check_quantised(d_q, sf, ref_d, ref_sf_flat, rows, cols, by_cols=False):
     assert np.mean(ulp[same_scale] == 0) >= 0.97
 
 
-@pytest.mark.parametrize("fixture,ab_dtype", [("reference_kernel_fc1.npz", "e4m3"), ("reference_kernel_fc1_e5m2.npz", "e5m2")])
-def test_fc1_oracle_against_the_reference_kernel_fixture(golden_dir, fixture, ab_dtype):
+@pytest.mark.parametrize(
+    "fixture,ab_dtype,d_dtype",
+    [("reference_kernel_fc1.npz", "e4m3", "e4m3"), ("reference_kernel_fc1_e5m2.npz", "e5m2", "e4m3"), ("reference_kernel_fc1_d_e5m2.npz", "e4m3", "e5m2")],
+)
+def test_fc1_oracle_against_the_reference_kernel_fixture(golden_dir, fixture, ab_dtype, d_dtype):
     g = _load(golden_dir, fixture)
     m, n = g["c"].shape
     e = g["b"].shape[0]
     k = g["a"].shape[1]
     sfa, sfb = orc.sf_unpack(g["sfa"], m, k // 32)[0], orc.sf_unpack(g["sfb"], n, k // 32, e)
-    out = orc.fc1_reference(g["a"], sfa, g["b"], sfb, g["offsets"], np.ones(e, np.float32), g["prob"], norm_const=1.0, ab_dtype=ab_dtype)
+    out = orc.fc1_reference(g["a"], sfa, g["b"], sfb, g["offsets"], np.ones(e, np.float32), g["prob"], norm_const=1.0, ab_dtype=ab_dtype, d_dtype=d_dtype)
     c_ref = _bf16_bits_to_f32(g["c"].view(np.uint16))
     rel = np.linalg.norm(orc.bf16_round(out["c"][:m]) - c_ref) / np.linalg.norm(c_ref)
     assert rel <= 2e-3  # task gate: 2e-2; a differing element is one bf16 ULP
