@@ -485,6 +485,8 @@ def main():
     if world > 1 or args.gpus > 1:
         from cudnn_frontend_b200 import ep_bench
 
+        args.peaks = load_peaks()
+        args.clock_sampler = ClockSampler
         ep_bench.run(args)
     else:
         bench_single(args)

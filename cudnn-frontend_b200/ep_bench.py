@@ -60,6 +60,18 @@ def single_gpu_layer(dev, steps: int = 5, warmup: int = 3, tokens: int = 65536) 
     return {"tflops": layer_flops(tokens) / (ms * 1e-3) / 1e12, "ms": ms, "tokens": tokens, "launches_per_step": 7}
 
 
+def _step_roofline(tflops_per_gpu: float, peaks):
+    """Whole step against the tensor roof: algorithmic FLOPs of FC1 + FC2 per GPU and step over the step
+    time (the two GEMMs are about three quarters of a step), peak = twice the measured sustained bf16
+    rate as for the single-GPU line."""
+    if not peaks:
+        return None
+    peak = 2.0 * peaks["bf16_sustained"]
+    return {"bound": "tensor", "achieved": tflops_per_gpu, "peak": peak, "unit": "TFLOP/s", "frac": tflops_per_gpu / peak, "traffic": None,
+            "kernel": "whole step per GPU (quantise+dispatch, FC1, FC2, combine)",
+            "peak_source": f"2 x bf16_tflops_sustained of {peaks['source']} MEASURED_PEAKS.json (dense fp8 proxy)"}  # fmt: skip
+
+
 def _trace_one_step(step, barrier, write: bool, path: str, min_us: float = 30.0) -> None:
     """One step under the torch profiler (every rank runs it, one rank writes): start, duration and
     name of every kernel of at least ``min_us`` microseconds."""
@@ -141,11 +153,15 @@ def run(args, tokens_per_gpu: int = 65536):
     barrier()
     torch.cuda.synchronize()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record(stream)
-    for _ in range(args.steps):
-        y = step()
-    stop.record(stream)
-    torch.cuda.synchronize()
+    import contextlib
+
+    sampler = getattr(args, "clock_sampler", None)
+    with (sampler(local) if sampler is not None and rank == 0 else contextlib.nullcontext()) as clk:
+        start.record(stream)
+        for _ in range(args.steps):
+            y = step()
+        stop.record(stream)
+        torch.cuda.synchronize()
     barrier()
     ms = torch.tensor([start.elapsed_time(stop) / args.steps], device=dev)
     rows_recv = torch.tensor([float(layer.last_rows_received)], device=dev)
@@ -237,7 +253,8 @@ def run(args, tokens_per_gpu: int = 65536):
             "e2e": {"value": flops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
                     "ms_per_step": ms_e2e,
                     "note": "bytes are one rank's, the value is the aggregate over ranks; the copy of step i + 1 overlaps step i"},
-            "roofline": None,
+            "roofline": _step_roofline(value / world, getattr(args, "peaks", None)),
+            "clocks": clk.summary() if clk is not None else None,
             "cpu_baseline": None,
         }
         print(json.dumps(line))
