@@ -12,7 +12,7 @@ compared (C bf16, E8M0 scale bytes, E4M3 ULP distance) and both are timed with C
 interleaved A B A B in one queue, which is the comparison that is independent of the GPU's power state).  Results go to
 <out dir>/reference_kernels_<cases>.json; the tiny cases' inputs and reference-kernel outputs are saved
 to <out dir>/reference_kernel_*golden.npz so they can be committed as golden vectors (tests/golden/).  The
-output directory is B200MOE_OUT_DIR, else the directory named by OUT_DIR_DEFAULT below.
+output directory is --out (or the environment variable B200MOE_OUT_DIR); one of the two is required.
 
     python baseline/run_reference_kernels.py --cases tiny      # one case per process: the reference's
     python baseline/run_reference_kernels.py --cases c2        # wrapper cache does not key on the expert count
@@ -33,8 +33,7 @@ sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
 import numpy as np  # noqa: E402
 import torch  # noqa: E402
 
-OUT_DIR_DEFAULT = "gpurun_out"
-OUT_DIR = os.path.join(ROOT, os.environ.get("B200MOE_OUT_DIR", OUT_DIR_DEFAULT))
+OUT_DIR = os.environ.get("B200MOE_OUT_DIR")  # main() replaces it with --out when given
 
 
 def timed(fn, trials=10, warmup=3):
@@ -188,10 +187,11 @@ def run_case(name, cfg, out):
     out.append(res)
     print(json.dumps(res), flush=True)
 
-    if name in ("tiny", "tiny_e5m2", "tiny_d_e5m2"):
+    if name in ("tiny", "tiny_e5m2", "tiny_d_e5m2", "tiny_deepk"):
         np.savez_compressed(
             os.path.join(OUT_DIR, {"tiny": "reference_kernel_golden.npz", "tiny_e5m2": "reference_kernel_e5m2_golden.npz",
-                                   "tiny_d_e5m2": "reference_kernel_d_e5m2_golden.npz"}[name]),
+                                   "tiny_d_e5m2": "reference_kernel_d_e5m2_golden.npz",
+                                   "tiny_deepk": "reference_kernel_deepk_golden.npz"}[name]),
             a=p["a"][:, :, 0].view(torch.uint8).cpu().numpy(),
             b=p["b"].permute(2, 0, 1).contiguous().view(torch.uint8).cpu().numpy(),
             sfa=flat(p["sfa"]).cpu().numpy(),
@@ -358,6 +358,8 @@ CASES = {
     "tiny": dict(experts=2, k=128, n=128, tokens=128, topk=2, routing="uniform"),
     "tiny_e5m2": dict(experts=2, k=128, n=128, tokens=128, topk=2, routing="uniform", ab="e5m2"),
     "tiny_d_e5m2": dict(experts=2, k=128, n=128, tokens=128, topk=2, routing="uniform", d="e5m2"),
+    # eight k-tiles deep (the accumulation across k-tiles and the wrap of the shared-memory ring), still small enough to commit
+    "tiny_deepk": dict(experts=2, k=1024, n=128, tokens=64, topk=2, routing="uniform"),
     "small": dict(experts=4, k=512, n=512, tokens=512, topk=2, routing="uniform"),
     "c2": dict(experts=8, k=4096, n=28672, tokens=16384, topk=2, routing="uniform"),
     "c3": dict(experts=256, k=7168, n=4096, tokens=8192, topk=8, routing="zipf"),
@@ -380,8 +382,12 @@ def main():
     ap.add_argument("--cases", default="tiny")
     ap.add_argument("--own-first", action="store_true", help="time this repository's kernel before the reference's")
     ap.add_argument("--profile", action="store_true", help="launch each kernel twice and exit (for ncu)")
+    ap.add_argument("--out", default=None, help="output directory (else the environment variable B200MOE_OUT_DIR)")
     args = ap.parse_args()
-    global PROFILE_ONLY, OWN_FIRST
+    global PROFILE_ONLY, OWN_FIRST, OUT_DIR
+    OUT_DIR = args.out or OUT_DIR
+    if not OUT_DIR:
+        ap.error("give the output directory with --out or B200MOE_OUT_DIR")
     PROFILE_ONLY = args.profile
     OWN_FIRST = args.own_first
     os.makedirs(OUT_DIR, exist_ok=True)

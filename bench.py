@@ -347,7 +347,7 @@ def bench_single(args):
         torch.cuda.empty_cache()
         extras.update(bench_other_configs(dev, stream))
         torch.cuda.empty_cache()
-        from cudnn_frontend_b200 import ep_bench
+        import ep_bench
 
         # the workload of the multi-GPU runs (--gpus 2/4/8) with all experts on this GPU
         extras["ep_layer_1gpu"] = ep_bench.single_gpu_layer(dev)
@@ -483,7 +483,7 @@ def main():
         return
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if world > 1 or args.gpus > 1:
-        from cudnn_frontend_b200 import ep_bench
+        import ep_bench
 
         args.peaks = load_peaks()
         args.clock_sampler = ClockSampler

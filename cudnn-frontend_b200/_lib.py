@@ -14,10 +14,15 @@ from . import _build
 E_NULL, E_SHAPE, E_ALIGN, E_UNSUPPORTED, E_WORKSPACE, E_DEVICE = -1, -2, -3, -4, -5, -6
 DTYPE_BF16, DTYPE_E4M3, DTYPE_F16, DTYPE_F32, DTYPE_E5M2 = 0, 1, 2, 3, 4
 ACT_SWIGLU, ACT_GEGLU = 0, 1
-ABI_VERSION = 5  # b200moe_abi_version() of the header these declarations mirror
+ABI_VERSION = 6  # b200moe_abi_version() of the header these declarations mirror
 FLAG_DISCRETE_COL_SFD = 1
 FLAG_TILE_SINGLE = 2
 FLAG_TILE_PAIR = 4
+FLAG_DYNAMIC_SCHED = 8
+FLAG_B_NMAJOR = 16
+FLAG_OFFSETS_HAVE_PREV = 32
+FLAG_TEST_SKIP_B_LOADS = 64
+WORKSPACE_DISCRETE, WORKSPACE_DYNAMIC_SCHED = 1, 2
 NOALLOC_MAX_EXPERTS = 256
 
 
@@ -56,6 +61,8 @@ class GemmArgs(Structure):
         ("act_func", c_int32),
         ("ab_dtype", c_int32),
         ("c_dtype", c_int32),
+        ("wait_limit_ms", c_int32),
+        ("sched_light_m_tiles", c_int32),
     ]
 
 

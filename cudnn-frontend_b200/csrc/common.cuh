@@ -107,29 +107,55 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
   return done;
 }
 
-// Bounded wait.  Spins on the barrier phase; after kWaitLimitNs without progress it records
+// Bounded wait.  Spins on the barrier phase; after `limit_ns` without progress it records
 // `code` in the device status word, raises the CTA's abort flag and returns false so the
 // caller can leave its loop and fall through to the kernel's teardown.  A raised abort flag
 // makes every other waiter of the CTA give up quickly as well.
-constexpr uint64_t kWaitLimitNs = 4000000000ull;  // 4 s: far above any legitimate wait
+constexpr uint64_t kWaitLimitNs = 4000000000ull;  // default limit, 4 s: far above any legitimate wait
 
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int code) {
+struct WaitCtx {
+  volatile int* abort_flag;
+  uint64_t limit_ns;
+};
+
+// kCluster: acquire at cluster scope (the data guarded by the barrier was written by the other CTA
+// of the pair)
+template <bool kCluster = false>
+__device__ __forceinline__ uint32_t mbar_try_wait_scoped(uint32_t bar, uint32_t parity) {
+  if constexpr (!kCluster) {
+    return mbar_try_wait(bar, parity);
+  } else {
+    uint32_t done;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done;
+  }
+}
+
+template <bool kCluster = false>
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx& w, int code) {
 #pragma unroll 1
   for (int i = 0; i < 128; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait_scoped<kCluster>(bar, parity)) return true;
   }
   const uint64_t t0 = global_timer_ns();
 #pragma unroll 1
   while (true) {
 #pragma unroll 1
     for (int i = 0; i < 256; ++i) {
-      if (mbar_try_wait(bar, parity)) return true;
+      if (mbar_try_wait_scoped<kCluster>(bar, parity)) return true;
     }
-    if (*abort_flag) return false;
-    if (global_timer_ns() - t0 > kWaitLimitNs) {
+    if (*w.abort_flag) return false;
+    if (global_timer_ns() - t0 > w.limit_ns) {
       atomicCAS(&g_device_status, 0, code);
-      *abort_flag = 1;
+      *w.abort_flag = 1;
       return false;
     }
   }
@@ -256,6 +282,22 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
 // TMEM loads, and tcgen05.wait::ld plus tcgen05.fence::before_thread_sync order those.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// Releasing arrive on a barrier of any CTA of the cluster (orders this thread's earlier writes,
+// remote shared-memory stores included, before the arrival).
+__device__ __forceinline__ void mbar_arrive_cluster_release(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// 32-bit store into the shared memory of any CTA of the cluster
+__device__ __forceinline__ void st_shared_cluster(uint32_t cluster_addr, uint32_t v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+// 0, computed from `v` in a way the compiler cannot fold: adding it to an address makes the
+// instruction that uses the address wait for the load that produced `v`.
+__device__ __forceinline__ uint32_t zero_after(int v) {
+  uint32_t z;
+  asm volatile("and.b32 %0, %1, 0;" : "=r"(z) : "r"(v));
+  return z;
 }
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_dst, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols)

@@ -4,8 +4,10 @@
 //        32-column blocks of C) ; per-expert amax, or row / column MXFP8 re-quantisation.
 //   FC2: D = alpha_e acc * prob ; bf16 + amax, or E4M3 + row / column E8M0 scale factors.
 //
-// Persistent kernel, one CTA per SM, walking a static tile schedule derived on the device from
-// the per-expert END offsets.  Warp roles:
+// Persistent kernel, one CTA per SM, walking a tile schedule derived on the device from the
+// per-expert END offsets: tiles of small expert groups (which stream their weights from HBM for one
+// or two row tiles) are interleaved with tiles of large groups (which reuse weights from L2), and
+// the sequence is walked with a static stride or through an atomic counter.  Warp roles:
 //   warp 0, 10  producers: TMA loads of the A tile (warp 0) and the B tile (warp 10), 128-byte
 //               swizzled, plus their 512-byte scale-factor chunks, into a shared-memory ring
 //   warp 1      TMEM owner and MMA issuer: tcgen05.cp moves the scale factors to TMEM, then
@@ -56,6 +58,8 @@ constexpr int MAX_EXPERTS = 1024;
 constexpr int RASTER_GROUP_ROWS = 4096;        // rows of one expert that share a B tile back to back ...
 constexpr int64_t RASTER_GROUP_BYTES = 32 << 20;  // ... unless that many rows of A exceed this share of L2
 
+constexpr int DEFAULT_LIGHT_M_TILES = 2;
+
 constexpr int TMEM_COLS = 512;
 constexpr int TMEM_ACC1_COL = 224;
 constexpr int TMEM_SF_COL = 480;  // per SF buffer i: SFA at +16 i (4 cols), SFB at +16 i + 4 (8 cols)
@@ -65,6 +69,10 @@ constexpr int ST_PRODUCER_EMPTY = 101;
 constexpr int ST_MMA_FULL = 102;
 constexpr int ST_MMA_OVERLAP = 103;
 constexpr int ST_EPI_ACC = 104;
+constexpr int ST_SCHED_FULL = 105;   // a consumer of the dynamic scheduler's ring
+constexpr int ST_SCHED_EMPTY = 106;  // the fetching warp waiting for a free ring slot
+
+constexpr int SCHED_RING = 8;  // tile ids in flight between the fetching warp and the other warps (dynamic scheduler)
 
 // kBulk: bf16 D rows leave through a shared-memory staging area and one bulk copy per row (used
 // when the rows go to peer GPUs: 256-byte bursts instead of 32-byte stores); the staging area
@@ -84,10 +92,10 @@ struct Cfg {
   static constexpr int SFA_OFF = B_OFF + STAGES * B_STAGE_BYTES;
   static constexpr int SFB_OFF = SFA_OFF + STAGES * SFA_STAGE_BYTES;
   static constexpr int BAR_OFF = SFB_OFF + STAGES * SFB_STAGE_BYTES;  // 8-byte barriers
-  static constexpr int NUM_BARS = 2 * STAGES + 2 + 1;
-  static constexpr int MISC_OFF = BAR_OFF + NUM_BARS * 8;  // tmem ptr, abort flag, total tiles
-  static constexpr int PREFIX_OFF = MISC_OFF + 16;         // (E + 1) int32 tile prefix
-  static constexpr int STAGING_OFF = (PREFIX_OFF + (MAX_EXPERTS + 1) * 4 + 15) & ~15;
+  static constexpr int NUM_BARS = 2 * STAGES + 2 + 1 + 2 * SCHED_RING;
+  static constexpr int MISC_OFF = BAR_OFF + NUM_BARS * 8;  // tmem ptr, abort flag, tile totals, scheduler ring
+  static constexpr int PREFIX_OFF = MISC_OFF + 16 + SCHED_RING * 4;  // 2 x (E + 1) int32 tile prefixes (heavy, light)
+  static constexpr int STAGING_OFF = (PREFIX_OFF + 2 * (MAX_EXPERTS + 1) * 4 + 15) & ~15;
   static constexpr int TOTAL = STAGING_OFF + (kBulk ? NUM_EPI_WARPS * STAGING_WARP_BYTES : 0);
   static constexpr int SMEM_BYTES = TOTAL + 1024;  // slack for manual 1024-byte alignment
   // bytes credited to a "full" barrier per stage (both CTAs of a pair together)
@@ -136,29 +144,69 @@ struct GemmParams {
   int act_geglu;       // FC1: 0 = SwiGLU, 1 = GeGLU
   uint32_t ab_format;  // A / B format bits of the instruction descriptor (0 = E4M3, E5M2 = 1 in both fields)
   int raster_group_m;  // row tiles per raster group
+  int light_m_tiles;   // experts with at most this many row tiles form the "light" class (0 = one class)
+  int first_has_prev;  // offsets[-1] is readable and is the first row of expert 0 (a slice of a longer expert list)
+  int b_nmajor;        // B is [K][N] per expert (N contiguous) instead of [N][K]
+  int dynamic_sched;   // tiles after each CTA's first come from an atomic counter
+  int* tile_counter;   // dynamic scheduler: zeroed before the launch
+  int test_skip_b_loads;  // test hook: the B-side producer issues no load, so every wait runs out
+  uint64_t wait_limit_ns;
 };
 
 // ---------------------------------------------------------------------------------------
-// Tile schedule.  Expert e owns tiles [prefix[e], prefix[e+1]); inside an expert tiles run
-// in groups of `group_m` row tiles, row tile fastest, so that CTAs working on adjacent
-// schedule slots read the same B tile at the same time and the A rows of the group stay in L2
-// while the B tiles stream past once.  With groups of 4096 rows every B tile of a Mixtral-size
-// expert comes from HBM exactly once; groups of 2048 rows measured 4-6 % slower, 1024 rows 10 %.
+// Tile schedule.
+//
+// Experts fall into two classes by their number of row tiles.  A "heavy" expert has many row tiles
+// per weight tile: its weights are read from HBM once and reused from L2, so its tiles are bound by
+// the tensor pipe.  A "light" expert (at most `light_m_tiles` row tiles) streams every weight tile
+// from HBM for one or two MMAs' worth of rows: its tiles are bound by HBM.  Walking the experts in
+// order would alternate between phases where every SM waits for HBM and phases where HBM idles.
+// The linear schedule therefore interleaves the two classes evenly (position s is the
+// floor(s nL / total)-th light tile when that count steps up at s, else the next heavy tile), so
+// that at any time a fixed share of the SMs streams weights while the others compute.
+//
+// Inside a class expert e owns tiles [prefix[e], prefix[e+1]); inside an expert tiles run in
+// groups of `group_m` row tiles, row tile fastest, so that CTAs working on adjacent schedule slots
+// read the same B tile at the same time and the A rows of the group stay in L2 while the B tiles
+// stream past once.  With groups of 4096 rows every B tile of a Mixtral-size expert comes from HBM
+// exactly once; groups of 2048 rows measured 4-6 % slower, 1024 rows 10 %.
 // A row tile is 128 rows (single) or 256 rows (pair).
 // ---------------------------------------------------------------------------------------
 struct Tile {
   int expert, row0, n_tile, row_end;
 };
 
-__device__ __forceinline__ Tile decode_tile(const int* prefix, const int32_t* offsets, int num_experts,
-                                            int n_tiles, int tile_m, int group_m, int t) {
-  int lo = 0, hi = num_experts;  // find e with prefix[e] <= t < prefix[e + 1]
+struct Sched {
+  const int* prefix_heavy;  // [E + 1]
+  const int* prefix_light;  // [E + 1]
+  int n_light, total;
+};
+
+__device__ __forceinline__ int expert_first_row(const GemmParams& p, int e) {
+  return e == 0 ? (p.first_has_prev ? p.offsets[-1] : 0) : p.offsets[e - 1];
+}
+
+__device__ __forceinline__ Tile decode_tile(const Sched& sc, const GemmParams& p, int tile_m, int s) {
+  const int* prefix = sc.prefix_heavy;
+  int t = s;
+  if (sc.n_light > 0) {
+    const int before = (int)(((int64_t)s * sc.n_light) / sc.total);
+    const int after = (int)(((int64_t)(s + 1) * sc.n_light) / sc.total);
+    if (after > before) {
+      prefix = sc.prefix_light;
+      t = before;
+    } else {
+      t = s - before;
+    }
+  }
+  int lo = 0, hi = p.num_experts;  // find e with prefix[e] <= t < prefix[e + 1]
   while (hi - lo > 1) {
     const int mid = (lo + hi) >> 1;
     if (prefix[mid] <= t) lo = mid; else hi = mid;
   }
   const int e = lo;
   const int j = t - prefix[e];
+  const int n_tiles = p.n_tiles, group_m = p.raster_group_m;
   const int m_tiles = (prefix[e + 1] - prefix[e]) / n_tiles;
   const int per_group = group_m * n_tiles;
   const int g = j / per_group;
@@ -168,9 +216,8 @@ __device__ __forceinline__ Tile decode_tile(const int* prefix, const int32_t* of
   Tile tile;
   tile.expert = e;
   tile.n_tile = jj / gsize;
-  const int start = e == 0 ? 0 : offsets[e - 1];
-  tile.row0 = start + (first_m + jj % gsize) * tile_m;
-  tile.row_end = offsets[e];
+  tile.row0 = expert_first_row(p, e) + (first_m + jj % gsize) * tile_m;
+  tile.row_end = p.offsets[e];
   return tile;
 }
 
@@ -355,15 +402,22 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
   auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
   auto acc_full_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + b); };
   const uint32_t overlap_bar = bar_base + 8u * (2 * STAGES + 2);
+  // dynamic scheduler: ring slot q holds a tile id once info_full(q) completes; its readers arrive on info_empty(q)
+  auto info_full_bar = [&](int q) { return bar_base + 8u * (2 * STAGES + 3 + q); };
+  auto info_empty_bar = [&](int q) { return bar_base + 8u * (2 * STAGES + 3 + SCHED_RING + q); };
   uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(smem + C::MISC_OFF);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::MISC_OFF + 4);
-  int* total_tiles_smem = reinterpret_cast<int*>(smem + C::MISC_OFF + 8);
-  int* prefix = reinterpret_cast<int*>(smem + C::PREFIX_OFF);
+  int* totals_smem = reinterpret_cast<int*>(smem + C::MISC_OFF + 8);  // [0] all tiles, [1] light tiles
+  volatile int* ring = reinterpret_cast<volatile int*>(smem + C::MISC_OFF + 16);
+  int* prefix_heavy = reinterpret_cast<int*>(smem + C::PREFIX_OFF);
+  int* prefix_light = prefix_heavy + (MAX_EXPERTS + 1);
+  const WaitCtx wc = {abort_flag, p.wait_limit_ns};
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   // pair mode: rank 0 of the 2-CTA cluster is the leader (issues the MMAs, owns the "full" and
-  // "overlap" barriers); a scheduled tile is 256 rows and this CTA covers rows [128 rank, +128)
+  // "overlap" barriers, fetches tiles for both CTAs); a scheduled tile is 256 rows and this CTA
+  // covers rows [128 rank, +128)
   const uint32_t cta_rank = kPair ? cluster_ctarank() : 0u;
   const int sched_id = kPair ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
   const int sched_stride = kPair ? (int)(gridDim.x >> 1) : (int)gridDim.x;
@@ -377,6 +431,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     mbar_init(acc_full_bar(0), 1);
     mbar_init(acc_full_bar(1), 1);
     mbar_init(overlap_bar, C::CTAS * NUM_EPI_WARPS);
+    for (int q = 0; q < SCHED_RING; ++q) {
+      mbar_init(info_full_bar(q), 1);
+      // readers of a slot: MMA warp (leader), B producer and 8 epilogue warps per CTA, A producer of the second CTA
+      mbar_init(info_empty_bar(q), kPair ? 2 * (NUM_EPI_WARPS + 1) + 2 : NUM_EPI_WARPS + 2);
+    }
     *abort_flag = 0;
     fence_mbar_init();
     prefetch_tensormap(&tmap_a);
@@ -396,31 +455,42 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     }
   }
   if (warp == 2) {
-    // tile prefix over experts: lane l scans a contiguous chunk, then a warp scan of the sums
+    // tile prefixes over experts, one per class: lane l scans a contiguous chunk of experts, then a
+    // warp scan of the chunk sums
     const int chunk = (p.num_experts + 31) / 32;
-    const int e0 = lane * chunk;
-    int sum = 0;
-    for (int e = e0; e < min(e0 + chunk, p.num_experts); ++e) {
-      const int start = e == 0 ? 0 : p.offsets[e - 1];
-      const int rows = max(p.offsets[e] - start, 0);
-      sum += ((rows + C::TILE_M - 1) / C::TILE_M) * p.n_tiles;
+    const int e0 = lane * chunk, e1 = min(e0 + chunk, p.num_experts);
+    auto tiles_of = [&](int e, bool& light) {
+      const int rows = max(p.offsets[e] - expert_first_row(p, e), 0);
+      const int m_tiles = (rows + C::TILE_M - 1) / C::TILE_M;
+      light = m_tiles <= p.light_m_tiles;
+      return m_tiles * p.n_tiles;
+    };
+    int sum_h = 0, sum_l = 0;
+    for (int e = e0; e < e1; ++e) {
+      bool light;
+      const int t = tiles_of(e, light);
+      if (light) sum_l += t; else sum_h += t;
     }
-    int incl = sum;
+    int incl_h = sum_h, incl_l = sum_l;
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {
-      const int t = __shfl_up_sync(0xffffffffu, incl, d);
-      if (lane >= d) incl += t;
+      const int th = __shfl_up_sync(0xffffffffu, incl_h, d);
+      const int tl = __shfl_up_sync(0xffffffffu, incl_l, d);
+      if (lane >= d) { incl_h += th; incl_l += tl; }
     }
-    int run = incl - sum;
-    for (int e = e0; e < min(e0 + chunk, p.num_experts); ++e) {
-      prefix[e] = run;
-      const int start = e == 0 ? 0 : p.offsets[e - 1];
-      const int rows = max(p.offsets[e] - start, 0);
-      run += ((rows + C::TILE_M - 1) / C::TILE_M) * p.n_tiles;
+    int run_h = incl_h - sum_h, run_l = incl_l - sum_l;
+    for (int e = e0; e < e1; ++e) {
+      prefix_heavy[e] = run_h;
+      prefix_light[e] = run_l;
+      bool light;
+      const int t = tiles_of(e, light);
+      if (light) run_l += t; else run_h += t;
     }
     if (lane == 31) {
-      prefix[p.num_experts] = incl;
-      *total_tiles_smem = incl;
+      prefix_heavy[p.num_experts] = incl_h;
+      prefix_light[p.num_experts] = incl_l;
+      totals_smem[0] = incl_h + incl_l;
+      totals_smem[1] = incl_l;
     }
   }
   tc_fence_before();
@@ -432,7 +502,34 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
   }
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr_smem;
-  const int total_tiles = *total_tiles_smem;
+  const int total_tiles = totals_smem[0];
+  const Sched sched = {prefix_heavy, prefix_light, totals_smem[1], total_tiles};
+
+  // ---- tile sequence of this CTA (pair) ---------------------------------------------------
+  // Static: schedule positions sched_id, sched_id + stride, ...  Dynamic: the first position is
+  // sched_id as well; the following ones are drawn from a global counter by the leader's A-producer
+  // warp (`fetcher`), which hands them to every other warp of the CTA pair through a ring in shared
+  // memory.  next_tile(i) is what a non-fetching warp calls for its i-th tile (all lanes together);
+  // it returns a negative number when the CTA is done (or a wait gave up).
+  const bool dynamic = p.dynamic_sched != 0;
+  const bool fetcher = dynamic && warp == 0 && cta_rank == 0;
+  const uint32_t info_empty_target0 = kPair ? map_to_cta(info_empty_bar(0), 0) : info_empty_bar(0);
+  auto next_tile = [&](int i) -> int {
+    if (!dynamic || i == 0) {
+      const int s = sched_id + i * sched_stride;
+      return s < total_tiles ? s : -1;
+    }
+    const int q = (i - 1) % SCHED_RING;
+    if (!mbar_wait<kPair>(info_full_bar(q), (uint32_t)((i - 1) / SCHED_RING) & 1u, wc, ST_SCHED_FULL)) return -1;
+    const int s = ring[q];
+    __syncwarp();
+    if (lane == 0) {
+      // the arrival address depends on the value read, so the slot is released only after the read
+      const uint32_t target = info_empty_target0 + 8u * q + zero_after(s);
+      if (kPair) mbar_arrive_cluster(target); else mbar_arrive(target);
+    }
+    return s;
+  };
 
   if (warp == 0 || warp == PRODUCER_B_WARP) {
     // ================= producers ======================================================
@@ -447,8 +544,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       const uint32_t a_dst0 = smem_base + C::A_OFF, b_dst0 = smem_base + C::B_OFF;
       const uint32_t sfa_dst0 = smem_base + C::SFA_OFF, sfb_dst0 = smem_base + C::SFB_OFF;
       const uint32_t leader_full0 = kPair ? map_to_cta(full_bar(0), 0) : full_bar(0);
-      for (int t = sched_id; t < total_tiles && ok; t += sched_stride) {
-        const Tile tile = decode_tile(prefix, p.offsets, p.num_experts, p.n_tiles, C::TILE_M, p.raster_group_m, t);
+      const bool skip_loads = side_b && p.test_skip_b_loads != 0;
+      int it = 0;
+      int t = fetcher ? (sched_id < total_tiles ? sched_id : -1) : next_tile(0);
+      while (t >= 0 && ok) {
+        int fetched = 0;
+        if (fetcher && lane == 0) fetched = atomicAdd(p.tile_counter, 1) + sched_stride;  // used after the k loop
+        const Tile tile = decode_tile(sched, p, C::TILE_M, t);
         const int n0 = tile.n_tile * BN;
         const int my_row0 = tile.row0 + (int)cta_rank * BM;
         const int nblk0 = n0 / 128;
@@ -457,10 +559,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         if (kDiscrete && side_b) {
           bmap = p.b_maps + tile.expert;
           tensormap_fence_acquire(bmap);
-          if (kPair) {
-            sfbmap = p.b_maps + p.num_experts + tile.expert;
-            tensormap_fence_acquire(sfbmap);
-          }
+          sfbmap = p.b_maps + p.num_experts + tile.expert;
+          tensormap_fence_acquire(sfbmap);
         }
         // Everything that changes per k-tile is a running value: the K coordinate, the scale-chunk
         // pointers and the stage's shared-memory / barrier addresses.
@@ -470,18 +570,20 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           const int b_row = n0 + (int)cta_rank * 128;
           const int m_blk = my_row0 / BM;
           for (int kt = 0; kt < p.k_tiles; ++kt, kc += BK) {
-            if (!__all_sync(0xffffffffu, mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, ST_PRODUCER_EMPTY))) { ok = false; break; }
+            if (!__all_sync(0xffffffffu, mbar_wait(empty_bar(stage), phase ^ 1, wc, ST_PRODUCER_EMPTY))) { ok = false; break; }
             const uint32_t fb = leader_full0 + 8u * stage;
-            if (elect_one()) {
+            if (elect_one() && !skip_loads) {
               if (!side_b) {
                 if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(stage), C::TX_BYTES);
                 tma_load_2d_pair(a_dst0 + stage * A_STAGE_BYTES, &tmap_a, fb, kc, my_row0);
                 tma_load_3d_pair(sfa_dst0 + stage * SFA_STAGE_BYTES, &tmap_sfa, fb, 0, kt, m_blk);
               } else if (kDiscrete) {
-                tma_load_2d_pair(b_dst0 + stage * C::B_STAGE_BYTES, bmap, fb, kc, b_row);
+                if (p.b_nmajor) tma_load_2d_pair(b_dst0 + stage * C::B_STAGE_BYTES, bmap, fb, b_row, kc);
+                else tma_load_2d_pair(b_dst0 + stage * C::B_STAGE_BYTES, bmap, fb, kc, b_row);
                 tma_load_3d_pair(sfb_dst0 + stage * SFB_STAGE_BYTES, sfbmap, fb, 0, kt, nblk0);
               } else {
-                tma_load_3d_pair(b_dst0 + stage * C::B_STAGE_BYTES, bmap, fb, kc, b_row, tile.expert);
+                if (p.b_nmajor) tma_load_3d_pair(b_dst0 + stage * C::B_STAGE_BYTES, bmap, fb, b_row, kc, tile.expert);
+                else tma_load_3d_pair(b_dst0 + stage * C::B_STAGE_BYTES, bmap, fb, kc, b_row, tile.expert);
                 tma_load_4d_pair(sfb_dst0 + stage * SFB_STAGE_BYTES, sfbmap, fb, 0, kt, nblk0, tile.expert);
               }
             }
@@ -489,12 +591,14 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             if (++stage == STAGES) { stage = 0; phase ^= 1; }
           }
         } else {
-          const bool two_chunks = p.n_blocks - nblk0 >= 2;
+          // scale chunks of B: per-expert tensor maps in discrete mode (a 128-row block beyond N reads as
+          // zeros and still counts its bytes), plain bulk copies of the chunks that exist otherwise
+          const bool two_chunks = kDiscrete || p.n_blocks - nblk0 >= 2;
           if (!side_b) {
             const uint8_t* sfa_src = p.sfa + (int64_t)(tile.row0 / BM) * p.rest_k * 512;
             const uint32_t tx = A_STAGE_BYTES + C::B_STAGE_BYTES + SFA_STAGE_BYTES + (two_chunks ? 1024u : 512u);
             for (int kt = 0; kt < p.k_tiles; ++kt, kc += BK, sfa_src += 512) {
-              if (!__all_sync(0xffffffffu, mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, ST_PRODUCER_EMPTY))) { ok = false; break; }
+              if (!__all_sync(0xffffffffu, mbar_wait(empty_bar(stage), phase ^ 1, wc, ST_PRODUCER_EMPTY))) { ok = false; break; }
               const uint32_t fb = full_bar(stage);
               if (elect_one()) {
                 mbar_arrive_expect_tx(fb, tx);
@@ -505,25 +609,58 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
               if (++stage == STAGES) { stage = 0; phase ^= 1; }
             }
           } else {
-            const uint8_t* sfb_e = kDiscrete ? reinterpret_cast<const uint8_t*>(p.sfb_ptrs[tile.expert])
-                                             : p.sfb + (int64_t)tile.expert * p.sfb_expert_bytes;
-            const uint8_t* sfb_src0 = sfb_e + (int64_t)nblk0 * p.rest_k * 512;
+            const uint8_t* sfb_src0 = kDiscrete ? nullptr : p.sfb + (int64_t)tile.expert * p.sfb_expert_bytes + (int64_t)nblk0 * p.rest_k * 512;
             const uint8_t* sfb_src1 = sfb_src0 + (int64_t)p.rest_k * 512;
             for (int kt = 0; kt < p.k_tiles; ++kt, kc += BK, sfb_src0 += 512, sfb_src1 += 512) {
-              if (!__all_sync(0xffffffffu, mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, ST_PRODUCER_EMPTY))) { ok = false; break; }
+              if (!__all_sync(0xffffffffu, mbar_wait(empty_bar(stage), phase ^ 1, wc, ST_PRODUCER_EMPTY))) { ok = false; break; }
               const uint32_t fb = full_bar(stage);
-              if (elect_one()) {
-                if (kDiscrete)
-                  tma_load_2d(b_dst0 + stage * C::B_STAGE_BYTES, bmap, fb, kc, n0);
-                else
-                  tma_load_3d(b_dst0 + stage * C::B_STAGE_BYTES, bmap, fb, kc, n0, tile.expert);
-                bulk_load(sfb_dst0 + stage * SFB_STAGE_BYTES, sfb_src0, 512, fb);
-                if (two_chunks) bulk_load(sfb_dst0 + stage * SFB_STAGE_BYTES + 512, sfb_src1, 512, fb);
+              if (elect_one() && !skip_loads) {
+                const uint32_t b_dst = b_dst0 + stage * C::B_STAGE_BYTES;
+                if (kDiscrete) {
+                  if (p.b_nmajor) {
+                    // two slabs of 128 columns x 128 K rows
+                    tma_load_2d(b_dst, bmap, fb, n0, kc);
+                    tma_load_2d(b_dst + 128 * BK, bmap, fb, n0 + 128, kc);
+                  } else {
+                    tma_load_2d(b_dst, bmap, fb, kc, n0);
+                  }
+                  tma_load_3d(sfb_dst0 + stage * SFB_STAGE_BYTES, sfbmap, fb, 0, kt, nblk0);
+                } else {
+                  if (p.b_nmajor) {
+                    tma_load_3d(b_dst, bmap, fb, n0, kc, tile.expert);
+                    tma_load_3d(b_dst + 128 * BK, bmap, fb, n0 + 128, kc, tile.expert);
+                  } else {
+                    tma_load_3d(b_dst, bmap, fb, kc, n0, tile.expert);
+                  }
+                  bulk_load(sfb_dst0 + stage * SFB_STAGE_BYTES, sfb_src0, 512, fb);
+                  if (two_chunks) bulk_load(sfb_dst0 + stage * SFB_STAGE_BYTES + 512, sfb_src1, 512, fb);
+                }
               }
               __syncwarp();
               if (++stage == STAGES) { stage = 0; phase ^= 1; }
             }
           }
+        }
+        if (!ok) break;
+        ++it;
+        if (fetcher) {
+          // hand the next position (or the end mark) to every other warp of the CTA pair, then take it
+          fetched = __shfl_sync(0xffffffffu, fetched, 0);
+          const int next = fetched < total_tiles ? fetched : -1;
+          const int q = (it - 1) % SCHED_RING;
+          if (!__all_sync(0xffffffffu, mbar_wait(info_empty_bar(q), ((uint32_t)((it - 1) / SCHED_RING) & 1u) ^ 1u, wc, ST_SCHED_EMPTY))) { ok = false; break; }
+          if (lane == 0) {
+            ring[q] = next;
+            mbar_arrive(info_full_bar(q));
+            if (kPair) {
+              st_shared_cluster(map_to_cta(smem_u32(const_cast<int*>(&ring[q])), 1), (uint32_t)next);
+              mbar_arrive_cluster_release(map_to_cta(info_full_bar(q), 1));
+            }
+          }
+          __syncwarp();
+          t = next;
+        } else {
+          t = next_tile(it);
         }
       }
     }
@@ -535,12 +672,15 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       // The issuing thread is a serial instruction stream: four MMAs, three scale copies and a
       // commit per k-tile must cost as few instructions as possible, so every descriptor is
       // (constant high word, running low word) and the instruction descriptors are immediates.
-      const uint32_t idesc = make_idesc_mxf8(C::TILE_M, BN) | p.ab_format;
+      // B in N-major form: bit 16 of the instruction descriptor, 128-column slabs 16 KB apart
+      // (leading byte offset), 32 K rows = 4096 bytes per MMA.
+      const uint32_t idesc = make_idesc_mxf8(C::TILE_M, BN) | p.ab_format | (p.b_nmajor ? (1u << 16) : 0u);
       constexpr uint32_t AB_HI = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO 1024, version 1, 128-byte swizzle
       constexpr uint32_t SF_HI = (128u >> 4) | (1u << 14);                // SBO 128, version 1, no swizzle
       constexpr uint32_t AB_LBO = 1u << 16;                               // leading byte offset 16 (unused by swizzled K-major)
       const uint32_t a_lo0 = ((smem_base + C::A_OFF) >> 4) | AB_LBO;
-      const uint32_t b_lo0 = ((smem_base + C::B_OFF) >> 4) | AB_LBO;
+      const uint32_t b_lo0 = ((smem_base + C::B_OFF) >> 4) | (p.b_nmajor ? ((uint32_t)(128 * BK) >> 4) << 16 : AB_LBO);
+      const uint32_t b_kstep = p.b_nmajor ? (32u * 128u) >> 4 : 2u;  // 32 K elements further, in 16-byte units
       const uint32_t sfa_lo0 = (smem_base + C::SFA_OFF) >> 4;
       const uint32_t sfb_lo0 = (smem_base + C::SFB_OFF) >> 4;
       auto desc = [](uint32_t lo, uint32_t hi) { return ((uint64_t)hi << 32) | lo; };
@@ -549,11 +689,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       uint32_t sf_buf = 0;
       int it = 0;
       bool ok = true;
-      for (int t = sched_id; t < total_tiles && ok; t += sched_stride, ++it) {
+      for (int t = next_tile(0); t >= 0 && ok; t = next_tile(++it)) {
         const uint32_t acc = tmem_base + ((it & 1) ? TMEM_ACC1_COL : 0);
         if (it > 0) {
           // previous tile's epilogue has drained the 32 columns both accumulators share
-          if (!__all_sync(0xffffffffu, mbar_wait(overlap_bar, (it - 1) & 1, abort_flag, ST_MMA_OVERLAP))) { ok = false; break; }
+          if (!__all_sync(0xffffffffu, mbar_wait(overlap_bar, (it - 1) & 1, wc, ST_MMA_OVERLAP))) { ok = false; break; }
           tc_fence_after();
         }
         for (int kt = 0; kt < p.k_tiles; ++kt) {
@@ -561,7 +701,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           // transaction count; no tcgen05 fence is needed between this wait and the MMAs
           // (the outcome is voted so that a wait that gives up takes the whole warp out of the loop)
           bool landed = mbar_try_wait(full_bar(stage), phase);
-          if (!landed) landed = mbar_wait(full_bar(stage), phase, abort_flag, ST_MMA_FULL);
+          if (!landed) landed = mbar_wait(full_bar(stage), phase, wc, ST_MMA_FULL);
           if (!__all_sync(0xffffffffu, landed)) { ok = false; break; }
           const uint32_t sfa_t = tmem_base + TMEM_SF_COL + 16 * sf_buf;
           const uint32_t sfb_t = sfa_t + 4;
@@ -580,13 +720,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             if (full_k) {
               // 32 bytes along K inside the 128-byte swizzle row = +2 in 16-byte units
               mma_mxf8_ss_pair(acc, desc(a_lo, AB_HI), desc(b_lo, AB_HI), idesc_with_sf_id(idesc, 0, 0), sfa_t, sfb_t, not_first);
-              mma_mxf8_ss_pair(acc, desc(a_lo + 2, AB_HI), desc(b_lo + 2, AB_HI), idesc_with_sf_id(idesc, 1, 1), sfa_t, sfb_t, 1);
-              mma_mxf8_ss_pair(acc, desc(a_lo + 4, AB_HI), desc(b_lo + 4, AB_HI), idesc_with_sf_id(idesc, 2, 2), sfa_t, sfb_t, 1);
-              mma_mxf8_ss_pair(acc, desc(a_lo + 6, AB_HI), desc(b_lo + 6, AB_HI), idesc_with_sf_id(idesc, 3, 3), sfa_t, sfb_t, 1);
+              mma_mxf8_ss_pair(acc, desc(a_lo + 2, AB_HI), desc(b_lo + b_kstep, AB_HI), idesc_with_sf_id(idesc, 1, 1), sfa_t, sfb_t, 1);
+              mma_mxf8_ss_pair(acc, desc(a_lo + 4, AB_HI), desc(b_lo + 2 * b_kstep, AB_HI), idesc_with_sf_id(idesc, 2, 2), sfa_t, sfb_t, 1);
+              mma_mxf8_ss_pair(acc, desc(a_lo + 6, AB_HI), desc(b_lo + 3 * b_kstep, AB_HI), idesc_with_sf_id(idesc, 3, 3), sfa_t, sfb_t, 1);
             } else {
               const int kblocks = (p.k - kt * BK + 31) / 32;
               for (int kb = 0; kb < kblocks; ++kb)
-                mma_mxf8_ss_pair(acc, desc(a_lo + 2 * kb, AB_HI), desc(b_lo + 2 * kb, AB_HI), idesc_with_sf_id(idesc, kb, kb), sfa_t,
+                mma_mxf8_ss_pair(acc, desc(a_lo + 2 * kb, AB_HI), desc(b_lo + kb * b_kstep, AB_HI), idesc_with_sf_id(idesc, kb, kb), sfa_t,
                                  sfb_t, (kt | kb) != 0);
             }
             tc_commit_pair(empty_bar(stage), 3);  // frees this stage in both CTAs
@@ -596,13 +736,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             tmem_cp_sf(sfb_t + 4, desc(sfb_lo + 32, SF_HI));
             if (full_k) {
               mma_mxf8_ss(acc, desc(a_lo, AB_HI), desc(b_lo, AB_HI), idesc_with_sf_id(idesc, 0, 0), sfa_t, sfb_t, not_first);
-              mma_mxf8_ss(acc, desc(a_lo + 2, AB_HI), desc(b_lo + 2, AB_HI), idesc_with_sf_id(idesc, 1, 1), sfa_t, sfb_t, 1);
-              mma_mxf8_ss(acc, desc(a_lo + 4, AB_HI), desc(b_lo + 4, AB_HI), idesc_with_sf_id(idesc, 2, 2), sfa_t, sfb_t, 1);
-              mma_mxf8_ss(acc, desc(a_lo + 6, AB_HI), desc(b_lo + 6, AB_HI), idesc_with_sf_id(idesc, 3, 3), sfa_t, sfb_t, 1);
+              mma_mxf8_ss(acc, desc(a_lo + 2, AB_HI), desc(b_lo + b_kstep, AB_HI), idesc_with_sf_id(idesc, 1, 1), sfa_t, sfb_t, 1);
+              mma_mxf8_ss(acc, desc(a_lo + 4, AB_HI), desc(b_lo + 2 * b_kstep, AB_HI), idesc_with_sf_id(idesc, 2, 2), sfa_t, sfb_t, 1);
+              mma_mxf8_ss(acc, desc(a_lo + 6, AB_HI), desc(b_lo + 3 * b_kstep, AB_HI), idesc_with_sf_id(idesc, 3, 3), sfa_t, sfb_t, 1);
             } else {
               const int kblocks = (p.k - kt * BK + 31) / 32;
               for (int kb = 0; kb < kblocks; ++kb)
-                mma_mxf8_ss(acc, desc(a_lo + 2 * kb, AB_HI), desc(b_lo + 2 * kb, AB_HI), idesc_with_sf_id(idesc, kb, kb), sfa_t, sfb_t,
+                mma_mxf8_ss(acc, desc(a_lo + 2 * kb, AB_HI), desc(b_lo + kb * b_kstep, AB_HI), idesc_with_sf_id(idesc, kb, kb), sfa_t, sfb_t,
                             (kt | kb) != 0);
             }
             tc_commit(empty_bar(stage));  // frees the smem stage once these MMAs have read it
@@ -639,8 +779,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     };
     int it = 0;
     bool ok = true;
-    for (int t = sched_id; t < total_tiles && ok; t += sched_stride, ++it) {
-      Tile tile = decode_tile(prefix, p.offsets, p.num_experts, p.n_tiles, C::TILE_M, p.raster_group_m, t);
+    for (int t = next_tile(0); t >= 0 && ok; t = next_tile(++it)) {
+      Tile tile = decode_tile(sched, p, C::TILE_M, t);
       tile.row0 += (int)cta_rank * BM;  // this CTA's 128 rows
       const int n0 = tile.n_tile * BN;
       const int row = tile.row0 + r_in_tile;
@@ -661,7 +801,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       float thread_amax = 0.f;
       uint32_t sf_row_word = 0;  // four E8M0 bytes of this row (K group = 128 output columns)
 
-      if (!mbar_wait(acc_full_bar(it & 1), (it >> 1) & 1, abort_flag, ST_EPI_ACC)) { ok = false; break; }
+      if (!mbar_wait(acc_full_bar(it & 1), (it >> 1) & 1, wc, ST_EPI_ACC)) { ok = false; break; }
       tc_fence_after();
 
       if (kEpi == EPI_FC1) {
@@ -748,7 +888,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
               int rest = p.sfd_col_rest_k;
               if (p.discrete_col_sfd) {
                 // per-expert block: rows counted from the expert's first row
-                const int start = tile.expert == 0 ? 0 : p.offsets[tile.expert - 1];
+                const int start = expert_first_row(p, tile.expert);
                 blk_base = (int64_t)(start / 128) * ((p.n_out + 127) / 128) * 512;
                 rb = ((tile.row0 - start) >> 5) + quarter;
                 rest = ((p.offsets[tile.expert] - start) / 32 + 3) / 4;
@@ -833,7 +973,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
               int rb = (tile.row0 >> 5) + quarter;
               int rest = p.sfd_col_rest_k;
               if (p.discrete_col_sfd) {
-                const int start = tile.expert == 0 ? 0 : p.offsets[tile.expert - 1];
+                const int start = expert_first_row(p, tile.expert);
                 blk_base = (int64_t)(start / 128) * ((p.n_out + 127) / 128) * 512;
                 rb = ((tile.row0 - start) >> 5) + quarter;
                 rest = ((p.offsets[tile.expert] - start) / 32 + 3) / 4;
@@ -901,8 +1041,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 // ---------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(32)
     build_expert_tensormaps_kernel(const __grid_constant__ CUtensorMap proto_b, const __grid_constant__ CUtensorMap proto_sfb,
-                                   const int64_t* b_ptrs, const int64_t* sfb_ptrs, const void* fallback, CUtensorMap* out,
-                                   int num_experts) {
+                                   const int64_t* b_ptrs, const int64_t* sfb_ptrs, const void* fallback_b, const void* fallback_sf,
+                                   CUtensorMap* out, int num_experts) {
   // slots [0, E): weight maps; slots [E, 2E): scale-factor maps
   __shared__ __align__(128) CUtensorMap s_map;
   const int slot = blockIdx.x;
@@ -915,16 +1055,20 @@ __global__ void __launch_bounds__(32)
   __syncwarp();
   if (lane == 0) {
     uint64_t addr = (uint64_t)(is_sf ? sfb_ptrs[e] : b_ptrs[e]);
+    const uint32_t map_smem = smem_u32(&s_map);
     if (addr == 0 || (addr & 15)) {
-      // a misaligned or null pointer would fault the TMA unit: record it and point the map at
-      // memory that is known to be valid instead
+      // A misaligned or null pointer would fault the TMA unit.  Record it, point the map at memory
+      // that is known to be valid (the caller's A / SFA) and shrink the map's extents to what that
+      // memory surely holds (16 bytes of A, one 512-byte chunk of SFA): every load through the map
+      // then reads at most that and fills the rest of its box with zeros.  The expert's results are
+      // meaningless; the status word says why.
       atomicCAS(&g_device_status, 0, 201);
-      addr = (uint64_t)fallback;
+      addr = (uint64_t)(is_sf ? fallback_sf : fallback_b);
+      if (!is_sf) asm volatile("tensormap.replace.tile.global_dim.shared::cta.b1024.b32 [%0], 0, %1;" ::"r"(map_smem), "r"(16) : "memory");
+      asm volatile("tensormap.replace.tile.global_dim.shared::cta.b1024.b32 [%0], 1, %1;" ::"r"(map_smem), "r"(1) : "memory");
+      if (is_sf) asm volatile("tensormap.replace.tile.global_dim.shared::cta.b1024.b32 [%0], 2, %1;" ::"r"(map_smem), "r"(1) : "memory");
     }
-    asm volatile("tensormap.replace.tile.global_address.shared::cta.b1024.b64 [%0], %1;" ::"r"(
-                     smem_u32(&s_map)),
-                 "l"(addr)
-                 : "memory");
+    asm volatile("tensormap.replace.tile.global_address.shared::cta.b1024.b64 [%0], %1;" ::"r"(map_smem), "l"(addr) : "memory");
   }
   __syncwarp();
   asm volatile(
@@ -1073,6 +1217,8 @@ static int run_gemm(int epi, const b200moe_gemm_args* a, void* stream_v) {
   if (a->num_experts > MAX_EXPERTS)
     return fail(B200MOE_E_SHAPE, "%s: at most %d experts are supported, got %d", op, MAX_EXPERTS, a->num_experts);
   if (a->k % 16 != 0) return fail(B200MOE_E_SHAPE, "%s: k (%lld) must be a multiple of 16", op, (long long)a->k);
+  if ((a->flags & B200MOE_FLAG_B_NMAJOR) && a->n % 16 != 0)
+    return fail(B200MOE_E_SHAPE, "%s: N-major B needs n (%lld) to be a multiple of 16", op, (long long)a->n);
   if (epi == EPI_FC1 && a->n % 64 != 0)
     return fail(B200MOE_E_SHAPE, "%s: n (%lld) must be a multiple of 64 (32-column gate/up blocks)", op, (long long)a->n);
   if (epi == EPI_FC2 && a->n % 32 != 0)
@@ -1090,6 +1236,10 @@ static int run_gemm(int epi, const b200moe_gemm_args* a, void* stream_v) {
     return fail(B200MOE_E_UNSUPPORTED, "%s: ab_dtype %d (E4M3 and E5M2 are built)", op, a->ab_dtype);
   if (a->act_func != B200MOE_ACT_SWIGLU && a->act_func != B200MOE_ACT_GEGLU)
     return fail(B200MOE_E_UNSUPPORTED, "%s: act_func %d", op, a->act_func);
+  if (a->wait_limit_ms < 0) return fail(B200MOE_E_SHAPE, "%s: wait_limit_ms must not be negative", op);
+  if (a->sched_light_m_tiles < -1) return fail(B200MOE_E_SHAPE, "%s: sched_light_m_tiles must be -1, 0 or positive", op);
+  const bool dynamic = (a->flags & B200MOE_FLAG_DYNAMIC_SCHED) != 0;
+  const bool b_nmajor = (a->flags & B200MOE_FLAG_B_NMAJOR) != 0;
   if (a->bias) {
     if (a->bias_dtype != B200MOE_DTYPE_BF16 && a->bias_dtype != B200MOE_DTYPE_F16 && a->bias_dtype != B200MOE_DTYPE_F32)
       return fail(B200MOE_E_UNSUPPORTED, "%s: bias_dtype %d", op, a->bias_dtype);
@@ -1151,6 +1301,13 @@ static int run_gemm(int epi, const b200moe_gemm_args* a, void* stream_v) {
   p.d_f16 = a->d_dtype == B200MOE_DTYPE_F16;
   p.c_f16 = a->c_dtype == B200MOE_DTYPE_F16;
   p.discrete_col_sfd = (a->flags & B200MOE_FLAG_DISCRETE_COL_SFD) ? 1 : 0;
+  p.first_has_prev = (a->flags & B200MOE_FLAG_OFFSETS_HAVE_PREV) ? 1 : 0;
+  p.b_nmajor = b_nmajor ? 1 : 0;
+  p.dynamic_sched = dynamic ? 1 : 0;
+  p.test_skip_b_loads = (a->flags & B200MOE_FLAG_TEST_SKIP_B_LOADS) ? 1 : 0;
+  p.wait_limit_ns = a->wait_limit_ms > 0 ? (uint64_t)a->wait_limit_ms * 1000000ull : kWaitLimitNs;
+  // experts of at most this many row tiles count as weight-streaming ("light") in the tile schedule
+  p.light_m_tiles = a->sched_light_m_tiles < 0 ? 0 : (a->sched_light_m_tiles == 0 ? DEFAULT_LIGHT_M_TILES : a->sched_light_m_tiles);
   {
     // 256-bit stores need 32-byte aligned bases and row pitches that keep a 32-column block aligned
     const int64_t d_pitch = (int64_t)p.n_out * (d_fp8 ? 1 : 2);
@@ -1189,11 +1346,24 @@ static int run_gemm(int epi, const b200moe_gemm_args* a, void* stream_v) {
     rc = encode_map(&maps[2], CU_TENSOR_MAP_DATA_TYPE_UINT32, a->sfa, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (rc) return rc;
   }
+  // workspace: [E x 2 tensor maps of 128 bytes] (discrete) then [128 bytes, the tile counter] (dynamic scheduler)
+  const int64_t maps_bytes = discrete ? (int64_t)p.num_experts * 256 : 0;
+  const int64_t need = maps_bytes + (dynamic ? 128 : 0);
+  if (need > 0 && (!a->workspace || a->workspace_bytes < need || ((uintptr_t)a->workspace & 127)))
+    return fail(B200MOE_E_WORKSPACE, "%s: needs a 128-byte aligned workspace of %lld bytes (b200moe_workspace_bytes)", op, (long long)need);
   if (!discrete) {
-    const uint64_t dims[3] = {(uint64_t)p.k, (uint64_t)p.n, (uint64_t)p.num_experts};
-    const uint64_t strides[2] = {(uint64_t)p.k, (uint64_t)p.n * (uint64_t)p.k};
-    const uint32_t box[3] = {BK, b_rows, 1};
-    rc = encode_map(&maps[1], CU_TENSOR_MAP_DATA_TYPE_UINT8, a->b, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (!b_nmajor) {
+      const uint64_t dims[3] = {(uint64_t)p.k, (uint64_t)p.n, (uint64_t)p.num_experts};
+      const uint64_t strides[2] = {(uint64_t)p.k, (uint64_t)p.n * (uint64_t)p.k};
+      const uint32_t box[3] = {BK, b_rows, 1};
+      rc = encode_map(&maps[1], CU_TENSOR_MAP_DATA_TYPE_UINT8, a->b, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    } else {
+      // [E][K][N]: slabs of 128 columns x 128 K rows (128-byte swizzle rows run along N)
+      const uint64_t dims[3] = {(uint64_t)p.n, (uint64_t)p.k, (uint64_t)p.num_experts};
+      const uint64_t strides[2] = {(uint64_t)p.n, (uint64_t)p.n * (uint64_t)p.k};
+      const uint32_t box[3] = {128, BK, 1};
+      rc = encode_map(&maps[1], CU_TENSOR_MAP_DATA_TYPE_UINT8, a->b, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    }
     if (rc) return rc;
     if (pair) {
       const uint64_t sdims[4] = {128, (uint64_t)p.rest_k, (uint64_t)p.n_blocks, (uint64_t)p.num_experts};
@@ -1203,14 +1373,18 @@ static int run_gemm(int epi, const b200moe_gemm_args* a, void* stream_v) {
       if (rc) return rc;
     }
   } else {
-    const int64_t need = b200moe_workspace_bytes(p.num_experts, 1);
-    if (!a->workspace || a->workspace_bytes < need || ((uintptr_t)a->workspace & 127))
-      return fail(B200MOE_E_WORKSPACE, "%s: discrete mode needs a 128-byte aligned workspace of %lld bytes", op, (long long)need);
     // prototypes; the global addresses are patched per expert on the device
-    const uint64_t dims[2] = {(uint64_t)p.k, (uint64_t)p.n};
-    const uint64_t strides[1] = {(uint64_t)p.k};
-    const uint32_t box[2] = {BK, b_rows};
-    rc = encode_map(&maps[1], CU_TENSOR_MAP_DATA_TYPE_UINT8, a->a, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (!b_nmajor) {
+      const uint64_t dims[2] = {(uint64_t)p.k, (uint64_t)p.n};
+      const uint64_t strides[1] = {(uint64_t)p.k};
+      const uint32_t box[2] = {BK, b_rows};
+      rc = encode_map(&maps[1], CU_TENSOR_MAP_DATA_TYPE_UINT8, a->a, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    } else {
+      const uint64_t dims[2] = {(uint64_t)p.n, (uint64_t)p.k};
+      const uint64_t strides[1] = {(uint64_t)p.n};
+      const uint32_t box[2] = {128, BK};
+      rc = encode_map(&maps[1], CU_TENSOR_MAP_DATA_TYPE_UINT8, a->a, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    }
     if (rc) return rc;
     const uint64_t sdims[3] = {128, (uint64_t)p.rest_k, (uint64_t)p.n_blocks};
     const uint64_t sstrides[2] = {sf_chunk_stride, sf_row_stride};
@@ -1218,9 +1392,13 @@ static int run_gemm(int epi, const b200moe_gemm_args* a, void* stream_v) {
     rc = encode_map(&maps[3], CU_TENSOR_MAP_DATA_TYPE_UINT32, a->sfa, 3, sdims, sstrides, sbox, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (rc) return rc;
     p.b_maps = (const CUtensorMap*)a->workspace;
-    build_expert_tensormaps_kernel<<<2 * p.num_experts, 32, 0, stream>>>(maps[1], maps[3], a->b_ptrs, a->sfb_ptrs, a->a,
+    build_expert_tensormaps_kernel<<<2 * p.num_experts, 32, 0, stream>>>(maps[1], maps[3], a->b_ptrs, a->sfb_ptrs, a->a, a->sfa,
                                                                           (CUtensorMap*)a->workspace, p.num_experts);
     B200_CUDA_CHECK(cudaGetLastError());
+  }
+  if (dynamic) {
+    p.tile_counter = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(a->workspace) + maps_bytes);
+    B200_CUDA_CHECK(cudaMemsetAsync(p.tile_counter, 0, sizeof(int), stream));
   }
 
   const int tile_m = pair ? 256 : 128;
@@ -1291,6 +1469,8 @@ int b200moe_fc1_swiglu_discrete_noalloc(const b200moe_gemm_args* args, void* str
                 args->num_experts, B200MOE_NOALLOC_MAX_EXPERTS);
   if (b200moe_workspace_bytes(args->num_experts, 1) > (int64_t)B200MOE_NOALLOC_SCRATCH_BYTES)
     return fail(B200MOE_E_SHAPE, "fc1_swiglu_discrete_noalloc: built-in scratch too small for %d experts", args->num_experts);
+  if (args->flags & B200MOE_FLAG_DYNAMIC_SCHED)
+    return fail(B200MOE_E_UNSUPPORTED, "fc1_swiglu_discrete_noalloc: the dynamic tile scheduler needs a caller workspace; use b200moe_fc1_swiglu");
   if (args->m_rows == 0 || args->num_experts <= 0) return run_gemm(EPI_FC1, args, stream);
   void* scratch = nullptr;
   int rc = noalloc_scratch_address(&scratch);
@@ -1305,9 +1485,12 @@ int b200moe_fc1_swiglu(const b200moe_gemm_args* args, void* stream) { return b20
 
 int b200moe_fc2_quant(const b200moe_gemm_args* args, void* stream) { return b200moe::run_gemm(b200moe::EPI_FC2, args, stream); }
 
-int64_t b200moe_workspace_bytes(int32_t num_experts, int32_t discrete) {
-  if (!discrete || num_experts <= 0) return 0;
-  return (int64_t)num_experts * 256;  // one weight map and one scale-factor map per expert
+int64_t b200moe_workspace_bytes(int32_t num_experts, int32_t mode) {
+  if (num_experts <= 0) return 0;
+  int64_t bytes = 0;
+  if (mode & B200MOE_WORKSPACE_DISCRETE) bytes += (int64_t)num_experts * 256;  // one weight map and one scale-factor map per expert
+  if (mode & B200MOE_WORKSPACE_DYNAMIC_SCHED) bytes += 128;                      // the tile counter
+  return bytes;
 }
 
 const char* b200moe_last_error(void) { return b200moe::tl_error; }
@@ -1322,6 +1505,6 @@ int b200moe_device_status(int clear) {
   return v;
 }
 
-int b200moe_abi_version(void) { return 5; }
+int b200moe_abi_version(void) { return 6; }
 
 }  // extern "C"

@@ -8,7 +8,8 @@ device addresses arrive as two 1-D int64 CUDA tensors that are only ever read on
 ``execute`` allocates nothing (descriptor workspace is created in ``compile``).
 
 ``act_func="geglu"`` and a fused bias ``(n, l)`` (stride ``(1, n)``) are supported as in the reference's
-GLU kernel.  Not built (``NotImplementedError``): N-major weights.
+GLU kernel; ``b_major="n"`` takes per-expert ``[k][n]`` weights and ``use_dynamic_sched=True`` the
+atomic-counter tile scheduler.
 """
 
 from __future__ import annotations
@@ -147,7 +148,6 @@ class DiscreteGroupedGemmSwigluSm100(OperatorBase):
         if self.bias is not None:
             self._check_stride(self.bias, (1, n), "bias must have stride (1, n)")
             self._check_dtype(self.bias, [torch.bfloat16, torch.float16], "bias")
-        self._not_implemented_error_if(self.b_major != "k", "N-major B is not built; pass K-major weights")
         self._not_implemented_error_if(self.ab_dtype not in (torch.float8_e4m3fn, torch.float8_e5m2), f"only MXFP8 (E4M3 or E5M2) inputs are built, got {self.ab_dtype}")
         self._not_implemented_error_if(self.sf_dtype != torch.float8_e8m0fnu, f"only E8M0 scale factors are built, got {self.sf_dtype}")
         self._not_implemented_error_if(self.c is not None and self.c_dtype not in (torch.bfloat16, torch.float16), f"only bf16 and fp16 C are built, got {self.c_dtype}")
@@ -166,7 +166,8 @@ class DiscreteGroupedGemmSwigluSm100(OperatorBase):
             self.check_support()
         ops._lib.load()
         if self._workspace is None:
-            self._workspace = torch.empty(ops.workspace_bytes(self.expert_cnt, True), dtype=torch.uint8, device=self.a.device)
+            nbytes = ops.workspace_bytes(self.expert_cnt, True, bool(self.use_dynamic_sched))
+            self._workspace = torch.empty(nbytes, dtype=torch.uint8, device=self.a.device)
         self._is_compiled = True
 
     def execute(
@@ -221,6 +222,8 @@ class DiscreteGroupedGemmSwigluSm100(OperatorBase):
             bias=bias_tensor,
             act_func=self.act_func,
             stream=current_stream,
+            dynamic_sched=bool(self.use_dynamic_sched),
+            b_nmajor=self.b_major == "n",
         )
 
 

@@ -12,8 +12,8 @@ with stride ``(1, n)``:
     geglu:   gate <= 7, -7 <= up <= 7 (after the C store);  D = (up + 1) * gate * sigmoid(1.702 gate) * prob
 
 The class owns one of this package's two FC1 operators and forwards to it; both launch the same
-kernel.  ``use_dynamic_sched`` is accepted and ignored (the tile schedule is static), N-major weights
-raise ``NotImplementedError``.
+kernel.  ``use_dynamic_sched=True`` hands tiles out through an atomic counter in either weight mode;
+``b_major="n"`` (discrete mode) takes per-expert ``[k][n]`` weights.
 """
 
 from __future__ import annotations
@@ -86,11 +86,13 @@ class GroupedGemmGluSm100(OperatorBase):
             self._value_error_if(sample_b is None or sample_sfb is None, "dense mode needs sample_b and sample_sfb")
             self._op = GroupedGemmSwigluSm100(sample_a, sample_b, sample_c, sample_d, sample_sfa, sample_sfb, sample_padded_offsets,
                                               sample_alpha, sample_d_col, **common)  # fmt: skip
+            self._op.use_dynamic_sched = bool(use_dynamic_sched)
         self.expert_cnt = self._op.expert_cnt
 
     def check_support(self) -> bool:
         self._value_error_if(self.b_major not in ("k", "n"), f"b_major must be 'k' or 'n', got {self.b_major}")
-        self._not_implemented_error_if(self.b_major != "k", "N-major B is not built; pass K-major weights")
+        # dense weights carry their layout in their strides (K-major only for FC1, as in the reference);
+        # b_major describes the allocations behind the pointers of discrete mode
         self._is_supported = self._op.check_support()
         return self._is_supported
 

@@ -8,9 +8,14 @@ descriptors are built on the device from the pointer arrays into a workspace the
 allocates in ``compile()``, so ``execute()`` allocates nothing and never reads the pointers on
 the host.
 
-Not built (``NotImplementedError``): N-major B (``b_major="n"``), inputs other than
-E4M3 + E8M0/32, D other than bf16 / E4M3.  ``use_dynamic_sched`` is accepted and ignored: the
-tile schedule is static.
+B may be K-major or, as in the reference for FP8 operands, N-major: a dense ``b_tensor`` with
+strides ``(1, n, n*k)``, or ``b_major="n"`` with discrete pointers (each expert one ``[k][n]``
+allocation).  ``use_dynamic_sched=True`` hands tiles out through an atomic counter (the reference's
+dynamic MoE scheduler, python/cudnn/grouped_gemm/moe_persistent_scheduler.py:838-893); results are
+bit-identical to the static schedule.
+
+Not built (``NotImplementedError``): inputs other than MXFP8 (E4M3 / E5M2 with E8M0 scales per
+32), D other than bf16 / fp16 / E4M3 / E5M2.
 """
 
 from __future__ import annotations
@@ -159,8 +164,15 @@ class GroupedGemmQuantSm100(OperatorBase):
 
         self._check_stride(self.a, (k, 1, tensor_m * k), "A must have k-major layout")
         self._value_error_if(self.b_major not in ("k", "n"), f"b_major must be 'k' or 'n', got {self.b_major}")
-        if self.b is not None and self.b_major == "k":
-            self._check_stride(self.b, (k, 1, n * k), "B must have k-major layout")
+        self._b_nmajor = self.b_major == "n"
+        if self.b is not None:
+            # dense weights: the strides say which way B is stored (the reference accepts both for fp8)
+            if n > 1 and k > 1 and self.b.stride[0] == 1 and self.b.stride[1] == n:
+                self._check_stride(self.b, (1, n, n * k), "For fp8 ab_dtype, B must have k- or n-major layout")
+                self._b_nmajor = True
+            else:
+                self._check_stride(self.b, (k, 1, n * k), "For fp8 ab_dtype, B must have k- or n-major layout")
+                self._b_nmajor = False
         self._check_stride(self.d, (n, 1, tensor_m * n), "D must have n-major layout")
         self._check_stride(self.d_col, (n, 1, tensor_m * n), "D_col must have n-major layout")
         for spec, mn, kk, ll in ((self.sfa, tensor_m, k, 1), (self.sfb, n, k, l), (self.sfd_row, tensor_m, n, 1), (self.sfd_col, n, tensor_m, 1)):
@@ -198,7 +210,6 @@ class GroupedGemmQuantSm100(OperatorBase):
             # (n, l) with stride (1, n), as the reference demands
             self._check_stride(self.bias, (1, n), "bias must have stride (1, n)")
             self._check_dtype(self.bias, [torch.bfloat16, torch.float16, torch.float32], "bias")
-        self._not_implemented_error_if(self.b_major != "k", "N-major B is not built; pass K-major weights")
         self._not_implemented_error_if(self.ab_dtype not in (torch.float8_e4m3fn, torch.float8_e5m2), f"only MXFP8 (E4M3 or E5M2) inputs are built, got {self.ab_dtype}")
         self._not_implemented_error_if(self.sf_dtype != torch.float8_e8m0fnu, f"only E8M0 scale factors are built, got {self.sf_dtype}")
         self._not_implemented_error_if(self.d_dtype not in (torch.bfloat16, torch.float16, torch.float8_e4m3fn, torch.float8_e5m2), f"only bf16, fp16, E4M3 and E5M2 D are built, got {self.d_dtype}")
@@ -217,8 +228,8 @@ class GroupedGemmQuantSm100(OperatorBase):
         if not self._is_supported:
             self.check_support()
         ops._lib.load()
-        if self.discrete and self._workspace is None:
-            nbytes = ops.workspace_bytes(self.expert_cnt, True)
+        nbytes = ops.workspace_bytes(self.expert_cnt, self.discrete, bool(self.use_dynamic_sched))
+        if nbytes and self._workspace is None:
             self._workspace = torch.empty(nbytes, dtype=torch.uint8, device=self.a.device)
         self._is_compiled = True
 
@@ -244,13 +255,15 @@ class GroupedGemmQuantSm100(OperatorBase):
         d_row_map: Optional[torch.Tensor] = None,
         d_peer_ptrs: Optional[torch.Tensor] = None,
         d_peer_slots: int = 0,
+        expert_range: Optional[Tuple[int, int]] = None,
     ) -> None:
         """Launch on ``current_stream``; allocates nothing.  ``d_row_map`` (int32 ``[M]``, not in the
         reference) stores row ``r`` of a bf16 result at row ``d_row_map[r]`` of ``d_tensor`` (negative:
         not stored), so a caller can receive the rows in another order, e.g. all-to-all order.  With
         ``d_peer_ptrs`` (int64 device tensor of G buffer addresses, each ``[d_peer_slots, N]`` bf16) a map
         value ``v`` addresses row ``v % d_peer_slots`` of rank ``v // d_peer_slots``'s buffer: the epilogue
-        stores over NVLink into the ranks the rows came from."""
+        stores over NVLink into the ranks the rows came from.  ``expert_range = (lo, hi)`` (not in the
+        reference) computes experts ``lo .. hi - 1`` only, on the same full tensors."""
         self._ensure_compiled()
         tensor_m, k = a_tensor.shape[0], a_tensor.shape[1]
         if tensor_m == 0:
@@ -294,6 +307,9 @@ class GroupedGemmQuantSm100(OperatorBase):
             d_peer_slots=d_peer_slots,
             bias=bias_tensor,
             stream=current_stream,
+            dynamic_sched=bool(self.use_dynamic_sched),
+            b_nmajor=self._b_nmajor,
+            expert_range=expert_range,
         )
 
 
@@ -378,7 +394,7 @@ def grouped_gemm_quant_wrapper_sm100(
 
     cache_key = (
         is_dense, a_tensor.dtype, sfa_tensor.dtype, d_dtype, tuple(a_tensor.shape[1:]),
-        tuple(b_tensor.shape) if is_dense else (n, l, b_dtype), b_major, acc_dtype, tuple(mma_tiler_mn),
+        (tuple(b_tensor.shape), tuple(b_tensor.stride())) if is_dense else (n, l, b_dtype), b_major, acc_dtype, tuple(mma_tiler_mn),
         None if cluster_shape_mn is None else tuple(cluster_shape_mn), sf_vec_size, vector_f32, m_aligned,
         discrete_col_sfd, use_dynamic_sched, norm_const_tensor is not None, bias_tensor is not None, str(dev),
     )  # fmt: skip

@@ -94,6 +94,10 @@ class GroupedGemmSwigluSm100(OperatorBase):
         self.discrete_col_sfd = discrete_col_sfd
         # SMs left free for a concurrently running (e.g. NCCL) kernel, as in the reference
         self.num_cluster_overlap_margin = int(os.getenv("CUDNNFE_CLUSTER_OVERLAP_MARGIN", "0"))
+        # the reference's dense FC1 class has a static scheduler only; its unified GLU front end
+        # (grouped_gemm_glu.py) owns one of these objects and may switch the dynamic scheduler on
+        self.use_dynamic_sched = False
+        self._workspace = None
 
     # ------------------------------------------------------------------------------------
     def check_support(self) -> bool:
@@ -191,6 +195,9 @@ class GroupedGemmSwigluSm100(OperatorBase):
         if not self._is_supported:
             self.check_support()
         ops._lib.load()  # fails loudly when the CUDA library is missing
+        nbytes = ops.workspace_bytes(self.b.shape[2], False, bool(self.use_dynamic_sched))
+        if nbytes and self._workspace is None:
+            self._workspace = torch.empty(nbytes, dtype=torch.uint8, device=self.a.device)
         self._is_compiled = True
 
     def execute(
@@ -211,9 +218,11 @@ class GroupedGemmSwigluSm100(OperatorBase):
         prob_tensor: Optional[torch.Tensor] = None,
         current_stream=None,
         bias_tensor: Optional[torch.Tensor] = None,
+        expert_range: Optional[Tuple[int, int]] = None,
     ) -> None:
         """Launch on ``current_stream`` (``None`` = torch's current stream).  Allocates nothing and
-        does not synchronise; ``amax_tensor`` is only ever raised (atomic max)."""
+        does not synchronise; ``amax_tensor`` is only ever raised (atomic max).  ``expert_range = (lo, hi)``
+        (not in the reference) computes experts ``lo .. hi - 1`` only, on the same full tensors."""
         self._ensure_compiled()
         tensor_m, k = a_tensor.shape[0], a_tensor.shape[1]
         if tensor_m == 0:
@@ -245,6 +254,9 @@ class GroupedGemmSwigluSm100(OperatorBase):
             bias=bias_tensor,
             act_func=self.act_func,
             stream=current_stream,
+            workspace=self._workspace,
+            dynamic_sched=bool(self.use_dynamic_sched),
+            expert_range=expert_range,
         )
 
 

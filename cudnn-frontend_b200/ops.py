@@ -120,12 +120,27 @@ def launch_grouped_gemm(
     bias: Optional[torch.Tensor] = None,
     act_func: str = "swiglu",
     stream=None,
+    dynamic_sched: bool = False,
+    b_nmajor: bool = False,
+    expert_range: Optional[Tuple[int, int]] = None,
+    wait_limit_ms: int = 0,
+    light_m_tiles: Optional[int] = None,
+    test_skip_b_loads: bool = False,
 ) -> None:
     """Fill the C struct and call b200moe_fc1_swiglu / b200moe_fc2_quant.
 
     ``tile_mode``: ``"single"`` (128 x 256 tiles, one CTA), ``"pair"`` (256 x 256 tiles on CTA pairs)
     or ``None`` / ``"auto"`` (the library picks from the average group size).  The environment
-    variable ``B200MOE_TILE_MODE`` overrides ``None``."""
+    variable ``B200MOE_TILE_MODE`` overrides ``None``.
+
+    ``dynamic_sched``: tiles are drawn from an atomic counter (needs ``workspace`` with room for it,
+    see :func:`workspace_bytes`).  ``b_nmajor``: ``b`` is stored ``[E][k][n]`` (or one ``[k][n]``
+    allocation per expert behind ``b_ptrs``).  ``expert_range = (lo, hi)``: run experts ``lo .. hi - 1``
+    only; all per-expert tensors are still the full ones, rows of the other experts are left alone
+    (``lo > 0`` reads ``padded_offsets[lo - 1]`` as the slice's first row).  ``light_m_tiles``: experts with at
+    most that many row tiles are interleaved with the larger ones in the tile schedule (``None`` = the
+    library's default or ``B200MOE_LIGHT_M_TILES``, ``-1`` = experts in order).  ``wait_limit_ms`` and
+    ``test_skip_b_loads`` drive the bounded-wait test hook."""
     _require_cuda(a, sfa, padded_offsets, alpha, d, b, sfb, b_ptrs, sfb_ptrs, prob, norm_const, c, d_col, amax, sfd_row, sfd_col)
     args = _lib.GemmArgs()
     args.a, args.sfa = _ptr(a), _ptr(sfa)
@@ -138,6 +153,36 @@ def launch_grouped_gemm(
     args.workspace = _ptr(workspace)
     args.workspace_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
     args.m_rows, args.n, args.k, args.num_experts = m_rows, n, k, num_experts
+    extra_flags = 0
+    if expert_range is not None:
+        lo, hi = int(expert_range[0]), int(expert_range[1])
+        if not (0 <= lo < hi <= num_experts):
+            raise ValueError(f"expert_range {expert_range} outside [0, {num_experts}]")
+        # the slice's per-expert entries start at expert lo; its rows stay where they are
+        args.num_experts = hi - lo
+        args.padded_offsets = padded_offsets.data_ptr() + 4 * lo
+        args.alpha = alpha.data_ptr() + 4 * lo
+        if amax is not None:
+            args.amax = amax.data_ptr() + 4 * lo
+        if b is not None:
+            rest_k = ceil_div(ceil_div(k, 32), 4)
+            args.b = b.data_ptr() + lo * n * k
+            args.sfb = sfb.data_ptr() + lo * ceil_div(n, 128) * rest_k * 512
+        else:
+            args.b_ptrs = b_ptrs.data_ptr() + 8 * lo
+            args.sfb_ptrs = sfb_ptrs.data_ptr() + 8 * lo
+        if lo > 0:
+            extra_flags |= _lib.FLAG_OFFSETS_HAVE_PREV
+    if dynamic_sched:
+        extra_flags |= _lib.FLAG_DYNAMIC_SCHED
+    if b_nmajor:
+        extra_flags |= _lib.FLAG_B_NMAJOR
+    if test_skip_b_loads:
+        extra_flags |= _lib.FLAG_TEST_SKIP_B_LOADS
+    args.wait_limit_ms = int(wait_limit_ms)
+    if light_m_tiles is None:
+        light_m_tiles = int(os.environ.get("B200MOE_LIGHT_M_TILES", "0"))
+    args.sched_light_m_tiles = int(light_m_tiles)
     if d.dtype not in _D_DTYPES:
         raise NotImplementedError(f"D dtype {d.dtype} is not built (bf16, fp16, E4M3, E5M2 are)")
     args.d_dtype = _D_DTYPES[d.dtype]
@@ -149,6 +194,7 @@ def launch_grouped_gemm(
     if mode not in ("auto", "single", "pair"):
         raise ValueError(f"tile_mode must be 'auto', 'single' or 'pair', got {mode!r}")
     args.flags |= {"auto": 0, "single": _lib.FLAG_TILE_SINGLE, "pair": _lib.FLAG_TILE_PAIR}[mode]
+    args.flags |= extra_flags
     args.sm_margin = sm_margin
     args.d_row_map = _ptr(d_row_map)
     args.d_peer_ptrs = _ptr(d_peer_ptrs)
@@ -158,6 +204,8 @@ def launch_grouped_gemm(
         if bias.dtype not in _BIAS_DTYPES:
             raise NotImplementedError(f"bias dtype {bias.dtype} is not built (bf16, f16, f32 are)")
         args.bias_dtype = _BIAS_DTYPES[bias.dtype]
+        if expert_range is not None:
+            args.bias = bias.data_ptr() + int(expert_range[0]) * n * bias.element_size()
     if act_func not in ("swiglu", "geglu"):
         raise ValueError(f"act_func must be 'swiglu' or 'geglu', got {act_func!r}")
     args.act_func = _lib.ACT_GEGLU if act_func == "geglu" else _lib.ACT_SWIGLU
@@ -180,8 +228,11 @@ _D_DTYPES = {torch.bfloat16: _lib.DTYPE_BF16, torch.float16: _lib.DTYPE_F16, tor
 _BIAS_DTYPES = {torch.bfloat16: _lib.DTYPE_BF16, torch.float16: _lib.DTYPE_F16, torch.float32: _lib.DTYPE_F32}
 
 
-def workspace_bytes(num_experts: int, discrete: bool) -> int:
-    return int(_lib.load().b200moe_workspace_bytes(num_experts, 1 if discrete else 0))
+def workspace_bytes(num_experts: int, discrete: bool, dynamic_sched: bool = False) -> int:
+    """Bytes of workspace a launch needs: per-expert descriptors (discrete weights) plus the tile
+    counter of the dynamic scheduler."""
+    mode = (_lib.WORKSPACE_DISCRETE if discrete else 0) | (_lib.WORKSPACE_DYNAMIC_SCHED if dynamic_sched else 0)
+    return int(_lib.load().b200moe_workspace_bytes(num_experts, mode))
 
 
 def device_status(clear: bool = False) -> int:
@@ -214,18 +265,20 @@ def _fc1_swiglu_op(
     a: torch.Tensor, sfa: torch.Tensor, b: _T, sfb: _T, b_ptrs: _T, sfb_ptrs: _T, padded_offsets: torch.Tensor,
     alpha: torch.Tensor, prob: _T, norm_const: _T, c: _T, d: torch.Tensor, d_col: _T, amax: _T, sfd_row: _T,
     sfd_col: _T, workspace: _T, bias: _T, n: int, discrete_col_sfd: bool, sm_margin: int, tile_mode: str, act_func: str,
+    dynamic_sched: bool = False, b_nmajor: bool = False,
 ) -> None:  # fmt: skip
     launch_grouped_gemm(
         "fc1", a=a, sfa=sfa, b=b, sfb=sfb, b_ptrs=b_ptrs, sfb_ptrs=sfb_ptrs, padded_offsets=padded_offsets, alpha=alpha,
         prob=prob, norm_const=norm_const, c=c, d=d, d_col=d_col, amax=amax, sfd_row=sfd_row, sfd_col=sfd_col,
         workspace=workspace, m_rows=a.shape[0], n=n, k=a.shape[1], num_experts=padded_offsets.shape[0],
         discrete_col_sfd=discrete_col_sfd, sm_margin=sm_margin, tile_mode=tile_mode or None, bias=bias, act_func=act_func or "swiglu",
+        dynamic_sched=dynamic_sched, b_nmajor=b_nmajor,
     )  # fmt: skip
 
 
 @_fc1_swiglu_op.register_fake
 def _(a, sfa, b, sfb, b_ptrs, sfb_ptrs, padded_offsets, alpha, prob, norm_const, c, d, d_col, amax, sfd_row, sfd_col,
-      workspace, bias, n, discrete_col_sfd, sm_margin, tile_mode, act_func) -> None:  # fmt: skip
+      workspace, bias, n, discrete_col_sfd, sm_margin, tile_mode, act_func, dynamic_sched=False, b_nmajor=False) -> None:  # fmt: skip
     return None
 
 
@@ -236,20 +289,21 @@ def _fc2_quant_op(
     a: torch.Tensor, sfa: torch.Tensor, b: _T, sfb: _T, b_ptrs: _T, sfb_ptrs: _T, padded_offsets: torch.Tensor,
     alpha: torch.Tensor, prob: torch.Tensor, norm_const: _T, d: torch.Tensor, d_col: _T, amax: _T, sfd_row: _T,
     sfd_col: _T, workspace: _T, d_row_map: _T, d_peer_ptrs: _T, d_peer_slots: int, bias: _T, n: int, discrete_col_sfd: bool,
-    sm_margin: int, tile_mode: str,
+    sm_margin: int, tile_mode: str, dynamic_sched: bool = False, b_nmajor: bool = False,
 ) -> None:  # fmt: skip
     launch_grouped_gemm(
         "fc2", a=a, sfa=sfa, b=b, sfb=sfb, b_ptrs=b_ptrs, sfb_ptrs=sfb_ptrs, padded_offsets=padded_offsets, alpha=alpha,
         prob=prob, norm_const=norm_const, d=d, d_col=d_col, amax=amax, sfd_row=sfd_row, sfd_col=sfd_col,
         workspace=workspace, m_rows=a.shape[0], n=n, k=a.shape[1], num_experts=padded_offsets.shape[0],
         discrete_col_sfd=discrete_col_sfd, sm_margin=sm_margin, tile_mode=tile_mode or None, d_row_map=d_row_map,
-        d_peer_ptrs=d_peer_ptrs, d_peer_slots=d_peer_slots, bias=bias,
+        d_peer_ptrs=d_peer_ptrs, d_peer_slots=d_peer_slots, bias=bias, dynamic_sched=dynamic_sched, b_nmajor=b_nmajor,
     )  # fmt: skip
 
 
 @_fc2_quant_op.register_fake
 def _(a, sfa, b, sfb, b_ptrs, sfb_ptrs, padded_offsets, alpha, prob, norm_const, d, d_col, amax, sfd_row, sfd_col, workspace,
-      d_row_map, d_peer_ptrs, d_peer_slots, bias, n, discrete_col_sfd, sm_margin, tile_mode) -> None:  # fmt: skip
+      d_row_map, d_peer_ptrs, d_peer_slots, bias, n, discrete_col_sfd, sm_margin, tile_mode, dynamic_sched=False,
+      b_nmajor=False) -> None:  # fmt: skip
     return None
 
 
@@ -274,6 +328,9 @@ def grouped_gemm_op(kind: str, *, stream=None, **kw) -> None:
             workspace=kw.get("workspace"), discrete_col_sfd=bool(kw.get("discrete_col_sfd", False)), sm_margin=int(kw.get("sm_margin", 0)),
             tile_mode=kw.get("tile_mode") or None, d_row_map=kw.get("d_row_map"), d_peer_ptrs=kw.get("d_peer_ptrs"),
             d_peer_slots=int(kw.get("d_peer_slots", 0)), bias=kw.get("bias"), act_func=kw.get("act_func") or "swiglu", stream=stream,
+            dynamic_sched=bool(kw.get("dynamic_sched", False)), b_nmajor=bool(kw.get("b_nmajor", False)),
+            expert_range=kw.get("expert_range"), wait_limit_ms=int(kw.get("wait_limit_ms", 0)), light_m_tiles=kw.get("light_m_tiles"),
+            test_skip_b_loads=bool(kw.get("test_skip_b_loads", False)),
         )  # fmt: skip
         return
     ctx = torch.cuda.stream(stream) if isinstance(stream, torch.cuda.Stream) else None
@@ -281,15 +338,18 @@ def grouped_gemm_op(kind: str, *, stream=None, **kw) -> None:
         ctx = torch.cuda.stream(torch.cuda.ExternalStream(int(stream)))
     common = (kw["a"], kw["sfa"], kw.get("b"), kw.get("sfb"), kw.get("b_ptrs"), kw.get("sfb_ptrs"), kw["padded_offsets"],
               kw["alpha"], kw.get("prob"), kw.get("norm_const"))  # fmt: skip
+    if kw.get("expert_range") is not None or kw.get("test_skip_b_loads"):
+        raise NotImplementedError("expert_range and the test hook are eager-only launch options")
     tail = (kw["n"], bool(kw.get("discrete_col_sfd", False)), int(kw.get("sm_margin", 0)), kw.get("tile_mode") or "")
+    sched = (bool(kw.get("dynamic_sched", False)), bool(kw.get("b_nmajor", False)))
     outs = (kw["d"], kw.get("d_col"), kw.get("amax"), kw.get("sfd_row"), kw.get("sfd_col"), kw.get("workspace"))
 
     def call():
         if kind == "fc1":
-            torch.ops.b200moe.fc1_swiglu(*common, kw.get("c"), *outs, kw.get("bias"), *tail, kw.get("act_func") or "swiglu")
+            torch.ops.b200moe.fc1_swiglu(*common, kw.get("c"), *outs, kw.get("bias"), *tail, kw.get("act_func") or "swiglu", *sched)
         else:
             torch.ops.b200moe.fc2_quant(*common, *outs, kw.get("d_row_map"), kw.get("d_peer_ptrs"), int(kw.get("d_peer_slots", 0)),
-                                        kw.get("bias"), *tail)  # fmt: skip
+                                        kw.get("bias"), *tail, *sched)  # fmt: skip
 
     if ctx is None:
         call()

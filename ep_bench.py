@@ -39,8 +39,8 @@ def layer_flops(tokens_total: int) -> float:
 def single_gpu_layer(dev, steps: int = 5, warmup: int = 3, tokens: int = 65536) -> dict:
     """The same layer with all 256 experts on one GPU (no exchange): the like-for-like N = 1 point of
     the multi-GPU series."""
-    from . import synthetic
-    from .ep_layer import ExpertParallelMoE
+    from cudnn_frontend_b200 import synthetic
+    from cudnn_frontend_b200.ep_layer import ExpertParallelMoE
 
     w1, sfw1 = synthetic.make_weights(EXPERTS, 2 * INTER, HIDDEN, 100, dev)
     w2, sfw2 = synthetic.make_weights(EXPERTS, HIDDEN, INTER, 200, dev)
@@ -72,34 +72,9 @@ def _step_roofline(tflops_per_gpu: float, peaks):
             "peak_source": f"2 x bf16_tflops_sustained of {peaks['source']} MEASURED_PEAKS.json (dense fp8 proxy)"}  # fmt: skip
 
 
-def _trace_one_step(step, barrier, write: bool, path: str, min_us: float = 30.0) -> None:
-    """One step under the torch profiler (every rank runs it, one rank writes): start, duration and
-    name of every kernel of at least ``min_us`` microseconds."""
-    from torch.profiler import ProfilerActivity, profile
-
-    barrier()
-    torch.cuda.synchronize()
-    with profile(activities=[ProfilerActivity.CUDA]) as prof:
-        step()
-        torch.cuda.synchronize()
-    barrier()
-    if not write:
-        return
-    evs = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA), key=lambda e: e.time_range.start)
-    if not evs:
-        return
-    t0 = evs[0].time_range.start
-    with open(path, "w") as f:
-        for e in evs:
-            dur = e.time_range.end - e.time_range.start
-            if dur >= min_us:
-                f.write(f"{(e.time_range.start - t0) / 1e3:9.3f} ms +{dur / 1e3:8.3f} ms  {e.name[:90]}\n")
-        f.write(f"total {(max(e.time_range.end for e in evs) - t0) / 1e3:.3f} ms\n")
-
-
 def run(args, tokens_per_gpu: int = 65536):
-    from . import synthetic
-    from .ep_layer import ExpertParallelMoE
+    from cudnn_frontend_b200 import synthetic
+    from cudnn_frontend_b200.ep_layer import ExpertParallelMoE
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -258,11 +233,6 @@ def run(args, tokens_per_gpu: int = 65536):
             "cpu_baseline": None,
         }
         print(json.dumps(line))
-    # optional kernel timeline of one step on one rank: B200MOE_EP_TRACE=<rank>:<output file>
-    trace = os.environ.get("B200MOE_EP_TRACE")
-    if trace:
-        trace_rank, _, trace_file = trace.partition(":")
-        _trace_one_step(step, barrier, rank == int(trace_rank), trace_file or f"ep_trace_rank{rank}.txt")
     layer.release_peer_buffers()
     if world > 1:
         dist.destroy_process_group()

@@ -2,9 +2,11 @@
  * b200moe.h - C ABI of the B200-native MoE grouped-GEMM hot path.
  *
  * One shared library (libb200moe.so) built for sm_100a only.  Every entry point takes
- * plain device pointers, sizes and a CUDA stream (passed as void*), launches its kernels
- * asynchronously on that stream, never synchronises, never allocates device memory and
- * never throws.  Return value: 0 = launched, < 0 = argument error (B200MOE_E_*),
+ * plain device pointers, sizes and a CUDA stream (passed as void*) and never throws.  The
+ * compute entry points (GEMMs, quantiser, routing and row movers) launch their kernels
+ * asynchronously on that stream, never synchronise and never allocate device memory; the only
+ * calls that allocate, map or free device memory are b200moe_peer_alloc / _open / _close /
+ * _free, and b200moe_device_status synchronises the device.  Return value: 0 = launched, < 0 = argument error (B200MOE_E_*),
  * > 0 = CUDA runtime / driver error code.  b200moe_last_error() returns a thread-local
  * human-readable description of the last non-zero return.
  *
@@ -43,6 +45,27 @@ extern "C" {
 #define B200MOE_FLAG_DISCRETE_COL_SFD 1 /* per-expert column scale-factor blocks */
 #define B200MOE_FLAG_TILE_SINGLE 2      /* force 128 x 256 single-CTA tiles                    */
 #define B200MOE_FLAG_TILE_PAIR 4        /* force 256 x 256 CTA-pair tiles (cta_group::2)       */
+/* Tiles are handed out through an atomic counter instead of a fixed stride (the reference's
+   use_dynamic_sched, python/cudnn/grouped_gemm/moe_persistent_scheduler.py:838-893); needs 128
+   bytes of workspace (b200moe_workspace_bytes with B200MOE_WORKSPACE_DYNAMIC_SCHED).  Results are
+   bit-identical to the static schedule. */
+#define B200MOE_FLAG_DYNAMIC_SCHED 8
+/* B is N-major: memory [E][k][n] (dense) or one [k][n] allocation per expert (discrete), the
+   reference's b_major = "n" (python/cudnn/grouped_gemm/grouped_gemm_quant/api.py:288-294) */
+#define B200MOE_FLAG_B_NMAJOR 16
+/* The call covers a slice [e0, e0 + num_experts) of a longer expert list: padded_offsets, alpha,
+   amax, b / sfb (or b_ptrs / sfb_ptrs) and bias point at expert e0's entries, padded_offsets[-1] is
+   readable and is the first row of expert e0; a, sfa, prob, c, d, ... and m_rows describe the whole
+   row range.  Lets a layer run its experts in chunks on the same buffers. */
+#define B200MOE_FLAG_OFFSETS_HAVE_PREV 32
+/* Test hook: the producer of the B side issues no loads, so the kernel's bounded waits run out,
+   the kernel returns and b200moe_device_status reports which wait gave up.  Use with a small
+   wait_limit_ms.  The outputs of such a launch are undefined. */
+#define B200MOE_FLAG_TEST_SKIP_B_LOADS 64
+
+/* mode bits of b200moe_workspace_bytes */
+#define B200MOE_WORKSPACE_DISCRETE 1
+#define B200MOE_WORKSPACE_DYNAMIC_SCHED 2
 
 /*
  * Arguments of one grouped GEMM launch.  All pointers are device pointers.
@@ -61,7 +84,8 @@ extern "C" {
  *   d_col  [m_rows, n_out]  E4M3 quantised with the column scales (optional)
  *   amax   [E] f32, updated with atomic max (caller initialises, e.g. to -inf)
  *   sfd_row  128x4 layout of (m_rows, n_out/32); sfd_col  128x4 layout of (n_out, m_rows/32)
- *   workspace  only for discrete mode, b200moe_workspace_bytes(E, 1) bytes, 128-B aligned
+ *   workspace  discrete mode and / or dynamic scheduler: b200moe_workspace_bytes(E, mode) bytes,
+ *              128-B aligned
  */
 typedef struct b200moe_gemm_args {
   const void* a;
@@ -117,6 +141,13 @@ typedef struct b200moe_gemm_args {
      with E8M0 scales; the block maximum maps to 448 resp. 128 as in the reference's
      get_dtype_rcp_limits, grouped_gemm_swiglu_quant.py:2996-3012). */
   int32_t c_dtype;
+  /* limit of every wait inside the kernel in milliseconds (0 = the default, 4000): a wait that runs
+     out records a code in the device status word and the kernel returns */
+  int32_t wait_limit_ms;
+  /* tile schedule: experts with at most this many row tiles are treated as weight-streaming and
+     their tiles are interleaved with those of the larger experts (0 = the library's default,
+     -1 = no interleaving: experts in order) */
+  int32_t sched_light_m_tiles;
 } b200moe_gemm_args;
 
 /*
@@ -162,11 +193,13 @@ int b200moe_fc1_swiglu_discrete_noalloc(const b200moe_gemm_args* args, void* str
 int b200moe_fc2_quant(const b200moe_gemm_args* args, void* stream);
 
 /*
- * Bytes of caller-owned workspace a launch needs (0 in dense mode; two 128-byte tensor-map
- * slots per expert in discrete mode).  Mirrors the workspace the reference allocates in compile()
- * (python/cudnn/grouped_gemm/grouped_gemm_quant/grouped_gemm_quant.py:425-445).
+ * Bytes of caller-owned workspace a launch needs.  mode = B200MOE_WORKSPACE_DISCRETE (two 128-byte
+ * tensor-map slots per expert) | B200MOE_WORKSPACE_DYNAMIC_SCHED (128 bytes for the tile counter);
+ * 0 for a dense launch with the static schedule.  Mirrors the workspace the reference allocates in
+ * compile() (python/cudnn/grouped_gemm/grouped_gemm_quant/grouped_gemm_quant.py:425-445: descriptors
+ * plus a 4-byte counter).
  */
-int64_t b200moe_workspace_bytes(int32_t num_experts, int32_t discrete);
+int64_t b200moe_workspace_bytes(int32_t num_experts, int32_t mode);
 
 /*
  * Activation quantiser: x [rows, cols] bf16 (row pitch ld_elems) -> q [rows, cols] E4M3

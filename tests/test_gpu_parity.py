@@ -35,7 +35,12 @@ def _api():
 
 
 def _run(kind, seed, groups, n, k, *, d_fp8=False, discrete=False, m_aligned=128, extra_rows=0, norm=1.0,
-         use_prob=True, write_c=True, alpha=None, wrapper=False, discrete_col_sfd=False):  # fmt: skip
+         use_prob=True, write_c=True, alpha=None, wrapper=False, discrete_col_sfd=False, n_major=False, dynamic=False,
+         sm_margin=0, operands=None, expert_slices=None):  # fmt: skip
+    """One FC1 / FC2 call through the operator classes (or the wrappers) and its oracle result.
+    ``n_major``: weights stored [k][n]; ``dynamic``: atomic-counter tile scheduler; ``sm_margin``: SMs the
+    launch leaves free (a small grid gives every CTA many tiles); ``operands``: (a, b, sfa, sfb) bytes
+    instead of the seeded ones; ``expert_slices``: run the experts in these (lo, hi) slices, one launch each."""
     cf = _api()
     from cudnn_frontend_b200 import ops
 
@@ -43,7 +48,7 @@ def _run(kind, seed, groups, n, k, *, d_fp8=False, discrete=False, m_aligned=128
     e = len(groups)
     valid, aligned, offs = orc.padded_end_offsets(groups, m_aligned)
     m_rows = valid + extra_rows
-    a, b, sfa, sfb = H.gen_operands(seed, m_rows, n, k, e)
+    a, b, sfa, sfb = H.gen_operands(seed, m_rows, n, k, e) if operands is None else operands
     H.zero_padding_rows(a, groups, aligned)
     rng = np.random.default_rng(seed)
     if alpha is None:
@@ -62,15 +67,18 @@ def _run(kind, seed, groups, n, k, *, d_fp8=False, discrete=False, m_aligned=128
     tnorm = torch.tensor([norm], dtype=torch.float32, device=dev) if d_fp8 else None
     d_dtype = torch.float8_e4m3fn if d_fp8 else torch.bfloat16
     keep = []
+    b_major = "n" if n_major else "k"
     if discrete:
-        bl = [tb_store[i].clone() for i in range(e)]
+        bl = [(tb_store[i].t().contiguous() if n_major else tb_store[i].clone()) for i in range(e)]
         sl = [H.dev_sf(sfb[i], n, k) for i in range(e)]
         keep += bl + sl
         b_ptrs = torch.tensor([x.data_ptr() for x in bl], dtype=torch.int64, device=dev)
         sfb_ptrs = torch.tensor([x.data_ptr() for x in sl], dtype=torch.int64, device=dev)
     else:
-        tb = tb_store.permute(1, 2, 0)
+        # (n, k, e) view of [e][n][k] memory, or of [e][k][n] memory for N-major weights
+        tb = tb_store.transpose(1, 2).contiguous().permute(2, 1, 0) if n_major else tb_store.permute(1, 2, 0)
         tsfb = H.dev_sf(sfb, n, k, e)
+    assert not (n_major and kind == "fc1" and not discrete), "dense FC1 takes K-major weights only"
 
     if wrapper:
         if kind == "fc1" and not discrete:
@@ -79,14 +87,17 @@ def _run(kind, seed, groups, n, k, *, d_fp8=False, discrete=False, m_aligned=128
         elif kind == "fc1":
             res = cf.discrete_grouped_gemm_swiglu_wrapper_sm100(ta, b_ptrs, tsfa, sfb_ptrs, toffs, talpha, n, torch.float8_e4m3fn,
                                                                 norm_const_tensor=tnorm, prob_tensor=tprob, d_dtype=d_dtype,
-                                                                sf_vec_size=32, m_aligned=m_aligned)  # fmt: skip
+                                                                sf_vec_size=32, m_aligned=m_aligned, b_major=b_major,
+                                                                use_dynamic_sched=dynamic)  # fmt: skip
         elif not discrete:
             res = cf.grouped_gemm_quant_wrapper_sm100(ta, tsfa, toffs, talpha, b_tensor=tb, sfb_tensor=tsfb, norm_const_tensor=tnorm,
-                                                      prob_tensor=tprob, d_dtype=d_dtype, sf_vec_size=32, m_aligned=m_aligned)  # fmt: skip
+                                                      prob_tensor=tprob, d_dtype=d_dtype, sf_vec_size=32, m_aligned=m_aligned,
+                                                      use_dynamic_sched=dynamic)  # fmt: skip
         else:
             res = cf.grouped_gemm_quant_wrapper_sm100(ta, tsfa, toffs, talpha, b_ptrs=b_ptrs, sfb_ptrs=sfb_ptrs, n=n,
                                                       b_dtype=torch.float8_e4m3fn, norm_const_tensor=tnorm, prob_tensor=tprob,
-                                                      d_dtype=d_dtype, sf_vec_size=32, m_aligned=m_aligned)  # fmt: skip
+                                                      d_dtype=d_dtype, sf_vec_size=32, m_aligned=m_aligned, b_major=b_major,
+                                                      use_dynamic_sched=dynamic)  # fmt: skip
         out = dict(res)
         out.setdefault("c_tensor", None)
     else:
@@ -98,30 +109,45 @@ def _run(kind, seed, groups, n, k, *, d_fp8=False, discrete=False, m_aligned=128
         sfd_row = ops.empty_sf(m_rows, n_out, 1, zero=True) if d_fp8 else None
         sfd_col = ops.empty_sf(n_out, m_rows, 1, zero=True) if d_fp8 else None
         common = dict(acc_dtype=torch.float32, sf_vec_size=32, m_aligned=m_aligned, discrete_col_sfd=discrete_col_sfd)
+        slices = [None] if expert_slices is None else list(expert_slices)
         if kind == "fc1" and not discrete:
-            op = cf.GroupedGemmSwigluSm100(ta, tb, c, d, tsfa, tsfb, toffs, talpha, d_col, sample_sfd_row=sfd_row, sample_sfd_col=sfd_col,
-                                           sample_amax=amax, sample_norm_const=tnorm, sample_prob=tprob, **common)  # fmt: skip
+            if dynamic:  # the dense FC1 class of the reference has no dynamic scheduler; its unified GLU front has
+                op = cf.GroupedGemmGluSm100(ta, c, d, tsfa, toffs, talpha, d_col, sample_b=tb, sample_sfb=tsfb, sample_sfd_row=sfd_row,
+                                            sample_sfd_col=sfd_col, sample_amax=amax, sample_norm_const=tnorm, sample_prob=tprob,
+                                            use_dynamic_sched=True, **common)  # fmt: skip
+            else:
+                op = cf.GroupedGemmSwigluSm100(ta, tb, c, d, tsfa, tsfb, toffs, talpha, d_col, sample_sfd_row=sfd_row, sample_sfd_col=sfd_col,
+                                               sample_amax=amax, sample_norm_const=tnorm, sample_prob=tprob, **common)  # fmt: skip
             assert op.check_support()
             op.compile()
-            op.execute(ta, tb, c, d, tsfa, tsfb, toffs, talpha, d_col_tensor=d_col, sfd_row_tensor=sfd_row, sfd_col_tensor=sfd_col,
-                       amax_tensor=amax, norm_const_tensor=tnorm, prob_tensor=tprob)  # fmt: skip
+            inner = op._op if dynamic else op
+            inner.num_cluster_overlap_margin = sm_margin
+            for sl_ in slices:
+                inner.execute(ta, tb, c, d, tsfa, tsfb, toffs, talpha, d_col_tensor=d_col, sfd_row_tensor=sfd_row, sfd_col_tensor=sfd_col,
+                              amax_tensor=amax, norm_const_tensor=tnorm, prob_tensor=tprob, expert_range=sl_)  # fmt: skip
         elif kind == "fc1":
+            assert expert_slices is None
             op = cf.DiscreteGroupedGemmSwigluSm100(ta, e, (n, k), torch.float8_e4m3fn, c, d, tsfa, toffs, talpha, d_col,
                                                    sample_sfd_row=sfd_row, sample_sfd_col=sfd_col, sample_amax=amax,
-                                                   sample_norm_const=tnorm, sample_prob=tprob, **common)  # fmt: skip
+                                                   sample_norm_const=tnorm, sample_prob=tprob, b_major=b_major,
+                                                   use_dynamic_sched=dynamic, **common)  # fmt: skip
             assert op.check_support()
             op.compile()
+            op.num_cluster_overlap_margin = sm_margin
             op.execute(ta, b_ptrs, c, d, tsfa, sfb_ptrs, toffs, talpha, d_col_tensor=d_col, sfd_row_tensor=sfd_row,
                        sfd_col_tensor=sfd_col, amax_tensor=amax, norm_const_tensor=tnorm, prob_tensor=tprob)  # fmt: skip
         else:
             kw = dict(num_experts=e, b_shape=(n, k), b_dtype=torch.float8_e4m3fn) if discrete else dict(sample_b=tb, sample_sfb=tsfb)
             op = cf.GroupedGemmQuantSm100(ta, tsfa, toffs, talpha, d, sample_d_col=d_col, sample_sfd_row=sfd_row, sample_sfd_col=sfd_col,
-                                          sample_amax=amax, sample_norm_const=tnorm, sample_prob=tprob, **kw, **common)  # fmt: skip
+                                          sample_amax=amax, sample_norm_const=tnorm, sample_prob=tprob, b_major=b_major,
+                                          use_dynamic_sched=dynamic, **kw, **common)  # fmt: skip
             assert op.check_support()
             op.compile()
+            op.num_cluster_overlap_margin = sm_margin
             ekw = dict(b_ptrs=b_ptrs, sfb_ptrs=sfb_ptrs) if discrete else dict(b_tensor=tb, sfb_tensor=tsfb)
-            op.execute(ta, tsfa, toffs, talpha, d, d_col_tensor=d_col, sfd_row_tensor=sfd_row, sfd_col_tensor=sfd_col, amax_tensor=amax,
-                       norm_const_tensor=tnorm, prob_tensor=tprob, **ekw)  # fmt: skip
+            for sl_ in slices:
+                op.execute(ta, tsfa, toffs, talpha, d, d_col_tensor=d_col, sfd_row_tensor=sfd_row, sfd_col_tensor=sfd_col, amax_tensor=amax,
+                           norm_const_tensor=tnorm, prob_tensor=tprob, expert_range=sl_, **ekw)  # fmt: skip
         out = dict(c_tensor=c, d_tensor=d, d_col_tensor=d_col, amax_tensor=amax, sfd_row_tensor=sfd_row, sfd_col_tensor=sfd_col)
     torch.cuda.synchronize()
     assert ops.device_status(clear=True) == 0
@@ -291,6 +317,61 @@ def test_discrete_equals_dense_bitwise(tile_mode):
         assert torch.equal(o1[key], o2[key]), key
 
 
+def _same_outputs(o1, o2, keys=("c_tensor", "d_tensor", "d_col_tensor", "amax_tensor", "sfd_row_tensor", "sfd_col_tensor")):
+    for key in keys:
+        t1, t2 = o1.get(key), o2.get(key)
+        assert (t1 is None) == (t2 is None), key
+        if t1 is not None:
+            b1, b2 = t1.view(torch.uint8) if t1.element_size() == 1 else t1, t2.view(torch.uint8) if t2.element_size() == 1 else t2
+            if b1.dim() == 6:  # scale tensors are strided views: compare their storage
+                b1 = torch.as_strided(b1, (b1.numel(),), (1,))
+                b2 = torch.as_strided(b2, (b2.numel(),), (1,))
+            assert torch.equal(b1, b2), key
+
+
+@pytest.mark.parametrize("kind,discrete", [("fc2", False), ("fc2", True), ("fc1", True)])
+@pytest.mark.parametrize("d_fp8", [False, True])
+def test_n_major_weights_equal_k_major_bitwise(kind, discrete, d_fp8, tile_mode):
+    """The reference accepts FP8 weights stored N-major (b strides (1, n, n*k), or b_major="n" with
+    pointers: test/python/fe_api/test_grouped_gemm_quant.py:303-308).  The same numbers enter the same
+    MMAs in the same order, so the results must equal the K-major run exactly; the K-major run is
+    checked against the oracle."""
+    groups, n, k = [300, 0, 128, 513], 640, 416  # ragged N (two and a half 256-column tiles) and K (three and a quarter k-tiles)
+    o_k, ref, info = _run(kind, 61, groups, n, k, discrete=discrete, d_fp8=d_fp8)
+    _check(kind, o_k, ref, info, d_fp8=d_fp8)
+    o_n, _, _ = _run(kind, 61, groups, n, k, discrete=discrete, d_fp8=d_fp8, n_major=True)
+    _same_outputs(o_k, o_n)
+
+
+@pytest.mark.parametrize("kind,discrete", [("fc1", False), ("fc1", True), ("fc2", False), ("fc2", True)])
+def test_dynamic_scheduler_equals_static_bitwise(kind, discrete, tile_mode):
+    """use_dynamic_sched hands the same tiles to different CTAs: every output byte must equal the static
+    run's.  With 140 SMs left free the 8 remaining CTAs (4 pairs) take a dozen or more tiles each, so the
+    ring of tile ids between the fetching warp and the other warps wraps."""
+    groups, n, k = [700, 0, 130, 1200, 1, 128], 1024, 256
+    o_s, ref, info = _run(kind, 62, groups, n, k, discrete=discrete, d_fp8=True, sm_margin=140)
+    _check(kind, o_s, ref, info, d_fp8=True)
+    o_d, _, _ = _run(kind, 62, groups, n, k, discrete=discrete, d_fp8=True, sm_margin=140, dynamic=True)
+    _same_outputs(o_s, o_d)
+    o_d2, _, _ = _run(kind, 62, groups, n, k, discrete=discrete, sm_margin=0, dynamic=True)  # full grid, bf16 D + amax
+    o_s2, _, _ = _run(kind, 62, groups, n, k, discrete=discrete, sm_margin=0)
+    _same_outputs(o_s2, o_d2)
+
+
+@pytest.mark.parametrize("kind", ["fc1", "fc2"])
+def test_expert_slices_equal_one_launch_bitwise(kind, tile_mode):
+    """A layer may run its experts in chunks (expert_range): two or three launches over slices of the
+    expert list, on the same tensors, must leave exactly what one launch over all experts leaves."""
+    groups, n, k = [256, 130, 0, 384, 128, 1], 512, 256
+    whole, ref, info = _run(kind, 63, groups, n, k, d_fp8=True)
+    _check(kind, whole, ref, info, d_fp8=True, col=True)
+    parts, _, _ = _run(kind, 63, groups, n, k, d_fp8=True, expert_slices=[(0, 2), (2, 5), (5, 6)])
+    _same_outputs(whole, parts)
+    whole, _, _ = _run(kind, 63, groups, n, k)
+    parts, _, _ = _run(kind, 63, groups, n, k, expert_slices=[(3, 6), (0, 3)])
+    _same_outputs(whole, parts)
+
+
 def test_zero_alpha_gives_exact_zeros(tile_mode):
     """Known-answer case of the reference (test_grouped_gemm_quant.py:372-401)."""
     out, _, info = _run("fc2", 3, [64, 256, 320], 384, 160, alpha=np.zeros(3, dtype=np.float32), m_aligned=256)
@@ -411,6 +492,7 @@ def test_fc1_fc2_chain_matches_layer_oracle(tile_mode):
         ("reference_kernel_fc1.npz", torch.float8_e4m3fn, torch.float8_e4m3fn),
         ("reference_kernel_fc1_e5m2.npz", torch.float8_e5m2, torch.float8_e4m3fn),  # E5M2 operands
         ("reference_kernel_fc1_d_e5m2.npz", torch.float8_e4m3fn, torch.float8_e5m2),  # E5M2 D and D_col
+        ("reference_kernel_fc1_deepk.npz", torch.float8_e4m3fn, torch.float8_e4m3fn),  # K = 1024: eight k-tiles
     ],
 )
 def test_fc1_is_bit_identical_to_the_reference_kernel_fixture(golden_dir, tile_mode, fixture, ab_dtype, d_dtype):

@@ -30,9 +30,11 @@ def test_library_builds_loads_and_exports_every_declared_symbol():
     for name in declared:
         assert hasattr(lib, name), f"{name} declared in include/b200moe.h but not exported"
     assert set(declared) == set(_lib.EXPORTED_SYMBOLS)
-    assert _lib.load().b200moe_abi_version() == _lib.ABI_VERSION == 5
-    assert _lib.load().b200moe_workspace_bytes(256, 1) == 256 * 256
+    assert _lib.load().b200moe_abi_version() == _lib.ABI_VERSION == 6
+    assert _lib.load().b200moe_workspace_bytes(256, _lib.WORKSPACE_DISCRETE) == 256 * 256
     assert _lib.load().b200moe_workspace_bytes(256, 0) == 0
+    assert _lib.load().b200moe_workspace_bytes(256, _lib.WORKSPACE_DYNAMIC_SCHED) == 128
+    assert ops.workspace_bytes(8, True, True) == 8 * 256 + 128
 
 
 def test_c_abi_rejects_bad_arguments_without_touching_a_device():
@@ -245,9 +247,9 @@ def test_unified_glu_api_argument_rules():
     with pytest.raises(ValueError, match="act_func"):
         cf.GroupedGemmGluSm100(a, None, d, sfa, offs, alpha, None, sample_b=b, sample_sfb=sfb, sf_vec_size=32,
                                act_func="relu").check_support()  # fmt: skip
-    with pytest.raises(NotImplementedError, match="N-major"):
-        cf.GroupedGemmGluSm100(a, None, d, sfa, offs, alpha, None, sample_b=b, sample_sfb=sfb, sf_vec_size=32,
-                               b_major="n").check_support()  # fmt: skip
+    with pytest.raises(ValueError, match="b_major"):
+        cf.GroupedGemmGluSm100(a, None, d, sfa, offs, alpha, None, num_experts=e, b_shape=(n, k), b_dtype=torch.float8_e4m3fn,
+                               sf_vec_size=32, b_major="x").check_support()  # fmt: skip
     with pytest.raises(ValueError, match="not both"):
         cf.grouped_gemm_glu_wrapper_sm100(a, sfa, offs, alpha, b_tensor=b, sfb_tensor=sfb, b_ptrs=torch.zeros(2, dtype=torch.int64))
 

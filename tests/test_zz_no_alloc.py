@@ -4,7 +4,7 @@ Some users of the library cannot allocate device memory when they call it (an in
 that has already handed all free GPU memory to its own arena, a plugin that is given tensors but
 no allocator, a loop that must never reach cudaMalloc).  ``b200moe_fc1_swiglu_discrete_noalloc``
 serves them: it keeps the per-expert descriptor table in a fixed array inside the library instead
-of in a caller workspace.  This test calls it through the C ABI twice in a row, with different
+of in a caller workspace.  This test calls it through the C ABI several times in a row, with different
 experts and weights each time (the array keeps the previous call's contents), and requires
 bit-identical outputs to ``b200moe_fc1_swiglu`` given a caller workspace.
 """
@@ -48,8 +48,9 @@ def _problem(seed, groups, n, k):
             amax=torch.full((e,), float("-inf"), device=dev),
         )
 
-    def args(out, workspace):
+    def args(out, workspace, flags=0):
         g = _lib.GemmArgs()
+        g.flags = flags
         g.a, g.sfa = keep["a"].data_ptr(), keep["sfa"].data_ptr()
         g.b_ptrs, g.sfb_ptrs = keep["b_ptrs"].data_ptr(), keep["sfb_ptrs"].data_ptr()
         g.padded_offsets, g.alpha, g.prob = keep["offs"].data_ptr(), keep["alpha"].data_ptr(), keep["prob"].data_ptr()
@@ -69,12 +70,14 @@ def test_noalloc_entry_point_matches_workspace_entry_point_twice():
 
     lib = _lib.load()
     stream = torch.cuda.current_stream().cuda_stream
-    for seed, groups, n, k in ((71, [256, 0, 128], 512, 256), (72, [128, 128, 384, 1, 200], 256, 384)):
+    # the third call forces CTA-pair tiles: that mode also reads the scale-factor half of the descriptor table
+    cases = ((71, [256, 0, 128], 512, 256, 0), (72, [128, 128, 384, 1, 200], 256, 384, 0), (74, [256, 0, 512], 512, 256, _lib.FLAG_TILE_PAIR))
+    for seed, groups, n, k, flags in cases:
         keep, outputs, args, ws = _problem(seed, groups, n, k)
         ref, got = outputs(), outputs()
-        rc = lib.b200moe_fc1_swiglu(ctypes.byref(args(ref, ws)), stream)
+        rc = lib.b200moe_fc1_swiglu(ctypes.byref(args(ref, ws, flags)), stream)
         assert rc == 0, _lib.last_error()
-        rc = lib.b200moe_fc1_swiglu_discrete_noalloc(ctypes.byref(args(got, None)), stream)
+        rc = lib.b200moe_fc1_swiglu_discrete_noalloc(ctypes.byref(args(got, None, flags)), stream)
         assert rc == 0, _lib.last_error()
         torch.cuda.synchronize()
         assert lib.b200moe_device_status(1) == 0
