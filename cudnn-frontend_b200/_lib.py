@@ -63,6 +63,7 @@ class GemmArgs(Structure):
         ("c_dtype", c_int32),
         ("wait_limit_ms", c_int32),
         ("sched_light_m_tiles", c_int32),
+        ("l2_stream_m_tiles", c_int32),
     ]
 
 

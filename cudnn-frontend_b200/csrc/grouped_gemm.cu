@@ -59,6 +59,7 @@ constexpr int RASTER_GROUP_ROWS = 4096;        // rows of one expert that share 
 constexpr int64_t RASTER_GROUP_BYTES = 32 << 20;  // ... unless that many rows of A exceed this share of L2
 
 constexpr int DEFAULT_LIGHT_M_TILES = 2;
+constexpr int DEFAULT_STREAM_M_TILES = 2;
 
 constexpr int TMEM_COLS = 512;
 constexpr int TMEM_ACC1_COL = 224;
@@ -145,6 +146,7 @@ struct GemmParams {
   uint32_t ab_format;  // A / B format bits of the instruction descriptor (0 = E4M3, E5M2 = 1 in both fields)
   int raster_group_m;  // row tiles per raster group
   int light_m_tiles;   // experts with at most this many row tiles form the "light" class (0 = one class)
+  int stream_m_tiles;  // weight tiles of experts with at most this many row tiles are loaded with an evict-first L2 hint
   int first_has_prev;  // offsets[-1] is readable and is the first row of expert 0 (a slice of a longer expert list)
   int b_nmajor;        // B is [K][N] per expert (N contiguous) instead of [N][K]
   int dynamic_sched;   // tiles after each CTA's first come from an atomic counter
@@ -173,7 +175,7 @@ struct GemmParams {
 // A row tile is 128 rows (single) or 256 rows (pair).
 // ---------------------------------------------------------------------------------------
 struct Tile {
-  int expert, row0, n_tile, row_end;
+  int expert, row0, n_tile, row_end, m_tiles;
 };
 
 struct Sched {
@@ -215,6 +217,7 @@ __device__ __forceinline__ Tile decode_tile(const Sched& sc, const GemmParams& p
   const int jj = j - g * per_group;
   Tile tile;
   tile.expert = e;
+  tile.m_tiles = m_tiles;
   tile.n_tile = jj / gsize;
   tile.row0 = expert_first_row(p, e) + (first_m + jj % gsize) * tile_m;
   tile.row_end = p.offsets[e];
@@ -562,6 +565,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           sfbmap = p.b_maps + p.num_experts + tile.expert;
           tensormap_fence_acquire(sfbmap);
         }
+        // weights that only one or two row tiles will ever read pass through L2 with the lowest
+        // priority, so that they do not push out the activations and the weight tiles other CTAs share
+        const uint64_t b_policy = tile.m_tiles <= p.stream_m_tiles ? L2_EVICT_FIRST : L2_EVICT_NORMAL;
         // Everything that changes per k-tile is a running value: the K coordinate, the scale-chunk
         // pointers and the stage's shared-memory / barrier addresses.
         int kc = 0;
@@ -578,12 +584,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 tma_load_2d_pair(a_dst0 + stage * A_STAGE_BYTES, &tmap_a, fb, kc, my_row0);
                 tma_load_3d_pair(sfa_dst0 + stage * SFA_STAGE_BYTES, &tmap_sfa, fb, 0, kt, m_blk);
               } else if (kDiscrete) {
-                if (p.b_nmajor) tma_load_2d_pair(b_dst0 + stage * C::B_STAGE_BYTES, bmap, fb, b_row, kc);
-                else tma_load_2d_pair(b_dst0 + stage * C::B_STAGE_BYTES, bmap, fb, kc, b_row);
+                if (p.b_nmajor) tma_load_2d_pair_hint(b_dst0 + stage * C::B_STAGE_BYTES, bmap, fb, b_row, kc, b_policy);
+                else tma_load_2d_pair_hint(b_dst0 + stage * C::B_STAGE_BYTES, bmap, fb, kc, b_row, b_policy);
                 tma_load_3d_pair(sfb_dst0 + stage * SFB_STAGE_BYTES, sfbmap, fb, 0, kt, nblk0);
               } else {
-                if (p.b_nmajor) tma_load_3d_pair(b_dst0 + stage * C::B_STAGE_BYTES, bmap, fb, b_row, kc, tile.expert);
-                else tma_load_3d_pair(b_dst0 + stage * C::B_STAGE_BYTES, bmap, fb, kc, b_row, tile.expert);
+                if (p.b_nmajor) tma_load_3d_pair_hint(b_dst0 + stage * C::B_STAGE_BYTES, bmap, fb, b_row, kc, tile.expert, b_policy);
+                else tma_load_3d_pair_hint(b_dst0 + stage * C::B_STAGE_BYTES, bmap, fb, kc, b_row, tile.expert, b_policy);
                 tma_load_4d_pair(sfb_dst0 + stage * SFB_STAGE_BYTES, sfbmap, fb, 0, kt, nblk0, tile.expert);
               }
             }
@@ -619,18 +625,18 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 if (kDiscrete) {
                   if (p.b_nmajor) {
                     // two slabs of 128 columns x 128 K rows
-                    tma_load_2d(b_dst, bmap, fb, n0, kc);
-                    tma_load_2d(b_dst + 128 * BK, bmap, fb, n0 + 128, kc);
+                    tma_load_2d_hint(b_dst, bmap, fb, n0, kc, b_policy);
+                    tma_load_2d_hint(b_dst + 128 * BK, bmap, fb, n0 + 128, kc, b_policy);
                   } else {
-                    tma_load_2d(b_dst, bmap, fb, kc, n0);
+                    tma_load_2d_hint(b_dst, bmap, fb, kc, n0, b_policy);
                   }
                   tma_load_3d(sfb_dst0 + stage * SFB_STAGE_BYTES, sfbmap, fb, 0, kt, nblk0);
                 } else {
                   if (p.b_nmajor) {
-                    tma_load_3d(b_dst, bmap, fb, n0, kc, tile.expert);
-                    tma_load_3d(b_dst + 128 * BK, bmap, fb, n0 + 128, kc, tile.expert);
+                    tma_load_3d_hint(b_dst, bmap, fb, n0, kc, tile.expert, b_policy);
+                    tma_load_3d_hint(b_dst + 128 * BK, bmap, fb, n0 + 128, kc, tile.expert, b_policy);
                   } else {
-                    tma_load_3d(b_dst, bmap, fb, kc, n0, tile.expert);
+                    tma_load_3d_hint(b_dst, bmap, fb, kc, n0, tile.expert, b_policy);
                   }
                   bulk_load(sfb_dst0 + stage * SFB_STAGE_BYTES, sfb_src0, 512, fb);
                   if (two_chunks) bulk_load(sfb_dst0 + stage * SFB_STAGE_BYTES + 512, sfb_src1, 512, fb);
@@ -1307,6 +1313,7 @@ static int run_gemm(int epi, const b200moe_gemm_args* a, void* stream_v) {
   p.test_skip_b_loads = (a->flags & B200MOE_FLAG_TEST_SKIP_B_LOADS) ? 1 : 0;
   p.wait_limit_ns = a->wait_limit_ms > 0 ? (uint64_t)a->wait_limit_ms * 1000000ull : kWaitLimitNs;
   // experts of at most this many row tiles count as weight-streaming ("light") in the tile schedule
+  p.stream_m_tiles = a->l2_stream_m_tiles < 0 ? 0 : (a->l2_stream_m_tiles == 0 ? DEFAULT_STREAM_M_TILES : a->l2_stream_m_tiles);
   p.light_m_tiles = a->sched_light_m_tiles < 0 ? 0 : (a->sched_light_m_tiles == 0 ? DEFAULT_LIGHT_M_TILES : a->sched_light_m_tiles);
   {
     // 256-bit stores need 32-byte aligned bases and row pitches that keep a 32-column block aligned

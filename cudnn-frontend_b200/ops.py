@@ -126,6 +126,7 @@ def launch_grouped_gemm(
     wait_limit_ms: int = 0,
     light_m_tiles: Optional[int] = None,
     test_skip_b_loads: bool = False,
+    stream_m_tiles: Optional[int] = None,
 ) -> None:
     """Fill the C struct and call b200moe_fc1_swiglu / b200moe_fc2_quant.
 
@@ -139,7 +140,9 @@ def launch_grouped_gemm(
     only; all per-expert tensors are still the full ones, rows of the other experts are left alone
     (``lo > 0`` reads ``padded_offsets[lo - 1]`` as the slice's first row).  ``light_m_tiles``: experts with at
     most that many row tiles are interleaved with the larger ones in the tile schedule (``None`` = the
-    library's default or ``B200MOE_LIGHT_M_TILES``, ``-1`` = experts in order).  ``wait_limit_ms`` and
+    library's default or ``B200MOE_LIGHT_M_TILES``, ``-1`` = experts in order); ``stream_m_tiles``: weight tiles of
+    experts with at most that many row tiles are read with an evict-first L2 hint (``None`` = default or
+    ``B200MOE_STREAM_M_TILES``, ``-1`` = no hints).  ``wait_limit_ms`` and
     ``test_skip_b_loads`` drive the bounded-wait test hook."""
     _require_cuda(a, sfa, padded_offsets, alpha, d, b, sfb, b_ptrs, sfb_ptrs, prob, norm_const, c, d_col, amax, sfd_row, sfd_col)
     args = _lib.GemmArgs()
@@ -183,6 +186,9 @@ def launch_grouped_gemm(
     if light_m_tiles is None:
         light_m_tiles = int(os.environ.get("B200MOE_LIGHT_M_TILES", "0"))
     args.sched_light_m_tiles = int(light_m_tiles)
+    if stream_m_tiles is None:
+        stream_m_tiles = int(os.environ.get("B200MOE_STREAM_M_TILES", "0"))
+    args.l2_stream_m_tiles = int(stream_m_tiles)
     if d.dtype not in _D_DTYPES:
         raise NotImplementedError(f"D dtype {d.dtype} is not built (bf16, fp16, E4M3, E5M2 are)")
     args.d_dtype = _D_DTYPES[d.dtype]
@@ -330,7 +336,7 @@ def grouped_gemm_op(kind: str, *, stream=None, **kw) -> None:
             d_peer_slots=int(kw.get("d_peer_slots", 0)), bias=kw.get("bias"), act_func=kw.get("act_func") or "swiglu", stream=stream,
             dynamic_sched=bool(kw.get("dynamic_sched", False)), b_nmajor=bool(kw.get("b_nmajor", False)),
             expert_range=kw.get("expert_range"), wait_limit_ms=int(kw.get("wait_limit_ms", 0)), light_m_tiles=kw.get("light_m_tiles"),
-            test_skip_b_loads=bool(kw.get("test_skip_b_loads", False)),
+            test_skip_b_loads=bool(kw.get("test_skip_b_loads", False)), stream_m_tiles=kw.get("stream_m_tiles"),
         )  # fmt: skip
         return
     ctx = torch.cuda.stream(stream) if isinstance(stream, torch.cuda.Stream) else None

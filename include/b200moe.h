@@ -148,6 +148,10 @@ typedef struct b200moe_gemm_args {
      their tiles are interleaved with those of the larger experts (0 = the library's default,
      -1 = no interleaving: experts in order) */
   int32_t sched_light_m_tiles;
+  /* weight tiles of experts with at most this many row tiles are read with an evict-first L2 hint:
+     they are used once or twice and should not displace activations and shared weight tiles
+     (0 = the library's default, -1 = no hints) */
+  int32_t l2_stream_m_tiles;
 } b200moe_gemm_args;
 
 /*

@@ -145,7 +145,8 @@ def _check_quantised(d_q, sf, ref_d, ref_sf_flat, rows, cols, by_cols=False):
 
 @pytest.mark.parametrize(
     "fixture,ab_dtype,d_dtype",
-    [("reference_kernel_fc1.npz", "e4m3", "e4m3"), ("reference_kernel_fc1_e5m2.npz", "e5m2", "e4m3"), ("reference_kernel_fc1_d_e5m2.npz", "e4m3", "e5m2")],
+    [("reference_kernel_fc1.npz", "e4m3", "e4m3"), ("reference_kernel_fc1_e5m2.npz", "e5m2", "e4m3"), ("reference_kernel_fc1_d_e5m2.npz", "e4m3", "e5m2"),
+     ("reference_kernel_fc1_deepk.npz", "e4m3", "e4m3")],
 )
 def test_fc1_oracle_against_the_reference_kernel_fixture(golden_dir, fixture, ab_dtype, d_dtype):
     g = _load(golden_dir, fixture)
