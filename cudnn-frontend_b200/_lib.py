@@ -96,6 +96,12 @@ _SIGNATURES = {
         [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_int64, c_int32, c_int32, c_int32, c_int64,
          c_int64, c_void_p, c_void_p, c_void_p],
     ),  # fmt: skip
+    "b200moe_dispatch_quantize_peer_range": (
+        ctypes.c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_int64, c_int32, c_int32, c_int32, c_int64,
+         c_int64, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_void_p],
+    ),  # fmt: skip
+    "b200moe_copy_segments": (ctypes.c_int, [c_int32, POINTER(c_int64), POINTER(c_int64), POINTER(c_int64), c_void_p]),
     "b200moe_dispatch_record_pitch": (ctypes.c_int, [c_int64]),
     "b200moe_unpack_dispatch_records": (ctypes.c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p]),
     "b200moe_peer_alloc": (ctypes.c_int, [c_int64, POINTER(c_void_p), c_void_p]),

@@ -58,8 +58,10 @@ constexpr int MAX_EXPERTS = 1024;
 constexpr int RASTER_GROUP_ROWS = 4096;        // rows of one expert that share a B tile back to back ...
 constexpr int64_t RASTER_GROUP_BYTES = 32 << 20;  // ... unless that many rows of A exceed this share of L2
 
-constexpr int DEFAULT_LIGHT_M_TILES = 2;
-constexpr int DEFAULT_STREAM_M_TILES = 2;
+// Defaults of the two schedule options: off.  Measured on the DeepSeek-shape cases both move the
+// launch time by a few per cent in either direction depending on the GPU's power state.
+constexpr int DEFAULT_LIGHT_M_TILES = 0;
+constexpr int DEFAULT_STREAM_M_TILES = 0;
 
 constexpr int TMEM_COLS = 512;
 constexpr int TMEM_ACC1_COL = 224;
@@ -567,7 +569,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         }
         // weights that only one or two row tiles will ever read pass through L2 with the lowest
         // priority, so that they do not push out the activations and the weight tiles other CTAs share
-        const uint64_t b_policy = tile.m_tiles <= p.stream_m_tiles ? L2_EVICT_FIRST : L2_EVICT_NORMAL;
+        const bool b_stream = tile.m_tiles <= p.stream_m_tiles;
+        constexpr uint64_t b_policy = L2_EVICT_FIRST;
         // Everything that changes per k-tile is a running value: the K coordinate, the scale-chunk
         // pointers and the stage's shared-memory / barrier addresses.
         int kc = 0;
@@ -584,12 +587,14 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 tma_load_2d_pair(a_dst0 + stage * A_STAGE_BYTES, &tmap_a, fb, kc, my_row0);
                 tma_load_3d_pair(sfa_dst0 + stage * SFA_STAGE_BYTES, &tmap_sfa, fb, 0, kt, m_blk);
               } else if (kDiscrete) {
-                if (p.b_nmajor) tma_load_2d_pair_hint(b_dst0 + stage * C::B_STAGE_BYTES, bmap, fb, b_row, kc, b_policy);
-                else tma_load_2d_pair_hint(b_dst0 + stage * C::B_STAGE_BYTES, bmap, fb, kc, b_row, b_policy);
+                const int c0 = p.b_nmajor ? b_row : kc, c1 = p.b_nmajor ? kc : b_row;
+                if (b_stream) tma_load_2d_pair_hint(b_dst0 + stage * C::B_STAGE_BYTES, bmap, fb, c0, c1, b_policy);
+                else tma_load_2d_pair(b_dst0 + stage * C::B_STAGE_BYTES, bmap, fb, c0, c1);
                 tma_load_3d_pair(sfb_dst0 + stage * SFB_STAGE_BYTES, sfbmap, fb, 0, kt, nblk0);
               } else {
-                if (p.b_nmajor) tma_load_3d_pair_hint(b_dst0 + stage * C::B_STAGE_BYTES, bmap, fb, b_row, kc, tile.expert, b_policy);
-                else tma_load_3d_pair_hint(b_dst0 + stage * C::B_STAGE_BYTES, bmap, fb, kc, b_row, tile.expert, b_policy);
+                const int c0 = p.b_nmajor ? b_row : kc, c1 = p.b_nmajor ? kc : b_row;
+                if (b_stream) tma_load_3d_pair_hint(b_dst0 + stage * C::B_STAGE_BYTES, bmap, fb, c0, c1, tile.expert, b_policy);
+                else tma_load_3d_pair(b_dst0 + stage * C::B_STAGE_BYTES, bmap, fb, c0, c1, tile.expert);
                 tma_load_4d_pair(sfb_dst0 + stage * SFB_STAGE_BYTES, sfbmap, fb, 0, kt, nblk0, tile.expert);
               }
             }
@@ -622,21 +627,24 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
               const uint32_t fb = full_bar(stage);
               if (elect_one() && !skip_loads) {
                 const uint32_t b_dst = b_dst0 + stage * C::B_STAGE_BYTES;
+                // B tile: one box of 256 rows x 128 K bytes, or (N-major) two slabs of 128 columns x 128 K rows
+                const int c0 = p.b_nmajor ? n0 : kc, c1 = p.b_nmajor ? kc : n0;
                 if (kDiscrete) {
-                  if (p.b_nmajor) {
-                    // two slabs of 128 columns x 128 K rows
-                    tma_load_2d_hint(b_dst, bmap, fb, n0, kc, b_policy);
-                    tma_load_2d_hint(b_dst + 128 * BK, bmap, fb, n0 + 128, kc, b_policy);
+                  if (b_stream) {
+                    tma_load_2d_hint(b_dst, bmap, fb, c0, c1, b_policy);
+                    if (p.b_nmajor) tma_load_2d_hint(b_dst + 128 * BK, bmap, fb, n0 + 128, kc, b_policy);
                   } else {
-                    tma_load_2d_hint(b_dst, bmap, fb, kc, n0, b_policy);
+                    tma_load_2d(b_dst, bmap, fb, c0, c1);
+                    if (p.b_nmajor) tma_load_2d(b_dst + 128 * BK, bmap, fb, n0 + 128, kc);
                   }
                   tma_load_3d(sfb_dst0 + stage * SFB_STAGE_BYTES, sfbmap, fb, 0, kt, nblk0);
                 } else {
-                  if (p.b_nmajor) {
-                    tma_load_3d_hint(b_dst, bmap, fb, n0, kc, tile.expert, b_policy);
-                    tma_load_3d_hint(b_dst + 128 * BK, bmap, fb, n0 + 128, kc, tile.expert, b_policy);
+                  if (b_stream) {
+                    tma_load_3d_hint(b_dst, bmap, fb, c0, c1, tile.expert, b_policy);
+                    if (p.b_nmajor) tma_load_3d_hint(b_dst + 128 * BK, bmap, fb, n0 + 128, kc, tile.expert, b_policy);
                   } else {
-                    tma_load_3d_hint(b_dst, bmap, fb, kc, n0, tile.expert, b_policy);
+                    tma_load_3d(b_dst, bmap, fb, c0, c1, tile.expert);
+                    if (p.b_nmajor) tma_load_3d(b_dst + 128 * BK, bmap, fb, n0 + 128, kc, tile.expert);
                   }
                   bulk_load(sfb_dst0 + stage * SFB_STAGE_BYTES, sfb_src0, 512, fb);
                   if (two_chunks) bulk_load(sfb_dst0 + stage * SFB_STAGE_BYTES + 512, sfb_src1, 512, fb);

@@ -174,89 +174,102 @@ __global__ void __launch_bounds__(128)
 __global__ void __launch_bounds__(128)
     dispatch_quantize_peer_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ expert_ids,
                                   const int32_t* __restrict__ local_row, const int32_t* __restrict__ delta,
-                                  const float* __restrict__ topk_prob, int topk, int cols, int rec_pitch, int experts_per_rank,
-                                  int num_ranks, int my_rank, int64_t slot_capacity, int64_t row_capacity,
-                                  const int64_t* __restrict__ peer_q, const int64_t* __restrict__ peer_rec) {
+                                  const float* __restrict__ topk_prob, int64_t num_tokens, int topk, int cols, int rec_pitch,
+                                  int experts_per_rank, int num_ranks, int my_rank, int64_t slot_capacity, int64_t row_capacity,
+                                  int local_lo, int local_hi, const int64_t* __restrict__ peer_q,
+                                  const int64_t* __restrict__ peer_rec) {
   extern __shared__ __align__(16) uint8_t s_dyn[];  // [cols] E4M3 row, then topk records of rec_pitch bytes
   uint8_t* const s_qrow = s_dyn;
   uint8_t* const s_rec = s_dyn + cols;
-  const int64_t t = blockIdx.x;
   const int lane = threadIdx.x & 31;
-  const int sf_cols = cols / 32;
   __shared__ int64_t s_row[16];
   __shared__ int s_rank[16];
-  if (threadIdx.x < topk) {
-    const int64_t slot = t * topk + threadIdx.x;
-    const int e = expert_ids[slot];
-    int64_t row = -1;
-    int rank = 0;
-    if (e >= 0 && e < experts_per_rank * num_ranks) {
-      rank = e / experts_per_rank;
-      row = (int64_t)delta[e] + local_row[slot];
-      if (row < 0 || row >= row_capacity) {
-        atomicCAS(&g_device_status, 0, 301);  // never store outside a peer's buffer
-        row = -1;
+  __shared__ int s_any;
+  // a block walks tokens blockIdx.x, blockIdx.x + gridDim.x, ...: one token per block when the grid is
+  // the token count, a few persistent blocks when the kernel shares the GPU with a GEMM
+  for (int64_t t = blockIdx.x; t < num_tokens; t += gridDim.x) {
+    if (threadIdx.x == 0) s_any = 0;
+    __syncthreads();
+    if (threadIdx.x < topk) {
+      const int64_t slot = t * topk + threadIdx.x;
+      const int e = expert_ids[slot];
+      int64_t row = -1;
+      int rank = 0;
+      if (e >= 0 && e < experts_per_rank * num_ranks) {
+        rank = e / experts_per_rank;
+        const int local = e - rank * experts_per_rank;
+        // this launch moves the rows of local experts [local_lo, local_hi) of every rank only
+        if (local >= local_lo && local < local_hi) {
+          row = (int64_t)delta[e] + local_row[slot];
+          if (row < 0 || row >= row_capacity) {
+            atomicCAS(&g_device_status, 0, 301);  // never store outside a peer's buffer
+            row = -1;
+          }
+        }
+      }
+      s_row[threadIdx.x] = row;
+      s_rank[threadIdx.x] = rank;
+      if (row >= 0) s_any = 1;
+      uint8_t* rec = s_rec + threadIdx.x * rec_pitch;
+      *reinterpret_cast<float*>(rec + rec_pitch - 8) = topk_prob ? topk_prob[slot] : 1.0f;
+      *reinterpret_cast<int32_t*>(rec + rec_pitch - 4) = (int32_t)(my_rank * slot_capacity + slot);
+    }
+    __syncthreads();
+    if (!s_any) continue;  // no slot of this token belongs to this launch's experts (block-uniform)
+    // the row is read in batches of four 16-byte loads per thread, all issued before the first use
+    const int vecs = cols / 8;
+    const uint4* xrow = reinterpret_cast<const uint4*>(x + t * cols);
+    for (int v0 = threadIdx.x; v0 < vecs; v0 += 4 * blockDim.x) {
+      uint4 raw4[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int v = v0 + u * blockDim.x;
+        raw4[u] = v < vecs ? __ldg(xrow + v) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int v = v0 + u * blockDim.x;
+        // whole warps run in or out together: vecs is a multiple of 32 (host check), v - lane too
+        if (v - lane >= vecs) break;
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw4[u]);
+        float f[8];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 p2 = __bfloat1622float2(h[j]);
+          f[2 * j] = p2.x;
+          f[2 * j + 1] = p2.y;
+        }
+        float amax = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(f[j]));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        const uint32_t sfb = e8m0_from_float(amax * (1.0f / 448.0f));
+        const float scale = quant_scale(1.0f, e8m0_to_float(sfb));
+        uint2 o;
+        o.x = e4m3x4_from_float(f[0] * scale, f[1] * scale, f[2] * scale, f[3] * scale);
+        o.y = e4m3x4_from_float(f[4] * scale, f[5] * scale, f[6] * scale, f[7] * scale);
+        reinterpret_cast<uint2*>(s_qrow)[v] = o;
+        if ((lane & 3) == 0) {
+          for (int j = 0; j < topk; ++j) s_rec[j * rec_pitch + (v >> 2)] = (uint8_t)sfb;
+        }
       }
     }
-    s_row[threadIdx.x] = row;
-    s_rank[threadIdx.x] = rank;
-    uint8_t* rec = s_rec + threadIdx.x * rec_pitch;
-    *reinterpret_cast<float*>(rec + rec_pitch - 8) = topk_prob ? topk_prob[slot] : 1.0f;
-    *reinterpret_cast<int32_t*>(rec + rec_pitch - 4) = (int32_t)(my_rank * slot_capacity + slot);
-  }
-  // the row is read in batches of four 16-byte loads per thread, all issued before the first use
-  const int vecs = cols / 8;
-  const uint4* xrow = reinterpret_cast<const uint4*>(x + t * cols);
-  for (int v0 = threadIdx.x; v0 < vecs; v0 += 4 * blockDim.x) {
-    uint4 raw4[4];
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int v = v0 + u * blockDim.x;
-      raw4[u] = v < vecs ? __ldg(xrow + v) : make_uint4(0, 0, 0, 0);
-    }
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int v = v0 + u * blockDim.x;
-      // whole warps run in or out together: vecs is a multiple of 32 (host check), v - lane too
-      if (v - lane >= vecs) break;
-      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw4[u]);
-      float f[8];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 p2 = __bfloat1622float2(h[j]);
-        f[2 * j] = p2.x;
-        f[2 * j + 1] = p2.y;
+    fence_proxy_async_smem();  // this thread's writes, for the bulk copies below
+    __syncthreads();
+    if (threadIdx.x < topk) {
+      const int64_t row = s_row[threadIdx.x];
+      if (row >= 0) {
+        const int rank = s_rank[threadIdx.x];
+        bulk_store(reinterpret_cast<uint8_t*>(peer_q[rank]) + row * cols, smem_u32(s_qrow), (uint32_t)cols);
+        bulk_store(reinterpret_cast<uint8_t*>(peer_rec[rank]) + row * rec_pitch, smem_u32(s_rec + threadIdx.x * rec_pitch),
+                   (uint32_t)rec_pitch);
       }
-      float amax = 0.f;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(f[j]));
-      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-      const uint32_t sfb = e8m0_from_float(amax * (1.0f / 448.0f));
-      const float scale = quant_scale(1.0f, e8m0_to_float(sfb));
-      uint2 o;
-      o.x = e4m3x4_from_float(f[0] * scale, f[1] * scale, f[2] * scale, f[3] * scale);
-      o.y = e4m3x4_from_float(f[4] * scale, f[5] * scale, f[6] * scale, f[7] * scale);
-      reinterpret_cast<uint2*>(s_qrow)[v] = o;
-      if ((lane & 3) == 0) {
-        for (int j = 0; j < topk; ++j) s_rec[j * rec_pitch + (v >> 2)] = (uint8_t)sfb;
-      }
+      bulk_commit();
+      bulk_wait_read0();  // shared memory must outlive the copies' reads
     }
+    __syncthreads();  // the next token reuses the row and the records
   }
-  fence_proxy_async_smem();  // this thread's writes, for the bulk copies below
-  __syncthreads();
-  if (threadIdx.x < topk) {
-    const int64_t row = s_row[threadIdx.x];
-    if (row >= 0) {
-      const int rank = s_rank[threadIdx.x];
-      bulk_store(reinterpret_cast<uint8_t*>(peer_q[rank]) + row * cols, smem_u32(s_qrow), (uint32_t)cols);
-      bulk_store(reinterpret_cast<uint8_t*>(peer_rec[rank]) + row * rec_pitch, smem_u32(s_rec + threadIdx.x * rec_pitch),
-                 (uint32_t)rec_pitch);
-    }
-    bulk_commit();
-    bulk_wait_read0();  // shared memory must outlive the copies' reads
-  }
-  (void)sf_cols;
 }
 
 // Receive side of the peer dispatch, after the ranks' barrier: records -> scales in the swizzled
@@ -419,10 +432,11 @@ int b200moe_dispatch_quantize(const void* x, const int32_t* send_pos, const floa
 
 int b200moe_dispatch_record_pitch(int64_t cols) { return (int)(((cols / 32 + 8) + 15) / 16 * 16); }
 
-int b200moe_dispatch_quantize_peer(const void* x, const int32_t* expert_ids, const int32_t* local_row, const int32_t* delta,
-                                   const float* topk_prob, int64_t num_tokens, int32_t topk, int64_t cols,
-                                   int32_t experts_per_rank, int32_t num_ranks, int32_t my_rank, int64_t slot_capacity,
-                                   int64_t row_capacity, const int64_t* peer_q, const int64_t* peer_rec, void* stream) {
+int b200moe_dispatch_quantize_peer_range(const void* x, const int32_t* expert_ids, const int32_t* local_row, const int32_t* delta,
+                                         const float* topk_prob, int64_t num_tokens, int32_t topk, int64_t cols,
+                                         int32_t experts_per_rank, int32_t num_ranks, int32_t my_rank, int64_t slot_capacity,
+                                         int64_t row_capacity, const int64_t* peer_q, const int64_t* peer_rec,
+                                         int32_t local_expert_lo, int32_t local_expert_hi, int32_t max_blocks, void* stream) {
   using namespace b200moe;
   if (num_tokens == 0) return B200MOE_OK;
   if (!x || !expert_ids || !local_row || !delta || !peer_q || !peer_rec)
@@ -433,14 +447,41 @@ int b200moe_dispatch_quantize_peer(const void* x, const int32_t* expert_ids, con
   if (experts_per_rank <= 0 || num_ranks <= 0 || my_rank < 0 || my_rank >= num_ranks || slot_capacity < num_tokens * topk ||
       (int64_t)num_ranks * slot_capacity > 0x7fffffffll || row_capacity <= 0)
     return fail(B200MOE_E_SHAPE, "dispatch_quantize_peer: bad rank layout or capacities");
+  if (local_expert_lo < 0 || local_expert_hi > experts_per_rank || local_expert_lo >= local_expert_hi || max_blocks < 0)
+    return fail(B200MOE_E_SHAPE, "dispatch_quantize_peer: bad local expert range [%d, %d) or block limit", local_expert_lo, local_expert_hi);
   if ((uintptr_t)x & 15) return fail(B200MOE_E_ALIGN, "dispatch_quantize_peer: 16-byte alignment required");
   const int rec_pitch = b200moe_dispatch_record_pitch(cols);
   const size_t smem = (size_t)cols + (size_t)topk * rec_pitch;
   if (smem > 48 * 1024) return fail(B200MOE_E_SHAPE, "dispatch_quantize_peer: a row and its records must fit 48 KiB of shared memory");
-  dispatch_quantize_peer_kernel<<<(unsigned)num_tokens, 128, smem, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)x, expert_ids, local_row, delta, topk_prob, topk, (int)cols, rec_pitch, experts_per_rank, num_ranks,
-      my_rank, slot_capacity, row_capacity, peer_q, peer_rec);
+  const int64_t blocks = max_blocks > 0 ? std::min<int64_t>(max_blocks, num_tokens) : num_tokens;
+  dispatch_quantize_peer_kernel<<<(unsigned)blocks, 128, smem, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)x, expert_ids, local_row, delta, topk_prob, num_tokens, topk, (int)cols, rec_pitch, experts_per_rank,
+      num_ranks, my_rank, slot_capacity, row_capacity, local_expert_lo, local_expert_hi, peer_q, peer_rec);
   B200_CUDA_CHECK(cudaGetLastError());
+  return B200MOE_OK;
+}
+
+int b200moe_dispatch_quantize_peer(const void* x, const int32_t* expert_ids, const int32_t* local_row, const int32_t* delta,
+                                   const float* topk_prob, int64_t num_tokens, int32_t topk, int64_t cols,
+                                   int32_t experts_per_rank, int32_t num_ranks, int32_t my_rank, int64_t slot_capacity,
+                                   int64_t row_capacity, const int64_t* peer_q, const int64_t* peer_rec, void* stream) {
+  return b200moe_dispatch_quantize_peer_range(x, expert_ids, local_row, delta, topk_prob, num_tokens, topk, cols, experts_per_rank,
+                                              num_ranks, my_rank, slot_capacity, row_capacity, peer_q, peer_rec, 0, experts_per_rank,
+                                              0, stream);
+}
+
+int b200moe_copy_segments(int32_t count, const int64_t* dst, const int64_t* src, const int64_t* bytes, void* stream) {
+  using namespace b200moe;
+  if (count < 0 || (count > 0 && (!dst || !src || !bytes))) return fail(B200MOE_E_NULL, "copy_segments: null table");
+  for (int i = 0; i < count; ++i) {
+    if (bytes[i] < 0 || (bytes[i] > 0 && (!dst[i] || !src[i]))) return fail(B200MOE_E_NULL, "copy_segments: segment %d is null or negative", i);
+  }
+  // one asynchronous device-to-device copy per segment (copy engines: no SM takes part)
+  for (int i = 0; i < count; ++i) {
+    if (bytes[i] == 0) continue;
+    B200_CUDA_CHECK(cudaMemcpyAsync(reinterpret_cast<void*>(dst[i]), reinterpret_cast<const void*>(src[i]), (size_t)bytes[i],
+                                    cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+  }
   return B200MOE_OK;
 }
 

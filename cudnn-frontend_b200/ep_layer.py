@@ -131,6 +131,35 @@ def plan_fused(counts_all: torch.Tensor, rank: int, m_aligned: int = 128) -> Fus
     return FusedPlan(delta.to(torch.int32), ends[rank].to(torch.int32), ends[:, -1].contiguous(), total.view(g, e_local).sum(1))
 
 
+def return_segments(counts_host, padded_ends, rank: int, lo: int, hi: int):
+    """Row blocks that rank ``rank`` returns for its local experts ``lo .. hi - 1``.
+
+    ``counts_host [G, E]`` (host integers): rows source rank s routes to physical expert e;
+    ``padded_ends [E_local]``: END offsets of this rank's expert groups.  The group of local expert j holds
+    the rows of source 0 first, then source 1, ...; source s keeps its result rows sorted by expert, expert
+    e starting at the exclusive prefix of its own histogram.  Returns a list of
+    ``(source rank, first row in the source's result buffer, first row here, rows)``, the sources rotated
+    to start behind this rank so that the ranks do not all send to the same destination at once."""
+    import numpy as np
+
+    cnt = np.asarray(counts_host, dtype=np.int64)
+    g, e = cnt.shape
+    el = e // g
+    ends = np.asarray(padded_ends, dtype=np.int64)
+    starts = np.concatenate([[0], ends[:-1]])
+    before = np.cumsum(cnt, axis=0) - cnt
+    compact = np.cumsum(cnt, axis=1) - cnt
+    out = []
+    for i in range(g):
+        s_ = (rank + 1 + i) % g
+        for j in range(lo, hi):
+            e_glob = rank * el + j
+            rows = int(cnt[s_, e_glob])
+            if rows:
+                out.append((s_, int(compact[s_, e_glob]), int(starts[j]) + int(before[s_, e_glob]), rows))
+    return out
+
+
 def balanced_placement(rows_per_expert, num_ranks: int):
     """Placement of E experts on G ranks, E / G per rank, that evens out the rows per rank: experts in
     order of decreasing load, each onto the least-loaded rank that still has a free slot (ties: lower
@@ -208,6 +237,12 @@ class ExpertParallelMoE:
         self.last_rows_received = 0
         # SMs the GEMMs leave to the all-to-all kernels that run beside them in the pipelined path
         self.overlap_sm_margin = overlap_sm_margin if self.world > 1 else 0
+        # chunked peer path: SMs the GEMMs leave to the quantise-and-dispatch launch (and the barrier
+        # kernels) that run beside them, and the persistent blocks of that launch
+        import os
+
+        self.chunk_sm_margin = int(os.environ.get("B200MOE_EP_SM_MARGIN", "8")) if self.world > 1 else 0
+        self.dispatch_blocks = int(os.environ.get("B200MOE_EP_DISPATCH_BLOCKS", "256"))
 
     def _fc_ops(self, m_rows: int, bufs, sm_margin: int = 0):
         """Operator objects are cached per padded row count (shapes are part of their samples)."""
@@ -326,15 +361,18 @@ class ExpertParallelMoE:
         epilogue stores into."""
         from .peer_memory import PeerBuffer
 
-        key = (tokens, topk, capacity_factor)
-        if getattr(self, "_peer_key", None) == key:
-            return self._peer
-        if getattr(self, "_peer", None) is not None:
-            self.release_peer_buffers()
+        # One set of buffers per (tokens, topk).  A step that needed more rows than the caller's factor
+        # gives has grown them; later calls with the smaller factor keep the grown buffers instead of
+        # shrinking and growing again on every step.
+        key = (tokens, topk)
         slots = tokens * topk
         # rows this rank may receive: its fair share times the factor, plus the padding of every group
         cap = int(slots * capacity_factor) + self.e_local * self.m_aligned
         cap = ((cap + 127) // 128) * 128
+        if getattr(self, "_peer_key", None) == key and self._peer["cap"] >= cap:
+            return self._peer
+        if getattr(self, "_peer", None) is not None:
+            self.release_peer_buffers()
         h = self.hidden
         rest_k = (h // 32 + 3) // 4
         from . import moe
@@ -360,11 +398,18 @@ class ExpertParallelMoE:
         peer = getattr(self, "_peer", None)
         if peer is None:
             return
+        # Three phases, the ranks in step: (1) nobody still computes on or stores into a buffer; (2) every
+        # rank unmaps its views of the others' buffers; (3) only then does an owner free its allocation
+        # (freeing memory that another process still has mapped is undefined).
         torch.cuda.synchronize()
         if self.world > 1:
             dist.barrier(group=self.group)
         for b in peer["bufs"].values():
-            b.close()
+            b.unmap_peers()
+        if self.world > 1:
+            dist.barrier(group=self.group)
+        for b in peer["bufs"].values():
+            b.free_own()
         self._peer, self._peer_key = None, None
 
     def _rank_barrier(self):
@@ -374,7 +419,21 @@ class ExpertParallelMoE:
         if self.world > 1:
             dist.all_reduce(self._token, group=self.group)
 
-    def forward_fused(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_prob: torch.Tensor, capacity_factor: float = 2.0) -> torch.Tensor:
+    def forward_fused(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_prob: torch.Tensor, capacity_factor: float = 2.0,
+                      chunks: Optional[int] = None) -> torch.Tensor:
+        """The peer-memory path.  On one rank: :meth:`forward_fused_direct`.  On several ranks:
+        :meth:`forward_fused_chunked`, which overlaps the NVLink traffic with the GEMMs (``chunks``
+        expert chunks, default 4 or the environment variable ``B200MOE_EP_CHUNKS``; ``chunks=0`` selects
+        the direct form on any number of ranks)."""
+        import os
+
+        if chunks is None:
+            chunks = int(os.environ.get("B200MOE_EP_CHUNKS", "4")) if self.world > 1 else 0
+        if chunks <= 0:
+            return self.forward_fused_direct(x, topk_ids, topk_prob, capacity_factor)
+        return self.forward_fused_chunked(x, topk_ids, topk_prob, capacity_factor, chunks)
+
+    def forward_fused_direct(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_prob: torch.Tensor, capacity_factor: float = 2.0) -> torch.Tensor:
         """Same result as :meth:`forward`, without any all-to-all of rows: the dispatch kernel stores
         quantised rows straight into the owning rank's GEMM operand over NVLink, and the FC2 epilogue
         stores result rows straight into the source rank's result buffer.
@@ -442,6 +501,145 @@ class ExpertParallelMoE:
                         d_peer_ptrs=bufs["back"].ptrs_dev, d_peer_slots=slots)  # fmt: skip
         self._rank_barrier()
         return moe.combine_rows(bufs["back"].view(torch.bfloat16, (slots, h)), peer["identity"], t, k)
+
+    # ------------------------------------------------------------------------------------------
+    # peer-memory path in expert chunks: transfers run beside the GEMMs
+    # ------------------------------------------------------------------------------------------
+    def _side_streams(self):
+        if getattr(self, "_streams", None) is None:
+            self._streams = dict(disp=torch.cuda.Stream(), copy=[torch.cuda.Stream(), torch.cuda.Stream()])
+        return self._streams
+
+    def forward_fused_chunked(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_prob: torch.Tensor, capacity_factor: float = 2.0,
+                              chunks: int = 4) -> torch.Tensor:
+        """Same result as :meth:`forward_fused_direct`, with the local experts run in ``chunks`` slices so
+        that the traffic over NVLink hides behind the GEMMs:
+
+            plan (as forward_fused_direct: histogram all-gather, one host synchronisation)
+            dispatch of chunk 0 (all SMs) -> barrier
+            for every chunk c:   FC1(c), FC2(c) on the compute stream (FC2 stores bf16 rows locally, in
+                                 expert-grouped order: full-speed stores, no row map)
+                                 | quantise + dispatch of chunk c + 1 on a side stream, on the few SMs the
+                                 |   GEMMs leave free (``chunk_sm_margin``), then a barrier
+                                 | return of chunk c - 1 by the copy engines: every (expert, source rank)
+                                 |   block of result rows is one contiguous device-to-device copy into the
+                                 |   source rank's result buffer, which holds its rows in its own
+                                 |   expert-sorted order
+            barrier -> top-k sum (each token gathers its k rows through its sorted positions)
+
+        Only the dispatch of the first chunk and the return of the last one are exposed.  All tables of
+        the copies come from the all-gathered histogram, which the host reads in the plan's one
+        synchronisation."""
+        import numpy as np
+
+        from . import moe, ops
+
+        if not x.is_cuda:
+            raise RuntimeError("ExpertParallelMoE.forward_fused_chunked needs CUDA tensors")
+        t, k = topk_ids.shape
+        h, dev, g, el = self.hidden, x.device, self.world, self.e_local
+        rank = 0 if self.group is None else dist.get_rank(self.group)
+        if not hasattr(self, "_token"):
+            self._token = torch.zeros(1, dtype=torch.float32, device=dev)
+        peer = self._peer_setup(t, k, capacity_factor)
+        bufs, cap, slots = peer["bufs"], peer["cap"], peer["slots"]
+        main = torch.cuda.current_stream()
+        streams = self._side_streams()
+
+        ids = self._physical_ids(topk_ids).contiguous()
+        counts, _, local_row = moe.route(ids.view(-1), self.num_experts, 1)
+        bufs["rec"].local.fill_(0xFF)  # a record nobody writes reads as "padding row"
+        if g > 1:
+            counts_all = torch.empty((g, self.num_experts), dtype=torch.int32, device=dev)
+            dist.all_gather_into_tensor(counts_all, counts, group=self.group)
+        else:
+            counts_all = counts.view(1, -1)
+        plan = plan_fused(counts_all, rank, self.m_aligned)
+        host = torch.cat([plan.m_rows_all, plan.rows_all, plan.padded_offsets.to(torch.int64), counts_all.reshape(-1).to(torch.int64)]).cpu().numpy()
+        m_all = host[:g]
+        m = int(m_all[rank])
+        self.last_rows_received = int(host[g + rank])
+        ends = host[2 * g : 2 * g + el]  # padded END offsets of my expert groups
+        cnt = host[2 * g + el :].reshape(g, self.num_experts)  # rows source s routes to (physical) expert e
+        if int(m_all.max()) > cap:
+            if int(m_all.max()) > 64 * slots:
+                raise RuntimeError(f"a rank would receive {int(m_all.max())} padded rows from {slots} slots per rank")
+            peer = self._peer_setup(t, k, 1.25 * float(m_all.max()) / slots)
+            bufs, cap = peer["bufs"], peer["cap"]
+            bufs["rec"].local.fill_(0xFF)
+            self._rank_barrier()
+        ev_plan = torch.cuda.Event()
+        ev_plan.record(main)
+
+        chunks = max(1, min(int(chunks), el))
+        bounds = [(c * el // chunks, (c + 1) * el // chunks) for c in range(chunks)]
+        flat_prob = topk_prob.reshape(t * k).contiguous()
+
+        def dispatch(c, max_blocks):
+            moe.dispatch_quantize_peer(x, ids, local_row, plan.delta, flat_prob, el, g, rank, slots, cap, bufs["q"].ptrs_dev,
+                                       bufs["rec"].ptrs_dev, local_experts=bounds[c], max_blocks=max_blocks)  # fmt: skip
+
+        starts = np.concatenate([[0], ends[:-1]])  # first row of my expert groups
+        row_bytes = h * 2
+        back_ptrs = bufs["back"].ptrs
+
+        loc = peer["local"]
+        rest_k = (h // 32 + 3) // 4
+        pitch = peer["pitch"]
+        y = h8 = sfh = None
+        if m > 0:
+            a = torch.as_strided(bufs["q"].view(torch.float8_e4m3fn, (m, h)), (m, h, 1), (h, 1, m * h))
+            shape, stride = ops.sf_shape_stride(m, h, 1)
+            sfa = torch.as_strided(loc["sf"].view(torch.float8_e8m0fnu), shape, stride)
+            prob3 = loc["prob"][:m].view(m, 1, 1)
+            h8 = torch.empty((m, self.inter, 1), dtype=torch.float8_e4m3fn, device=dev)
+            sfh = ops.empty_sf(m, self.inter, 1, device=dev)
+            y = torch.empty((m, h, 1), dtype=torch.bfloat16, device=dev)
+            fc1, fc2 = self._fc_ops(m, (a, sfa, h8, sfh, None, prob3, plan.padded_offsets), self.chunk_sm_margin)
+
+        dispatch(0, 0)
+        self._rank_barrier()
+        ev_disp = [None] * chunks
+        ev_fc2 = [None] * chunks
+        for c, (lo, hi) in enumerate(bounds):
+            if c > 0:
+                main.wait_event(ev_disp[c])
+            r0, r1 = int(starts[lo]), int(ends[hi - 1])
+            if r1 > r0:
+                moe.unpack_dispatch_records(bufs["rec"].local[r0 * pitch :], r1 - r0, h, loc["sf"][(r0 // 128) * rest_k * 512 :], loc["prob"][r0:],
+                                            loc["map"][r0:])  # fmt: skip
+                fc1.execute(a, self.w1, None, h8, sfa, self.sfw1, plan.padded_offsets, self.alpha, sfd_row_tensor=sfh, norm_const_tensor=self.norm,
+                            expert_range=(lo, hi))  # fmt: skip
+            if c + 1 < chunks:
+                # the next chunk's rows travel while this chunk computes
+                with torch.cuda.stream(streams["disp"]):
+                    if c == 0:
+                        streams["disp"].wait_event(ev_plan)
+                    dispatch(c + 1, self.dispatch_blocks)
+                    self._rank_barrier()
+                    ev_disp[c + 1] = torch.cuda.Event()
+                    ev_disp[c + 1].record(streams["disp"])
+            if r1 > r0:
+                fc2.execute(h8, sfh, plan.padded_offsets, self.alpha, y, b_tensor=self.w2, sfb_tensor=self.sfw2, prob_tensor=prob3,
+                            expert_range=(lo, hi))  # fmt: skip
+            ev_fc2[c] = torch.cuda.Event()
+            ev_fc2[c].record(main)
+            # return of this chunk's result rows: one copy per (expert, source rank), destinations rotated
+            # so that the ranks do not all send to the same one at the same time
+            if y is not None:
+                y_ptr = y.data_ptr()
+                seg = [[], []]
+                for s_, dst_row, src_row, n_rows in return_segments(cnt, ends, rank, lo, hi):
+                    seg[s_ % 2].append((back_ptrs[s_] + dst_row * row_bytes, y_ptr + src_row * row_bytes, n_rows * row_bytes))
+                for cs, lane_ in zip(streams["copy"], seg):
+                    if lane_:
+                        cs.wait_event(ev_fc2[c])
+                        moe.copy_segments([v[0] for v in lane_], [v[1] for v in lane_], [v[2] for v in lane_], stream=cs)
+        for cs in streams["copy"]:
+            main.wait_stream(cs)
+        main.wait_stream(streams["disp"])
+        self._rank_barrier()  # every rank's copies into my result buffer are complete
+        return moe.combine_rows(bufs["back"].view(torch.bfloat16, (slots, h)), local_row, t, k)
 
     def forward_pipelined(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_prob: torch.Tensor, micro_batches: int = 4) -> torch.Tensor:
         """Same result as :meth:`forward`, computed as ``micro_batches`` slices of the tokens in a

@@ -64,16 +64,38 @@ class PeerBuffer:
             raise ValueError(f"view of {nbytes} bytes exceeds the buffer ({self.nbytes} bytes)")
         return self.local[:nbytes].view(dtype).view(shape)
 
-    def close(self) -> None:
-        """Unmap the peers' copies and free this rank's.  Call on every rank after a barrier: a peer
-        may still be storing into this rank's copy until then."""
+    def _device_ctx(self):
+        """This buffer's device made current, all its work finished (a no-op context for a CPU stand-in)."""
+        import contextlib
+
+        if self.device.type != "cuda":
+            return contextlib.nullcontext()
+        torch.cuda.synchronize(self.device)
+        return torch.cuda.device(self.device)
+
+    def unmap_peers(self) -> None:
+        """First half of the teardown: drop this rank's mappings of the other ranks' copies.  Every rank
+        does this, then the ranks meet at a barrier, then :meth:`free_own` runs: an owner must not free
+        memory that another process still has mapped."""
         lib = _lib.load()
-        with torch.cuda.device(self.device):
-            torch.cuda.synchronize()
+        with self._device_ctx():
             for p in self._opened:
                 lib.b200moe_peer_close(p)
-            self._opened = []
+        self._opened = []
+
+    def free_own(self) -> None:
+        """Second half of the teardown: free this rank's own allocation (after every rank has unmapped it)."""
+        lib = _lib.load()
+        with self._device_ctx():
             if self._own:
                 lib.b200moe_peer_free(self._own)
                 self._own = 0
         self.local = None
+
+    def close(self) -> None:
+        """Unmap the peers' copies, wait for every rank to have done so, free this rank's copy.  Collective
+        over the buffer's group; call after a barrier that ends the last use of the buffers."""
+        self.unmap_peers()
+        if self.world > 1:
+            dist.barrier(group=self.group)
+        self.free_own()

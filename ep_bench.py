@@ -72,6 +72,23 @@ def _step_roofline(tflops_per_gpu: float, peaks):
             "peak_source": f"2 x bf16_tflops_sustained of {peaks['source']} MEASURED_PEAKS.json (dense fp8 proxy)"}  # fmt: skip
 
 
+def _timed(step, steps, warmup, stream, barrier):
+    """Warm-up, then `steps` calls between two events (barrier + synchronize on both sides), an event after
+    every step too.  Returns (ms per step over the region, sorted single-step times)."""
+    for _ in range(warmup):
+        step()
+    barrier()
+    torch.cuda.synchronize()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+    ev[0].record(stream)
+    for i in range(steps):
+        step()
+        ev[i + 1].record(stream)
+    torch.cuda.synchronize()
+    barrier()
+    return ev[0].elapsed_time(ev[steps]) / steps, sorted(ev[i].elapsed_time(ev[i + 1]) for i in range(steps))
+
+
 def run(args, tokens_per_gpu: int = 65536):
     from cudnn_frontend_b200 import synthetic
     from cudnn_frontend_b200.ep_layer import ExpertParallelMoE
@@ -92,84 +109,104 @@ def run(args, tokens_per_gpu: int = 65536):
 
     x, ids, prob = _synthetic_tokens(tokens_per_gpu, dev, 1000 + rank)
 
-    # Expert placement.  "contiguous": expert e on rank e // (E / G).  "balanced": an untimed
-    # observation of the routing (this step's histogram, summed over ranks) re-shards the experts so
-    # that every rank gets about the same number of rows, as load-aware expert placement does in
-    # production; the weights move between the ranks once, before the warm-up.
-    placement = os.environ.get("B200MOE_EP_PLACEMENT", "balanced")
-    counts_global = torch.bincount(ids.reshape(-1).long(), minlength=EXPERTS).float()
-    if world > 1:
-        dist.all_reduce(counts_global)
-    per_rank = counts_global.view(world, e_local).sum(1)
-    contiguous_ratio = float(per_rank.max() / per_rank.mean())
-    if placement == "balanced" and world > 1:
-        layer.rebalance(counts_global)
-
     def barrier():
         if world > 1:
             dist.barrier()
 
-    # data path: "peer" = rows cross NVLink by stores from the dispatch kernel and the FC2 epilogue;
-    # "nccl" = all-to-all of rows (optionally pipelined over micro-batches)
+    def max_over_ranks(v):
+        tns = torch.tensor([float(v)], device=dev)
+        if world > 1:
+            dist.all_reduce(tns, op=dist.ReduceOp.MAX)
+        return tns.item()
+
+    # data path: "peer" = rows cross NVLink by stores from the dispatch kernel and by device-to-device
+    # copies of result rows, in expert chunks beside the GEMMs; "peer-direct" = one dispatch kernel, result
+    # rows stored from the FC2 epilogue, nothing overlapped; "nccl" = all-to-all of rows
     path = os.environ.get("B200MOE_EP_PATH", "peer")
     micro = int(os.environ.get("B200MOE_EP_MICRO_BATCHES", "1"))
 
-    def run_layer(xx, ii, pp):
-        if path == "peer":
+    def run_layer(xx, ii, pp, which=None):
+        which = which or path
+        if which == "peer":
             return layer.forward_fused(xx, ii, pp)
+        if which == "peer-direct":
+            return layer.forward_fused(xx, ii, pp, chunks=0)
         return layer.forward_pipelined(xx, ii, pp, micro) if micro > 1 else layer(xx, ii, pp)
 
-    def step():
-        return run_layer(x, ids, prob)
-
     stream = torch.cuda.current_stream()
-    for _ in range(max(args.warmup, 3)):
-        y = step()
-    barrier()
-    torch.cuda.synchronize()
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    steps, warmup = args.steps, max(args.warmup, 3)
+    sampler = getattr(args, "clock_sampler", None)
     import contextlib
 
-    sampler = getattr(args, "clock_sampler", None)
-    with (sampler(local) if sampler is not None and rank == 0 else contextlib.nullcontext()) as clk:
-        start.record(stream)
-        for _ in range(args.steps):
-            y = step()
-        stop.record(stream)
-        torch.cuda.synchronize()
-    barrier()
-    ms = torch.tensor([start.elapsed_time(stop) / args.steps], device=dev)
-    rows_recv = torch.tensor([float(layer.last_rows_received)], device=dev)
-    rows_max = rows_recv.clone()
-    if world > 1:
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        dist.all_reduce(rows_max, op=dist.ReduceOp.MAX)
-        dist.all_reduce(rows_recv, op=dist.ReduceOp.SUM)
-    ms = ms.item()
-    flops = layer_flops(tokens_per_gpu * world)
-    value = flops / (ms * 1e-3) / 1e12
-    finite = bool(torch.isfinite(y.float()).all().item())
+    def measure(which=None, with_clocks=False):
+        with (sampler(local) if with_clocks and sampler is not None and rank == 0 else contextlib.nullcontext()) as clk:
+            ms, per = _timed(lambda: run_layer(x, ids, prob, which), steps, warmup, stream, barrier)
+        rows_recv = torch.tensor([float(layer.last_rows_received)], device=dev)
+        rows_max = rows_recv.clone()
+        if world > 1:
+            dist.all_reduce(rows_max, op=dist.ReduceOp.MAX)
+            dist.all_reduce(rows_recv, op=dist.ReduceOp.SUM)
+        return dict(ms=max_over_ranks(ms), median_ms=max_over_ranks(per[len(per) // 2]), min_ms=max_over_ranks(per[0]),
+                    rows_ratio=rows_max.item() / (rows_recv.item() / world), clk=None if clk is None else clk.summary())  # fmt: skip
 
-    # end to end: tokens, expert ids and gate probabilities start in pinned host memory every step and a
-    # checksum of the layer's output is read back to the host; the copy of step i + 1 runs on a copy
-    # stream while step i computes (two sets of device input buffers, events in both directions)
+    flops = layer_flops(tokens_per_gpu * world)
+    placement = os.environ.get("B200MOE_EP_PLACEMENT", "balanced")
+    side = {}
+    if world > 1 and placement == "balanced" and not getattr(args, "no_extras", False):
+        # the plain sharding (expert e on rank e // (E / G)) first, as a side measurement
+        r = measure()
+        side["contiguous_placement"] = {"ms_per_step": r["ms"], "tflops": flops / (r["ms"] * 1e-3) / 1e12,
+                                        "rows_received_max_over_mean": r["rows_ratio"]}  # fmt: skip
+    if world > 1 and placement == "balanced":
+        # Load-aware placement, as production systems do it: the routing histogram of an EARLIER batch
+        # (another seed than the batch that is timed), summed over ranks, re-shards the experts so that
+        # every rank gets about the same number of rows; the weights move between the ranks once.
+        _, ids_prev, _ = _synthetic_tokens(tokens_per_gpu, dev, 5000 + rank)
+        hist = torch.bincount(ids_prev.reshape(-1).long(), minlength=EXPERTS).float()
+        dist.all_reduce(hist)
+        layer.rebalance(hist)
+        del ids_prev
+
+    # one untimed step through both data paths on the same inputs: the NCCL all-to-all path is the check
+    y = run_layer(x, ids, prob)
+    finite = bool(torch.isfinite(y.float()).all().item())
+    matches = None
+    if world > 1:
+        y_nccl = layer(x, ids, prob)
+        matches = bool(max_over_ranks(0.0 if torch.equal(y, y_nccl) else 1.0) == 0.0)
+        del y_nccl
+
+    head = measure(with_clocks=True)
+    ms = head["ms"]
+    value = flops / (ms * 1e-3) / 1e12
+    if world > 1 and path == "peer" and not getattr(args, "no_extras", False):
+        r = measure("peer-direct")
+        side["peer_direct_path"] = {"ms_per_step": r["ms"], "tflops": flops / (r["ms"] * 1e-3) / 1e12,
+                                    "what": "one dispatch kernel, result rows stored over NVLink from the FC2 epilogue, no overlap"}  # fmt: skip
+
+    # end to end: tokens, expert ids and gate probabilities start in pinned host memory every step and the
+    # layer's output goes back to pinned host memory; the transfers overlap the neighbouring steps (a copy
+    # stream per direction, two buffers each, events both ways)
     x_h, ids_h, prob_h = x.cpu().pin_memory(), ids.cpu().pin_memory(), prob.cpu().pin_memory()
     in_bufs = [(torch.empty_like(x), torch.empty_like(ids), torch.empty_like(prob)) for _ in range(2)]
-    check_h = torch.empty(1, dtype=torch.float32).pin_memory()
-    copy_stream = torch.cuda.Stream()
+    out_bufs = [torch.empty((tokens_per_gpu, HIDDEN), dtype=torch.bfloat16, device=dev) for _ in range(2)]
+    out_h = [torch.empty((tokens_per_gpu, HIDDEN), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+    h2d_stream, d2h_stream = torch.cuda.Stream(), torch.cuda.Stream()
     copied = [torch.cuda.Event() for _ in range(2)]
     consumed = [torch.cuda.Event() for _ in range(2)]
+    computed = [torch.cuda.Event() for _ in range(2)]
+    drained = [torch.cuda.Event() for _ in range(2)]
     step_no = [0]
 
     def start_copy(i):
         x_d, ids_d, prob_d = in_bufs[i % 2]
-        with torch.cuda.stream(copy_stream):
+        with torch.cuda.stream(h2d_stream):
             if i >= 2:
-                copy_stream.wait_event(consumed[i % 2])
+                h2d_stream.wait_event(consumed[i % 2])
             x_d.copy_(x_h, non_blocking=True)
             ids_d.copy_(ids_h, non_blocking=True)
             prob_d.copy_(prob_h, non_blocking=True)
-            copied[i % 2].record(copy_stream)
+            copied[i % 2].record(h2d_stream)
 
     def e2e_step():
         i = step_no[0]
@@ -180,33 +217,41 @@ def run(args, tokens_per_gpu: int = 65536):
         stream.wait_event(copied[i % 2])
         out = run_layer(x_d, ids_d, prob_d)
         consumed[i % 2].record(stream)
-        check_h.copy_(out.float().abs().max().view(1), non_blocking=True)
+        if i >= 2:
+            stream.wait_event(drained[i % 2])
+        out_bufs[i % 2].copy_(out)
+        computed[i % 2].record(stream)
+        with torch.cuda.stream(d2h_stream):
+            d2h_stream.wait_event(computed[i % 2])
+            out_h[i % 2].copy_(out_bufs[i % 2], non_blocking=True)
+            drained[i % 2].record(d2h_stream)
         step_no[0] = i + 1
 
-    e2e_steps = max(args.steps // 4, 3)
+    e2e_steps = max(steps // 4, 3)
     for _ in range(2):
         e2e_step()
     barrier()
     torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record(stream)
     for _ in range(e2e_steps):
         e2e_step()
+    stream.wait_stream(d2h_stream)  # the last outputs have reached the host
     stop.record(stream)
     torch.cuda.synchronize()
     barrier()
-    ms_e2e = torch.tensor([start.elapsed_time(stop) / e2e_steps], device=dev)
-    if world > 1:
-        dist.all_reduce(ms_e2e, op=dist.ReduceOp.MAX)
-    ms_e2e = ms_e2e.item()
+    ms_e2e = max_over_ranks(start.elapsed_time(stop) / e2e_steps)
+    e2e_same = bool(max_over_ranks(0.0 if torch.equal(out_h[(step_no[0] - 1) % 2], y.cpu()) else 1.0) == 0.0)
     h2d = x_h.numel() * 2 + ids_h.numel() * 4 + prob_h.numel() * 4
+    d2h = out_h[0].numel() * 2
     if rank == 0:
         line = {
             "metric": "MXFP8 grouped-GEMM+SwiGLU TFLOP/s",
             "value": value,
             "unit": "TFLOP/s",
             "n_gpus": world,
-            "steps": args.steps,
-            "warmup": max(args.warmup, 3),
+            "steps": steps,
+            "warmup": warmup,
             "ms_per_step": ms,
             "higher_is_better": True,
             "scaling": "weak",
@@ -216,22 +261,26 @@ def run(args, tokens_per_gpu: int = 65536):
             "config": {
                 "workload": f"expert-parallel MoE layer: E=256 sharded {e_local}/GPU, hidden 7168, intermediate 2048, {tokens_per_gpu} tokens/GPU top-8 Zipf(1.2); one step = quantise + dispatch to the owning ranks, FC1 + SwiGLU, FC2 with gating, return + top-k sum",
                 "parallelism": f"ep{world}",
-                "data_path": "peer stores over NVLink from the quantise+dispatch kernel and from the FC2 epilogue; no all-to-all of rows" if path == "peer" else f"NCCL all-to-all, {micro} micro-batch(es)",
+                "data_path": {"peer": "peer stores over NVLink from the quantise+dispatch kernel, result rows returned by device-to-device copies; expert chunks, transfers beside the GEMMs",
+                              "peer-direct": "peer stores over NVLink from the quantise+dispatch kernel and from the FC2 epilogue; nothing overlapped",
+                              "nccl": f"NCCL all-to-all, {micro} micro-batch(es)"}[path],
                 "l2": "inputs larger than L2 (0.94 GB tokens, 11 GB local weights), no flush",
-                "expert_placement": placement if world > 1 else "single rank",
-                "rows_received_max_over_mean": rows_max.item() / (rows_recv.item() / world),
-                "rows_received_max_over_mean_contiguous_placement": contiguous_ratio,
+                "expert_placement": (placement + " (histogram of an earlier batch, another seed than the timed one)" if placement == "balanced" else placement) if world > 1 else "single rank",
+                "rows_received_max_over_mean": head["rows_ratio"],
                 "pct_of_fp8_nominal_4500_per_gpu": 100.0 * value / world / 4500.0,
                 "output_finite": finite,
+                "output_matches_nccl_path": matches,
             },
-            "gpu_launches": args.steps * (7 if path == "peer" else 5 * micro),
-            "e2e": {"value": flops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
-                    "ms_per_step": ms_e2e,
-                    "note": "bytes are one rank's, the value is the aggregate over ranks; the copy of step i + 1 overlaps step i"},
+            "timing": {"median_ms": head["median_ms"], "min_ms": head["min_ms"], "steps": steps},
+            "gpu_launches": steps * (7 if path != "nccl" else 5 * micro),
+            "e2e": {"value": flops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": ms_e2e, "steps": e2e_steps, "output_on_host_matches": e2e_same,
+                    "note": "bytes are one rank's, the value is the aggregate over ranks; inputs of step i + 1 and the output of step i - 1 travel while step i computes; the region ends when the last output is on the host"},
             "roofline": _step_roofline(value / world, getattr(args, "peaks", None)),
-            "clocks": clk.summary() if clk is not None else None,
+            "clocks": head["clk"],
             "cpu_baseline": None,
-        }
+            "extras": side,
+        }  # fmt: skip
         print(json.dumps(line))
     layer.release_peer_buffers()
     if world > 1:

@@ -287,7 +287,23 @@ int b200moe_dispatch_quantize_peer(const void* x, const int32_t* expert_ids, con
                                    int32_t num_ranks, int32_t my_rank, int64_t slot_capacity,
                                    int64_t row_capacity, const int64_t* peer_q,
                                    const int64_t* peer_rec, void* stream);
+ /* as above for the rows of local experts [local_expert_lo, local_expert_hi) of every rank only (a
+    layer that runs its experts in chunks dispatches chunk by chunk); max_blocks > 0 bounds the grid
+    (the blocks then walk the tokens), so that the kernel can run beside a GEMM that owns most SMs */
+int b200moe_dispatch_quantize_peer_range(const void* x, const int32_t* expert_ids, const int32_t* local_row,
+                                         const int32_t* delta, const float* topk_prob, int64_t num_tokens,
+                                         int32_t topk, int64_t cols, int32_t experts_per_rank,
+                                         int32_t num_ranks, int32_t my_rank, int64_t slot_capacity,
+                                         int64_t row_capacity, const int64_t* peer_q,
+                                         const int64_t* peer_rec, int32_t local_expert_lo,
+                                         int32_t local_expert_hi, int32_t max_blocks, void* stream);
 int b200moe_dispatch_record_pitch(int64_t cols);
+/* count asynchronous device-to-device copies on one stream: segment i moves bytes[i] bytes from
+   address src[i] to address dst[i] (HOST arrays of device addresses; peer-mapped buffers included).
+   The copy engines do the work, no SM is used: this is how a layer returns result rows to the
+   ranks they came from while its GEMMs keep running.  No reference counterpart. */
+int b200moe_copy_segments(int32_t count, const int64_t* dst, const int64_t* src, const int64_t* bytes,
+                          void* stream);
 int b200moe_unpack_dispatch_records(const void* rec, int64_t m_rows, int64_t cols, void* sfa,
                                     float* prob, int32_t* row_map, void* stream);
 int b200moe_peer_alloc(int64_t bytes, void** ptr, void* handle64);

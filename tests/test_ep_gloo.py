@@ -248,3 +248,91 @@ def test_rebalance_moves_every_expert_to_its_new_slot_world_size_2():
     ret = mgr.dict()
     mp.spawn(_move_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
     assert all(ret.get(r) for r in range(world)), dict(ret)
+
+
+def test_return_segments_put_every_row_where_its_source_expects_it():
+    """The chunked peer path returns result rows as contiguous blocks, one per (expert, source rank).
+    Emulated on the host for 4 ranks: every rank labels the rows of its expert groups with (source, expert,
+    index), applies its segments to the sources' result buffers chunk by chunk, and every source must find
+    its rows in its own expert-sorted order."""
+    from cudnn_frontend_b200.ep_layer import return_segments
+
+    g, e, m_aligned = 4, 12, 128
+    el = e // g
+    rng = np.random.default_rng(3)
+    cnt = rng.integers(0, 40, (g, e))
+    cnt[:, 5] = 0  # an expert nobody routes to
+    cnt[2, :] = 0  # a rank without tokens
+    total = cnt.sum(0)
+    padded = (total + m_aligned - 1) // m_aligned * m_aligned
+    back = [np.full((int(cnt[s].sum()), 3), -1, dtype=np.int64) for s in range(g)]
+    for rank in range(g):
+        ends = np.cumsum(padded[rank * el : (rank + 1) * el])
+        starts = np.concatenate([[0], ends[:-1]])
+        y = np.full((int(ends[-1]), 3), -1, dtype=np.int64)
+        for j in range(el):
+            eg = rank * el + j
+            row = int(starts[j])
+            for s in range(g):
+                for i in range(int(cnt[s, eg])):
+                    y[row] = (s, eg, i)
+                    row += 1
+        seen = set()
+        for lo, hi in ((0, 1), (1, 3)):  # two chunks
+            for s, dst_row, src_row, rows in return_segments(cnt, ends, rank, lo, hi):
+                assert (s, dst_row) not in seen
+                seen.add((s, dst_row))
+                back[s][dst_row : dst_row + rows] = y[src_row : src_row + rows]
+    for s in range(g):
+        expect = [(s, eg, i) for eg in range(e) for i in range(int(cnt[s, eg]))]
+        assert back[s].tolist() == [list(v) for v in expect]
+
+
+def _teardown_worker(rank, world, port, log):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import time
+
+        from cudnn_frontend_b200 import _lib, ep_layer, peer_memory
+
+        class FakeLib:
+            def b200moe_peer_close(self, p):
+                log.append((rank, "unmap", int(p)))
+                return 0
+
+            def b200moe_peer_free(self, p):
+                log.append((rank, "free", int(p)))
+                return 0
+
+        _lib.load = lambda: FakeLib()
+        bufs = {}
+        for name in ("q", "rec", "back"):
+            b = peer_memory.PeerBuffer.__new__(peer_memory.PeerBuffer)
+            b.group, b.world, b.rank, b.device = dist.group.WORLD, world, rank, torch.device("cpu")
+            b._own, b._opened, b.local = 1000 + rank, [2000 + r for r in range(world) if r != rank], None
+            bufs[name] = b
+        layer = ep_layer.ExpertParallelMoE.__new__(ep_layer.ExpertParallelMoE)
+        layer.world, layer.group = world, dist.group.WORLD
+        layer._peer, layer._peer_key = dict(bufs=bufs), ("x",)
+        ep_layer.torch.cuda.synchronize = lambda *a, **k: None  # CPU ranks
+        if rank == 1:
+            time.sleep(0.3)  # a slow rank: the others must not free before it has unmapped
+        layer.release_peer_buffers()
+        assert layer._peer is None
+    finally:
+        dist.destroy_process_group()
+
+
+def test_peer_buffers_are_freed_only_after_every_rank_unmapped_them():
+    """Teardown order of the peer buffers on 2 CPU ranks with a stand-in library that logs the calls: every
+    'free' comes after every rank's 'unmap' (freeing memory another process still maps is undefined)."""
+    mgr = mp.Manager()
+    log = mgr.list()
+    mp.spawn(_teardown_worker, args=(2, _free_port(), log), nprocs=2, join=True)
+    events = list(log)
+    assert sum(1 for e in events if e[1] == "unmap") == 2 * 3 and sum(1 for e in events if e[1] == "free") == 2 * 3
+    last_unmap = max(i for i, e in enumerate(events) if e[1] == "unmap")
+    first_free = min(i for i, e in enumerate(events) if e[1] == "free")
+    assert last_unmap < first_free, events

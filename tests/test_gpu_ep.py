@@ -74,6 +74,27 @@ def test_peer_memory_layer_equals_the_plain_layer():
     layer.release_peer_buffers()
 
 
+@pytest.mark.parametrize("chunks", [1, 3, 8])
+def test_chunked_peer_path_equals_the_plain_layer(chunks):
+    """The chunked form of the peer path (experts in slices, dispatch of the next slice on a side stream,
+    result rows returned by device-to-device copies in the sources' sorted order) on one rank: the same
+    bytes as the plain layer, step after step."""
+    from cudnn_frontend_b200 import ops
+    from cudnn_frontend_b200.ep_layer import ExpertParallelMoE
+
+    x, ids, prob, w1, sfw1, w2, sfw2 = _inputs(7, "cuda")
+    layer = ExpertParallelMoE(w1, sfw1, w2, sfw2, E)
+    y = layer(x, ids, prob)
+    yc = layer.forward_fused(x, ids, prob, chunks=chunks)
+    x2, ids2, prob2, *_ = _inputs(8, "cuda")
+    y2 = layer(x2, ids2, prob2)
+    yc2 = layer.forward_fused(x2, ids2, prob2, chunks=chunks)  # buffers and streams are reused
+    torch.cuda.synchronize()
+    assert ops.device_status(clear=True) == 0
+    assert torch.equal(y, yc) and torch.equal(y2, yc2)
+    layer.release_peer_buffers()
+
+
 def test_peer_buffers_grow_when_a_step_needs_more_rows():
     """A capacity factor far too small for the step: the layer reallocates larger peer buffers (all
     ranks together in the multi-rank case) and still returns the plain layer's result."""
@@ -152,8 +173,9 @@ def _ep_worker(rank, world, port, ret):
         full = ExpertParallelMoE(w1, sfw1, w2, sfw2, E)
         y1 = full(x, ids, prob)
         yp = layer.forward_pipelined(x, ids, prob, micro_batches=3)
-        yf = layer.forward_fused(x, ids, prob)  # rows cross NVLink by peer stores, no all-to-all
-        yf2 = layer.forward_fused(x, ids, prob)
+        yf = layer.forward_fused(x, ids, prob, chunks=0)  # rows cross NVLink by peer stores, no all-to-all
+        yf2 = layer.forward_fused(x, ids, prob)  # in expert chunks (the default on several ranks)
+        yc2 = layer.forward_fused(x, ids, prob, chunks=2)
         # re-shard by load (weights cross ranks) and run again: same function
         counts = torch.bincount(ids.reshape(-1).long(), minlength=E).float()
         dist.all_reduce(counts)
@@ -167,7 +189,7 @@ def _ep_worker(rank, world, port, ret):
         status = _ops.device_status(clear=True)
         layer.release_peer_buffers()
         # row order inside an expert group differs between the runs, the per-row maths does not
-        ret[rank] = bool(torch.equal(y, y1)) and bool(torch.equal(yp, y1)) and bool(torch.equal(yf, y1)) and bool(torch.equal(yf2, y1)) and bool(torch.equal(yr, y1)) and bool(torch.equal(yr2, y1)) and status == 0
+        ret[rank] = bool(torch.equal(y, y1)) and bool(torch.equal(yp, y1)) and bool(torch.equal(yf, y1)) and bool(torch.equal(yf2, y1)) and bool(torch.equal(yc2, y1)) and bool(torch.equal(yr, y1)) and bool(torch.equal(yr2, y1)) and status == 0
     finally:
         dist.destroy_process_group()
 
