@@ -360,11 +360,27 @@ def vs_reference_kernel(prob256, stream):
     torch.cuda.synchronize()
     t_ref = sorted(ev[2 * i].elapsed_time(ev[2 * i + 1]) for i in range(rounds))
     t_own = sorted(ev[2 * i + 1].elapsed_time(ev[2 * i + 2]) for i in range(rounds))
-    iso_ref = time_trials(run_ref, stream)
-    iso_own = time_trials(run_own, stream)
+    # isolated launches (L2 flushed, GPU idle before each), the two kernels taking turns so that both see
+    # the same power and clock state of the GPU
+    dev = torch.cuda.current_device()
+    if dev not in _FLUSH:
+        _FLUSH[dev] = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    iso = {"ref": [], "own": []}
+    for _ in range(10):
+        for name, fn in (("ref", run_ref), ("own", run_own)):
+            _FLUSH[dev].zero_()
+            s_, e_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s_.record(stream)
+            fn()
+            e_.record(stream)
+            torch.cuda.synchronize()
+            iso[name].append(s_.elapsed_time(e_))
+    iso_ref = {"median_ms": sorted(iso["ref"])[5], "min_ms": min(iso["ref"])}
+    iso_own = {"median_ms": sorted(iso["own"])[5], "min_ms": min(iso["own"])}
     return {
         "workload": "c2 FC1 through both wrappers: groups padded to 256, C + E4M3 D + D_col + row and column scales",
-        "protocol": "interleaved A B A B in one queue (medians of 12 rounds); isolated = 10 trials with an L2 flush",
+        "protocol": "interleaved A B A B in one queue (medians of 12 rounds); isolated = 10 trials each with an L2 flush and an idle GPU before "
+                    "every launch, the two kernels taking turns",
         "reference_ms": t_ref[rounds // 2], "own_ms": t_own[rounds // 2], "own_over_reference": t_ref[rounds // 2] / t_own[rounds // 2],
         "reference_isolated_ms": iso_ref["median_ms"], "own_isolated_ms": iso_own["median_ms"],
         "own_over_reference_isolated": iso_ref["median_ms"] / iso_own["median_ms"],
