@@ -176,7 +176,7 @@ __global__ void __launch_bounds__(128)
                                   const int32_t* __restrict__ local_row, const int32_t* __restrict__ delta,
                                   const float* __restrict__ topk_prob, int64_t num_tokens, int topk, int cols, int rec_pitch,
                                   int experts_per_rank, int num_ranks, int my_rank, int64_t slot_capacity, int64_t row_capacity,
-                                  int local_lo, int local_hi, const int64_t* __restrict__ peer_q,
+                                  const int32_t* __restrict__ expert_chunk, int chunk, const int64_t* __restrict__ peer_q,
                                   const int64_t* __restrict__ peer_rec) {
   extern __shared__ __align__(16) uint8_t s_dyn[];  // [cols] E4M3 row, then topk records of rec_pitch bytes
   uint8_t* const s_qrow = s_dyn;
@@ -197,9 +197,8 @@ __global__ void __launch_bounds__(128)
       int rank = 0;
       if (e >= 0 && e < experts_per_rank * num_ranks) {
         rank = e / experts_per_rank;
-        const int local = e - rank * experts_per_rank;
-        // this launch moves the rows of local experts [local_lo, local_hi) of every rank only
-        if (local >= local_lo && local < local_hi) {
+        // with a chunk table this launch moves only the rows of the experts of one chunk
+        if (expert_chunk == nullptr || expert_chunk[e] == chunk) {
           row = (int64_t)delta[e] + local_row[slot];
           if (row < 0 || row >= row_capacity) {
             atomicCAS(&g_device_status, 0, 301);  // never store outside a peer's buffer
@@ -432,11 +431,11 @@ int b200moe_dispatch_quantize(const void* x, const int32_t* send_pos, const floa
 
 int b200moe_dispatch_record_pitch(int64_t cols) { return (int)(((cols / 32 + 8) + 15) / 16 * 16); }
 
-int b200moe_dispatch_quantize_peer_range(const void* x, const int32_t* expert_ids, const int32_t* local_row, const int32_t* delta,
+int b200moe_dispatch_quantize_peer_chunk(const void* x, const int32_t* expert_ids, const int32_t* local_row, const int32_t* delta,
                                          const float* topk_prob, int64_t num_tokens, int32_t topk, int64_t cols,
                                          int32_t experts_per_rank, int32_t num_ranks, int32_t my_rank, int64_t slot_capacity,
                                          int64_t row_capacity, const int64_t* peer_q, const int64_t* peer_rec,
-                                         int32_t local_expert_lo, int32_t local_expert_hi, int32_t max_blocks, void* stream) {
+                                         const int32_t* expert_chunk, int32_t chunk, int32_t max_blocks, void* stream) {
   using namespace b200moe;
   if (num_tokens == 0) return B200MOE_OK;
   if (!x || !expert_ids || !local_row || !delta || !peer_q || !peer_rec)
@@ -447,8 +446,7 @@ int b200moe_dispatch_quantize_peer_range(const void* x, const int32_t* expert_id
   if (experts_per_rank <= 0 || num_ranks <= 0 || my_rank < 0 || my_rank >= num_ranks || slot_capacity < num_tokens * topk ||
       (int64_t)num_ranks * slot_capacity > 0x7fffffffll || row_capacity <= 0)
     return fail(B200MOE_E_SHAPE, "dispatch_quantize_peer: bad rank layout or capacities");
-  if (local_expert_lo < 0 || local_expert_hi > experts_per_rank || local_expert_lo >= local_expert_hi || max_blocks < 0)
-    return fail(B200MOE_E_SHAPE, "dispatch_quantize_peer: bad local expert range [%d, %d) or block limit", local_expert_lo, local_expert_hi);
+  if (max_blocks < 0) return fail(B200MOE_E_SHAPE, "dispatch_quantize_peer: negative block limit");
   if ((uintptr_t)x & 15) return fail(B200MOE_E_ALIGN, "dispatch_quantize_peer: 16-byte alignment required");
   const int rec_pitch = b200moe_dispatch_record_pitch(cols);
   const size_t smem = (size_t)cols + (size_t)topk * rec_pitch;
@@ -456,7 +454,7 @@ int b200moe_dispatch_quantize_peer_range(const void* x, const int32_t* expert_id
   const int64_t blocks = max_blocks > 0 ? std::min<int64_t>(max_blocks, num_tokens) : num_tokens;
   dispatch_quantize_peer_kernel<<<(unsigned)blocks, 128, smem, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)x, expert_ids, local_row, delta, topk_prob, num_tokens, topk, (int)cols, rec_pitch, experts_per_rank,
-      num_ranks, my_rank, slot_capacity, row_capacity, local_expert_lo, local_expert_hi, peer_q, peer_rec);
+      num_ranks, my_rank, slot_capacity, row_capacity, expert_chunk, chunk, peer_q, peer_rec);
   B200_CUDA_CHECK(cudaGetLastError());
   return B200MOE_OK;
 }
@@ -465,9 +463,8 @@ int b200moe_dispatch_quantize_peer(const void* x, const int32_t* expert_ids, con
                                    const float* topk_prob, int64_t num_tokens, int32_t topk, int64_t cols,
                                    int32_t experts_per_rank, int32_t num_ranks, int32_t my_rank, int64_t slot_capacity,
                                    int64_t row_capacity, const int64_t* peer_q, const int64_t* peer_rec, void* stream) {
-  return b200moe_dispatch_quantize_peer_range(x, expert_ids, local_row, delta, topk_prob, num_tokens, topk, cols, experts_per_rank,
-                                              num_ranks, my_rank, slot_capacity, row_capacity, peer_q, peer_rec, 0, experts_per_rank,
-                                              0, stream);
+  return b200moe_dispatch_quantize_peer_chunk(x, expert_ids, local_row, delta, topk_prob, num_tokens, topk, cols, experts_per_rank,
+                                              num_ranks, my_rank, slot_capacity, row_capacity, peer_q, peer_rec, nullptr, 0, 0, stream);
 }
 
 int b200moe_copy_segments(int32_t count, const int64_t* dst, const int64_t* src, const int64_t* bytes, void* stream) {

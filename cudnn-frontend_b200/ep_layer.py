@@ -111,6 +111,7 @@ class FusedPlan:
     padded_offsets: torch.Tensor  # [E_local] int32 END offsets of this rank's expert groups
     m_rows_all: torch.Tensor  # [G] int64 padded rows every rank will hold
     rows_all: torch.Tensor  # [G] int64 true rows every rank receives
+    group_starts: Optional[torch.Tensor] = None  # [G, E_local] int64 first padded row of every expert group on its rank
 
 
 def plan_fused(counts_all: torch.Tensor, rank: int, m_aligned: int = 128) -> FusedPlan:
@@ -128,7 +129,35 @@ def plan_fused(counts_all: torch.Tensor, rank: int, m_aligned: int = 128) -> Fus
     before = torch.cumsum(c, dim=0) - c  # rows of earlier source ranks inside each group
     compact_start = torch.cumsum(c[rank], 0) - c[rank]  # this rank's route(m_aligned=1) starts
     delta = group_start + before[rank] - compact_start
-    return FusedPlan(delta.to(torch.int32), ends[rank].to(torch.int32), ends[:, -1].contiguous(), total.view(g, e_local).sum(1))
+    return FusedPlan(delta.to(torch.int32), ends[rank].to(torch.int32), ends[:, -1].contiguous(), total.view(g, e_local).sum(1),
+                     group_start.view(g, e_local))
+
+
+def chunk_weights(chunks: int):
+    """Relative sizes of the chunks of the chunked peer path: equal, except that the last two are 0.6 and
+    0.4 of a share, because the return of the last chunk's rows is the one transfer nothing hides."""
+    if chunks < 3:
+        return [10] * chunks
+    return [10] * (chunks - 2) + [6, 4]
+
+
+def chunk_of_experts(group_starts: torch.Tensor, rows_per_rank: torch.Tensor, weights) -> torch.Tensor:
+    """Chunk of every expert for a layer that runs each rank's experts in ``len(weights)`` slices whose
+    rows are in the proportion ``weights`` (integers): ``group_starts [G, E_local]`` (first padded row of
+    every expert group on its rank) and ``rows_per_rank [G]`` (padded rows per rank) -> int32
+    ``[G * E_local]``.  Chunk c of rank r begins at row ``rows_r * sum(weights[:c]) // sum(weights)``; an
+    expert belongs to the chunk its first row falls in.  Monotone in the local expert index, so a chunk is a
+    contiguous range of local experts; a chunk is empty when one expert spans several shares.  Integer
+    arithmetic only: every rank computes the same table from the all-gathered histogram, on any device,
+    and the host repeats it with the same numbers."""
+    total = int(sum(weights))
+    rows = rows_per_rank.to(torch.int64).view(-1, 1)
+    cum = 0
+    c = torch.zeros_like(group_starts, dtype=torch.int64)
+    for w in list(weights)[:-1]:
+        cum += int(w)
+        c += (group_starts.to(torch.int64) >= (rows * cum) // total).to(torch.int64)
+    return c.to(torch.int32).reshape(-1).contiguous()
 
 
 def return_segments(counts_host, padded_ends, rank: int, lo: int, hi: int):
@@ -423,12 +452,12 @@ class ExpertParallelMoE:
                       chunks: Optional[int] = None) -> torch.Tensor:
         """The peer-memory path.  On one rank: :meth:`forward_fused_direct`.  On several ranks:
         :meth:`forward_fused_chunked`, which overlaps the NVLink traffic with the GEMMs (``chunks``
-        expert chunks, default 4 or the environment variable ``B200MOE_EP_CHUNKS``; ``chunks=0`` selects
+        expert chunks, default 5 or the environment variable ``B200MOE_EP_CHUNKS``; ``chunks=0`` selects
         the direct form on any number of ranks)."""
         import os
 
         if chunks is None:
-            chunks = int(os.environ.get("B200MOE_EP_CHUNKS", "4")) if self.world > 1 else 0
+            chunks = int(os.environ.get("B200MOE_EP_CHUNKS", "5")) if self.world > 1 else 0
         if chunks <= 0:
             return self.forward_fused_direct(x, topk_ids, topk_prob, capacity_factor)
         return self.forward_fused_chunked(x, topk_ids, topk_prob, capacity_factor, chunks)
@@ -571,15 +600,20 @@ class ExpertParallelMoE:
         ev_plan = torch.cuda.Event()
         ev_plan.record(main)
 
+        # chunks of about equal rows on every rank: a table on the device for the dispatch kernel (it covers
+        # every rank's experts), the same numbers on the host for this rank's launches
         chunks = max(1, min(int(chunks), el))
-        bounds = [(c * el // chunks, (c + 1) * el // chunks) for c in range(chunks)]
+        weights = chunk_weights(chunks)
+        chunk_table = chunk_of_experts(plan.group_starts, plan.m_rows_all, weights)
+        starts = np.concatenate([[0], ends[:-1]])  # first row of my expert groups
+        my_chunk = sum((starts >= (m * int(cw)) // sum(weights)).astype(np.int64) for cw in np.cumsum(weights)[:-1]) if chunks > 1 else np.zeros(el, dtype=np.int64)
+        bounds = [(int(np.searchsorted(my_chunk, c, "left")), int(np.searchsorted(my_chunk, c, "right"))) for c in range(chunks)]
         flat_prob = topk_prob.reshape(t * k).contiguous()
 
         def dispatch(c, max_blocks):
             moe.dispatch_quantize_peer(x, ids, local_row, plan.delta, flat_prob, el, g, rank, slots, cap, bufs["q"].ptrs_dev,
-                                       bufs["rec"].ptrs_dev, local_experts=bounds[c], max_blocks=max_blocks)  # fmt: skip
+                                       bufs["rec"].ptrs_dev, expert_chunk=chunk_table, chunk=c, max_blocks=max_blocks)  # fmt: skip
 
-        starts = np.concatenate([[0], ends[:-1]])  # first row of my expert groups
         row_bytes = h * 2
         back_ptrs = bufs["back"].ptrs
 
@@ -604,7 +638,7 @@ class ExpertParallelMoE:
         for c, (lo, hi) in enumerate(bounds):
             if c > 0:
                 main.wait_event(ev_disp[c])
-            r0, r1 = int(starts[lo]), int(ends[hi - 1])
+            r0, r1 = (int(starts[lo]), int(ends[hi - 1])) if hi > lo else (0, 0)
             if r1 > r0:
                 moe.unpack_dispatch_records(bufs["rec"].local[r0 * pitch :], r1 - r0, h, loc["sf"][(r0 // 128) * rest_k * 512 :], loc["prob"][r0:],
                                             loc["map"][r0:])  # fmt: skip

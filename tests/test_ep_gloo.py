@@ -336,3 +336,24 @@ def test_peer_buffers_are_freed_only_after_every_rank_unmapped_them():
     last_unmap = max(i for i, e in enumerate(events) if e[1] == "unmap")
     first_free = min(i for i, e in enumerate(events) if e[1] == "free")
     assert last_unmap < first_free, events
+
+
+def test_chunk_table_is_monotone_and_matches_its_host_restatement():
+    """The chunk of every expert (device table for the dispatch kernel, all ranks) against the host
+    arithmetic one rank uses for its own launches; chunks are contiguous ranges of local experts."""
+    from cudnn_frontend_b200.ep_layer import chunk_of_experts, chunk_weights
+
+    g, el = 4, 16
+    gen = torch.Generator().manual_seed(0)
+    padded = torch.randint(0, 5, (g, el), generator=gen) * 128
+    padded[2] = 0  # a rank without rows
+    ends = torch.cumsum(padded, 1)
+    starts, rows = ends - padded, ends[:, -1]
+    for chunks in (1, 2, 4, 5, 16):
+        w = chunk_weights(chunks)
+        assert len(w) == chunks
+        table = chunk_of_experts(starts, rows, w).view(g, el).numpy()
+        for r in range(g):
+            m, st = int(rows[r]), starts[r].numpy()
+            host = sum((st >= (m * int(cw)) // sum(w)).astype(np.int64) for cw in np.cumsum(w)[:-1]) if chunks > 1 else np.zeros(el, dtype=np.int64)
+            assert (table[r] == host).all() and (np.diff(table[r]) >= 0).all() and table[r].max() < chunks
