@@ -114,7 +114,8 @@ def run_case(name, cfg, out):
         p["b"] = (torch.randn(cfg["experts"], n, k, generator=g5, device="cuda") * 0.5).to(torch.float8_e5m2).permute(1, 2, 0)
     norm = torch.tensor([1.0], dtype=torch.float32, device="cuda")
     stream = cuda.CUstream(torch.cuda.current_stream().cuda_stream)
-    d_dtype = torch.float8_e5m2 if cfg.get("d") == "e5m2" else torch.float8_e4m3fn
+    d_dtype = {"e5m2": torch.float8_e5m2, "bf16": torch.bfloat16}.get(cfg.get("d"), torch.float8_e4m3fn)
+    d16 = d_dtype == torch.bfloat16  # scale factors generated, D and D_col hold the scaled values in bf16
     common = dict(norm_const_tensor=norm, prob_tensor=p["prob"], d_dtype=d_dtype, sf_vec_size=32, m_aligned=256)
     res = {"case": name, "cfg": cfg, "m_rows": p["m_rows"], "flops": p["flops"]}
 
@@ -143,14 +144,24 @@ def run_case(name, cfg, out):
 
     sf_r, sf_o = flat(r_ref["sfd_row_tensor"]), flat(r_own["sfd_row_tensor"])
     res["sfd_row_bytes_equal_frac"] = float((sf_r == sf_o).float().mean())
-    d_r, d_o = r_ref["d_tensor"][:m].view(torch.uint8), r_own["d_tensor"][:m].view(torch.uint8)
-    u = ulp(d_r, d_o)
-    res["d_e4m3_within_1ulp_frac"] = float((u <= 1).float().mean())
-    res["d_e4m3_equal_frac"] = float((u == 0).float().mean())
+    def raw(t):  # [m, n_out] bytes (FP8) or 16-bit patterns (bf16)
+        t2 = t[:m, :, 0]
+        return t2.view(torch.uint8) if t.element_size() == 1 else t2.contiguous().view(torch.int16)
+
+    d_r, d_o = raw(r_ref["d_tensor"]), raw(r_own["d_tensor"])
+    dc_r, dc_o = raw(r_ref["d_col_tensor"]), raw(r_own["d_col_tensor"])
+    if d16:
+        res["d_bf16_equal_frac"] = float((d_r == d_o).float().mean())
+        res["d_col_bf16_equal_frac"] = float((dc_r == dc_o).float().mean())
+        res["amax_equal"] = bool(torch.equal(r_ref["amax_tensor"], r_own["amax_tensor"]))
+    else:
+        u = ulp(d_r, d_o)
+        res["d_e4m3_within_1ulp_frac"] = float((u <= 1).float().mean())
+        res["d_e4m3_equal_frac"] = float((u == 0).float().mean())
+        uc = ulp(dc_r, dc_o)
+        res["d_col_within_1ulp_frac"] = float((uc <= 1).float().mean())
     sc_r, sc_o = flat(r_ref["sfd_col_tensor"]), flat(r_own["sfd_col_tensor"])
     res["sfd_col_bytes_equal_frac"] = float((sc_r == sc_o).float().mean())
-    uc = ulp(r_ref["d_col_tensor"][:m].view(torch.uint8), r_own["d_col_tensor"][:m].view(torch.uint8))
-    res["d_col_within_1ulp_frac"] = float((uc <= 1).float().mean())
 
     def run_ref():
         return ref.grouped_gemm_swiglu_wrapper_sm100(p["a"], p["b"], p["sfa"], p["sfb"], p["padded_offsets"], p["alpha"],
@@ -187,11 +198,12 @@ def run_case(name, cfg, out):
     out.append(res)
     print(json.dumps(res), flush=True)
 
-    if name in ("tiny", "tiny_e5m2", "tiny_d_e5m2", "tiny_deepk"):
+    if name in ("tiny", "tiny_e5m2", "tiny_d_e5m2", "tiny_deepk", "tiny_d_bf16"):
         np.savez_compressed(
             os.path.join(OUT_DIR, {"tiny": "reference_kernel_golden.npz", "tiny_e5m2": "reference_kernel_e5m2_golden.npz",
                                    "tiny_d_e5m2": "reference_kernel_d_e5m2_golden.npz",
-                                   "tiny_deepk": "reference_kernel_deepk_golden.npz"}[name]),
+                                   "tiny_deepk": "reference_kernel_deepk_golden.npz",
+                                   "tiny_d_bf16": "reference_kernel_d_bf16_golden.npz"}[name]),
             a=p["a"][:, :, 0].view(torch.uint8).cpu().numpy(),
             b=p["b"].permute(2, 0, 1).contiguous().view(torch.uint8).cpu().numpy(),
             sfa=flat(p["sfa"]).cpu().numpy(),
@@ -199,8 +211,9 @@ def run_case(name, cfg, out):
             offsets=p["padded_offsets"].cpu().numpy(),
             prob=p["prob"].view(-1).cpu().numpy(),
             c=r_ref["c_tensor"][:, :, 0].view(torch.int16).cpu().numpy(),
-            d=d_r[:, :, 0].cpu().numpy(),
-            d_col=r_ref["d_col_tensor"][:m, :, 0].view(torch.uint8).cpu().numpy(),
+            d=d_r.cpu().numpy(),
+            d_col=dc_r.cpu().numpy(),
+            amax=(r_ref["amax_tensor"].cpu().numpy() if d16 else np.zeros(0, dtype=np.float32)),
             sfd_row=sf_r.cpu().numpy(),
             sfd_col=sc_r.cpu().numpy(),
         )
@@ -360,6 +373,8 @@ CASES = {
     "tiny_d_e5m2": dict(experts=2, k=128, n=128, tokens=128, topk=2, routing="uniform", d="e5m2"),
     # eight k-tiles deep (the accumulation across k-tiles and the wrap of the shared-memory ring), still small enough to commit
     "tiny_deepk": dict(experts=2, k=1024, n=128, tokens=64, topk=2, routing="uniform"),
+    # scale factors generated with a bf16 D: D and D_col hold the scaled values (block maximum mapped to 1), amax too
+    "tiny_d_bf16": dict(experts=2, k=128, n=128, tokens=128, topk=2, routing="uniform", d="bf16"),
     "small": dict(experts=4, k=512, n=512, tokens=512, topk=2, routing="uniform"),
     "c2": dict(experts=8, k=4096, n=28672, tokens=16384, topk=2, routing="uniform"),
     "c3": dict(experts=256, k=7168, n=4096, tokens=8192, topk=8, routing="zipf"),

@@ -99,7 +99,7 @@ _SIGNATURES = {
     "b200moe_dispatch_quantize_peer_chunk": (
         ctypes.c_int,
         [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_int64, c_int32, c_int32, c_int32, c_int64,
-         c_int64, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_void_p],
+         c_int64, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_void_p],
     ),  # fmt: skip
     "b200moe_copy_segments": (ctypes.c_int, [c_int32, POINTER(c_int64), POINTER(c_int64), POINTER(c_int64), c_void_p]),
     "b200moe_dispatch_record_pitch": (ctypes.c_int, [c_int64]),

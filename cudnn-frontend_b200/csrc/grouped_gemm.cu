@@ -139,6 +139,7 @@ struct GemmParams {
   int sfd_row_rest_k;  // ceil(ceil(n_out / 32) / 4)
   int sfd_col_rest_k;  // ceil(ceil(m_rows / 32) / 4)
   int d_is_fp8;
+  int gen_sfd;        // row (and column) scale factors are generated and D holds scaled values
   int d_e5m2;         // FP8 D (and D_col) in E5M2 instead of E4M3
   float d_rcp_limit;  // 1/448 (E4M3) or 1/128 (E5M2)
   int d_f16, c_f16;   // 16-bit D / C in fp16 instead of bf16
@@ -275,21 +276,38 @@ __device__ __forceinline__ void store_e4m3x32(uint8_t* dst, const float* v, floa
   store_32B(dst, o[0], o[1], wide);
 }
 
-// Output quantisation format: reciprocal of the value the block maximum is mapped to (the reference's
-// get_dtype_rcp_limits: 1/448 for E4M3, 1/128 for E5M2) and the byte format.
+// Output format of the scale-factor-generating epilogue: the reciprocal of the value the block maximum is
+// mapped to (the reference's get_dtype_rcp_limits: 1/448 for E4M3, 1/128 for E5M2, 1 for a 16-bit D) and
+// how the scaled values are stored (FP8 bytes, or bf16 / fp16 when D is a 16-bit tensor: the reference
+// then keeps the scaled values, which lie in (-1, 1], in D's own type).
 struct OutFormat {
   float rcp_limit;
   bool e5m2;
+  bool bits16;  // D and D_col hold 16-bit values
+  bool f16;     // ... fp16 instead of bf16
 };
 
-// Row-wise MXFP8 of one 32-element block: returns the E8M0 byte, stores 32 FP8 bytes.
-__device__ __forceinline__ uint32_t quant_row_block(uint8_t* dst, const float* v, float norm_const, bool wide, OutFormat fmt) {
+// 32 scaled values of one row: element `col` of the row that starts at `row_base` (a byte pointer)
+__device__ __forceinline__ void store_scaled32(uint8_t* row_base, int64_t col, const float* v, float scale, bool wide, OutFormat fmt) {
+  if (fmt.bits16) {
+    float t[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) t[i] = v[i] * scale;
+    store_bf16x32(reinterpret_cast<__nv_bfloat16*>(row_base) + col, t, wide, fmt.f16);
+  } else {
+    store_e4m3x32(row_base + col, v, scale, wide, fmt.e5m2);
+  }
+}
+
+// Row-wise scaling of one 32-element block: returns the E8M0 byte, stores the 32 scaled values.
+__device__ __forceinline__ uint32_t quant_row_block(uint8_t* row_base, int64_t col, const float* v, float norm_const, bool wide,
+                                                    OutFormat fmt) {
   float amax = 0.f;
 #pragma unroll
   for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(v[i]));
   const float pv = amax * fmt.rcp_limit * norm_const;
   const uint32_t sf = e8m0_from_float(pv);
-  store_e4m3x32(dst, v, quant_scale(norm_const, e8m0_to_float(sf)), wide, fmt.e5m2);
+  store_scaled32(row_base, col, v, quant_scale(norm_const, e8m0_to_float(sf)), wide, fmt);
   return sf;
 }
 
@@ -301,8 +319,8 @@ __device__ __forceinline__ uint32_t quant_row_block(uint8_t* dst, const float* v
 // (lane ^ d), so 16 + 8 + 4 + 2 + 1 shuffles leave lane i with the maximum of column i (a
 // butterfly per column would take 160).  Each lane then derives the scale of its own column
 // once, and 32 broadcasts hand the scales round.
-__device__ __forceinline__ uint32_t quant_col_block(uint8_t* dst, bool do_store, const float* v, float norm_const, bool wide,
-                                                    OutFormat fmt) {
+__device__ __forceinline__ uint32_t quant_col_block(uint8_t* row_base, int64_t col, bool do_store, const float* v, float norm_const,
+                                                    bool wide, OutFormat fmt) {
   const uint32_t lane = lane_id();
   float m16[16], m8[8], m4[4], m2[2];
   {
@@ -349,6 +367,13 @@ __device__ __forceinline__ uint32_t quant_col_block(uint8_t* dst, bool do_store,
   const float sfv = e8m0_to_float(my_sf);
   float my_sc = sfv == 0.0f ? 0.0f : norm_const * rcp_approx(sfv);
   my_sc = fminf(my_sc, 3.40282346638528859812e38f);
+  if (fmt.bits16) {
+    float t[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) t[i] = v[i] * __shfl_sync(0xffffffffu, my_sc, i);
+    if (do_store) store_bf16x32(reinterpret_cast<__nv_bfloat16*>(row_base) + col, t, wide, fmt.f16);
+    return my_sf;
+  }
   uint32_t packed[8];
 #pragma unroll
   for (int i = 0; i < 32; i += 4) {
@@ -358,7 +383,8 @@ __device__ __forceinline__ uint32_t quant_col_block(uint8_t* dst, bool do_store,
     packed[i >> 2] = fp8x4_from_float(s[0], s[1], s[2], s[3], fmt.e5m2);
   }
   if (do_store)
-    store_32B(dst, make_uint4(packed[0], packed[1], packed[2], packed[3]), make_uint4(packed[4], packed[5], packed[6], packed[7]), wide);
+    store_32B(row_base + col, make_uint4(packed[0], packed[1], packed[2], packed[3]), make_uint4(packed[4], packed[5], packed[6], packed[7]),
+              wide);
   return my_sf;
 }
 
@@ -787,7 +813,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     const float norm_const = p.norm_const ? *p.norm_const : 1.0f;
     const bool wide = p.wide_stores != 0;
     const bool c_f16 = p.c_f16 != 0, d_f16 = p.d_f16 != 0;
-    const OutFormat out_fmt = {p.d_rcp_limit, p.d_e5m2 != 0};
+    const OutFormat out_fmt = {p.d_rcp_limit, p.d_e5m2 != 0, p.d_is_fp8 == 0, d_f16};
+    const int64_t d_row_bytes = (int64_t)p.n_out * (p.d_is_fp8 ? 1 : 2);
     uint8_t* const stage_row = smem + C::STAGING_OFF + ew * STAGING_WARP_BYTES + lane * STAGING_ROW_BYTES;  // kBulk only
     const uint32_t overlap_target = kPair ? map_to_cta(overlap_bar, 0) : overlap_bar;
     auto arrive_overlap = [&]() {
@@ -881,15 +908,15 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
               g[j] = ((s * g[j]) * u[j]) * prob;
             }
           }
-          if (!p.d_is_fp8) {
-            if (row_ok) {
+          if (p.amax && row_ok) {
 #pragma unroll
-              for (int j = 0; j < 32; ++j) thread_amax = fmaxf(thread_amax, fabsf(g[j]));
-            }
+            for (int j = 0; j < 32; ++j) thread_amax = fmaxf(thread_amax, fabsf(g[j]));
+          }
+          if (!p.gen_sfd) {
             if (row_ok && out_row >= 0) store_bf16x32(d_rows + (int64_t)out_row * p.n_out + dn, g, wide, d_f16);
           } else {
             if (row_ok) {
-              const uint32_t sf = quant_row_block(reinterpret_cast<uint8_t*>(p.d) + (int64_t)row * p.n_out + dn, g, norm_const, wide, out_fmt);
+              const uint32_t sf = quant_row_block(reinterpret_cast<uint8_t*>(p.d) + (int64_t)row * d_row_bytes, dn, g, norm_const, wide, out_fmt);
               sf_row_word |= sf << (8 * (half * 2 + pp));
             }
             if (p.d_col) {
@@ -898,7 +925,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 #pragma unroll
                 for (int j = 0; j < 32; ++j) g[j] = 0.f;
               }
-              const uint32_t sfc = quant_col_block(p.d_col + (int64_t)row * p.n_out + dn, row_ok, g, norm_const, wide, out_fmt);
+              const uint32_t sfc = quant_col_block(p.d_col + (int64_t)row * d_row_bytes, dn, row_ok, g, norm_const, wide, out_fmt);
               int64_t blk_base = 0;
               int rb = (tile.row0 >> 5) + quarter;
               int rest = p.sfd_col_rest_k;
@@ -913,7 +940,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             }
           }
         }
-        if (p.d_is_fp8 && row_ok && p.sfd_row) {
+        if (p.gen_sfd && row_ok && p.sfd_row) {
           // output columns [128 n_tile + 64 half, +64) = scale blocks 2 half, 2 half + 1 of K group n_tile
           uint8_t* dst = p.sfd_row + sf_offset(row, (int64_t)tile.n_tile * 4 + half * 2, p.sfd_row_rest_k);
           const int blocks_left = (p.n_out - ((n0 >> 1) + half * 64) + 31) / 32;
@@ -954,11 +981,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = (v[j] * alpha) * prob;
           }
-          if (!p.d_is_fp8) {
-            if (row_ok) {
+          if (p.amax && row_ok) {
 #pragma unroll
-              for (int j = 0; j < 32; ++j) thread_amax = fmaxf(thread_amax, fabsf(v[j]));
-            }
+            for (int j = 0; j < 32; ++j) thread_amax = fmaxf(thread_amax, fabsf(v[j]));
+          }
+          if (!p.gen_sfd) {
             if constexpr (kBulk) {
               // this row's 32 columns -> its slot of the staging area (64 bytes)
               uint4* st = reinterpret_cast<uint4*>(stage_row + bb * 64);
@@ -976,7 +1003,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             }
           } else {
             if (row_ok) {
-              const uint32_t sf = quant_row_block(reinterpret_cast<uint8_t*>(p.d) + (int64_t)row * p.n_out + dn, v, norm_const, wide, out_fmt);
+              const uint32_t sf = quant_row_block(reinterpret_cast<uint8_t*>(p.d) + (int64_t)row * d_row_bytes, dn, v, norm_const, wide, out_fmt);
               sf_row_word |= sf << (8 * bb);
             }
             if (p.d_col) {
@@ -984,7 +1011,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 #pragma unroll
                 for (int j = 0; j < 32; ++j) v[j] = 0.f;
               }
-              const uint32_t sfc = quant_col_block(p.d_col + (int64_t)row * p.n_out + dn, row_ok, v, norm_const, wide, out_fmt);
+              const uint32_t sfc = quant_col_block(p.d_col + (int64_t)row * d_row_bytes, dn, row_ok, v, norm_const, wide, out_fmt);
               int64_t blk_base = 0;
               int rb = (tile.row0 >> 5) + quarter;
               int rest = p.sfd_col_rest_k;
@@ -999,7 +1026,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           }
         }
         if constexpr (kBulk) {
-          if (!p.d_is_fp8) {
+          if (!p.gen_sfd) {
             // one asynchronous copy per row: up to 128 columns = 256 contiguous bytes at the destination
             fence_proxy_async_smem();
             const int c0 = n0 + half * 128;
@@ -1009,7 +1036,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             bulk_commit();
           }
         }
-        if (p.d_is_fp8 && row_ok && p.sfd_row) {
+        if (p.gen_sfd && row_ok && p.sfd_row) {
           // output columns [256 n_tile + 128 half, +128) = K group 2 n_tile + half, 4 blocks
           uint8_t* dst = p.sfd_row + sf_offset(row, (int64_t)(tile.n_tile * 2 + half) * 4, p.sfd_row_rest_k);
           const int blocks_left = (p.n_out - (n0 + half * 128) + 31) / 32;
@@ -1021,7 +1048,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         }
       }
 
-      if (p.amax && !p.d_is_fp8) {
+      if (p.amax) {
         float wmax = thread_amax;
 #pragma unroll
         for (int d = 16; d > 0; d >>= 1) wmax = fmaxf(wmax, __shfl_xor_sync(0xffffffffu, wmax, d));
@@ -1262,12 +1289,13 @@ static int run_gemm(int epi, const b200moe_gemm_args* a, void* stream_v) {
     if ((uintptr_t)a->bias % 16 != 0 || a->n % 8 != 0)
       return fail(B200MOE_E_ALIGN, "%s: bias must be 16-byte aligned and n a multiple of 8", op);
   }
-  if (d_fp8) {
-    if (!a->sfd_row || !a->norm_const)
-      return fail(B200MOE_E_NULL, "%s: E4M3 output needs sfd_row and norm_const", op);
-    if ((a->d_col == nullptr) != (a->sfd_col == nullptr))
-      return fail(B200MOE_E_NULL, "%s: d_col and sfd_col go together", op);
-  }
+  // Scale factors are generated when sfd_row and norm_const are given (always for an FP8 D; for a 16-bit
+  // D the reference then stores the scaled values, block maximum mapped to 1, in D's own type)
+  const bool gen_sfd = a->sfd_row != nullptr && a->norm_const != nullptr;
+  if (d_fp8 && !gen_sfd) return fail(B200MOE_E_NULL, "%s: FP8 output needs sfd_row and norm_const", op);
+  if (gen_sfd && ((a->d_col == nullptr) != (a->sfd_col == nullptr)))
+    return fail(B200MOE_E_NULL, "%s: d_col and sfd_col go together", op);
+  if (gen_sfd && a->d_row_map) return fail(B200MOE_E_UNSUPPORTED, "%s: d_row_map cannot be combined with scale-factor generation", op);
   const uintptr_t align_or = (uintptr_t)a->a | (uintptr_t)a->sfa | (uintptr_t)a->b | (uintptr_t)a->sfb | (uintptr_t)a->c |
                              (uintptr_t)a->d | (uintptr_t)a->d_col | (uintptr_t)a->sfd_row | (uintptr_t)a->sfd_col;
   if (align_or & 15) return fail(B200MOE_E_ALIGN, "%s: tensor base addresses must be 16-byte aligned", op);
@@ -1295,7 +1323,8 @@ static int run_gemm(int epi, const b200moe_gemm_args* a, void* stream_v) {
   p.d_peer_slots = a->d_peer_slots;
   p.c = epi == EPI_FC1 ? (__nv_bfloat16*)a->c : nullptr;
   p.d = a->d;
-  p.d_col = d_fp8 ? (uint8_t*)a->d_col : nullptr;
+  p.d_col = gen_sfd ? (uint8_t*)a->d_col : nullptr;
+  p.gen_sfd = gen_sfd ? 1 : 0;
   p.amax = a->amax;
   p.sfd_row = (uint8_t*)a->sfd_row;
   p.sfd_col = (uint8_t*)a->sfd_col;
@@ -1313,7 +1342,7 @@ static int run_gemm(int epi, const b200moe_gemm_args* a, void* stream_v) {
   p.sfd_col_rest_k = ((p.m_rows + 31) / 32 + 3) / 4;
   p.d_is_fp8 = d_fp8;
   p.d_e5m2 = a->d_dtype == B200MOE_DTYPE_E5M2;
-  p.d_rcp_limit = p.d_e5m2 ? 1.0f / 128.0f : 1.0f / 448.0f;
+  p.d_rcp_limit = !d_fp8 ? 1.0f : (p.d_e5m2 ? 1.0f / 128.0f : 1.0f / 448.0f);
   p.d_f16 = a->d_dtype == B200MOE_DTYPE_F16;
   p.c_f16 = a->c_dtype == B200MOE_DTYPE_F16;
   p.discrete_col_sfd = (a->flags & B200MOE_FLAG_DISCRETE_COL_SFD) ? 1 : 0;
@@ -1428,7 +1457,7 @@ static int run_gemm(int epi, const b200moe_gemm_args* a, void* stream_v) {
   const int grid = pair ? 2 * units : units;
 
   // FC2 rows that go to peer buffers leave through shared memory and one bulk copy per row
-  if (epi == EPI_FC2 && !discrete && !d_fp8 && p.d_peer_ptrs && ((uintptr_t)a->d % 16 == 0))
+  if (epi == EPI_FC2 && !discrete && !d_fp8 && !gen_sfd && p.d_peer_ptrs && ((uintptr_t)a->d % 16 == 0))
     return pair ? launch<EPI_FC2, false, true, true>(maps, p, grid, di, stream)
                 : launch<EPI_FC2, false, false, true>(maps, p, grid, di, stream);
   return epi == EPI_FC1 ? dispatch<EPI_FC1>(discrete, pair, maps, p, grid, di, stream)

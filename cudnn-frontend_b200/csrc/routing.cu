@@ -176,8 +176,8 @@ __global__ void __launch_bounds__(128)
                                   const int32_t* __restrict__ local_row, const int32_t* __restrict__ delta,
                                   const float* __restrict__ topk_prob, int64_t num_tokens, int topk, int cols, int rec_pitch,
                                   int experts_per_rank, int num_ranks, int my_rank, int64_t slot_capacity, int64_t row_capacity,
-                                  const int32_t* __restrict__ expert_chunk, int chunk, const int64_t* __restrict__ peer_q,
-                                  const int64_t* __restrict__ peer_rec) {
+                                  const int32_t* __restrict__ row_bounds, int num_chunks, int chunk,
+                                  const int64_t* __restrict__ peer_q, const int64_t* __restrict__ peer_rec) {
   extern __shared__ __align__(16) uint8_t s_dyn[];  // [cols] E4M3 row, then topk records of rec_pitch bytes
   uint8_t* const s_qrow = s_dyn;
   uint8_t* const s_rec = s_dyn + cols;
@@ -197,13 +197,14 @@ __global__ void __launch_bounds__(128)
       int rank = 0;
       if (e >= 0 && e < experts_per_rank * num_ranks) {
         rank = e / experts_per_rank;
-        // with a chunk table this launch moves only the rows of the experts of one chunk
-        if (expert_chunk == nullptr || expert_chunk[e] == chunk) {
-          row = (int64_t)delta[e] + local_row[slot];
-          if (row < 0 || row >= row_capacity) {
-            atomicCAS(&g_device_status, 0, 301);  // never store outside a peer's buffer
-            row = -1;
-          }
+        row = (int64_t)delta[e] + local_row[slot];
+        if (row < 0 || row >= row_capacity) {
+          atomicCAS(&g_device_status, 0, 301);  // never store outside a peer's buffer
+          row = -1;
+        } else if (row_bounds != nullptr) {
+          // this launch moves only the rows that land in chunk `chunk` of their destination rank
+          const int32_t* b = row_bounds + rank * (num_chunks + 1) + chunk;
+          if (row < b[0] || row >= b[1]) row = -1;
         }
       }
       s_row[threadIdx.x] = row;
@@ -435,7 +436,8 @@ int b200moe_dispatch_quantize_peer_chunk(const void* x, const int32_t* expert_id
                                          const float* topk_prob, int64_t num_tokens, int32_t topk, int64_t cols,
                                          int32_t experts_per_rank, int32_t num_ranks, int32_t my_rank, int64_t slot_capacity,
                                          int64_t row_capacity, const int64_t* peer_q, const int64_t* peer_rec,
-                                         const int32_t* expert_chunk, int32_t chunk, int32_t max_blocks, void* stream) {
+                                         const int32_t* row_bounds, int32_t num_chunks, int32_t chunk, int32_t max_blocks,
+                                         void* stream) {
   using namespace b200moe;
   if (num_tokens == 0) return B200MOE_OK;
   if (!x || !expert_ids || !local_row || !delta || !peer_q || !peer_rec)
@@ -447,6 +449,8 @@ int b200moe_dispatch_quantize_peer_chunk(const void* x, const int32_t* expert_id
       (int64_t)num_ranks * slot_capacity > 0x7fffffffll || row_capacity <= 0)
     return fail(B200MOE_E_SHAPE, "dispatch_quantize_peer: bad rank layout or capacities");
   if (max_blocks < 0) return fail(B200MOE_E_SHAPE, "dispatch_quantize_peer: negative block limit");
+  if (row_bounds && (num_chunks <= 0 || chunk < 0 || chunk >= num_chunks))
+    return fail(B200MOE_E_SHAPE, "dispatch_quantize_peer: chunk %d outside [0, %d)", chunk, num_chunks);
   if ((uintptr_t)x & 15) return fail(B200MOE_E_ALIGN, "dispatch_quantize_peer: 16-byte alignment required");
   const int rec_pitch = b200moe_dispatch_record_pitch(cols);
   const size_t smem = (size_t)cols + (size_t)topk * rec_pitch;
@@ -454,7 +458,7 @@ int b200moe_dispatch_quantize_peer_chunk(const void* x, const int32_t* expert_id
   const int64_t blocks = max_blocks > 0 ? std::min<int64_t>(max_blocks, num_tokens) : num_tokens;
   dispatch_quantize_peer_kernel<<<(unsigned)blocks, 128, smem, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)x, expert_ids, local_row, delta, topk_prob, num_tokens, topk, (int)cols, rec_pitch, experts_per_rank,
-      num_ranks, my_rank, slot_capacity, row_capacity, expert_chunk, chunk, peer_q, peer_rec);
+      num_ranks, my_rank, slot_capacity, row_capacity, row_bounds, num_chunks, chunk, peer_q, peer_rec);
   B200_CUDA_CHECK(cudaGetLastError());
   return B200MOE_OK;
 }
@@ -464,7 +468,7 @@ int b200moe_dispatch_quantize_peer(const void* x, const int32_t* expert_ids, con
                                    int32_t experts_per_rank, int32_t num_ranks, int32_t my_rank, int64_t slot_capacity,
                                    int64_t row_capacity, const int64_t* peer_q, const int64_t* peer_rec, void* stream) {
   return b200moe_dispatch_quantize_peer_chunk(x, expert_ids, local_row, delta, topk_prob, num_tokens, topk, cols, experts_per_rank,
-                                              num_ranks, my_rank, slot_capacity, row_capacity, peer_q, peer_rec, nullptr, 0, 0, stream);
+                                              num_ranks, my_rank, slot_capacity, row_capacity, peer_q, peer_rec, nullptr, 0, 0, 0, stream);
 }
 
 int b200moe_copy_segments(int32_t count, const int64_t* dst, const int64_t* src, const int64_t* bytes, void* stream) {

@@ -152,7 +152,6 @@ class DiscreteGroupedGemmSwigluSm100(OperatorBase):
         self._not_implemented_error_if(self.sf_dtype != torch.float8_e8m0fnu, f"only E8M0 scale factors are built, got {self.sf_dtype}")
         self._not_implemented_error_if(self.c is not None and self.c_dtype not in (torch.bfloat16, torch.float16), f"only bf16 and fp16 C are built, got {self.c_dtype}")
         self._not_implemented_error_if(self.d_dtype not in (torch.bfloat16, torch.float16, torch.float8_e4m3fn, torch.float8_e5m2), f"only bf16, fp16, E4M3 and E5M2 D are built, got {self.d_dtype}")
-        self._not_implemented_error_if(self.generate_sfd and self.d_dtype not in (torch.float8_e4m3fn, torch.float8_e5m2), "scale-factor generation with a 16-bit D is not built")
         self._not_implemented_error_if(not self.generate_sfd and self.d_dtype in (torch.float8_e4m3fn, torch.float8_e5m2), "FP8 D needs sfd_row, sfd_col and norm_const")
         self._value_error_if(n % 64 != 0, f"n must be a multiple of 64 (32-column gate / up blocks), got {n}")
         self._value_error_if(self.generate_sfd and self.d_col is None, "sample_d_col is required when scale factors are generated")
@@ -198,6 +197,7 @@ class DiscreteGroupedGemmSwigluSm100(OperatorBase):
         _require_pointer_tensor(b_ptrs, "b_ptrs", self.expert_cnt)
         _require_pointer_tensor(sfb_ptrs, "sfb_ptrs", self.expert_cnt)
         fp8_out = d_tensor.dtype in (torch.float8_e4m3fn, torch.float8_e5m2)
+        gen = bool(getattr(self, "generate_sfd", fp8_out)) and sfd_row_tensor is not None and norm_const_tensor is not None
         ops.grouped_gemm_op(
             "fc1",
             a=a_tensor,
@@ -207,13 +207,13 @@ class DiscreteGroupedGemmSwigluSm100(OperatorBase):
             padded_offsets=padded_offsets,
             alpha=alpha_tensor,
             prob=prob_tensor,
-            norm_const=norm_const_tensor if fp8_out else None,
+            norm_const=norm_const_tensor if gen else None,
             c=c_tensor,
             d=d_tensor,
-            d_col=d_col_tensor if fp8_out and sfd_col_tensor is not None else None,
-            amax=None if fp8_out else amax_tensor,
-            sfd_row=sfd_row_tensor if fp8_out else None,
-            sfd_col=sfd_col_tensor if fp8_out and d_col_tensor is not None else None,
+            d_col=d_col_tensor if gen and sfd_col_tensor is not None else None,
+            amax=None if fp8_out else amax_tensor,  # the reference has no amax for an FP8 D either
+            sfd_row=sfd_row_tensor if gen else None,
+            sfd_col=sfd_col_tensor if gen and d_col_tensor is not None else None,
             workspace=self._workspace,
             n=self._n,
             discrete_col_sfd=self.discrete_col_sfd,
@@ -272,7 +272,9 @@ def discrete_grouped_gemm_swiglu_wrapper_sm100(
     d_col_tensor = torch.empty_strided((valid_m, n_out, 1), (n_out, 1, valid_m * n_out), dtype=d_dtype, device=dev)
     sfd_row_tensor = sfd_col_tensor = amax_tensor = None
     fp8_in = a_tensor.dtype in (torch.float8_e4m3fn, torch.float8_e5m2) and sfa_tensor.dtype in (torch.float8_e8m0fnu, torch.float8_e4m3fn)
-    if fp8_in and d_dtype in (torch.float8_e4m3fn, torch.float8_e5m2):
+    # as in the reference: fp8 inputs get scale-factor outputs whatever d_dtype is (here: whenever a
+    # norm_const is given; a 16-bit d_dtype without one gives the plain D plus amax)
+    if fp8_in and (d_dtype in (torch.float8_e4m3fn, torch.float8_e5m2) or norm_const_tensor is not None):
         sfd_row_tensor = _alloc_sfd(valid_m, n_out, sf_vec_size, sfa_tensor.dtype, dev)
         sfd_col_tensor = _alloc_sfd(n_out, valid_m, sf_vec_size, sfa_tensor.dtype, dev)
     if d_dtype in (torch.bfloat16, torch.float16):

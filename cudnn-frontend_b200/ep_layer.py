@@ -141,27 +141,36 @@ def chunk_weights(chunks: int):
     return [10] * (chunks - 2) + [6, 4]
 
 
-def chunk_of_experts(group_starts: torch.Tensor, rows_per_rank: torch.Tensor, weights) -> torch.Tensor:
-    """Chunk of every expert for a layer that runs each rank's experts in ``len(weights)`` slices whose
-    rows are in the proportion ``weights`` (integers): ``group_starts [G, E_local]`` (first padded row of
-    every expert group on its rank) and ``rows_per_rank [G]`` (padded rows per rank) -> int32
-    ``[G * E_local]``.  Chunk c of rank r begins at row ``rows_r * sum(weights[:c]) // sum(weights)``; an
-    expert belongs to the chunk its first row falls in.  Monotone in the local expert index, so a chunk is a
-    contiguous range of local experts; a chunk is empty when one expert spans several shares.  Integer
-    arithmetic only: every rank computes the same table from the all-gathered histogram, on any device,
-    and the host repeats it with the same numbers."""
+def chunk_row_bounds(rows_per_rank: torch.Tensor, weights) -> torch.Tensor:
+    """Row ranges of the chunks of every rank: ``rows_per_rank [G]`` (padded rows, multiples of 128) ->
+    int64 ``[G, C + 1]`` with ``bounds[r, c] = rows_r * sum(weights[:c]) // sum(weights)`` rounded down to a
+    multiple of 128, ``bounds[r, 0] = 0`` and ``bounds[r, C] = rows_r``.  Chunks cut through expert groups:
+    an expert that holds half of a rank's rows is spread over several chunks.  Integer arithmetic only, so
+    every rank computes the same table from the all-gathered histogram on any device and the host can
+    repeat it with the same numbers."""
     total = int(sum(weights))
     rows = rows_per_rank.to(torch.int64).view(-1, 1)
-    cum = 0
-    c = torch.zeros_like(group_starts, dtype=torch.int64)
-    for w in list(weights)[:-1]:
-        cum += int(w)
-        c += (group_starts.to(torch.int64) >= (rows * cum) // total).to(torch.int64)
-    return c.to(torch.int32).reshape(-1).contiguous()
+    cum = torch.tensor([0] + [int(v) for v in torch.tensor(list(weights)).cumsum(0).tolist()], dtype=torch.int64, device=rows.device).view(1, -1)
+    bounds = ((rows * cum) // total) // 128 * 128
+    bounds[:, -1] = rows.view(-1)
+    return bounds
 
 
-def return_segments(counts_host, padded_ends, rank: int, lo: int, hi: int):
-    """Row blocks that rank ``rank`` returns for its local experts ``lo .. hi - 1``.
+def chunk_offsets(padded_ends: torch.Tensor, bounds_row: torch.Tensor) -> torch.Tensor:
+    """END offsets of one rank's expert groups restricted to each chunk's row range: ``padded_ends
+    [E_local]``, ``bounds_row [C + 1]`` -> int32 ``[C, 1 + E_local]``; row c is ``[first row of chunk c,
+    ends clamped to the chunk's range]``.  A GEMM launch for chunk c takes ``out[c, 1:]`` as its
+    padded_offsets with the flag that the element before the view is the first row: experts before the
+    chunk get no rows, the expert the chunk starts in begins at the chunk's first row."""
+    lo = bounds_row[:-1].to(torch.int64).view(-1, 1)
+    hi = bounds_row[1:].to(torch.int64).view(-1, 1)
+    ends = torch.minimum(torch.maximum(padded_ends.to(torch.int64).view(1, -1), lo), hi)
+    return torch.cat([lo, ends], dim=1).to(torch.int32).contiguous()
+
+
+def return_segments(counts_host, padded_ends, rank: int, row_lo: int, row_hi: int):
+    """Row blocks that rank ``rank`` returns for the rows ``row_lo .. row_hi - 1`` of its expert-grouped
+    buffer.
 
     ``counts_host [G, E]`` (host integers): rows source rank s routes to physical expert e;
     ``padded_ends [E_local]``: END offsets of this rank's expert groups.  The group of local expert j holds
@@ -178,14 +187,19 @@ def return_segments(counts_host, padded_ends, rank: int, lo: int, hi: int):
     starts = np.concatenate([[0], ends[:-1]])
     before = np.cumsum(cnt, axis=0) - cnt
     compact = np.cumsum(cnt, axis=1) - cnt
+    # local experts whose groups touch the row range
+    j_lo = int(np.searchsorted(ends, row_lo, "right"))
+    j_hi = int(np.searchsorted(starts, row_hi, "left"))
     out = []
     for i in range(g):
         s_ = (rank + 1 + i) % g
-        for j in range(lo, hi):
+        for j in range(j_lo, min(j_hi, el)):
             e_glob = rank * el + j
-            rows = int(cnt[s_, e_glob])
-            if rows:
-                out.append((s_, int(compact[s_, e_glob]), int(starts[j]) + int(before[s_, e_glob]), rows))
+            a = int(starts[j]) + int(before[s_, e_glob])  # this source's rows of expert j: [a, b)
+            b = a + int(cnt[s_, e_glob])
+            a2, b2 = max(a, row_lo), min(b, row_hi)
+            if b2 > a2:
+                out.append((s_, int(compact[s_, e_glob]) + (a2 - a), a2, b2 - a2))
     return out
 
 
@@ -545,6 +559,7 @@ class ExpertParallelMoE:
         that the traffic over NVLink hides behind the GEMMs:
 
             plan (as forward_fused_direct: histogram all-gather, one host synchronisation)
+            chunks = row ranges of this rank's expert-grouped buffer (they cut through large expert groups)
             dispatch of chunk 0 (all SMs) -> barrier
             for every chunk c:   FC1(c), FC2(c) on the compute stream (FC2 stores bf16 rows locally, in
                                  expert-grouped order: full-speed stores, no row map)
@@ -600,19 +615,22 @@ class ExpertParallelMoE:
         ev_plan = torch.cuda.Event()
         ev_plan.record(main)
 
-        # chunks of about equal rows on every rank: a table on the device for the dispatch kernel (it covers
-        # every rank's experts), the same numbers on the host for this rank's launches
-        chunks = max(1, min(int(chunks), el))
+        # chunks = row ranges of about equal size on every rank: a table on the device for the dispatch
+        # kernel (it covers every rank), the same numbers on the host for this rank's launches and copies,
+        # and per chunk the expert END offsets clamped to the chunk's rows for the GEMM launches
+        chunks = max(1, int(chunks))
         weights = chunk_weights(chunks)
-        chunk_table = chunk_of_experts(plan.group_starts, plan.m_rows_all, weights)
-        starts = np.concatenate([[0], ends[:-1]])  # first row of my expert groups
-        my_chunk = sum((starts >= (m * int(cw)) // sum(weights)).astype(np.int64) for cw in np.cumsum(weights)[:-1]) if chunks > 1 else np.zeros(el, dtype=np.int64)
-        bounds = [(int(np.searchsorted(my_chunk, c, "left")), int(np.searchsorted(my_chunk, c, "right"))) for c in range(chunks)]
+        bounds_dev = chunk_row_bounds(plan.m_rows_all, weights)
+        bounds_i32 = bounds_dev.to(torch.int32).contiguous()
+        offs_c = chunk_offsets(plan.padded_offsets, bounds_dev[rank])
+        cum = np.concatenate([[0], np.cumsum(weights)])
+        row_bounds = [int(v) for v in ((m * cum) // int(sum(weights))) // 128 * 128]
+        row_bounds[-1] = m
         flat_prob = topk_prob.reshape(t * k).contiguous()
 
         def dispatch(c, max_blocks):
             moe.dispatch_quantize_peer(x, ids, local_row, plan.delta, flat_prob, el, g, rank, slots, cap, bufs["q"].ptrs_dev,
-                                       bufs["rec"].ptrs_dev, expert_chunk=chunk_table, chunk=c, max_blocks=max_blocks)  # fmt: skip
+                                       bufs["rec"].ptrs_dev, row_bounds=bounds_i32, chunk=c, max_blocks=max_blocks)  # fmt: skip
 
         row_bytes = h * 2
         back_ptrs = bufs["back"].ptrs
@@ -635,15 +653,16 @@ class ExpertParallelMoE:
         self._rank_barrier()
         ev_disp = [None] * chunks
         ev_fc2 = [None] * chunks
-        for c, (lo, hi) in enumerate(bounds):
+        for c in range(chunks):
             if c > 0:
                 main.wait_event(ev_disp[c])
-            r0, r1 = (int(starts[lo]), int(ends[hi - 1])) if hi > lo else (0, 0)
+            r0, r1 = row_bounds[c], row_bounds[c + 1]
+            offs = offs_c[c, 1:]  # the element before this view is the chunk's first row
             if r1 > r0:
                 moe.unpack_dispatch_records(bufs["rec"].local[r0 * pitch :], r1 - r0, h, loc["sf"][(r0 // 128) * rest_k * 512 :], loc["prob"][r0:],
                                             loc["map"][r0:])  # fmt: skip
-                fc1.execute(a, self.w1, None, h8, sfa, self.sfw1, plan.padded_offsets, self.alpha, sfd_row_tensor=sfh, norm_const_tensor=self.norm,
-                            expert_range=(lo, hi))  # fmt: skip
+                fc1.execute(a, self.w1, None, h8, sfa, self.sfw1, offs, self.alpha, sfd_row_tensor=sfh, norm_const_tensor=self.norm,
+                            offsets_have_prev=True)  # fmt: skip
             if c + 1 < chunks:
                 # the next chunk's rows travel while this chunk computes
                 with torch.cuda.stream(streams["disp"]):
@@ -654,16 +673,15 @@ class ExpertParallelMoE:
                     ev_disp[c + 1] = torch.cuda.Event()
                     ev_disp[c + 1].record(streams["disp"])
             if r1 > r0:
-                fc2.execute(h8, sfh, plan.padded_offsets, self.alpha, y, b_tensor=self.w2, sfb_tensor=self.sfw2, prob_tensor=prob3,
-                            expert_range=(lo, hi))  # fmt: skip
+                fc2.execute(h8, sfh, offs, self.alpha, y, b_tensor=self.w2, sfb_tensor=self.sfw2, prob_tensor=prob3, offsets_have_prev=True)
             ev_fc2[c] = torch.cuda.Event()
             ev_fc2[c].record(main)
-            # return of this chunk's result rows: one copy per (expert, source rank), destinations rotated
-            # so that the ranks do not all send to the same one at the same time
-            if y is not None:
+            # return of this chunk's result rows: one copy per (expert, source rank) block inside the chunk,
+            # destinations rotated so that the ranks do not all send to the same one at the same time
+            if y is not None and r1 > r0:
                 y_ptr = y.data_ptr()
                 seg = [[], []]
-                for s_, dst_row, src_row, n_rows in return_segments(cnt, ends, rank, lo, hi):
+                for s_, dst_row, src_row, n_rows in return_segments(cnt, ends, rank, r0, r1):
                     seg[s_ % 2].append((back_ptrs[s_] + dst_row * row_bytes, y_ptr + src_row * row_bytes, n_rows * row_bytes))
                 for cs, lane_ in zip(streams["copy"], seg):
                     if lane_:

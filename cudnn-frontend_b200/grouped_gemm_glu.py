@@ -197,10 +197,10 @@ def grouped_gemm_glu_wrapper_sm100(
     d_col_tensor = torch.empty_strided((valid_m, n_out, 1), (n_out, 1, valid_m * n_out), dtype=d_dtype, device=dev)
     sfd_row_tensor = sfd_col_tensor = amax_tensor = None
     fp8_in = a_tensor.dtype in (torch.float8_e4m3fn, torch.float8_e5m2)
-    if fp8_in and d_dtype in (torch.float8_e4m3fn, torch.float8_e5m2):
+    if fp8_in and (d_dtype in (torch.float8_e4m3fn, torch.float8_e5m2) or norm_const_tensor is not None):
         sfd_row_tensor = _alloc_sfd(valid_m, n_out, sf_vec_size, sfa_tensor.dtype, dev)
         sfd_col_tensor = _alloc_sfd(n_out, valid_m, sf_vec_size, sfa_tensor.dtype, dev)
-    elif d_dtype in (torch.bfloat16, torch.float16):
+    if d_dtype in (torch.bfloat16, torch.float16):
         amax_tensor = torch.full((l, 1), float("-inf"), dtype=torch.float32, device=dev)
     out = TupleDict(c_tensor=c_tensor, d_tensor=d_tensor, d_col_tensor=d_col_tensor, amax_tensor=amax_tensor,
                     sfd_row_tensor=sfd_row_tensor, sfd_col_tensor=sfd_col_tensor)  # fmt: skip

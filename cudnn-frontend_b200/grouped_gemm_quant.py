@@ -213,7 +213,6 @@ class GroupedGemmQuantSm100(OperatorBase):
         self._not_implemented_error_if(self.ab_dtype not in (torch.float8_e4m3fn, torch.float8_e5m2), f"only MXFP8 (E4M3 or E5M2) inputs are built, got {self.ab_dtype}")
         self._not_implemented_error_if(self.sf_dtype != torch.float8_e8m0fnu, f"only E8M0 scale factors are built, got {self.sf_dtype}")
         self._not_implemented_error_if(self.d_dtype not in (torch.bfloat16, torch.float16, torch.float8_e4m3fn, torch.float8_e5m2), f"only bf16, fp16, E4M3 and E5M2 D are built, got {self.d_dtype}")
-        self._not_implemented_error_if(self.generate_sfd and self.d_dtype not in (torch.float8_e4m3fn, torch.float8_e5m2), "scale-factor generation with a 16-bit D is not built")
         self._not_implemented_error_if(not self.generate_sfd and self.d_dtype in (torch.float8_e4m3fn, torch.float8_e5m2), "FP8 D needs sfd_row, sfd_col and norm_const")
         self._value_error_if(n % 32 != 0, f"n must be a multiple of 32, got {n}")
         self._n, self._k = n, k
@@ -256,6 +255,7 @@ class GroupedGemmQuantSm100(OperatorBase):
         d_peer_ptrs: Optional[torch.Tensor] = None,
         d_peer_slots: int = 0,
         expert_range: Optional[Tuple[int, int]] = None,
+        offsets_have_prev: bool = False,
     ) -> None:
         """Launch on ``current_stream``; allocates nothing.  ``d_row_map`` (int32 ``[M]``, not in the
         reference) stores row ``r`` of a bf16 result at row ``d_row_map[r]`` of ``d_tensor`` (negative:
@@ -263,7 +263,9 @@ class GroupedGemmQuantSm100(OperatorBase):
         ``d_peer_ptrs`` (int64 device tensor of G buffer addresses, each ``[d_peer_slots, N]`` bf16) a map
         value ``v`` addresses row ``v % d_peer_slots`` of rank ``v // d_peer_slots``'s buffer: the epilogue
         stores over NVLink into the ranks the rows came from.  ``expert_range = (lo, hi)`` (not in the
-        reference) computes experts ``lo .. hi - 1`` only, on the same full tensors."""
+        reference) computes experts ``lo .. hi - 1`` only, on the same full tensors; ``offsets_have_prev`` (not in the
+        reference either) says that ``padded_offsets`` is a view one element into a longer array whose element
+        before it is the first row of expert 0."""
         self._ensure_compiled()
         tensor_m, k = a_tensor.shape[0], a_tensor.shape[1]
         if tensor_m == 0:
@@ -280,6 +282,7 @@ class GroupedGemmQuantSm100(OperatorBase):
         if prob_tensor is None:
             raise ValueError("prob_tensor is required")
         fp8_out = d_tensor.dtype in (torch.float8_e4m3fn, torch.float8_e5m2)
+        gen = bool(getattr(self, "generate_sfd", fp8_out)) and sfd_row_tensor is not None and norm_const_tensor is not None
         ops.grouped_gemm_op(
             "fc2",
             a=a_tensor,
@@ -291,12 +294,12 @@ class GroupedGemmQuantSm100(OperatorBase):
             padded_offsets=padded_offsets,
             alpha=alpha_tensor,
             prob=prob_tensor,
-            norm_const=norm_const_tensor if fp8_out else None,
+            norm_const=norm_const_tensor if gen else None,
             d=d_tensor,
-            d_col=d_col_tensor if fp8_out and sfd_col_tensor is not None else None,
-            amax=None if fp8_out else amax_tensor,
-            sfd_row=sfd_row_tensor if fp8_out else None,
-            sfd_col=sfd_col_tensor if fp8_out and d_col_tensor is not None else None,
+            d_col=d_col_tensor if gen and sfd_col_tensor is not None else None,
+            amax=None if fp8_out else amax_tensor,  # the reference has no amax for an FP8 D either
+            sfd_row=sfd_row_tensor if gen else None,
+            sfd_col=sfd_col_tensor if gen and d_col_tensor is not None else None,
             workspace=self._workspace,
             n=self._n,
             discrete_col_sfd=self.discrete_col_sfd,
@@ -310,6 +313,7 @@ class GroupedGemmQuantSm100(OperatorBase):
             dynamic_sched=bool(self.use_dynamic_sched),
             b_nmajor=self._b_nmajor,
             expert_range=expert_range,
+            offsets_have_prev=offsets_have_prev,
         )
 
 

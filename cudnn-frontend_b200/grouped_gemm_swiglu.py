@@ -177,7 +177,6 @@ class GroupedGemmSwigluSm100(OperatorBase):
         self._not_implemented_error_if(self.sf_dtype != torch.float8_e8m0fnu, f"only E8M0 scale factors are built, got {self.sf_dtype}")
         self._not_implemented_error_if(self.c is not None and self.c_dtype not in (torch.bfloat16, torch.float16), f"only bf16 and fp16 C are built, got {self.c_dtype}")
         self._not_implemented_error_if(self.d_dtype not in (torch.bfloat16, torch.float16, torch.float8_e4m3fn, torch.float8_e5m2), f"only bf16, fp16, E4M3 and E5M2 D are built, got {self.d_dtype}")
-        self._not_implemented_error_if(self.generate_sfd and self.d_dtype not in (torch.float8_e4m3fn, torch.float8_e5m2), "scale-factor generation with a 16-bit D is not built; drop sfd_row / sfd_col / norm_const to get bf16 D with amax")
         self._not_implemented_error_if(not self.generate_sfd and self.d_dtype in (torch.float8_e4m3fn, torch.float8_e5m2), "FP8 D needs sfd_row, sfd_col and norm_const")
         self._value_error_if(n % 64 != 0, f"n must be a multiple of 64 (32-column gate / up blocks), got {n}")
         self._value_error_if(self.generate_sfd and self.d_col is None, "sample_d_col is required when scale factors are generated")
@@ -219,10 +218,13 @@ class GroupedGemmSwigluSm100(OperatorBase):
         current_stream=None,
         bias_tensor: Optional[torch.Tensor] = None,
         expert_range: Optional[Tuple[int, int]] = None,
+        offsets_have_prev: bool = False,
     ) -> None:
         """Launch on ``current_stream`` (``None`` = torch's current stream).  Allocates nothing and
         does not synchronise; ``amax_tensor`` is only ever raised (atomic max).  ``expert_range = (lo, hi)``
-        (not in the reference) computes experts ``lo .. hi - 1`` only, on the same full tensors."""
+        (not in the reference) computes experts ``lo .. hi - 1`` only, on the same full tensors; ``offsets_have_prev`` (not in the
+        reference either) says that ``padded_offsets`` is a view one element into a longer array whose element
+        before it is the first row of expert 0."""
         self._ensure_compiled()
         tensor_m, k = a_tensor.shape[0], a_tensor.shape[1]
         if tensor_m == 0:
@@ -231,6 +233,7 @@ class GroupedGemmSwigluSm100(OperatorBase):
             raise ValueError("bias fusion is fixed at construction: pass bias_tensor exactly when sample_bias was given")
         n, l = b_tensor.shape[0], b_tensor.shape[2]
         fp8_out = d_tensor.dtype in (torch.float8_e4m3fn, torch.float8_e5m2)
+        gen = bool(getattr(self, "generate_sfd", fp8_out)) and sfd_row_tensor is not None and norm_const_tensor is not None
         ops.grouped_gemm_op(
             "fc1",
             a=a_tensor,
@@ -240,13 +243,13 @@ class GroupedGemmSwigluSm100(OperatorBase):
             padded_offsets=padded_offsets,
             alpha=alpha_tensor,
             prob=prob_tensor,
-            norm_const=norm_const_tensor if fp8_out else None,
+            norm_const=norm_const_tensor if gen else None,
             c=c_tensor,
             d=d_tensor,
-            d_col=d_col_tensor if fp8_out and sfd_col_tensor is not None else None,
-            amax=None if fp8_out else amax_tensor,
-            sfd_row=sfd_row_tensor if fp8_out else None,
-            sfd_col=sfd_col_tensor if fp8_out and d_col_tensor is not None else None,
+            d_col=d_col_tensor if gen and sfd_col_tensor is not None else None,
+            amax=None if fp8_out else amax_tensor,  # the reference has no amax for an FP8 D either
+            sfd_row=sfd_row_tensor if gen else None,
+            sfd_col=sfd_col_tensor if gen and d_col_tensor is not None else None,
             n=n,
             discrete_col_sfd=self.discrete_col_sfd,
             sm_margin=self.num_cluster_overlap_margin,
@@ -257,6 +260,7 @@ class GroupedGemmSwigluSm100(OperatorBase):
             workspace=self._workspace,
             dynamic_sched=bool(self.use_dynamic_sched),
             expert_range=expert_range,
+            offsets_have_prev=offsets_have_prev,
         )
 
 
@@ -292,9 +296,11 @@ def grouped_gemm_swiglu_wrapper_sm100(
 ) -> TupleDict:
     """One-shot FC1: allocates the outputs, reuses a cached operator object per configuration and
     launches.  Returns ``TupleDict(c_tensor, d_tensor, d_col_tensor, amax_tensor, sfd_row_tensor,
-    sfd_col_tensor)``.  Scale-factor outputs are allocated when D is fp8 (the reference allocates
-    them for every fp8 input, which makes a 16-bit D unreachable through its wrapper; here a
-    16-bit ``d_dtype`` gives plain bf16 D plus amax).  As in the reference, the amax buffer of a
+    sfd_col_tensor)``.  As in the reference (api.py:880-911), fp8 inputs get row and column scale-factor
+    outputs whatever ``d_dtype`` is: with a 16-bit ``d_dtype`` D and D_col then hold the scaled values
+    (block maximum mapped to 1) in that type, and amax is produced too.  The reference demands
+    ``norm_const_tensor`` in that case; here a 16-bit ``d_dtype`` without ``norm_const_tensor`` gives the
+    plain bf16 / fp16 D plus amax instead of an error.  As in the reference, the amax buffer of a
     cached configuration is reused across calls: it holds a running maximum until the caller
     resets it."""
     valid_m, k, _ = a_tensor.shape
@@ -308,7 +314,7 @@ def grouped_gemm_swiglu_wrapper_sm100(
     d_col_tensor = torch.empty_strided((valid_m, n_out, 1), (n_out, 1, valid_m * n_out), dtype=d_dtype, device=dev)
     sfd_row_tensor = sfd_col_tensor = amax_tensor = None
     fp8_in = a_tensor.dtype in (torch.float8_e4m3fn, torch.float8_e5m2) and sfa_tensor.dtype in (torch.float8_e8m0fnu, torch.float8_e4m3fn)
-    if fp8_in and d_dtype in (torch.float8_e4m3fn, torch.float8_e5m2):
+    if fp8_in and (d_dtype in (torch.float8_e4m3fn, torch.float8_e5m2) or norm_const_tensor is not None):
         sfd_row_tensor = _alloc_sfd(valid_m, n_out, sf_vec_size, sfa_tensor.dtype, dev)
         sfd_col_tensor = _alloc_sfd(n_out, valid_m, sf_vec_size, sfa_tensor.dtype, dev)
     if valid_m == 0:

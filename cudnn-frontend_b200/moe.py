@@ -133,20 +133,23 @@ def dispatch_record_pitch(cols: int) -> int:
 def dispatch_quantize_peer(x: torch.Tensor, topk_ids: torch.Tensor, local_row: torch.Tensor, delta: torch.Tensor,
                            topk_prob: Optional[torch.Tensor], experts_per_rank: int, num_ranks: int, my_rank: int,
                            slot_capacity: int, row_capacity: int, peer_q: torch.Tensor, peer_rec: torch.Tensor, stream=None,
-                           expert_chunk: Optional[torch.Tensor] = None, chunk: int = 0, max_blocks: int = 0) -> None:  # fmt: skip
+                           row_bounds: Optional[torch.Tensor] = None, chunk: int = 0, max_blocks: int = 0) -> None:  # fmt: skip
     """Fused quantise + dispatch over peer memory: token rows of ``x [T, H]`` are quantised to MXFP8 and
     stored straight into the expert-grouped GEMM operand of the rank that owns each slot's expert,
     each with a record of its scales, gate probability and return address
     (see ``b200moe_dispatch_quantize_peer`` in include/b200moe.h).  ``peer_*`` are int64 device tensors
-    of ``num_ranks`` base addresses.  With ``expert_chunk`` (int32 ``[E]``, the chunk of every expert) only
-    the slots of the experts of chunk ``chunk`` are moved; ``max_blocks`` bounds the grid for a launch that
-    runs beside a GEMM."""
+    of ``num_ranks`` base addresses.  With ``row_bounds`` (int32 ``[num_ranks, C + 1]``: first row of every
+    chunk on every rank, the rank's row count last) only the slots whose destination row lies in chunk
+    ``chunk`` of its rank are moved; ``max_blocks`` bounds the grid for a launch that runs beside a GEMM."""
     if x.dtype != torch.bfloat16 or not x.is_contiguous():
         raise ValueError("x must be a contiguous bf16 tensor")
     t, h = x.shape
     k = topk_ids.shape[1]
-    if expert_chunk is not None and (expert_chunk.dtype != torch.int32 or not expert_chunk.is_contiguous()):
-        raise ValueError("expert_chunk must be a contiguous int32 tensor")
+    num_chunks = 0
+    if row_bounds is not None:
+        if row_bounds.dtype != torch.int32 or not row_bounds.is_contiguous() or row_bounds.dim() != 2 or row_bounds.shape[0] != num_ranks:
+            raise ValueError("row_bounds must be a contiguous int32 tensor [num_ranks, chunks + 1]")
+        num_chunks = row_bounds.shape[1] - 1
     for name, ten in (("topk_ids", topk_ids), ("local_row", local_row), ("delta", delta)):
         if ten.dtype != torch.int32 or not ten.is_contiguous():
             raise ValueError(f"{name} must be a contiguous int32 tensor")
@@ -154,7 +157,7 @@ def dispatch_quantize_peer(x: torch.Tensor, topk_ids: torch.Tensor, local_row: t
         rc = _lib.load().b200moe_dispatch_quantize_peer_chunk(
             x.data_ptr(), topk_ids.data_ptr(), local_row.data_ptr(), delta.data_ptr(),
             None if topk_prob is None else topk_prob.data_ptr(), t, k, h, experts_per_rank, num_ranks, my_rank, slot_capacity,
-            row_capacity, peer_q.data_ptr(), peer_rec.data_ptr(), None if expert_chunk is None else expert_chunk.data_ptr(), int(chunk),
+            row_capacity, peer_q.data_ptr(), peer_rec.data_ptr(), None if row_bounds is None else row_bounds.data_ptr(), num_chunks, int(chunk),
             int(max_blocks), _stream_ptr(stream))  # fmt: skip
     _lib.check(rc)
 

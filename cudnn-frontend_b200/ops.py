@@ -127,6 +127,7 @@ def launch_grouped_gemm(
     light_m_tiles: Optional[int] = None,
     test_skip_b_loads: bool = False,
     stream_m_tiles: Optional[int] = None,
+    offsets_have_prev: bool = False,
 ) -> None:
     """Fill the C struct and call b200moe_fc1_swiglu / b200moe_fc2_quant.
 
@@ -143,7 +144,9 @@ def launch_grouped_gemm(
     library's default or ``B200MOE_LIGHT_M_TILES``, ``-1`` = experts in order); ``stream_m_tiles``: weight tiles of
     experts with at most that many row tiles are read with an evict-first L2 hint (``None`` = default or
     ``B200MOE_STREAM_M_TILES``, ``-1`` = no hints).  ``wait_limit_ms`` and
-    ``test_skip_b_loads`` drive the bounded-wait test hook."""
+    ``test_skip_b_loads`` drive the bounded-wait test hook.  ``offsets_have_prev``: ``padded_offsets`` is a view that
+    starts one element into a longer int32 array whose element before it is the first row of expert 0 (a
+    layer that runs row ranges of its expert groups passes clamped offsets this way)."""
     _require_cuda(a, sfa, padded_offsets, alpha, d, b, sfb, b_ptrs, sfb_ptrs, prob, norm_const, c, d_col, amax, sfd_row, sfd_col)
     args = _lib.GemmArgs()
     args.a, args.sfa = _ptr(a), _ptr(sfa)
@@ -176,6 +179,9 @@ def launch_grouped_gemm(
             args.sfb_ptrs = sfb_ptrs.data_ptr() + 8 * lo
         if lo > 0:
             extra_flags |= _lib.FLAG_OFFSETS_HAVE_PREV
+    if offsets_have_prev:
+        # padded_offsets is a view one element into a longer array: the element before it is the first row
+        extra_flags |= _lib.FLAG_OFFSETS_HAVE_PREV
     if dynamic_sched:
         extra_flags |= _lib.FLAG_DYNAMIC_SCHED
     if b_nmajor:
@@ -337,6 +343,7 @@ def grouped_gemm_op(kind: str, *, stream=None, **kw) -> None:
             dynamic_sched=bool(kw.get("dynamic_sched", False)), b_nmajor=bool(kw.get("b_nmajor", False)),
             expert_range=kw.get("expert_range"), wait_limit_ms=int(kw.get("wait_limit_ms", 0)), light_m_tiles=kw.get("light_m_tiles"),
             test_skip_b_loads=bool(kw.get("test_skip_b_loads", False)), stream_m_tiles=kw.get("stream_m_tiles"),
+            offsets_have_prev=bool(kw.get("offsets_have_prev", False)),
         )  # fmt: skip
         return
     ctx = torch.cuda.stream(stream) if isinstance(stream, torch.cuda.Stream) else None
@@ -344,7 +351,7 @@ def grouped_gemm_op(kind: str, *, stream=None, **kw) -> None:
         ctx = torch.cuda.stream(torch.cuda.ExternalStream(int(stream)))
     common = (kw["a"], kw["sfa"], kw.get("b"), kw.get("sfb"), kw.get("b_ptrs"), kw.get("sfb_ptrs"), kw["padded_offsets"],
               kw["alpha"], kw.get("prob"), kw.get("norm_const"))  # fmt: skip
-    if kw.get("expert_range") is not None or kw.get("test_skip_b_loads"):
+    if kw.get("expert_range") is not None or kw.get("test_skip_b_loads") or kw.get("offsets_have_prev"):
         raise NotImplementedError("expert_range and the test hook are eager-only launch options")
     tail = (kw["n"], bool(kw.get("discrete_col_sfd", False)), int(kw.get("sm_margin", 0)), kw.get("tile_mode") or "")
     sched = (bool(kw.get("dynamic_sched", False)), bool(kw.get("b_nmajor", False)))

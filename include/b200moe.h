@@ -287,17 +287,19 @@ int b200moe_dispatch_quantize_peer(const void* x, const int32_t* expert_ids, con
                                    int32_t num_ranks, int32_t my_rank, int64_t slot_capacity,
                                    int64_t row_capacity, const int64_t* peer_q,
                                    const int64_t* peer_rec, void* stream);
-/* as above for the experts of one chunk only: expert_chunk [E] int32 (device) names the chunk of every
-   expert, and only slots whose expert has expert_chunk[e] == chunk are moved (NULL = all experts).  A
-   layer that runs its experts in chunks dispatches chunk by chunk.  max_blocks > 0 bounds the grid (the
-   blocks then walk the tokens), so that the kernel can run beside a GEMM that owns most SMs. */
+/* as above for one chunk of the destination rows only: row_bounds [num_ranks][num_chunks + 1] int32
+   (device) holds, for every rank, the first row of each of its chunks (and its row count at the end);
+   only slots whose destination row r on rank d has row_bounds[d][chunk] <= r < row_bounds[d][chunk + 1]
+   are moved (NULL = all rows).  A layer that runs its rows in chunks dispatches chunk by chunk.
+   max_blocks > 0 bounds the grid (the blocks then walk the tokens), so that the kernel can run beside a
+   GEMM that owns most SMs. */
 int b200moe_dispatch_quantize_peer_chunk(const void* x, const int32_t* expert_ids, const int32_t* local_row,
                                          const int32_t* delta, const float* topk_prob, int64_t num_tokens,
                                          int32_t topk, int64_t cols, int32_t experts_per_rank,
                                          int32_t num_ranks, int32_t my_rank, int64_t slot_capacity,
                                          int64_t row_capacity, const int64_t* peer_q,
-                                         const int64_t* peer_rec, const int32_t* expert_chunk,
-                                         int32_t chunk, int32_t max_blocks, void* stream);
+                                         const int64_t* peer_rec, const int32_t* row_bounds,
+                                         int32_t num_chunks, int32_t chunk, int32_t max_blocks, void* stream);
 int b200moe_dispatch_record_pitch(int64_t cols);
 /* count asynchronous device-to-device copies on one stream: segment i moves bytes[i] bytes from
    address src[i] to address dst[i] (HOST arrays of device addresses; peer-mapped buffers included).

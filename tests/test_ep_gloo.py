@@ -251,40 +251,47 @@ def test_rebalance_moves_every_expert_to_its_new_slot_world_size_2():
 
 
 def test_return_segments_put_every_row_where_its_source_expects_it():
-    """The chunked peer path returns result rows as contiguous blocks, one per (expert, source rank).
-    Emulated on the host for 4 ranks: every rank labels the rows of its expert groups with (source, expert,
-    index), applies its segments to the sources' result buffers chunk by chunk, and every source must find
-    its rows in its own expert-sorted order."""
-    from cudnn_frontend_b200.ep_layer import return_segments
+    """The chunked peer path returns result rows as contiguous blocks, one per (expert, source rank) and
+    chunk.  Emulated on the host for 4 ranks: every rank labels the rows of its expert groups with (source,
+    expert, index), applies its segments to the sources' result buffers chunk by chunk (row ranges that cut
+    through expert groups), and every source must find its rows in its own expert-sorted order."""
+    from cudnn_frontend_b200.ep_layer import chunk_row_bounds, chunk_weights, return_segments
 
     g, e, m_aligned = 4, 12, 128
     el = e // g
     rng = np.random.default_rng(3)
-    cnt = rng.integers(0, 40, (g, e))
+    cnt = rng.integers(0, 400, (g, e))
     cnt[:, 5] = 0  # an expert nobody routes to
     cnt[2, :] = 0  # a rank without tokens
+    cnt[0, 1] = 3000  # one expert holds most rows of its rank: chunks must cut through it
     total = cnt.sum(0)
     padded = (total + m_aligned - 1) // m_aligned * m_aligned
     back = [np.full((int(cnt[s].sum()), 3), -1, dtype=np.int64) for s in range(g)]
+    rows_per_rank = torch.tensor([int(padded[r * el : (r + 1) * el].sum()) for r in range(g)])
+    bounds = chunk_row_bounds(rows_per_rank, chunk_weights(5)).numpy()
     for rank in range(g):
         ends = np.cumsum(padded[rank * el : (rank + 1) * el])
         starts = np.concatenate([[0], ends[:-1]])
         y = np.full((int(ends[-1]), 3), -1, dtype=np.int64)
-        for j in range(el):
-            eg = rank * el + j
-            row = int(starts[j])
+        for j_ in range(el):
+            eg = rank * el + j_
+            row = int(starts[j_])
             for s in range(g):
-                for i in range(int(cnt[s, eg])):
-                    y[row] = (s, eg, i)
+                for i_ in range(int(cnt[s, eg])):
+                    y[row] = (s, eg, i_)
                     row += 1
-        seen = set()
-        for lo, hi in ((0, 1), (1, 3)):  # two chunks
-            for s, dst_row, src_row, rows in return_segments(cnt, ends, rank, lo, hi):
-                assert (s, dst_row) not in seen
-                seen.add((s, dst_row))
+        b = bounds[rank]
+        assert b[0] == 0 and b[-1] == ends[-1] and (np.diff(b) >= 0).all() and (b % 128 == 0).all()
+        written = 0
+        for c in range(len(b) - 1):
+            for s, dst_row, src_row, rows in return_segments(cnt, ends, rank, int(b[c]), int(b[c + 1])):
+                assert b[c] <= src_row and src_row + rows <= b[c + 1]
+                assert (back[s][dst_row : dst_row + rows] == -1).all()  # nothing is written twice
                 back[s][dst_row : dst_row + rows] = y[src_row : src_row + rows]
+                written += rows
+        assert written == int(total[rank * el : (rank + 1) * el].sum())
     for s in range(g):
-        expect = [(s, eg, i) for eg in range(e) for i in range(int(cnt[s, eg]))]
+        expect = [(s, eg, i_) for eg in range(e) for i_ in range(int(cnt[s, eg]))]
         assert back[s].tolist() == [list(v) for v in expect]
 
 
@@ -338,22 +345,36 @@ def test_peer_buffers_are_freed_only_after_every_rank_unmapped_them():
     assert last_unmap < first_free, events
 
 
-def test_chunk_table_is_monotone_and_matches_its_host_restatement():
-    """The chunk of every expert (device table for the dispatch kernel, all ranks) against the host
-    arithmetic one rank uses for its own launches; chunks are contiguous ranges of local experts."""
-    from cudnn_frontend_b200.ep_layer import chunk_of_experts, chunk_weights
+def test_chunk_offsets_restrict_every_expert_group_to_the_chunk():
+    """Per chunk, the expert END offsets clamped to the chunk's row range (what a GEMM launch of the chunk
+    gets): over all chunks every row of every group is covered exactly once, and the host's restatement of
+    the bounds agrees with the device table."""
+    from cudnn_frontend_b200.ep_layer import chunk_offsets, chunk_row_bounds, chunk_weights
 
-    g, el = 4, 16
-    gen = torch.Generator().manual_seed(0)
-    padded = torch.randint(0, 5, (g, el), generator=gen) * 128
-    padded[2] = 0  # a rank without rows
+    gen = torch.Generator().manual_seed(1)
+    padded = torch.randint(0, 6, (3, 10), generator=gen) * 128
+    padded[1, 2] = 128 * 40  # a group larger than any chunk
+    padded[2] = 0
     ends = torch.cumsum(padded, 1)
-    starts, rows = ends - padded, ends[:, -1]
-    for chunks in (1, 2, 4, 5, 16):
+    rows = ends[:, -1]
+    for chunks in (1, 2, 5, 7):
         w = chunk_weights(chunks)
-        assert len(w) == chunks
-        table = chunk_of_experts(starts, rows, w).view(g, el).numpy()
-        for r in range(g):
-            m, st = int(rows[r]), starts[r].numpy()
-            host = sum((st >= (m * int(cw)) // sum(w)).astype(np.int64) for cw in np.cumsum(w)[:-1]) if chunks > 1 else np.zeros(el, dtype=np.int64)
-            assert (table[r] == host).all() and (np.diff(table[r]) >= 0).all() and table[r].max() < chunks
+        bounds = chunk_row_bounds(rows, w)
+        for r in range(3):
+            m = int(rows[r])
+            cum = np.concatenate([[0], np.cumsum(w)])
+            host = ((m * cum) // int(sum(w))) // 128 * 128
+            host[-1] = m
+            assert bounds[r].tolist() == host.tolist()
+            offs = chunk_offsets(ends[r], bounds[r]).numpy()
+            assert offs.shape == (chunks, 11)
+            covered = np.zeros(m, dtype=np.int64)
+            starts_full = np.concatenate([[0], ends[r].numpy()[:-1]])
+            for c in range(chunks):
+                assert offs[c, 0] == bounds[r, c] and (np.diff(offs[c]) >= 0).all() and offs[c, -1] <= bounds[r, c + 1]
+                for j_ in range(10):
+                    lo, hi = int(offs[c, j_]), int(offs[c, j_ + 1])
+                    if hi > lo:
+                        assert lo >= starts_full[j_] and hi <= int(ends[r, j_])  # rows of group j only
+                        covered[lo:hi] += 1
+            assert (covered == 1).all()

@@ -301,6 +301,65 @@ def test_mxfp8_requantised_output(kind, groups, n, k, norm, tile_mode):
 
 
 @pytest.mark.parametrize("kind", ["fc1", "fc2"])
+def test_scale_factor_generation_with_a_bf16_d(kind, tile_mode):
+    """The reference generates scale factors for a 16-bit D as well (its FC1 wrapper always does for fp8
+    inputs, grouped_gemm_swiglu/api.py:880-911): the block maximum maps to 1 (get_dtype_rcp_limits), D and
+    D_col hold the scaled values in bf16, row and column E8M0 factors are written, and amax is produced on
+    the unscaled values."""
+    cf = _api()
+    from cudnn_frontend_b200 import ops
+
+    dev = "cuda"
+    groups, n, k, norm = [256, 100, 0, 384], 512, 256, 0.5
+    e = len(groups)
+    valid, aligned, offs = orc.padded_end_offsets(groups, 128)
+    a, b, sfa, sfb = H.gen_operands(91, valid, n, k, e)
+    H.zero_padding_rows(a, groups, aligned)
+    rng = np.random.default_rng(91)
+    alpha = np.ones(e, dtype=np.float32)
+    prob = rng.uniform(0.1, 1.0, valid).astype(np.float32)
+    n_out = n // 2 if kind == "fc1" else n
+    ref = (orc.fc1_reference if kind == "fc1" else orc.fc2_reference)(a, sfa, b, sfb, offs, alpha, prob, norm_const=norm, d_dtype="bf16")
+    ta, tb = H.dev_fp8(a).view(valid, k, 1), H.dev_fp8(b).permute(1, 2, 0)
+    tsfa, tsfb = H.dev_sf(sfa, valid, k), H.dev_sf(sfb, n, k, e)
+    toffs, talpha = torch.from_numpy(offs).to(dev), torch.from_numpy(alpha).to(dev)
+    tprob = torch.from_numpy(prob).to(dev).view(valid, 1, 1)
+    tnorm = torch.tensor([norm], device=dev)
+    d = torch.zeros((valid, n_out, 1), dtype=torch.bfloat16, device=dev)
+    d_col = torch.zeros((valid, n_out, 1), dtype=torch.bfloat16, device=dev)
+    amax = torch.full((e, 1), float("-inf"), device=dev)
+    sfd_row, sfd_col = ops.empty_sf(valid, n_out, 1, zero=True), ops.empty_sf(n_out, valid, 1, zero=True)
+    if kind == "fc1":
+        op = cf.GroupedGemmSwigluSm100(ta, tb, None, d, tsfa, tsfb, toffs, talpha, d_col, sample_sfd_row=sfd_row, sample_sfd_col=sfd_col,
+                                       sample_amax=amax, sample_norm_const=tnorm, sample_prob=tprob, sf_vec_size=32, m_aligned=128)  # fmt: skip
+        assert op.check_support()
+        op.compile()
+        op.execute(ta, tb, None, d, tsfa, tsfb, toffs, talpha, d_col_tensor=d_col, sfd_row_tensor=sfd_row, sfd_col_tensor=sfd_col,
+                   amax_tensor=amax, norm_const_tensor=tnorm, prob_tensor=tprob)  # fmt: skip
+    else:
+        op = cf.GroupedGemmQuantSm100(ta, tsfa, toffs, talpha, d, sample_d_col=d_col, sample_b=tb, sample_sfb=tsfb, sample_sfd_row=sfd_row,
+                                      sample_sfd_col=sfd_col, sample_amax=amax, sample_norm_const=tnorm, sample_prob=tprob, sf_vec_size=32,
+                                      m_aligned=128)  # fmt: skip
+        assert op.check_support()
+        op.compile()
+        op.execute(ta, tsfa, toffs, talpha, d, b_tensor=tb, sfb_tensor=tsfb, d_col_tensor=d_col, sfd_row_tensor=sfd_row,
+                   sfd_col_tensor=sfd_col, amax_tensor=amax, norm_const_tensor=tnorm, prob_tensor=tprob)  # fmt: skip
+    torch.cuda.synchronize()
+    assert ops.device_status(clear=True) == 0
+    sfr = H.sf_to_numpy(sfd_row, valid, n_out // 32)[0]
+    sfc = H.sf_to_numpy(sfd_col, n_out, valid // 32)[0]
+    tol = 1e-3 if kind == "fc1" else 1e-4
+    assert (sfr != ref["sfd_row"]).mean() <= tol and (sfc != ref["sfd_col"]).mean() <= tol
+    got, got_col = d[:, :, 0].float().cpu().numpy(), d_col[:, :, 0].float().cpu().numpy()
+    same_r = np.repeat(sfr == ref["sfd_row"], 32, axis=1)
+    same_c = np.repeat((sfc == ref["sfd_col"]).T, 32, axis=0)
+    assert H.rel_fro(got[same_r], ref["d_q"][same_r]) <= 4e-3  # one bf16 rounding of nearly equal float32 values
+    assert H.rel_fro(got_col[same_c], ref["d_col_q"][same_c]) <= 4e-3
+    assert np.abs(got).max() <= 1.0 and np.abs(got_col).max() <= 1.0  # scaled values: block maximum at most 1 (norm 0.5)
+    np.testing.assert_allclose(amax.cpu().numpy().reshape(-1), ref["amax"], rtol=1e-2)
+
+
+@pytest.mark.parametrize("kind", ["fc1", "fc2"])
 def test_wrappers_allocate_and_match(kind):
     out, ref, info = _run(kind, 5, [256, 256], 512, 256, d_fp8=True, norm=0.01, wrapper=True, m_aligned=256)
     _check(kind, out, ref, info, d_fp8=True)
@@ -536,6 +595,48 @@ def test_fc1_is_bit_identical_to_the_reference_kernel_fixture(golden_dir, tile_m
     np.testing.assert_array_equal(orc.sf_unpack(flat(out["sfd_row_tensor"]), m, n_out // 32), orc.sf_unpack(g["sfd_row"], m, n_out // 32))
     np.testing.assert_array_equal(out["d_col_tensor"][:, :, 0].view(torch.uint8).cpu().numpy(), g["d_col"])
     np.testing.assert_array_equal(orc.sf_unpack(flat(out["sfd_col_tensor"]), n_out, m // 32), orc.sf_unpack(g["sfd_col"], n_out, m // 32))
+
+
+def test_fc1_with_bf16_d_and_scale_factors_is_bit_identical_to_the_reference_kernel_fixture(golden_dir, tile_mode):
+    """fp8 inputs, bf16 d_dtype and a norm_const through the wrapper: as the reference's wrapper, scale
+    factors are generated, D and D_col hold the scaled values in bf16 and amax is produced.  Every output
+    must equal the recording of the reference's kernel (--cases tiny_d_bf16) bit for bit."""
+    path = os.path.join(golden_dir, "reference_kernel_fc1_d_bf16.npz")
+    if not os.path.exists(path):
+        pytest.skip("reference-kernel fixture not recorded")
+    cf = _api()
+    from cudnn_frontend_b200 import ops
+
+    g = np.load(path)
+    m, k = g["a"].shape
+    e, n, _ = g["b"].shape
+    dev = "cuda"
+
+    def sf(flat_, mn, kk, l):
+        shape, stride = ops.sf_shape_stride(mn, kk, l)
+        return torch.as_strided(torch.from_numpy(flat_).to(dev).view(torch.float8_e8m0fnu), shape, stride)
+
+    a = torch.as_strided(H.dev_fp8(g["a"]), (m, k, 1), (k, 1, m * k))
+    b = H.dev_fp8(g["b"]).permute(1, 2, 0)
+    out = cf.grouped_gemm_swiglu_wrapper_sm100(
+        a, b, sf(g["sfa"], m, k, 1), sf(g["sfb"], n, k, e), torch.from_numpy(g["offsets"]).to(dev), torch.ones(e, device=dev),
+        norm_const_tensor=torch.ones(1, device=dev), prob_tensor=torch.from_numpy(g["prob"]).to(dev).view(m, 1, 1),
+        d_dtype=torch.bfloat16, sf_vec_size=32, m_aligned=256,
+    )  # fmt: skip
+    torch.cuda.synchronize()
+    assert out["sfd_row_tensor"] is not None and out["sfd_col_tensor"] is not None and out["amax_tensor"] is not None
+
+    def flat(t):
+        t = t.view(torch.uint8)
+        return torch.as_strided(t, (t.numel(),), (1,)).cpu().numpy()
+
+    n_out = n // 2
+    np.testing.assert_array_equal(out["c_tensor"][:, :, 0].view(torch.int16).cpu().numpy(), g["c"])
+    np.testing.assert_array_equal(out["d_tensor"][:, :, 0].contiguous().view(torch.int16).cpu().numpy(), g["d"])
+    np.testing.assert_array_equal(out["d_col_tensor"][:, :, 0].contiguous().view(torch.int16).cpu().numpy(), g["d_col"])
+    np.testing.assert_array_equal(orc.sf_unpack(flat(out["sfd_row_tensor"]), m, n_out // 32), orc.sf_unpack(g["sfd_row"], m, n_out // 32))
+    np.testing.assert_array_equal(orc.sf_unpack(flat(out["sfd_col_tensor"]), n_out, m // 32), orc.sf_unpack(g["sfd_col"], n_out, m // 32))
+    np.testing.assert_array_equal(out["amax_tensor"].cpu().numpy().reshape(-1), g["amax"].reshape(-1))
 
 
 def test_fc2_is_bit_identical_to_the_reference_kernel_fixture(golden_dir, tile_mode):

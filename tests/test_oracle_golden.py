@@ -163,6 +163,30 @@ def test_fc1_oracle_against_the_reference_kernel_fixture(golden_dir, fixture, ab
     _check_quantised(out["d_col_q"], out["sfd_col"], g["d_col"], g["sfd_col"], m, n // 2, by_cols=True)
 
 
+def test_fc1_oracle_against_the_reference_kernel_fixture_with_bf16_d(golden_dir):
+    """Scale-factor generation with a bf16 D (block maximum mapped to 1, D and D_col = scaled values in
+    bf16, amax on the unscaled values), recorded from the reference's wrapper (--cases tiny_d_bf16)."""
+    import os
+
+    if not os.path.exists(os.path.join(golden_dir, "reference_kernel_fc1_d_bf16.npz")):
+        pytest.skip("reference-kernel fixture not recorded")
+    g = _load(golden_dir, "reference_kernel_fc1_d_bf16.npz")
+    m, n = g["c"].shape
+    e, k = g["b"].shape[0], g["a"].shape[1]
+    sfa, sfb = orc.sf_unpack(g["sfa"], m, k // 32)[0], orc.sf_unpack(g["sfb"], n, k // 32, e)
+    out = orc.fc1_reference(g["a"], sfa, g["b"], sfb, g["offsets"], np.ones(e, np.float32), g["prob"], norm_const=1.0, d_dtype="bf16")
+    n_out = n // 2
+    ref_row = orc.sf_unpack(g["sfd_row"], m, n_out // 32)[0]
+    ref_col = orc.sf_unpack(g["sfd_col"], n_out, m // 32)[0]
+    assert np.mean(out["sfd_row"] == ref_row) >= 0.999 and np.mean(out["sfd_col"] == ref_col) >= 0.999
+    d_ref, dc_ref = _bf16_bits_to_f32(g["d"].view(np.uint16)), _bf16_bits_to_f32(g["d_col"].view(np.uint16))
+    same_r = np.repeat(out["sfd_row"] == ref_row, 32, axis=1)
+    same_c = np.repeat((out["sfd_col"] == ref_col).T, 32, axis=0)
+    assert np.mean(out["d_q"][same_r] == d_ref[same_r]) >= 0.97 and np.mean(out["d_col_q"][same_c] == dc_ref[same_c]) >= 0.97
+    assert np.linalg.norm(out["d_q"][same_r] - d_ref[same_r]) <= 4e-3 * np.linalg.norm(d_ref[same_r])
+    np.testing.assert_allclose(out["amax"], g["amax"].reshape(-1), rtol=1e-2)
+
+
 def test_fc2_oracle_against_the_reference_kernel_fixture(golden_dir):
     g = _load(golden_dir, "reference_kernel_fc2.npz")
     m, n = g["d"].shape
