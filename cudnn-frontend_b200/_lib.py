@@ -12,9 +12,9 @@ from ctypes import POINTER, Structure, c_char_p, c_float, c_int32, c_int64, c_vo
 from . import _build
 
 E_NULL, E_SHAPE, E_ALIGN, E_UNSUPPORTED, E_WORKSPACE, E_DEVICE = -1, -2, -3, -4, -5, -6
-DTYPE_BF16, DTYPE_E4M3, DTYPE_F16, DTYPE_F32, DTYPE_E5M2 = 0, 1, 2, 3, 4
+DTYPE_BF16, DTYPE_E4M3, DTYPE_F16, DTYPE_F32, DTYPE_E5M2, DTYPE_E2M1 = 0, 1, 2, 3, 4, 5
 ACT_SWIGLU, ACT_GEGLU = 0, 1
-ABI_VERSION = 6  # b200moe_abi_version() of the header these declarations mirror
+ABI_VERSION = 7  # b200moe_abi_version() of the header these declarations mirror
 FLAG_DISCRETE_COL_SFD = 1
 FLAG_TILE_SINGLE = 2
 FLAG_TILE_PAIR = 4
@@ -64,6 +64,8 @@ class GemmArgs(Structure):
         ("wait_limit_ms", c_int32),
         ("sched_light_m_tiles", c_int32),
         ("l2_stream_m_tiles", c_int32),
+        ("sf_vec_size", c_int32),
+        ("sf_dtype", c_int32),
     ]
 
 

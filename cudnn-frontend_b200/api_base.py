@@ -62,6 +62,17 @@ class TensorSpec:
             raise TypeError(f"{name} must be a torch.Tensor, got {type(t).__name__}")
         return TensorSpec(name, t.dtype, tuple(t.shape), tuple(t.stride()), t.device)
 
+    def logical(self) -> "TensorSpec":
+        """Shape and strides in elements.  ``float4_e2m1fn_x2`` packs two elements per byte along its
+        contiguous dimension: that extent doubles and every other stride doubles, as the reference's
+        ``_tensor_shape`` / ``_tensor_stride`` do (python/cudnn/api_base.py:650-713)."""
+        if self.dtype != torch.float4_e2m1fn_x2 or 1 not in self.stride:
+            return self
+        inner = self.stride.index(1)
+        shape = tuple(d * 2 if i == inner else d for i, d in enumerate(self.shape))
+        stride = tuple(st if i == inner else st * 2 for i, st in enumerate(self.stride))
+        return TensorSpec(self.name, self.dtype, shape, stride, self.device)
+
 
 class TupleDict(dict):
     """A dict whose iteration yields values in insertion order (so it unpacks like a tuple)
@@ -83,7 +94,7 @@ class TupleDict(dict):
 
 
 _FP8 = (torch.float8_e4m3fn, torch.float8_e5m2)
-_FP4 = (torch.float4_e2m1fn_x2, torch.uint8)
+_FP4 = (torch.float4_e2m1fn_x2, torch.uint8)  # the reference reads uint8 operands as raw packed FP4
 
 
 class OperatorBase:

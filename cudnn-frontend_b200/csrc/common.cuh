@@ -409,6 +409,42 @@ __device__ __forceinline__ void mma_mxf8_ss(uint32_t tmem_d, uint64_t adesc, uin
       : "memory");
 }
 
+// Block-scaled MMA of any of the three operand formats, one CTA or a CTA pair.
+//   kFmt 0  kind::mxf8f6f4, 8-bit operands, K = 32, one scale per row and MMA (scale id = byte of the TMEM word)
+//   kFmt 1  kind::mxf4, packed E2M1 operands, K = 64, two E8M0 scales per row and MMA (scale id 0 or 2)
+//   kFmt 2  kind::mxf4nvf4, packed E2M1 operands, K = 64, four scales (E8M0 or UE4M3) per row and MMA
+// Every form consumes 32 bytes of K per operand row.
+template <int kFmt, bool kPair>
+__device__ __forceinline__ void mma_block_scaled(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t tmem_sfa,
+                                                 uint32_t tmem_sfb, uint32_t accumulate) {
+#define B200_MMA_ASM(GROUP, KIND)                                                                               \
+  asm volatile(                                                                                                 \
+      "{\n\t"                                                                                                   \
+      ".reg .pred p;\n\t"                                                                                       \
+      "setp.ne.b32 p, %4, 0;\n\t"                                                                               \
+      "tcgen05.mma.cta_group::" GROUP ".kind::" KIND " [%0], %1, %2, %3, [%5], [%6], p;\n\t"                    \
+      "}" ::"r"(tmem_d),                                                                                        \
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)                         \
+      : "memory")
+  if constexpr (kFmt == 0) {
+    if constexpr (kPair) B200_MMA_ASM("2", "mxf8f6f4.block_scale");
+    else B200_MMA_ASM("1", "mxf8f6f4.block_scale");
+  } else if constexpr (kFmt == 1) {
+    if constexpr (kPair) B200_MMA_ASM("2", "mxf4.block_scale.scale_vec::2X");
+    else B200_MMA_ASM("1", "mxf4.block_scale.scale_vec::2X");
+  } else {
+    if constexpr (kPair) B200_MMA_ASM("2", "mxf4nvf4.block_scale.scale_vec::4X");
+    else B200_MMA_ASM("1", "mxf4nvf4.block_scale.scale_vec::4X");
+  }
+#undef B200_MMA_ASM
+}
+
+template <bool kPair>
+__device__ __forceinline__ void tmem_cp_sf_any(uint32_t taddr, uint64_t sdesc) {
+  if constexpr (kPair) asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+  else asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+
 // Copy 32 rows x 16 bytes of shared memory into TMEM columns [taddr, taddr+4), replicated
 // into the four 32-lane quarters (the scale-factor operand format of block-scaled MMA).
 __device__ __forceinline__ void tmem_cp_sf(uint32_t taddr, uint64_t sdesc) {

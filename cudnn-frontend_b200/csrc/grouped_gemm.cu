@@ -1,4 +1,4 @@
-// Block-scaled MXFP8 grouped GEMM for MoE experts with fused epilogues (sm_100a).
+// Block-scaled (MXFP8, MXFP4, NVFP4) grouped GEMM for MoE experts with fused epilogues (sm_100a).
 //
 //   FC1: C = alpha_e (A SFA)(B_e SFB_e)^T ; D = up * silu(gate) * prob   (gate/up = even/odd
 //        32-column blocks of C) ; per-expert amax, or row / column MXFP8 re-quantisation.
@@ -27,6 +27,13 @@
 // first (even tiles from the top, odd tiles from the bottom) and then lets the MMA warp start
 // the next tile while it finishes the rest.
 //
+// Operand formats (template parameter kFmt): 0 = 8-bit operands (E4M3 / E5M2), one E8M0 scale per 32
+// elements, tcgen05.mma.kind::mxf8f6f4; 1 = packed E2M1 (two per byte), one E8M0 scale per 32 elements,
+// kind::mxf4; 2 = packed E2M1, one E8M0 or UE4M3 scale per 16 elements, kind::mxf4nvf4.  A k-tile is 128
+// bytes of K in every format (128, 256, 256 elements) and four MMAs; it carries 1, 2 or 4 scale chunks
+// of 512 bytes per 128 operand rows.  With E2M1 operands the scale factors take 48 TMEM columns (one
+// buffer), so the accumulators overlap by 48 columns instead of 32.
+//
 // Every CTA loads what it needs into its own shared memory with plain (one-destination) TMA
 // loads, so the same binary serves single- and multi-GPU processes.
 #include <stdarg.h>
@@ -49,8 +56,6 @@ constexpr int BM = 128;  // rows per CTA
 constexpr int BN = 256;
 constexpr int BK = 128;  // bytes == elements (E4M3); one 128-byte swizzle row
 constexpr int A_STAGE_BYTES = BM * BK;  // 16 KiB
-constexpr int SFA_STAGE_BYTES = 512;
-constexpr int SFB_STAGE_BYTES = 1024;
 constexpr int NUM_EPI_WARPS = 8;
 constexpr int PRODUCER_B_WARP = 2 + NUM_EPI_WARPS;  // the last warp
 constexpr int NUM_THREADS = (3 + NUM_EPI_WARPS) * 32;
@@ -66,8 +71,6 @@ constexpr int DEFAULT_LIGHT_M_TILES = 2;
 constexpr int DEFAULT_STREAM_M_TILES = 0;
 
 constexpr int TMEM_COLS = 512;
-constexpr int TMEM_ACC1_COL = 224;
-constexpr int TMEM_SF_COL = 480;  // per SF buffer i: SFA at +16 i (4 cols), SFB at +16 i + 4 (8 cols)
 
 // status codes recorded by bounded waits
 constexpr int ST_PRODUCER_EMPTY = 101;
@@ -85,9 +88,17 @@ constexpr int SCHED_RING = 8;  // tile ids in flight between the fetching warp a
 constexpr int STAGING_ROW_BYTES = 256 + 16;  // 128 bf16 columns of one row, padded against bank conflicts
 constexpr int STAGING_WARP_BYTES = 32 * STAGING_ROW_BYTES;
 
-template <bool kPair, bool kBulk = false>
+template <bool kPair, bool kBulk = false, int kFmt = 0>
 struct Cfg {
-  static constexpr int STAGES = kBulk ? (kPair ? 4 : 3) : (kPair ? 6 : 4);
+  static constexpr int CPK = 1 << kFmt;  // 512-byte scale chunks per k-tile and 128 operand rows
+  static constexpr int SFA_STAGE_BYTES = 512 * CPK;
+  static constexpr int SFB_STAGE_BYTES = 1024 * CPK;  // [128-row block of B][chunk]
+  // TMEM: accumulator 0 at column 0, accumulator 1 at ACC1_COL, scale factors from SF_COL.
+  // 8-bit operands: two scale buffers of 16 columns (SFA 4 + SFB 8 used); E2M1: one buffer, SFA at +0
+  // (4 columns per chunk), SFB at +16 (8 columns per chunk: both 128-row blocks of B side by side)
+  static constexpr int TMEM_ACC1_COL = kFmt ? 208 : 224;
+  static constexpr int TMEM_SF_COL = kFmt ? 464 : 480;
+  static constexpr int STAGES = kBulk ? (kPair ? 4 : 3) : (kPair ? (kFmt == 2 ? 5 : 6) : 4);
   static constexpr int B_ROWS = kPair ? 128 : 256;  // rows of B this CTA loads per stage
   static constexpr int B_STAGE_BYTES = B_ROWS * BK;
   static constexpr int TILE_M = kPair ? 256 : 128;  // rows of one scheduled tile
@@ -107,6 +118,8 @@ struct Cfg {
   static constexpr uint32_t TX_BYTES = CTAS * (A_STAGE_BYTES + B_STAGE_BYTES + SFA_STAGE_BYTES + SFB_STAGE_BYTES);
 };
 static_assert(Cfg<false>::SMEM_BYTES <= 232448 && Cfg<true>::SMEM_BYTES <= 232448, "shared memory budget exceeded");
+static_assert(Cfg<false, false, 1>::SMEM_BYTES <= 232448 && Cfg<true, false, 1>::SMEM_BYTES <= 232448, "shared memory budget exceeded");
+static_assert(Cfg<false, false, 2>::SMEM_BYTES <= 232448 && Cfg<true, false, 2>::SMEM_BYTES <= 232448, "shared memory budget exceeded");
 static_assert(Cfg<false, true>::SMEM_BYTES <= 232448 && Cfg<true, true>::SMEM_BYTES <= 232448, "shared memory budget exceeded");
 
 enum : int { EPI_FC1 = 0, EPI_FC2 = 1 };
@@ -131,10 +144,11 @@ struct GemmParams {
   uint8_t* sfd_col;
   int64_t sfb_expert_bytes;
   int m_rows, n, k, num_experts;
+  int k_bytes;         // bytes of one operand row: k (8-bit operands) or k / 2 (packed E2M1)
   int n_out;           // n / 2 (FC1) or n (FC2)
   int n_tiles;         // ceil(n / 256)
-  int k_tiles;         // ceil(k / 128)
-  int rest_k;          // ceil(ceil(k / 32) / 4): K groups of SFA / SFB
+  int k_tiles;         // ceil(k_bytes / 128)
+  int rest_k;          // ceil(ceil(k / sf_vec) / 4): 512-byte scale chunks along K of SFA / SFB
   int n_blocks;        // ceil(n / 128): 128-row blocks of SFB
   int sfd_row_rest_k;  // ceil(ceil(n_out / 32) / 4)
   int sfd_col_rest_k;  // ceil(ceil(m_rows / 32) / 4)
@@ -143,12 +157,14 @@ struct GemmParams {
   int d_e5m2;         // FP8 D (and D_col) in E5M2 instead of E4M3
   float d_rcp_limit;  // 1/448 (E4M3) or 1/128 (E5M2)
   int d_f16, c_f16;   // 16-bit D / C in fp16 instead of bf16
+  int d_f32;          // D in float32 (E2M1 operands only)
   int discrete_col_sfd;
   int wide_stores;     // every output row segment of 32 bytes is 32-byte aligned
   const void* bias;    // optional [E][N] (element (n, e) at e * N + n), added after alpha
   int bias_dtype;      // B200MOE_DTYPE_BF16 / _F16 / _F32
   int act_geglu;       // FC1: 0 = SwiGLU, 1 = GeGLU
-  uint32_t ab_format;  // A / B format bits of the instruction descriptor (0 = E4M3, E5M2 = 1 in both fields)
+  uint32_t ab_format;  // A / B format bits of the instruction descriptor (0 = E4M3; E5M2 and E2M1 = 1 in both fields)
+  int sf_e4m3;         // scale factors are UE4M3 instead of E8M0 (kFmt 2 only)
   int raster_group_m;  // row tiles per raster group
   int light_m_tiles;   // experts with at most this many row tiles form the "light" class (0 = one class)
   int stream_m_tiles;  // weight tiles of experts with at most this many row tiles are loaded with an evict-first L2 hint
@@ -261,6 +277,21 @@ __device__ __forceinline__ void store_bf16x32(__nv_bfloat16* dst, const float* v
     hi.z = pack16x2_from_float(v[16 * i + 12], v[16 * i + 13], f16);
     hi.w = pack16x2_from_float(v[16 * i + 14], v[16 * i + 15], f16);
     store_32B(dst + 16 * i, lo, hi, wide);
+  }
+}
+
+// 32 values of a 16-bit or float32 D: element index `idx` counts from `base` in elements of D's type
+__device__ __forceinline__ void store_d32(__nv_bfloat16* base, int64_t idx, const float* v, bool wide, bool f16, bool f32) {
+  if (f32) {
+    float* dst = reinterpret_cast<float*>(base) + idx;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint4 lo = make_uint4(__float_as_uint(v[8 * i]), __float_as_uint(v[8 * i + 1]), __float_as_uint(v[8 * i + 2]), __float_as_uint(v[8 * i + 3]));
+      const uint4 hi = make_uint4(__float_as_uint(v[8 * i + 4]), __float_as_uint(v[8 * i + 5]), __float_as_uint(v[8 * i + 6]), __float_as_uint(v[8 * i + 7]));
+      store_32B(dst + 8 * i, lo, hi, wide);
+    }
+  } else {
+    store_bf16x32(base + idx, v, wide, f16);
   }
 }
 
@@ -420,13 +451,16 @@ __device__ __forceinline__ void load_bias8(const void* bias, int dtype, int64_t 
 // ---------------------------------------------------------------------------------------
 // The kernel
 // ---------------------------------------------------------------------------------------
-template <int kEpi, bool kDiscrete, bool kPair, bool kBulk = false>
+template <int kEpi, bool kDiscrete, bool kPair, bool kBulk = false, int kFmt = 0>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
     grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                         const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
                         const GemmParams p) {
-  using C = Cfg<kPair, kBulk>;
+  using C = Cfg<kPair, kBulk, kFmt>;
   constexpr int STAGES = C::STAGES;
+  constexpr int CPK = C::CPK;
+  constexpr int SFA_STAGE_BYTES = C::SFA_STAGE_BYTES, SFB_STAGE_BYTES = C::SFB_STAGE_BYTES;
+  constexpr int TMEM_ACC1_COL = C::TMEM_ACC1_COL, TMEM_SF_COL = C::TMEM_SF_COL;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const uint32_t smem_base = smem_u32(smem);
@@ -613,17 +647,17 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
               if (!side_b) {
                 if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(stage), C::TX_BYTES);
                 tma_load_2d_pair(a_dst0 + stage * A_STAGE_BYTES, &tmap_a, fb, kc, my_row0);
-                tma_load_3d_pair(sfa_dst0 + stage * SFA_STAGE_BYTES, &tmap_sfa, fb, 0, kt, m_blk);
+                tma_load_3d_pair(sfa_dst0 + stage * SFA_STAGE_BYTES, &tmap_sfa, fb, 0, kt * CPK, m_blk);
               } else if (kDiscrete) {
                 const int c0 = p.b_nmajor ? b_row : kc, c1 = p.b_nmajor ? kc : b_row;
                 if (b_stream) tma_load_2d_pair_hint(b_dst0 + stage * C::B_STAGE_BYTES, bmap, fb, c0, c1, b_policy);
                 else tma_load_2d_pair(b_dst0 + stage * C::B_STAGE_BYTES, bmap, fb, c0, c1);
-                tma_load_3d_pair(sfb_dst0 + stage * SFB_STAGE_BYTES, sfbmap, fb, 0, kt, nblk0);
+                tma_load_3d_pair(sfb_dst0 + stage * SFB_STAGE_BYTES, sfbmap, fb, 0, kt * CPK, nblk0);
               } else {
                 const int c0 = p.b_nmajor ? b_row : kc, c1 = p.b_nmajor ? kc : b_row;
                 if (b_stream) tma_load_3d_pair_hint(b_dst0 + stage * C::B_STAGE_BYTES, bmap, fb, c0, c1, tile.expert, b_policy);
                 else tma_load_3d_pair(b_dst0 + stage * C::B_STAGE_BYTES, bmap, fb, c0, c1, tile.expert);
-                tma_load_4d_pair(sfb_dst0 + stage * SFB_STAGE_BYTES, sfbmap, fb, 0, kt, nblk0, tile.expert);
+                tma_load_4d_pair(sfb_dst0 + stage * SFB_STAGE_BYTES, sfbmap, fb, 0, kt * CPK, nblk0, tile.expert);
               }
             }
             __syncwarp();
@@ -635,14 +669,16 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           const bool two_chunks = kDiscrete || p.n_blocks - nblk0 >= 2;
           if (!side_b) {
             const uint8_t* sfa_src = p.sfa + (int64_t)(tile.row0 / BM) * p.rest_k * 512;
-            const uint32_t tx = A_STAGE_BYTES + C::B_STAGE_BYTES + SFA_STAGE_BYTES + (two_chunks ? 1024u : 512u);
-            for (int kt = 0; kt < p.k_tiles; ++kt, kc += BK, sfa_src += 512) {
+            for (int kt = 0; kt < p.k_tiles; ++kt, kc += BK, sfa_src += 512 * CPK) {
               if (!__all_sync(0xffffffffu, mbar_wait(empty_bar(stage), phase ^ 1, wc, ST_PRODUCER_EMPTY))) { ok = false; break; }
               const uint32_t fb = full_bar(stage);
+              // scale chunks this k-tile has (the last k-tile of a row block may have fewer than CPK)
+              const uint32_t sf_bytes = 512u * (uint32_t)min(CPK, p.rest_k - kt * CPK);
+              const uint32_t tx = A_STAGE_BYTES + C::B_STAGE_BYTES + sf_bytes + (kDiscrete ? (uint32_t)SFB_STAGE_BYTES : (two_chunks ? 2u : 1u) * sf_bytes);
               if (elect_one()) {
                 mbar_arrive_expect_tx(fb, tx);
                 tma_load_2d(a_dst0 + stage * A_STAGE_BYTES, &tmap_a, fb, kc, tile.row0);
-                bulk_load(sfa_dst0 + stage * SFA_STAGE_BYTES, sfa_src, 512, fb);
+                bulk_load(sfa_dst0 + stage * SFA_STAGE_BYTES, sfa_src, sf_bytes, fb);
               }
               __syncwarp();
               if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -650,7 +686,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           } else {
             const uint8_t* sfb_src0 = kDiscrete ? nullptr : p.sfb + (int64_t)tile.expert * p.sfb_expert_bytes + (int64_t)nblk0 * p.rest_k * 512;
             const uint8_t* sfb_src1 = sfb_src0 + (int64_t)p.rest_k * 512;
-            for (int kt = 0; kt < p.k_tiles; ++kt, kc += BK, sfb_src0 += 512, sfb_src1 += 512) {
+            for (int kt = 0; kt < p.k_tiles; ++kt, kc += BK, sfb_src0 += 512 * CPK, sfb_src1 += 512 * CPK) {
               if (!__all_sync(0xffffffffu, mbar_wait(empty_bar(stage), phase ^ 1, wc, ST_PRODUCER_EMPTY))) { ok = false; break; }
               const uint32_t fb = full_bar(stage);
               if (elect_one() && !skip_loads) {
@@ -665,7 +701,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                     tma_load_2d(b_dst, bmap, fb, c0, c1);
                     if (p.b_nmajor) tma_load_2d(b_dst + 128 * BK, bmap, fb, n0 + 128, kc);
                   }
-                  tma_load_3d(sfb_dst0 + stage * SFB_STAGE_BYTES, sfbmap, fb, 0, kt, nblk0);
+                  tma_load_3d(sfb_dst0 + stage * SFB_STAGE_BYTES, sfbmap, fb, 0, kt * CPK, nblk0);
                 } else {
                   if (b_stream) {
                     tma_load_3d_hint(b_dst, bmap, fb, c0, c1, tile.expert, b_policy);
@@ -674,8 +710,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                     tma_load_3d(b_dst, bmap, fb, c0, c1, tile.expert);
                     if (p.b_nmajor) tma_load_3d(b_dst + 128 * BK, bmap, fb, n0 + 128, kc, tile.expert);
                   }
-                  bulk_load(sfb_dst0 + stage * SFB_STAGE_BYTES, sfb_src0, 512, fb);
-                  if (two_chunks) bulk_load(sfb_dst0 + stage * SFB_STAGE_BYTES + 512, sfb_src1, 512, fb);
+                  const uint32_t sf_bytes = 512u * (uint32_t)min(CPK, p.rest_k - kt * CPK);
+                  bulk_load(sfb_dst0 + stage * SFB_STAGE_BYTES, sfb_src0, sf_bytes, fb);
+                  if (two_chunks) bulk_load(sfb_dst0 + stage * SFB_STAGE_BYTES + 512 * CPK, sfb_src1, sf_bytes, fb);
                 }
               }
               __syncwarp();
@@ -716,7 +753,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       // (constant high word, running low word) and the instruction descriptors are immediates.
       // B in N-major form: bit 16 of the instruction descriptor, 128-column slabs 16 KB apart
       // (leading byte offset), 32 K rows = 4096 bytes per MMA.
-      const uint32_t idesc = make_idesc_mxf8(C::TILE_M, BN) | p.ab_format | (p.b_nmajor ? (1u << 16) : 0u);
+      const uint32_t idesc = (make_idesc_mxf8(C::TILE_M, BN) | p.ab_format | (p.b_nmajor ? (1u << 16) : 0u)) & ~(p.sf_e4m3 ? (1u << 23) : 0u);
       constexpr uint32_t AB_HI = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO 1024, version 1, 128-byte swizzle
       constexpr uint32_t SF_HI = (128u >> 4) | (1u << 14);                // SBO 128, version 1, no swizzle
       constexpr uint32_t AB_LBO = 1u << 16;                               // leading byte offset 16 (unused by swizzled K-major)
@@ -745,50 +782,45 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           bool landed = mbar_try_wait(full_bar(stage), phase);
           if (!landed) landed = mbar_wait(full_bar(stage), phase, wc, ST_MMA_FULL);
           if (!__all_sync(0xffffffffu, landed)) { ok = false; break; }
-          const uint32_t sfa_t = tmem_base + TMEM_SF_COL + 16 * sf_buf;
-          const uint32_t sfb_t = sfa_t + 4;
+          // scale chunks: 8-bit operands alternate between two TMEM buffers; E2M1 operands have one
+          // (tcgen05.cp and tcgen05.mma of one thread execute in issue order)
+          const uint32_t sfa_t = tmem_base + TMEM_SF_COL + (kFmt ? 0 : 16 * sf_buf);
+          const uint32_t sfb_t = sfa_t + (kFmt ? 16 : 4);
           const uint32_t a_lo = a_lo0 + stage * (A_STAGE_BYTES >> 4);
           const uint32_t b_lo = b_lo0 + stage * (C::B_STAGE_BYTES >> 4);
           const uint32_t sfa_lo = sfa_lo0 + stage * (SFA_STAGE_BYTES >> 4);
           const uint32_t sfb_lo = sfb_lo0 + stage * (SFB_STAGE_BYTES >> 4);
           const uint32_t not_first = kt != 0;
-          const bool full_k = p.k - kt * BK >= BK;
+          const int k_left = p.k_bytes - kt * BK;  // bytes of K this k-tile still has
           if (elect_one()) {
-          if constexpr (kPair) {
-            // one instruction acts on both CTAs: each copies from its own smem to its own TMEM
-            tmem_cp_sf_pair(sfa_t, desc(sfa_lo, SF_HI));
-            tmem_cp_sf_pair(sfb_t, desc(sfb_lo, SF_HI));
-            tmem_cp_sf_pair(sfb_t + 4, desc(sfb_lo + 32, SF_HI));
-            if (full_k) {
-              // 32 bytes along K inside the 128-byte swizzle row = +2 in 16-byte units
-              mma_mxf8_ss_pair(acc, desc(a_lo, AB_HI), desc(b_lo, AB_HI), idesc_with_sf_id(idesc, 0, 0), sfa_t, sfb_t, not_first);
-              mma_mxf8_ss_pair(acc, desc(a_lo + 2, AB_HI), desc(b_lo + b_kstep, AB_HI), idesc_with_sf_id(idesc, 1, 1), sfa_t, sfb_t, 1);
-              mma_mxf8_ss_pair(acc, desc(a_lo + 4, AB_HI), desc(b_lo + 2 * b_kstep, AB_HI), idesc_with_sf_id(idesc, 2, 2), sfa_t, sfb_t, 1);
-              mma_mxf8_ss_pair(acc, desc(a_lo + 6, AB_HI), desc(b_lo + 3 * b_kstep, AB_HI), idesc_with_sf_id(idesc, 3, 3), sfa_t, sfb_t, 1);
-            } else {
-              const int kblocks = (p.k - kt * BK + 31) / 32;
-              for (int kb = 0; kb < kblocks; ++kb)
-                mma_mxf8_ss_pair(acc, desc(a_lo + 2 * kb, AB_HI), desc(b_lo + kb * b_kstep, AB_HI), idesc_with_sf_id(idesc, kb, kb), sfa_t,
-                                 sfb_t, (kt | kb) != 0);
+            // chunk g of SFA -> 4 columns; chunk g of both 128-row blocks of SFB -> 8 columns side by side.
+            // (in pair mode one instruction acts on both CTAs: each copies from its own smem to its own TMEM)
+#pragma unroll
+            for (int g = 0; g < CPK; ++g) {
+              tmem_cp_sf_any<kPair>(sfa_t + 4 * g, desc(sfa_lo + 32 * g, SF_HI));
+              tmem_cp_sf_any<kPair>(sfb_t + 8 * g, desc(sfb_lo + 32 * g, SF_HI));
+              tmem_cp_sf_any<kPair>(sfb_t + 8 * g + 4, desc(sfb_lo + 32 * (CPK + g), SF_HI));
             }
-            tc_commit_pair(empty_bar(stage), 3);  // frees this stage in both CTAs
-          } else {
-            tmem_cp_sf(sfa_t, desc(sfa_lo, SF_HI));
-            tmem_cp_sf(sfb_t, desc(sfb_lo, SF_HI));
-            tmem_cp_sf(sfb_t + 4, desc(sfb_lo + 32, SF_HI));
-            if (full_k) {
-              mma_mxf8_ss(acc, desc(a_lo, AB_HI), desc(b_lo, AB_HI), idesc_with_sf_id(idesc, 0, 0), sfa_t, sfb_t, not_first);
-              mma_mxf8_ss(acc, desc(a_lo + 2, AB_HI), desc(b_lo + b_kstep, AB_HI), idesc_with_sf_id(idesc, 1, 1), sfa_t, sfb_t, 1);
-              mma_mxf8_ss(acc, desc(a_lo + 4, AB_HI), desc(b_lo + 2 * b_kstep, AB_HI), idesc_with_sf_id(idesc, 2, 2), sfa_t, sfb_t, 1);
-              mma_mxf8_ss(acc, desc(a_lo + 6, AB_HI), desc(b_lo + 3 * b_kstep, AB_HI), idesc_with_sf_id(idesc, 3, 3), sfa_t, sfb_t, 1);
+            // MMA j reads bytes [32 j, 32 j + 32) of K (+2 in 16-byte units inside the 128-byte swizzle row) and
+            // the scales of those elements: byte j of the chunk (kFmt 0), bytes 2 (j & 1) .. + 1 of chunk
+            // j / 2 (kFmt 1), chunk j (kFmt 2)
+            auto mma = [&](int j, uint32_t acc_flag) {
+              const uint32_t sf_id = kFmt == 0 ? (uint32_t)j : (kFmt == 1 ? 2u * (j & 1) : 0u);
+              const uint32_t chunk = kFmt == 0 ? 0u : (kFmt == 1 ? (uint32_t)(j >> 1) : (uint32_t)j);
+              mma_block_scaled<kFmt, kPair>(acc, desc(a_lo + 2 * j, AB_HI), desc(b_lo + j * b_kstep, AB_HI), idesc_with_sf_id(idesc, sf_id, sf_id),
+                                            sfa_t + 4 * chunk, sfb_t + 8 * chunk, acc_flag);
+            };
+            if (k_left >= BK) {
+              mma(0, not_first);
+              mma(1, 1);
+              mma(2, 1);
+              mma(3, 1);
             } else {
-              const int kblocks = (p.k - kt * BK + 31) / 32;
-              for (int kb = 0; kb < kblocks; ++kb)
-                mma_mxf8_ss(acc, desc(a_lo + 2 * kb, AB_HI), desc(b_lo + kb * b_kstep, AB_HI), idesc_with_sf_id(idesc, kb, kb), sfa_t, sfb_t,
-                            (kt | kb) != 0);
+              const int kblocks = (k_left + 31) / 32;
+              for (int kb = 0; kb < kblocks; ++kb) mma(kb, (kt | kb) != 0);
             }
-            tc_commit(empty_bar(stage));  // frees the smem stage once these MMAs have read it
-          }
+            if constexpr (kPair) tc_commit_pair(empty_bar(stage), 3);  // frees this stage in both CTAs
+            else tc_commit(empty_bar(stage));  // frees the smem stage once these MMAs have read it
           }
           __syncwarp();
           sf_buf ^= 1;
@@ -913,7 +945,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             for (int j = 0; j < 32; ++j) thread_amax = fmaxf(thread_amax, fabsf(g[j]));
           }
           if (!p.gen_sfd) {
-            if (row_ok && out_row >= 0) store_bf16x32(d_rows + (int64_t)out_row * p.n_out + dn, g, wide, d_f16);
+            if (row_ok && out_row >= 0) store_d32(d_rows, (int64_t)out_row * p.n_out + dn, g, wide, d_f16, p.d_f32 != 0);
           } else {
             if (row_ok) {
               const uint32_t sf = quant_row_block(reinterpret_cast<uint8_t*>(p.d) + (int64_t)row * d_row_bytes, dn, g, norm_const, wide, out_fmt);
@@ -960,7 +992,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           tmem_ld_32x32(acc + col, v);
           tmem_ld_wait();
           reg_fence32(v);
-          if (i == 0) {
+          // the accumulators share 32 columns (48 with E2M1 operands: two blocks)
+          if (i == (kFmt ? 1 : 0)) {
             tc_fence_before();
             __syncwarp();
             if (lane == 0) arrive_overlap();
@@ -999,7 +1032,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 st[q] = o;
               }
             } else {
-              if (row_ok && out_row >= 0) store_bf16x32(d_rows + (int64_t)out_row * p.n_out + dn, v, wide, d_f16);
+              if (row_ok && out_row >= 0) store_d32(d_rows, (int64_t)out_row * p.n_out + dn, v, wide, d_f16, p.d_f32 != 0);
             }
           } else {
             if (row_ok) {
@@ -1182,7 +1215,7 @@ static int encode_map(CUtensorMap* map, CUtensorMapDataType dtype, const void* b
 struct DeviceInfo {
   int sm_count = 0;
   int cc_major = 0;
-  bool attr_set[2][2][2] = {};
+  bool attr_set[3][2][2][2] = {};
   bool attr_set_bulk[2] = {};
 };
 
@@ -1202,11 +1235,11 @@ static int get_device_info(DeviceInfo** out) {
   return B200MOE_OK;
 }
 
-template <int kEpi, bool kDiscrete, bool kPair, bool kBulk = false>
+template <int kEpi, bool kDiscrete, bool kPair, bool kBulk = false, int kFmt = 0>
 static int launch(const CUtensorMap* maps, const GemmParams& p, int grid, DeviceInfo* di, cudaStream_t stream) {
-  auto kern = grouped_gemm_kernel<kEpi, kDiscrete, kPair, kBulk>;
-  constexpr int smem = Cfg<kPair, kBulk>::SMEM_BYTES;
-  bool& attr_set = kBulk ? di->attr_set_bulk[kPair ? 1 : 0] : di->attr_set[kEpi][kDiscrete ? 1 : 0][kPair ? 1 : 0];
+  auto kern = grouped_gemm_kernel<kEpi, kDiscrete, kPair, kBulk, kFmt>;
+  constexpr int smem = Cfg<kPair, kBulk, kFmt>::SMEM_BYTES;
+  bool& attr_set = kBulk ? di->attr_set_bulk[kPair ? 1 : 0] : di->attr_set[kFmt][kEpi][kDiscrete ? 1 : 0][kPair ? 1 : 0];
   if (!attr_set) {
     B200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     attr_set = true;
@@ -1230,13 +1263,21 @@ static int launch(const CUtensorMap* maps, const GemmParams& p, int grid, Device
   return B200MOE_OK;
 }
 
-template <int kEpi>
-static int dispatch(bool discrete, bool pair, const CUtensorMap* maps, const GemmParams& p, int grid, DeviceInfo* di,
-                    cudaStream_t stream) {
+template <int kEpi, int kFmt>
+static int dispatch_fmt(bool discrete, bool pair, const CUtensorMap* maps, const GemmParams& p, int grid, DeviceInfo* di,
+                        cudaStream_t stream) {
   if (discrete) {
-    return pair ? launch<kEpi, true, true>(maps, p, grid, di, stream) : launch<kEpi, true, false>(maps, p, grid, di, stream);
+    return pair ? launch<kEpi, true, true, false, kFmt>(maps, p, grid, di, stream) : launch<kEpi, true, false, false, kFmt>(maps, p, grid, di, stream);
   }
-  return pair ? launch<kEpi, false, true>(maps, p, grid, di, stream) : launch<kEpi, false, false>(maps, p, grid, di, stream);
+  return pair ? launch<kEpi, false, true, false, kFmt>(maps, p, grid, di, stream) : launch<kEpi, false, false, false, kFmt>(maps, p, grid, di, stream);
+}
+
+template <int kEpi>
+static int dispatch(int fmt, bool discrete, bool pair, const CUtensorMap* maps, const GemmParams& p, int grid, DeviceInfo* di,
+                    cudaStream_t stream) {
+  if (fmt == 1) return dispatch_fmt<kEpi, 1>(discrete, pair, maps, p, grid, di, stream);
+  if (fmt == 2) return dispatch_fmt<kEpi, 2>(discrete, pair, maps, p, grid, di, stream);
+  return dispatch_fmt<kEpi, 0>(discrete, pair, maps, p, grid, di, stream);
 }
 
 static int run_gemm(int epi, const b200moe_gemm_args* a, void* stream_v) {
@@ -1260,6 +1301,18 @@ static int run_gemm(int epi, const b200moe_gemm_args* a, void* stream_v) {
   if (a->num_experts > MAX_EXPERTS)
     return fail(B200MOE_E_SHAPE, "%s: at most %d experts are supported, got %d", op, MAX_EXPERTS, a->num_experts);
   if (a->k % 16 != 0) return fail(B200MOE_E_SHAPE, "%s: k (%lld) must be a multiple of 16", op, (long long)a->k);
+  // operand format: 0 = 8-bit operands with E8M0 scales per 32; 1 = E2M1, E8M0 per 32; 2 = E2M1, E8M0 or UE4M3 per 16
+  const bool fp4 = a->ab_dtype == B200MOE_DTYPE_E2M1;
+  const int sf_vec = a->sf_vec_size == 0 ? 32 : a->sf_vec_size;
+  const bool sf_e4m3 = a->sf_dtype == B200MOE_DTYPE_E4M3;
+  if (sf_vec != 16 && sf_vec != 32) return fail(B200MOE_E_SHAPE, "%s: sf_vec_size must be 16 or 32, got %d", op, sf_vec);
+  if (a->sf_dtype != 0 && !sf_e4m3) return fail(B200MOE_E_UNSUPPORTED, "%s: sf_dtype %d (0 = E8M0 and E4M3 are built)", op, a->sf_dtype);
+  if (!fp4 && (sf_vec != 32 || sf_e4m3)) return fail(B200MOE_E_SHAPE, "%s: 8-bit operands take E8M0 scale factors per 32 elements", op);
+  if (sf_e4m3 && sf_vec != 16) return fail(B200MOE_E_SHAPE, "%s: E4M3 scale factors go with sf_vec_size 16", op);
+  if (fp4 && a->k % 64 != 0)
+    return fail(B200MOE_E_UNSUPPORTED, "%s: E2M1 operands need k (%lld) to be a multiple of 64 (one MMA consumes 64 elements)", op, (long long)a->k);
+  if (fp4 && (a->flags & B200MOE_FLAG_B_NMAJOR)) return fail(B200MOE_E_SHAPE, "%s: E2M1 operands need a K-major B", op);
+  const int fmt = !fp4 ? 0 : (sf_vec == 32 ? 1 : 2);
   if ((a->flags & B200MOE_FLAG_B_NMAJOR) && a->n % 16 != 0)
     return fail(B200MOE_E_SHAPE, "%s: N-major B needs n (%lld) to be a multiple of 16", op, (long long)a->n);
   if (epi == EPI_FC1 && a->n % 64 != 0)
@@ -1271,12 +1324,16 @@ static int run_gemm(int epi, const b200moe_gemm_args* a, void* stream_v) {
   if (a->d_row_map && (d_fp8 || a->c)) return fail(B200MOE_E_UNSUPPORTED, "%s: d_row_map needs a bf16 D and no C", op);
   if (a->d_peer_ptrs && (!a->d_row_map || a->d_peer_slots <= 0))
     return fail(B200MOE_E_SHAPE, "%s: d_peer_ptrs needs d_row_map and a positive d_peer_slots", op);
-  if (a->d_dtype != B200MOE_DTYPE_BF16 && a->d_dtype != B200MOE_DTYPE_F16 && !d_fp8)
+  const bool d_f32 = a->d_dtype == B200MOE_DTYPE_F32;
+  if (a->d_dtype != B200MOE_DTYPE_BF16 && a->d_dtype != B200MOE_DTYPE_F16 && !d_fp8 && !d_f32)
     return fail(B200MOE_E_UNSUPPORTED, "%s: d_dtype %d", op, a->d_dtype);
+  if (d_f32 && !fp4) return fail(B200MOE_E_UNSUPPORTED, "%s: a float32 D goes with E2M1 operands only (as in the reference)", op);
+  if (d_f32 && a->d_row_map) return fail(B200MOE_E_UNSUPPORTED, "%s: d_row_map needs a bf16 D", op);
+  if (fp4 && d_fp8) return fail(B200MOE_E_SHAPE, "%s: E2M1 operands take a bf16, fp16 or float32 D", op);
   if (a->c_dtype != B200MOE_DTYPE_BF16 && a->c_dtype != B200MOE_DTYPE_F16)
     return fail(B200MOE_E_UNSUPPORTED, "%s: c_dtype %d (bf16 and fp16 are built)", op, a->c_dtype);
-  if (a->ab_dtype != 0 && a->ab_dtype != B200MOE_DTYPE_E4M3 && a->ab_dtype != B200MOE_DTYPE_E5M2)
-    return fail(B200MOE_E_UNSUPPORTED, "%s: ab_dtype %d (E4M3 and E5M2 are built)", op, a->ab_dtype);
+  if (a->ab_dtype != 0 && a->ab_dtype != B200MOE_DTYPE_E4M3 && a->ab_dtype != B200MOE_DTYPE_E5M2 && !fp4)
+    return fail(B200MOE_E_UNSUPPORTED, "%s: ab_dtype %d (E4M3, E5M2 and E2M1 are built)", op, a->ab_dtype);
   if (a->act_func != B200MOE_ACT_SWIGLU && a->act_func != B200MOE_ACT_GEGLU)
     return fail(B200MOE_E_UNSUPPORTED, "%s: act_func %d", op, a->act_func);
   if (a->wait_limit_ms < 0) return fail(B200MOE_E_SHAPE, "%s: wait_limit_ms must not be negative", op);
@@ -1292,6 +1349,7 @@ static int run_gemm(int epi, const b200moe_gemm_args* a, void* stream_v) {
   // Scale factors are generated when sfd_row and norm_const are given (always for an FP8 D; for a 16-bit
   // D the reference then stores the scaled values, block maximum mapped to 1, in D's own type)
   const bool gen_sfd = a->sfd_row != nullptr && a->norm_const != nullptr;
+  if (gen_sfd && fp4) return fail(B200MOE_E_UNSUPPORTED, "%s: scale-factor generation goes with 8-bit operands only (as in the reference)", op);
   if (d_fp8 && !gen_sfd) return fail(B200MOE_E_NULL, "%s: FP8 output needs sfd_row and norm_const", op);
   if (gen_sfd && ((a->d_col == nullptr) != (a->sfd_col == nullptr)))
     return fail(B200MOE_E_NULL, "%s: d_col and sfd_col go together", op);
@@ -1314,7 +1372,8 @@ static int run_gemm(int epi, const b200moe_gemm_args* a, void* stream_v) {
   p.alpha = a->alpha;
   p.prob = a->prob;
   p.norm_const = a->norm_const;
-  p.ab_format = a->ab_dtype == B200MOE_DTYPE_E5M2 ? ((1u << 7) | (1u << 10)) : 0u;
+  p.ab_format = (a->ab_dtype == B200MOE_DTYPE_E5M2 || fp4) ? ((1u << 7) | (1u << 10)) : 0u;  // E5M2 of mxf8f6f4 and E2M1 of mxf4 are both code 1
+  p.sf_e4m3 = sf_e4m3 ? 1 : 0;
   p.bias = a->bias;
   p.bias_dtype = a->bias_dtype;
   p.act_geglu = (epi == EPI_FC1 && a->act_func == B200MOE_ACT_GEGLU) ? 1 : 0;
@@ -1334,8 +1393,9 @@ static int run_gemm(int epi, const b200moe_gemm_args* a, void* stream_v) {
   p.num_experts = a->num_experts;
   p.n_out = epi == EPI_FC1 ? p.n / 2 : p.n;
   p.n_tiles = (p.n + BN - 1) / BN;
-  p.k_tiles = (p.k + BK - 1) / BK;
-  p.rest_k = ((p.k + 31) / 32 + 3) / 4;
+  p.k_bytes = fp4 ? p.k / 2 : p.k;
+  p.k_tiles = (p.k_bytes + BK - 1) / BK;
+  p.rest_k = ((p.k + sf_vec - 1) / sf_vec + 3) / 4;
   p.n_blocks = (p.n + 127) / 128;
   p.sfb_expert_bytes = (int64_t)p.n_blocks * p.rest_k * 512;
   p.sfd_row_rest_k = ((p.n_out + 31) / 32 + 3) / 4;
@@ -1344,6 +1404,7 @@ static int run_gemm(int epi, const b200moe_gemm_args* a, void* stream_v) {
   p.d_e5m2 = a->d_dtype == B200MOE_DTYPE_E5M2;
   p.d_rcp_limit = !d_fp8 ? 1.0f : (p.d_e5m2 ? 1.0f / 128.0f : 1.0f / 448.0f);
   p.d_f16 = a->d_dtype == B200MOE_DTYPE_F16;
+  p.d_f32 = d_f32 ? 1 : 0;
   p.c_f16 = a->c_dtype == B200MOE_DTYPE_F16;
   p.discrete_col_sfd = (a->flags & B200MOE_FLAG_DISCRETE_COL_SFD) ? 1 : 0;
   p.first_has_prev = (a->flags & B200MOE_FLAG_OFFSETS_HAVE_PREV) ? 1 : 0;
@@ -1356,7 +1417,7 @@ static int run_gemm(int epi, const b200moe_gemm_args* a, void* stream_v) {
   p.light_m_tiles = a->sched_light_m_tiles < 0 ? 0 : (a->sched_light_m_tiles == 0 ? DEFAULT_LIGHT_M_TILES : a->sched_light_m_tiles);
   {
     // 256-bit stores need 32-byte aligned bases and row pitches that keep a 32-column block aligned
-    const int64_t d_pitch = (int64_t)p.n_out * (d_fp8 ? 1 : 2);
+    const int64_t d_pitch = (int64_t)p.n_out * (d_fp8 ? 1 : (d_f32 ? 4 : 2));
     const uintptr_t bases = (uintptr_t)a->c | (uintptr_t)a->d | (uintptr_t)a->d_col;
     p.wide_stores = (bases % 32 == 0) && (d_pitch % 32 == 0) && (((int64_t)p.n * 2) % 32 == 0);
   }
@@ -1369,7 +1430,7 @@ static int run_gemm(int epi, const b200moe_gemm_args* a, void* stream_v) {
   else if (a->flags & B200MOE_FLAG_TILE_PAIR) pair = true;
   else pair = a->m_rows / a->num_experts >= 1024;
   {
-    const int64_t rows = std::min<int64_t>(RASTER_GROUP_ROWS, RASTER_GROUP_BYTES / std::max<int64_t>(p.k, 1));
+    const int64_t rows = std::min<int64_t>(RASTER_GROUP_ROWS, RASTER_GROUP_BYTES / std::max<int64_t>(p.k_bytes, 1));
     p.raster_group_m = (int)std::max<int64_t>(1, rows / (pair ? 2 * BM : BM));
   }
 
@@ -1377,18 +1438,19 @@ static int run_gemm(int epi, const b200moe_gemm_args* a, void* stream_v) {
   memset(maps, 0, sizeof(maps));
   const uint32_t b_rows = pair ? 128 : BN;
   {
-    const uint64_t dims[2] = {(uint64_t)p.k, (uint64_t)p.m_rows};
-    const uint64_t strides[1] = {(uint64_t)p.k};
+    const uint64_t dims[2] = {(uint64_t)p.k_bytes, (uint64_t)p.m_rows};
+    const uint64_t strides[1] = {(uint64_t)p.k_bytes};
     const uint32_t box[2] = {BK, BM};
     rc = encode_map(&maps[0], CU_TENSOR_MAP_DATA_TYPE_UINT8, a->a, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
   }
   const uint64_t sf_chunk_stride = 512, sf_row_stride = (uint64_t)p.rest_k * 512;
+  const uint32_t cpk = 1u << fmt;  // scale chunks per k-tile
   if (pair) {
     // scale factors as 512-byte chunks of 128 uint32: (chunk word, K group, 128-row block[, expert])
     const uint64_t dims[3] = {128, (uint64_t)p.rest_k, (uint64_t)((p.m_rows + 127) / 128)};
     const uint64_t strides[2] = {sf_chunk_stride, sf_row_stride};
-    const uint32_t box[3] = {128, 1, 1};
+    const uint32_t box[3] = {128, cpk, 1};
     rc = encode_map(&maps[2], CU_TENSOR_MAP_DATA_TYPE_UINT32, a->sfa, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (rc) return rc;
   }
@@ -1399,8 +1461,8 @@ static int run_gemm(int epi, const b200moe_gemm_args* a, void* stream_v) {
     return fail(B200MOE_E_WORKSPACE, "%s: needs a 128-byte aligned workspace of %lld bytes (b200moe_workspace_bytes)", op, (long long)need);
   if (!discrete) {
     if (!b_nmajor) {
-      const uint64_t dims[3] = {(uint64_t)p.k, (uint64_t)p.n, (uint64_t)p.num_experts};
-      const uint64_t strides[2] = {(uint64_t)p.k, (uint64_t)p.n * (uint64_t)p.k};
+      const uint64_t dims[3] = {(uint64_t)p.k_bytes, (uint64_t)p.n, (uint64_t)p.num_experts};
+      const uint64_t strides[2] = {(uint64_t)p.k_bytes, (uint64_t)p.n * (uint64_t)p.k_bytes};
       const uint32_t box[3] = {BK, b_rows, 1};
       rc = encode_map(&maps[1], CU_TENSOR_MAP_DATA_TYPE_UINT8, a->b, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
     } else {
@@ -1414,15 +1476,15 @@ static int run_gemm(int epi, const b200moe_gemm_args* a, void* stream_v) {
     if (pair) {
       const uint64_t sdims[4] = {128, (uint64_t)p.rest_k, (uint64_t)p.n_blocks, (uint64_t)p.num_experts};
       const uint64_t sstrides[3] = {sf_chunk_stride, sf_row_stride, (uint64_t)p.sfb_expert_bytes};
-      const uint32_t sbox[4] = {128, 1, 2, 1};
+      const uint32_t sbox[4] = {128, cpk, 2, 1};
       rc = encode_map(&maps[3], CU_TENSOR_MAP_DATA_TYPE_UINT32, a->sfb, 4, sdims, sstrides, sbox, CU_TENSOR_MAP_SWIZZLE_NONE);
       if (rc) return rc;
     }
   } else {
     // prototypes; the global addresses are patched per expert on the device
     if (!b_nmajor) {
-      const uint64_t dims[2] = {(uint64_t)p.k, (uint64_t)p.n};
-      const uint64_t strides[1] = {(uint64_t)p.k};
+      const uint64_t dims[2] = {(uint64_t)p.k_bytes, (uint64_t)p.n};
+      const uint64_t strides[1] = {(uint64_t)p.k_bytes};
       const uint32_t box[2] = {BK, b_rows};
       rc = encode_map(&maps[1], CU_TENSOR_MAP_DATA_TYPE_UINT8, a->a, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
     } else {
@@ -1434,7 +1496,7 @@ static int run_gemm(int epi, const b200moe_gemm_args* a, void* stream_v) {
     if (rc) return rc;
     const uint64_t sdims[3] = {128, (uint64_t)p.rest_k, (uint64_t)p.n_blocks};
     const uint64_t sstrides[2] = {sf_chunk_stride, sf_row_stride};
-    const uint32_t sbox[3] = {128, 1, 2};
+    const uint32_t sbox[3] = {128, cpk, 2};
     rc = encode_map(&maps[3], CU_TENSOR_MAP_DATA_TYPE_UINT32, a->sfa, 3, sdims, sstrides, sbox, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (rc) return rc;
     p.b_maps = (const CUtensorMap*)a->workspace;
@@ -1457,11 +1519,11 @@ static int run_gemm(int epi, const b200moe_gemm_args* a, void* stream_v) {
   const int grid = pair ? 2 * units : units;
 
   // FC2 rows that go to peer buffers leave through shared memory and one bulk copy per row
-  if (epi == EPI_FC2 && !discrete && !d_fp8 && !gen_sfd && p.d_peer_ptrs && ((uintptr_t)a->d % 16 == 0))
+  if (epi == EPI_FC2 && !discrete && !d_fp8 && !gen_sfd && fmt == 0 && p.d_peer_ptrs && ((uintptr_t)a->d % 16 == 0))
     return pair ? launch<EPI_FC2, false, true, true>(maps, p, grid, di, stream)
                 : launch<EPI_FC2, false, false, true>(maps, p, grid, di, stream);
-  return epi == EPI_FC1 ? dispatch<EPI_FC1>(discrete, pair, maps, p, grid, di, stream)
-                        : dispatch<EPI_FC2>(discrete, pair, maps, p, grid, di, stream);
+  return epi == EPI_FC1 ? dispatch<EPI_FC1>(fmt, discrete, pair, maps, p, grid, di, stream)
+                        : dispatch<EPI_FC2>(fmt, discrete, pair, maps, p, grid, di, stream);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -1551,6 +1613,6 @@ int b200moe_device_status(int clear) {
   return v;
 }
 
-int b200moe_abi_version(void) { return 6; }
+int b200moe_abi_version(void) { return 7; }
 
 }  // extern "C"

@@ -131,16 +131,18 @@ class GroupedGemmQuantSm100(OperatorBase):
             self.discrete_col_sfd = False
 
         self._value_error_if(len(self.a.shape) != 3, "A must be (m, k, 1)")
-        tensor_m, k, _ = self.a.shape
+        a_l = self.a.logical()  # FP4 operands: two elements per byte along K
+        b_l = None if self.b is None else self.b.logical()
+        tensor_m, k, _ = a_l.shape
         if not self.discrete:
             self._value_error_if(len(self.b.shape) != 3, "B must be (n, k, l)")
-            n, _, l = self.b.shape
+            n, _, l = b_l.shape
         else:
             n, b_k = self.b_shape[0], self.b_shape[1]
             self._value_error_if(b_k != k, f"B K dimension ({b_k}) must match A K dimension ({k})")
             l = self.expert_cnt
-        self._check_shape(self.a, (tensor_m, k, 1), "A")
-        self._check_shape(self.b, (n, k, l), "B")
+        self._check_shape(a_l, (tensor_m, k, 1), "A")
+        self._check_shape(b_l, (n, k, l), "B")
         self._check_shape(self.d, (tensor_m, n, 1), "D")
         self._check_shape(self.d_col, (tensor_m, n, 1), "D_col")
         rest_k = ceil_div(ceil_div(k, self.sf_vec_size), 4)
@@ -162,16 +164,16 @@ class GroupedGemmQuantSm100(OperatorBase):
         self._check_shape(self.norm_const, (1,), "norm_const")
         self._check_shape(self.padded_offsets, (self.expert_cnt,), "padded_offsets")
 
-        self._check_stride(self.a, (k, 1, tensor_m * k), "A must have k-major layout")
+        self._check_stride(a_l, (k, 1, tensor_m * k), "A must have k-major layout")
         self._value_error_if(self.b_major not in ("k", "n"), f"b_major must be 'k' or 'n', got {self.b_major}")
         self._b_nmajor = self.b_major == "n"
         if self.b is not None:
             # dense weights: the strides say which way B is stored (the reference accepts both for fp8)
-            if n > 1 and k > 1 and self.b.stride[0] == 1 and self.b.stride[1] == n:
+            if n > 1 and k > 1 and self.b.stride[0] == 1 and self.b.stride[1] == n and not self._is_fp4x2(self.b.dtype):
                 self._check_stride(self.b, (1, n, n * k), "For fp8 ab_dtype, B must have k- or n-major layout")
                 self._b_nmajor = True
             else:
-                self._check_stride(self.b, (k, 1, n * k), "For fp8 ab_dtype, B must have k- or n-major layout")
+                self._check_stride(b_l, (k, 1, n * k), "For fp4 ab_dtype, B must have k-major layout" if self._is_fp4x2(self.b.dtype) else "For fp8 ab_dtype, B must have k- or n-major layout")
                 self._b_nmajor = False
         self._check_stride(self.d, (n, 1, tensor_m * n), "D must have n-major layout")
         self._check_stride(self.d_col, (n, 1, tensor_m * n), "D_col must have n-major layout")
@@ -195,6 +197,13 @@ class GroupedGemmQuantSm100(OperatorBase):
             self.d, [torch.float16, torch.bfloat16, torch.float32, torch.float8_e4m3fn, torch.float8_e5m2, torch.float4_e2m1fn_x2], "D"
         )
         self._check_dtype(self.d_col, self.d_dtype, "D_col", "D_col must have the same dtype as D")
+        fp4 = self._is_fp4x2(self.ab_dtype)
+        self._value_error_if(fp4 and self.d_dtype not in (torch.float16, torch.bfloat16, torch.float32), "D must be fp16, bf16, or float32 when ab_dtype is fp4")
+        self._not_implemented_error_if(
+            fp4 and self.sf_vec_size == 16 and self.d_dtype == torch.float32,
+            "Invalid configuration: fp4 ab_dtype, sf_vec_size 16, d_dtype float32 is not supported. Please use sf_vec_size 32 or d_dtype bf16 instead",
+        )
+        self._value_error_if(fp4 and self.b_major != "k", "b_major must be 'k' when ab_dtype is fp4")
         self._check_dtype(self.padded_offsets, torch.int32, "padded_offsets")
         self._check_dtype(self.alpha, torch.float32, "alpha")
         self._check_dtype(self.prob, torch.float32, "prob")
@@ -202,7 +211,7 @@ class GroupedGemmQuantSm100(OperatorBase):
         self._check_dtype(self.norm_const, torch.float32, "norm_const")
 
         check_tile_and_cluster(self, self.mma_tiler_mn, self.cluster_shape_mn, self.m_aligned, only_n256=True)
-        self._value_error_if(k % 16 != 0 or n % 16 != 0, "Invalid tensor alignment: tensors must be 16B aligned")
+        self._value_error_if(k % (32 if fp4 else 16) != 0 or n % 16 != 0, "Invalid tensor alignment: tensors must be 16B aligned")
         if self.expert_cnt > 1024:
             raise ValueError(f"expert_cnt must be <= 1024, got {self.expert_cnt}")
 
@@ -210,9 +219,14 @@ class GroupedGemmQuantSm100(OperatorBase):
             # (n, l) with stride (1, n), as the reference demands
             self._check_stride(self.bias, (1, n), "bias must have stride (1, n)")
             self._check_dtype(self.bias, [torch.bfloat16, torch.float16, torch.float32], "bias")
-        self._not_implemented_error_if(self.ab_dtype not in (torch.float8_e4m3fn, torch.float8_e5m2), f"only MXFP8 (E4M3 or E5M2) inputs are built, got {self.ab_dtype}")
-        self._not_implemented_error_if(self.sf_dtype != torch.float8_e8m0fnu, f"only E8M0 scale factors are built, got {self.sf_dtype}")
-        self._not_implemented_error_if(self.d_dtype not in (torch.bfloat16, torch.float16, torch.float8_e4m3fn, torch.float8_e5m2), f"only bf16, fp16, E4M3 and E5M2 D are built, got {self.d_dtype}")
+        self._not_implemented_error_if(self.ab_dtype == torch.uint8, "uint8 (raw packed FP4) operands are not built: pass float4_e2m1fn_x2 tensors")
+        self._not_implemented_error_if(self.sf_dtype == torch.float8_e4m3fn and not fp4, f"E4M3 scale factors go with FP4 operands, got {self.ab_dtype}")
+        self._not_implemented_error_if(fp4 and k % 64 != 0, f"FP4 operands need k to be a multiple of 64, got {k}")
+        self._not_implemented_error_if(fp4 and self.generate_sfd, "scale-factor generation is built for fp8 operands only")
+        self._not_implemented_error_if(
+            self.d_dtype not in (torch.bfloat16, torch.float16, torch.float8_e4m3fn, torch.float8_e5m2) and not (fp4 and self.d_dtype == torch.float32),
+            f"only bf16, fp16, E4M3 and E5M2 D (and float32 D with FP4 operands) are built, got {self.d_dtype}",
+        )
         self._not_implemented_error_if(not self.generate_sfd and self.d_dtype in (torch.float8_e4m3fn, torch.float8_e5m2), "FP8 D needs sfd_row, sfd_col and norm_const")
         self._value_error_if(n % 32 != 0, f"n must be a multiple of 32, got {n}")
         self._n, self._k = n, k
@@ -297,7 +311,8 @@ class GroupedGemmQuantSm100(OperatorBase):
             norm_const=norm_const_tensor if gen else None,
             d=d_tensor,
             d_col=d_col_tensor if gen and sfd_col_tensor is not None else None,
-            amax=None if fp8_out else amax_tensor,  # the reference has no amax for an FP8 D either
+            amax=None if fp8_out or d_tensor.dtype == torch.float32 else amax_tensor,  # the reference has amax for a 16-bit D only
+            sf_vec_size=self.sf_vec_size,
             sfd_row=sfd_row_tensor if gen else None,
             sfd_col=sfd_col_tensor if gen and d_col_tensor is not None else None,
             workspace=self._workspace,
@@ -356,6 +371,8 @@ def grouped_gemm_quant_wrapper_sm100(
     if not is_dense and not is_discrete:
         raise ValueError("Must provide either (b_tensor, sfb_tensor) or (b_ptrs, sfb_ptrs)")
     valid_m, k, _ = a_tensor.shape
+    if a_tensor.dtype == torch.float4_e2m1fn_x2:
+        k *= 2  # two elements per byte (grouped_gemm_quant/api.py:1204)
     if is_dense:
         n_out, _, l = b_tensor.shape
     else:

@@ -12,8 +12,9 @@ Differences a caller can observe:
 * ``c_tensor=None`` in ``execute`` skips the bf16 pre-activation store (the reference always
   writes C);
 * the wrapper allocates scale-factor outputs only for an fp8 ``d_dtype`` (see its docstring);
-* inputs other than E4M3 data with E8M0 scales per 32 elements (MXFP8), C other than bf16 and
-  D other than bf16 / E4M3 raise ``NotImplementedError``.
+* operands are E4M3 / E5M2 with E8M0 scales per 32 elements (MXFP8) or ``float4_e2m1fn_x2`` with E8M0
+  scales per 32 (MXFP4) or E8M0 / E4M3 scales per 16 (NVFP4); raw ``uint8`` FP4 operands, FP4 / FP8 / float32
+  C, an FP4 D and k that is not a multiple of 64 with FP4 operands raise ``NotImplementedError``.
 """
 
 from __future__ import annotations
@@ -111,11 +112,12 @@ class GroupedGemmSwigluSm100(OperatorBase):
             self.discrete_col_sfd = False
 
         self._value_error_if(len(self.a.shape) != 3 or len(self.b.shape) != 3, "A must be (m, k, 1) and B (n, k, l)")
-        tensor_m, k, _ = self.a.shape
-        n, _, l = self.b.shape
+        a_l, b_l = self.a.logical(), self.b.logical()  # FP4 operands: two elements per byte along K
+        tensor_m, k, _ = a_l.shape
+        n, _, l = b_l.shape
         n_2 = n // 2
-        self._check_shape(self.a, (tensor_m, k, 1), "A")
-        self._check_shape(self.b, (n, k, l), "B")
+        self._check_shape(a_l, (tensor_m, k, 1), "A")
+        self._check_shape(b_l, (n, k, l), "B")
         self._check_shape(self.c, (tensor_m, n, 1), "C")
         self._check_shape(self.d, (tensor_m, n_2, 1), "D")
         self._check_shape(self.d_col, (tensor_m, n_2, 1), "D_col")
@@ -132,8 +134,8 @@ class GroupedGemmSwigluSm100(OperatorBase):
         self._check_shape(self.norm_const, (1,), "norm_const")
         self._check_shape(self.padded_offsets, (l,), "padded_offsets")
 
-        self._check_stride(self.a, (k, 1, tensor_m * k), "A must have k-major layout")
-        self._check_stride(self.b, (k, 1, n * k), "B must have k-major layout")
+        self._check_stride(a_l, (k, 1, tensor_m * k), "A must have k-major layout")
+        self._check_stride(b_l, (k, 1, n * k), "B must have k-major layout")
         self._check_stride(self.c, (n, 1, tensor_m * n), "C must have n-major layout")
         self._check_stride(self.d, (n_2, 1, tensor_m * n_2), "D must have n-major layout")
         self._check_stride(self.d_col, (n_2, 1, tensor_m * n_2), "D_col must have n-major layout")
@@ -157,6 +159,12 @@ class GroupedGemmSwigluSm100(OperatorBase):
             self.d, [torch.float16, torch.bfloat16, torch.float32, torch.float8_e4m3fn, torch.float8_e5m2, torch.float4_e2m1fn_x2], "D"
         )
         self._check_dtype(self.d_col, self.d_dtype, "D_col", "D_col must have the same dtype as D")
+        fp4 = self._is_fp4x2(self.ab_dtype)
+        self._value_error_if(fp4 and self.d_dtype not in (torch.float16, torch.bfloat16, torch.float32), "D must be fp16, bf16, or float32 when ab_dtype is fp4")
+        self._not_implemented_error_if(
+            fp4 and self.sf_vec_size == 16 and self.d_dtype == torch.float32,
+            "Invalid configuration: fp4 ab_dtype, sf_vec_size 16, d_dtype float32 is not supported. Please use sf_vec_size 32 or d_dtype bf16 instead",
+        )
         self._check_dtype(self.padded_offsets, torch.int32, "padded_offsets")
         self._check_dtype(self.alpha, torch.float32, "alpha")
         self._check_dtype(self.prob, torch.float32, "prob")
@@ -164,7 +172,7 @@ class GroupedGemmSwigluSm100(OperatorBase):
         self._check_dtype(self.norm_const, torch.float32, "norm_const")
 
         check_tile_and_cluster(self, self.mma_tiler_mn, self.cluster_shape_mn, self.m_aligned, only_n256=False)
-        self._value_error_if(k % 16 != 0 or n % 16 != 0, "Invalid tensor alignment: tensors must be 16B aligned")
+        self._value_error_if(k % (32 if fp4 else 16) != 0 or n % 16 != 0, "Invalid tensor alignment: tensors must be 16B aligned")
         if self.expert_cnt > 1024:
             raise ValueError(f"expert_cnt must be <= 1024, got {self.expert_cnt}")
         self._not_implemented_error_if(
@@ -172,11 +180,18 @@ class GroupedGemmSwigluSm100(OperatorBase):
             "Invalid configuration: fp8 ab_dtype and sf_vec_size 32 with mma_tiler_mn[1] == 128 and fp8 d_dtype is not supported. Please use mma_tiler_mn[1] == 256 instead",
         )
 
+        self._not_implemented_error_if(fp4 and self.c is not None and self.c_dtype not in (torch.float16, torch.bfloat16), f"Invalid configuration: for fp4 ab_dtype, c_dtype must be float16 or bfloat16, got {self.c_dtype}")
+
         # what this build implements of the reference's surface
-        self._not_implemented_error_if(self.ab_dtype not in (torch.float8_e4m3fn, torch.float8_e5m2), f"only MXFP8 (E4M3 or E5M2) inputs are built, got {self.ab_dtype}")
-        self._not_implemented_error_if(self.sf_dtype != torch.float8_e8m0fnu, f"only E8M0 scale factors are built, got {self.sf_dtype}")
+        self._not_implemented_error_if(self.ab_dtype == torch.uint8, "uint8 (raw packed FP4) operands are not built: pass float4_e2m1fn_x2 tensors")
+        self._not_implemented_error_if(self.sf_dtype == torch.float8_e4m3fn and not fp4, f"E4M3 scale factors go with FP4 operands, got {self.ab_dtype}")
+        self._not_implemented_error_if(fp4 and k % 64 != 0, f"FP4 operands need k to be a multiple of 64, got {k}")
+        self._not_implemented_error_if(fp4 and self.generate_sfd, "scale-factor generation is built for fp8 operands only")
         self._not_implemented_error_if(self.c is not None and self.c_dtype not in (torch.bfloat16, torch.float16), f"only bf16 and fp16 C are built, got {self.c_dtype}")
-        self._not_implemented_error_if(self.d_dtype not in (torch.bfloat16, torch.float16, torch.float8_e4m3fn, torch.float8_e5m2), f"only bf16, fp16, E4M3 and E5M2 D are built, got {self.d_dtype}")
+        self._not_implemented_error_if(
+            self.d_dtype not in (torch.bfloat16, torch.float16, torch.float8_e4m3fn, torch.float8_e5m2) and not (fp4 and self.d_dtype == torch.float32),
+            f"only bf16, fp16, E4M3 and E5M2 D (and float32 D with FP4 operands) are built, got {self.d_dtype}",
+        )
         self._not_implemented_error_if(not self.generate_sfd and self.d_dtype in (torch.float8_e4m3fn, torch.float8_e5m2), "FP8 D needs sfd_row, sfd_col and norm_const")
         self._value_error_if(n % 64 != 0, f"n must be a multiple of 64 (32-column gate / up blocks), got {n}")
         self._value_error_if(self.generate_sfd and self.d_col is None, "sample_d_col is required when scale factors are generated")
@@ -226,7 +241,7 @@ class GroupedGemmSwigluSm100(OperatorBase):
         reference either) says that ``padded_offsets`` is a view one element into a longer array whose element
         before it is the first row of expert 0."""
         self._ensure_compiled()
-        tensor_m, k = a_tensor.shape[0], a_tensor.shape[1]
+        tensor_m = a_tensor.shape[0]
         if tensor_m == 0:
             return
         if (bias_tensor is not None) != (self.bias is not None):
@@ -247,7 +262,8 @@ class GroupedGemmSwigluSm100(OperatorBase):
             c=c_tensor,
             d=d_tensor,
             d_col=d_col_tensor if gen and sfd_col_tensor is not None else None,
-            amax=None if fp8_out else amax_tensor,  # the reference has no amax for an FP8 D either
+            amax=None if fp8_out or d_tensor.dtype == torch.float32 else amax_tensor,  # the reference has amax for a 16-bit D only
+            sf_vec_size=self.sf_vec_size,
             sfd_row=sfd_row_tensor if gen else None,
             sfd_col=sfd_col_tensor if gen and d_col_tensor is not None else None,
             n=n,

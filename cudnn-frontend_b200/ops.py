@@ -128,6 +128,7 @@ def launch_grouped_gemm(
     test_skip_b_loads: bool = False,
     stream_m_tiles: Optional[int] = None,
     offsets_have_prev: bool = False,
+    sf_vec_size: int = 32,
 ) -> None:
     """Fill the C struct and call b200moe_fc1_swiglu / b200moe_fc2_quant.
 
@@ -144,7 +145,9 @@ def launch_grouped_gemm(
     library's default or ``B200MOE_LIGHT_M_TILES``, ``-1`` = experts in order); ``stream_m_tiles``: weight tiles of
     experts with at most that many row tiles are read with an evict-first L2 hint (``None`` = default or
     ``B200MOE_STREAM_M_TILES``, ``-1`` = no hints).  ``wait_limit_ms`` and
-    ``test_skip_b_loads`` drive the bounded-wait test hook.  ``offsets_have_prev``: ``padded_offsets`` is a view that
+    ``test_skip_b_loads`` drive the bounded-wait test hook.  ``k`` counts elements: with ``float4_e2m1fn_x2``
+    operands (two per byte) it is twice the byte width of ``a``; ``sf_vec_size`` is 32, or 16 with FP4 operands,
+    and the scale-factor type (E8M0 or E4M3) is taken from ``sfa``.  ``offsets_have_prev``: ``padded_offsets`` is a view that
     starts one element into a longer int32 array whose element before it is the first row of expert 0 (a
     layer that runs row ranges of its expert groups passes clamped offsets this way)."""
     _require_cuda(a, sfa, padded_offsets, alpha, d, b, sfb, b_ptrs, sfb_ptrs, prob, norm_const, c, d_col, amax, sfd_row, sfd_col)
@@ -196,7 +199,7 @@ def launch_grouped_gemm(
         stream_m_tiles = int(os.environ.get("B200MOE_STREAM_M_TILES", "0"))
     args.l2_stream_m_tiles = int(stream_m_tiles)
     if d.dtype not in _D_DTYPES:
-        raise NotImplementedError(f"D dtype {d.dtype} is not built (bf16, fp16, E4M3, E5M2 are)")
+        raise NotImplementedError(f"D dtype {d.dtype} is not built (bf16, fp16, float32, E4M3, E5M2 are)")
     args.d_dtype = _D_DTYPES[d.dtype]
     if c is not None and c.dtype not in (torch.bfloat16, torch.float16):
         raise NotImplementedError(f"C dtype {c.dtype} is not built (bf16 and fp16 are)")
@@ -221,13 +224,15 @@ def launch_grouped_gemm(
     if act_func not in ("swiglu", "geglu"):
         raise ValueError(f"act_func must be 'swiglu' or 'geglu', got {act_func!r}")
     args.act_func = _lib.ACT_GEGLU if act_func == "geglu" else _lib.ACT_SWIGLU
-    if a.dtype == torch.float8_e5m2:
-        other = b.dtype if b is not None else torch.float8_e5m2  # discrete weights: the caller vouches for the pointers
-        if other != torch.float8_e5m2:
+    if a.dtype in (torch.float8_e5m2, torch.float4_e2m1fn_x2):
+        other = b.dtype if b is not None else a.dtype  # discrete weights: the caller vouches for the pointers
+        if other != a.dtype:
             raise ValueError("A and B must have the same element type")
-        args.ab_dtype = _lib.DTYPE_E5M2
+        args.ab_dtype = _lib.DTYPE_E5M2 if a.dtype == torch.float8_e5m2 else _lib.DTYPE_E2M1
     else:
         args.ab_dtype = _lib.DTYPE_E4M3
+    args.sf_vec_size = int(sf_vec_size)
+    args.sf_dtype = _lib.DTYPE_E4M3 if sfa.dtype == torch.float8_e4m3fn else 0
     lib = _lib.load()
     fn = lib.b200moe_fc1_swiglu if kind == "fc1" else lib.b200moe_fc2_quant
     with torch.cuda.device(a.device):
@@ -236,7 +241,7 @@ def launch_grouped_gemm(
 
 
 _D_DTYPES = {torch.bfloat16: _lib.DTYPE_BF16, torch.float16: _lib.DTYPE_F16, torch.float8_e4m3fn: _lib.DTYPE_E4M3,
-             torch.uint8: _lib.DTYPE_E4M3, torch.float8_e5m2: _lib.DTYPE_E5M2}
+             torch.uint8: _lib.DTYPE_E4M3, torch.float8_e5m2: _lib.DTYPE_E5M2, torch.float32: _lib.DTYPE_F32}
 _BIAS_DTYPES = {torch.bfloat16: _lib.DTYPE_BF16, torch.float16: _lib.DTYPE_F16, torch.float32: _lib.DTYPE_F32}
 
 
@@ -334,7 +339,7 @@ def grouped_gemm_op(kind: str, *, stream=None, **kw) -> None:
         a = kw["a"]
         launch_grouped_gemm(
             kind, a=a, sfa=kw["sfa"], padded_offsets=kw["padded_offsets"], alpha=kw["alpha"], d=kw["d"], m_rows=a.shape[0], n=kw["n"],
-            k=a.shape[1], num_experts=kw["padded_offsets"].shape[0], b=kw.get("b"), sfb=kw.get("sfb"), b_ptrs=kw.get("b_ptrs"),
+            k=a.shape[1] * (2 if a.dtype == torch.float4_e2m1fn_x2 else 1), sf_vec_size=int(kw.get("sf_vec_size", 32)), num_experts=kw["padded_offsets"].shape[0], b=kw.get("b"), sfb=kw.get("sfb"), b_ptrs=kw.get("b_ptrs"),
             sfb_ptrs=kw.get("sfb_ptrs"), prob=kw.get("prob"), norm_const=kw.get("norm_const"), c=kw.get("c") if kind == "fc1" else None,
             d_col=kw.get("d_col"), amax=kw.get("amax"), sfd_row=kw.get("sfd_row"), sfd_col=kw.get("sfd_col"),
             workspace=kw.get("workspace"), discrete_col_sfd=bool(kw.get("discrete_col_sfd", False)), sm_margin=int(kw.get("sm_margin", 0)),
@@ -353,6 +358,8 @@ def grouped_gemm_op(kind: str, *, stream=None, **kw) -> None:
               kw["alpha"], kw.get("prob"), kw.get("norm_const"))  # fmt: skip
     if kw.get("expert_range") is not None or kw.get("test_skip_b_loads") or kw.get("offsets_have_prev"):
         raise NotImplementedError("expert_range and the test hook are eager-only launch options")
+    if kw["a"].dtype == torch.float4_e2m1fn_x2:
+        raise NotImplementedError("FP4 operands are launched eagerly only (the custom-op schema carries 8-bit operands)")
     tail = (kw["n"], bool(kw.get("discrete_col_sfd", False)), int(kw.get("sm_margin", 0)), kw.get("tile_mode") or "")
     sched = (bool(kw.get("dynamic_sched", False)), bool(kw.get("b_nmajor", False)))
     outs = (kw["d"], kw.get("d_col"), kw.get("amax"), kw.get("sfd_row"), kw.get("sfd_col"), kw.get("workspace"))

@@ -37,6 +37,7 @@ extern "C" {
 #define B200MOE_DTYPE_F16 2
 #define B200MOE_DTYPE_F32 3
 #define B200MOE_DTYPE_E5M2 4
+#define B200MOE_DTYPE_E2M1 5 /* FP4, two values per byte, the even element in the low nibble */
 
 #define B200MOE_ACT_SWIGLU 0
 #define B200MOE_ACT_GEGLU 1
@@ -71,9 +72,9 @@ extern "C" {
  * Arguments of one grouped GEMM launch.  All pointers are device pointers.
  *
  * Layouts (the reference's, python/cudnn/grouped_gemm/grouped_gemm_swiglu/api.py:193-247):
- *   a      [m_rows, k]  E4M3, K contiguous
- *   sfa    E8M0, "128x4" swizzled layout of (m_rows, k/32)
- *   b      [E, n, k]    E4M3, K contiguous (dense mode)           | exactly one of
+ *   a      [m_rows, k]  E4M3 / E5M2 (or k / 2 bytes of packed E2M1), K contiguous
+ *   sfa    E8M0 (or E4M3), "128x4" swizzled layout of (m_rows, k / sf_vec_size)
+ *   b      [E, n, k]    same element type as a, K contiguous (dense mode) | exactly one of
  *   sfb    E blocks, each the 128x4 layout of (n, k/32)           | (b, sfb) and
  *   b_ptrs / sfb_ptrs   int64 device arrays [E] of per-expert     | (b_ptrs, sfb_ptrs)
  *                       addresses of [n, k] / its 128x4 layout    | is non-NULL
@@ -152,6 +153,14 @@ typedef struct b200moe_gemm_args {
      they are used once or twice and should not displace activations and shared weight tiles
      (0 = the library's default, -1 = no hints) */
   int32_t l2_stream_m_tiles;
+  /* Block scaling of A and B (python/cudnn/grouped_gemm/grouped_gemm_swiglu/api.py:249-352).  sf_vec_size:
+     elements of K per scale factor, 32 (also when left 0) or 16; sf_dtype: 0 = E8M0, B200MOE_DTYPE_E4M3 =
+     E4M3 read as unsigned (sf_vec_size 16 only).  8-bit operands (ab_dtype E4M3 / E5M2) take E8M0 per 32
+     (MXFP8).  ab_dtype B200MOE_DTYPE_E2M1: a and b hold k / 2 bytes per row and k counts elements; E8M0
+     per 32 (MXFP4), E8M0 per 16, or E4M3 per 16 (NVFP4); k must be a multiple of 64, B K-major, D bf16 /
+     fp16 (with amax) or float32, no scale-factor generation (the reference's rules for FP4 operands). */
+  int32_t sf_vec_size;
+  int32_t sf_dtype;
 } b200moe_gemm_args;
 
 /*

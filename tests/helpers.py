@@ -19,6 +19,19 @@ def gen_operands(seed, m_rows, n, k, e, sf_lo=124, sf_hi=131, scale=2.0, dtype=t
     return a, b, sfa, sfb
 
 
+def gen_operands_fp4(seed, m_rows, n, k, e, sf_vec=16, sf_dtype="e4m3"):
+    """Random packed E2M1 bytes ([rows, k/2], every nibble pattern) and scale bytes per ``sf_vec`` elements:
+    E8M0 in [124, 131) or positive E4M3 in [0.5, 3.5]."""
+    g = torch.Generator().manual_seed(seed)
+    a = torch.randint(0, 256, (m_rows, k // 2), generator=g, dtype=torch.int32).to(torch.uint8).numpy()
+    b = torch.randint(0, 256, (e, n, k // 2), generator=g, dtype=torch.int32).to(torch.uint8).numpy()
+    kb = (k + sf_vec - 1) // sf_vec
+    lo, hi = (0x30, 0x46) if sf_dtype == "e4m3" else (124, 131)
+    sfa = torch.randint(lo, hi, (m_rows, kb), generator=g, dtype=torch.int32).to(torch.uint8).numpy()
+    sfb = torch.randint(lo, hi, (e, n, kb), generator=g, dtype=torch.int32).to(torch.uint8).numpy()
+    return a, b, sfa, sfb
+
+
 def zero_padding_rows(a, groups, aligned):
     start = 0
     for g_, al in zip(groups, aligned):
@@ -31,14 +44,14 @@ def dev_fp8(x, device="cuda", dtype=torch.float8_e4m3fn):
     return torch.from_numpy(np.ascontiguousarray(x)).to(device).view(dtype)
 
 
-def dev_sf(sf_bytes, mn, k, l=1, device="cuda"):
-    """[L, MN, KB] / [MN, KB] E8M0 bytes -> 6-D float8_e8m0fnu tensor in the 128x4 layout.
+def dev_sf(sf_bytes, mn, k, l=1, device="cuda", sf_vec=32, dtype=torch.float8_e8m0fnu):
+    """[L, MN, KB] / [MN, KB] scale bytes -> 6-D tensor (E8M0, or E4M3 with ``dtype``) in the 128x4 layout.
     Unused bytes of the layout are set to 0xFF (NaN) on purpose: nothing may depend on them."""
     from cudnn_frontend_b200 import ops
 
     flat = torch.from_numpy(orc.sf_pack(sf_bytes, fill=0xFF)).to(device)
-    shape, stride = ops.sf_shape_stride(mn, k, l)
-    return torch.as_strided(flat.view(torch.float8_e8m0fnu), shape, stride)
+    shape, stride = ops.sf_shape_stride(mn, k, l, sf_vec)
+    return torch.as_strided(flat.view(dtype), shape, stride)
 
 
 def sf_to_numpy(sf6d, mn, kb, l=1):

