@@ -361,6 +361,106 @@ def run_case_glu(name, cfg, out):
         )
 
 
+def run_case_fp4(name, cfg, out):
+    """FC1 with FP4 operands (float4_e2m1fn_x2): bf16 C and bf16 D, no scale-factor generation.
+    cfg["sf"] = (sf_vec_size, "e8m0" | "e4m3")."""
+    import cuda.bindings.driver as cuda
+    import cudnn as ref  # the overlay
+
+    import cudnn_frontend_b200 as ours
+    from cudnn_frontend_b200 import ops, synthetic
+
+    e, n, k = cfg["experts"], cfg["n"], cfg["k"]
+    sf_vec, sf_kind = cfg["sf"]
+    sf_dtype = torch.float8_e4m3fn if sf_kind == "e4m3" else torch.float8_e8m0fnu
+    r = synthetic.make_routing(cfg["tokens"], e, cfg["topk"], cfg["routing"], 3, "cuda", 256)
+    m = r.m_rows
+    g = torch.Generator(device="cuda").manual_seed(17)
+    a8 = torch.randint(0, 256, (m, k // 2), generator=g, device="cuda", dtype=torch.int32).to(torch.uint8)
+    # padding rows of every group are zero (amax covers them)
+    ends = r.padded_offsets.long()
+    starts = torch.cat([ends.new_zeros(1), ends[:-1]])
+    rows = torch.arange(m, device="cuda")
+    owner = torch.searchsorted(ends, rows, right=True).clamp(max=e - 1)
+    a8[(rows - starts[owner]) >= r.counts.long()[owner]] = 0
+    b8 = torch.randint(0, 256, (e, n, k // 2), generator=g, device="cuda", dtype=torch.int32).to(torch.uint8)
+    a = torch.as_strided(a8.view(torch.float4_e2m1fn_x2), (m, k // 2, 1), (k // 2, 1, m * k // 2))
+    b = b8.view(torch.float4_e2m1fn_x2).permute(1, 2, 0)
+    lo, hi = (0x30, 0x46) if sf_kind == "e4m3" else (124, 131)
+
+    def rand_sf(mn, l):
+        t = ops.empty_sf(mn, k, l, device="cuda", dtype=sf_dtype, sf_vec=sf_vec)
+        flat_ = torch.as_strided(t.view(torch.uint8), (t.numel(),), (1,))
+        flat_.copy_(torch.randint(lo, hi, (t.numel(),), generator=g, device="cuda", dtype=torch.int32).to(torch.uint8))
+        return t
+
+    sfa, sfb = rand_sf(m, 1), rand_sf(n, e)
+    alpha = torch.ones(e, device="cuda")
+    prob = torch.zeros(m, device="cuda")
+    prob[r.dst_row.long()] = r.topk_prob.reshape(-1)
+    prob = prob.view(m, 1, 1)
+    stream = cuda.CUstream(torch.cuda.current_stream().cuda_stream)
+    res = {"case": name, "op": "fc1_fp4", "cfg": {k_: v for k_, v in cfg.items()}, "m_rows": m, "flops": 2.0 * r.routed_rows * n * k}
+
+    # Through the operator classes with no amax tensor: the reference's amax code (its atomic_max_float32) does not
+    # compile with the CuTe DSL release of this image, and its wrapper always allocates amax for a bf16 D.
+    def outputs():
+        return dict(c_tensor=torch.empty_strided((m, n, 1), (n, 1, m * n), dtype=torch.bfloat16, device="cuda"),
+                    d_tensor=torch.empty_strided((m, n // 2, 1), (n // 2, 1, m * n // 2), dtype=torch.bfloat16, device="cuda"))  # fmt: skip
+
+    r_ref, r_own = outputs(), outputs()
+    d_col_dummy = torch.empty_like(r_ref["d_tensor"])
+    mk = dict(sample_prob=prob, mma_tiler_mn=(256, 256), sf_vec_size=sf_vec, m_aligned=256)
+    op_ref = ref.GroupedGemmSwigluSm100(a, b, r_ref["c_tensor"], r_ref["d_tensor"], sfa, sfb, r.padded_offsets, alpha, d_col_dummy, **mk)
+    op_own = ours.GroupedGemmSwigluSm100(a, b, r_own["c_tensor"], r_own["d_tensor"], sfa, sfb, r.padded_offsets, alpha, None, **mk)
+    t0 = time.time()
+    assert op_ref.check_support()
+    op_ref.compile()
+    assert op_own.check_support()
+    op_own.compile()
+
+    def run_ref():
+        op_ref.execute(a, b, r_ref["c_tensor"], r_ref["d_tensor"], sfa, sfb, r.padded_offsets, alpha, d_col_tensor=d_col_dummy, prob_tensor=prob,
+                       current_stream=stream)  # fmt: skip
+
+    def run_own():
+        op_own.execute(a, b, r_own["c_tensor"], r_own["d_tensor"], sfa, sfb, r.padded_offsets, alpha, prob_tensor=prob)
+
+    run_ref()
+    torch.cuda.synchronize()
+    res["ref_first_call_s"] = time.time() - t0
+    run_own()
+    torch.cuda.synchronize()
+    if PROFILE_ONLY:
+        run_ref()
+        run_own()
+        torch.cuda.synchronize()
+        return
+    bits = lambda t: t[:m, :, 0].contiguous().view(torch.int16)  # noqa: E731
+    res["c_equal_frac"] = float((bits(r_ref["c_tensor"]) == bits(r_own["c_tensor"])).float().mean())
+    res["d_equal_frac"] = float((bits(r_ref["d_tensor"]) == bits(r_own["d_tensor"])).float().mean())
+    if not name.startswith("fp4_tiny"):
+        il_ref, il_own = timed_interleaved(run_ref, run_own, rounds=12)
+        res["ref_ms_interleaved"], res["own_ms_interleaved"] = il_ref, il_own
+        res["own_over_ref_interleaved"] = il_ref / il_own
+        res["ref_tflops_interleaved"] = res["flops"] / (il_ref * 1e-3) / 1e12
+        res["own_tflops_interleaved"] = res["flops"] / (il_own * 1e-3) / 1e12
+    out.append(res)
+    print(json.dumps(res), flush=True)
+    if name.startswith("fp4_tiny"):
+        def flat(t):
+            t = t.view(torch.uint8)
+            return torch.as_strided(t, (t.numel(),), (1,))
+
+        np.savez_compressed(
+            os.path.join(OUT_DIR, f"reference_kernel_{name}_golden.npz"),
+            a=a8.cpu().numpy(), b=b8.cpu().numpy(), sfa=flat(sfa).cpu().numpy(), sfb=flat(sfb).cpu().numpy(),
+            offsets=r.padded_offsets.cpu().numpy(), prob=prob.view(-1).cpu().numpy(),
+            c=bits(r_ref["c_tensor"]).cpu().numpy(), d=bits(r_ref["d_tensor"]).cpu().numpy(),
+            sf_vec=np.int32(sf_vec), sf_is_e4m3=np.int32(sf_kind == "e4m3"),
+        )  # fmt: skip
+
+
 PROFILE_ONLY = False
 OWN_FIRST = False
 
@@ -390,6 +490,14 @@ FC2_CASES = ("fc2_tiny", "fc2_mixtral", "c4", "fc2_mid")
 CASES["glu_tiny"] = dict(experts=2, k=128, n=128, tokens=128, topk=2, routing="uniform")
 CASES["glu_mid"] = dict(experts=8, k=4096, n=7168, tokens=4096, topk=2, routing="uniform")
 GLU_CASES = ("glu_tiny", "glu_mid")
+# FP4 operands: NVFP4 (E4M3 scales per 16), MXFP4 (E8M0 per 32) and E8M0 per 16; the tiny ones record fixtures
+# (two k-tiles of 256 elements deep), the others compare speed
+CASES["fp4_tiny_nvfp4"] = dict(experts=2, k=512, n=128, tokens=128, topk=2, routing="uniform", sf=(16, "e4m3"))
+CASES["fp4_tiny_mxfp4"] = dict(experts=2, k=512, n=128, tokens=128, topk=2, routing="uniform", sf=(32, "e8m0"))
+CASES["fp4_tiny_e8m0x16"] = dict(experts=2, k=512, n=128, tokens=128, topk=2, routing="uniform", sf=(16, "e8m0"))
+CASES["fp4_mid_nvfp4"] = dict(experts=8, k=4096, n=7168, tokens=4096, topk=2, routing="uniform", sf=(16, "e4m3"))
+CASES["fp4_c2_nvfp4"] = dict(experts=8, k=4096, n=28672, tokens=16384, topk=2, routing="uniform", sf=(16, "e4m3"))
+CASES["fp4_c2_mxfp4"] = dict(experts=8, k=4096, n=28672, tokens=16384, topk=2, routing="uniform", sf=(32, "e8m0"))
 
 
 def main():
@@ -409,7 +517,8 @@ def main():
     out = []
     for name in args.cases.split(","):
         try:
-            (run_case_glu if name in GLU_CASES else run_case_fc2 if name in FC2_CASES else run_case)(name, CASES[name], out)
+            (run_case_fp4 if name.startswith("fp4_") else run_case_glu if name in GLU_CASES else run_case_fc2 if name in FC2_CASES else run_case)(
+                name, CASES[name], out)
         except Exception as exc:  # keep going: a JIT failure of one case is a result too
             out.append({"case": name, "error": f"{type(exc).__name__}: {exc}"})
             traceback.print_exc()

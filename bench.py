@@ -594,6 +594,8 @@ def bench_single(args):
             torch.cuda.empty_cache()
         extras.update(bench_other_configs(dev, stream, peaks))
         torch.cuda.empty_cache()
+        extras.update(bench_fp4(dev, stream))
+        torch.cuda.empty_cache()
         import ep_bench
 
         # the workload of the multi-GPU runs (--gpus 2/4/8) with all experts on this GPU
@@ -732,6 +734,45 @@ def bench_other_configs(dev, stream, peaks):
                                              norm_const_tensor=norm, prob_tensor=p3["prob"]), stream)  # fmt: skip
         out["deepseek_fc2_quant" + ("_dynamic_sched" if dyn else "")] = report(t4, flops4, bytes4)
     out["protocol"] = "3 warm-ups, 10 trials with a 256 MiB L2 flush between them, median (ms) and best (ms_best)"
+    return out
+
+
+def bench_fp4(dev, stream):
+    """The Mixtral-shape FC1 with FP4 operands (random E2M1 bytes; E4M3 scales per 16 = NVFP4, E8M0 per 32 =
+    MXFP4), bf16 D + amax, same rows and offsets as the headline: reported beside it."""
+    import torch
+
+    import cudnn_frontend_b200 as cf
+    from cudnn_frontend_b200 import ops, synthetic
+
+    cfg = synthetic.CONFIGS["c2"]
+    e, n, k = cfg["experts"], cfg["n"], cfg["k"]
+    r = synthetic.make_routing(cfg["tokens"], e, cfg["topk"], cfg["routing"], 0, dev, 128)
+    m = r.m_rows
+    g = torch.Generator(device=dev).manual_seed(5)
+    a8 = torch.randint(0, 256, (m, k // 2), generator=g, device=dev, dtype=torch.int32).to(torch.uint8)
+    b8 = torch.randint(0, 256, (e, n, k // 2), generator=g, device=dev, dtype=torch.int32).to(torch.uint8)
+    a = torch.as_strided(a8.view(torch.float4_e2m1fn_x2), (m, k // 2, 1), (k // 2, 1, m * k // 2))
+    b = b8.view(torch.float4_e2m1fn_x2).permute(1, 2, 0)
+    d = torch.empty((m, n // 2, 1), dtype=torch.bfloat16, device=dev)
+    amax = torch.full((e, 1), float("-inf"), dtype=torch.float32, device=dev)
+    alpha = torch.ones(e, device=dev)
+    flops = 2.0 * r.routed_rows * n * k
+    out = {}
+    for name, sf_vec, sf_dtype, lo, hi in (("nvfp4", 16, torch.float8_e4m3fn, 0x30, 0x46), ("mxfp4", 32, torch.float8_e8m0fnu, 124, 131)):
+        def rand_sf(mn, l):
+            t = ops.empty_sf(mn, k, l, device=dev, dtype=sf_dtype, sf_vec=sf_vec)
+            flat = torch.as_strided(t.view(torch.uint8), (t.numel(),), (1,))
+            flat.copy_(torch.randint(lo, hi, (t.numel(),), generator=g, device=dev, dtype=torch.int32).to(torch.uint8))
+            return t
+
+        sfa, sfb = rand_sf(m, 1), rand_sf(n, e)
+        op = cf.GroupedGemmSwigluSm100(a, b, None, d, sfa, sfb, r.padded_offsets, alpha, None, sample_amax=amax, sf_vec_size=sf_vec, m_aligned=128)
+        assert op.check_support()
+        op.compile()
+        t = time_trials(lambda: op.execute(a, b, None, d, sfa, sfb, r.padded_offsets, alpha, amax_tensor=amax), stream)
+        out["fc1_" + name] = {"tflops": flops / (t["median_ms"] * 1e-3) / 1e12, "timing": t, "pct_of_fp4_nominal_9000": 100.0 * flops / (t["median_ms"] * 1e-3) / 9e15,
+                              "operands": f"E2M1 with {'E4M3' if sf_vec == 16 else 'E8M0'} scales per {sf_vec} elements"}  # fmt: skip
     return out
 
 

@@ -102,13 +102,14 @@ class DiscreteGroupedGemmSwigluSm100(OperatorBase):
         self._value_error_if(self.act_func not in ("swiglu", "geglu"), f"act_func must be 'swiglu' or 'geglu', got {self.act_func}")
         self._value_error_if(self.b_major not in ("k", "n"), f"b_major must be 'k' or 'n', got {self.b_major}")
         self._value_error_if(len(self.a.shape) != 3 or len(self.b_shape) < 2, "A must be (m, k, 1) and b_shape (n, k)")
-        tensor_m, k, _ = self.a.shape
+        a_l = self.a.logical()  # FP4 operands: two elements per byte along K; b_shape counts elements
+        tensor_m, k, _ = a_l.shape
         n, b_k = self.b_shape[0], self.b_shape[1]
         self._value_error_if(b_k != k, f"B K dimension ({b_k}) must match A K dimension ({k})")
         self._value_error_if(self.padded_offsets.shape[0] != self.expert_cnt, f"padded_offsets length ({self.padded_offsets.shape[0]}) must equal num_experts ({self.expert_cnt})")
         n_2 = n // 2
         l = self.expert_cnt
-        self._check_shape(self.a, (tensor_m, k, 1), "A")
+        self._check_shape(a_l, (tensor_m, k, 1), "A")
         self._check_shape(self.c, (tensor_m, n, 1), "C")
         self._check_shape(self.d, (tensor_m, n_2, 1), "D")
         self._check_shape(self.d_col, (tensor_m, n_2, 1), "D_col")
@@ -121,7 +122,7 @@ class DiscreteGroupedGemmSwigluSm100(OperatorBase):
         self._check_shape(self.bias, (n, l), "bias")
         self._check_shape(self.amax, (l, 1), "amax")
         self._check_shape(self.norm_const, (1,), "norm_const")
-        self._check_stride(self.a, (k, 1, tensor_m * k), "A must have k-major layout")
+        self._check_stride(a_l, (k, 1, tensor_m * k), "A must have k-major layout")
         self._check_stride(self.c, (n, 1, tensor_m * n), "C must have n-major layout")
         self._check_stride(self.d, (n_2, 1, tensor_m * n_2), "D must have n-major layout")
         self._check_stride(self.d_col, (n_2, 1, tensor_m * n_2), "D_col must have n-major layout")
@@ -139,19 +140,32 @@ class DiscreteGroupedGemmSwigluSm100(OperatorBase):
         self.c_dtype = self._check_dtype(self.c, [torch.float32, torch.float16, torch.bfloat16, torch.float8_e4m3fn, torch.float8_e5m2], "C")
         self.d_dtype = self._check_dtype(self.d, [torch.float16, torch.bfloat16, torch.float32, torch.float8_e4m3fn, torch.float8_e5m2, torch.float4_e2m1fn_x2], "D")
         self._check_dtype(self.d_col, self.d_dtype, "D_col", "D_col must have the same dtype as D")
+        fp4 = self._is_fp4x2(self.ab_dtype)
+        self._value_error_if(self.sf_dtype == torch.float8_e4m3fn and self.sf_vec_size == 32, f"sf_dtype {self.sf_dtype} and sf_vec_size {self.sf_vec_size} combination is not supported")
+        self._value_error_if(fp4 and self.d_dtype not in (torch.float16, torch.bfloat16, torch.float32), "D must be fp16, bf16, or float32 when ab_dtype is fp4")
+        self._not_implemented_error_if(
+            fp4 and self.sf_vec_size == 16 and self.d_dtype == torch.float32,
+            "Invalid configuration: fp4 ab_dtype, sf_vec_size 16, d_dtype float32 is not supported",
+        )
+        self._value_error_if(fp4 and self.b_major != "k", "b_major must be 'k' when ab_dtype is fp4")
         self._check_dtype(self.padded_offsets, torch.int32, "padded_offsets")
         check_tile_and_cluster(self, self.mma_tiler_mn, self.cluster_shape_mn, self.m_aligned, only_n256=True)
-        self._value_error_if(k % 16 != 0 or n % 16 != 0, "Invalid tensor alignment: tensors must be 16B aligned")
+        self._value_error_if(k % (32 if fp4 else 16) != 0 or n % 16 != 0, "Invalid tensor alignment: tensors must be 16B aligned")
         if self.expert_cnt > 1024:
             raise ValueError(f"expert_cnt must be <= 1024, got {self.expert_cnt}")
 
         if self.bias is not None:
             self._check_stride(self.bias, (1, n), "bias must have stride (1, n)")
             self._check_dtype(self.bias, [torch.bfloat16, torch.float16], "bias")
-        self._not_implemented_error_if(self.ab_dtype not in (torch.float8_e4m3fn, torch.float8_e5m2), f"only MXFP8 (E4M3 or E5M2) inputs are built, got {self.ab_dtype}")
-        self._not_implemented_error_if(self.sf_dtype != torch.float8_e8m0fnu, f"only E8M0 scale factors are built, got {self.sf_dtype}")
+        self._not_implemented_error_if(self.ab_dtype == torch.uint8, "uint8 (raw packed FP4) operands are not built: pass float4_e2m1fn_x2 tensors")
+        self._not_implemented_error_if(self.sf_dtype == torch.float8_e4m3fn and not fp4, f"E4M3 scale factors go with FP4 operands, got {self.ab_dtype}")
+        self._not_implemented_error_if(fp4 and k % 64 != 0, f"FP4 operands need k to be a multiple of 64, got {k}")
+        self._not_implemented_error_if(fp4 and self.generate_sfd, "scale-factor generation is built for fp8 operands only")
         self._not_implemented_error_if(self.c is not None and self.c_dtype not in (torch.bfloat16, torch.float16), f"only bf16 and fp16 C are built, got {self.c_dtype}")
-        self._not_implemented_error_if(self.d_dtype not in (torch.bfloat16, torch.float16, torch.float8_e4m3fn, torch.float8_e5m2), f"only bf16, fp16, E4M3 and E5M2 D are built, got {self.d_dtype}")
+        self._not_implemented_error_if(
+            self.d_dtype not in (torch.bfloat16, torch.float16, torch.float8_e4m3fn, torch.float8_e5m2) and not (fp4 and self.d_dtype == torch.float32),
+            f"only bf16, fp16, E4M3 and E5M2 D (and float32 D with FP4 operands) are built, got {self.d_dtype}",
+        )
         self._not_implemented_error_if(not self.generate_sfd and self.d_dtype in (torch.float8_e4m3fn, torch.float8_e5m2), "FP8 D needs sfd_row, sfd_col and norm_const")
         self._value_error_if(n % 64 != 0, f"n must be a multiple of 64 (32-column gate / up blocks), got {n}")
         self._value_error_if(self.generate_sfd and self.d_col is None, "sample_d_col is required when scale factors are generated")
@@ -211,7 +225,8 @@ class DiscreteGroupedGemmSwigluSm100(OperatorBase):
             c=c_tensor,
             d=d_tensor,
             d_col=d_col_tensor if gen and sfd_col_tensor is not None else None,
-            amax=None if fp8_out else amax_tensor,  # the reference has no amax for an FP8 D either
+            amax=None if fp8_out or d_tensor.dtype == torch.float32 else amax_tensor,  # the reference has amax for a 16-bit D only
+            sf_vec_size=self.sf_vec_size,
             sfd_row=sfd_row_tensor if gen else None,
             sfd_col=sfd_col_tensor if gen and d_col_tensor is not None else None,
             workspace=self._workspace,
@@ -265,6 +280,8 @@ def discrete_grouped_gemm_swiglu_wrapper_sm100(
     if cd_major != "n":
         raise ValueError(f"cd_major must be 'n', got {cd_major}")
     valid_m, k, _ = a_tensor.shape
+    if a_tensor.dtype == torch.float4_e2m1fn_x2:
+        k *= 2  # two elements per byte
     n_out = n // 2
     dev = a_tensor.device
     c_tensor = torch.empty_strided((valid_m, n, 1), (n, 1, valid_m * n), dtype=c_dtype, device=dev)

@@ -183,6 +183,8 @@ def grouped_gemm_glu_wrapper_sm100(
     if cd_major != "n":
         raise ValueError(f"cd_major must be 'n', got {cd_major}")
     valid_m, k, _ = a_tensor.shape
+    if a_tensor.dtype == torch.float4_e2m1fn_x2:
+        k *= 2  # two elements per byte
     if dense:
         n_full, _, l = b_tensor.shape
     else:

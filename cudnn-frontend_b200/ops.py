@@ -34,9 +34,9 @@ def sf_shape_stride(mn: int, k: int, l: int = 1, sf_vec: int = 32) -> Tuple[Tupl
     return (32, 4, rm, 4, rk, l), (16, 4, rk * 512, 1, 512, rm * rk * 512)
 
 
-def empty_sf(mn: int, k: int, l: int = 1, device="cuda", dtype=torch.float8_e8m0fnu, zero: bool = False) -> torch.Tensor:
+def empty_sf(mn: int, k: int, l: int = 1, device="cuda", dtype=torch.float8_e8m0fnu, zero: bool = False, sf_vec: int = 32) -> torch.Tensor:
     """Allocate a scale-factor tensor for an (mn, k) operand: 6-D view over a flat byte buffer."""
-    shape, stride = sf_shape_stride(mn, k, l)
+    shape, stride = sf_shape_stride(mn, k, l, sf_vec)
     n = l * shape[2] * shape[4] * 512
     flat = (torch.zeros if zero else torch.empty)(n, dtype=torch.uint8, device=device)
     return torch.as_strided(flat.view(dtype), shape, stride)

@@ -138,3 +138,75 @@ def test_fp4_rejections():
         cf.grouped_gemm_swiglu_wrapper_sm100(*args, d_dtype=torch.float8_e4m3fn, sf_vec_size=16, m_aligned=128)
     with pytest.raises(ValueError):  # E4M3 scale factors go with sf_vec_size 16 only
         cf.grouped_gemm_swiglu_wrapper_sm100(*args, d_dtype=torch.bfloat16, sf_vec_size=32, m_aligned=128)
+
+
+@pytest.mark.parametrize("fixture", ["reference_kernel_fc1_fp4_nvfp4.npz", "reference_kernel_fc1_fp4_mxfp4.npz", "reference_kernel_fc1_fp4_e8m0x16.npz"])
+def test_fc1_fp4_is_bit_identical_to_the_reference_kernel_fixture(golden_dir, tile_mode, fixture):
+    """Inputs and outputs of cudnn-frontend's GroupedGemmSwigluSm100 with float4_e2m1fn_x2 operands (bf16 C and
+    D, groups padded to 256) recorded on a B200: C and D must match bit for bit in both tile modes."""
+    import os
+
+    import cudnn_frontend_b200 as cf
+    from cudnn_frontend_b200 import ops
+
+    g = np.load(os.path.join(golden_dir, fixture))
+    m, kb = g["a"].shape
+    e, n, _ = g["b"].shape
+    k = 2 * kb
+    sf_vec = int(g["sf_vec"])
+    sf_t = torch.float8_e4m3fn if int(g["sf_is_e4m3"]) else torch.float8_e8m0fnu
+
+    def sf(flat, mn, l):
+        shape, stride = ops.sf_shape_stride(mn, k, l, sf_vec)
+        return torch.as_strided(torch.from_numpy(flat).cuda().view(sf_t), shape, stride)
+
+    out = cf.grouped_gemm_swiglu_wrapper_sm100(
+        _fp4(g["a"], (m, kb, 1)), _fp4(g["b"], (e, n, kb)).permute(1, 2, 0), sf(g["sfa"], m, 1), sf(g["sfb"], n, e),
+        torch.from_numpy(g["offsets"]).cuda(), torch.ones(e, device="cuda"), prob_tensor=torch.from_numpy(g["prob"]).cuda().view(m, 1, 1),
+        d_dtype=torch.bfloat16, sf_vec_size=sf_vec, m_aligned=256)  # fmt: skip
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(out["c_tensor"][:, :, 0].contiguous().view(torch.int16).cpu().numpy(), g["c"])
+    np.testing.assert_array_equal(out["d_tensor"][:, :, 0].contiguous().view(torch.int16).cpu().numpy(), g["d"])
+
+
+def test_discrete_and_glu_fp4_equal_dense_bitwise(tile_mode):
+    """FP4 weights behind per-expert pointers (discrete FC1) and through the unified GLU front end (GeGLU and a
+    fused bias) give the same bits as the dense FC1 on the same operands."""
+    import cudnn_frontend_b200 as cf
+
+    groups, n, k, sf_vec, sf_dtype = [128, 300, 0, 64], 256, 768, 16, "e4m3"
+    e = len(groups)
+    valid, aligned, offs = orc.padded_end_offsets(groups, 128)
+    a, b, sfa, sfb = H.gen_operands_fp4(31, valid, n, k, e, sf_vec, sf_dtype)
+    H.zero_padding_rows(a, groups, aligned)
+    ta = _fp4(a, (valid, k // 2, 1))
+    tb = _fp4(b, (e, n, k // 2))
+    tsfa = H.dev_sf(sfa, valid, k, 1, sf_vec=sf_vec, dtype=torch.float8_e4m3fn)
+    tsfb = H.dev_sf(sfb, n, k, e, sf_vec=sf_vec, dtype=torch.float8_e4m3fn)
+    toffs, talpha = torch.from_numpy(offs).cuda(), torch.ones(e, device="cuda")
+    # seeded: the dense wrapper keeps a running amax per cached configuration, so both tile modes must see the same rows
+    prob = torch.from_numpy(np.random.default_rng(7).uniform(0.1, 1.0, valid).astype(np.float32)).cuda().view(valid, 1, 1)
+    kw = dict(prob_tensor=prob, d_dtype=torch.bfloat16, sf_vec_size=sf_vec, m_aligned=128)
+    dense = cf.grouped_gemm_swiglu_wrapper_sm100(ta, tb.permute(1, 2, 0), tsfa, tsfb, toffs, talpha, **kw)
+    bl = [tb[i].clone() for i in range(e)]
+    sl = [H.dev_sf(sfb[i], n, k, 1, sf_vec=sf_vec, dtype=torch.float8_e4m3fn) for i in range(e)]
+    b_ptrs = torch.tensor([x.data_ptr() for x in bl], dtype=torch.int64, device="cuda")
+    sfb_ptrs = torch.tensor([x.data_ptr() for x in sl], dtype=torch.int64, device="cuda")
+    disc = cf.discrete_grouped_gemm_swiglu_wrapper_sm100(ta, b_ptrs, tsfa, sfb_ptrs, toffs, talpha, n, torch.float4_e2m1fn_x2, **kw)
+    torch.cuda.synchronize()
+    assert torch.equal(dense["c_tensor"], disc["c_tensor"]) and torch.equal(dense["d_tensor"], disc["d_tensor"])
+    assert torch.equal(dense["amax_tensor"], disc["amax_tensor"])
+
+    # GeGLU + bias through the unified front end, dense and discrete, against the oracle
+    rng = np.random.default_rng(2)
+    bias = rng.uniform(-2, 2, (e, n)).astype(np.float32)
+    tbias = torch.from_numpy(bias).cuda().to(torch.bfloat16).t()  # (n, e), stride (1, n)
+    ref = orc.fc1_reference(a, sfa, b, sfb, offs, np.ones(e, np.float32), prob.view(-1).cpu().numpy(), bias=orc.bf16_round(bias).T,
+                            act_func="geglu", ab_dtype="e2m1", sf_vec=sf_vec, sf_dtype=sf_dtype)  # fmt: skip
+    g1 = cf.grouped_gemm_glu_wrapper_sm100(ta, tsfa, toffs, talpha, b_tensor=tb.permute(1, 2, 0), sfb_tensor=tsfb, bias_tensor=tbias, act_func="geglu", **kw)
+    g2 = cf.grouped_gemm_glu_wrapper_sm100(ta, tsfa, toffs, talpha, b_ptrs=b_ptrs, sfb_ptrs=sfb_ptrs, n=n, b_dtype=torch.float4_e2m1fn_x2,
+                                           bias_tensor=tbias, act_func="geglu", **kw)  # fmt: skip
+    torch.cuda.synchronize()
+    assert torch.equal(g1["d_tensor"], g2["d_tensor"]) and torch.equal(g1["c_tensor"], g2["c_tensor"])
+    assert H.rel_fro(g1["c_tensor"][:, :, 0].float().cpu().numpy(), ref["c"]) <= BF16_GATE
+    assert H.rel_fro(g1["d_tensor"][:, :, 0].float().cpu().numpy(), ref["d"]) <= BF16_GATE

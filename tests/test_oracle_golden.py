@@ -213,3 +213,22 @@ def test_geglu_bias_oracle_against_the_reference_kernel_fixture(golden_dir):
     assert np.mean(orc.bf16_round(out["c"][:m]) == c_ref) >= 0.99
     _check_quantised(out["d_q"], out["sfd_row"], g["d"], g["sfd_row"], m, n // 2)
     _check_quantised(out["d_col_q"], out["sfd_col"], g["d_col"], g["sfd_col"], m, n // 2, by_cols=True)
+
+
+@pytest.mark.parametrize("fixture", ["reference_kernel_fc1_fp4_nvfp4.npz", "reference_kernel_fc1_fp4_mxfp4.npz", "reference_kernel_fc1_fp4_e8m0x16.npz"])
+def test_fp4_oracle_against_the_reference_kernel_fixture(golden_dir, fixture):
+    """FP4 operands (packed E2M1) with E4M3 scales per 16 (NVFP4), E8M0 per 32 (MXFP4) and E8M0 per 16: inputs
+    and the bf16 C and D of the reference's GroupedGemmSwigluSm100 recorded on a B200
+    (baseline/run_reference_kernels.py --cases fp4_tiny_*).  Pins the oracle's E2M1 decode, its nibble order and
+    its reading of the scale bytes."""
+    g = _load(golden_dir, fixture)
+    m, n = g["c"].shape
+    e, k = g["b"].shape[0], g["a"].shape[1] * 2
+    sf_vec, sf_dtype = int(g["sf_vec"]), ("e4m3" if int(g["sf_is_e4m3"]) else "e8m0")
+    sfa, sfb = orc.sf_unpack(g["sfa"], m, k // sf_vec)[0], orc.sf_unpack(g["sfb"], n, k // sf_vec, e)
+    out = orc.fc1_reference(g["a"], sfa, g["b"], sfb, g["offsets"], np.ones(e, np.float32), g["prob"], ab_dtype="e2m1", sf_vec=sf_vec, sf_dtype=sf_dtype)
+    c_ref, d_ref = _bf16_bits_to_f32(g["c"].view(np.uint16)), _bf16_bits_to_f32(g["d"].view(np.uint16))
+    # every product is exact in float32; the sums differ by their order only
+    assert np.mean(orc.bf16_round(out["c"][:m]) == c_ref) >= 0.995
+    assert np.linalg.norm(orc.bf16_round(out["c"][:m]) - c_ref) <= 1e-3 * np.linalg.norm(c_ref)
+    assert np.linalg.norm(orc.bf16_round(out["d"][:m]) - d_ref) <= 4e-3 * np.linalg.norm(d_ref)  # approximate SiLU in the kernel
