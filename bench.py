@@ -262,6 +262,78 @@ def cpu_baseline_c1(repeats=3):
             "sample": "configuration c1 at full size (512 routed rows, padded to 256 per expert), best of 3"}  # fmt: skip
 
 
+def reference_gpu_kernel():
+    """The reference's own FC1 GPU kernel (its CuTe-DSL grouped_gemm_swiglu_wrapper_sm100, JIT-compiled from the
+    overlay under baseline/_ref) on the benchmark's configuration, timed with the reference's protocol: 3 warm-ups,
+    10 trials with an L2 flush, median and best.  Inputs are made with plain torch (nothing of this package runs):
+    E4M3 operands of N(0, 1) values scaled to the E4M3 range, unit scale factors, 16384 tokens top-2 uniform, groups
+    padded to 256 (the only alignment the reference accepts), full output set (C, E4M3 D and D_col, scales).
+    Returns None where the overlay, a GPU or the CuTe DSL is missing; only ever run in a 1-GPU process."""
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_dir, "cudnn")) or int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        return None
+    try:
+        import torch
+
+        if not torch.cuda.is_available():
+            return None
+        sys.path.insert(0, ref_dir)
+        try:
+            import cuda.bindings.driver as cuda
+            import cudnn as ref
+        finally:
+            sys.path.remove(ref_dir)
+        dev = torch.device("cuda", 0)
+        torch.cuda.set_device(0)
+        e, k, n, tokens, topk = 8, 4096, 28672, 16384, 2
+        g = torch.Generator(device=dev).manual_seed(0)
+        ids = torch.multinomial(torch.ones(tokens, e, device=dev), topk, replacement=False, generator=g)
+        counts = torch.bincount(ids.reshape(-1), minlength=e)
+        padded = (counts + 255) // 256 * 256
+        offsets = torch.cumsum(padded, 0).to(torch.int32)
+        m = int(offsets[-1].item())
+        a = (torch.randn(m, k, generator=g, device=dev) * 100.0).clamp_(-448, 448).to(torch.float8_e4m3fn)
+        starts = offsets.long() - padded
+        rows = torch.arange(m, device=dev)
+        owner = torch.searchsorted(offsets.long(), rows, right=True).clamp(max=e - 1)
+        a[(rows - starts[owner]) >= counts[owner]] = 0
+        a = torch.as_strided(a, (m, k, 1), (k, 1, m * k))
+        b = torch.empty((e, n, k), dtype=torch.float8_e4m3fn, device=dev)
+        for i in range(e):
+            b[i] = (torch.randn(n, k, generator=g, device=dev) * 100.0).clamp_(-448, 448).to(torch.float8_e4m3fn)
+        b = b.permute(1, 2, 0)
+
+        def unit_sf(mn, l):  # 128x4 layout, every scale 2^-7
+            rm, rk = (mn + 127) // 128, (k // 32 + 3) // 4
+            flat = torch.full((l * rm * rk * 512,), 120, dtype=torch.uint8, device=dev)
+            return torch.as_strided(flat.view(torch.float8_e8m0fnu), (32, 4, rm, 4, rk, l), (16, 4, rk * 512, 1, 512, rm * rk * 512))
+
+        sfa, sfb = unit_sf(m, 1), unit_sf(n, e)
+        alpha, norm = torch.ones(e, device=dev), torch.ones(1, device=dev)
+        prob = torch.rand(m, 1, 1, generator=g, device=dev)
+        stream = torch.cuda.current_stream()
+        cu_stream = cuda.CUstream(stream.cuda_stream)
+
+        def step():
+            ref.grouped_gemm_swiglu_wrapper_sm100(a, b, sfa, sfb, offsets, alpha, norm_const_tensor=norm, prob_tensor=prob, d_dtype=torch.float8_e4m3fn,
+                                                  sf_vec_size=32, m_aligned=256, mma_tiler_mn=(256, 256), current_stream=cu_stream)  # fmt: skip
+
+        t0 = time.perf_counter()
+        step()
+        torch.cuda.synchronize()
+        jit_s = time.perf_counter() - t0
+        t = time_trials(step, stream)
+        ms_b2b, _ = time_steps(step, 20, 3, stream)
+        flops = 2.0 * tokens * topk * n * k
+        return {"kernel": "the reference's BlockScaledContiguousGroupedGemmKernel through grouped_gemm_swiglu_wrapper_sm100 (CuTe DSL, JIT)",
+                "workload": "c2 FC1: E=8, K=4096, N=28672, 32768 routed rows, groups padded to 256; C + E4M3 D + D_col + row and column scales",
+                "tflops": flops / (t["median_ms"] * 1e-3) / 1e12, "timing": t, "ms_back_to_back": ms_b2b,
+                "tflops_back_to_back": flops / (ms_b2b * 1e-3) / 1e12, "first_call_s": jit_s,
+                "compare_with": "extras.vs_reference_kernel of the own arm (both kernels on the same tensors in one process)"}  # fmt: skip
+    except Exception as exc:  # a JIT or import failure on this box is a result, not an error of the arm
+        return {"unavailable": f"{type(exc).__name__}: {exc}"[:300]}
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -294,6 +366,10 @@ def run_reference(args):
         "cpu_baseline": base,
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
+    gpu_kernel = reference_gpu_kernel() if args.gpus == 1 else None
+    if gpu_kernel is not None:
+        # beside the CPU figure this arm is defined by: what the reference's own sm_100 kernel does on this GPU
+        line["extras"] = {"reference_gpu_kernel": gpu_kernel}
     print(json.dumps(line))
 
 

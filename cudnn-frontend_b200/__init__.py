@@ -7,6 +7,8 @@ Public names mirror what the reference exports from its package root through laz
     GroupedGemmQuantSm100, grouped_gemm_quant_wrapper_sm100
     DiscreteGroupedGemmSwigluSm100, discrete_grouped_gemm_swiglu_wrapper_sm100
     GroupedGemmGluSm100, grouped_gemm_glu_wrapper_sm100      (unified FC1: swiglu / geglu, bias)
+    GroupedGemmDswigluSm100, grouped_gemm_dswiglu_wrapper_sm100  (backward of FC1's activation)
+    GroupedGemmWgradSm100, grouped_gemm_wgrad_wrapper_sm100      (weight gradient: the experts split K)
 
 plus what the reference does not have: ``quantize_mxfp8`` (activation quantiser), the routing
 helpers of ``moe`` and the expert-parallel layer ``ExpertParallelMoE``.
@@ -23,6 +25,10 @@ _LAZY = {
     "discrete_grouped_gemm_swiglu_wrapper_sm100": "discrete_grouped_gemm_swiglu",
     "GroupedGemmGluSm100": "grouped_gemm_glu",
     "grouped_gemm_glu_wrapper_sm100": "grouped_gemm_glu",
+    "GroupedGemmDswigluSm100": "grouped_gemm_dswiglu",
+    "grouped_gemm_dswiglu_wrapper_sm100": "grouped_gemm_dswiglu",
+    "GroupedGemmWgradSm100": "grouped_gemm_wgrad",
+    "grouped_gemm_wgrad_wrapper_sm100": "grouped_gemm_wgrad",
     "TupleDict": "api_base",
     "quantize_mxfp8": "ops",
     "quantize_mxfp8_out": "ops",

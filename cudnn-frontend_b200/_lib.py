@@ -22,6 +22,7 @@ FLAG_DYNAMIC_SCHED = 8
 FLAG_B_NMAJOR = 16
 FLAG_OFFSETS_HAVE_PREV = 32
 FLAG_TEST_SKIP_B_LOADS = 64
+FLAG_ACCUMULATE = 128
 WORKSPACE_DISCRETE, WORKSPACE_DYNAMIC_SCHED = 1, 2
 NOALLOC_MAX_EXPERTS = 256
 
@@ -66,12 +67,16 @@ class GemmArgs(Structure):
         ("l2_stream_m_tiles", c_int32),
         ("sf_vec_size", c_int32),
         ("sf_dtype", c_int32),
+        ("beta", c_void_p),
+        ("dprob", c_void_p),
     ]
 
 
 _SIGNATURES = {
     "b200moe_fc1_swiglu": (ctypes.c_int, [POINTER(GemmArgs), c_void_p]),
     "b200moe_fc2_quant": (ctypes.c_int, [POINTER(GemmArgs), c_void_p]),
+    "b200moe_dswiglu": (ctypes.c_int, [POINTER(GemmArgs), c_void_p]),
+    "b200moe_wgrad": (ctypes.c_int, [POINTER(GemmArgs), c_void_p]),
     "b200moe_fc1_swiglu_discrete_noalloc": (ctypes.c_int, [POINTER(GemmArgs), c_void_p]),
     "b200moe_workspace_bytes": (c_int64, [c_int32, c_int32]),
     "b200moe_quantize_mxfp8": (ctypes.c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),

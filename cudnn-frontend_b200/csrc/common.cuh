@@ -539,6 +539,11 @@ __device__ __forceinline__ uint32_t e5m2x2_from_float(float lo, float hi) {
 __device__ __forceinline__ uint32_t fp8x4_from_float(float a, float b, float c, float d, bool e5m2) {
   return e5m2 ? (e5m2x2_from_float(a, b) | (e5m2x2_from_float(c, d) << 16)) : e4m3x4_from_float(a, b, c, d);
 }
+// one FP8 byte (E4M3 or E5M2) -> float32, exact
+__device__ __forceinline__ float fp8_to_float(uint8_t b, bool e5m2) {
+  const __half_raw h = __nv_cvt_fp8_to_halfraw(b, e5m2 ? __NV_E5M2 : __NV_E4M3);
+  return __half2float(*reinterpret_cast<const __half*>(&h));
+}
 // two float32 -> packed 16-bit pair, bf16 or fp16 (warp-uniform choice)
 __device__ __forceinline__ uint32_t pack16x2_from_float(float lo, float hi, bool f16) {
   if (f16) {

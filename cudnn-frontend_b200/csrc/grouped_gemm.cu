@@ -3,6 +3,14 @@
 //   FC1: C = alpha_e (A SFA)(B_e SFB_e)^T ; D = up * silu(gate) * prob   (gate/up = even/odd
 //        32-column blocks of C) ; per-expert amax, or row / column MXFP8 re-quantisation.
 //   FC2: D = alpha_e acc * prob ; bf16 + amax, or E4M3 + row / column E8M0 scale factors.
+//   dSwiGLU (backward of FC1's activation): G = alpha_e^2 acc is the gradient of the SwiGLU output; with the
+//        forward pre-activation C (gate / up = even / odd 32-column blocks, scaled by beta_e) the epilogue
+//        writes d_gate = G prob up sig (1 + gate (1 - sig)) and d_up = G prob gate sig into the same blocks
+//        of D (twice as wide as the GEMM's N), adds sum(G gate sig up) to dprob, and re-quantises like FC2.
+//
+//   wgrad (weight gradient): the experts split K instead of M.  A is [m, T] and B is [n, T], both contiguous along
+//        the token dimension T; expert e owns tokens [offsets[e-1], offsets[e]) and its own 128x4 block of scale
+//        factors; wgrad[e] = gs_e (A_e SFA_e)(B_e SFB_e)^T, [E, m, n] in bf16 / fp16 / float32, stored or added to.
 //
 // Persistent kernel, one CTA per SM, walking a tile schedule derived on the device from the
 // per-expert END offsets: tiles of small expert groups (which stream their weights from HBM for one
@@ -79,6 +87,7 @@ constexpr int ST_MMA_OVERLAP = 103;
 constexpr int ST_EPI_ACC = 104;
 constexpr int ST_SCHED_FULL = 105;   // a consumer of the dynamic scheduler's ring
 constexpr int ST_SCHED_EMPTY = 106;  // the fetching warp waiting for a free ring slot
+constexpr int ST_WGRAD_K_UNALIGNED = 202;  // wgrad: an expert's token range is not a multiple of 32
 
 constexpr int SCHED_RING = 8;  // tile ids in flight between the fetching warp and the other warps (dynamic scheduler)
 
@@ -122,7 +131,7 @@ static_assert(Cfg<false, false, 1>::SMEM_BYTES <= 232448 && Cfg<true, false, 1>:
 static_assert(Cfg<false, false, 2>::SMEM_BYTES <= 232448 && Cfg<true, false, 2>::SMEM_BYTES <= 232448, "shared memory budget exceeded");
 static_assert(Cfg<false, true>::SMEM_BYTES <= 232448 && Cfg<true, true>::SMEM_BYTES <= 232448, "shared memory budget exceeded");
 
-enum : int { EPI_FC1 = 0, EPI_FC2 = 1 };
+enum : int { EPI_FC1 = 0, EPI_FC2 = 1, EPI_DSWIGLU = 2, EPI_WGRAD = 3 };
 
 struct GemmParams {
   const uint8_t* sfa;
@@ -160,6 +169,10 @@ struct GemmParams {
   int d_f32;          // D in float32 (E2M1 operands only)
   int discrete_col_sfd;
   int wide_stores;     // every output row segment of 32 bytes is 32-byte aligned
+  const void* c_in;    // dSwiGLU: forward pre-activation [m_rows, 2 n], bf16 / fp16 / E4M3 / E5M2
+  int c_in_dtype;
+  const float* beta;   // dSwiGLU: per-expert scale of c_in (NULL = 1)
+  float* dprob;        // dSwiGLU: [m_rows], atomically accumulated
   const void* bias;    // optional [E][N] (element (n, e) at e * N + n), added after alpha
   int bias_dtype;      // B200MOE_DTYPE_BF16 / _F16 / _F32
   int act_geglu;       // FC1: 0 = SwiGLU, 1 = GeGLU
@@ -168,6 +181,7 @@ struct GemmParams {
   int raster_group_m;  // row tiles per raster group
   int light_m_tiles;   // experts with at most this many row tiles form the "light" class (0 = one class)
   int stream_m_tiles;  // weight tiles of experts with at most this many row tiles are loaded with an evict-first L2 hint
+  int accumulate;      // wgrad: add to the output instead of overwriting it
   int first_has_prev;  // offsets[-1] is readable and is the first row of expert 0 (a slice of a longer expert list)
   int b_nmajor;        // B is [K][N] per expert (N contiguous) instead of [N][K]
   int dynamic_sched;   // tiles after each CTA's first come from an atomic counter
@@ -197,6 +211,9 @@ struct GemmParams {
 // ---------------------------------------------------------------------------------------
 struct Tile {
   int expert, row0, n_tile, row_end, m_tiles;
+  // wgrad only: the expert's range of K (tokens) in bytes, its k-tiles, its scale chunks along K and the number
+  // of scale chunks (along K, per 128-row block) of all experts before it
+  int k0, kbytes, k_tiles, rest_k, chunk0;
 };
 
 struct Sched {
@@ -243,6 +260,32 @@ __device__ __forceinline__ Tile decode_tile(const Sched& sc, const GemmParams& p
   tile.row0 = expert_first_row(p, e) + (first_m + jj % gsize) * tile_m;
   tile.row_end = p.offsets[e];
   return tile;
+}
+
+// wgrad: every expert has the same m_tiles x n_tiles output tiles; the row tile runs fastest so that CTAs working at
+// the same time share the B tile.  `chunk_prefix[e]` = scale chunks along K of the experts before e.
+__device__ __forceinline__ Tile decode_tile_wgrad(const GemmParams& p, const int* chunk_prefix, int s, int sf_vec_shift, int bytes_shift) {
+  const int m_tiles = (p.m_rows + BM - 1) / BM;
+  const int per_expert = m_tiles * p.n_tiles;
+  Tile t;
+  t.expert = s / per_expert;
+  const int j = s - t.expert * per_expert;
+  t.n_tile = j / m_tiles;
+  t.row0 = (j - t.n_tile * m_tiles) * BM;
+  t.row_end = p.m_rows;
+  t.m_tiles = m_tiles;
+  const int tok0 = t.expert == 0 ? 0 : p.offsets[t.expert - 1];
+  int toks = max(p.offsets[t.expert] - tok0, 0);
+  if ((tok0 | toks) & 31) {  // scale blocks and TMA coordinates need whole blocks of 32 tokens
+    atomicCAS(&g_device_status, 0, ST_WGRAD_K_UNALIGNED);
+    toks = 0;
+  }
+  t.k0 = tok0 >> bytes_shift;
+  t.kbytes = toks >> bytes_shift;
+  t.k_tiles = (t.kbytes + BK - 1) / BK;
+  t.rest_k = ((toks >> sf_vec_shift) + 3) >> 2;
+  t.chunk0 = chunk_prefix[t.expert];
+  return t;
 }
 
 // ---------------------------------------------------------------------------------------
@@ -521,7 +564,31 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       tmem_relinquish();
     }
   }
-  if (warp == 2) {
+  if (kEpi == EPI_WGRAD && warp == 2) {
+    // scale chunks along K of the experts before each expert (every expert has the same number of tiles)
+    const int sf_shift = kFmt == 2 ? 4 : 5;
+    int run = 0;
+    for (int e0 = 0; e0 < p.num_experts; e0 += 32) {
+      const int e = e0 + lane;
+      int c = 0;
+      if (e < p.num_experts) {
+        const int toks = max(p.offsets[e] - (e == 0 ? 0 : p.offsets[e - 1]), 0);
+        c = ((toks >> sf_shift) + 3) >> 2;
+      }
+      int incl = c;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int o = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += o;
+      }
+      if (e < p.num_experts) prefix_heavy[e] = run + incl - c;
+      run += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) {
+      totals_smem[0] = p.num_experts * ((p.m_rows + BM - 1) / BM) * p.n_tiles;
+      totals_smem[1] = 0;
+    }
+  } else if (warp == 2) {
     // tile prefixes over experts, one per class: lane l scans a contiguous chunk of experts, then a
     // warp scan of the chunk sums
     const int chunk = (p.num_experts + 31) / 32;
@@ -571,6 +638,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
   const uint32_t tmem_base = *tmem_ptr_smem;
   const int total_tiles = totals_smem[0];
   const Sched sched = {prefix_heavy, prefix_light, totals_smem[1], total_tiles};
+  auto decode = [&](int s) -> Tile {
+    if constexpr (kEpi == EPI_WGRAD) return decode_tile_wgrad(p, prefix_heavy, s, kFmt == 2 ? 4 : 5, kFmt ? 1 : 0);
+    else return decode_tile(sched, p, C::TILE_M, s);
+  };
 
   // ---- tile sequence of this CTA (pair) ---------------------------------------------------
   // Static: schedule positions sched_id, sched_id + stride, ...  Dynamic: the first position is
@@ -617,7 +688,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       while (t >= 0 && ok) {
         int fetched = 0;
         if (fetcher && lane == 0) fetched = atomicAdd(p.tile_counter, 1) + sched_stride;  // used after the k loop
-        const Tile tile = decode_tile(sched, p, C::TILE_M, t);
+        const Tile tile = decode(t);
+        // the k-tiles of this tile: all of K, or (wgrad) the expert's range of it with the expert's own scale chunks
+        const int k_tiles = kEpi == EPI_WGRAD ? tile.k_tiles : p.k_tiles;
+        const int rest_k = kEpi == EPI_WGRAD ? tile.rest_k : p.rest_k;
         const int n0 = tile.n_tile * BN;
         const int my_row0 = tile.row0 + (int)cta_rank * BM;
         const int nblk0 = n0 / 128;
@@ -635,12 +709,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         constexpr uint64_t b_policy = L2_EVICT_FIRST;
         // Everything that changes per k-tile is a running value: the K coordinate, the scale-chunk
         // pointers and the stage's shared-memory / barrier addresses.
-        int kc = 0;
+        int kc = kEpi == EPI_WGRAD ? tile.k0 : 0;
         if constexpr (kPair) {
           // every load of either CTA credits the leader's barrier of this stage
           const int b_row = n0 + (int)cta_rank * 128;
           const int m_blk = my_row0 / BM;
-          for (int kt = 0; kt < p.k_tiles; ++kt, kc += BK) {
+          for (int kt = 0; kt < k_tiles; ++kt, kc += BK) {
             if (!__all_sync(0xffffffffu, mbar_wait(empty_bar(stage), phase ^ 1, wc, ST_PRODUCER_EMPTY))) { ok = false; break; }
             const uint32_t fb = leader_full0 + 8u * stage;
             if (elect_one() && !skip_loads) {
@@ -668,12 +742,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           // zeros and still counts its bytes), plain bulk copies of the chunks that exist otherwise
           const bool two_chunks = kDiscrete || p.n_blocks - nblk0 >= 2;
           if (!side_b) {
-            const uint8_t* sfa_src = p.sfa + (int64_t)(tile.row0 / BM) * p.rest_k * 512;
-            for (int kt = 0; kt < p.k_tiles; ++kt, kc += BK, sfa_src += 512 * CPK) {
+            const uint8_t* sfa_src = p.sfa + (int64_t)(tile.row0 / BM) * rest_k * 512;
+            if constexpr (kEpi == EPI_WGRAD) sfa_src += (int64_t)tile.chunk0 * ((p.m_rows + BM - 1) / BM) * 512;
+            for (int kt = 0; kt < k_tiles; ++kt, kc += BK, sfa_src += 512 * CPK) {
               if (!__all_sync(0xffffffffu, mbar_wait(empty_bar(stage), phase ^ 1, wc, ST_PRODUCER_EMPTY))) { ok = false; break; }
               const uint32_t fb = full_bar(stage);
               // scale chunks this k-tile has (the last k-tile of a row block may have fewer than CPK)
-              const uint32_t sf_bytes = 512u * (uint32_t)min(CPK, p.rest_k - kt * CPK);
+              const uint32_t sf_bytes = 512u * (uint32_t)min(CPK, rest_k - kt * CPK);
               const uint32_t tx = A_STAGE_BYTES + C::B_STAGE_BYTES + sf_bytes + (kDiscrete ? (uint32_t)SFB_STAGE_BYTES : (two_chunks ? 2u : 1u) * sf_bytes);
               if (elect_one()) {
                 mbar_arrive_expect_tx(fb, tx);
@@ -684,9 +759,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
               if (++stage == STAGES) { stage = 0; phase ^= 1; }
             }
           } else {
-            const uint8_t* sfb_src0 = kDiscrete ? nullptr : p.sfb + (int64_t)tile.expert * p.sfb_expert_bytes + (int64_t)nblk0 * p.rest_k * 512;
-            const uint8_t* sfb_src1 = sfb_src0 + (int64_t)p.rest_k * 512;
-            for (int kt = 0; kt < p.k_tiles; ++kt, kc += BK, sfb_src0 += 512 * CPK, sfb_src1 += 512 * CPK) {
+            const uint8_t* sfb_src0 = kDiscrete ? nullptr
+                                      : (kEpi == EPI_WGRAD ? p.sfb + ((int64_t)tile.chunk0 * p.n_blocks + (int64_t)nblk0 * rest_k) * 512
+                                                           : p.sfb + (int64_t)tile.expert * p.sfb_expert_bytes + (int64_t)nblk0 * rest_k * 512);
+            const uint8_t* sfb_src1 = sfb_src0 + (int64_t)rest_k * 512;
+            for (int kt = 0; kt < k_tiles; ++kt, kc += BK, sfb_src0 += 512 * CPK, sfb_src1 += 512 * CPK) {
               if (!__all_sync(0xffffffffu, mbar_wait(empty_bar(stage), phase ^ 1, wc, ST_PRODUCER_EMPTY))) { ok = false; break; }
               const uint32_t fb = full_bar(stage);
               if (elect_one() && !skip_loads) {
@@ -702,6 +779,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                     if (p.b_nmajor) tma_load_2d(b_dst + 128 * BK, bmap, fb, n0 + 128, kc);
                   }
                   tma_load_3d(sfb_dst0 + stage * SFB_STAGE_BYTES, sfbmap, fb, 0, kt * CPK, nblk0);
+                } else if constexpr (kEpi == EPI_WGRAD) {
+                  tma_load_2d(b_dst, bmap, fb, kc, n0);  // B is [n, T]: no expert dimension
+                  const uint32_t sf_bytes = 512u * (uint32_t)min(CPK, rest_k - kt * CPK);
+                  bulk_load(sfb_dst0 + stage * SFB_STAGE_BYTES, sfb_src0, sf_bytes, fb);
+                  if (two_chunks) bulk_load(sfb_dst0 + stage * SFB_STAGE_BYTES + 512 * CPK, sfb_src1, sf_bytes, fb);
                 } else {
                   if (b_stream) {
                     tma_load_3d_hint(b_dst, bmap, fb, c0, c1, tile.expert, b_policy);
@@ -710,7 +792,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                     tma_load_3d(b_dst, bmap, fb, c0, c1, tile.expert);
                     if (p.b_nmajor) tma_load_3d(b_dst + 128 * BK, bmap, fb, n0 + 128, kc, tile.expert);
                   }
-                  const uint32_t sf_bytes = 512u * (uint32_t)min(CPK, p.rest_k - kt * CPK);
+                  const uint32_t sf_bytes = 512u * (uint32_t)min(CPK, rest_k - kt * CPK);
                   bulk_load(sfb_dst0 + stage * SFB_STAGE_BYTES, sfb_src0, sf_bytes, fb);
                   if (two_chunks) bulk_load(sfb_dst0 + stage * SFB_STAGE_BYTES + 512 * CPK, sfb_src1, sf_bytes, fb);
                 }
@@ -775,7 +857,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           if (!__all_sync(0xffffffffu, mbar_wait(overlap_bar, (it - 1) & 1, wc, ST_MMA_OVERLAP))) { ok = false; break; }
           tc_fence_after();
         }
-        for (int kt = 0; kt < p.k_tiles; ++kt) {
+        int k_tiles = p.k_tiles, k_bytes = p.k_bytes;
+        if constexpr (kEpi == EPI_WGRAD) {
+          const Tile tile = decode(t);
+          k_tiles = tile.k_tiles;
+          k_bytes = tile.kbytes;
+        }
+        for (int kt = 0; kt < k_tiles; ++kt) {
           // the stage's bytes were written by TMA (async proxy) and are made visible by the barrier's
           // transaction count; no tcgen05 fence is needed between this wait and the MMAs
           // (the outcome is voted so that a wait that gives up takes the whole warp out of the loop)
@@ -791,7 +879,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           const uint32_t sfa_lo = sfa_lo0 + stage * (SFA_STAGE_BYTES >> 4);
           const uint32_t sfb_lo = sfb_lo0 + stage * (SFB_STAGE_BYTES >> 4);
           const uint32_t not_first = kt != 0;
-          const int k_left = p.k_bytes - kt * BK;  // bytes of K this k-tile still has
+          const int k_left = k_bytes - kt * BK;  // bytes of K this k-tile still has
           if (elect_one()) {
             // chunk g of SFA -> 4 columns; chunk g of both 128-row blocks of SFB -> 8 columns side by side.
             // (in pair mode one instruction acts on both CTAs: each copies from its own smem to its own TMEM)
@@ -855,13 +943,14 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     int it = 0;
     bool ok = true;
     for (int t = next_tile(0); t >= 0 && ok; t = next_tile(++it)) {
-      Tile tile = decode_tile(sched, p, C::TILE_M, t);
+      Tile tile = decode(t);
       tile.row0 += (int)cta_rank * BM;  // this CTA's 128 rows
       const int n0 = tile.n_tile * BN;
       const int row = tile.row0 + r_in_tile;
       // in pair mode the second half of a 256-row tile may lie beyond the expert's last row
       const bool row_ok = row < min(p.m_rows, tile.row_end);
-      const float alpha = p.alpha[tile.expert];
+      // wgrad: the product of the two optional per-expert global scales
+      const float alpha = kEpi == EPI_WGRAD ? (p.alpha ? p.alpha[tile.expert] : 1.0f) * (p.beta ? p.beta[tile.expert] : 1.0f) : p.alpha[tile.expert];
       const float prob = (p.prob && row_ok) ? p.prob[row] : 1.0f;
       int out_row = (p.d_row_map && row_ok) ? p.d_row_map[row] : row;
       // destination of this thread's bf16 D row: d, or the buffer of the rank the row returns to
@@ -981,6 +1070,162 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           else if (blocks_left == 1)
             *dst = (uint8_t)(sf_row_word >> (16 * half));
         }
+      } else if constexpr (kEpi == EPI_WGRAD) {
+        // plain store (or accumulation) of the expert's [m, n] tile, scaled by the expert's global scale
+        const bool empty = tile.k_tiles == 0;  // an expert without tokens: nothing was accumulated
+        const int64_t out_base = ((int64_t)tile.expert * p.m_rows + row) * p.n;
+#pragma unroll 1
+        for (int i = 0; i < 4; ++i) {
+          const int bb = reverse ? 3 - i : i;
+          const int col = half * 128 + bb * 32;
+          float v[32];
+          tmem_ld_32x32(acc + col, v);
+          tmem_ld_wait();
+          reg_fence32(v);
+          if (i == (kFmt ? 1 : 0)) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) arrive_overlap();
+          }
+          const int dn = n0 + col;
+          if (dn >= p.n || !row_ok) continue;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = empty ? 0.f : v[j] * alpha;
+          if (p.accumulate) {
+            if (p.d_f32) {
+              const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.d) + out_base + dn);
+#pragma unroll
+              for (int q = 0; q < 8; ++q) {
+                const float4 o = src[q];
+                v[4 * q] += o.x; v[4 * q + 1] += o.y; v[4 * q + 2] += o.z; v[4 * q + 3] += o.w;
+              }
+            } else {
+              const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.d) + out_base + dn);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const uint4 o = src[q];
+                const uint16_t* h = reinterpret_cast<const uint16_t*>(&o);
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                  v[8 * q + j] += d_f16 ? __half2float(__ushort_as_half(h[j])) : __uint_as_float((uint32_t)h[j] << 16);
+              }
+            }
+          }
+          store_d32(reinterpret_cast<__nv_bfloat16*>(p.d), out_base + dn, v, wide, d_f16, p.d_f32 != 0);
+        }
+      } else if constexpr (kEpi == EPI_DSWIGLU) {
+        // 4 blocks of 32 accumulator columns per half; block b of the GEMM's N owns columns [64 b, 64 b + 64) of C and D
+        const float alpha2 = alpha * alpha;
+        const float beta = p.beta ? p.beta[tile.expert] : 1.0f;
+        const int c_bytes = (p.c_in_dtype == B200MOE_DTYPE_E4M3 || p.c_in_dtype == B200MOE_DTYPE_E5M2) ? 1 : 2;
+        const uint8_t* c_row = reinterpret_cast<const uint8_t*>(p.c_in) + (int64_t)row * p.n_out * c_bytes;
+        float dprob_sum = 0.f, amax_up = 0.f;  // thread_amax collects d_gate, amax_up collects d_up
+#pragma unroll 1
+        for (int i = 0; i < 4; ++i) {
+          const int bb = reverse ? 3 - i : i;
+          const int col = half * 128 + bb * 32;
+          const int dn = n0 + col;  // column of the GEMM result
+          const bool live = dn < p.n;
+          // this row's gate and up block of the forward C (64 consecutive elements), requested before the TMEM load
+          uint4 craw[8];
+          if (live && row_ok) {
+            const uint4* src = reinterpret_cast<const uint4*>(c_row + (int64_t)dn * 2 * c_bytes);
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              if (q < 4 * c_bytes) craw[q] = __ldg(src + q);
+          } else {
+#pragma unroll
+            for (int q = 0; q < 8; ++q) craw[q] = make_uint4(0, 0, 0, 0);
+          }
+          float v[32];
+          tmem_ld_32x32(acc + col, v);
+          tmem_ld_wait();
+          reg_fence32(v);
+          if (i == (kFmt ? 1 : 0)) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) arrive_overlap();
+          }
+          if (!live) continue;
+          float d1[32];  // d_gate; v becomes d_up
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            // element j of the gate block and of the up block
+            float cg, cu;
+            if (c_bytes == 2) {
+              const uint16_t* h = reinterpret_cast<const uint16_t*>(craw);
+              cg = p.c_in_dtype == B200MOE_DTYPE_F16 ? __half2float(__ushort_as_half(h[j])) : __uint_as_float((uint32_t)h[j] << 16);
+              cu = p.c_in_dtype == B200MOE_DTYPE_F16 ? __half2float(__ushort_as_half(h[32 + j])) : __uint_as_float((uint32_t)h[32 + j] << 16);
+            } else {
+              const uint8_t* b8 = reinterpret_cast<const uint8_t*>(craw);
+              cg = fp8_to_float(b8[j], p.c_in_dtype == B200MOE_DTYPE_E5M2);
+              cu = fp8_to_float(b8[32 + j], p.c_in_dtype == B200MOE_DTYPE_E5M2);
+            }
+            // the reference kernel's operation order, every product and sum rounded on its own
+            const float g = __fmul_rn(v[j], alpha2);
+            const float gate = __fmul_rn(cg, beta);
+            const float up = __fmul_rn(cu, beta);
+            const float e = ex2_approx(__fmul_rn(gate, -1.4426950408889634f));
+            const float sig = rcp_approx(__fadd_rn(e, 1.0f));
+            const float swish = __fmul_rn(gate, sig);
+            dprob_sum = __fadd_rn(dprob_sum, __fmul_rn(__fmul_rn(up, swish), g));
+            const float gp = __fmul_rn(g, prob);
+            v[j] = __fmul_rn(gp, swish);
+            const float dsig1 = __fadd_rn(__fmul_rn(gate, __fsub_rn(1.0f, sig)), 1.0f);
+            d1[j] = __fmul_rn(__fmul_rn(__fmul_rn(gp, up), sig), dsig1);
+          }
+          if (p.amax && row_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              thread_amax = fmaxf(thread_amax, fabsf(d1[j]));
+              amax_up = fmaxf(amax_up, fabsf(v[j]));
+            }
+          }
+          const int64_t on = 2 * (int64_t)dn;  // column of D of the gate block; the up block follows it
+          if (!p.gen_sfd) {
+            if (row_ok) {
+              store_d32(d_rows, (int64_t)row * p.n_out + on, d1, wide, d_f16, p.d_f32 != 0);
+              store_d32(d_rows, (int64_t)row * p.n_out + on + 32, v, wide, d_f16, p.d_f32 != 0);
+            }
+          } else {
+            if (row_ok) {
+              uint8_t* d_row_base = reinterpret_cast<uint8_t*>(p.d) + (int64_t)row * d_row_bytes;
+              const uint32_t sf1 = quant_row_block(d_row_base, on, d1, norm_const, wide, out_fmt);
+              const uint32_t sf2 = quant_row_block(d_row_base, on + 32, v, norm_const, wide, out_fmt);
+              // scale blocks 2 (dn / 32) and 2 (dn / 32) + 1 of this row: two adjacent bytes of one K group
+              if (p.sfd_row) *reinterpret_cast<uint16_t*>(p.sfd_row + sf_offset(row, on >> 5, p.sfd_row_rest_k)) = (uint16_t)(sf1 | (sf2 << 8));
+            }
+            if (p.d_col) {
+              if (!row_ok) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) { d1[j] = 0.f; v[j] = 0.f; }
+              }
+              int64_t blk_base = 0;
+              int rb = (tile.row0 >> 5) + quarter;
+              int rest = p.sfd_col_rest_k;
+              if (p.discrete_col_sfd) {
+                const int start = expert_first_row(p, tile.expert);
+                blk_base = (int64_t)(start / 128) * ((p.n_out + 127) / 128) * 512;
+                rb = ((tile.row0 - start) >> 5) + quarter;
+                rest = ((p.offsets[tile.expert] - start) / 32 + 3) / 4;
+              }
+              const bool rows_live = tile.row0 + quarter * 32 < min(p.m_rows, tile.row_end);
+              uint8_t* d_col_base = p.d_col + (int64_t)row * d_row_bytes;
+              const uint32_t sfc1 = quant_col_block(d_col_base, on, row_ok, d1, norm_const, wide, out_fmt);
+              if (rows_live) p.sfd_col[blk_base + sf_offset(on + lane, rb, rest)] = (uint8_t)sfc1;
+              const uint32_t sfc2 = quant_col_block(d_col_base, on + 32, row_ok, v, norm_const, wide, out_fmt);
+              if (rows_live) p.sfd_col[blk_base + sf_offset(on + 32 + lane, rb, rest)] = (uint8_t)sfc2;
+            }
+          }
+        }
+        if (p.dprob && row_ok) atomicAdd(p.dprob + row, dprob_sum);
+        if (p.amax) {
+          // amax[expert][0] = d_gate, amax[expert][1] = d_up; d_gate goes through the common reduction below
+          float wmax = amax_up;
+#pragma unroll
+          for (int d = 16; d > 0; d >>= 1) wmax = fmaxf(wmax, __shfl_xor_sync(0xffffffffu, wmax, d));
+          if (lane == 0) atomicMax(reinterpret_cast<int*>(p.amax) + 2 * tile.expert + 1, __float_as_int(wmax));
+        }
       } else {
         // FC2: 4 blocks of 32 columns per half
         if constexpr (kBulk) bulk_wait_read0();  // the previous tile's row copies have left the staging area
@@ -1087,7 +1332,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         for (int d = 16; d > 0; d >>= 1) wmax = fmaxf(wmax, __shfl_xor_sync(0xffffffffu, wmax, d));
         // non-negative floats order like their bit patterns; -inf (the caller's initial
         // value) has a negative pattern, so a signed integer max is exact
-        if (lane == 0) atomicMax(reinterpret_cast<int*>(p.amax) + tile.expert, __float_as_int(wmax));
+        if (lane == 0) atomicMax(reinterpret_cast<int*>(p.amax) + (kEpi == EPI_DSWIGLU ? 2 * tile.expert : tile.expert), __float_as_int(wmax));
       }
     }
   }
@@ -1215,7 +1460,7 @@ static int encode_map(CUtensorMap* map, CUtensorMapDataType dtype, const void* b
 struct DeviceInfo {
   int sm_count = 0;
   int cc_major = 0;
-  bool attr_set[3][2][2][2] = {};
+  bool attr_set[3][4][2][2] = {};
   bool attr_set_bulk[2] = {};
 };
 
@@ -1284,7 +1529,7 @@ static int run_gemm(int epi, const b200moe_gemm_args* a, void* stream_v) {
   cudaStream_t stream = (cudaStream_t)stream_v;
   if (!a) return fail(B200MOE_E_NULL, "args is NULL");
   const bool discrete = a->b_ptrs != nullptr || a->sfb_ptrs != nullptr;
-  const char* op = epi == EPI_FC1 ? "fc1_swiglu" : "fc2_quant";
+  const char* op = epi == EPI_FC1 ? "fc1_swiglu" : (epi == EPI_FC2 ? "fc2_quant" : "dswiglu");
   if (a->m_rows == 0 || a->num_experts == 0) return B200MOE_OK;
   if (!a->a || !a->sfa || !a->padded_offsets || !a->alpha || !a->d)
     return fail(B200MOE_E_NULL, "%s: a, sfa, padded_offsets, alpha and d are required", op);
@@ -1294,7 +1539,9 @@ static int run_gemm(int epi, const b200moe_gemm_args* a, void* stream_v) {
   } else if (!a->b || !a->sfb) {
     return fail(B200MOE_E_NULL, "%s: b and sfb are required in dense mode", op);
   }
-  if (epi == EPI_FC2 && !a->prob) return fail(B200MOE_E_NULL, "%s: prob is required", op);
+  if (epi != EPI_FC1 && !a->prob) return fail(B200MOE_E_NULL, "%s: prob is required", op);
+  if (epi == EPI_DSWIGLU && (!a->c || !a->dprob)) return fail(B200MOE_E_NULL, "%s: c (the forward pre-activation) and dprob are required", op);
+  if (epi == EPI_DSWIGLU && (a->bias || a->d_row_map)) return fail(B200MOE_E_UNSUPPORTED, "%s: no bias and no row map", op);
   if (a->m_rows < 0 || a->m_rows > (1ll << 30) || a->n <= 0 || a->k <= 0 || a->num_experts < 0)
     return fail(B200MOE_E_SHAPE, "%s: bad sizes m=%lld n=%lld k=%lld E=%d", op, (long long)a->m_rows, (long long)a->n,
                 (long long)a->k, a->num_experts);
@@ -1317,7 +1564,7 @@ static int run_gemm(int epi, const b200moe_gemm_args* a, void* stream_v) {
     return fail(B200MOE_E_SHAPE, "%s: N-major B needs n (%lld) to be a multiple of 16", op, (long long)a->n);
   if (epi == EPI_FC1 && a->n % 64 != 0)
     return fail(B200MOE_E_SHAPE, "%s: n (%lld) must be a multiple of 64 (32-column gate/up blocks)", op, (long long)a->n);
-  if (epi == EPI_FC2 && a->n % 32 != 0)
+  if (epi != EPI_FC1 && a->n % 32 != 0)
     return fail(B200MOE_E_SHAPE, "%s: n (%lld) must be a multiple of 32", op, (long long)a->n);
   if (a->n * a->k > (1ll << 40)) return fail(B200MOE_E_SHAPE, "%s: n*k too large", op);
   const bool d_fp8 = a->d_dtype == B200MOE_DTYPE_E4M3 || a->d_dtype == B200MOE_DTYPE_E5M2;
@@ -1330,8 +1577,9 @@ static int run_gemm(int epi, const b200moe_gemm_args* a, void* stream_v) {
   if (d_f32 && !fp4) return fail(B200MOE_E_UNSUPPORTED, "%s: a float32 D goes with E2M1 operands only (as in the reference)", op);
   if (d_f32 && a->d_row_map) return fail(B200MOE_E_UNSUPPORTED, "%s: d_row_map needs a bf16 D", op);
   if (fp4 && d_fp8) return fail(B200MOE_E_SHAPE, "%s: E2M1 operands take a bf16, fp16 or float32 D", op);
-  if (a->c_dtype != B200MOE_DTYPE_BF16 && a->c_dtype != B200MOE_DTYPE_F16)
-    return fail(B200MOE_E_UNSUPPORTED, "%s: c_dtype %d (bf16 and fp16 are built)", op, a->c_dtype);
+  const bool c_fp8 = a->c_dtype == B200MOE_DTYPE_E4M3 || a->c_dtype == B200MOE_DTYPE_E5M2;
+  if (a->c_dtype != B200MOE_DTYPE_BF16 && a->c_dtype != B200MOE_DTYPE_F16 && !(epi == EPI_DSWIGLU && c_fp8))
+    return fail(B200MOE_E_UNSUPPORTED, "%s: c_dtype %d (bf16 and fp16 are built; E4M3 and E5M2 as the input of dswiglu)", op, a->c_dtype);
   if (a->ab_dtype != 0 && a->ab_dtype != B200MOE_DTYPE_E4M3 && a->ab_dtype != B200MOE_DTYPE_E5M2 && !fp4)
     return fail(B200MOE_E_UNSUPPORTED, "%s: ab_dtype %d (E4M3, E5M2 and E2M1 are built)", op, a->ab_dtype);
   if (a->act_func != B200MOE_ACT_SWIGLU && a->act_func != B200MOE_ACT_GEGLU)
@@ -1381,6 +1629,10 @@ static int run_gemm(int epi, const b200moe_gemm_args* a, void* stream_v) {
   p.d_peer_ptrs = a->d_row_map ? a->d_peer_ptrs : nullptr;
   p.d_peer_slots = a->d_peer_slots;
   p.c = epi == EPI_FC1 ? (__nv_bfloat16*)a->c : nullptr;
+  p.c_in = epi == EPI_DSWIGLU ? a->c : nullptr;
+  p.c_in_dtype = a->c_dtype;
+  p.beta = a->beta;
+  p.dprob = epi == EPI_DSWIGLU ? a->dprob : nullptr;
   p.d = a->d;
   p.d_col = gen_sfd ? (uint8_t*)a->d_col : nullptr;
   p.gen_sfd = gen_sfd ? 1 : 0;
@@ -1391,7 +1643,7 @@ static int run_gemm(int epi, const b200moe_gemm_args* a, void* stream_v) {
   p.n = (int)a->n;
   p.k = (int)a->k;
   p.num_experts = a->num_experts;
-  p.n_out = epi == EPI_FC1 ? p.n / 2 : p.n;
+  p.n_out = epi == EPI_FC1 ? p.n / 2 : (epi == EPI_DSWIGLU ? 2 * p.n : p.n);
   p.n_tiles = (p.n + BN - 1) / BN;
   p.k_bytes = fp4 ? p.k / 2 : p.k;
   p.k_tiles = (p.k_bytes + BK - 1) / BK;
@@ -1418,7 +1670,7 @@ static int run_gemm(int epi, const b200moe_gemm_args* a, void* stream_v) {
   {
     // 256-bit stores need 32-byte aligned bases and row pitches that keep a 32-column block aligned
     const int64_t d_pitch = (int64_t)p.n_out * (d_fp8 ? 1 : (d_f32 ? 4 : 2));
-    const uintptr_t bases = (uintptr_t)a->c | (uintptr_t)a->d | (uintptr_t)a->d_col;
+    const uintptr_t bases = (epi == EPI_FC1 ? (uintptr_t)a->c : 0) | (uintptr_t)a->d | (uintptr_t)a->d_col;
     p.wide_stores = (bases % 32 == 0) && (d_pitch % 32 == 0) && (((int64_t)p.n * 2) % 32 == 0);
   }
 
@@ -1522,8 +1774,95 @@ static int run_gemm(int epi, const b200moe_gemm_args* a, void* stream_v) {
   if (epi == EPI_FC2 && !discrete && !d_fp8 && !gen_sfd && fmt == 0 && p.d_peer_ptrs && ((uintptr_t)a->d % 16 == 0))
     return pair ? launch<EPI_FC2, false, true, true>(maps, p, grid, di, stream)
                 : launch<EPI_FC2, false, false, true>(maps, p, grid, di, stream);
+  if (epi == EPI_DSWIGLU) return dispatch<EPI_DSWIGLU>(fmt, discrete, pair, maps, p, grid, di, stream);
   return epi == EPI_FC1 ? dispatch<EPI_FC1>(fmt, discrete, pair, maps, p, grid, di, stream)
                         : dispatch<EPI_FC2>(fmt, discrete, pair, maps, p, grid, di, stream);
+}
+
+// ---------------------------------------------------------------------------------------
+// Weight gradient: the experts partition the contraction dimension (tokens).
+// ---------------------------------------------------------------------------------------
+static int run_wgrad(const b200moe_gemm_args* a, void* stream_v) {
+  cudaStream_t stream = (cudaStream_t)stream_v;
+  const char* op = "wgrad";
+  if (!a) return fail(B200MOE_E_NULL, "args is NULL");
+  if (a->num_experts == 0 || a->m_rows == 0 || a->n == 0) return B200MOE_OK;
+  if (!a->a || !a->b || !a->sfa || !a->sfb || !a->padded_offsets || !a->d)
+    return fail(B200MOE_E_NULL, "%s: a, b, sfa, sfb, padded_offsets (token END offsets) and d are required", op);
+  if (a->b_ptrs || a->sfb_ptrs) return fail(B200MOE_E_UNSUPPORTED, "%s: one [E, m, n] output tensor only (no per-expert pointers)", op);
+  if (a->m_rows < 0 || a->m_rows > (1ll << 30) || a->n <= 0 || a->k < 0 || a->k > (1ll << 30) || a->num_experts < 0 || a->num_experts > MAX_EXPERTS)
+    return fail(B200MOE_E_SHAPE, "%s: bad sizes m=%lld n=%lld tokens=%lld E=%d", op, (long long)a->m_rows, (long long)a->n, (long long)a->k, a->num_experts);
+  const bool fp4 = a->ab_dtype == B200MOE_DTYPE_E2M1;
+  const int sf_vec = a->sf_vec_size == 0 ? 32 : a->sf_vec_size;
+  const bool sf_e4m3 = a->sf_dtype == B200MOE_DTYPE_E4M3;
+  if (sf_vec != 16 && sf_vec != 32) return fail(B200MOE_E_SHAPE, "%s: sf_vec_size must be 16 or 32, got %d", op, sf_vec);
+  if (!fp4 && (sf_vec != 32 || sf_e4m3)) return fail(B200MOE_E_SHAPE, "%s: 8-bit operands take E8M0 scale factors per 32 elements", op);
+  if (sf_e4m3 && sf_vec != 16) return fail(B200MOE_E_SHAPE, "%s: E4M3 scale factors go with sf_vec_size 16", op);
+  if (a->ab_dtype != 0 && a->ab_dtype != B200MOE_DTYPE_E4M3 && a->ab_dtype != B200MOE_DTYPE_E5M2 && !fp4)
+    return fail(B200MOE_E_UNSUPPORTED, "%s: ab_dtype %d", op, a->ab_dtype);
+  if (a->k % 32 != 0) return fail(B200MOE_E_SHAPE, "%s: the token count (%lld) must be a multiple of 32", op, (long long)a->k);
+  if (a->n % 32 != 0) return fail(B200MOE_E_SHAPE, "%s: n (%lld) must be a multiple of 32", op, (long long)a->n);
+  const bool d_f32 = a->d_dtype == B200MOE_DTYPE_F32;
+  if (a->d_dtype != B200MOE_DTYPE_BF16 && a->d_dtype != B200MOE_DTYPE_F16 && !d_f32)
+    return fail(B200MOE_E_UNSUPPORTED, "%s: d_dtype %d (bf16, fp16 and float32 are built)", op, a->d_dtype);
+  if (a->wait_limit_ms < 0) return fail(B200MOE_E_SHAPE, "%s: wait_limit_ms must not be negative", op);
+  const uintptr_t align_or = (uintptr_t)a->a | (uintptr_t)a->sfa | (uintptr_t)a->b | (uintptr_t)a->sfb | (uintptr_t)a->d;
+  if (align_or & 15) return fail(B200MOE_E_ALIGN, "%s: tensor base addresses must be 16-byte aligned", op);
+  const int fmt = !fp4 ? 0 : (sf_vec == 32 ? 1 : 2);
+
+  DeviceInfo* di = nullptr;
+  int rc = get_device_info(&di);
+  if (rc) return rc;
+  if (di->cc_major != 10) return fail(B200MOE_E_DEVICE, "%s: needs an sm_100 device, found compute capability %d.x", op, di->cc_major);
+
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.sfa = (const uint8_t*)a->sfa;
+  p.sfb = (const uint8_t*)a->sfb;
+  p.offsets = a->padded_offsets;
+  p.alpha = a->alpha;
+  p.beta = a->beta;
+  p.ab_format = (a->ab_dtype == B200MOE_DTYPE_E5M2 || fp4) ? ((1u << 7) | (1u << 10)) : 0u;
+  p.sf_e4m3 = sf_e4m3 ? 1 : 0;
+  p.d = a->d;
+  p.m_rows = (int)a->m_rows;
+  p.n = (int)a->n;
+  p.k = (int)a->k;
+  p.num_experts = a->num_experts;
+  p.n_out = p.n;
+  p.n_tiles = (p.n + BN - 1) / BN;
+  p.n_blocks = (p.n + 127) / 128;
+  p.k_bytes = fp4 ? p.k / 2 : p.k;
+  p.d_f16 = a->d_dtype == B200MOE_DTYPE_F16;
+  p.d_f32 = d_f32 ? 1 : 0;
+  p.accumulate = (a->flags & B200MOE_FLAG_ACCUMULATE) ? 1 : 0;
+  p.raster_group_m = 1;
+  p.wait_limit_ns = a->wait_limit_ms > 0 ? (uint64_t)a->wait_limit_ms * 1000000ull : kWaitLimitNs;
+  p.wide_stores = ((uintptr_t)a->d % 32 == 0) && (((int64_t)p.n * (d_f32 ? 4 : 2)) % 32 == 0);
+
+  CUtensorMap maps[4];
+  memset(maps, 0, sizeof(maps));
+  {
+    const uint64_t dims[2] = {(uint64_t)p.k_bytes, (uint64_t)p.m_rows};
+    const uint64_t strides[1] = {(uint64_t)p.k_bytes};
+    const uint32_t box[2] = {BK, BM};
+    rc = encode_map(&maps[0], CU_TENSOR_MAP_DATA_TYPE_UINT8, a->a, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+  }
+  {
+    const uint64_t dims[2] = {(uint64_t)p.k_bytes, (uint64_t)p.n};
+    const uint64_t strides[1] = {(uint64_t)p.k_bytes};
+    const uint32_t box[2] = {BK, BN};
+    rc = encode_map(&maps[1], CU_TENSOR_MAP_DATA_TYPE_UINT8, a->b, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+  }
+  const int64_t tiles = (int64_t)p.num_experts * ((p.m_rows + BM - 1) / BM) * p.n_tiles;
+  int units = di->sm_count - (a->sm_margin > 0 ? a->sm_margin : 0);
+  if (units < 1) units = 1;
+  if ((int64_t)units > tiles) units = (int)tiles;
+  if (fmt == 1) return launch<EPI_WGRAD, false, false, false, 1>(maps, p, units, di, stream);
+  if (fmt == 2) return launch<EPI_WGRAD, false, false, false, 2>(maps, p, units, di, stream);
+  return launch<EPI_WGRAD, false, false, false, 0>(maps, p, units, di, stream);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -1592,6 +1931,10 @@ int b200moe_fc1_swiglu_discrete_noalloc(const b200moe_gemm_args* args, void* str
 int b200moe_fc1_swiglu(const b200moe_gemm_args* args, void* stream) { return b200moe::run_gemm(b200moe::EPI_FC1, args, stream); }
 
 int b200moe_fc2_quant(const b200moe_gemm_args* args, void* stream) { return b200moe::run_gemm(b200moe::EPI_FC2, args, stream); }
+
+int b200moe_dswiglu(const b200moe_gemm_args* args, void* stream) { return b200moe::run_gemm(b200moe::EPI_DSWIGLU, args, stream); }
+
+int b200moe_wgrad(const b200moe_gemm_args* args, void* stream) { return b200moe::run_wgrad(args, stream); }
 
 int64_t b200moe_workspace_bytes(int32_t num_experts, int32_t mode) {
   if (num_experts <= 0) return 0;

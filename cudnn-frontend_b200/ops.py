@@ -129,8 +129,12 @@ def launch_grouped_gemm(
     stream_m_tiles: Optional[int] = None,
     offsets_have_prev: bool = False,
     sf_vec_size: int = 32,
+    beta: Optional[torch.Tensor] = None,
+    dprob: Optional[torch.Tensor] = None,
 ) -> None:
-    """Fill the C struct and call b200moe_fc1_swiglu / b200moe_fc2_quant.
+    """Fill the C struct and call b200moe_fc1_swiglu / b200moe_fc2_quant / b200moe_dswiglu (``kind`` "fc1", "fc2",
+    "dswiglu"; for the last ``c`` is the forward pre-activation, an input, ``beta`` its per-expert scale and
+    ``dprob`` the float32 ``[m_rows]`` accumulator of the gate-probability gradient).
 
     ``tile_mode``: ``"single"`` (128 x 256 tiles, one CTA), ``"pair"`` (256 x 256 tiles on CTA pairs)
     or ``None`` / ``"auto"`` (the library picks from the average group size).  The environment
@@ -201,9 +205,13 @@ def launch_grouped_gemm(
     if d.dtype not in _D_DTYPES:
         raise NotImplementedError(f"D dtype {d.dtype} is not built (bf16, fp16, float32, E4M3, E5M2 are)")
     args.d_dtype = _D_DTYPES[d.dtype]
-    if c is not None and c.dtype not in (torch.bfloat16, torch.float16):
-        raise NotImplementedError(f"C dtype {c.dtype} is not built (bf16 and fp16 are)")
-    args.c_dtype = _lib.DTYPE_F16 if (c is not None and c.dtype == torch.float16) else _lib.DTYPE_BF16
+    c_types = {torch.bfloat16: _lib.DTYPE_BF16, torch.float16: _lib.DTYPE_F16}
+    if kind == "dswiglu":
+        c_types.update({torch.float8_e4m3fn: _lib.DTYPE_E4M3, torch.float8_e5m2: _lib.DTYPE_E5M2})
+    if c is not None and c.dtype not in c_types:
+        raise NotImplementedError(f"C dtype {c.dtype} is not built ({', '.join(str(t) for t in c_types)} are)")
+    args.c_dtype = _lib.DTYPE_BF16 if c is None else c_types[c.dtype]
+    args.beta, args.dprob = _ptr(beta), _ptr(dprob)
     args.flags = _lib.FLAG_DISCRETE_COL_SFD if discrete_col_sfd else 0
     mode = tile_mode or os.environ.get("B200MOE_TILE_MODE", "auto")
     if mode not in ("auto", "single", "pair"):
@@ -234,9 +242,36 @@ def launch_grouped_gemm(
     args.sf_vec_size = int(sf_vec_size)
     args.sf_dtype = _lib.DTYPE_E4M3 if sfa.dtype == torch.float8_e4m3fn else 0
     lib = _lib.load()
-    fn = lib.b200moe_fc1_swiglu if kind == "fc1" else lib.b200moe_fc2_quant
+    fn = {"fc1": lib.b200moe_fc1_swiglu, "fc2": lib.b200moe_fc2_quant, "dswiglu": lib.b200moe_dswiglu}[kind]
     with torch.cuda.device(a.device):
         rc = fn(ctypes.byref(args), _stream_ptr(stream))
+    _lib.check(rc)
+
+
+def launch_wgrad(
+    *, a: torch.Tensor, b: torch.Tensor, sfa: torch.Tensor, sfb: torch.Tensor, offsets: torch.Tensor, wgrad: torch.Tensor, m: int, n: int,
+    tokens: int, sf_vec_size: int = 32, scale_a: Optional[torch.Tensor] = None, scale_b: Optional[torch.Tensor] = None, accumulate: bool = False,
+    sm_margin: int = 0, stream=None,
+) -> None:  # fmt: skip
+    """Call b200moe_wgrad: ``a [m, tokens]`` and ``b`` stored ``[n, tokens]`` (both contiguous along the tokens),
+    ``offsets [E]`` int32 token END offsets, ``wgrad [E, m, n]`` bf16 / fp16 / float32."""
+    _require_cuda(a, b, sfa, sfb, offsets, wgrad, scale_a, scale_b)
+    args = _lib.GemmArgs()
+    args.a, args.b, args.sfa, args.sfb = _ptr(a), _ptr(b), _ptr(sfa), _ptr(sfb)
+    args.padded_offsets = _ptr(offsets)
+    args.alpha, args.beta = _ptr(scale_a), _ptr(scale_b)
+    args.d = _ptr(wgrad)
+    if wgrad.dtype not in (torch.bfloat16, torch.float16, torch.float32):
+        raise ValueError(f"wgrad dtype must be bfloat16, float16 or float32, got {wgrad.dtype}")
+    args.d_dtype = _D_DTYPES[wgrad.dtype]
+    args.m_rows, args.n, args.k, args.num_experts = m, n, tokens, offsets.shape[0]
+    args.ab_dtype = {torch.float8_e5m2: _lib.DTYPE_E5M2, torch.float4_e2m1fn_x2: _lib.DTYPE_E2M1}.get(a.dtype, _lib.DTYPE_E4M3)
+    args.sf_vec_size = int(sf_vec_size)
+    args.sf_dtype = _lib.DTYPE_E4M3 if sfa.dtype == torch.float8_e4m3fn else 0
+    args.flags = _lib.FLAG_ACCUMULATE if accumulate else 0
+    args.sm_margin = sm_margin
+    with torch.cuda.device(a.device):
+        rc = _lib.load().b200moe_wgrad(ctypes.byref(args), _stream_ptr(stream))
     _lib.check(rc)
 
 
@@ -340,7 +375,8 @@ def grouped_gemm_op(kind: str, *, stream=None, **kw) -> None:
         launch_grouped_gemm(
             kind, a=a, sfa=kw["sfa"], padded_offsets=kw["padded_offsets"], alpha=kw["alpha"], d=kw["d"], m_rows=a.shape[0], n=kw["n"],
             k=a.shape[1] * (2 if a.dtype == torch.float4_e2m1fn_x2 else 1), sf_vec_size=int(kw.get("sf_vec_size", 32)), num_experts=kw["padded_offsets"].shape[0], b=kw.get("b"), sfb=kw.get("sfb"), b_ptrs=kw.get("b_ptrs"),
-            sfb_ptrs=kw.get("sfb_ptrs"), prob=kw.get("prob"), norm_const=kw.get("norm_const"), c=kw.get("c") if kind == "fc1" else None,
+            sfb_ptrs=kw.get("sfb_ptrs"), prob=kw.get("prob"), norm_const=kw.get("norm_const"), c=kw.get("c") if kind != "fc2" else None,
+            beta=kw.get("beta"), dprob=kw.get("dprob"),
             d_col=kw.get("d_col"), amax=kw.get("amax"), sfd_row=kw.get("sfd_row"), sfd_col=kw.get("sfd_col"),
             workspace=kw.get("workspace"), discrete_col_sfd=bool(kw.get("discrete_col_sfd", False)), sm_margin=int(kw.get("sm_margin", 0)),
             tile_mode=kw.get("tile_mode") or None, d_row_map=kw.get("d_row_map"), d_peer_ptrs=kw.get("d_peer_ptrs"),
@@ -358,8 +394,8 @@ def grouped_gemm_op(kind: str, *, stream=None, **kw) -> None:
               kw["alpha"], kw.get("prob"), kw.get("norm_const"))  # fmt: skip
     if kw.get("expert_range") is not None or kw.get("test_skip_b_loads") or kw.get("offsets_have_prev"):
         raise NotImplementedError("expert_range and the test hook are eager-only launch options")
-    if kw["a"].dtype == torch.float4_e2m1fn_x2:
-        raise NotImplementedError("FP4 operands are launched eagerly only (the custom-op schema carries 8-bit operands)")
+    if kw["a"].dtype == torch.float4_e2m1fn_x2 or kind == "dswiglu":
+        raise NotImplementedError("FP4 operands and the dSwiGLU kernel are launched eagerly only (no custom-op schema is registered for them)")
     tail = (kw["n"], bool(kw.get("discrete_col_sfd", False)), int(kw.get("sm_margin", 0)), kw.get("tile_mode") or "")
     sched = (bool(kw.get("dynamic_sched", False)), bool(kw.get("b_nmajor", False)))
     outs = (kw["d"], kw.get("d_col"), kw.get("amax"), kw.get("sfd_row"), kw.get("sfd_col"), kw.get("workspace"))

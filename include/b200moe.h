@@ -63,6 +63,8 @@ extern "C" {
    the kernel returns and b200moe_device_status reports which wait gave up.  Use with a small
    wait_limit_ms.  The outputs of such a launch are undefined. */
 #define B200MOE_FLAG_TEST_SKIP_B_LOADS 64
+/* b200moe_wgrad: add the result to d instead of overwriting it (the reference's accumulate_on_output) */
+#define B200MOE_FLAG_ACCUMULATE 128
 
 /* mode bits of b200moe_workspace_bytes */
 #define B200MOE_WORKSPACE_DISCRETE 1
@@ -161,6 +163,10 @@ typedef struct b200moe_gemm_args {
      fp16 (with amax) or float32, no scale-factor generation (the reference's rules for FP4 operands). */
   int32_t sf_vec_size;
   int32_t sf_dtype;
+  /* b200moe_dswiglu only: per-expert scale of the forward pre-activation read through `c` (NULL = 1), and the
+     gradient of the gate probabilities [m_rows] f32, accumulated with atomic adds (the caller zeroes it) */
+  const float* beta;
+  float* dprob;
 } b200moe_gemm_args;
 
 /*
@@ -204,6 +210,37 @@ int b200moe_fc1_swiglu_discrete_noalloc(const b200moe_gemm_args* args, void* str
  * (python/cudnn/grouped_gemm/grouped_gemm_quant/grouped_gemm_quant.py:1073-1985).
  */
 int b200moe_fc2_quant(const b200moe_gemm_args* args, void* stream);
+
+/*
+ * Backward of FC1's activation: G = alpha_e^2 * (A*SFA)(B_e*SFB_e)^T is the gradient of the SwiGLU output
+ * [m_rows, n]; `c` is an INPUT here, the forward pre-activation [m_rows, 2n] (c_dtype bf16 / fp16 / E4M3 / E5M2;
+ * gate / up = even / odd 32-column blocks), scaled by beta_e.  D and D_col are [m_rows, 2n]:
+ *   D[:, 64j:64j+32]    = G_j * prob * up_j * sig_j * (1 + gate_j * (1 - sig_j))     (gradient of the gate block)
+ *   D[:, 64j+32:64j+64] = G_j * prob * gate_j * sig_j                                (gradient of the up block)
+ *   dprob[r]           += sum over columns of G * gate * sig * up
+ * with sig = sigmoid(gate).  Outputs as for FC2: E4M3 / E5M2 D and D_col with row and column E8M0 scale factors,
+ * or a 16-bit / float32 D with amax, which is [E][2] here (gate gradient, up gradient).
+ * Replaces GroupedGemmDswigluSm100.execute
+ * (python/cudnn/grouped_gemm/grouped_gemm_dswiglu/api.py:621-695), kernel BlockScaledContiguousGroupedGemmKernel of
+ * python/cudnn/grouped_gemm/grouped_gemm_dswiglu/grouped_gemm_dswiglu_quant.py (epilogue :2590-3095).
+ */
+int b200moe_dswiglu(const b200moe_gemm_args* args, void* stream);
+
+/*
+ * Weight gradient of a grouped GEMM: the experts partition the contraction dimension.  Fields of the argument
+ * struct are read as follows:
+ *   a  [m_rows, k] and b [n, k]: both contiguous along k = the total number of tokens (k / 2 bytes per row with
+ *      E2M1 operands); expert e owns tokens [padded_offsets[e-1], padded_offsets[e]), a multiple of 32 each (an expert
+ *      whose range is not gets a zero result and status 202 in b200moe_device_status);
+ *   sfa, sfb: per expert the 128x4 layout of (m_rows, tokens_e / sf_vec) resp. (n, tokens_e / sf_vec), the experts'
+ *      blocks one after the other (the layout torch's scaled_grouped_mm takes for its 2D-2D case);
+ *   alpha, beta: optional per-expert scales (the reference's global_scale_a and global_scale_b), NULL = 1;
+ *   d: [E, m_rows, n] bf16 / fp16 / float32 (d_dtype), d[e] = alpha_e beta_e (A_e SFA_e)(B_e SFB_e)^T, added to the existing
+ *      contents with B200MOE_FLAG_ACCUMULATE.  Everything else in the struct is ignored.
+ * Replaces GroupedGemmWgradSm100.execute (python/cudnn/grouped_gemm/grouped_gemm_wgrad/api.py), kernel
+ * BlockScaledMoEGroupedGemmWgradKernel (python/cudnn/grouped_gemm/grouped_gemm_wgrad/moe_blockscaled_grouped_gemm_wgrad.py).
+ */
+int b200moe_wgrad(const b200moe_gemm_args* args, void* stream);
 
 /*
  * Bytes of caller-owned workspace a launch needs.  mode = B200MOE_WORKSPACE_DISCRETE (two 128-byte

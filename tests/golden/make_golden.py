@@ -15,6 +15,8 @@ inputs, and stores inputs + outputs as small .npz files:
 * fc1_swiglu.npz       run_grouped_gemm_swiglu_ref, float32 branch (same file, :472-573)
 * fc2_quant.npz        run_grouped_gemm_quant_ref, float32 branch
                        (test/python/fe_api/test_grouped_gemm_quant_utils.py:270-345)
+* dswiglu.npz          run_grouped_gemm_dswiglu_ref, float32 branch with amax
+                       (test/python/fe_api/test_grouped_gemm_dswiglu_utils.py:334-491)
 
 The re-quantisation branch of those functions (generate_sfd=True) needs a GPU and the CuTe
 DSL, so it is not part of these fixtures.  The reference_kernel_*.npz files are different: they
@@ -39,6 +41,7 @@ sys.path.insert(0, os.path.join(REF, "test", "python"))
 sys.path.insert(0, os.path.join(REF, "test", "python", "fe_api"))
 
 import test_fe_api_utils as fu  # noqa: E402
+import test_grouped_gemm_dswiglu_utils as du  # noqa: E402
 import test_grouped_gemm_quant_utils as qu  # noqa: E402
 import test_grouped_gemm_swiglu_utils as su  # noqa: E402
 from cutlass.cute.runtime import from_dlpack  # noqa: E402
@@ -158,6 +161,44 @@ def main():
         alpha=alpha.numpy(),
         prob=prob.numpy().reshape(-1),
         d_ref=ref["d_ref"][:, :, 0].numpy(),
+    )
+    # ---- dSwiGLU: backward of FC1's activation ---------------------------------------------
+    e, n, k = 3, 64, 96
+    groups = [256, 40, 512]
+    valid_m, aligned, offs = su.create_mask(groups, 256)
+    a, b, sfa, sfb = gen_operands(g, valid_m, n, k, e)
+    alpha = torch.randint(1, 3, (e,), generator=g).float()
+    beta = torch.tensor([1.0, 0.5, 2.0])
+    prob = torch.empty(valid_m, 1, 1).uniform_(0.1, 1, generator=g)
+    c_fwd = torch.empty(valid_m, 2 * n, 1).uniform_(-3, 3, generator=g).to(torch.bfloat16)
+    ref = du.run_grouped_gemm_dswiglu_ref(
+        a_ref=a.float().unsqueeze(-1),
+        b_ref=b.float().permute(1, 2, 0),
+        c_ref=c_fwd.float(),
+        sfa_ref=expand_sf(sfa).unsqueeze(-1),
+        sfb_ref=expand_sf(sfb).permute(1, 2, 0),
+        alpha_tensor=alpha,
+        beta_tensor=beta,
+        prob_tensor=prob,
+        aligned_group_m_list=aligned,
+        valid_m=valid_m,
+        generate_amax=True,
+        generate_sfd=False,
+    )
+    np.savez_compressed(
+        os.path.join(HERE, "dswiglu.npz"),
+        a=a.view(torch.uint8).numpy(),
+        b=b.view(torch.uint8).numpy(),
+        sfa=sfa.numpy(),
+        sfb=sfb.numpy(),
+        offsets=offs.numpy(),
+        alpha=alpha.numpy(),
+        beta=beta.numpy(),
+        prob=prob.numpy().reshape(-1),
+        c_fwd=c_fwd.view(torch.int16).numpy()[:, :, 0],
+        d_ref=ref["d_ref"][:, :, 0].numpy(),
+        dprob_ref=ref["dprob_ref"].numpy().reshape(-1),
+        amax_ref=ref["amax_ref"].numpy().reshape(e, 2),
     )
     print("golden fixtures written to", HERE)
 

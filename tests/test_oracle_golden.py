@@ -51,6 +51,15 @@ def test_fc2_matches_reference(golden_dir):
     assert out["amax"][2] == -np.inf  # empty expert keeps the initial value
 
 
+def test_dswiglu_matches_reference(golden_dir):
+    g = _load(golden_dir, "dswiglu.npz")
+    c_fwd = (g["c_fwd"].view(np.uint16).astype(np.uint32) << 16).view(np.float32)
+    out = orc.dswiglu_reference(g["a"], g["sfa"], g["b"], g["sfb"], c_fwd, g["offsets"], g["alpha"], g["beta"], g["prob"])
+    np.testing.assert_allclose(out["d"], g["d_ref"], rtol=1e-4, atol=1e-3)
+    np.testing.assert_allclose(out["dprob"], g["dprob_ref"], rtol=1e-4, atol=1e-2)
+    np.testing.assert_allclose(out["amax"], g["amax_ref"], rtol=1e-5)
+
+
 def test_e8m0_rounds_up_and_saturates():
     x = np.array([0.0, 1.0, 1.0000001, 1.5, 2.0, 3.9, 2.0**-126, 2.0**-127, 1e-45, 3e38, np.inf], dtype=np.float32)
     b = orc.e8m0_encode(x)
