@@ -461,6 +461,135 @@ def run_case_fp4(name, cfg, out):
         )  # fmt: skip
 
 
+def run_case_dswiglu(name, cfg, out):
+    """dSwiGLU backward (grouped_gemm_dswiglu): fp8 operands, bf16 forward C, E4M3 D_row / D_col with row and column
+    scales, dprob."""
+    import cuda.bindings.driver as cuda
+    from cudnn.grouped_gemm.grouped_gemm_dswiglu.api import grouped_gemm_dswiglu_wrapper_sm100 as ref_dswiglu  # the overlay
+
+    import cudnn_frontend_b200 as ours
+    from cudnn_frontend_b200 import synthetic
+
+    p = synthetic.make_problem(cfg, "cuda", seed=13, m_aligned=256)
+    e, n, k = cfg["experts"], cfg["n"], cfg["k"]
+    m = p["m_rows"]
+    g = torch.Generator(device="cuda").manual_seed(6)
+    c_fwd = torch.empty((m, 2 * n), device="cuda").uniform_(-3, 3, generator=g).to(torch.bfloat16)
+    c_fwd = torch.as_strided(c_fwd, (m, 2 * n, 1), (2 * n, 1, m * 2 * n))  # the reference checks the stride of the unit dimension too
+    beta = torch.tensor([1.0, 0.5] * (e // 2) + [2.0] * (e % 2), device="cuda")
+    norm = torch.tensor([1.0], dtype=torch.float32, device="cuda")
+    stream = cuda.CUstream(torch.cuda.current_stream().cuda_stream)
+    kw = dict(norm_const_tensor=norm, d_dtype=torch.float8_e4m3fn, sf_vec_size=32, m_aligned=256)
+    res = {"case": name, "op": "dswiglu", "cfg": cfg, "m_rows": m, "flops": 2.0 * p["routing"].routed_rows * n * k}
+
+    def run_ref():
+        return ref_dswiglu(p["a"], p["b"], c_fwd, p["sfa"], p["sfb"], p["padded_offsets"], p["alpha"], beta, p["prob"], mma_tiler_mn=(256, 256),
+                           current_stream=stream, **kw)  # fmt: skip
+
+    def run_own():
+        return ours.grouped_gemm_dswiglu_wrapper_sm100(p["a"], p["b"], c_fwd, p["sfa"], p["sfb"], p["padded_offsets"], p["alpha"], beta, p["prob"], **kw)
+
+    t0 = time.time()
+    r_ref = run_ref()
+    torch.cuda.synchronize()
+    res["ref_first_call_s"] = time.time() - t0
+    r_own = run_own()
+    torch.cuda.synchronize()
+    if PROFILE_ONLY:
+        run_ref()
+        run_own()
+        torch.cuda.synchronize()
+        return
+
+    def flat(t):
+        t = t.view(torch.uint8)
+        return torch.as_strided(t, (t.numel(),), (1,))
+
+    for key in ("d_row_tensor", "d_col_tensor"):
+        u = ulp(r_ref[key][:m].view(torch.uint8), r_own[key][:m].view(torch.uint8))
+        res[key + "_equal_frac"] = float((u == 0).float().mean())
+        res[key + "_within_1ulp_frac"] = float((u <= 1).float().mean())
+    res["sfd_row_bytes_equal_frac"] = float((flat(r_ref["sfd_row_tensor"]) == flat(r_own["sfd_row_tensor"])).float().mean())
+    res["sfd_col_bytes_equal_frac"] = float((flat(r_ref["sfd_col_tensor"]) == flat(r_own["sfd_col_tensor"])).float().mean())
+    dp_r, dp_o = r_ref["dprob_tensor"].view(-1), r_own["dprob_tensor"].view(-1)
+    res["dprob_rel_fro"] = float((dp_r - dp_o).norm() / dp_r.norm())
+    if not name.endswith("tiny"):
+        il_ref, il_own = timed_interleaved(run_ref, run_own, rounds=12)
+        res["ref_ms_interleaved"], res["own_ms_interleaved"] = il_ref, il_own
+        res["own_over_ref_interleaved"] = il_ref / il_own
+    out.append(res)
+    print(json.dumps(res), flush=True)
+    if name.endswith("tiny"):
+        np.savez_compressed(
+            os.path.join(OUT_DIR, "reference_kernel_dswiglu_golden.npz"),
+            a=p["a"][:, :, 0].view(torch.uint8).cpu().numpy(), b=p["b"].permute(2, 0, 1).contiguous().view(torch.uint8).cpu().numpy(),
+            sfa=flat(p["sfa"]).cpu().numpy(), sfb=flat(p["sfb"]).cpu().numpy(), offsets=p["padded_offsets"].cpu().numpy(),
+            prob=p["prob"].view(-1).cpu().numpy(), beta=beta.cpu().numpy(), c_fwd=c_fwd[:, :, 0].view(torch.int16).cpu().numpy(),
+            d_row=r_ref["d_row_tensor"][:m, :, 0].view(torch.uint8).cpu().numpy(), d_col=r_ref["d_col_tensor"][:m, :, 0].view(torch.uint8).cpu().numpy(),
+            sfd_row=flat(r_ref["sfd_row_tensor"]).cpu().numpy(), sfd_col=flat(r_ref["sfd_col_tensor"]).cpu().numpy(),
+            dprob=r_ref["dprob_tensor"].view(-1).cpu().numpy(),
+        )  # fmt: skip
+
+
+def run_case_wgrad(name, cfg, out):
+    """Weight gradient (grouped_gemm_wgrad): fp8 operands with E8M0 scales per 32 tokens, bf16 output, dense mode."""
+    import cuda.bindings.driver as cuda
+    from cudnn.grouped_gemm.grouped_gemm_wgrad.api import grouped_gemm_wgrad_wrapper_sm100 as ref_wgrad  # the overlay
+
+    import cudnn_frontend_b200 as ours
+
+    m, n, groups = cfg["m"], cfg["n"], cfg["groups"]
+    tokens, e = sum(groups), len(groups)
+    g = torch.Generator(device="cuda").manual_seed(23)
+    a = torch.empty((m, tokens), device="cuda").uniform_(-2, 2, generator=g).to(torch.float8_e4m3fn)
+    b_store = torch.empty((n, tokens), device="cuda").uniform_(-2, 2, generator=g).to(torch.float8_e4m3fn)
+    b = b_store.t()  # (tokens, n), contiguous along the tokens
+    cols = (tokens // 32 + 3) // 4 * 4
+
+    def rand_sf(rows):
+        rows_p = (rows + 127) // 128 * 128
+        return torch.randint(124, 131, (rows_p, cols), generator=g, device="cuda", dtype=torch.int32).to(torch.uint8).view(torch.float8_e8m0fnu)
+
+    sfa, sfb = rand_sf(m), rand_sf(n)
+    offs = torch.tensor(np.cumsum(groups), dtype=torch.int32, device="cuda")
+    stream = cuda.CUstream(torch.cuda.current_stream().cuda_stream)
+    res = {"case": name, "op": "wgrad", "cfg": cfg, "flops": 2.0 * tokens * m * n}
+
+    def run_ref():
+        return ref_wgrad(a, b, sfa, sfb, offs, sf_vec_size=32, mma_tiler_mn=(256, 256), current_stream=stream)["wgrad_tensor"]
+
+    def run_own():
+        return ours.grouped_gemm_wgrad_wrapper_sm100(a, b, sfa, sfb, offs, sf_vec_size=32)["wgrad_tensor"]
+
+    t0 = time.time()
+    w_ref = run_ref()
+    torch.cuda.synchronize()
+    res["ref_first_call_s"] = time.time() - t0
+    w_own = run_own()
+    torch.cuda.synchronize()
+    if PROFILE_ONLY:
+        run_ref()
+        run_own()
+        torch.cuda.synchronize()
+        return
+    res["wgrad_equal_frac"] = float((w_ref.view(torch.int16) == w_own.view(torch.int16)).float().mean())
+    res["wgrad_rel_fro"] = float((w_ref.float() - w_own.float()).norm() / w_ref.float().norm())
+    if not name.endswith("tiny"):
+        il_ref, il_own = timed_interleaved(run_ref, run_own, rounds=12)
+        res["ref_ms_interleaved"], res["own_ms_interleaved"] = il_ref, il_own
+        res["own_over_ref_interleaved"] = il_ref / il_own
+        res["ref_tflops_interleaved"] = res["flops"] / (il_ref * 1e-3) / 1e12
+        res["own_tflops_interleaved"] = res["flops"] / (il_own * 1e-3) / 1e12
+    out.append(res)
+    print(json.dumps(res), flush=True)
+    if name.endswith("tiny"):
+        np.savez_compressed(
+            os.path.join(OUT_DIR, "reference_kernel_wgrad_golden.npz"),
+            a=a.view(torch.uint8).cpu().numpy(), b=b_store.view(torch.uint8).cpu().numpy(), sfa=sfa.view(torch.uint8).cpu().numpy().reshape(-1),
+            sfb=sfb.view(torch.uint8).cpu().numpy().reshape(-1), offsets=offs.cpu().numpy(), wgrad=w_ref.view(torch.int16).cpu().numpy(),
+        )  # fmt: skip
+
+
 PROFILE_ONLY = False
 OWN_FIRST = False
 
@@ -492,6 +621,11 @@ CASES["glu_mid"] = dict(experts=8, k=4096, n=7168, tokens=4096, topk=2, routing=
 GLU_CASES = ("glu_tiny", "glu_mid")
 # FP4 operands: NVFP4 (E4M3 scales per 16), MXFP4 (E8M0 per 32) and E8M0 per 16; the tiny ones record fixtures
 # (two k-tiles of 256 elements deep), the others compare speed
+# backward pair: dSwiGLU (K = hidden, N = intermediate; D is 2 N wide) and the weight gradient (experts split the tokens)
+CASES["dswiglu_tiny"] = dict(experts=2, k=256, n=128, tokens=128, topk=2, routing="uniform")
+CASES["dswiglu_mid"] = dict(experts=8, k=4096, n=3584, tokens=4096, topk=2, routing="uniform")
+CASES["wgrad_tiny"] = dict(m=384, n=640, groups=[256, 384])
+CASES["wgrad_mid"] = dict(m=4096, n=7168, groups=[4096] * 8)
 CASES["fp4_tiny_nvfp4"] = dict(experts=2, k=512, n=128, tokens=128, topk=2, routing="uniform", sf=(16, "e4m3"))
 CASES["fp4_tiny_mxfp4"] = dict(experts=2, k=512, n=128, tokens=128, topk=2, routing="uniform", sf=(32, "e8m0"))
 CASES["fp4_tiny_e8m0x16"] = dict(experts=2, k=512, n=128, tokens=128, topk=2, routing="uniform", sf=(16, "e8m0"))
@@ -517,7 +651,7 @@ def main():
     out = []
     for name in args.cases.split(","):
         try:
-            (run_case_fp4 if name.startswith("fp4_") else run_case_glu if name in GLU_CASES else run_case_fc2 if name in FC2_CASES else run_case)(
+            (run_case_dswiglu if name.startswith("dswiglu") else run_case_wgrad if name.startswith("wgrad") else run_case_fp4 if name.startswith("fp4_") else run_case_glu if name in GLU_CASES else run_case_fc2 if name in FC2_CASES else run_case)(
                 name, CASES[name], out)
         except Exception as exc:  # keep going: a JIT failure of one case is a result too
             out.append({"case": name, "error": f"{type(exc).__name__}: {exc}"})

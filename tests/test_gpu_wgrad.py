@@ -5,6 +5,8 @@ E4M3 per 16 plus per-expert global scales), widened by an empty expert, accumula
 Gate: relative Frobenius error <= 2e-2 of the float32 reference for bf16 / fp16 outputs, <= 1e-5 for float32.
 """
 
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -83,9 +85,10 @@ def test_wgrad_ragged_groups_empty_expert_accumulate_and_float32():
     import cudnn_frontend_b200 as cf
     from cudnn_frontend_b200 import ops
 
-    # token groups that are not multiples of the 128-byte k-tile (96, 32), an empty expert, rows and columns that do
-    # not fill their last tile (m = 200, n = 288), nine k-tiles in the last expert (the ring wraps twice)
-    m, n, groups = 200, 288, [96, 0, 32, 1152]
+    # an empty expert, rows and columns that do not fill their last tile (m = 200, n = 288), nine k-tiles in the last
+    # expert (the ring wraps twice).  Groups are multiples of 128 tokens: the reference's scale-tensor shape
+    # (round_up(rows, 128), round_up(tokens / 32, 4)) holds the experts' blocks only then.
+    m, n, groups = 200, 288, [128, 0, 256, 1152]
     fmt = ("e4m3", 32, "e8m0")
     a, b, sfa, sfb = _operands(2, m, n, groups, fmt)
     ta, tb, tsfa, tsfb, offs = _device(a, b, sfa, sfb, groups, fmt, m, n)
@@ -122,3 +125,21 @@ def test_wgrad_unaligned_group_is_reported_not_computed():
     torch.cuda.synchronize()
     assert ops.device_status(clear=True) == 202
     assert float(out.float().abs().max()) == 0.0
+
+
+def test_wgrad_is_bit_identical_to_the_reference_kernel_fixture(golden_dir):
+    """Inputs and the bf16 output of cudnn-frontend's grouped_gemm_wgrad_wrapper_sm100 recorded on a B200: every bit
+    of the [E, m, n] result must match."""
+    import cudnn_frontend_b200 as cf
+
+    g = np.load(os.path.join(golden_dir, "reference_kernel_wgrad.npz"))
+    m, tokens = g["a"].shape
+    n = g["b"].shape[0]
+    cols = (tokens // 32 + 3) // 4 * 4
+    ta = torch.from_numpy(g["a"]).cuda().view(torch.float8_e4m3fn)
+    tb = torch.from_numpy(g["b"]).cuda().view(torch.float8_e4m3fn).t()
+    sfa = torch.from_numpy(g["sfa"]).cuda().view(torch.float8_e8m0fnu).view(-1, cols)
+    sfb = torch.from_numpy(g["sfb"]).cuda().view(torch.float8_e8m0fnu).view(-1, cols)
+    out = cf.grouped_gemm_wgrad_wrapper_sm100(ta, tb, sfa, sfb, torch.from_numpy(g["offsets"]).cuda(), sf_vec_size=32)["wgrad_tensor"]
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(out.view(torch.int16).cpu().numpy(), g["wgrad"])

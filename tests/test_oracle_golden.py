@@ -241,3 +241,29 @@ def test_fp4_oracle_against_the_reference_kernel_fixture(golden_dir, fixture):
     assert np.mean(orc.bf16_round(out["c"][:m]) == c_ref) >= 0.995
     assert np.linalg.norm(orc.bf16_round(out["c"][:m]) - c_ref) <= 1e-3 * np.linalg.norm(c_ref)
     assert np.linalg.norm(orc.bf16_round(out["d"][:m]) - d_ref) <= 4e-3 * np.linalg.norm(d_ref)  # approximate SiLU in the kernel
+
+
+def test_wgrad_oracle_against_the_reference_kernel_fixture(golden_dir):
+    """Inputs and the bf16 output of the reference's grouped_gemm_wgrad_wrapper_sm100 (fp8 operands, E8M0 scales per
+    32 tokens, token groups [256, 384], m = 384, n = 640) recorded on a B200 (baseline/run_reference_kernels.py --cases
+    wgrad_tiny).  Pins the oracle's reading of the per-expert scale blocks and of the token ranges."""
+    g = _load(golden_dir, "reference_kernel_wgrad.npz")
+    m, tokens = g["a"].shape
+    n = g["b"].shape[0]
+    offs = g["offsets"]
+    sfa_groups, sfb_groups, start, pos_a, pos_b = [], [], 0, 0, 0
+    for end in offs.tolist():
+        kb = (end - start) // 32
+        for rows, flat, groups, which in ((m, g["sfa"], sfa_groups, "a"), (n, g["sfb"], sfb_groups, "b")):
+            size = orc.sf_nbytes(rows, end - start)
+            pos = pos_a if which == "a" else pos_b
+            groups.append(orc.sf_unpack(flat[pos : pos + size], rows, kb)[0])
+            if which == "a":
+                pos_a += size
+            else:
+                pos_b += size
+        start = end
+    out = orc.wgrad_reference(g["a"], g["b"], sfa_groups, sfb_groups, offs)
+    ref = _bf16_bits_to_f32(g["wgrad"].view(np.uint16))
+    assert np.mean(orc.bf16_round(out) == ref) >= 0.995
+    assert np.linalg.norm(orc.bf16_round(out) - ref) <= 1e-3 * np.linalg.norm(ref)
