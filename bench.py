@@ -672,6 +672,8 @@ def bench_single(args):
         torch.cuda.empty_cache()
         extras.update(bench_fp4(dev, stream))
         torch.cuda.empty_cache()
+        extras.update(bench_backward(dev, stream))
+        torch.cuda.empty_cache()
         import ep_bench
 
         # the workload of the multi-GPU runs (--gpus 2/4/8) with all experts on this GPU
@@ -849,6 +851,54 @@ def bench_fp4(dev, stream):
         t = time_trials(lambda: op.execute(a, b, None, d, sfa, sfb, r.padded_offsets, alpha, amax_tensor=amax), stream)
         out["fc1_" + name] = {"tflops": flops / (t["median_ms"] * 1e-3) / 1e12, "timing": t, "pct_of_fp4_nominal_9000": 100.0 * flops / (t["median_ms"] * 1e-3) / 9e15,
                               "operands": f"E2M1 with {'E4M3' if sf_vec == 16 else 'E8M0'} scales per {sf_vec} elements"}  # fmt: skip
+    return out
+
+
+def bench_backward(dev, stream):
+    """The backward pair on the Mixtral shape (E=8, hidden 4096, intermediate 14336, 32768 routed rows): dSwiGLU
+    (gradient GEMM with K = hidden, N = intermediate, fused activation backward, E4M3 D_row / D_col with scales) and
+    the weight gradient of FC1 (m = hidden, n = 2 x intermediate, the experts split the 32768 tokens), bf16 output."""
+    import torch
+
+    import cudnn_frontend_b200 as cf
+    from cudnn_frontend_b200 import ops, synthetic
+
+    out = {}
+    cfg = dict(experts=8, k=4096, n=14336, tokens=16384, topk=2, routing="uniform")
+    p = synthetic.make_problem(cfg, dev, seed=4, m_aligned=128)
+    e, n, k, m = cfg["experts"], cfg["n"], cfg["k"], p["m_rows"]
+    g = torch.Generator(device=dev).manual_seed(8)
+    c_fwd = torch.empty((m, 2 * n), device=dev).uniform_(-3, 3, generator=g).to(torch.bfloat16).view(m, 2 * n, 1)
+    d_row = torch.empty((m, 2 * n, 1), dtype=torch.float8_e4m3fn, device=dev)
+    d_col = torch.empty_like(d_row)
+    dprob = torch.zeros((m, 1, 1), device=dev)
+    sfd_row, sfd_col = ops.empty_sf(m, 2 * n, 1, device=dev), ops.empty_sf(2 * n, m, 1, device=dev)
+    beta, norm = torch.ones(e, device=dev), torch.ones(1, device=dev)
+    op = cf.GroupedGemmDswigluSm100(p["a"], p["b"], c_fwd, d_row, d_col, p["sfa"], p["sfb"], p["padded_offsets"], p["alpha"], beta, p["prob"], dprob,
+                                    sample_sfd_row=sfd_row, sample_sfd_col=sfd_col, sample_norm_const=norm, sf_vec_size=32, m_aligned=128)  # fmt: skip
+    assert op.check_support()
+    op.compile()
+    t = time_trials(lambda: op.execute(p["a"], p["b"], c_fwd, d_row, d_col, p["sfa"], p["sfb"], p["padded_offsets"], p["alpha"], beta, p["prob"], dprob,
+                                       sfd_row_tensor=sfd_row, sfd_col_tensor=sfd_col, norm_const_tensor=norm), stream)  # fmt: skip
+    out["dswiglu_mixtral"] = {"tflops": p["flops"] / (t["median_ms"] * 1e-3) / 1e12, "timing": t,
+                              "outputs": "E4M3 D_row and D_col [32768+pad, 28672] with row and column scales, dprob"}  # fmt: skip
+    del p, c_fwd, d_row, d_col, sfd_row, sfd_col, op
+    torch.cuda.empty_cache()
+
+    m_w, n_w, tokens = 4096, 28672, 32768
+    a = torch.empty((m_w, tokens), device=dev).uniform_(-2, 2, generator=g).to(torch.float8_e4m3fn)
+    b = torch.empty((n_w, tokens), device=dev).uniform_(-2, 2, generator=g).to(torch.float8_e4m3fn).t()
+    cols = tokens // 32
+    sfa = torch.randint(124, 131, (m_w, cols), generator=g, device=dev, dtype=torch.int32).to(torch.uint8).view(torch.float8_e8m0fnu)
+    sfb = torch.randint(124, 131, (n_w, cols), generator=g, device=dev, dtype=torch.int32).to(torch.uint8).view(torch.float8_e8m0fnu)
+    offs = torch.arange(1, e + 1, device=dev, dtype=torch.int32) * (tokens // e)
+    w = torch.empty((e, m_w, n_w), dtype=torch.bfloat16, device=dev)
+    opw = cf.GroupedGemmWgradSm100(a, b, sfa, sfb, offs, sample_wgrad=w, sf_vec_size=32)
+    assert opw.check_support()
+    opw.compile()
+    tw = time_trials(lambda: opw.execute(a, b, sfa, sfb, offs, wgrad_tensor=w), stream)
+    flops_w = 2.0 * tokens * m_w * n_w
+    out["wgrad_mixtral_fc1"] = {"tflops": flops_w / (tw["median_ms"] * 1e-3) / 1e12, "timing": tw, "outputs": "bf16 [8, 4096, 28672]"}
     return out
 
 

@@ -264,14 +264,14 @@ __device__ __forceinline__ Tile decode_tile(const Sched& sc, const GemmParams& p
 
 // wgrad: every expert has the same m_tiles x n_tiles output tiles; the row tile runs fastest so that CTAs working at
 // the same time share the B tile.  `chunk_prefix[e]` = scale chunks along K of the experts before e.
-__device__ __forceinline__ Tile decode_tile_wgrad(const GemmParams& p, const int* chunk_prefix, int s, int sf_vec_shift, int bytes_shift) {
-  const int m_tiles = (p.m_rows + BM - 1) / BM;
+__device__ __forceinline__ Tile decode_tile_wgrad(const GemmParams& p, const int* chunk_prefix, int tile_m, int s, int sf_vec_shift, int bytes_shift) {
+  const int m_tiles = (p.m_rows + tile_m - 1) / tile_m;
   const int per_expert = m_tiles * p.n_tiles;
   Tile t;
   t.expert = s / per_expert;
   const int j = s - t.expert * per_expert;
   t.n_tile = j / m_tiles;
-  t.row0 = (j - t.n_tile * m_tiles) * BM;
+  t.row0 = (j - t.n_tile * m_tiles) * tile_m;
   t.row_end = p.m_rows;
   t.m_tiles = m_tiles;
   const int tok0 = t.expert == 0 ? 0 : p.offsets[t.expert - 1];
@@ -585,7 +585,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       run += __shfl_sync(0xffffffffu, incl, 31);
     }
     if (lane == 0) {
-      totals_smem[0] = p.num_experts * ((p.m_rows + BM - 1) / BM) * p.n_tiles;
+      totals_smem[0] = p.num_experts * ((p.m_rows + C::TILE_M - 1) / C::TILE_M) * p.n_tiles;
       totals_smem[1] = 0;
     }
   } else if (warp == 2) {
@@ -639,7 +639,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
   const int total_tiles = totals_smem[0];
   const Sched sched = {prefix_heavy, prefix_light, totals_smem[1], total_tiles};
   auto decode = [&](int s) -> Tile {
-    if constexpr (kEpi == EPI_WGRAD) return decode_tile_wgrad(p, prefix_heavy, s, kFmt == 2 ? 4 : 5, kFmt ? 1 : 0);
+    if constexpr (kEpi == EPI_WGRAD) return decode_tile_wgrad(p, prefix_heavy, C::TILE_M, s, kFmt == 2 ? 4 : 5, kFmt ? 1 : 0);
     else return decode_tile(sched, p, C::TILE_M, s);
   };
 
@@ -718,7 +718,21 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             if (!__all_sync(0xffffffffu, mbar_wait(empty_bar(stage), phase ^ 1, wc, ST_PRODUCER_EMPTY))) { ok = false; break; }
             const uint32_t fb = leader_full0 + 8u * stage;
             if (elect_one() && !skip_loads) {
-              if (!side_b) {
+              if (kEpi == EPI_WGRAD) {
+                // scale chunks are addressed by their index in the operand's whole chunk array: the experts' blocks
+                // follow one another, each [128-row block][chunk along K]
+                if (!side_b) {
+                  if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(stage), C::TX_BYTES);
+                  tma_load_2d_pair(a_dst0 + stage * A_STAGE_BYTES, &tmap_a, fb, kc, my_row0);
+                  tma_load_2d_pair(sfa_dst0 + stage * SFA_STAGE_BYTES, &tmap_sfa, fb, 0,
+                                   tile.chunk0 * ((p.m_rows + BM - 1) / BM) + m_blk * rest_k + kt * CPK);
+                } else {
+                  tma_load_2d_pair(b_dst0 + stage * C::B_STAGE_BYTES, bmap, fb, kc, b_row);
+                  const int c = tile.chunk0 * p.n_blocks + nblk0 * rest_k + kt * CPK;
+                  tma_load_2d_pair(sfb_dst0 + stage * SFB_STAGE_BYTES, sfbmap, fb, 0, c);
+                  tma_load_2d_pair(sfb_dst0 + stage * SFB_STAGE_BYTES + 512 * CPK, sfbmap, fb, 0, c + rest_k);
+                }
+              } else if (!side_b) {
                 if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(stage), C::TX_BYTES);
                 tma_load_2d_pair(a_dst0 + stage * A_STAGE_BYTES, &tmap_a, fb, kc, my_row0);
                 tma_load_3d_pair(sfa_dst0 + stage * SFA_STAGE_BYTES, &tmap_sfa, fb, 0, kt * CPK, m_blk);
@@ -1856,10 +1870,40 @@ static int run_wgrad(const b200moe_gemm_args* a, void* stream_v) {
     rc = encode_map(&maps[1], CU_TENSOR_MAP_DATA_TYPE_UINT8, a->b, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
   }
-  const int64_t tiles = (int64_t)p.num_experts * ((p.m_rows + BM - 1) / BM) * p.n_tiles;
+  // 256 x 256 tiles on CTA pairs when the output has at least two row blocks (every expert has the same tiles, so
+  // nothing is lost to padding beyond m's own remainder); flags force either mode
+  bool pair = p.m_rows > BM;
+  if (a->flags & B200MOE_FLAG_TILE_SINGLE) pair = false;
+  if (a->flags & B200MOE_FLAG_TILE_PAIR) pair = true;
+  if (pair) {
+    // B: this CTA's half of the 256 columns; scale chunks as a plain array of 512-byte chunks (an expert's blocks may
+    // hold up to one chunk per row block more than k / (4 sf_vec): the bound below covers that)
+    const uint64_t dims[2] = {(uint64_t)p.k_bytes, (uint64_t)p.n};
+    const uint64_t strides[1] = {(uint64_t)p.k_bytes};
+    const uint32_t box[2] = {BK, 128};
+    rc = encode_map(&maps[1], CU_TENSOR_MAP_DATA_TYPE_UINT8, a->b, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    const uint64_t chunks_k = (uint64_t)((p.k + sf_vec - 1) / sf_vec + 3) / 4 + (uint64_t)p.num_experts;
+    const uint32_t sbox[2] = {128, 1u << fmt};
+    const uint64_t sstrides[1] = {512};
+    const uint64_t adims[2] = {128, chunks_k * (uint64_t)((p.m_rows + 127) / 128)};
+    rc = encode_map(&maps[2], CU_TENSOR_MAP_DATA_TYPE_UINT32, a->sfa, 2, adims, sstrides, sbox, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc) return rc;
+    const uint64_t bdims[2] = {128, chunks_k * (uint64_t)p.n_blocks};
+    rc = encode_map(&maps[3], CU_TENSOR_MAP_DATA_TYPE_UINT32, a->sfb, 2, bdims, sstrides, sbox, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc) return rc;
+  }
+  const int tile_m = pair ? 2 * BM : BM;
+  const int64_t tiles = (int64_t)p.num_experts * ((p.m_rows + tile_m - 1) / tile_m) * p.n_tiles;
   int units = di->sm_count - (a->sm_margin > 0 ? a->sm_margin : 0);
+  if (pair) units /= 2;
   if (units < 1) units = 1;
   if ((int64_t)units > tiles) units = (int)tiles;
+  if (pair) {
+    if (fmt == 1) return launch<EPI_WGRAD, false, true, false, 1>(maps, p, 2 * units, di, stream);
+    if (fmt == 2) return launch<EPI_WGRAD, false, true, false, 2>(maps, p, 2 * units, di, stream);
+    return launch<EPI_WGRAD, false, true, false, 0>(maps, p, 2 * units, di, stream);
+  }
   if (fmt == 1) return launch<EPI_WGRAD, false, false, false, 1>(maps, p, units, di, stream);
   if (fmt == 2) return launch<EPI_WGRAD, false, false, false, 2>(maps, p, units, di, stream);
   return launch<EPI_WGRAD, false, false, false, 0>(maps, p, units, di, stream);

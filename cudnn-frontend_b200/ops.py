@@ -251,7 +251,7 @@ def launch_grouped_gemm(
 def launch_wgrad(
     *, a: torch.Tensor, b: torch.Tensor, sfa: torch.Tensor, sfb: torch.Tensor, offsets: torch.Tensor, wgrad: torch.Tensor, m: int, n: int,
     tokens: int, sf_vec_size: int = 32, scale_a: Optional[torch.Tensor] = None, scale_b: Optional[torch.Tensor] = None, accumulate: bool = False,
-    sm_margin: int = 0, stream=None,
+    sm_margin: int = 0, stream=None, tile_mode: Optional[str] = None,
 ) -> None:  # fmt: skip
     """Call b200moe_wgrad: ``a [m, tokens]`` and ``b`` stored ``[n, tokens]`` (both contiguous along the tokens),
     ``offsets [E]`` int32 token END offsets, ``wgrad [E, m, n]`` bf16 / fp16 / float32."""
@@ -269,6 +269,8 @@ def launch_wgrad(
     args.sf_vec_size = int(sf_vec_size)
     args.sf_dtype = _lib.DTYPE_E4M3 if sfa.dtype == torch.float8_e4m3fn else 0
     args.flags = _lib.FLAG_ACCUMULATE if accumulate else 0
+    mode = tile_mode or os.environ.get("B200MOE_TILE_MODE", "auto")
+    args.flags |= {"auto": 0, "single": _lib.FLAG_TILE_SINGLE, "pair": _lib.FLAG_TILE_PAIR}[mode]
     args.sm_margin = sm_margin
     with torch.cuda.device(a.device):
         rc = _lib.load().b200moe_wgrad(ctypes.byref(args), _stream_ptr(stream))

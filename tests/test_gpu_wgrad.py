@@ -17,6 +17,13 @@ from tests import helpers as H
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(params=["single", "pair"], autouse=True)
+def tile_mode(request, monkeypatch):
+    """Every case runs with 128 x 256 single-CTA tiles and with 256 x 256 CTA-pair tiles."""
+    monkeypatch.setenv("B200MOE_TILE_MODE", request.param)
+    return request.param
+
+
 def _operands(seed, m, n, groups, fmt):
     """fmt: ("e4m3", 32, "e8m0") | ("e2m1", 32, "e8m0") | ("e2m1", 16, "e4m3") ..."""
     ab, sf_vec, sf_dtype = fmt

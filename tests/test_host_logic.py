@@ -97,7 +97,7 @@ def test_fc1_check_support_error_classes():
         cf.GroupedGemmSwigluSm100(**ok, sf_vec_size=32, m_aligned=192).check_support()
     with pytest.raises(ValueError, match="cluster"):
         cf.GroupedGemmSwigluSm100(**ok, sf_vec_size=32, cluster_shape_mn=(3, 1)).check_support()
-    # FP4 inputs are in the reference's matrix but not built here; E4M3 and E5M2 are
+    # raw uint8 FP4 operands (the reference reads uint8 as packed FP4) are not built; float4_e2m1fn_x2 is
     bad = dict(ok, sample_a=torch.empty((256, 128, 1), dtype=torch.uint8), sample_b=ok["sample_b"].view(torch.uint8))
     with pytest.raises(NotImplementedError):
         cf.GroupedGemmSwigluSm100(**bad, sf_vec_size=32).check_support()
@@ -296,3 +296,73 @@ def test_balanced_placement_fills_every_rank_and_evens_out_rows():
     assert balanced_placement(loads, 8) == slot  # deterministic
     with pytest.raises(ValueError):
         balanced_placement(loads[:63], 8)
+
+
+def test_fp4_operands_are_validated_on_their_logical_shape():
+    """float4_e2m1fn_x2 packs two elements per byte along K: the operator classes validate the element counts
+    (python/cudnn/api_base.py:650-713), the scale-factor shapes follow sf_vec_size."""
+    m, n, k, e = 256, 256, 256, 2
+    a = torch.empty((m, k // 2, 1), dtype=torch.uint8).view(torch.float4_e2m1fn_x2)
+    b = torch.empty((e, n, k // 2), dtype=torch.uint8).view(torch.float4_e2m1fn_x2).permute(1, 2, 0)
+    assert api_base.TensorSpec.of(a, "a").logical().shape == (m, k, 1)
+    assert api_base.TensorSpec.of(b, "b").logical().stride == (k, 1, n * k)
+    sfa = ops.empty_sf(m, k, 1, device="cpu", dtype=torch.float8_e4m3fn, sf_vec=16)
+    sfb = ops.empty_sf(n, k, e, device="cpu", dtype=torch.float8_e4m3fn, sf_vec=16)
+    common = dict(sample_a=a, sample_b=b, sample_c=torch.empty((m, n, 1), dtype=torch.bfloat16), sample_sfa=sfa, sample_sfb=sfb,
+                  sample_padded_offsets=torch.zeros(e, dtype=torch.int32), sample_alpha=torch.ones(e), sample_d_col=None)  # fmt: skip
+    with pytest.raises(ValueError, match="fp16, bf16, or float32"):
+        cf.GroupedGemmSwigluSm100(**common, sample_d=torch.empty((m, n // 2, 1), dtype=torch.float8_e4m3fn), sf_vec_size=16).check_support()
+    with pytest.raises(NotImplementedError, match="float32"):  # the reference disables fp4 + sf_vec 16 + float32 D
+        cf.GroupedGemmSwigluSm100(**common, sample_d=torch.empty((m, n // 2, 1), dtype=torch.float32), sf_vec_size=16).check_support()
+    with pytest.raises(ValueError, match="SFA must have shape"):  # scale tensors made for 16 do not fit 32
+        cf.GroupedGemmSwigluSm100(**common, sample_d=torch.empty((m, n // 2, 1), dtype=torch.bfloat16), sf_vec_size=32).check_support()
+    if not torch.cuda.is_available():  # a valid NVFP4 configuration gets as far as the device check
+        with pytest.raises(RuntimeError, match="CUDA"):
+            cf.GroupedGemmSwigluSm100(**common, sample_d=torch.empty((m, n // 2, 1), dtype=torch.bfloat16), sf_vec_size=16).check_support()
+
+
+def test_dswiglu_and_wgrad_check_support_error_classes():
+    m, n, k, e = 256, 128, 128, 2
+    a = torch.empty((m, k, 1), dtype=torch.float8_e4m3fn)
+    b = torch.empty((e, n, k), dtype=torch.float8_e4m3fn).permute(1, 2, 0)
+    c = torch.empty((m, 2 * n, 1), dtype=torch.bfloat16)
+    d8 = torch.empty((m, 2 * n, 1), dtype=torch.float8_e4m3fn)
+    sfa, sfb = ops.empty_sf(m, k, 1, device="cpu"), ops.empty_sf(n, k, e, device="cpu")
+    offs, ones = torch.zeros(e, dtype=torch.int32), torch.ones(e)
+    prob, dprob = torch.ones((m, 1, 1)), torch.zeros((m, 1, 1))
+    sfd = dict(sample_sfd_row=ops.empty_sf(m, 2 * n, 1, device="cpu"), sample_sfd_col=ops.empty_sf(2 * n, m, 1, device="cpu"), sample_norm_const=torch.ones(1))
+    args = (a, b, c, d8, d8, sfa, sfb, offs, ones, ones, prob, dprob)
+    with pytest.raises(ValueError, match="epilogue operation"):
+        cf.GroupedGemmDswigluSm100(*args, **sfd, sf_vec_size=32, epilogue_op="gelu")
+    with pytest.raises(NotImplementedError, match="epilogue_op"):
+        cf.GroupedGemmDswigluSm100(*args, **sfd, sf_vec_size=32, epilogue_op="relu").check_support()
+    with pytest.raises(ValueError, match="D_row must be fp8"):  # fp8 operands take an fp8 D_row, as in the reference
+        cf.GroupedGemmDswigluSm100(a, b, c, c, c, sfa, sfb, offs, ones, ones, prob, dprob, sf_vec_size=32).check_support()
+    with pytest.raises(ValueError, match="C must have shape"):
+        cf.GroupedGemmDswigluSm100(a, b, torch.empty((m, n, 1), dtype=torch.bfloat16), d8, d8, sfa, sfb, offs, ones, ones, prob, dprob, **sfd,
+                                   sf_vec_size=32).check_support()  # fmt: skip
+    if not torch.cuda.is_available():
+        with pytest.raises(RuntimeError, match="CUDA"):
+            cf.GroupedGemmDswigluSm100(*args, **sfd, sf_vec_size=32).check_support()
+
+    # weight gradient: A (m, T) and B (T, n) stored [n, T]; scale tensors (round_up(rows, 128), round_up(T / 32, 4))
+    mw, nw, t = 384, 640, 640
+    aw = torch.empty((mw, t), dtype=torch.float8_e4m3fn)
+    bw = torch.empty((nw, t), dtype=torch.float8_e4m3fn).t()
+    sa = torch.empty((384, 20), dtype=torch.uint8).view(torch.float8_e8m0fnu)
+    sb = torch.empty((640, 20), dtype=torch.uint8).view(torch.float8_e8m0fnu)
+    off = torch.tensor([256, 640], dtype=torch.int32)
+    w = torch.empty((2, mw, nw), dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="not both"):
+        cf.GroupedGemmWgradSm100(aw, bw, sa, sb, off, sample_wgrad=w, num_experts=2)
+    with pytest.raises(ValueError, match="contiguous along the tokens"):
+        cf.GroupedGemmWgradSm100(aw, torch.empty((t, nw), dtype=torch.float8_e4m3fn), sa, sb, off, sample_wgrad=w, sf_vec_size=32).check_support()
+    with pytest.raises(ValueError, match="sample_sfa must have shape"):
+        cf.GroupedGemmWgradSm100(aw, bw, sb, sb, off, sample_wgrad=w, sf_vec_size=32).check_support()
+    with pytest.raises(NotImplementedError, match="discrete"):
+        cf.GroupedGemmWgradSm100(aw, bw, sa, sb, off, num_experts=2, wgrad_shape=(mw, nw), wgrad_dtype=torch.bfloat16, sf_vec_size=32).check_support()
+    with pytest.raises(NotImplementedError, match="discrete"):
+        cf.grouped_gemm_wgrad_wrapper_sm100(aw, bw, sa, sb, off, output_mode="discrete")
+    if not torch.cuda.is_available():
+        with pytest.raises(RuntimeError, match="CUDA"):
+            cf.GroupedGemmWgradSm100(aw, bw, sa, sb, off, sample_wgrad=w, sf_vec_size=32).check_support()
