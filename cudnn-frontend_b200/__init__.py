@@ -8,6 +8,7 @@ Public names mirror what the reference exports from its package root through laz
     DiscreteGroupedGemmSwigluSm100, discrete_grouped_gemm_swiglu_wrapper_sm100
     GroupedGemmGluSm100, grouped_gemm_glu_wrapper_sm100      (unified FC1: swiglu / geglu, bias)
     GroupedGemmDswigluSm100, grouped_gemm_dswiglu_wrapper_sm100  (backward of FC1's activation)
+    DiscreteGroupedGemmDswigluSm100, discrete_grouped_gemm_dswiglu_wrapper_sm100
     GroupedGemmWgradSm100, grouped_gemm_wgrad_wrapper_sm100      (weight gradient: the experts split K)
 
 plus what the reference does not have: ``quantize_mxfp8`` (activation quantiser), the routing
@@ -27,6 +28,8 @@ _LAZY = {
     "grouped_gemm_glu_wrapper_sm100": "grouped_gemm_glu",
     "GroupedGemmDswigluSm100": "grouped_gemm_dswiglu",
     "grouped_gemm_dswiglu_wrapper_sm100": "grouped_gemm_dswiglu",
+    "DiscreteGroupedGemmDswigluSm100": "grouped_gemm_dswiglu",
+    "discrete_grouped_gemm_dswiglu_wrapper_sm100": "grouped_gemm_dswiglu",
     "GroupedGemmWgradSm100": "grouped_gemm_wgrad",
     "grouped_gemm_wgrad_wrapper_sm100": "grouped_gemm_wgrad",
     "TupleDict": "api_base",

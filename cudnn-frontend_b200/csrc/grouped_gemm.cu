@@ -1087,7 +1087,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       } else if constexpr (kEpi == EPI_WGRAD) {
         // plain store (or accumulation) of the expert's [m, n] tile, scaled by the expert's global scale
         const bool empty = tile.k_tiles == 0;  // an expert without tokens: nothing was accumulated
-        const int64_t out_base = ((int64_t)tile.expert * p.m_rows + row) * p.n;
+        // one [E, m, n] tensor, or (discrete output) one [m, n] allocation per expert behind a pointer array
+        void* const d_out = p.d_peer_ptrs ? reinterpret_cast<void*>(p.d_peer_ptrs[tile.expert]) : p.d;
+        const int64_t out_base = ((int64_t)(p.d_peer_ptrs ? 0 : tile.expert) * p.m_rows + row) * p.n;
 #pragma unroll 1
         for (int i = 0; i < 4; ++i) {
           const int bb = reverse ? 3 - i : i;
@@ -1107,14 +1109,14 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           for (int j = 0; j < 32; ++j) v[j] = empty ? 0.f : v[j] * alpha;
           if (p.accumulate) {
             if (p.d_f32) {
-              const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.d) + out_base + dn);
+              const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(d_out) + out_base + dn);
 #pragma unroll
               for (int q = 0; q < 8; ++q) {
                 const float4 o = src[q];
                 v[4 * q] += o.x; v[4 * q + 1] += o.y; v[4 * q + 2] += o.z; v[4 * q + 3] += o.w;
               }
             } else {
-              const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.d) + out_base + dn);
+              const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(d_out) + out_base + dn);
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
                 const uint4 o = src[q];
@@ -1125,7 +1127,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
               }
             }
           }
-          store_d32(reinterpret_cast<__nv_bfloat16*>(p.d), out_base + dn, v, wide, d_f16, p.d_f32 != 0);
+          store_d32(reinterpret_cast<__nv_bfloat16*>(d_out), out_base + dn, v, wide, d_f16, p.d_f32 != 0);
         }
       } else if constexpr (kEpi == EPI_DSWIGLU) {
         // 4 blocks of 32 accumulator columns per half; block b of the GEMM's N owns columns [64 b, 64 b + 64) of C and D
@@ -1801,9 +1803,9 @@ static int run_wgrad(const b200moe_gemm_args* a, void* stream_v) {
   const char* op = "wgrad";
   if (!a) return fail(B200MOE_E_NULL, "args is NULL");
   if (a->num_experts == 0 || a->m_rows == 0 || a->n == 0) return B200MOE_OK;
-  if (!a->a || !a->b || !a->sfa || !a->sfb || !a->padded_offsets || !a->d)
-    return fail(B200MOE_E_NULL, "%s: a, b, sfa, sfb, padded_offsets (token END offsets) and d are required", op);
-  if (a->b_ptrs || a->sfb_ptrs) return fail(B200MOE_E_UNSUPPORTED, "%s: one [E, m, n] output tensor only (no per-expert pointers)", op);
+  if (!a->a || !a->b || !a->sfa || !a->sfb || !a->padded_offsets || (!a->d && !a->d_peer_ptrs))
+    return fail(B200MOE_E_NULL, "%s: a, b, sfa, sfb, padded_offsets (token END offsets) and d (or d_peer_ptrs) are required", op);
+  if (a->b_ptrs || a->sfb_ptrs) return fail(B200MOE_E_UNSUPPORTED, "%s: a and b are single tensors (per-expert outputs go in d_peer_ptrs)", op);
   if (a->m_rows < 0 || a->m_rows > (1ll << 30) || a->n <= 0 || a->k < 0 || a->k > (1ll << 30) || a->num_experts < 0 || a->num_experts > MAX_EXPERTS)
     return fail(B200MOE_E_SHAPE, "%s: bad sizes m=%lld n=%lld tokens=%lld E=%d", op, (long long)a->m_rows, (long long)a->n, (long long)a->k, a->num_experts);
   const bool fp4 = a->ab_dtype == B200MOE_DTYPE_E2M1;
@@ -1839,6 +1841,7 @@ static int run_wgrad(const b200moe_gemm_args* a, void* stream_v) {
   p.ab_format = (a->ab_dtype == B200MOE_DTYPE_E5M2 || fp4) ? ((1u << 7) | (1u << 10)) : 0u;
   p.sf_e4m3 = sf_e4m3 ? 1 : 0;
   p.d = a->d;
+  p.d_peer_ptrs = a->d_peer_ptrs;  // discrete output: one [m, n] allocation per expert (the kernel trusts them to be 16-byte aligned)
   p.m_rows = (int)a->m_rows;
   p.n = (int)a->n;
   p.k = (int)a->k;
@@ -1852,7 +1855,7 @@ static int run_wgrad(const b200moe_gemm_args* a, void* stream_v) {
   p.accumulate = (a->flags & B200MOE_FLAG_ACCUMULATE) ? 1 : 0;
   p.raster_group_m = 1;
   p.wait_limit_ns = a->wait_limit_ms > 0 ? (uint64_t)a->wait_limit_ms * 1000000ull : kWaitLimitNs;
-  p.wide_stores = ((uintptr_t)a->d % 32 == 0) && (((int64_t)p.n * (d_f32 ? 4 : 2)) % 32 == 0);
+  p.wide_stores = !a->d_peer_ptrs && ((uintptr_t)a->d % 32 == 0) && (((int64_t)p.n * (d_f32 ? 4 : 2)) % 32 == 0);
 
   CUtensorMap maps[4];
   memset(maps, 0, sizeof(maps));

@@ -14,8 +14,14 @@ with ``gate / up`` the even / odd 32-column blocks of ``beta_e * C`` and ``sig =
 ``D_col`` come out row- and column-quantised (fp8 operands) or as a 16-bit / float32 ``D_row`` with an ``(l, 2, 1)``
 amax (FP4 operands), as in the reference.
 
+``DiscreteGroupedGemmDswigluSm100`` / ``discrete_grouped_gemm_dswiglu_wrapper_sm100``
+(python/cudnn/discrete_grouped_gemm/discrete_grouped_gemm_dswiglu/api.py:70-768, :770-1000) are the same operator
+with one weight allocation per expert behind ``b_ptrs`` / ``sfb_ptrs``, K- or N-major (``b_major``), optionally with the
+dynamic tile scheduler.
+
 Differences a caller can observe: groups may be padded to any multiple of 128 rows; ``epilogue_op`` other than the
-identity, a float32 ``C`` and the dbias output are not built (``NotImplementedError``).
+identity, ``act_func`` other than ``"dswiglu"``, a float32 ``C`` and the dbias output are not built
+(``NotImplementedError``).
 """
 
 from __future__ import annotations
@@ -58,8 +64,15 @@ class GroupedGemmDswigluSm100(OperatorBase):
         m_aligned: int = 256,
         discrete_col_sfd: bool = False,
         epilogue_op: Optional[str] = None,
+        _discrete: Optional[dict] = None,
     ):
+        """``_discrete`` is how :class:`DiscreteGroupedGemmDswigluSm100` describes its weights (``num_experts``,
+        ``b_shape``, ``b_dtype``, ``b_major``, ``use_dynamic_sched``); ``sample_b`` / ``sample_sfb`` are then ``None``."""
         super().__init__()
+        self.discrete = _discrete is not None
+        self._dw = _discrete or {}
+        self.use_dynamic_sched = bool(self._dw.get("use_dynamic_sched", False))
+        self._workspace = None
         self.a = TensorSpec.of(sample_a, "sample_a")
         self.b = TensorSpec.of(sample_b, "sample_b")
         self.c = TensorSpec.of(sample_c, "sample_c")
@@ -102,10 +115,21 @@ class GroupedGemmDswigluSm100(OperatorBase):
             self._logger.warning("discrete_col_sfd is True but generate_sfd is False, discrete_col_sfd will be ignored")
             self.discrete_col_sfd = False
 
-        self._value_error_if(len(self.a.shape) != 3 or len(self.b.shape) != 3, "A must be (m, k, 1) and B (n, k, l)")
-        a_l, b_l = self.a.logical(), self.b.logical()  # FP4 operands: two elements per byte along K
+        self._value_error_if(len(self.a.shape) != 3, "A must be (m, k, 1)")
+        a_l = self.a.logical()  # FP4 operands: two elements per byte along K
         tensor_m, k, _ = a_l.shape
-        n, _, l = b_l.shape
+        if self.discrete:
+            b_l = None
+            self._value_error_if(len(self._dw["b_shape"]) < 2, "b_shape must be (n, k)")
+            n, b_k = self._dw["b_shape"][0], self._dw["b_shape"][1]
+            l = int(self._dw["num_experts"])
+            self._value_error_if(b_k != k, f"B K dimension ({b_k}) must match A K dimension ({k})")
+            self._value_error_if(self.padded_offsets.shape[0] != l, f"padded_offsets length ({self.padded_offsets.shape[0]}) must equal num_experts ({l})")
+            self._value_error_if(self._dw["b_major"] not in ("k", "n"), f"b_major must be 'k' or 'n', got {self._dw['b_major']}")
+        else:
+            self._value_error_if(len(self.b.shape) != 3, "B must be (n, k, l)")
+            b_l = self.b.logical()
+            n, _, l = b_l.shape
         self._check_shape(a_l, (tensor_m, k, 1), "A")
         self._check_shape(b_l, (n, k, l), "B")
         self._check_shape(self.c, (tensor_m, n * 2, 1), "C")
@@ -131,7 +155,11 @@ class GroupedGemmDswigluSm100(OperatorBase):
         self._check_dtype(self.b, self.ab_dtype, "B", "B must have the same dtype as A")
         fp4 = self._is_fp4x2(self.ab_dtype)
         self._b_nmajor = False
-        if not fp4 and n > 1 and k > 1 and self.b.stride[0] == 1 and self.b.stride[1] == n:
+        if self.discrete:
+            self._value_error_if(self._dw["b_dtype"] != self.ab_dtype, f"b_dtype ({self._dw['b_dtype']}) must match A dtype ({self.ab_dtype})")
+            self._value_error_if(fp4 and self._dw["b_major"] != "k", "b_major must be 'k' when ab_dtype is fp4")
+            self._b_nmajor = self._dw["b_major"] == "n"
+        elif not fp4 and n > 1 and k > 1 and self.b.stride[0] == 1 and self.b.stride[1] == n:
             self._check_stride(self.b, (1, n, n * k), "For fp8 ab_dtype, B must have k- or n-major layout")
             self._b_nmajor = True
         else:
@@ -192,6 +220,9 @@ class GroupedGemmDswigluSm100(OperatorBase):
         if not self._is_supported:
             self.check_support()
         ops._lib.load()  # fails loudly when the CUDA library is missing
+        nbytes = ops.workspace_bytes(self.expert_cnt, self.discrete, self.use_dynamic_sched)
+        if nbytes and self._workspace is None:
+            self._workspace = torch.empty(nbytes, dtype=torch.uint8, device=self.a.device)
         self._is_compiled = True
 
     def execute(
@@ -220,12 +251,17 @@ class GroupedGemmDswigluSm100(OperatorBase):
         if a_tensor.shape[0] == 0:
             return
         gen = bool(self.generate_sfd) and sfd_row_tensor is not None and norm_const_tensor is not None
+        # discrete weights: b_tensor / sfb_tensor carry the int64 pointer arrays
         ops.grouped_gemm_op(
             "dswiglu",
             a=a_tensor,
             sfa=sfa_tensor,
-            b=b_tensor,
-            sfb=sfb_tensor,
+            b=None if self.discrete else b_tensor,
+            sfb=None if self.discrete else sfb_tensor,
+            b_ptrs=b_tensor if self.discrete else None,
+            sfb_ptrs=sfb_tensor if self.discrete else None,
+            workspace=self._workspace,
+            dynamic_sched=self.use_dynamic_sched,
             padded_offsets=padded_offsets,
             alpha=alpha_tensor,
             beta=beta_tensor,
@@ -337,3 +373,170 @@ def grouped_gemm_dswiglu_wrapper_sm100(
     )  # fmt: skip
     return TupleDict(d_row_tensor=d_row_tensor, d_col_tensor=d_col_tensor, dprob_tensor=dprob_tensor, amax_tensor=amax_tensor,
                      sfd_row_tensor=sfd_row_tensor, sfd_col_tensor=sfd_col_tensor)  # fmt: skip
+
+
+class DiscreteGroupedGemmDswigluSm100(GroupedGemmDswigluSm100):
+    """dSwiGLU with one weight allocation per expert: ``b_ptrs`` / ``sfb_ptrs`` are int64 device arrays of the experts'
+    ``[n, k]`` (``b_major="k"``) or ``[k, n]`` (``"n"``) weights and of their 128x4 scale tensors."""
+
+    def __init__(
+        self,
+        sample_a: torch.Tensor,
+        num_experts: int,
+        b_shape: Tuple[int, ...],
+        b_dtype: torch.dtype,
+        sample_c: torch.Tensor,
+        sample_d_row: torch.Tensor,
+        sample_d_col: Optional[torch.Tensor],
+        sample_sfa: torch.Tensor,
+        sample_padded_offsets: torch.Tensor,
+        sample_alpha: torch.Tensor,
+        sample_beta: torch.Tensor,
+        sample_prob: torch.Tensor,
+        sample_dprob: torch.Tensor,
+        sample_dbias: Optional[torch.Tensor] = None,
+        sample_sfd_row: Optional[torch.Tensor] = None,
+        sample_sfd_col: Optional[torch.Tensor] = None,
+        sample_amax: Optional[torch.Tensor] = None,
+        sample_norm_const: Optional[torch.Tensor] = None,
+        acc_dtype: torch.dtype = torch.float32,
+        mma_tiler_mn: Tuple[int, int] = (256, 256),
+        cluster_shape_mn: Optional[Tuple[int, int]] = None,
+        sf_vec_size: int = 16,
+        vector_f32: bool = False,
+        m_aligned: int = 256,
+        discrete_col_sfd: bool = False,
+        act_func: str = "dswiglu",
+        b_major: str = "k",
+        epilogue_op: Optional[str] = None,
+        use_dynamic_sched: bool = False,
+    ):
+        super().__init__(
+            sample_a, None, sample_c, sample_d_row, sample_d_col, sample_sfa, None, sample_padded_offsets, sample_alpha, sample_beta, sample_prob,
+            sample_dprob, sample_sfd_row=sample_sfd_row, sample_sfd_col=sample_sfd_col, sample_amax=sample_amax, sample_norm_const=sample_norm_const,
+            acc_dtype=acc_dtype, mma_tiler_mn=mma_tiler_mn, cluster_shape_mn=cluster_shape_mn, sf_vec_size=sf_vec_size, vector_f32=vector_f32,
+            m_aligned=m_aligned, discrete_col_sfd=discrete_col_sfd, epilogue_op=epilogue_op,
+            _discrete=dict(num_experts=num_experts, b_shape=tuple(b_shape), b_dtype=b_dtype, b_major=b_major, use_dynamic_sched=use_dynamic_sched),
+        )  # fmt: skip
+        self._value_error_if(act_func not in ("dswiglu", "dgeglu"), f"act_func must be 'dswiglu' or 'dgeglu', got {act_func}")
+        self.act_func = act_func
+        self.dbias = TensorSpec.of(sample_dbias, "sample_dbias")
+
+    def check_support(self) -> bool:
+        self._not_implemented_error_if(self.act_func != "dswiglu", f"act_func {self.act_func!r} is not built ('dswiglu' is)")
+        self._not_implemented_error_if(self.dbias is not None, "the dbias output is not built")
+        return super().check_support()
+
+    def execute(
+        self,
+        a_tensor: torch.Tensor,
+        b_ptrs: torch.Tensor,
+        c_tensor: torch.Tensor,
+        d_row_tensor: torch.Tensor,
+        d_col_tensor: Optional[torch.Tensor],
+        sfa_tensor: torch.Tensor,
+        sfb_ptrs: torch.Tensor,
+        padded_offsets: torch.Tensor,
+        alpha_tensor: torch.Tensor,
+        beta_tensor: torch.Tensor,
+        prob_tensor: torch.Tensor,
+        dprob_tensor: torch.Tensor,
+        dbias_tensor: Optional[torch.Tensor] = None,
+        sfd_row_tensor: Optional[torch.Tensor] = None,
+        sfd_col_tensor: Optional[torch.Tensor] = None,
+        amax_tensor: Optional[torch.Tensor] = None,
+        norm_const_tensor: Optional[torch.Tensor] = None,
+        current_stream=None,
+    ) -> None:
+        """Launch on ``current_stream``; allocates nothing and never reads the pointer values on the host."""
+        from .discrete_grouped_gemm_swiglu import _require_pointer_tensor
+
+        if dbias_tensor is not None:
+            raise NotImplementedError("the dbias output is not built")
+        _require_pointer_tensor(b_ptrs, "b_ptrs", self.expert_cnt)
+        _require_pointer_tensor(sfb_ptrs, "sfb_ptrs", self.expert_cnt)
+        super().execute(a_tensor, b_ptrs, c_tensor, d_row_tensor, d_col_tensor, sfa_tensor, sfb_ptrs, padded_offsets, alpha_tensor, beta_tensor,
+                        prob_tensor, dprob_tensor, sfd_row_tensor=sfd_row_tensor, sfd_col_tensor=sfd_col_tensor, amax_tensor=amax_tensor,
+                        norm_const_tensor=norm_const_tensor, current_stream=current_stream)  # fmt: skip
+
+
+_cache_of_DiscreteGroupedGemmDswigluSm100Objects = {}
+
+
+def discrete_grouped_gemm_dswiglu_wrapper_sm100(
+    a_tensor: torch.Tensor,
+    b_ptrs: torch.Tensor,
+    c_tensor: torch.Tensor,
+    sfa_tensor: torch.Tensor,
+    sfb_ptrs: torch.Tensor,
+    padded_offsets: torch.Tensor,
+    alpha_tensor: torch.Tensor,
+    beta_tensor: torch.Tensor,
+    prob_tensor: torch.Tensor,
+    dprob_tensor: torch.Tensor,
+    n: int,
+    b_dtype: torch.dtype,
+    generate_dbias: bool = False,
+    norm_const_tensor: Optional[torch.Tensor] = None,
+    acc_dtype: torch.dtype = torch.float32,
+    d_dtype: torch.dtype = torch.bfloat16,
+    cd_major: str = "n",
+    mma_tiler_mn: Tuple[int, int] = (256, 256),
+    cluster_shape_mn: Optional[Tuple[int, int]] = None,
+    sf_vec_size: int = 16,
+    vector_f32: bool = False,
+    m_aligned: int = 256,
+    discrete_col_sfd: bool = False,
+    act_func: str = "dswiglu",
+    b_major: str = "k",
+    epilogue_op: Optional[str] = None,
+    use_dynamic_sched: bool = False,
+    current_stream=None,
+) -> TupleDict:
+    """One-shot discrete-weight dSwiGLU.  The caller owns ``dprob_tensor`` (zeroed by the caller, as in the reference).
+    Returns ``TupleDict(d_row_tensor, d_col_tensor, dprob_tensor, dbias_tensor, amax_tensor, sfd_row_tensor,
+    sfd_col_tensor)``."""
+    from .discrete_grouped_gemm_swiglu import _require_pointer_tensor
+
+    if generate_dbias:
+        raise NotImplementedError("the dbias output is not built")
+    if cd_major != "n":
+        raise ValueError(f"cd_major must be 'n', got {cd_major}")
+    _require_pointer_tensor(b_ptrs, "b_ptrs")
+    l = b_ptrs.shape[0]
+    _require_pointer_tensor(sfb_ptrs, "sfb_ptrs", l)
+    valid_m, k, _ = a_tensor.shape
+    if a_tensor.dtype == torch.float4_e2m1fn_x2:
+        k *= 2
+    dev = a_tensor.device
+    d_row_tensor = torch.empty_strided((valid_m, n * 2, 1), (n * 2, 1, valid_m * n * 2), dtype=d_dtype, device=dev)
+    d_col_tensor = torch.empty_strided((valid_m, n * 2, 1), (n * 2, 1, valid_m * n * 2), dtype=d_dtype, device=dev)
+    sfd_row_tensor = sfd_col_tensor = amax_tensor = None
+    if a_tensor.dtype in (torch.float8_e4m3fn, torch.float8_e5m2):
+        sfd_row_tensor = _alloc_sfd(valid_m, n * 2, sf_vec_size, sfa_tensor.dtype, dev)
+        sfd_col_tensor = _alloc_sfd(n * 2, valid_m, sf_vec_size, sfa_tensor.dtype, dev)
+    if d_dtype in (torch.bfloat16, torch.float16):
+        amax_tensor = torch.full((l, 2, 1), float("-inf"), dtype=torch.float32, device=dev)
+    out = TupleDict(d_row_tensor=d_row_tensor, d_col_tensor=d_col_tensor, dprob_tensor=dprob_tensor, dbias_tensor=None, amax_tensor=amax_tensor,
+                    sfd_row_tensor=sfd_row_tensor, sfd_col_tensor=sfd_col_tensor)  # fmt: skip
+    if valid_m == 0:
+        return out
+    key = (a_tensor.dtype, c_tensor.dtype, sfa_tensor.dtype, b_dtype, tuple(a_tensor.shape[1:]), n, l, norm_const_tensor is not None, acc_dtype, d_dtype,
+           tuple(mma_tiler_mn), None if cluster_shape_mn is None else tuple(cluster_shape_mn), sf_vec_size, vector_f32, m_aligned, discrete_col_sfd,
+           act_func, b_major, epilogue_op, use_dynamic_sched, str(dev))  # fmt: skip
+    op = _cache_of_DiscreteGroupedGemmDswigluSm100Objects.get(key)
+    if op is None:
+        op = DiscreteGroupedGemmDswigluSm100(
+            a_tensor, l, (n, k), b_dtype, c_tensor, d_row_tensor, d_col_tensor, sfa_tensor, padded_offsets, alpha_tensor, beta_tensor, prob_tensor,
+            dprob_tensor, sample_sfd_row=sfd_row_tensor, sample_sfd_col=sfd_col_tensor, sample_amax=amax_tensor,
+            sample_norm_const=norm_const_tensor if sfd_row_tensor is not None else None, acc_dtype=acc_dtype, mma_tiler_mn=mma_tiler_mn,
+            cluster_shape_mn=cluster_shape_mn, sf_vec_size=sf_vec_size, vector_f32=vector_f32, m_aligned=m_aligned,
+            discrete_col_sfd=discrete_col_sfd, act_func=act_func, b_major=b_major, epilogue_op=epilogue_op, use_dynamic_sched=use_dynamic_sched,
+        )  # fmt: skip
+        assert op.check_support(), "Unsupported configuration"
+        op.compile()
+        _cache_of_DiscreteGroupedGemmDswigluSm100Objects[key] = op
+    op.execute(a_tensor, b_ptrs, c_tensor, d_row_tensor, d_col_tensor, sfa_tensor, sfb_ptrs, padded_offsets, alpha_tensor, beta_tensor, prob_tensor,
+               dprob_tensor, sfd_row_tensor=sfd_row_tensor, sfd_col_tensor=sfd_col_tensor, amax_tensor=amax_tensor,
+               norm_const_tensor=norm_const_tensor if sfd_row_tensor is not None else None, current_stream=current_stream)  # fmt: skip
+    return out

@@ -7,9 +7,12 @@ owns tokens ``[offsets[e-1], offsets[e])`` and its own 128x4 block of scale fact
 cols)`` / ``SFB (round_up(n, 128), cols)``; ``wgrad[e] = gs_a[e] gs_b[e] (A_e SFA_e)(B_e SFB_e)^T``, shape ``(E, m,
 n)`` in bf16 / fp16 / float32, overwritten or (``accumulate_on_output``) added to.
 
+Dense output mode writes one ``(E, m, n)`` tensor, discrete output mode one ``(m, n)`` allocation per expert behind the
+int64 pointer tensor ``wgrad_ptrs``.
+
 Differences a caller can observe: every expert's token count must be a multiple of 32 (the reference's scale shape
-rule already implies a multiple of ``4 * sf_vec_size``); the discrete output mode (one allocation per expert behind
-``wgrad_ptrs``) is not built (``NotImplementedError``).
+rule already implies a multiple of ``4 * sf_vec_size``); the per-expert allocations of the discrete mode must be
+contiguous ``(m, n)`` and 16-byte aligned.
 """
 
 from __future__ import annotations
@@ -62,6 +65,8 @@ class GroupedGemmWgradSm100(OperatorBase):
         self.sfb = TensorSpec.of(sample_sfb, "sample_sfb")
         self.offsets = TensorSpec.of(sample_offsets, "sample_offsets")
         self.wgrad = TensorSpec.of(sample_wgrad, "sample_wgrad")
+        self.wgrad_expert = TensorSpec.of(sample_wgrad_expert, "sample_wgrad_expert")
+        self.wgrad_shape = tuple(wgrad_shape) if wgrad_shape is not None else None
         self.gs_a = TensorSpec.of(sample_global_scale_a, "sample_global_scale_a")
         self.gs_b = TensorSpec.of(sample_global_scale_b, "sample_global_scale_b")
         self.expert_cnt = num_experts if self.discrete else self.wgrad.shape[0]
@@ -96,6 +101,11 @@ class GroupedGemmWgradSm100(OperatorBase):
         if not self.discrete:
             self._check_shape(self.wgrad, (self.expert_cnt, m, n), "sample_wgrad")
             self._check_stride(self.wgrad, (m * n, n, 1), "sample_wgrad must be contiguous")
+        else:
+            self._value_error_if(self.wgrad_shape != (m, n), f"wgrad_shape must be {(m, n)}, got {self.wgrad_shape}")
+            self._check_shape(self.wgrad_expert, (m, n), "single_expert_wgrad")
+            self._check_stride(self.wgrad_expert, (n, 1), "sample_wgrad_expert must be contiguous")
+            self._check_dtype(self.wgrad_expert, self.wgrad_dtype, "sample_wgrad_expert", "sample_wgrad_expert must have the same dtype as wgrad_dtype")
         self._value_error_if(self.mma_tiler_mn[0] not in (128, 256), f"mma_tiler_mn[0] must be 128 or 256, got {self.mma_tiler_mn[0]}")
         self._value_error_if(self.mma_tiler_mn[1] not in (128, 256), f"mma_tiler_mn[1] must be 128 or 256, got {self.mma_tiler_mn[1]}")
         cm, cn = self.cluster_shape_mn
@@ -115,7 +125,6 @@ class GroupedGemmWgradSm100(OperatorBase):
         self._value_error_if(self._is_fp8(dtype) and self.sf_vec_size != 32, f"fp8 operands take sf_vec_size 32, got {self.sf_vec_size}")
 
         # what this build implements of the reference's surface
-        self._not_implemented_error_if(self.discrete, "the discrete output mode (wgrad_ptrs) is not built")
         self._not_implemented_error_if(dtype in (torch.uint8, torch.bfloat16), f"operands of dtype {dtype} are not built (float8 and float4_e2m1fn_x2 are)")
         self._value_error_if(tokens % 32 != 0 or n % 32 != 0, f"tokens ({tokens}) and n ({n}) must be multiples of 32")
         self._m, self._n, self._tokens = m, n, tokens
@@ -145,11 +154,17 @@ class GroupedGemmWgradSm100(OperatorBase):
         """Launch on ``current_stream``; allocates nothing.  The token count may differ from the sample's (it is read
         from ``a_tensor``)."""
         self._ensure_compiled()
-        if wgrad_tensor is None:
+        if not self.discrete and wgrad_tensor is None:
             raise ValueError("wgrad_tensor is required in dense mode")
+        if self.discrete:
+            if wgrad_ptrs is None:
+                raise ValueError("wgrad_ptrs is required in discrete mode")
+            if wgrad_ptrs.dtype != torch.int64 or wgrad_ptrs.dim() != 1 or wgrad_ptrs.shape[0] != self.expert_cnt or not wgrad_ptrs.is_cuda:
+                raise ValueError(f"wgrad_ptrs must be a 1-D int64 CUDA tensor of {self.expert_cnt} addresses")
         tokens = a_tensor.shape[1] * (2 if a_tensor.dtype == torch.float4_e2m1fn_x2 else 1)
-        ops.launch_wgrad(a=a_tensor, b=b_tensor, sfa=sfa_tensor, sfb=sfb_tensor, offsets=offsets_tensor, wgrad=wgrad_tensor, m=self._m, n=self._n,
-                         tokens=tokens, sf_vec_size=self.sf_vec_size, scale_a=global_scale_a, scale_b=global_scale_b,
+        ops.launch_wgrad(a=a_tensor, b=b_tensor, sfa=sfa_tensor, sfb=sfb_tensor, offsets=offsets_tensor,
+                         wgrad=None if self.discrete else wgrad_tensor, wgrad_ptrs=wgrad_ptrs if self.discrete else None, wgrad_dtype=self.wgrad_dtype,
+                         m=self._m, n=self._n, tokens=tokens, sf_vec_size=self.sf_vec_size, scale_a=global_scale_a, scale_b=global_scale_b,
                          accumulate=self.accumulate_on_output, stream=current_stream)  # fmt: skip
 
 
@@ -179,11 +194,26 @@ def grouped_gemm_wgrad_wrapper_sm100(
     passes none (zeros with ``accumulate_on_output``, as in the reference, api.py:587-592)."""
     if output_mode not in ("dense", "discrete"):
         raise ValueError(f"output_mode must be 'dense' or 'discrete', got {output_mode}")
-    if output_mode == "discrete" or wgrad_ptrs is not None:
-        raise NotImplementedError("the discrete output mode (wgrad_ptrs) is not built")
     hidden = a_tensor.shape[0]
     intermediate = b_tensor.shape[1]
     e = offsets_tensor.shape[0]
+    if output_mode == "discrete":
+        if wgrad_ptrs is None:
+            raise ValueError("wgrad_ptrs is required in discrete output mode")
+        key = ("discrete", a_tensor.dtype, sfa_tensor.dtype, hidden, intermediate, e, wgrad_dtype, tuple(mma_tiler_mn), sf_vec_size, accumulate_on_output,
+               global_scale_a is not None, str(a_tensor.device))  # fmt: skip
+        op = _cache_of_GroupedGemmWgradSm100Objects.get(key)
+        if op is None:
+            op = GroupedGemmWgradSm100(a_tensor, b_tensor, sfa_tensor, sfb_tensor, offsets_tensor, num_experts=e, wgrad_shape=(hidden, intermediate),
+                                       wgrad_dtype=wgrad_dtype, sample_global_scale_a=global_scale_a, sample_global_scale_b=global_scale_b,
+                                       acc_dtype=acc_dtype, mma_tiler_mn=mma_tiler_mn, cluster_shape_mn=cluster_shape_mn, sf_vec_size=sf_vec_size,
+                                       accumulate_on_output=accumulate_on_output)  # fmt: skip
+            assert op.check_support(), "Unsupported configuration"
+            op.compile()
+            _cache_of_GroupedGemmWgradSm100Objects[key] = op
+        op.execute(a_tensor, b_tensor, sfa_tensor, sfb_tensor, offsets_tensor, wgrad_ptrs=wgrad_ptrs, global_scale_a=global_scale_a,
+                   global_scale_b=global_scale_b, current_stream=current_stream)  # fmt: skip
+        return TupleDict(wgrad_tensor=None)
     if wgrad_tensor is None:
         alloc = torch.zeros if accumulate_on_output else torch.empty
         wgrad_tensor = alloc((e, hidden, intermediate), dtype=wgrad_dtype, device=a_tensor.device)

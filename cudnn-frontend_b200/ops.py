@@ -249,21 +249,24 @@ def launch_grouped_gemm(
 
 
 def launch_wgrad(
-    *, a: torch.Tensor, b: torch.Tensor, sfa: torch.Tensor, sfb: torch.Tensor, offsets: torch.Tensor, wgrad: torch.Tensor, m: int, n: int,
-    tokens: int, sf_vec_size: int = 32, scale_a: Optional[torch.Tensor] = None, scale_b: Optional[torch.Tensor] = None, accumulate: bool = False,
+    *, a: torch.Tensor, b: torch.Tensor, sfa: torch.Tensor, sfb: torch.Tensor, offsets: torch.Tensor, wgrad: Optional[torch.Tensor], m: int, n: int,
+    tokens: int, wgrad_ptrs: Optional[torch.Tensor] = None, wgrad_dtype: Optional[torch.dtype] = None, sf_vec_size: int = 32, scale_a: Optional[torch.Tensor] = None, scale_b: Optional[torch.Tensor] = None, accumulate: bool = False,
     sm_margin: int = 0, stream=None, tile_mode: Optional[str] = None,
 ) -> None:  # fmt: skip
     """Call b200moe_wgrad: ``a [m, tokens]`` and ``b`` stored ``[n, tokens]`` (both contiguous along the tokens),
-    ``offsets [E]`` int32 token END offsets, ``wgrad [E, m, n]`` bf16 / fp16 / float32."""
-    _require_cuda(a, b, sfa, sfb, offsets, wgrad, scale_a, scale_b)
+    ``offsets [E]`` int32 token END offsets, ``wgrad [E, m, n]`` bf16 / fp16 / float32 — or ``wgrad_ptrs``, an int64
+    device tensor of E addresses of per-expert ``[m, n]`` allocations of ``wgrad_dtype``."""
+    _require_cuda(a, b, sfa, sfb, offsets, wgrad, scale_a, scale_b, wgrad_ptrs)
     args = _lib.GemmArgs()
     args.a, args.b, args.sfa, args.sfb = _ptr(a), _ptr(b), _ptr(sfa), _ptr(sfb)
     args.padded_offsets = _ptr(offsets)
     args.alpha, args.beta = _ptr(scale_a), _ptr(scale_b)
     args.d = _ptr(wgrad)
-    if wgrad.dtype not in (torch.bfloat16, torch.float16, torch.float32):
-        raise ValueError(f"wgrad dtype must be bfloat16, float16 or float32, got {wgrad.dtype}")
-    args.d_dtype = _D_DTYPES[wgrad.dtype]
+    args.d_peer_ptrs = _ptr(wgrad_ptrs)
+    out_dtype = wgrad.dtype if wgrad is not None else wgrad_dtype
+    if out_dtype not in (torch.bfloat16, torch.float16, torch.float32):
+        raise ValueError(f"wgrad dtype must be bfloat16, float16 or float32, got {out_dtype}")
+    args.d_dtype = _D_DTYPES[out_dtype]
     args.m_rows, args.n, args.k, args.num_experts = m, n, tokens, offsets.shape[0]
     args.ab_dtype = {torch.float8_e5m2: _lib.DTYPE_E5M2, torch.float4_e2m1fn_x2: _lib.DTYPE_E2M1}.get(a.dtype, _lib.DTYPE_E4M3)
     args.sf_vec_size = int(sf_vec_size)

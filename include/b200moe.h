@@ -236,7 +236,9 @@ int b200moe_dswiglu(const b200moe_gemm_args* args, void* stream);
  *      blocks one after the other (the layout torch's scaled_grouped_mm takes for its 2D-2D case);
  *   alpha, beta: optional per-expert scales (the reference's global_scale_a and global_scale_b), NULL = 1;
  *   d: [E, m_rows, n] bf16 / fp16 / float32 (d_dtype), d[e] = alpha_e beta_e (A_e SFA_e)(B_e SFB_e)^T, added to the existing
- *      contents with B200MOE_FLAG_ACCUMULATE.  Everything else in the struct is ignored.
+ *      contents with B200MOE_FLAG_ACCUMULATE; or (the reference's discrete output mode) d_peer_ptrs = int64 device array
+ *      of E addresses of per-expert [m_rows, n] allocations, 16-byte aligned, and d may be NULL.  Everything else in
+ *      the struct is ignored.
  * Replaces GroupedGemmWgradSm100.execute (python/cudnn/grouped_gemm/grouped_gemm_wgrad/api.py), kernel
  * BlockScaledMoEGroupedGemmWgradKernel (python/cudnn/grouped_gemm/grouped_gemm_wgrad/moe_blockscaled_grouped_gemm_wgrad.py).
  */

@@ -175,3 +175,43 @@ def test_dswiglu_fp4_matches_oracle(tile_mode, sf_vec, sf_dtype, d_dtype):
         live = np.isfinite(ref["amax"][:, 0])
         np.testing.assert_allclose(amax[live], ref["amax"][live], rtol=2e-2)
         assert np.all(np.isneginf(amax[~live]))
+
+
+@pytest.mark.parametrize("b_major,dynamic", [("k", False), ("n", False), ("k", True)])
+def test_discrete_dswiglu_equals_dense_bitwise(tile_mode, b_major, dynamic):
+    """One weight allocation per expert behind b_ptrs / sfb_ptrs (K- or N-major, static or dynamic scheduler) gives
+    the same bytes as the dense operator (the reference checks its discrete kernels the same way,
+    test/python/fe_api/test_discrete_grouped_gemm_swiglu.py:448-688)."""
+    import cudnn_frontend_b200 as cf
+
+    groups, n, k = [256, 0, 130, 384], 192, 256
+    e = len(groups)
+    valid, aligned, offs = orc.padded_end_offsets(groups, 128)
+    a, b, sfa, sfb = H.gen_operands(17, valid, n, k, e)
+    H.zero_padding_rows(a, groups, aligned)
+    rng = np.random.default_rng(17)
+    ta = H.dev_fp8(a).view(valid, k, 1)
+    tb_store = H.dev_fp8(b)
+    tsfa, tsfb = H.dev_sf(sfa, valid, k), H.dev_sf(sfb, n, k, e)
+    tc = torch.from_numpy(rng.uniform(-3, 3, (valid, 2 * n)).astype(np.float32)).to(torch.bfloat16).cuda().view(valid, 2 * n, 1)
+    toffs = torch.from_numpy(offs).cuda()
+    talpha, tbeta = torch.ones(e, device="cuda"), torch.full((e,), 0.5, device="cuda")
+    tprob = torch.from_numpy(rng.uniform(0.1, 1.0, valid).astype(np.float32)).cuda().view(valid, 1, 1)
+    norm = torch.ones(1, device="cuda")
+    kw = dict(norm_const_tensor=norm, d_dtype=torch.float8_e4m3fn, sf_vec_size=32, m_aligned=128)
+    dense = cf.grouped_gemm_dswiglu_wrapper_sm100(ta, tb_store.permute(1, 2, 0), tc, tsfa, tsfb, toffs, talpha, tbeta, tprob, **kw)
+    bl = [(tb_store[i].t().contiguous() if b_major == "n" else tb_store[i].clone()) for i in range(e)]
+    sl = [H.dev_sf(sfb[i], n, k) for i in range(e)]
+    b_ptrs = torch.tensor([x.data_ptr() for x in bl], dtype=torch.int64, device="cuda")
+    sfb_ptrs = torch.tensor([x.data_ptr() for x in sl], dtype=torch.int64, device="cuda")
+    dprob = torch.zeros((valid, 1, 1), device="cuda")
+    disc = cf.discrete_grouped_gemm_dswiglu_wrapper_sm100(ta, b_ptrs, tc, tsfa, sfb_ptrs, toffs, talpha, tbeta, tprob, dprob, n, torch.float8_e4m3fn,
+                                                          b_major=b_major, use_dynamic_sched=dynamic, **kw)  # fmt: skip
+    torch.cuda.synchronize()
+    for key in ("d_row_tensor", "d_col_tensor"):
+        assert torch.equal(dense[key].view(torch.uint8), disc[key].view(torch.uint8)), key
+    sfr_a = H.sf_to_numpy(dense["sfd_row_tensor"], valid, 2 * n // 32)
+    sfr_b = H.sf_to_numpy(disc["sfd_row_tensor"], valid, 2 * n // 32)
+    np.testing.assert_array_equal(sfr_a, sfr_b)
+    # dprob is accumulated with atomic adds from two tile halves per row: equal up to the order of two additions
+    torch.testing.assert_close(dense["dprob_tensor"], disc["dprob_tensor"], rtol=1e-5, atol=1e-5)

@@ -150,3 +150,21 @@ def test_wgrad_is_bit_identical_to_the_reference_kernel_fixture(golden_dir):
     out = cf.grouped_gemm_wgrad_wrapper_sm100(ta, tb, sfa, sfb, torch.from_numpy(g["offsets"]).cuda(), sf_vec_size=32)["wgrad_tensor"]
     torch.cuda.synchronize()
     np.testing.assert_array_equal(out.view(torch.int16).cpu().numpy(), g["wgrad"])
+
+
+def test_wgrad_discrete_output_equals_dense():
+    """One [m, n] allocation per expert behind wgrad_ptrs (the reference's discrete output mode) holds what the dense
+    [E, m, n] tensor holds."""
+    import cudnn_frontend_b200 as cf
+
+    m, n, groups = 384, 640, [256, 0, 384]
+    fmt = ("e4m3", 32, "e8m0")
+    a, b, sfa, sfb = _operands(5, m, n, groups, fmt)
+    ta, tb, tsfa, tsfb, offs = _device(a, b, sfa, sfb, groups, fmt, m, n)
+    dense = cf.grouped_gemm_wgrad_wrapper_sm100(ta, tb, tsfa, tsfb, offs, sf_vec_size=32)["wgrad_tensor"]
+    outs = [torch.full((m, n), 3.0, dtype=torch.bfloat16, device="cuda") for _ in groups]
+    ptrs = torch.tensor([o.data_ptr() for o in outs], dtype=torch.int64, device="cuda")
+    cf.grouped_gemm_wgrad_wrapper_sm100(ta, tb, tsfa, tsfb, offs, output_mode="discrete", wgrad_ptrs=ptrs, sf_vec_size=32)
+    torch.cuda.synchronize()
+    for e, o in enumerate(outs):
+        assert torch.equal(o, dense[e])

@@ -359,9 +359,9 @@ def test_dswiglu_and_wgrad_check_support_error_classes():
         cf.GroupedGemmWgradSm100(aw, torch.empty((t, nw), dtype=torch.float8_e4m3fn), sa, sb, off, sample_wgrad=w, sf_vec_size=32).check_support()
     with pytest.raises(ValueError, match="sample_sfa must have shape"):
         cf.GroupedGemmWgradSm100(aw, bw, sb, sb, off, sample_wgrad=w, sf_vec_size=32).check_support()
-    with pytest.raises(NotImplementedError, match="discrete"):
-        cf.GroupedGemmWgradSm100(aw, bw, sa, sb, off, num_experts=2, wgrad_shape=(mw, nw), wgrad_dtype=torch.bfloat16, sf_vec_size=32).check_support()
-    with pytest.raises(NotImplementedError, match="discrete"):
+    with pytest.raises(ValueError, match="wgrad_shape"):
+        cf.GroupedGemmWgradSm100(aw, bw, sa, sb, off, num_experts=2, wgrad_shape=(mw, 2 * nw), wgrad_dtype=torch.bfloat16, sf_vec_size=32).check_support()
+    with pytest.raises(ValueError, match="wgrad_ptrs is required"):
         cf.grouped_gemm_wgrad_wrapper_sm100(aw, bw, sa, sb, off, output_mode="discrete")
     if not torch.cuda.is_available():
         with pytest.raises(RuntimeError, match="CUDA"):
