@@ -292,12 +292,12 @@ def reference_gpu_kernel():
         padded = (counts + 255) // 256 * 256
         offsets = torch.cumsum(padded, 0).to(torch.int32)
         m = int(offsets[-1].item())
-        a = (torch.randn(m, k, generator=g, device=dev) * 100.0).clamp_(-448, 448).to(torch.float8_e4m3fn)
+        a = (torch.randn(m, k, generator=g, device=dev) * 100.0).clamp_(-448, 448)
         starts = offsets.long() - padded
         rows = torch.arange(m, device=dev)
         owner = torch.searchsorted(offsets.long(), rows, right=True).clamp(max=e - 1)
-        a[(rows - starts[owner]) >= counts[owner]] = 0
-        a = torch.as_strided(a, (m, k, 1), (k, 1, m * k))
+        a[(rows - starts[owner]) >= counts[owner]] = 0  # padding rows of every group are zero
+        a = torch.as_strided(a.to(torch.float8_e4m3fn), (m, k, 1), (k, 1, m * k))
         b = torch.empty((e, n, k), dtype=torch.float8_e4m3fn, device=dev)
         for i in range(e):
             b[i] = (torch.randn(n, k, generator=g, device=dev) * 100.0).clamp_(-448, 448).to(torch.float8_e4m3fn)
