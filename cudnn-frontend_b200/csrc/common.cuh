@@ -553,6 +553,25 @@ __device__ __forceinline__ uint32_t pack16x2_from_float(float lo, float hi, bool
   return bf16x2_from_float(lo, hi);
 }
 
+// Packed float32 arithmetic of sm_100: two products / sums / fused multiply-adds per instruction, each lane
+// rounded to nearest even exactly like the scalar instruction, so results do not change.
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
+__device__ __forceinline__ float2 mul2(float2 a, float b) { return __fmul2_rn(a, make_float2(b, b)); }
+__device__ __forceinline__ float2 add2(float2 a, float2 b) { return __fadd2_rn(a, b); }
+__device__ __forceinline__ float2 add2(float2 a, float b) { return __fadd2_rn(a, make_float2(b, b)); }
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
+// v[0..n) *= s, two at a time (n even)
+template <int N>
+__device__ __forceinline__ void scale_inplace(float* v, float s) {
+  const float2 ss = make_float2(s, s);
+#pragma unroll
+  for (int j = 0; j < N; j += 2) {
+    const float2 r = __fmul2_rn(make_float2(v[j], v[j + 1]), ss);
+    v[j] = r.x;
+    v[j + 1] = r.y;
+  }
+}
+
 // Scale applied to a block before the E4M3 conversion: norm / sf, clamped to FLT_MAX.
 __device__ __forceinline__ float quant_scale(float norm_const, float sf_value) {
   return fmin_nan(norm_const * rcp_approx(sf_value), 3.40282346638528859812e38f);

@@ -339,15 +339,14 @@ __device__ __forceinline__ void store_d32(__nv_bfloat16* base, int64_t idx, cons
 }
 
 __device__ __forceinline__ void store_e4m3x32(uint8_t* dst, const float* v, float scale, bool wide, bool e5m2 = false) {
-  uint4 o[2];
+  uint32_t o[8];
 #pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    o[i].x = fp8x4_from_float(v[16 * i + 0] * scale, v[16 * i + 1] * scale, v[16 * i + 2] * scale, v[16 * i + 3] * scale, e5m2);
-    o[i].y = fp8x4_from_float(v[16 * i + 4] * scale, v[16 * i + 5] * scale, v[16 * i + 6] * scale, v[16 * i + 7] * scale, e5m2);
-    o[i].z = fp8x4_from_float(v[16 * i + 8] * scale, v[16 * i + 9] * scale, v[16 * i + 10] * scale, v[16 * i + 11] * scale, e5m2);
-    o[i].w = fp8x4_from_float(v[16 * i + 12] * scale, v[16 * i + 13] * scale, v[16 * i + 14] * scale, v[16 * i + 15] * scale, e5m2);
+  for (int i = 0; i < 8; ++i) {
+    const float2 lo = mul2(make_float2(v[4 * i], v[4 * i + 1]), scale);
+    const float2 hi = mul2(make_float2(v[4 * i + 2], v[4 * i + 3]), scale);
+    o[i] = fp8x4_from_float(lo.x, lo.y, hi.x, hi.y, e5m2);
   }
-  store_32B(dst, o[0], o[1], wide);
+  store_32B(dst, make_uint4(o[0], o[1], o[2], o[3]), make_uint4(o[4], o[5], o[6], o[7]), wide);
 }
 
 // Output format of the scale-factor-generating epilogue: the reciprocal of the value the block maximum is
@@ -366,7 +365,8 @@ __device__ __forceinline__ void store_scaled32(uint8_t* row_base, int64_t col, c
   if (fmt.bits16) {
     float t[32];
 #pragma unroll
-    for (int i = 0; i < 32; ++i) t[i] = v[i] * scale;
+    for (int i = 0; i < 32; ++i) t[i] = v[i];
+    scale_inplace<32>(t, scale);
     store_bf16x32(reinterpret_cast<__nv_bfloat16*>(row_base) + col, t, wide, fmt.f16);
   } else {
     store_e4m3x32(row_base + col, v, scale, wide, fmt.e5m2);
@@ -444,17 +444,20 @@ __device__ __forceinline__ uint32_t quant_col_block(uint8_t* row_base, int64_t c
   if (fmt.bits16) {
     float t[32];
 #pragma unroll
-    for (int i = 0; i < 32; ++i) t[i] = v[i] * __shfl_sync(0xffffffffu, my_sc, i);
+    for (int i = 0; i < 32; i += 2) {
+      const float2 r = mul2(make_float2(v[i], v[i + 1]), make_float2(__shfl_sync(0xffffffffu, my_sc, i), __shfl_sync(0xffffffffu, my_sc, i + 1)));
+      t[i] = r.x;
+      t[i + 1] = r.y;
+    }
     if (do_store) store_bf16x32(reinterpret_cast<__nv_bfloat16*>(row_base) + col, t, wide, fmt.f16);
     return my_sf;
   }
   uint32_t packed[8];
 #pragma unroll
   for (int i = 0; i < 32; i += 4) {
-    float s[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) s[j] = v[i + j] * __shfl_sync(0xffffffffu, my_sc, i + j);
-    packed[i >> 2] = fp8x4_from_float(s[0], s[1], s[2], s[3], fmt.e5m2);
+    const float2 lo = mul2(make_float2(v[i], v[i + 1]), make_float2(__shfl_sync(0xffffffffu, my_sc, i), __shfl_sync(0xffffffffu, my_sc, i + 1)));
+    const float2 hi = mul2(make_float2(v[i + 2], v[i + 3]), make_float2(__shfl_sync(0xffffffffu, my_sc, i + 2), __shfl_sync(0xffffffffu, my_sc, i + 3)));
+    packed[i >> 2] = fp8x4_from_float(lo.x, lo.y, hi.x, hi.y, fmt.e5m2);
   }
   if (do_store)
     store_32B(row_base + col, make_uint4(packed[0], packed[1], packed[2], packed[3]), make_uint4(packed[4], packed[5], packed[6], packed[7]),
@@ -1017,8 +1020,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
               }
             }
           } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) { g[j] *= alpha; u[j] *= alpha; }
+            scale_inplace<32>(g, alpha);
+            scale_inplace<32>(u, alpha);
           }
           if (p.c && row_ok) {
             store_bf16x32(p.c + (int64_t)row * p.n + cn, g, wide, c_f16);
@@ -1037,10 +1040,14 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             }
           } else {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const float e = ex2_approx(g[j] * -1.4426950408889634f);
-              const float s = rcp_approx(1.0f + e);
-              g[j] = ((s * g[j]) * u[j]) * prob;
+            for (int j = 0; j < 32; j += 2) {
+              const float2 gg = make_float2(g[j], g[j + 1]);
+              const float2 t = mul2(gg, -1.4426950408889634f);
+              const float2 d = add2(make_float2(ex2_approx(t.x), ex2_approx(t.y)), 1.0f);
+              const float2 s = make_float2(rcp_approx(d.x), rcp_approx(d.y));
+              const float2 r = mul2(mul2(mul2(s, gg), make_float2(u[j], u[j + 1])), prob);
+              g[j] = r.x;
+              g[j + 1] = r.y;
             }
           }
           if (p.amax && row_ok) {
@@ -1105,8 +1112,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           }
           const int dn = n0 + col;
           if (dn >= p.n || !row_ok) continue;
+          scale_inplace<32>(v, alpha);
+          if (empty) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = empty ? 0.f : v[j] * alpha;
+            for (int j = 0; j < 32; ++j) v[j] = 0.f;
+          }
           if (p.accumulate) {
             if (p.d_f32) {
               const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(d_out) + out_base + dn);
@@ -1164,31 +1174,46 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           }
           if (!live) continue;
           float d1[32];  // d_gate; v becomes d_up
+          const bool c_e5m2 = p.c_in_dtype == B200MOE_DTYPE_E5M2, c_is_f16 = p.c_in_dtype == B200MOE_DTYPE_F16;
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            // element j of the gate block and of the up block
-            float cg, cu;
+          for (int j = 0; j < 32; j += 2) {
+            // elements j, j + 1 of the gate block and of the up block
+            float2 cg, cu;
             if (c_bytes == 2) {
-              const uint16_t* h = reinterpret_cast<const uint16_t*>(craw);
-              cg = p.c_in_dtype == B200MOE_DTYPE_F16 ? __half2float(__ushort_as_half(h[j])) : __uint_as_float((uint32_t)h[j] << 16);
-              cu = p.c_in_dtype == B200MOE_DTYPE_F16 ? __half2float(__ushort_as_half(h[32 + j])) : __uint_as_float((uint32_t)h[32 + j] << 16);
+              const uint32_t* w = reinterpret_cast<const uint32_t*>(craw);
+              const uint32_t wg = w[j >> 1], wu = w[16 + (j >> 1)];
+              if (c_is_f16) {
+                cg = __half22float2(*reinterpret_cast<const __half2*>(&wg));
+                cu = __half22float2(*reinterpret_cast<const __half2*>(&wu));
+              } else {
+                cg = make_float2(__uint_as_float(wg << 16), __uint_as_float(wg & 0xffff0000u));
+                cu = make_float2(__uint_as_float(wu << 16), __uint_as_float(wu & 0xffff0000u));
+              }
             } else {
               const uint8_t* b8 = reinterpret_cast<const uint8_t*>(craw);
-              cg = fp8_to_float(b8[j], p.c_in_dtype == B200MOE_DTYPE_E5M2);
-              cu = fp8_to_float(b8[32 + j], p.c_in_dtype == B200MOE_DTYPE_E5M2);
+              cg = make_float2(fp8_to_float(b8[j], c_e5m2), fp8_to_float(b8[j + 1], c_e5m2));
+              cu = make_float2(fp8_to_float(b8[32 + j], c_e5m2), fp8_to_float(b8[33 + j], c_e5m2));
             }
-            // the reference kernel's operation order, every product and sum rounded on its own
-            const float g = __fmul_rn(v[j], alpha2);
-            const float gate = __fmul_rn(cg, beta);
-            const float up = __fmul_rn(cu, beta);
-            const float e = ex2_approx(__fmul_rn(gate, -1.4426950408889634f));
-            const float sig = rcp_approx(__fadd_rn(e, 1.0f));
-            const float swish = __fmul_rn(gate, sig);
-            dprob_sum = __fadd_rn(dprob_sum, __fmul_rn(__fmul_rn(up, swish), g));
-            const float gp = __fmul_rn(g, prob);
-            v[j] = __fmul_rn(gp, swish);
-            const float dsig1 = __fadd_rn(__fmul_rn(gate, __fsub_rn(1.0f, sig)), 1.0f);
-            d1[j] = __fmul_rn(__fmul_rn(__fmul_rn(gp, up), sig), dsig1);
+            // the reference kernel's operation order, every product and sum rounded on its own (two elements per instruction)
+            const float2 g = mul2(make_float2(v[j], v[j + 1]), alpha2);
+            const float2 gate = mul2(cg, beta);
+            const float2 up = mul2(cu, beta);
+            const float2 t = mul2(gate, -1.4426950408889634f);
+            const float2 den = add2(make_float2(ex2_approx(t.x), ex2_approx(t.y)), 1.0f);
+            const float2 sig = make_float2(rcp_approx(den.x), rcp_approx(den.y));
+            const float2 swish = mul2(gate, sig);
+            const float2 dp = mul2(mul2(up, swish), g);
+            dprob_sum = __fadd_rn(__fadd_rn(dprob_sum, dp.x), dp.y);
+            const float2 gp = mul2(g, prob);
+            const float2 dup = mul2(gp, swish);
+            v[j] = dup.x;
+            v[j + 1] = dup.y;
+            // 1 - sig as one fused multiply-add (sig * -1 is exact, so the rounding is the subtraction's)
+            const float2 one_minus_sig = fma2(sig, make_float2(-1.0f, -1.0f), make_float2(1.0f, 1.0f));
+            const float2 dsig1 = add2(mul2(gate, one_minus_sig), 1.0f);
+            const float2 dg = mul2(mul2(mul2(gp, up), sig), dsig1);
+            d1[j] = dg.x;
+            d1[j + 1] = dg.y;
           }
           if (p.amax && row_ok) {
 #pragma unroll
@@ -1272,8 +1297,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
               for (int q = 0; q < 8; ++q) v[j + q] = fmaf(v[j + q], alpha, prob * bv[q]);
             }
           } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = (v[j] * alpha) * prob;
+            scale_inplace<32>(v, alpha);
+            scale_inplace<32>(v, prob);
           }
           if (p.amax && row_ok) {
 #pragma unroll
