@@ -506,6 +506,29 @@ __device__ __forceinline__ float warp_absmax(float x) {
   return r;
 }
 
+// the same, ignoring NaN inputs (fmaxf semantics)
+__device__ __forceinline__ float warp_absmax_number(float x) {
+  float r;
+  asm volatile("redux.sync.max.abs.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(x));
+  return r;
+}
+
+// float32 loads / stores at a shared-memory address (the .shared window, as smem_u32 returns it)
+__device__ __forceinline__ void st_shared_f32(uint32_t addr, float v) { asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory"); }
+__device__ __forceinline__ void st_shared_f32x4(uint32_t addr, float4 v) {
+  asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+__device__ __forceinline__ float ld_shared_f32(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ float4 ld_shared_f32x4(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
+  return v;
+}
+
 // float32 (>= 0) -> E8M0 byte: round up to a power of two, saturate to finite.
 __device__ __forceinline__ uint32_t e8m0_from_float(float x) {
   uint16_t out;

@@ -121,7 +121,10 @@ struct Cfg {
   static constexpr int MISC_OFF = BAR_OFF + NUM_BARS * 8;  // tmem ptr, abort flag, tile totals, scheduler ring
   static constexpr int PREFIX_OFF = MISC_OFF + 16 + SCHED_RING * 4;  // 2 x (E + 1) int32 tile prefixes (heavy, light)
   static constexpr int STAGING_OFF = (PREFIX_OFF + 2 * (MAX_EXPERTS + 1) * 4 + 15) & ~15;
-  static constexpr int TOTAL = STAGING_OFF + (kBulk ? NUM_EPI_WARPS * STAGING_WARP_BYTES : 0);
+  // column-quantisation scratch, 64 floats per epilogue warp: shares the staging area (staged rows are never
+  // quantised); E2M1 operands have no quantised output and no scratch
+  static constexpr int COLQ_OFF = STAGING_OFF;
+  static constexpr int TOTAL = STAGING_OFF + (kBulk ? NUM_EPI_WARPS * STAGING_WARP_BYTES : (kFmt ? 0 : NUM_EPI_WARPS * 256));
   static constexpr int SMEM_BYTES = TOTAL + 1024;  // slack for manual 1024-byte alignment
   // bytes credited to a "full" barrier per stage (both CTAs of a pair together)
   static constexpr uint32_t TX_BYTES = CTAS * (A_STAGE_BYTES + B_STAGE_BYTES + SFA_STAGE_BYTES + SFB_STAGE_BYTES);
@@ -388,66 +391,40 @@ __device__ __forceinline__ uint32_t quant_row_block(uint8_t* row_base, int64_t c
 // Column-wise MXFP8: the 32 rows of a scale block are the 32 lanes of the warp.  Lane i
 // returns the E8M0 byte of column i; every lane stores its row's 32 E4M3 bytes.
 //
-// The 32 column maxima come from a halving exchange: in the step of distance d a lane keeps the
-// half of its columns whose bit d matches its own lane bit and trades the other half with lane
-// (lane ^ d), so 16 + 8 + 4 + 2 + 1 shuffles leave lane i with the maximum of column i (a
-// butterfly per column would take 160).  Each lane then derives the scale of its own column
-// once, and 32 broadcasts hand the scales round.
+// One warp reduction per column yields the 32 column maxima (the same value in every lane); lane 0
+// parks them in the warp's 64-float scratch in shared memory (`scratch`, a .shared address), lane i picks up column i, derives that
+// column's scale once and parks it in the second half of the scratch, from where every lane reads all
+// 32 scales as eight broadcast loads.  (A halving exchange by shuffles, 31 shuffles and 62 selects per
+// lane, and 32 more shuffles to hand the scales round, was three times the instructions.)
 __device__ __forceinline__ uint32_t quant_col_block(uint8_t* row_base, int64_t col, bool do_store, const float* v, float norm_const,
-                                                    bool wide, OutFormat fmt) {
+                                                    bool wide, OutFormat fmt, uint32_t scratch) {
   const uint32_t lane = lane_id();
-  float m16[16], m8[8], m4[4], m2[2];
-  {
-    const bool up = lane & 16;
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      const float keep = up ? v[j + 16] : v[j];
-      const float send = up ? v[j] : v[j + 16];
-      m16[j] = fmaxf(fabsf(keep), fabsf(__shfl_xor_sync(0xffffffffu, send, 16)));
-    }
+  for (int j = 0; j < 32; j += 4) {
+    const float4 m = make_float4(warp_absmax_number(v[j]), warp_absmax_number(v[j + 1]), warp_absmax_number(v[j + 2]), warp_absmax_number(v[j + 3]));
+    if (lane == 0) st_shared_f32x4(scratch + 4 * j, m);
   }
-  {
-    const bool up = lane & 8;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const float keep = up ? m16[j + 8] : m16[j];
-      const float send = up ? m16[j] : m16[j + 8];
-      m8[j] = fmaxf(keep, __shfl_xor_sync(0xffffffffu, send, 8));
-    }
-  }
-  {
-    const bool up = lane & 4;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float keep = up ? m8[j + 4] : m8[j];
-      const float send = up ? m8[j] : m8[j + 4];
-      m4[j] = fmaxf(keep, __shfl_xor_sync(0xffffffffu, send, 4));
-    }
-  }
-  {
-    const bool up = lane & 2;
-#pragma unroll
-    for (int j = 0; j < 2; ++j) {
-      const float keep = up ? m4[j + 2] : m4[j];
-      const float send = up ? m4[j] : m4[j + 2];
-      m2[j] = fmaxf(keep, __shfl_xor_sync(0xffffffffu, send, 2));
-    }
-  }
-  const bool up1 = lane & 1;
-  const float cmax = fmaxf(up1 ? m2[1] : m2[0], __shfl_xor_sync(0xffffffffu, up1 ? m2[0] : m2[1], 1));
+  __syncwarp();
+  const float cmax = ld_shared_f32(scratch + 4 * lane);
   // scale of column `lane`
   const float pv = cmax * fmt.rcp_limit * norm_const;
   const uint32_t my_sf = e8m0_from_float(pv);
   const float sfv = e8m0_to_float(my_sf);
   float my_sc = sfv == 0.0f ? 0.0f : norm_const * rcp_approx(sfv);
   my_sc = fminf(my_sc, 3.40282346638528859812e38f);
+  st_shared_f32(scratch + 128 + 4 * lane, my_sc);
+  __syncwarp();
   if (fmt.bits16) {
     float t[32];
 #pragma unroll
-    for (int i = 0; i < 32; i += 2) {
-      const float2 r = mul2(make_float2(v[i], v[i + 1]), make_float2(__shfl_sync(0xffffffffu, my_sc, i), __shfl_sync(0xffffffffu, my_sc, i + 1)));
-      t[i] = r.x;
-      t[i + 1] = r.y;
+    for (int i = 0; i < 32; i += 4) {
+      const float4 sc = ld_shared_f32x4(scratch + 128 + 4 * i);
+      const float2 lo = mul2(make_float2(v[i], v[i + 1]), make_float2(sc.x, sc.y));
+      const float2 hi = mul2(make_float2(v[i + 2], v[i + 3]), make_float2(sc.z, sc.w));
+      t[i] = lo.x;
+      t[i + 1] = lo.y;
+      t[i + 2] = hi.x;
+      t[i + 3] = hi.y;
     }
     if (do_store) store_bf16x32(reinterpret_cast<__nv_bfloat16*>(row_base) + col, t, wide, fmt.f16);
     return my_sf;
@@ -455,8 +432,9 @@ __device__ __forceinline__ uint32_t quant_col_block(uint8_t* row_base, int64_t c
   uint32_t packed[8];
 #pragma unroll
   for (int i = 0; i < 32; i += 4) {
-    const float2 lo = mul2(make_float2(v[i], v[i + 1]), make_float2(__shfl_sync(0xffffffffu, my_sc, i), __shfl_sync(0xffffffffu, my_sc, i + 1)));
-    const float2 hi = mul2(make_float2(v[i + 2], v[i + 3]), make_float2(__shfl_sync(0xffffffffu, my_sc, i + 2), __shfl_sync(0xffffffffu, my_sc, i + 3)));
+    const float4 sc = ld_shared_f32x4(scratch + 128 + 4 * i);
+    const float2 lo = mul2(make_float2(v[i], v[i + 1]), make_float2(sc.x, sc.y));
+    const float2 hi = mul2(make_float2(v[i + 2], v[i + 3]), make_float2(sc.z, sc.w));
     packed[i >> 2] = fp8x4_from_float(lo.x, lo.y, hi.x, hi.y, fmt.e5m2);
   }
   if (do_store)
@@ -952,6 +930,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     const bool c_f16 = p.c_f16 != 0, d_f16 = p.d_f16 != 0;
     const OutFormat out_fmt = {p.d_rcp_limit, p.d_e5m2 != 0, p.d_is_fp8 == 0, d_f16};
     const int64_t d_row_bytes = (int64_t)p.n_out * (p.d_is_fp8 ? 1 : 2);
+    const uint32_t colq_scratch = smem_base + C::COLQ_OFF + ew * 256;
     uint8_t* const stage_row = smem + C::STAGING_OFF + ew * STAGING_WARP_BYTES + lane * STAGING_ROW_BYTES;  // kBulk only
     const uint32_t overlap_target = kPair ? map_to_cta(overlap_bar, 0) : overlap_bar;
     auto arrive_overlap = [&]() {
@@ -1067,7 +1046,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 #pragma unroll
                 for (int j = 0; j < 32; ++j) g[j] = 0.f;
               }
-              const uint32_t sfc = quant_col_block(p.d_col + (int64_t)row * d_row_bytes, dn, row_ok, g, norm_const, wide, out_fmt);
+              const uint32_t sfc = quant_col_block(p.d_col + (int64_t)row * d_row_bytes, dn, row_ok, g, norm_const, wide, out_fmt, colq_scratch);
               int64_t blk_base = 0;
               int rb = (tile.row0 >> 5) + quarter;
               int rest = p.sfd_col_rest_k;
@@ -1252,9 +1231,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
               }
               const bool rows_live = tile.row0 + quarter * 32 < min(p.m_rows, tile.row_end);
               uint8_t* d_col_base = p.d_col + (int64_t)row * d_row_bytes;
-              const uint32_t sfc1 = quant_col_block(d_col_base, on, row_ok, d1, norm_const, wide, out_fmt);
+              const uint32_t sfc1 = quant_col_block(d_col_base, on, row_ok, d1, norm_const, wide, out_fmt, colq_scratch);
               if (rows_live) p.sfd_col[blk_base + sf_offset(on + lane, rb, rest)] = (uint8_t)sfc1;
-              const uint32_t sfc2 = quant_col_block(d_col_base, on + 32, row_ok, v, norm_const, wide, out_fmt);
+              const uint32_t sfc2 = quant_col_block(d_col_base, on + 32, row_ok, v, norm_const, wide, out_fmt, colq_scratch);
               if (rows_live) p.sfd_col[blk_base + sf_offset(on + 32 + lane, rb, rest)] = (uint8_t)sfc2;
             }
           }
@@ -1330,7 +1309,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 #pragma unroll
                 for (int j = 0; j < 32; ++j) v[j] = 0.f;
               }
-              const uint32_t sfc = quant_col_block(p.d_col + (int64_t)row * d_row_bytes, dn, row_ok, v, norm_const, wide, out_fmt);
+              const uint32_t sfc = quant_col_block(p.d_col + (int64_t)row * d_row_bytes, dn, row_ok, v, norm_const, wide, out_fmt, colq_scratch);
               int64_t blk_base = 0;
               int rb = (tile.row0 >> 5) + quarter;
               int rest = p.sfd_col_rest_k;
