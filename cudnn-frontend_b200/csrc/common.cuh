@@ -139,18 +139,50 @@ __device__ __forceinline__ uint32_t mbar_try_wait_scoped(uint32_t bar, uint32_t 
   }
 }
 
+// The same test with a suspend-time hint: the thread may sleep up to `hint_ns` for the phase to complete
+// instead of returning at once, so a long wait costs a few instructions instead of a busy loop.
+template <bool kCluster = false>
+__device__ __forceinline__ uint32_t mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t done;
+  if constexpr (!kCluster) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity), "r"(hint_ns)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity), "r"(hint_ns)
+        : "memory");
+  }
+  return done;
+}
+
+constexpr uint32_t kWaitHintNs = 20000;
+
 template <bool kCluster = false>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx& w, int code) {
+  if (mbar_try_wait_scoped<kCluster>(bar, parity)) return true;
 #pragma unroll 1
-  for (int i = 0; i < 128; ++i) {
-    if (mbar_try_wait_scoped<kCluster>(bar, parity)) return true;
+  for (int i = 0; i < 64; ++i) {
+    if (mbar_try_wait_hint<kCluster>(bar, parity, kWaitHintNs)) return true;
   }
   const uint64_t t0 = global_timer_ns();
 #pragma unroll 1
   while (true) {
 #pragma unroll 1
-    for (int i = 0; i < 256; ++i) {
-      if (mbar_try_wait_scoped<kCluster>(bar, parity)) return true;
+    for (int i = 0; i < 64; ++i) {
+      if (mbar_try_wait_hint<kCluster>(bar, parity, kWaitHintNs)) return true;
     }
     if (*w.abort_flag) return false;
     if (global_timer_ns() - t0 > w.limit_ns) {
@@ -259,6 +291,8 @@ __device__ __forceinline__ void tensormap_fence_acquire(const void* tmap) {
   asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;" ::"l"(tmap) : "memory");
 }
 
+// request the 128-byte line at `ptr` into L2
+__device__ __forceinline__ void prefetch_l2(const void* ptr) { asm volatile("prefetch.global.L2 [%0];" ::"l"(ptr)); }
 __device__ __forceinline__ void prefetch_tensormap(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }

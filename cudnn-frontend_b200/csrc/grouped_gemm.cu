@@ -961,6 +961,18 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       float thread_amax = 0.f;
       uint32_t sf_row_word = 0;  // four E8M0 bytes of this row (K group = 128 output columns)
 
+      if constexpr (kEpi == EPI_DSWIGLU) {
+        // this row's part of the forward C that the tile reads (512 bytes when 16-bit) is requested into L2
+        // before the wait for the accumulator: the loads of the four blocks below then find it there
+        if (row_ok) {
+          const int c_bytes = (p.c_in_dtype == B200MOE_DTYPE_E4M3 || p.c_in_dtype == B200MOE_DTYPE_E5M2) ? 1 : 2;
+          const int g0 = n0 + half * 128;  // first column of G of this warp
+          const uint8_t* c0 = reinterpret_cast<const uint8_t*>(p.c_in) + ((int64_t)row * p.n_out + 2 * g0) * c_bytes;
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            if (q < 2 * c_bytes && g0 + q * (64 / c_bytes) < p.n) prefetch_l2(c0 + 128 * q);
+        }
+      }
       if (!mbar_wait(acc_full_bar(it & 1), (it >> 1) & 1, wc, ST_EPI_ACC)) { ok = false; break; }
       tc_fence_after();
 
