@@ -1005,9 +1005,14 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
               load_bias8(p.bias, p.bias_dtype, b0 + j, bg);
               load_bias8(p.bias, p.bias_dtype, b0 + 32 + j, bu);
 #pragma unroll
-              for (int q = 0; q < 8; ++q) {
-                g[j + q] = fmaf(g[j + q], alpha, bg[q]);
-                u[j + q] = fmaf(u[j + q], alpha, bu[q]);
+              for (int q = 0; q < 8; q += 2) {
+                const float2 a2 = make_float2(alpha, alpha);
+                const float2 rg = fma2(make_float2(g[j + q], g[j + q + 1]), a2, make_float2(bg[q], bg[q + 1]));
+                const float2 ru = fma2(make_float2(u[j + q], u[j + q + 1]), a2, make_float2(bu[q], bu[q + 1]));
+                g[j + q] = rg.x;
+                g[j + q + 1] = rg.y;
+                u[j + q] = ru.x;
+                u[j + q + 1] = ru.y;
               }
             }
           } else {
@@ -1022,12 +1027,15 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             // GeGLU of the reference: gate <= 7, -7 <= up <= 7 (after the C store),
             // D = (up + 1) * gate * sigmoid(1.702 gate) * prob
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const float gate = fminf(g[j], 7.0f);
-              const float up = fmaxf(fminf(u[j], 7.0f), -7.0f);
-              const float e = ex2_approx((gate * 1.702f) * -1.4426950408889634f);
-              const float s = rcp_approx(1.0f + e);
-              g[j] = ((s * gate) * (1.0f + up)) * prob;
+            for (int j = 0; j < 32; j += 2) {
+              const float2 gate = make_float2(fminf(g[j], 7.0f), fminf(g[j + 1], 7.0f));
+              const float2 up = make_float2(fmaxf(fminf(u[j], 7.0f), -7.0f), fmaxf(fminf(u[j + 1], 7.0f), -7.0f));
+              const float2 t = mul2(mul2(gate, 1.702f), -1.4426950408889634f);
+              const float2 den = add2(make_float2(ex2_approx(t.x), ex2_approx(t.y)), 1.0f);
+              const float2 s = make_float2(rcp_approx(den.x), rcp_approx(den.y));
+              const float2 r = mul2(mul2(mul2(s, gate), add2(up, 1.0f)), prob);
+              g[j] = r.x;
+              g[j + 1] = r.y;
             }
           } else {
 #pragma unroll
@@ -1285,7 +1293,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
               float bv[8];
               load_bias8(p.bias, p.bias_dtype, b0 + j, bv);
 #pragma unroll
-              for (int q = 0; q < 8; ++q) v[j + q] = fmaf(v[j + q], alpha, prob * bv[q]);
+              for (int q = 0; q < 8; q += 2) {
+                const float2 r = fma2(make_float2(v[j + q], v[j + q + 1]), make_float2(alpha, alpha), mul2(make_float2(bv[q], bv[q + 1]), prob));
+                v[j + q] = r.x;
+                v[j + q + 1] = r.y;
+              }
             }
           } else {
             scale_inplace<32>(v, alpha);
