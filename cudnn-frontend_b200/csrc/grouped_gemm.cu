@@ -847,16 +847,18 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       bool ok = true;
       for (int t = next_tile(0); t >= 0 && ok; t = next_tile(++it)) {
         const uint32_t acc = tmem_base + ((it & 1) ? TMEM_ACC1_COL : 0);
-        if (it > 0) {
-          // previous tile's epilogue has drained the 32 columns both accumulators share
-          if (!__all_sync(0xffffffffu, mbar_wait(overlap_bar, (it - 1) & 1, wc, ST_MMA_OVERLAP))) { ok = false; break; }
-          tc_fence_after();
-        }
+        // (wgrad: the tile's K range is read from the offsets before the wait below, not between the previous
+        // tile's last MMA and this tile's first)
         int k_tiles = p.k_tiles, k_bytes = p.k_bytes;
         if constexpr (kEpi == EPI_WGRAD) {
           const Tile tile = decode(t);
           k_tiles = tile.k_tiles;
           k_bytes = tile.kbytes;
+        }
+        if (it > 0) {
+          // previous tile's epilogue has drained the 32 columns both accumulators share
+          if (!__all_sync(0xffffffffu, mbar_wait(overlap_bar, (it - 1) & 1, wc, ST_MMA_OVERLAP))) { ok = false; break; }
+          tc_fence_after();
         }
         for (int kt = 0; kt < k_tiles; ++kt) {
           // the stage's bytes were written by TMA (async proxy) and are made visible by the barrier's
