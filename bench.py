@@ -920,6 +920,8 @@ def main():
         return
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if world > 1 or args.gpus > 1:
+        # stdout carries the one JSON line: NCCL's own messages (its version banner when NCCL_DEBUG is set) go to stderr
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         import ep_bench
 
         args.peaks = load_peaks()
