@@ -170,9 +170,10 @@ __device__ __forceinline__ uint32_t mbar_try_wait_hint(uint32_t bar, uint32_t pa
 
 constexpr uint32_t kWaitHintNs = 20000;
 
-template <bool kCluster = false>
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx& w, int code) {
-  if (mbar_try_wait_scoped<kCluster>(bar, parity)) return true;
+// The part of a wait that runs when the phase has not completed yet: kept out of line, so that a wait costs its
+// caller a test and a branch and the loops of the producer, issuer and epilogue warps stay short.
+template <bool kCluster>
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, uint64_t limit_ns, int code) {
 #pragma unroll 1
   for (int i = 0; i < 64; ++i) {
     if (mbar_try_wait_hint<kCluster>(bar, parity, kWaitHintNs)) return true;
@@ -184,13 +185,19 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
     for (int i = 0; i < 64; ++i) {
       if (mbar_try_wait_hint<kCluster>(bar, parity, kWaitHintNs)) return true;
     }
-    if (*w.abort_flag) return false;
-    if (global_timer_ns() - t0 > w.limit_ns) {
+    if (*abort_flag) return false;
+    if (global_timer_ns() - t0 > limit_ns) {
       atomicCAS(&g_device_status, 0, code);
-      *w.abort_flag = 1;
+      *abort_flag = 1;
       return false;
     }
   }
+}
+
+template <bool kCluster = false>
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx& w, int code) {
+  if (mbar_try_wait_scoped<kCluster>(bar, parity)) return true;
+  return mbar_wait_slow<kCluster>(bar, parity, w.abort_flag, w.limit_ns, code);
 }
 
 // ---------------------------------------------------------------------------------------

@@ -938,10 +938,35 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     auto arrive_overlap = [&]() {
       if (kPair) mbar_arrive_cluster(overlap_target); else mbar_arrive(overlap_bar);
     };
+    // amax: a warp keeps the running maximum of the expert it is working on and sends it (one atomic per warp) when
+    // the expert changes and after its last tile: max is associative, so the result is the same as with one atomic
+    // per warp and tile on the few amax words
+    int amax_expert = -1;
+    float run_amax = 0.f, run_amax_up = 0.f;
+    auto flush_amax = [&]() {
+      if (p.amax == nullptr || amax_expert < 0) return;
+      float wmax = run_amax, wmax_up = run_amax_up;
+#pragma unroll
+      for (int d = 16; d > 0; d >>= 1) {
+        wmax = fmaxf(wmax, __shfl_xor_sync(0xffffffffu, wmax, d));
+        if (kEpi == EPI_DSWIGLU) wmax_up = fmaxf(wmax_up, __shfl_xor_sync(0xffffffffu, wmax_up, d));
+      }
+      // non-negative floats order like their bit patterns; -inf (the caller's initial value) has a negative
+      // pattern, so a signed integer max is exact.  dSwiGLU: amax[expert][0] = d_gate, amax[expert][1] = d_up
+      if (lane == 0) {
+        atomicMax(reinterpret_cast<int*>(p.amax) + (kEpi == EPI_DSWIGLU ? 2 * amax_expert : amax_expert), __float_as_int(wmax));
+        if (kEpi == EPI_DSWIGLU) atomicMax(reinterpret_cast<int*>(p.amax) + 2 * amax_expert + 1, __float_as_int(wmax_up));
+      }
+    };
     int it = 0;
     bool ok = true;
     for (int t = next_tile(0); t >= 0 && ok; t = next_tile(++it)) {
       Tile tile = decode(t);
+      if (tile.expert != amax_expert) {
+        flush_amax();
+        amax_expert = tile.expert;
+        run_amax = run_amax_up = 0.f;
+      }
       tile.row0 += (int)cta_rank * BM;  // this CTA's 128 rows
       const int n0 = tile.n_tile * BN;
       const int row = tile.row0 + r_in_tile;
@@ -1261,13 +1286,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           }
         }
         if (p.dprob && row_ok) atomicAdd(p.dprob + row, dprob_sum);
-        if (p.amax) {
-          // amax[expert][0] = d_gate, amax[expert][1] = d_up; d_gate goes through the common reduction below
-          float wmax = amax_up;
-#pragma unroll
-          for (int d = 16; d > 0; d >>= 1) wmax = fmaxf(wmax, __shfl_xor_sync(0xffffffffu, wmax, d));
-          if (lane == 0) atomicMax(reinterpret_cast<int*>(p.amax) + 2 * tile.expert + 1, __float_as_int(wmax));
-        }
+        run_amax_up = fmaxf(run_amax_up, amax_up);
       } else {
         // FC2: 4 blocks of 32 columns per half
         if constexpr (kBulk) bulk_wait_read0();  // the previous tile's row copies have left the staging area
@@ -1372,15 +1391,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         }
       }
 
-      if (p.amax) {
-        float wmax = thread_amax;
-#pragma unroll
-        for (int d = 16; d > 0; d >>= 1) wmax = fmaxf(wmax, __shfl_xor_sync(0xffffffffu, wmax, d));
-        // non-negative floats order like their bit patterns; -inf (the caller's initial
-        // value) has a negative pattern, so a signed integer max is exact
-        if (lane == 0) atomicMax(reinterpret_cast<int*>(p.amax) + (kEpi == EPI_DSWIGLU ? 2 * tile.expert : tile.expert), __float_as_int(wmax));
-      }
+      run_amax = fmaxf(run_amax, thread_amax);
     }
+    flush_amax();
   }
 
   // ---- teardown ----------------------------------------------------------------------
