@@ -854,17 +854,18 @@ def bench_fp4(dev, stream):
     return out
 
 
-def bench_backward(dev, stream):
+def bench_backward(dev, stream, small=False):
     """The backward pair on the Mixtral shape (E=8, hidden 4096, intermediate 14336, 32768 routed rows): dSwiGLU
     (gradient GEMM with K = hidden, N = intermediate, fused activation backward, E4M3 D_row / D_col with scales) and
-    the weight gradient of FC1 (m = hidden, n = 2 x intermediate, the experts split the 32768 tokens), bf16 output."""
+    the weight gradient of FC1 (m = hidden, n = 2 x intermediate, the experts split the 32768 tokens), bf16 output.
+    small: a quarter of the intermediate size and of the rows, for profiler captures."""
     import torch
 
     import cudnn_frontend_b200 as cf
     from cudnn_frontend_b200 import ops, synthetic
 
     out = {}
-    cfg = dict(experts=8, k=4096, n=14336, tokens=16384, topk=2, routing="uniform")
+    cfg = dict(experts=8, k=4096, n=3584 if small else 14336, tokens=4096 if small else 16384, topk=2, routing="uniform")
     p = synthetic.make_problem(cfg, dev, seed=4, m_aligned=128)
     e, n, k, m = cfg["experts"], cfg["n"], cfg["k"], p["m_rows"]
     g = torch.Generator(device=dev).manual_seed(8)
@@ -881,11 +882,11 @@ def bench_backward(dev, stream):
     t = time_trials(lambda: op.execute(p["a"], p["b"], c_fwd, d_row, d_col, p["sfa"], p["sfb"], p["padded_offsets"], p["alpha"], beta, p["prob"], dprob,
                                        sfd_row_tensor=sfd_row, sfd_col_tensor=sfd_col, norm_const_tensor=norm), stream)  # fmt: skip
     out["dswiglu_mixtral"] = {"tflops": p["flops"] / (t["median_ms"] * 1e-3) / 1e12, "timing": t,
-                              "outputs": "E4M3 D_row and D_col [32768+pad, 28672] with row and column scales, dprob"}  # fmt: skip
+                              "outputs": f"E4M3 D_row and D_col [{m}, {2 * n}] with row and column scales, dprob"}  # fmt: skip
     del p, c_fwd, d_row, d_col, sfd_row, sfd_col, op
     torch.cuda.empty_cache()
 
-    m_w, n_w, tokens = 4096, 28672, 32768
+    m_w, n_w, tokens = 4096, (7168 if small else 28672), 32768
     a = torch.empty((m_w, tokens), device=dev).uniform_(-2, 2, generator=g).to(torch.float8_e4m3fn)
     b = torch.empty((n_w, tokens), device=dev).uniform_(-2, 2, generator=g).to(torch.float8_e4m3fn).t()
     cols = tokens // 32
@@ -898,7 +899,7 @@ def bench_backward(dev, stream):
     opw.compile()
     tw = time_trials(lambda: opw.execute(a, b, sfa, sfb, offs, wgrad_tensor=w), stream)
     flops_w = 2.0 * tokens * m_w * n_w
-    out["wgrad_mixtral_fc1"] = {"tflops": flops_w / (tw["median_ms"] * 1e-3) / 1e12, "timing": tw, "outputs": "bf16 [8, 4096, 28672]"}
+    out["wgrad_mixtral_fc1"] = {"tflops": flops_w / (tw["median_ms"] * 1e-3) / 1e12, "timing": tw, "outputs": f"bf16 [8, {m_w}, {n_w}]"}
     return out
 
 
@@ -913,12 +914,19 @@ def main():
                     help="c2 = Mixtral-shape FC1 (the benchmark); small / deepseek-small = reduced cases for profiler captures")  # fmt: skip
     ap.add_argument("--outputs", default="d", choices=["d", "full"], help="with --kernel-only: d = bf16 D + amax (the benchmark); full = C + E4M3 D + D_col + scale factors")
     ap.add_argument("--kernel-only", action="store_true", help="time the FC1 kernel only (no end-to-end, CPU baseline or side measurements)")
+    ap.add_argument("--backward-only", action="store_true", help="time the dSwiGLU and weight-gradient kernels only (--workload small: reduced sizes for profiler captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "own" else args.warmup
     if args.impl == "reference":
         run_reference(args)
         return
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.backward_only:
+        import torch
+
+        torch.cuda.set_device(0)
+        print(json.dumps(bench_backward(torch.device("cuda", 0), torch.cuda.current_stream(), small=args.workload == "small")))
+        return
     if world > 1 or args.gpus > 1:
         # stdout carries the one JSON line: NCCL's own messages (its version banner when NCCL_DEBUG is set) go to stderr
         os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
