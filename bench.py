@@ -928,8 +928,6 @@ def main():
         print(json.dumps(bench_backward(torch.device("cuda", 0), torch.cuda.current_stream(), small=args.workload == "small")))
         return
     if world > 1 or args.gpus > 1:
-        # stdout carries the one JSON line: NCCL's own messages (its version banner when NCCL_DEBUG is set) go to stderr
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         import ep_bench
 
         args.peaks = load_peaks()
