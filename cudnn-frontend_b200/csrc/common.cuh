@@ -107,21 +107,6 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
   return done;
 }
 
-// Non-blocking test of a barrier phase (never suspends the thread)
-__device__ __forceinline__ uint32_t mbar_test_wait(uint32_t bar, uint32_t parity) {
-  uint32_t done;
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t"
-      "}"
-      : "=r"(done)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return done;
-}
-
 // Bounded wait.  Spins on the barrier phase; after `limit_ns` without progress it records
 // `code` in the device status word, raises the CTA's abort flag and returns false so the
 // caller can leave its loop and fall through to the kernel's teardown.  A raised abort flag

@@ -860,25 +860,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           if (!__all_sync(0xffffffffu, mbar_wait(overlap_bar, (it - 1) & 1, wc, ST_MMA_OVERLAP))) { ok = false; break; }
           tc_fence_after();
         }
-        // Single-CTA tiles: a k-tile's four MMAs take about 270 cycles, less than one trip of this loop, so the loop
-        // itself sets the pace of compute-bound tiles.  There the next stage's barrier is tested (without blocking,
-        // voted warp-uniform) before this k-tile's instructions are issued, and its latency passes behind them.  CTA
-        // pairs (540 cycles per k-tile) keep the plain wait: the loop outruns the MMAs and is best left short.
-        bool peeked = !kPair && k_tiles > 0 && __all_sync(0xffffffffu, mbar_test_wait(full_bar(stage), phase));
         for (int kt = 0; kt < k_tiles; ++kt) {
           // the stage's bytes were written by TMA (async proxy) and are made visible by the barrier's
           // transaction count; no tcgen05 fence is needed between this wait and the MMAs
           // (the outcome is voted so that a wait that gives up takes the whole warp out of the loop)
-          if constexpr (kPair) {
-            bool landed = mbar_try_wait(full_bar(stage), phase);
-            if (!landed) landed = mbar_wait(full_bar(stage), phase, wc, ST_MMA_FULL);
-            if (!__all_sync(0xffffffffu, landed)) { ok = false; break; }
-          } else {
-            if (!peeked && !__all_sync(0xffffffffu, mbar_wait(full_bar(stage), phase, wc, ST_MMA_FULL))) { ok = false; break; }
-            const int next_stage = stage + 1 == STAGES ? 0 : stage + 1;
-            const uint32_t next_phase = stage + 1 == STAGES ? phase ^ 1u : phase;
-            peeked = kt + 1 < k_tiles && __all_sync(0xffffffffu, mbar_test_wait(full_bar(next_stage), next_phase));
-          }
+          bool landed = mbar_try_wait(full_bar(stage), phase);
+          if (!landed) landed = mbar_wait(full_bar(stage), phase, wc, ST_MMA_FULL);
+          if (!__all_sync(0xffffffffu, landed)) { ok = false; break; }
           // scale chunks: 8-bit operands alternate between two TMEM buffers; E2M1 operands have one
           // (tcgen05.cp and tcgen05.mma of one thread execute in issue order)
           const uint32_t sfa_t = tmem_base + TMEM_SF_COL + (kFmt ? 0 : 16 * sf_buf);
