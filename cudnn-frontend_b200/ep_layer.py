@@ -591,7 +591,17 @@ class ExpertParallelMoE:
         bufs, cap, slots = peer["bufs"], peer["cap"], peer["slots"]
         main = torch.cuda.current_stream()
         streams = self._side_streams()
+        # step breakdown: when ``self.step_events`` is a list, a timing event is recorded on the caller's
+        # stream at every phase boundary and appended as (label, event)
+        rec = getattr(self, "step_events", None)
 
+        def mark(label):
+            if rec is not None:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record(main)
+                rec.append((label, ev))
+
+        mark("start")
         ids = self._physical_ids(topk_ids).contiguous()
         counts, _, local_row = moe.route(ids.view(-1), self.num_experts, 1)
         bufs["rec"].local.fill_(0xFF)  # a record nobody writes reads as "padding row"
@@ -616,6 +626,7 @@ class ExpertParallelMoE:
             self._rank_barrier()
         ev_plan = torch.cuda.Event()
         ev_plan.record(main)
+        mark("route + plan (one host synchronisation)")
 
         # chunks = row ranges of about equal size on every rank: a table on the device for the dispatch
         # kernel (it covers every rank), the same numbers on the host for this rank's launches and copies,
@@ -653,11 +664,13 @@ class ExpertParallelMoE:
 
         dispatch(0, 0)
         self._rank_barrier()
+        mark("dispatch of chunk 0 + barrier")
         ev_disp = [None] * chunks
         ev_fc2 = [None] * chunks
         for c in range(chunks):
             if c > 0:
                 main.wait_event(ev_disp[c])
+                mark(f"wait for the dispatch of chunk {c}")
             r0, r1 = row_bounds[c], row_bounds[c + 1]
             offs = offs_c[c, 1:]  # the element before this view is the chunk's first row
             if r1 > r0:
@@ -665,6 +678,7 @@ class ExpertParallelMoE:
                                             loc["map"][r0:])  # fmt: skip
                 fc1.execute(a, self.w1, None, h8, sfa, self.sfw1, offs, self.alpha, sfd_row_tensor=sfh, norm_const_tensor=self.norm,
                             offsets_have_prev=True)  # fmt: skip
+            mark(f"unpack + FC1 of chunk {c}")
             if c + 1 < chunks:
                 # the next chunk's rows travel while this chunk computes
                 with torch.cuda.stream(streams["disp"]):
@@ -678,6 +692,7 @@ class ExpertParallelMoE:
                 fc2.execute(h8, sfh, offs, self.alpha, y, b_tensor=self.w2, sfb_tensor=self.sfw2, prob_tensor=prob3, offsets_have_prev=True)
             ev_fc2[c] = torch.cuda.Event()
             ev_fc2[c].record(main)
+            mark(f"FC2 of chunk {c}")
             # return of this chunk's result rows: one copy per (expert, source rank) block inside the chunk,
             # destinations rotated so that the ranks do not all send to the same one at the same time
             if y is not None and r1 > r0:
@@ -693,7 +708,10 @@ class ExpertParallelMoE:
             main.wait_stream(cs)
         main.wait_stream(streams["disp"])
         self._rank_barrier()  # every rank's copies into my result buffer are complete
-        return moe.combine_rows(bufs["back"].view(torch.bfloat16, (slots, h)), local_row, t, k)
+        mark("last result copies + barrier")
+        out = moe.combine_rows(bufs["back"].view(torch.bfloat16, (slots, h)), local_row, t, k)
+        mark("top-k sum")
+        return out
 
     def forward_pipelined(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_prob: torch.Tensor, micro_batches: int = 4) -> torch.Tensor:
         """Same result as :meth:`forward`, computed as ``micro_batches`` slices of the tokens in a

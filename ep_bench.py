@@ -178,6 +178,21 @@ def run(args, tokens_per_gpu: int = 65536):
 
     head = measure(with_clocks=True)
     ms = head["ms"]
+    breakdown_path = os.environ.get("B200MOE_EP_BREAKDOWN")
+    if breakdown_path and world > 1 and path == "peer":
+        # one extra step with a timing event at every phase boundary of the chunked peer path (caller's stream):
+        # every rank writes its own list, "<path>.rank<r>"
+        layer.step_events = []
+        dist.barrier()
+        torch.cuda.synchronize()
+        run_layer(x, ids, prob)
+        torch.cuda.synchronize()
+        evs = layer.step_events
+        layer.step_events = None
+        rows = [{"phase": evs[i][0], "ms": evs[i - 1][1].elapsed_time(evs[i][1])} for i in range(1, len(evs))]
+        total = evs[0][1].elapsed_time(evs[-1][1])
+        with open(f"{breakdown_path}.rank{rank}", "w") as f:
+            json.dump({"rank": rank, "world": world, "rows_received": int(layer.last_rows_received), "total_ms": total, "phases": rows}, f, indent=1)
     value = flops / (ms * 1e-3) / 1e12
     if world > 1 and path == "peer" and not getattr(args, "no_extras", False):
         r = measure("peer-direct")
