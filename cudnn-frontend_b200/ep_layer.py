@@ -462,18 +462,25 @@ class ExpertParallelMoE:
         if self.world > 1:
             dist.all_reduce(self._token, group=self.group)
 
+    def default_chunks(self) -> int:
+        """Chunks :meth:`forward_fused` uses when none are given (0 = the direct form)."""
+        import os
+
+        if self.world <= 1:
+            return 0
+        return int(os.environ.get("B200MOE_EP_CHUNKS", "0" if self.world <= 2 else "8"))
+
     def forward_fused(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_prob: torch.Tensor, capacity_factor: float = 2.0,
                       chunks: Optional[int] = None) -> torch.Tensor:
         """The peer-memory path.  On one rank: :meth:`forward_fused_direct`.  On several ranks:
         :meth:`forward_fused_chunked`, which overlaps the NVLink traffic with the GEMMs (``chunks``
-        expert chunks, default 5 on two ranks and 8 on more (measured on 4 GPUs: 29.5 / 30.2 / 28.9 / 31.0 ms
-        per step with 3 / 5 / 8 / 12 chunks), or the environment variable ``B200MOE_EP_CHUNKS``; ``chunks=0``
-        selects the direct form on any number of ranks)."""
-        import os
-
+        expert chunks; ``chunks=0`` selects the direct form on any number of ranks).  Default, unless the
+        environment variable ``B200MOE_EP_CHUNKS`` says otherwise: the direct form on two ranks (half of the
+        rows stay local and FC2's peer stores hide behind its MMAs: 26.9 ms against 27.7 ms with 5 chunks), 8
+        chunks on more (4 GPUs: 29.5 / 30.2 / 28.9 / 31.0 ms per step with 3 / 5 / 8 / 12 chunks, 30.4 direct;
+        8 GPUs: 33.0 against 36.7)."""
         if chunks is None:
-            default = 5 if self.world <= 2 else 8
-            chunks = int(os.environ.get("B200MOE_EP_CHUNKS", str(default))) if self.world > 1 else 0
+            chunks = self.default_chunks()
         if chunks <= 0:
             return self.forward_fused_direct(x, topk_ids, topk_prob, capacity_factor)
         return self.forward_fused_chunked(x, topk_ids, topk_prob, capacity_factor, chunks)

@@ -131,6 +131,8 @@ def run(args, tokens_per_gpu: int = 65536):
             return layer.forward_fused(xx, ii, pp)
         if which == "peer-direct":
             return layer.forward_fused(xx, ii, pp, chunks=0)
+        if which == "peer-chunked":
+            return layer.forward_fused(xx, ii, pp, chunks=5)
         return layer.forward_pipelined(xx, ii, pp, micro) if micro > 1 else layer(xx, ii, pp)
 
     stream = torch.cuda.current_stream()
@@ -176,16 +178,19 @@ def run(args, tokens_per_gpu: int = 65536):
         matches = bool(max_over_ranks(0.0 if torch.equal(y, y_nccl) else 1.0) == 0.0)
         del y_nccl
 
+    chunks_used = layer.default_chunks() if path == "peer" else 0
     head = measure(with_clocks=True)
     ms = head["ms"]
     breakdown_path = os.environ.get("B200MOE_EP_BREAKDOWN")
     if breakdown_path and world > 1 and path == "peer":
         # one extra step with a timing event at every phase boundary of the chunked peer path (caller's stream):
         # every rank writes its own list, "<path>.rank<r>"
+        form = None if chunks_used > 0 else "peer-chunked"  # the events sit in the chunked form
+        run_layer(x, ids, prob, form)  # untimed: side streams and operators of this form exist afterwards
         layer.step_events = []
         dist.barrier()
         torch.cuda.synchronize()
-        run_layer(x, ids, prob)
+        run_layer(x, ids, prob, form)
         torch.cuda.synchronize()
         evs = layer.step_events
         layer.step_events = None
@@ -195,9 +200,15 @@ def run(args, tokens_per_gpu: int = 65536):
             json.dump({"rank": rank, "world": world, "rows_received": int(layer.last_rows_received), "total_ms": total, "phases": rows}, f, indent=1)
     value = flops / (ms * 1e-3) / 1e12
     if world > 1 and path == "peer" and not getattr(args, "no_extras", False):
-        r = measure("peer-direct")
-        side["peer_direct_path"] = {"ms_per_step": r["ms"], "tflops": flops / (r["ms"] * 1e-3) / 1e12,
-                                    "what": "one dispatch kernel, result rows stored over NVLink from the FC2 epilogue, no overlap"}  # fmt: skip
+        # the other form of the peer path beside the default one
+        if chunks_used > 0:
+            r = measure("peer-direct")
+            side["peer_direct_path"] = {"ms_per_step": r["ms"], "tflops": flops / (r["ms"] * 1e-3) / 1e12,
+                                        "what": "one dispatch kernel, result rows stored over NVLink from the FC2 epilogue, no overlap"}  # fmt: skip
+        else:
+            r = measure("peer-chunked")
+            side["peer_chunked_path"] = {"ms_per_step": r["ms"], "tflops": flops / (r["ms"] * 1e-3) / 1e12,
+                                         "what": "5 expert chunks, dispatch and result copies beside the GEMMs"}  # fmt: skip
 
     # end to end: tokens, expert ids and gate probabilities start in pinned host memory every step and the
     # layer's output goes back to pinned host memory; the transfers overlap the neighbouring steps (a copy
@@ -276,7 +287,8 @@ def run(args, tokens_per_gpu: int = 65536):
             "config": {
                 "workload": f"expert-parallel MoE layer: E=256 sharded {e_local}/GPU, hidden 7168, intermediate 2048, {tokens_per_gpu} tokens/GPU top-8 Zipf(1.2); one step = quantise + dispatch to the owning ranks, FC1 + SwiGLU, FC2 with gating, return + top-k sum",
                 "parallelism": f"ep{world}",
-                "data_path": {"peer": "peer stores over NVLink from the quantise+dispatch kernel, result rows returned by device-to-device copies; expert chunks, transfers beside the GEMMs",
+                "data_path": {"peer": (f"peer stores over NVLink from the quantise+dispatch kernel, result rows returned by device-to-device copies; {chunks_used} expert chunks, transfers beside the GEMMs"
+                                       if chunks_used > 0 else "peer stores over NVLink from the quantise+dispatch kernel and from the FC2 epilogue (the default on two ranks)"),
                               "peer-direct": "peer stores over NVLink from the quantise+dispatch kernel and from the FC2 epilogue; nothing overlapped",
                               "nccl": f"NCCL all-to-all, {micro} micro-batch(es)"}[path],
                 "l2": "inputs larger than L2 (0.94 GB tokens, 11 GB local weights), no flush",
@@ -287,7 +299,7 @@ def run(args, tokens_per_gpu: int = 65536):
                 "output_matches_nccl_path": matches,
             },
             "timing": {"median_ms": head["median_ms"], "min_ms": head["min_ms"], "steps": steps},
-            "gpu_launches": steps * (7 if path != "nccl" else 5 * micro),
+            "gpu_launches": steps * ((5 + 4 * chunks_used if chunks_used > 0 else 7) if path != "nccl" else 5 * micro),
             "e2e": {"value": flops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": ms_e2e, "steps": e2e_steps, "output_on_host_matches": e2e_same,
                     "note": "bytes are one rank's, the value is the aggregate over ranks; inputs of step i + 1 and the output of step i - 1 travel while step i computes; the region ends when the last output is on the host"},

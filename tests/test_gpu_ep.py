@@ -174,7 +174,7 @@ def _ep_worker(rank, world, port, ret):
         y1 = full(x, ids, prob)
         yp = layer.forward_pipelined(x, ids, prob, micro_batches=3)
         yf = layer.forward_fused(x, ids, prob, chunks=0)  # rows cross NVLink by peer stores, no all-to-all
-        yf2 = layer.forward_fused(x, ids, prob)  # in expert chunks (the default on several ranks)
+        yf2 = layer.forward_fused(x, ids, prob)  # the default form for this number of ranks
         yc2 = layer.forward_fused(x, ids, prob, chunks=2)
         # re-shard by load (weights cross ranks) and run again: same function
         counts = torch.bincount(ids.reshape(-1).long(), minlength=E).float()
