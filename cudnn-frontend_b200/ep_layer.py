@@ -565,22 +565,23 @@ class ExpertParallelMoE:
     def forward_fused_chunked(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_prob: torch.Tensor, capacity_factor: float = 2.0,
                               chunks: int = 4) -> torch.Tensor:
         """Same result as :meth:`forward_fused_direct`, with the local experts run in ``chunks`` slices so
-        that the traffic over NVLink hides behind the GEMMs:
+        that the result rows return over NVLink while later slices still compute:
 
             plan (as forward_fused_direct: histogram all-gather, one host synchronisation)
             chunks = row ranges of this rank's expert-grouped buffer (they cut through large expert groups)
-            dispatch of chunk 0 (all SMs) -> barrier
+            quantise + dispatch of every row over NVLink (one kernel, all SMs) -> barrier
             for every chunk c:   FC1(c), FC2(c) on the compute stream (FC2 stores bf16 rows locally, in
                                  expert-grouped order: full-speed stores, no row map)
-                                 | quantise + dispatch of chunk c + 1 on a side stream, on the few SMs the
-                                 |   GEMMs leave free (``chunk_sm_margin``), then a barrier
                                  | return of chunk c - 1 by the copy engines: every (expert, source rank)
                                  |   block of result rows is one contiguous device-to-device copy into the
                                  |   source rank's result buffer, which holds its rows in its own
                                  |   expert-sorted order
             barrier -> top-k sum (each token gathers its k rows through its sorted positions)
 
-        Only the dispatch of the first chunk and the return of the last one are exposed.  All tables of
+        Only the dispatch and the return of the last chunk are exposed; the copy engines cost the GEMMs
+        nothing.  With ``B200MOE_EP_OVERLAP_DISPATCH=1`` only chunk 0 is dispatched ahead and the dispatch
+        of chunk c + 1 runs on a side stream beside the GEMMs of chunk c, with ``chunk_sm_margin`` SMs left
+        to it and a barrier after it (measured slower: the comment at the switch below).  All tables of
         the copies come from the all-gathered histogram, which the host reads in the plan's one
         synchronisation."""
         import numpy as np
@@ -652,6 +653,16 @@ class ExpertParallelMoE:
             moe.dispatch_quantize_peer(x, ids, local_row, plan.delta, flat_prob, el, g, rank, slots, cap, bufs["q"].ptrs_dev,
                                        bufs["rec"].ptrs_dev, row_bounds=bounds_i32, chunk=c, max_blocks=max_blocks)  # fmt: skip
 
+        # The quantise + dispatch kernel beside a GEMM shares the GEMM's SMs (its small blocks fit next to a GEMM
+        # CTA) and slows FC1 and FC2 by more than it takes alone (one GPU, 5 chunks: FC1 13.4 -> 16.6 ms, FC2
+        # 7.2 -> 9.7 ms for a kernel of 2.3 ms), while the copy engines' result copies cost the GEMMs nothing.  So
+        # by default every row is dispatched before the first chunk and only the return runs beside the GEMMs
+        # (4 GPUs: 27.8 against 29.7 ms per step, 8 GPUs: 30.7 against 34.4 ms);
+        # ``B200MOE_EP_OVERLAP_DISPATCH=1`` selects the chunk-by-chunk dispatch on the side stream instead.
+        import os
+
+        overlap_dispatch = os.environ.get("B200MOE_EP_OVERLAP_DISPATCH", "0") == "1"
+
         row_bytes = h * 2
         back_ptrs = bufs["back"].ptrs
 
@@ -667,15 +678,18 @@ class ExpertParallelMoE:
             h8 = torch.empty((m, self.inter, 1), dtype=torch.float8_e4m3fn, device=dev)
             sfh = ops.empty_sf(m, self.inter, 1, device=dev)
             y = torch.empty((m, h, 1), dtype=torch.bfloat16, device=dev)
-            fc1, fc2 = self._fc_ops(m, (a, sfa, h8, sfh, None, prob3, plan.padded_offsets), self.chunk_sm_margin)
+            fc1, fc2 = self._fc_ops(m, (a, sfa, h8, sfh, None, prob3, plan.padded_offsets), self.chunk_sm_margin if overlap_dispatch else 0)
 
-        dispatch(0, 0)
+        if overlap_dispatch:
+            dispatch(0, 0)
+        else:
+            moe.dispatch_quantize_peer(x, ids, local_row, plan.delta, flat_prob, el, g, rank, slots, cap, bufs["q"].ptrs_dev, bufs["rec"].ptrs_dev)
         self._rank_barrier()
-        mark("dispatch of chunk 0 + barrier")
+        mark("dispatch of chunk 0 + barrier" if overlap_dispatch else "dispatch of all rows + barrier")
         ev_disp = [None] * chunks
         ev_fc2 = [None] * chunks
         for c in range(chunks):
-            if c > 0:
+            if c > 0 and overlap_dispatch:
                 main.wait_event(ev_disp[c])
                 mark(f"wait for the dispatch of chunk {c}")
             r0, r1 = row_bounds[c], row_bounds[c + 1]
@@ -686,7 +700,7 @@ class ExpertParallelMoE:
                 fc1.execute(a, self.w1, None, h8, sfa, self.sfw1, offs, self.alpha, sfd_row_tensor=sfh, norm_const_tensor=self.norm,
                             offsets_have_prev=True)  # fmt: skip
             mark(f"unpack + FC1 of chunk {c}")
-            if c + 1 < chunks:
+            if c + 1 < chunks and overlap_dispatch:
                 # the next chunk's rows travel while this chunk computes
                 with torch.cuda.stream(streams["disp"]):
                     if c == 0:

@@ -208,7 +208,7 @@ def run(args, tokens_per_gpu: int = 65536):
         else:
             r = measure("peer-chunked")
             side["peer_chunked_path"] = {"ms_per_step": r["ms"], "tflops": flops / (r["ms"] * 1e-3) / 1e12,
-                                         "what": "5 expert chunks, dispatch and result copies beside the GEMMs"}  # fmt: skip
+                                         "what": "5 expert chunks, result copies beside the GEMMs"}  # fmt: skip
 
     # end to end: tokens, expert ids and gate probabilities start in pinned host memory every step and the
     # layer's output goes back to pinned host memory; the transfers overlap the neighbouring steps (a copy
@@ -287,7 +287,7 @@ def run(args, tokens_per_gpu: int = 65536):
             "config": {
                 "workload": f"expert-parallel MoE layer: E=256 sharded {e_local}/GPU, hidden 7168, intermediate 2048, {tokens_per_gpu} tokens/GPU top-8 Zipf(1.2); one step = quantise + dispatch to the owning ranks, FC1 + SwiGLU, FC2 with gating, return + top-k sum",
                 "parallelism": f"ep{world}",
-                "data_path": {"peer": (f"peer stores over NVLink from the quantise+dispatch kernel, result rows returned by device-to-device copies; {chunks_used} expert chunks, transfers beside the GEMMs"
+                "data_path": {"peer": (f"peer stores over NVLink from the quantise+dispatch kernel, result rows returned by device-to-device copies beside the GEMMs of {chunks_used} expert chunks"
                                        if chunks_used > 0 else "peer stores over NVLink from the quantise+dispatch kernel and from the FC2 epilogue (the default on two ranks)"),
                               "peer-direct": "peer stores over NVLink from the quantise+dispatch kernel and from the FC2 epilogue; nothing overlapped",
                               "nccl": f"NCCL all-to-all, {micro} micro-batch(es)"}[path],
@@ -299,7 +299,7 @@ def run(args, tokens_per_gpu: int = 65536):
                 "output_matches_nccl_path": matches,
             },
             "timing": {"median_ms": head["median_ms"], "min_ms": head["min_ms"], "steps": steps},
-            "gpu_launches": steps * ((5 + 4 * chunks_used if chunks_used > 0 else 7) if path != "nccl" else 5 * micro),
+            "gpu_launches": steps * ((6 + 3 * chunks_used if chunks_used > 0 else 7) if path != "nccl" else 5 * micro),
             "e2e": {"value": flops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": ms_e2e, "steps": e2e_steps, "output_on_host_matches": e2e_same,
                     "note": "bytes are one rank's, the value is the aggregate over ranks; inputs of step i + 1 and the output of step i - 1 travel while step i computes; the region ends when the last output is on the host"},

@@ -74,14 +74,16 @@ def test_peer_memory_layer_equals_the_plain_layer():
     layer.release_peer_buffers()
 
 
+@pytest.mark.parametrize("overlap_dispatch", ["0", "1"])
 @pytest.mark.parametrize("chunks", [1, 3, 8])
-def test_chunked_peer_path_equals_the_plain_layer(chunks):
-    """The chunked form of the peer path (experts in slices, dispatch of the next slice on a side stream,
-    result rows returned by device-to-device copies in the sources' sorted order) on one rank: the same
-    bytes as the plain layer, step after step."""
+def test_chunked_peer_path_equals_the_plain_layer(chunks, overlap_dispatch, monkeypatch):
+    """The chunked form of the peer path (experts in slices, result rows returned by device-to-device copies
+    in the sources' sorted order; every row dispatched ahead of the first slice, or the next slice's rows
+    dispatched on a side stream) on one rank: the same bytes as the plain layer, step after step."""
     from cudnn_frontend_b200 import ops
     from cudnn_frontend_b200.ep_layer import ExpertParallelMoE
 
+    monkeypatch.setenv("B200MOE_EP_OVERLAP_DISPATCH", overlap_dispatch)
     x, ids, prob, w1, sfw1, w2, sfw2 = _inputs(7, "cuda")
     layer = ExpertParallelMoE(w1, sfw1, w2, sfw2, E)
     y = layer(x, ids, prob)
@@ -176,6 +178,9 @@ def _ep_worker(rank, world, port, ret):
         yf = layer.forward_fused(x, ids, prob, chunks=0)  # rows cross NVLink by peer stores, no all-to-all
         yf2 = layer.forward_fused(x, ids, prob)  # the default form for this number of ranks
         yc2 = layer.forward_fused(x, ids, prob, chunks=2)
+        os.environ["B200MOE_EP_OVERLAP_DISPATCH"] = "1"  # the next slice's rows dispatched beside the GEMMs
+        yc3 = layer.forward_fused(x, ids, prob, chunks=3)
+        os.environ["B200MOE_EP_OVERLAP_DISPATCH"] = "0"
         # re-shard by load (weights cross ranks) and run again: same function
         counts = torch.bincount(ids.reshape(-1).long(), minlength=E).float()
         dist.all_reduce(counts)
@@ -189,7 +194,7 @@ def _ep_worker(rank, world, port, ret):
         status = _ops.device_status(clear=True)
         layer.release_peer_buffers()
         # row order inside an expert group differs between the runs, the per-row maths does not
-        ret[rank] = bool(torch.equal(y, y1)) and bool(torch.equal(yp, y1)) and bool(torch.equal(yf, y1)) and bool(torch.equal(yf2, y1)) and bool(torch.equal(yc2, y1)) and bool(torch.equal(yr, y1)) and bool(torch.equal(yr2, y1)) and status == 0
+        ret[rank] = bool(torch.equal(y, y1)) and bool(torch.equal(yp, y1)) and bool(torch.equal(yf, y1)) and bool(torch.equal(yf2, y1)) and bool(torch.equal(yc2, y1)) and bool(torch.equal(yc3, y1)) and bool(torch.equal(yr, y1)) and bool(torch.equal(yr2, y1)) and status == 0
     finally:
         dist.destroy_process_group()
 
