@@ -378,3 +378,19 @@ def test_chunk_offsets_restrict_every_expert_group_to_the_chunk():
                         assert lo >= starts_full[j_] and hi <= int(ends[r, j_])  # rows of group j only
                         covered[lo:hi] += 1
             assert (covered == 1).all()
+
+
+def test_default_form_of_the_peer_path_by_world_size(monkeypatch):
+    """One rank and two ranks take the direct form (no chunks), more ranks take eight chunks; the environment
+    variable overrides the choice on several ranks and never on one."""
+    from types import SimpleNamespace
+
+    from cudnn_frontend_b200.ep_layer import ExpertParallelMoE
+
+    monkeypatch.delenv("B200MOE_EP_CHUNKS", raising=False)
+    picks = {w: ExpertParallelMoE.default_chunks(SimpleNamespace(world=w)) for w in (1, 2, 4, 8)}
+    assert picks == {1: 0, 2: 0, 4: 8, 8: 8}
+    monkeypatch.setenv("B200MOE_EP_CHUNKS", "3")
+    assert ExpertParallelMoE.default_chunks(SimpleNamespace(world=2)) == 3
+    assert ExpertParallelMoE.default_chunks(SimpleNamespace(world=8)) == 3
+    assert ExpertParallelMoE.default_chunks(SimpleNamespace(world=1)) == 0
