@@ -19,9 +19,10 @@ amax (FP4 operands), as in the reference.
 with one weight allocation per expert behind ``b_ptrs`` / ``sfb_ptrs``, K- or N-major (``b_major``), optionally with the
 dynamic tile scheduler.
 
-Differences a caller can observe: groups may be padded to any multiple of 128 rows; ``epilogue_op`` other than the
-identity, ``act_func`` other than ``"dswiglu"``, a float32 ``C`` and the dbias output are not built
-(``NotImplementedError``).
+Differences a caller can observe: groups may be padded to any multiple of 128 rows; ``act_func`` other than
+``"dswiglu"``, a float32 ``C`` and the dbias output are not built (``NotImplementedError``).  ``epilogue_op``
+(``"relu"``, ``"srelu"``) is validated and then has no effect, exactly as in the reference: its kernel takes the
+lambda as a parameter and never applies it (grouped_gemm_dswiglu_quant.py:543, :1533).
 """
 
 from __future__ import annotations
@@ -203,7 +204,6 @@ class GroupedGemmDswigluSm100(OperatorBase):
 
         # what this build implements of the reference's surface
         self._not_implemented_error_if(self.ab_dtype == torch.uint8, "uint8 (raw packed FP4) operands are not built: pass float4_e2m1fn_x2 tensors")
-        self._not_implemented_error_if(self.epilogue_op not in (None, "none", "identity"), f"epilogue_op {self.epilogue_op!r} is not built (the identity is)")
         self._not_implemented_error_if(self.c_dtype == torch.float32, "a float32 C is not built (bf16, fp16, E4M3 and E5M2 are)")
         self._not_implemented_error_if(fp4 and k % 64 != 0, f"FP4 operands need k to be a multiple of 64, got {k}")
         self._not_implemented_error_if(fp4 and self.generate_sfd, "scale-factor generation is built for fp8 operands only")
