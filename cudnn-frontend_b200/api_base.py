@@ -97,6 +97,20 @@ _FP8 = (torch.float8_e4m3fn, torch.float8_e5m2)
 _FP4 = (torch.float4_e2m1fn_x2, torch.uint8)  # the reference reads uint8 operands as raw packed FP4
 
 
+def as_packed_fp4(t):
+    """A ``uint8`` A / B operand is raw packed FP4 (two E2M1 values per byte), as in the reference
+    (``interpret_uint8_as_fp4x2``, python/cudnn/api_base.py:602-609): seen as ``float4_e2m1fn_x2`` from here on.
+    Anything else passes through."""
+    if isinstance(t, torch.Tensor) and t.dtype == torch.uint8:
+        return t.view(torch.float4_e2m1fn_x2)
+    return t
+
+
+def packed_fp4_dtype(dtype):
+    """The dtype counterpart of :func:`as_packed_fp4` (for ``b_dtype`` of the discrete-weight forms)."""
+    return torch.float4_e2m1fn_x2 if dtype == torch.uint8 else dtype
+
+
 class OperatorBase:
     """Common state machine and validators of the operator classes."""
 

@@ -21,7 +21,7 @@ from typing import Optional, Tuple
 import torch
 
 from . import ops
-from .api_base import OperatorBase, TensorSpec, TupleDict, ceil_div, check_tile_and_cluster, pick_tile_mode
+from .api_base import OperatorBase, TensorSpec, TupleDict, as_packed_fp4, ceil_div, check_tile_and_cluster, packed_fp4_dtype, pick_tile_mode
 from .grouped_gemm_quant import _require_pointer_tensor
 from .grouped_gemm_swiglu import _SF_STRIDE_MSG, _alloc_sfd
 
@@ -58,8 +58,9 @@ class DiscreteGroupedGemmSwigluSm100(OperatorBase):
         b_major: str = "k",
         use_dynamic_sched: bool = False,
     ):
+        b_dtype = packed_fp4_dtype(b_dtype)
         super().__init__()
-        self.a = TensorSpec.of(sample_a, "sample_a")
+        self.a = TensorSpec.of(as_packed_fp4(sample_a), "sample_a")
         self.c = TensorSpec.of(sample_c, "sample_c")
         self.d = TensorSpec.of(sample_d, "sample_d")
         self.sfa = TensorSpec.of(sample_sfa, "sample_sfa")
@@ -157,7 +158,6 @@ class DiscreteGroupedGemmSwigluSm100(OperatorBase):
         if self.bias is not None:
             self._check_stride(self.bias, (1, n), "bias must have stride (1, n)")
             self._check_dtype(self.bias, [torch.bfloat16, torch.float16], "bias")
-        self._not_implemented_error_if(self.ab_dtype == torch.uint8, "uint8 (raw packed FP4) operands are not built: pass float4_e2m1fn_x2 tensors")
         self._not_implemented_error_if(self.sf_dtype == torch.float8_e4m3fn and not fp4, f"E4M3 scale factors go with FP4 operands, got {self.ab_dtype}")
         self._not_implemented_error_if(fp4 and k % 64 != 0, f"FP4 operands need k to be a multiple of 64, got {k}")
         self._not_implemented_error_if(fp4 and self.generate_sfd, "scale-factor generation is built for fp8 operands only")
@@ -202,6 +202,7 @@ class DiscreteGroupedGemmSwigluSm100(OperatorBase):
         prob_tensor: Optional[torch.Tensor] = None,
         current_stream=None,
     ) -> None:
+        a_tensor = as_packed_fp4(a_tensor)
         self._ensure_compiled()
         tensor_m, k = a_tensor.shape[0], a_tensor.shape[1]
         if tensor_m == 0:
@@ -274,6 +275,8 @@ def discrete_grouped_gemm_swiglu_wrapper_sm100(
 ) -> TupleDict:
     """One-shot discrete-weight FC1.  Returns ``TupleDict(c_tensor, d_tensor, d_col_tensor,
     amax_tensor, sfd_row_tensor, sfd_col_tensor)``."""
+    a_tensor = as_packed_fp4(a_tensor)
+    b_dtype = packed_fp4_dtype(b_dtype)
     _require_pointer_tensor(b_ptrs, "b_ptrs")
     l = b_ptrs.shape[0]
     _require_pointer_tensor(sfb_ptrs, "sfb_ptrs", l)

@@ -33,7 +33,7 @@ from typing import Optional, Tuple
 import torch
 
 from . import ops
-from .api_base import OperatorBase, TensorSpec, TupleDict, ceil_div, check_tile_and_cluster, pick_tile_mode
+from .api_base import OperatorBase, TensorSpec, TupleDict, as_packed_fp4, ceil_div, check_tile_and_cluster, packed_fp4_dtype, pick_tile_mode
 
 _SF_STRIDE_MSG = "scale-factor tensors must use the 128x4 layout (32, 4, rest_mn, 4, rest_k, l)"
 
@@ -74,8 +74,8 @@ class GroupedGemmDswigluSm100(OperatorBase):
         self._dw = _discrete or {}
         self.use_dynamic_sched = bool(self._dw.get("use_dynamic_sched", False))
         self._workspace = None
-        self.a = TensorSpec.of(sample_a, "sample_a")
-        self.b = TensorSpec.of(sample_b, "sample_b")
+        self.a = TensorSpec.of(as_packed_fp4(sample_a), "sample_a")
+        self.b = TensorSpec.of(as_packed_fp4(sample_b), "sample_b")
         self.c = TensorSpec.of(sample_c, "sample_c")
         self.d_row = TensorSpec.of(sample_d_row, "sample_d_row")
         self.d_col = TensorSpec.of(sample_d_col, "sample_d_col")
@@ -203,7 +203,6 @@ class GroupedGemmDswigluSm100(OperatorBase):
             raise ValueError(f"expert_cnt must be <= 1024, got {self.expert_cnt}")
 
         # what this build implements of the reference's surface
-        self._not_implemented_error_if(self.ab_dtype == torch.uint8, "uint8 (raw packed FP4) operands are not built: pass float4_e2m1fn_x2 tensors")
         self._not_implemented_error_if(self.c_dtype == torch.float32, "a float32 C is not built (bf16, fp16, E4M3 and E5M2 are)")
         self._not_implemented_error_if(fp4 and k % 64 != 0, f"FP4 operands need k to be a multiple of 64, got {k}")
         self._not_implemented_error_if(fp4 and self.generate_sfd, "scale-factor generation is built for fp8 operands only")
@@ -247,6 +246,8 @@ class GroupedGemmDswigluSm100(OperatorBase):
     ) -> None:
         """Launch on ``current_stream``; allocates nothing.  ``dprob_tensor`` must be zero on entry (the kernel adds
         to it); ``amax_tensor`` ``(l, 2, 1)`` is only ever raised."""
+        a_tensor = as_packed_fp4(a_tensor)
+        b_tensor = as_packed_fp4(b_tensor)
         self._ensure_compiled()
         if a_tensor.shape[0] == 0:
             return
@@ -320,6 +321,8 @@ def grouped_gemm_dswiglu_wrapper_sm100(
     """One-shot dSwiGLU.  Returns ``TupleDict(d_row_tensor, d_col_tensor, dprob_tensor, amax_tensor, sfd_row_tensor,
     sfd_col_tensor)``; ``dprob`` is zeroed here before the launch, amax (16-bit ``d_dtype``) is allocated per cached
     configuration like the reference's (api.py:838-860) and starts at -inf."""
+    a_tensor = as_packed_fp4(a_tensor)
+    b_tensor = as_packed_fp4(b_tensor)
     valid_m = a_tensor.shape[0]
     n, _, l = b_tensor.shape
     if cd_major != "n":
@@ -416,7 +419,7 @@ class DiscreteGroupedGemmDswigluSm100(GroupedGemmDswigluSm100):
             sample_dprob, sample_sfd_row=sample_sfd_row, sample_sfd_col=sample_sfd_col, sample_amax=sample_amax, sample_norm_const=sample_norm_const,
             acc_dtype=acc_dtype, mma_tiler_mn=mma_tiler_mn, cluster_shape_mn=cluster_shape_mn, sf_vec_size=sf_vec_size, vector_f32=vector_f32,
             m_aligned=m_aligned, discrete_col_sfd=discrete_col_sfd, epilogue_op=epilogue_op,
-            _discrete=dict(num_experts=num_experts, b_shape=tuple(b_shape), b_dtype=b_dtype, b_major=b_major, use_dynamic_sched=use_dynamic_sched),
+            _discrete=dict(num_experts=num_experts, b_shape=tuple(b_shape), b_dtype=packed_fp4_dtype(b_dtype), b_major=b_major, use_dynamic_sched=use_dynamic_sched),
         )  # fmt: skip
         self._value_error_if(act_func not in ("dswiglu", "dgeglu"), f"act_func must be 'dswiglu' or 'dgeglu', got {act_func}")
         self.act_func = act_func
@@ -449,6 +452,7 @@ class DiscreteGroupedGemmDswigluSm100(GroupedGemmDswigluSm100):
         current_stream=None,
     ) -> None:
         """Launch on ``current_stream``; allocates nothing and never reads the pointer values on the host."""
+        a_tensor = as_packed_fp4(a_tensor)
         from .discrete_grouped_gemm_swiglu import _require_pointer_tensor
 
         if dbias_tensor is not None:
@@ -496,6 +500,8 @@ def discrete_grouped_gemm_dswiglu_wrapper_sm100(
     """One-shot discrete-weight dSwiGLU.  The caller owns ``dprob_tensor`` (zeroed by the caller, as in the reference).
     Returns ``TupleDict(d_row_tensor, d_col_tensor, dprob_tensor, dbias_tensor, amax_tensor, sfd_row_tensor,
     sfd_col_tensor)``."""
+    a_tensor = as_packed_fp4(a_tensor)
+    b_dtype = packed_fp4_dtype(b_dtype)
     from .discrete_grouped_gemm_swiglu import _require_pointer_tensor
 
     if generate_dbias:

@@ -22,7 +22,7 @@ from typing import Optional, Tuple
 
 import torch
 
-from .api_base import OperatorBase, TupleDict
+from .api_base import OperatorBase, TupleDict, as_packed_fp4, packed_fp4_dtype
 from .discrete_grouped_gemm_swiglu import DiscreteGroupedGemmSwigluSm100
 from .grouped_gemm_quant import _require_pointer_tensor
 from .grouped_gemm_swiglu import GroupedGemmSwigluSm100, _alloc_sfd
@@ -174,6 +174,9 @@ def grouped_gemm_glu_wrapper_sm100(
     ``sfb_ptrs``, ``n`` and ``b_dtype``.  Allocates the outputs, reuses a cached operator per
     configuration and returns ``TupleDict(c_tensor, d_tensor, d_col_tensor, amax_tensor,
     sfd_row_tensor, sfd_col_tensor)``."""
+    a_tensor = as_packed_fp4(a_tensor)
+    b_tensor = as_packed_fp4(b_tensor)
+    b_dtype = packed_fp4_dtype(b_dtype)
     dense = b_tensor is not None
     discrete = b_ptrs is not None
     if dense and discrete:

@@ -27,7 +27,7 @@ from typing import Optional, Tuple
 import torch
 
 from . import ops
-from .api_base import OperatorBase, TensorSpec, TupleDict, ceil_div, check_tile_and_cluster, pick_tile_mode
+from .api_base import OperatorBase, TensorSpec, TupleDict, as_packed_fp4, ceil_div, check_tile_and_cluster, packed_fp4_dtype, pick_tile_mode
 from .grouped_gemm_swiglu import _SF_STRIDE_MSG, _alloc_sfd
 
 _logger = logging.getLogger(__name__)
@@ -78,7 +78,7 @@ class GroupedGemmQuantSm100(OperatorBase):
         use_dynamic_sched: bool = False,
     ):
         super().__init__()
-        self.a = TensorSpec.of(sample_a, "sample_a")
+        self.a = TensorSpec.of(as_packed_fp4(sample_a), "sample_a")
         self.sfa = TensorSpec.of(sample_sfa, "sample_sfa")
         self.padded_offsets = TensorSpec.of(sample_padded_offsets, "sample_padded_offsets")
         self.alpha = TensorSpec.of(sample_alpha, "sample_alpha")
@@ -92,7 +92,7 @@ class GroupedGemmQuantSm100(OperatorBase):
         self.prob = TensorSpec.of(sample_prob, "sample_prob")
         self.discrete = not (sample_b is not None and num_experts is None)
         if not self.discrete:
-            self.b = TensorSpec.of(sample_b, "sample_b")
+            self.b = TensorSpec.of(as_packed_fp4(sample_b), "sample_b")
             self.sfb = TensorSpec.of(sample_sfb, "sample_sfb")
             self.expert_cnt = self.padded_offsets.shape[0]
         else:
@@ -101,7 +101,7 @@ class GroupedGemmQuantSm100(OperatorBase):
             self.b = self.sfb = None
             self.expert_cnt = num_experts
             self.b_shape = tuple(b_shape)
-            self.b_dtype = b_dtype
+            self.b_dtype = packed_fp4_dtype(b_dtype)
             self._value_error_if(
                 self.padded_offsets.shape[0] != self.expert_cnt,
                 f"padded_offsets length ({self.padded_offsets.shape[0]}) must equal num_experts ({self.expert_cnt})",
@@ -219,7 +219,6 @@ class GroupedGemmQuantSm100(OperatorBase):
             # (n, l) with stride (1, n), as the reference demands
             self._check_stride(self.bias, (1, n), "bias must have stride (1, n)")
             self._check_dtype(self.bias, [torch.bfloat16, torch.float16, torch.float32], "bias")
-        self._not_implemented_error_if(self.ab_dtype == torch.uint8, "uint8 (raw packed FP4) operands are not built: pass float4_e2m1fn_x2 tensors")
         self._not_implemented_error_if(self.sf_dtype == torch.float8_e4m3fn and not fp4, f"E4M3 scale factors go with FP4 operands, got {self.ab_dtype}")
         self._not_implemented_error_if(fp4 and k % 64 != 0, f"FP4 operands need k to be a multiple of 64, got {k}")
         self._not_implemented_error_if(fp4 and self.generate_sfd, "scale-factor generation is built for fp8 operands only")
@@ -280,6 +279,8 @@ class GroupedGemmQuantSm100(OperatorBase):
         reference) computes experts ``lo .. hi - 1`` only, on the same full tensors; ``offsets_have_prev`` (not in the
         reference either) says that ``padded_offsets`` is a view one element into a longer array whose element
         before it is the first row of expert 0."""
+        a_tensor = as_packed_fp4(a_tensor)
+        b_tensor = as_packed_fp4(b_tensor)
         self._ensure_compiled()
         tensor_m, k = a_tensor.shape[0], a_tensor.shape[1]
         if tensor_m == 0:
@@ -364,6 +365,9 @@ def grouped_gemm_quant_wrapper_sm100(
 ) -> TupleDict:
     """One-shot FC2.  Returns ``TupleDict(d_tensor, d_col_tensor, amax_tensor, sfd_row_tensor,
     sfd_col_tensor)``; amax (bf16 D) is allocated per call and starts at -inf."""
+    a_tensor = as_packed_fp4(a_tensor)
+    b_tensor = as_packed_fp4(b_tensor)
+    b_dtype = packed_fp4_dtype(b_dtype)
     is_dense = b_tensor is not None
     is_discrete = b_ptrs is not None
     if is_dense and is_discrete:

@@ -12,9 +12,10 @@ Differences a caller can observe:
 * ``c_tensor=None`` in ``execute`` skips the bf16 pre-activation store (the reference always
   writes C);
 * the wrapper allocates scale-factor outputs only for an fp8 ``d_dtype`` (see its docstring);
-* operands are E4M3 / E5M2 with E8M0 scales per 32 elements (MXFP8) or ``float4_e2m1fn_x2`` with E8M0
-  scales per 32 (MXFP4) or E8M0 / E4M3 scales per 16 (NVFP4); raw ``uint8`` FP4 operands, FP4 / FP8 / float32
-  C, an FP4 D and k that is not a multiple of 64 with FP4 operands raise ``NotImplementedError``.
+* operands are E4M3 / E5M2 with E8M0 scales per 32 elements (MXFP8) or ``float4_e2m1fn_x2`` (or, as in the
+  reference, the same bytes as ``uint8``) with E8M0 scales per 32 (MXFP4) or E8M0 / E4M3 scales per 16 (NVFP4);
+  FP4 / FP8 / float32 C, an FP4 D and k that is not a multiple of 64 with FP4 operands raise
+  ``NotImplementedError``.
 """
 
 from __future__ import annotations
@@ -26,7 +27,7 @@ from typing import Optional, Tuple
 import torch
 
 from . import ops
-from .api_base import OperatorBase, TensorSpec, TupleDict, ceil_div, check_tile_and_cluster, pick_tile_mode
+from .api_base import OperatorBase, TensorSpec, TupleDict, as_packed_fp4, ceil_div, check_tile_and_cluster, packed_fp4_dtype, pick_tile_mode
 
 _logger = logging.getLogger(__name__)
 
@@ -70,8 +71,8 @@ class GroupedGemmSwigluSm100(OperatorBase):
         super().__init__()
         self.bias = TensorSpec.of(sample_bias, "sample_bias")
         self.act_func = act_func
-        self.a = TensorSpec.of(sample_a, "sample_a")
-        self.b = TensorSpec.of(sample_b, "sample_b")
+        self.a = TensorSpec.of(as_packed_fp4(sample_a), "sample_a")
+        self.b = TensorSpec.of(as_packed_fp4(sample_b), "sample_b")
         self.c = TensorSpec.of(sample_c, "sample_c")
         self.d = TensorSpec.of(sample_d, "sample_d")
         self.sfa = TensorSpec.of(sample_sfa, "sample_sfa")
@@ -183,7 +184,6 @@ class GroupedGemmSwigluSm100(OperatorBase):
         self._not_implemented_error_if(fp4 and self.c is not None and self.c_dtype not in (torch.float16, torch.bfloat16), f"Invalid configuration: for fp4 ab_dtype, c_dtype must be float16 or bfloat16, got {self.c_dtype}")
 
         # what this build implements of the reference's surface
-        self._not_implemented_error_if(self.ab_dtype == torch.uint8, "uint8 (raw packed FP4) operands are not built: pass float4_e2m1fn_x2 tensors")
         self._not_implemented_error_if(self.sf_dtype == torch.float8_e4m3fn and not fp4, f"E4M3 scale factors go with FP4 operands, got {self.ab_dtype}")
         self._not_implemented_error_if(fp4 and k % 64 != 0, f"FP4 operands need k to be a multiple of 64, got {k}")
         self._not_implemented_error_if(fp4 and self.generate_sfd, "scale-factor generation is built for fp8 operands only")
@@ -240,6 +240,8 @@ class GroupedGemmSwigluSm100(OperatorBase):
         (not in the reference) computes experts ``lo .. hi - 1`` only, on the same full tensors; ``offsets_have_prev`` (not in the
         reference either) says that ``padded_offsets`` is a view one element into a longer array whose element
         before it is the first row of expert 0."""
+        a_tensor = as_packed_fp4(a_tensor)
+        b_tensor = as_packed_fp4(b_tensor)
         self._ensure_compiled()
         tensor_m = a_tensor.shape[0]
         if tensor_m == 0:
@@ -319,6 +321,8 @@ def grouped_gemm_swiglu_wrapper_sm100(
     plain bf16 / fp16 D plus amax instead of an error.  As in the reference, the amax buffer of a
     cached configuration is reused across calls: it holds a running maximum until the caller
     resets it."""
+    a_tensor = as_packed_fp4(a_tensor)
+    b_tensor = as_packed_fp4(b_tensor)
     valid_m, k, _ = a_tensor.shape
     n, _, l = b_tensor.shape
     n_out = n // 2

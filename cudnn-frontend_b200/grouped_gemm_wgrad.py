@@ -22,7 +22,7 @@ from typing import Optional, Tuple
 import torch
 
 from . import ops
-from .api_base import OperatorBase, TensorSpec, TupleDict, ceil_div, is_power_of_2
+from .api_base import OperatorBase, TensorSpec, TupleDict, as_packed_fp4, ceil_div, is_power_of_2
 
 
 def _round_up(a: int, b: int) -> int:
@@ -59,8 +59,8 @@ class GroupedGemmWgradSm100(OperatorBase):
                 raise ValueError("wgrad_shape and wgrad_dtype are required in discrete mode")
         else:
             raise ValueError("Provide either sample_wgrad for dense mode or (num_experts, wgrad_shape, wgrad_dtype) for discrete mode, but not both")
-        self.a = TensorSpec.of(sample_a, "sample_a")
-        self.b = TensorSpec.of(sample_b, "sample_b")
+        self.a = TensorSpec.of(as_packed_fp4(sample_a), "sample_a")
+        self.b = TensorSpec.of(as_packed_fp4(sample_b), "sample_b")
         self.sfa = TensorSpec.of(sample_sfa, "sample_sfa")
         self.sfb = TensorSpec.of(sample_sfb, "sample_sfb")
         self.offsets = TensorSpec.of(sample_offsets, "sample_offsets")
@@ -153,6 +153,8 @@ class GroupedGemmWgradSm100(OperatorBase):
     ) -> None:
         """Launch on ``current_stream``; allocates nothing.  The token count may differ from the sample's (it is read
         from ``a_tensor``)."""
+        a_tensor = as_packed_fp4(a_tensor)
+        b_tensor = as_packed_fp4(b_tensor)
         self._ensure_compiled()
         if not self.discrete and wgrad_tensor is None:
             raise ValueError("wgrad_tensor is required in dense mode")
@@ -192,6 +194,8 @@ def grouped_gemm_wgrad_wrapper_sm100(
 ) -> TupleDict:
     """One-shot weight gradient.  Returns ``TupleDict(wgrad_tensor)``; the output is allocated here when the caller
     passes none (zeros with ``accumulate_on_output``, as in the reference, api.py:587-592)."""
+    a_tensor = as_packed_fp4(a_tensor)
+    b_tensor = as_packed_fp4(b_tensor)
     if output_mode not in ("dense", "discrete"):
         raise ValueError(f"output_mode must be 'dense' or 'discrete', got {output_mode}")
     hidden = a_tensor.shape[0]

@@ -140,6 +140,32 @@ def test_fp4_rejections():
         cf.grouped_gemm_swiglu_wrapper_sm100(*args, d_dtype=torch.bfloat16, sf_vec_size=32, m_aligned=128)
 
 
+def test_uint8_operands_are_raw_packed_fp4(tile_mode):
+    """The reference reads uint8 A / B as raw packed FP4 (python/cudnn/api_base.py:602-609): the same bytes as uint8
+    tensors give the same C and D as float4_e2m1fn_x2 tensors, through the wrapper and through the class."""
+    import cudnn_frontend_b200 as cf
+
+    valid, n, k, e = 256, 256, 512, 2
+    a, b, sfa, sfb = H.gen_operands_fp4(5, valid, n, k, e, 16, "e4m3")
+    ta, tb = _fp4(a, (valid, k // 2, 1)), _fp4(b, (e, n, k // 2)).permute(1, 2, 0)
+    rest = (H.dev_sf(sfa, valid, k, 1, sf_vec=16, dtype=torch.float8_e4m3fn), H.dev_sf(sfb, n, k, e, sf_vec=16, dtype=torch.float8_e4m3fn),
+            torch.tensor([128, 256], dtype=torch.int32, device="cuda"), torch.ones(e, device="cuda"))  # fmt: skip
+    kw = dict(d_dtype=torch.bfloat16, sf_vec_size=16, m_aligned=128)
+    want = cf.grouped_gemm_swiglu_wrapper_sm100(ta, tb, *rest, **kw)
+    got = cf.grouped_gemm_swiglu_wrapper_sm100(ta.view(torch.uint8), tb.view(torch.uint8), *rest, **kw)
+    torch.cuda.synchronize()
+    for key in ("c_tensor", "d_tensor", "amax_tensor"):
+        assert torch.equal(want[key], got[key]), key
+    c, d = torch.empty_like(want["c_tensor"]), torch.empty_like(want["d_tensor"])
+    amax = torch.full((e, 1), float("-inf"), device="cuda")
+    op = cf.GroupedGemmSwigluSm100(ta.view(torch.uint8), tb.view(torch.uint8), c, d, *rest, None, sample_amax=amax, sf_vec_size=16, m_aligned=128)
+    assert op.check_support()
+    op.compile()
+    op.execute(ta.view(torch.uint8), tb.view(torch.uint8), c, d, *rest, amax_tensor=amax)
+    torch.cuda.synchronize()
+    assert torch.equal(c, want["c_tensor"]) and torch.equal(d, want["d_tensor"])
+
+
 @pytest.mark.parametrize("fixture", ["reference_kernel_fc1_fp4_nvfp4.npz", "reference_kernel_fc1_fp4_mxfp4.npz", "reference_kernel_fc1_fp4_e8m0x16.npz"])
 def test_fc1_fp4_is_bit_identical_to_the_reference_kernel_fixture(golden_dir, tile_mode, fixture):
     """Inputs and outputs of cudnn-frontend's GroupedGemmSwigluSm100 with float4_e2m1fn_x2 operands (bf16 C and

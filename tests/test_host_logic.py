@@ -97,9 +97,10 @@ def test_fc1_check_support_error_classes():
         cf.GroupedGemmSwigluSm100(**ok, sf_vec_size=32, m_aligned=192).check_support()
     with pytest.raises(ValueError, match="cluster"):
         cf.GroupedGemmSwigluSm100(**ok, sf_vec_size=32, cluster_shape_mn=(3, 1)).check_support()
-    # raw uint8 FP4 operands (the reference reads uint8 as packed FP4) are not built; float4_e2m1fn_x2 is
+    # uint8 operands are raw packed FP4, as in the reference: the fp8 samples of this case then no longer fit (K
+    # doubles and the scale tensors are too short)
     bad = dict(ok, sample_a=torch.empty((256, 128, 1), dtype=torch.uint8), sample_b=ok["sample_b"].view(torch.uint8))
-    with pytest.raises(NotImplementedError):
+    with pytest.raises(ValueError):
         cf.GroupedGemmSwigluSm100(**bad, sf_vec_size=32).check_support()
     bad = dict(ok, sample_a=torch.empty((256, 128, 1), dtype=torch.float8_e5m2))  # A and B must agree
     with pytest.raises(ValueError):
@@ -319,6 +320,15 @@ def test_fp4_operands_are_validated_on_their_logical_shape():
     if not torch.cuda.is_available():  # a valid NVFP4 configuration gets as far as the device check
         with pytest.raises(RuntimeError, match="CUDA"):
             cf.GroupedGemmSwigluSm100(**common, sample_d=torch.empty((m, n // 2, 1), dtype=torch.bfloat16), sf_vec_size=16).check_support()
+    # the same operands as raw uint8 bytes (the reference's interpret_uint8_as_fp4x2) are the same configuration
+    raw = dict(common, sample_a=a.view(torch.uint8), sample_b=b.view(torch.uint8))
+    op = cf.GroupedGemmSwigluSm100(**raw, sample_d=torch.empty((m, n // 2, 1), dtype=torch.bfloat16), sf_vec_size=16)
+    assert op.a.dtype == torch.float4_e2m1fn_x2 and op.b.dtype == torch.float4_e2m1fn_x2
+    with pytest.raises(NotImplementedError, match="float32"):
+        cf.GroupedGemmSwigluSm100(**raw, sample_d=torch.empty((m, n // 2, 1), dtype=torch.float32), sf_vec_size=16).check_support()
+    if not torch.cuda.is_available():
+        with pytest.raises(RuntimeError, match="CUDA"):
+            op.check_support()
 
 
 def test_dswiglu_and_wgrad_check_support_error_classes():
